@@ -1,0 +1,117 @@
+// Row-wise kernels around the matrix products: embedding gather, residual add
+// fused with RMSNorm, SiLU(gate)*up.  All arithmetic is float32; only loads
+// and stores use the storage type.
+//
+// Formulas (PrefixServe prefixserve/model/llama.py): embedding :109, RMSNorm
+// :63-69 (mean of squares, rsqrt(mean+eps), then times the gain), residual
+// sums :117,:121, SiLU-gated product :121.
+#include "common.cuh"
+
+namespace {
+
+template <typename TT>
+__global__ void embedding_kernel(const int32_t* __restrict__ ids, const TT* __restrict__ table,
+                                 float* __restrict__ out, int H, int V) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  // ids are validated on the host; clamp so that a bad one can never read outside the table
+  id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+  const TT* row = table + (size_t)id * H;
+  float* o = out + (size_t)t * H;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) o[j] = to_float<TT>(row[j]);
+}
+
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  v = warp_sum(v);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  // every thread adds the partials in the same order: the result does not depend on the batch
+  float total = 0.f;
+  for (int w = 0; w < nwarp; ++w) total += scratch[w];
+  __syncthreads();
+  return total;
+}
+
+// x[i] = gain * ((h[r] + delta[r]) * rsqrt(mean((h[r]+delta[r])^2) + eps));  r = rows ? rows[i] : i.
+// With update_h the sum is stored back into h[r] (float32 residual stream).
+template <typename TD, typename TX>
+__global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ delta, const float* __restrict__ gain,
+                                   const int32_t* __restrict__ rows, TX* __restrict__ x, int H, float eps, int update_h) {
+  __shared__ float scratch[32];
+  const int i = blockIdx.x;
+  const int r = rows ? rows[i] : i;
+  float* hr = h + (size_t)r * H;
+  const TD* dr = delta ? delta + (size_t)r * H : nullptr;
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) {
+    float v = hr[j];
+    if (dr) v += to_float<TD>(dr[j]);
+    ss += v * v;
+  }
+  const float total = block_sum(ss, scratch);
+  const float inv = rsqrtf(total / (float)H + eps);
+  TX* xr = x + (size_t)i * H;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) {
+    float v = hr[j];
+    if (dr) v += to_float<TD>(dr[j]);
+    if (update_h && dr) hr[j] = v;
+    xr[j] = from_float<TX>(gain[j] * (v * inv));
+  }
+}
+
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const size_t t = idx / (size_t)I;
+  const int j = (int)(idx - t * (size_t)I);
+  const float g = to_float<T>(gu[t * 2 * (size_t)I + j]);
+  const float u = to_float<T>(gu[t * 2 * (size_t)I + I + j]);
+  const float s = g / (1.f + expf(-g));
+  out[idx] = from_float<T>(s * u);
+}
+
+}  // namespace
+
+PSB_API int psb_embedding(const void* ids, const void* table, int table_dtype, void* out, int T, int H, int V,
+                          cudaStream_t stream) {
+  if (T < 0 || H < 1 || V < 1) PSB_REFUSE("embedding: bad sizes T=%d H=%d V=%d", T, H, V);
+  if (T == 0) return 0;
+  const int threads = H >= 1024 ? 256 : 128;
+  PSB_DISPATCH_DTYPE(table_dtype, TT, {
+    embedding_kernel<TT><<<T, threads, 0, stream>>>((const int32_t*)ids, (const TT*)table, (float*)out, H, V);
+  });
+  PSB_LAUNCH_CHECK("embedding");
+  return 0;
+}
+
+PSB_API int psb_add_rmsnorm(void* h, const void* delta, int delta_dtype, const void* gain, const void* rows, void* x,
+                            int x_dtype, int n_rows, int H, float eps, int update_h, cudaStream_t stream) {
+  if (n_rows < 0 || H < 1) PSB_REFUSE("add_rmsnorm: bad sizes rows=%d H=%d", n_rows, H);
+  if (!(eps > 0.f)) PSB_REFUSE("add_rmsnorm: eps must be positive");
+  if (n_rows == 0) return 0;
+  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  PSB_DISPATCH_DTYPE(delta_dtype, TD, {
+    PSB_DISPATCH_DTYPE(x_dtype, TX, {
+      add_rmsnorm_kernel<TD, TX><<<n_rows, threads, 0, stream>>>((float*)h, (const TD*)delta, (const float*)gain,
+                                                                 (const int32_t*)rows, (TX*)x, H, eps, update_h);
+    });
+  });
+  PSB_LAUNCH_CHECK("add_rmsnorm");
+  return 0;
+}
+
+PSB_API int psb_silu_mul(const void* gate_up, int dtype, void* out, int T, int I, cudaStream_t stream) {
+  if (T < 0 || I < 1) PSB_REFUSE("silu_mul: bad sizes T=%d I=%d", T, I);
+  if (T == 0) return 0;
+  const size_t total = (size_t)T * I;
+  const int threads = 256;
+  const size_t blocks = (total + threads - 1) / threads;
+  if (blocks > 0x7fffffffull) PSB_REFUSE("silu_mul: too many elements");
+  PSB_DISPATCH_DTYPE(dtype, T_, {
+    silu_mul_kernel<T_><<<(unsigned)blocks, threads, 0, stream>>>((const T_*)gate_up, (T_*)out, I, total);
+  });
+  PSB_LAUNCH_CHECK("silu_mul");
+  return 0;
+}

@@ -1,0 +1,102 @@
+// Rotary position encoding fused with the append of new keys and values to
+// the paged cache.
+//
+// Input is the fused projection output [T, (hq + 2*hkv) * D] (queries, then
+// keys, then values).  Queries are rotated into q_out [T, hq, D]; keys are
+// rotated and, with the values, stored at their absolute position in the
+// request's pages, so attention afterwards reads everything from the cache.
+// Rotation is the split-half form: with x = (x1, x2) the halves of a head,
+//   out = (x1*cos - x2*sin, x2*cos + x1*sin)
+// (prefixserve/model/llama.py:72-77), angles indexed by ABSOLUTE position
+// (prefixserve/llama_engine.py:190-193); the tables are float32 and hold D/2
+// angles per position.  Destination of token at position p: page
+// table[item][p / page_size], slot p % page_size
+// (prefixserve/model/attention.py:14-16, :95-106).
+//
+// Cache layout of one entry: [num_pages, 2, hkv, page_size, D].
+#include "common.cuh"
+
+namespace {
+
+template <typename T, typename TKV>
+__global__ void rope_append_kernel(const T* __restrict__ qkv, const int32_t* __restrict__ positions,
+                                   const int32_t* __restrict__ token_item, const float* __restrict__ cos_t,
+                                   const float* __restrict__ sin_t, const int32_t* __restrict__ table, int table_width,
+                                   TKV* __restrict__ kv, T* __restrict__ q_out, int hq, int hkv, int D, int page_size,
+                                   int num_pages, int max_positions, int rotate, int write_kv) {
+  const int t = blockIdx.x;
+  const int half = D >> 1;
+  const int pos = positions[t];
+  const int heads_in = hq + 2 * hkv;
+  const T* row = qkv + (size_t)t * heads_in * D;
+  const int safe_pos = pos < 0 ? 0 : (pos >= max_positions ? max_positions - 1 : pos);
+  const float* c = cos_t + (size_t)safe_pos * half;
+  const float* s = sin_t + (size_t)safe_pos * half;
+
+  TKV* kdst = nullptr;
+  TKV* vdst = nullptr;
+  if (write_kv) {
+    const int item = token_item[t];
+    const int page = table[(size_t)item * table_width + pos / page_size];
+    // the host checks tables before launch; a bad id is skipped rather than written through
+    if (page >= 0 && page < num_pages) {
+      const size_t page_elems = (size_t)2 * hkv * page_size * D;
+      kdst = kv + (size_t)page * page_elems + (size_t)(pos % page_size) * D;
+      vdst = kdst + (size_t)hkv * page_size * D;
+    }
+  }
+  // rotated heads: queries then keys
+  const int rot_heads = write_kv ? hq + hkv : hq;
+  for (int idx = threadIdx.x; idx < rot_heads * half; idx += blockDim.x) {
+    const int head = idx / half, j = idx - head * half;
+    const float x1 = to_float<T>(row[head * D + j]);
+    const float x2 = to_float<T>(row[head * D + j + half]);
+    float o1 = x1, o2 = x2;
+    if (rotate) {
+      const float cs = c[j], sn = s[j];
+      o1 = x1 * cs - x2 * sn;
+      o2 = x2 * cs + x1 * sn;
+    }
+    if (head < hq) {
+      T* q = q_out + ((size_t)t * hq + head) * D;
+      q[j] = from_float<T>(o1);
+      q[j + half] = from_float<T>(o2);
+    } else if (kdst) {
+      TKV* k = kdst + (size_t)(head - hq) * page_size * D;
+      k[j] = from_float<TKV>(o1);
+      k[j + half] = from_float<TKV>(o2);
+    }
+  }
+  if (vdst) {
+    const T* vrow = row + (size_t)(hq + hkv) * D;
+    for (int idx = threadIdx.x; idx < hkv * D; idx += blockDim.x) {
+      const int head = idx / D, j = idx - head * D;
+      vdst[(size_t)head * page_size * D + j] = from_float<TKV>(to_float<T>(vrow[idx]));
+    }
+  }
+}
+
+}  // namespace
+
+PSB_API int psb_rope_append(const void* qkv, int dtype, const void* positions, const void* token_item, const void* cos_t,
+                            const void* sin_t, const void* table, int table_width, void* kv, int kv_dtype, void* q_out,
+                            int T, int hq, int hkv, int D, int page_size, int num_pages, int max_positions, int rotate,
+                            int write_kv, cudaStream_t stream) {
+  if (T < 0 || hq < 1 || hkv < 0 || D < 2 || (D & 1)) PSB_REFUSE("rope_append: bad sizes T=%d hq=%d hkv=%d D=%d", T, hq, hkv, D);
+  if (write_kv && (page_size < 1 || num_pages < 1 || table_width < 1 || !kv || !table || hkv < 1))
+    PSB_REFUSE("rope_append: cache arguments missing (page_size=%d num_pages=%d width=%d)", page_size, num_pages, table_width);
+  if (rotate && (!cos_t || !sin_t || max_positions < 1)) PSB_REFUSE("rope_append: angle tables missing");
+  if (T == 0) return 0;
+  const int work = (hq + hkv) * (D / 2);
+  const int threads = work >= 1024 ? 256 : 128;
+  PSB_DISPATCH_DTYPE(dtype, T_, {
+    PSB_DISPATCH_DTYPE(kv_dtype, TKV, {
+      rope_append_kernel<T_, TKV><<<T, threads, 0, stream>>>(
+          (const T_*)qkv, (const int32_t*)positions, (const int32_t*)token_item, (const float*)cos_t, (const float*)sin_t,
+          (const int32_t*)table, table_width, (TKV*)kv, (T_*)q_out, hq, hkv, D, page_size, num_pages, max_positions, rotate,
+          write_kv);
+    });
+  });
+  PSB_LAUNCH_CHECK("rope_append");
+  return 0;
+}

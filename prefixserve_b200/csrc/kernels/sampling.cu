@@ -1,0 +1,91 @@
+// Token choice from float32 logits: one block per row.
+//
+// temperature == 0: arg max, the lowest index winning ties (the reference's
+// only mode, torch.argmax at prefixserve/llama_engine.py:146).
+// temperature > 0: sampling from softmax(logits / temperature) by the
+// Gumbel-max rule, token = argmax_i(logits[i] / temperature + g_i) with
+// g_i = -log(-log(u_i)) and u_i drawn from a counter-based generator keyed by
+// (request seed, absolute position of the new token, i).  The draw therefore
+// does not depend on what else is in the batch, on how the prompt was cut, or
+// on a recomputation after preemption.
+#include <cfloat>
+
+#include "common.cuh"
+
+namespace {
+
+__host__ __device__ __forceinline__ uint64_t mix64(uint64_t z) {
+  z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ULL;
+  z = (z ^ (z >> 27)) * 0x94d049bb133111ebULL;
+  return z ^ (z >> 31);
+}
+
+// uniform in (0, 1) with 24 random bits
+__device__ __forceinline__ float uniform01(uint64_t seed, uint32_t position, uint32_t index) {
+  const uint64_t a = mix64(seed + 0x9e3779b97f4a7c15ULL * ((uint64_t)position + 1));
+  const uint64_t r = mix64(a ^ (0xd1b54a32d192ed03ULL * ((uint64_t)index + 1)));
+  return ((float)(uint32_t)(r >> 40) + 0.5f) * (1.0f / 16777216.0f);
+}
+
+__global__ void sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
+                              const int64_t* __restrict__ seed, const int32_t* __restrict__ position,
+                              int32_t* __restrict__ out, int V) {
+  __shared__ float best_v[32];
+  __shared__ int best_i[32];
+  const int row = blockIdx.x;
+  const float* x = logits + (size_t)row * V;
+  const float tau = temperature ? temperature[row] : 0.f;
+  float bv = -FLT_MAX;
+  int bi = 0x7fffffff;
+  if (tau > 0.f) {
+    const uint64_t sd = (uint64_t)seed[row];
+    const uint32_t pos = (uint32_t)position[row];
+    const float inv_tau = 1.f / tau;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float u = uniform01(sd, pos, (uint32_t)i);
+      const float v = x[i] * inv_tau - logf(-logf(u));
+      if (v > bv) { bv = v; bi = i; }   // strided scan keeps the lowest index of equal values
+    }
+  } else {
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float v = x[i];
+      if (v > bv) { bv = v; bi = i; }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { best_v[warp] = bv; best_i[warp] = bi; }
+  __syncthreads();
+  if (warp == 0) {
+    const int nwarp = blockDim.x >> 5;
+    bv = lane < nwarp ? best_v[lane] : -FLT_MAX;
+    bi = lane < nwarp ? best_i[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    // a row of NaNs (or of -FLT_MAX) never beats the initial value: answer 0 rather than an invalid id
+    if (lane == 0) out[row] = bi == 0x7fffffff ? 0 : bi;
+  }
+}
+
+}  // namespace
+
+PSB_API int psb_sample(const void* logits, const void* temperature, const void* seed, const void* position, void* out,
+                       int S, int V, cudaStream_t stream) {
+  if (S < 0 || V < 1) PSB_REFUSE("sample: bad sizes S=%d V=%d", S, V);
+  if (temperature && (!seed || !position)) PSB_REFUSE("sample: temperature given without seed and position");
+  if (S == 0) return 0;
+  const int threads = V >= 16384 ? 1024 : (V >= 1024 ? 256 : 64);
+  sample_kernel<<<S, threads, 0, stream>>>((const float*)logits, (const float*)temperature, (const int64_t*)seed,
+                                          (const int32_t*)position, (int32_t*)out, V);
+  PSB_LAUNCH_CHECK("sample");
+  return 0;
+}

@@ -1,0 +1,136 @@
+"""The engine: a model folder, a cache and the step function, driven by batches
+of the scheduler.
+
+Mirrors what the reference's engine offers a driver
+(prefixserve/engine.py:10-29, prefixserve/llama_engine.py:46-150):
+``num_blocks``, ``max_seq_len``, ``stop_token_ids`` and a blocking
+``step(batch) -> {request id: token}``; the pool is sized from free memory
+after a worst-case trial step when ``num_blocks`` is not given
+(prefixserve/llama_engine.py:231-267).
+"""
+
+from __future__ import annotations
+
+import gc
+import logging
+from dataclasses import dataclass
+from pathlib import Path
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager, pages_for
+from ..sampling.sampler import choose_tokens
+from .loading import load_model, parse_dtype
+from .scheduler import Batch
+from .step import EngineError, ModelRunner, StepItem
+
+log = logging.getLogger(__name__)
+
+
+@dataclass(frozen=True)
+class EngineConfig:
+    model_path: Path
+    dtype: torch.dtype = torch.bfloat16
+    device: str = "cuda"
+    max_num_seqs: int = 64           # must match the scheduler's max_decode_seqs
+    max_prefill_tokens: int = 512    # must match the scheduler's budget
+    max_seq_len: int = 8192
+    num_blocks: int | None = None    # None: size the pool from free memory
+    reserve_bytes: int = 1 << 30     # left free after the pool
+    page_size: int = 16
+    enable_prefix_cache: bool = True
+
+
+class Engine:
+    def __init__(self, cfg: EngineConfig) -> None:
+        self.cfg = cfg
+        self.device = torch.device(cfg.device)
+        if self.device.type != "cuda" or not torch.cuda.is_available():
+            raise EngineError("no CUDA device: this engine has no CPU path")
+        dtype = parse_dtype(cfg.dtype)
+        self.arch, self.model_cfg, self.model = load_model(cfg.model_path, dtype=dtype, device=self.device,
+                                                           max_positions=cfg.max_seq_len)
+        if cfg.max_seq_len > self.model.spec.max_positions:
+            raise ValueError(f"max_seq_len {cfg.max_seq_len} exceeds the model's {self.model.spec.max_positions} positions")
+        self.dtype = dtype
+        self.needs = self.model.cache_needs()
+        self.bytes_per_block = CacheManager.bytes_per_page(self.needs, cfg.page_size, dtype)
+        num_blocks = cfg.num_blocks if cfg.num_blocks is not None else self._size_pool()
+        self.cache = self._make_cache(num_blocks)
+        self.runner = ModelRunner(self.model, self.cache, device=self.device)
+        self.capture_logits = False
+        self.last_logits: dict[str, torch.Tensor] = {}
+        log.info("cache: %d pages of %d tokens (%.2f GB)", num_blocks, cfg.page_size, num_blocks * self.bytes_per_block / 1e9)
+
+    def _make_cache(self, num_blocks: int) -> CacheManager:
+        return CacheManager(self.needs, num_pages=num_blocks, num_slots=self.cfg.max_num_seqs,
+                            max_seq_len=self.cfg.max_seq_len, page_size=self.cfg.page_size, dtype=self.dtype,
+                            device=self.device, enable_prefix_cache=self.cfg.enable_prefix_cache)
+
+    # ---- what a driver needs ------------------------------------------------
+    @property
+    def num_blocks(self) -> int:
+        return self.cache.num_pages(0)
+
+    @property
+    def max_seq_len(self) -> int:
+        return self.cfg.max_seq_len
+
+    @property
+    def stop_token_ids(self) -> frozenset[int]:
+        return self.model.spec.stop_token_ids
+
+    @torch.inference_mode()
+    def step(self, batch: Batch) -> dict[str, int]:
+        """Runs one batch of the scheduler; returns request id -> next token for the items that sample."""
+        work = batch.work
+        if not work:
+            return {}
+        if len(work) > self.cfg.max_num_seqs or batch.num_tokens > self.cfg.max_prefill_tokens + self.cfg.max_num_seqs:
+            raise EngineError(f"batch of {len(work)} requests / {batch.num_tokens} tokens is over the engine's limits")
+        items = [StepItem(w.req.slot, w.start, w.req.tokens(w.start, w.end), (w.end - w.start - 1,) if w.samples else ())
+                 for w in work]
+        logits = self.runner.step(items)
+        sampling = [w for w in work if w.samples]
+        if not sampling:
+            return {}  # nothing to read back: the host runs ahead
+        tokens = choose_tokens(logits, [w.req.sampling for w in sampling], [w.end for w in sampling])
+        if self.capture_logits:
+            self.last_logits = {w.req.req_id: logits[i].cpu() for i, w in enumerate(sampling)}
+        return {w.req.req_id: tok for w, tok in zip(sampling, tokens.tolist())}  # the step's one device-to-host read
+
+    # ---- pool sizing ----------------------------------------------------------
+    def _size_pool(self) -> int:
+        """Pages that fit beside the weights and the activations of a worst-case step."""
+        cfg = self.cfg
+        prefill = min(cfg.max_prefill_tokens, cfg.max_seq_len)
+        trial_pages = pages_for(prefill, cfg.page_size) + cfg.max_num_seqs
+        torch.cuda.synchronize()
+        gc.collect()
+        torch.cuda.empty_cache()
+        torch.cuda.reset_peak_memory_stats()
+        before = torch.cuda.memory_allocated()
+        cache = self._make_cache(trial_pages)
+        runner = ModelRunner(self.model, cache, device=self.device)
+        held = torch.cuda.memory_allocated() - before
+        items = []
+        for i in range(cfg.max_num_seqs):
+            n = prefill if i == 0 else 1
+            slot = cache.open()
+            cache.reserve(slot, n)
+            items.append(StepItem(slot, 0, np.zeros(n, dtype=np.int32), (n - 1,)))
+        runner.step(items)
+        torch.cuda.synchronize()
+        activations = torch.cuda.max_memory_allocated() - before - held
+        del cache, runner
+        gc.collect()
+        torch.cuda.empty_cache()
+        free, _ = torch.cuda.mem_get_info()
+        usable = free - activations - cfg.reserve_bytes
+        n = int(usable // self.bytes_per_block)
+        need = pages_for(cfg.max_seq_len, cfg.page_size)
+        if n < need:
+            raise EngineError(f"only {n} cache pages fit ({usable / 1e9:.2f} GB usable); one request of max_seq_len needs {need}")
+        log.info("trial step: activations %.0f MB, %.2f GB free -> %d pages", activations / 1e6, free / 1e9, n)
+        return n

@@ -1,0 +1,416 @@
+"""Continuous batching: who runs in the next step, with how many tokens.
+
+Rules, after the reference's scheduler (prefixserve/scheduler.py:143-451):
+
+* A request is its token list (prompt + generated) and a count of tokens whose
+  keys and values are in the cache.  A step gives it the next portion of the
+  uncomputed tail; when the portion reaches the end of the list a token is
+  sampled.  One token left = decode; more = prefill; after a preemption the
+  same path recomputes.
+* Running requests are served oldest first.  Decodes always run and cost no
+  budget; portions of prompts share ``max_prefill_tokens`` per step and are at
+  most ``chunk_size`` long; a prompt whose budget is used up waits a step.
+* Waiting requests are admitted first-come-first-served while fewer than
+  ``max_decode_seqs`` run.  Admission matches the longest cached prefix of all
+  but the last token, takes pages for the first portion only, may evict cached
+  pages but never preempts; if the head of the queue cannot start, nobody
+  behind it does.
+* When a running request needs pages and none are free: evict unused cached
+  pages; if that is not enough, preempt the newest running request (its full
+  pages go to the prefix cache, its count returns to zero, it goes to the
+  front of the queue) and try again.  The asker may preempt itself.  The
+  oldest request can always take from newer ones, and add_request refuses
+  anything that could not fit alone, so the oldest always finishes.
+* schedule_step and commit alternate; aborts of running requests that arrive
+  in between take effect at commit.
+"""
+
+from __future__ import annotations
+
+import bisect
+import logging
+import time
+from collections import deque
+from dataclasses import dataclass, field
+from enum import Enum
+from typing import Iterable, Mapping
+
+import numpy as np
+
+from ..cache.manager import CacheManager, pages_for
+from ..parts.base import CacheNeed, PagedKV
+from ..sampling import SamplingParams
+
+log = logging.getLogger(__name__)
+
+DEFAULT_CHUNK_SIZE = 512
+SLOW_STEP_SECONDS = 1e-3
+
+
+class SchedulerError(RuntimeError):
+    """schedule_step/commit were called out of order, or with the wrong batch."""
+
+
+class ReqState(Enum):
+    WAITING = "waiting"
+    RUNNING = "running"
+    FINISHED = "finished"
+
+
+class FinishReason(str, Enum):
+    LENGTH = "length"
+    STOP = "stop"
+    ABORT = "abort"
+
+
+class AddResult(Enum):
+    ACCEPTED = "accepted"
+    QUEUE_FULL = "queue_full"
+    TOO_LONG = "too_long"
+    DUPLICATE_ID = "duplicate_id"
+    INVALID = "invalid"
+
+
+@dataclass(eq=False)
+class Request:
+    req_id: str
+    prompt: np.ndarray
+    max_tokens: int
+    arrival: int
+    ignore_eos: bool = False
+    sampling: SamplingParams = field(default_factory=SamplingParams)
+    state: ReqState = ReqState.WAITING
+    output: list[int] = field(default_factory=list)
+    slot: int | None = None
+    num_computed: int = 0
+    cached_tokens: int = 0
+    num_preemptions: int = 0
+    abort_pending: bool = False
+    prompt_cached: bool = False
+
+    @property
+    def seq_len(self) -> int:
+        return len(self.prompt) + len(self.output)
+
+    def seq(self) -> np.ndarray:
+        if not self.output:
+            return self.prompt
+        return np.concatenate((self.prompt, np.asarray(self.output, dtype=np.int32)))
+
+    def tokens(self, start: int, end: int) -> np.ndarray:
+        """seq()[start:end] without building the whole list."""
+        n = len(self.prompt)
+        if end <= n:
+            return self.prompt[start:end]
+        tail = np.asarray(self.output[max(start - n, 0): end - n], dtype=np.int32)
+        return tail if start >= n else np.concatenate((self.prompt[start:], tail))
+
+
+@dataclass(frozen=True)
+class WorkItem:
+    req: Request
+    start: int
+    end: int
+
+    @property
+    def samples(self) -> bool:
+        return self.end == self.req.seq_len
+
+
+@dataclass(frozen=True)
+class Batch:
+    work: list[WorkItem]
+    preempted: list[str]
+
+    @property
+    def num_tokens(self) -> int:
+        return sum(w.end - w.start for w in self.work)
+
+
+@dataclass(frozen=True)
+class StepResult:
+    new_tokens: dict[str, int]
+    finished: dict[str, FinishReason]
+
+
+@dataclass(frozen=True)
+class SchedulerStats:
+    num_waiting: int
+    num_running: int
+    free_blocks: int
+    cached_blocks: int
+    prompt_tokens: int
+    cached_prompt_tokens: int
+    preemptions: int
+    rejected: int
+
+    @property
+    def prefix_hit_rate(self) -> float:
+        return self.cached_prompt_tokens / self.prompt_tokens if self.prompt_tokens else 0.0
+
+
+def host_only_cache(num_blocks: int, *, page_size: int = 16, num_slots: int = 256, enable_prefix_cache: bool = True,
+                    max_seq_len: int | None = None) -> CacheManager:
+    """Bookkeeping without device tensors: one group of full attention (scheduler tests, simulations)."""
+    need = CacheNeed(paged=PagedKV(num_kv_heads=1, head_dim=1))
+    return CacheManager([need], num_pages=num_blocks, num_slots=num_slots,
+                        max_seq_len=max_seq_len or num_blocks * page_size, page_size=page_size, device=None,
+                        enable_prefix_cache=enable_prefix_cache)
+
+
+class Scheduler:
+    def __init__(
+        self,
+        cache: CacheManager | int,
+        *,
+        max_waiting: int = 1024,
+        chunk_size: int = DEFAULT_CHUNK_SIZE,
+        stop_token_ids: Iterable[int] = (),
+        enable_prefix_cache: bool = True,
+    ) -> None:
+        if max_waiting < 1 or chunk_size < 1:
+            raise ValueError("max_waiting and chunk_size must be >= 1")
+        if isinstance(cache, int):
+            cache = host_only_cache(cache, enable_prefix_cache=enable_prefix_cache)
+        self.cache = cache
+        self._share_prefixes = enable_prefix_cache and cache.tree is not None
+        self._max_waiting = max_waiting
+        self._chunk = chunk_size
+        self._stop = frozenset(int(t) for t in stop_token_ids)
+
+        self._by_id: dict[str, Request] = {}
+        self._waiting: deque[Request] = deque()
+        self._running: list[Request] = []  # by arrival, newest last
+        self._inflight: Batch | None = None
+        self._abort_at_commit: list[Request] = []
+        self._arrivals = 0
+        self._n_prompt = self._n_prompt_cached = self._n_preempt = self._n_rejected = 0
+
+    # ------------------------------------------------------------ interface
+    def add_request(self, req_id: str, prompt, max_tokens: int, *, ignore_eos: bool = False,
+                    sampling: SamplingParams | None = None) -> AddResult:
+        checked = self._vet(req_id, prompt, max_tokens)
+        if isinstance(checked, AddResult):
+            self._n_rejected += 1
+            return checked
+        req = Request(req_id, checked, max_tokens, self._arrivals, ignore_eos, sampling or SamplingParams())
+        self._arrivals += 1
+        self._by_id[req_id] = req
+        self._waiting.append(req)
+        self._n_prompt += len(checked)
+        return AddResult.ACCEPTED
+
+    def schedule_step(self, max_prefill_tokens: int, max_decode_seqs: int) -> Batch:
+        if self._inflight is not None:
+            raise SchedulerError("the previous batch has not been committed")
+        if max_prefill_tokens < 1 or max_decode_seqs < 1:
+            raise ValueError("max_prefill_tokens and max_decode_seqs must be >= 1")  # 0 would stall prompts forever
+        t0 = time.perf_counter()
+        work: list[WorkItem] = []
+        preempted: list[str] = []
+        budget = max_prefill_tokens
+
+        # Running requests, oldest first.  Victims of preemption are always
+        # newer than the asker, so they are never in `work` yet.
+        at = 0
+        while at < len(self._running):
+            req = self._running[at]
+            n = self._portion(req.seq_len - req.num_computed, budget)
+            if n == 0:
+                at += 1
+                continue
+            if not self._secure(req, req.num_computed + n, preempted):
+                continue  # req itself was preempted and left the list; `at` now names the next one
+            if req.seq_len - req.num_computed > 1:
+                budget -= n
+            work.append(WorkItem(req, req.num_computed, req.num_computed + n))
+            at += 1
+
+        # Newcomers, in order of arrival.
+        while self._waiting and len(self._running) < max_decode_seqs:
+            item = self._start(self._waiting[0], budget)
+            if item is None:
+                break
+            self._waiting.popleft()
+            if item.end - item.start > 1:
+                budget -= item.end - item.start
+            work.append(item)
+
+        batch = Batch(work, preempted)
+        self._inflight = batch
+        took = time.perf_counter() - t0
+        if took > SLOW_STEP_SECONDS:
+            log.debug("schedule_step took %.2f ms", took * 1e3)
+        return batch
+
+    def commit(self, batch: Batch, sampled: Mapping[str, int]) -> StepResult:
+        if batch is not self._inflight:
+            raise SchedulerError("commit() was given a batch that is not the one in flight")
+        self._inflight = None
+        new_tokens: dict[str, int] = {}
+        finished: dict[str, FinishReason] = {}
+        for w in batch.work:
+            req = w.req
+            if req.num_computed != w.start:
+                raise SchedulerError(f"{req.req_id}: the batch is stale")
+            samples = w.samples
+            req.num_computed = w.end
+            self.cache.advance(req.slot, w.end)
+            if not samples:
+                continue
+            if req.req_id not in sampled:
+                raise SchedulerError(f"no token was returned for {req.req_id}")
+            token = int(sampled[req.req_id])
+            if not req.prompt_cached:  # prompt complete for the first time: others may share it from now on
+                self._publish(req)
+                req.prompt_cached = True
+            req.output.append(token)
+            new_tokens[req.req_id] = token
+            if req.abort_pending:
+                continue
+            if token in self._stop and not req.ignore_eos:
+                reason = FinishReason.STOP
+            elif len(req.output) >= req.max_tokens:
+                reason = FinishReason.LENGTH
+            else:
+                continue
+            self._retire(req)
+            finished[req.req_id] = reason
+        for req in self._abort_at_commit:
+            if req.state is ReqState.RUNNING:
+                self._retire(req)
+                finished[req.req_id] = FinishReason.ABORT
+        self._abort_at_commit.clear()
+        return StepResult(new_tokens, finished)
+
+    def free_request(self, req_id: str) -> bool:
+        """Aborts a request; harmless for unknown ids and when called twice."""
+        req = self._by_id.get(req_id)
+        if req is None or req.abort_pending:
+            return False
+        if req.state is ReqState.WAITING:
+            self._waiting.remove(req)
+            req.state = ReqState.FINISHED
+            del self._by_id[req_id]
+            return True
+        if self._inflight is not None:
+            # the batch in flight may still write into its pages
+            req.abort_pending = True
+            self._abort_at_commit.append(req)
+            return True
+        self._retire(req)
+        return True
+
+    def get_request(self, req_id: str) -> Request | None:
+        return self._by_id.get(req_id)
+
+    def has_work(self) -> bool:
+        return bool(self._waiting) or bool(self._running)
+
+    def block_table(self, req: Request) -> list[int]:
+        return self.cache.page_ids(req.slot) if req.slot is not None else []
+
+    def stats(self) -> SchedulerStats:
+        return SchedulerStats(
+            num_waiting=len(self._waiting),
+            num_running=len(self._running),
+            free_blocks=self.cache.free_pages(0),
+            cached_blocks=self.cache.cached_pages(),
+            prompt_tokens=self._n_prompt,
+            cached_prompt_tokens=self._n_prompt_cached,
+            preemptions=self._n_preempt,
+            rejected=self._n_rejected,
+        )
+
+    # ------------------------------------------------------------ decisions
+    def _portion(self, remaining: int, budget: int) -> int:
+        return 1 if remaining == 1 else min(self._chunk, remaining, budget)
+
+    def _vet(self, req_id, prompt, max_tokens):
+        if not req_id or not isinstance(max_tokens, int) or isinstance(max_tokens, bool) or max_tokens < 1:
+            return AddResult.INVALID
+        try:
+            arr = np.asarray(prompt)
+        except (TypeError, ValueError, OverflowError):
+            return AddResult.INVALID
+        if arr.ndim != 1 or arr.size == 0 or arr.dtype.kind not in "iu":
+            return AddResult.INVALID
+        if int(arr.min()) < 0 or int(arr.max()) > np.iinfo(np.int32).max:
+            return AddResult.INVALID
+        if req_id in self._by_id:
+            return AddResult.DUPLICATE_ID
+        total = int(arr.size) + max_tokens
+        too_many_pages = any(pages_for(total, self.cache.page_size) > g.pool.num_blocks for g in self.cache.groups
+                             if g.window is None)
+        if too_many_pages or total > self.cache.max_seq_len:
+            return AddResult.TOO_LONG
+        if len(self._waiting) >= self._max_waiting:
+            return AddResult.QUEUE_FULL
+        return arr.astype(np.int32)  # a copy: later changes by the caller do not reach us
+
+    def _take_pages(self, req: Request, upto: int) -> bool:
+        """reserve, evicting unused cached pages if that is what it takes."""
+        if self.cache.reserve(req.slot, upto):
+            return True
+        lacking = self.cache.missing(req.slot, upto)
+        if set(lacking) != {0} or self.cache.tree is None:
+            return False
+        self.cache.evict(lacking[0])
+        return self.cache.reserve(req.slot, upto)
+
+    def _secure(self, req: Request, upto: int, preempted: list[str]) -> bool:
+        while not self._take_pages(req, upto):
+            victim = self._running[-1]
+            self._preempt(victim)
+            preempted.append(victim.req_id)
+            if victim is req:
+                return False
+        return True
+
+    def _start(self, req: Request, budget: int) -> WorkItem | None:
+        seq = req.seq()
+        # keep at least the last token to compute: its logits are what we are after
+        matched, pages = self.cache.match_prefix(seq[:-1]) if self._share_prefixes else (0, [])
+        n = self._portion(len(seq) - matched, budget)
+        slot = self.cache.open() if n > 0 else None
+        if slot is None:
+            self.cache.release_pages(pages)
+            return None
+        req.slot = slot
+        if pages:
+            self.cache.adopt(slot, pages, matched)
+        if not self._take_pages(req, matched + n):
+            self.cache.close(slot)  # returns the matched pages too; admission never preempts
+            req.slot = None
+            return None
+        req.num_computed = matched
+        req.cached_tokens += matched
+        if req.num_preemptions == 0:
+            self._n_prompt_cached += min(matched, len(req.prompt))
+        req.state = ReqState.RUNNING
+        bisect.insort(self._running, req, key=lambda r: r.arrival)
+        return WorkItem(req, matched, matched + n)
+
+    def _publish(self, req: Request) -> None:
+        if self._share_prefixes and req.num_computed >= self.cache.page_size:
+            self.cache.publish(req.slot, req.seq()[: req.num_computed])
+
+    def _preempt(self, req: Request) -> None:
+        # recompute, not swap; what it computed stays findable in the prefix cache
+        self._publish(req)
+        self.cache.close(req.slot)
+        req.slot = None
+        req.num_computed = 0
+        req.num_preemptions += 1
+        req.state = ReqState.WAITING
+        self._running.remove(req)
+        self._waiting.appendleft(req)
+        self._n_preempt += 1
+
+    def _retire(self, req: Request) -> None:
+        self._publish(req)
+        self.cache.close(req.slot)
+        req.slot = None
+        req.state = ReqState.FINISHED
+        self._running.remove(req)
+        del self._by_id[req.req_id]

@@ -1,0 +1,177 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+A batch mixes portions of prompts with single decoded tokens, cut anywhere.
+Only the given tokens are computed; everything earlier is read from the cache.
+The result is the float32 logits at the positions the caller asks for.
+
+Host work per step, after the reference (prefixserve/llama_engine.py:152-227):
+all integer inputs are laid out in one pinned buffer and reach the device in a
+single asynchronous copy; page tables and limits are checked on the host
+before anything is launched (prefixserve/llama_engine.py:270-287), so a bad
+table is an exception for one step, not a memory fault.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager, pages_for
+from ..parts.base import ItemView, StepContext
+from ..parts.model import DecoderModel
+
+
+class EngineError(RuntimeError):
+    """The step function was given a batch it cannot run."""
+
+
+@dataclass
+class StepItem:
+    slot: int
+    start: int                       # absolute position of the first token
+    tokens: np.ndarray               # int32, the next tokens of the request
+    want: Sequence[int] = field(default_factory=tuple)  # offsets into tokens whose logits are wanted
+
+
+class ModelRunner:
+    """Owns the per-step staging buffers and runs ``DecoderModel.forward`` on the cache."""
+
+    def __init__(self, model: DecoderModel, cache: CacheManager, *, device: torch.device | str) -> None:
+        if model.compute_dtype is None:
+            raise EngineError("the model has no weights yet")
+        self.model = model
+        self.cache = cache
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise EngineError(f"the engine runs on a CUDA device only, not on {self.device}")
+        self.vocab_size = model.spec.vocab_size
+        self._host: torch.Tensor | None = None
+        self._copied = torch.cuda.Event()
+        self._copy_pending = False
+        self.steps_run = 0
+
+    # ------------------------------------------------------------------ checks
+    def _check(self, items: Sequence[StepItem]) -> None:
+        seen: set[int] = set()
+        for it in items:
+            n = len(it.tokens)
+            if n < 1:
+                raise EngineError(f"slot {it.slot}: an item needs at least one token")
+            if it.slot in seen:
+                raise EngineError(f"slot {it.slot} appears twice in one step")
+            seen.add(it.slot)
+            if not self.cache.slots.taken(it.slot):
+                raise EngineError(f"slot {it.slot} is not open")
+            if it.start != self.cache.position(it.slot):
+                raise EngineError(f"slot {it.slot}: tokens start at {it.start} but the cache holds {self.cache.position(it.slot)}")
+            end = it.start + n
+            if end > self.cache.max_seq_len:
+                raise EngineError(f"slot {it.slot}: position {end} exceeds max_seq_len {self.cache.max_seq_len}")
+            if self.cache.shortfall(it.slot, end):
+                raise EngineError(f"slot {it.slot}: no pages reserved for positions up to {end}")
+            toks = np.asarray(it.tokens)
+            if toks.min() < 0 or toks.max() >= self.vocab_size:
+                raise EngineError(f"slot {it.slot}: token id outside [0, {self.vocab_size})")
+            for w in it.want:
+                if not 0 <= w < n:
+                    raise EngineError(f"slot {it.slot}: wanted offset {w} outside its {n} tokens")
+
+    def _check_tables(self, items: Sequence[StepItem], tables: dict[int, np.ndarray]) -> None:
+        page = self.cache.page_size
+        for gi, table in tables.items():
+            g = self.cache.groups[gi]
+            for row, it in zip(table, items):
+                end = it.start + len(it.tokens)
+                first = self.cache._first_needed_page(g, it.start)
+                live = row[first: pages_for(end, page)]
+                if live.size and (live.min() < 0 or live.max() >= g.pool.num_blocks):
+                    raise EngineError(f"slot {it.slot}: page table of group {gi} names a page outside the pool")
+
+    # ------------------------------------------------------------------- step
+    @torch.inference_mode()
+    def step(self, items: Sequence[StepItem]) -> torch.Tensor:
+        """Runs the batch. Returns float32 logits [number of wanted positions, vocab] on the device,
+        in the order of the items and of each item's ``want``."""
+        if not items:
+            return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
+        self._check(items)
+        lens = [len(it.tokens) for it in items]
+        b, t = len(items), sum(lens)
+        s = sum(len(it.want) for it in items)
+        page = self.cache.page_size
+        widths = {gi: max(pages_for(it.start + n, page) for it, n in zip(items, lens)) for gi in range(len(self.cache.groups))}
+        tables = self.cache.tables_for([it.slot for it in items], widths)
+        self._check_tables(items, tables)
+
+        # layout of the one staging buffer (int32 words)
+        o_ids, o_pos, o_item = 0, t, 2 * t
+        o_start = 3 * t
+        o_kvlen = o_start + b + 1
+        o_slot = o_kvlen + b
+        o_rows = o_slot + b
+        o_tab = o_rows + s
+        total = o_tab + sum(b * w for w in widths.values())
+
+        host = self._staging(total)
+        buf = host.numpy()
+        views: list[ItemView] = []
+        tok = ri = 0
+        buf[o_start] = 0
+        for i, (it, n) in enumerate(zip(items, lens)):
+            buf[o_ids + tok: o_ids + tok + n] = it.tokens
+            buf[o_pos + tok: o_pos + tok + n] = np.arange(it.start, it.start + n, dtype=np.int32)  # absolute
+            buf[o_item + tok: o_item + tok + n] = i
+            buf[o_kvlen + i] = it.start + n
+            buf[o_slot + i] = it.slot
+            for w in it.want:
+                buf[o_rows + ri] = tok + w
+                ri += 1
+            views.append(ItemView(slot=it.slot, start=it.start, end=it.start + n, first_token=tok))
+            tok += n
+            buf[o_start + i + 1] = tok
+        at = o_tab
+        table_at: dict[int, tuple[int, int]] = {}
+        for gi, table in tables.items():
+            w = widths[gi]
+            buf[at: at + b * w] = table.reshape(-1)
+            table_at[gi] = (at, w)
+            at += b * w
+
+        dev = host[:total].to(self.device, non_blocking=True)
+        self._copied.record()
+        self._copy_pending = True
+
+        ctx = StepContext(
+            num_tokens=t,
+            num_items=b,
+            compute_dtype=self.model.compute_dtype,
+            device=self.device,
+            items=views,
+            token_ids=dev[o_ids: o_ids + t],
+            positions=dev[o_pos: o_pos + t],
+            token_item=dev[o_item: o_item + t],
+            item_start=dev[o_start: o_start + b + 1],
+            kv_len=dev[o_kvlen: o_kvlen + b],
+            slots=dev[o_slot: o_slot + b],
+            block_tables={gi: dev[a: a + b * w].view(b, w) for gi, (a, w) in table_at.items()},
+            max_new_tokens=max(lens),
+            max_kv_len=max(it.start + n for it, n in zip(items, lens)),
+            all_decode=all(n == 1 for n in lens),
+        )
+        rows = dev[o_rows: o_rows + s]
+        logits = self.model.forward(ctx, self.cache.view, rows)
+        self.steps_run += 1
+        return logits
+
+    def _staging(self, words: int) -> torch.Tensor:
+        # the previous step's copy must have left the buffer before it is overwritten
+        if self._copy_pending:
+            self._copied.synchronize()
+            self._copy_pending = False
+        if self._host is None or self._host.numel() < words:
+            size = max(4096, 1 << (words - 1).bit_length())
+            self._host = torch.empty(size, dtype=torch.int32, pin_memory=True)
+        return self._host

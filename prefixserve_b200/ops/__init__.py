@@ -1,0 +1,14 @@
+"""Python faces of the CUDA kernels.  Each checks shapes, dtypes and layout on
+the host and raises ``KernelError`` instead of launching on arguments a kernel
+was not written for."""
+
+from .kernels import (  # noqa: F401
+    KernelError,
+    add_rmsnorm,
+    attention,
+    embedding,
+    linear,
+    rope_append,
+    sample,
+    silu_mul,
+)

@@ -1,0 +1,216 @@
+"""Host-side faces of the kernels: argument checks, output allocation, launch.
+
+Tensors are handed to the C ABI as raw device pointers on the current CUDA
+stream.  Everything here refuses CPU tensors: there is no CPU path.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .library import KernelError, check, lib
+
+F32, BF16 = 0, 1
+_CODES = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+def _code(t: torch.Tensor, what: str) -> int:
+    try:
+        return _CODES[t.dtype]
+    except KeyError:
+        raise KernelError(f"{what}: dtype {t.dtype} is not one of float32, bfloat16") from None
+
+
+def _dev(t: torch.Tensor, what: str) -> torch.Tensor:
+    if not t.is_cuda:
+        raise KernelError(f"{what} is on {t.device}; the kernels run on a CUDA device only")
+    if not t.is_contiguous():
+        raise KernelError(f"{what} must be contiguous, strides are {t.stride()}")
+    return t
+
+
+def _i32(t: torch.Tensor, what: str) -> torch.Tensor:
+    if t.dtype != torch.int32:
+        raise KernelError(f"{what} must be int32, is {t.dtype}")
+    return _dev(t, what)
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """h[t] = float32(table[ids[t]])."""
+    _i32(ids, "token ids")
+    _dev(table, "embedding table")
+    t, (v, h) = ids.numel(), table.shape
+    if out is None:
+        out = torch.empty((t, h), dtype=torch.float32, device=ids.device)
+    check(lib().psb_embedding(ids.data_ptr(), table.data_ptr(), _code(table, "embedding table"), out.data_ptr(),
+                              t, h, v, _stream()), "embedding")
+    return out
+
+
+def add_rmsnorm(h: torch.Tensor, delta: torch.Tensor | None, gain: torch.Tensor, eps: float,
+                out_dtype: torch.dtype, rows: torch.Tensor | None = None) -> torch.Tensor:
+    """h += delta (float32, in place, unless ``rows``); returns gain * rmsnorm(h) for all or the chosen rows."""
+    _dev(h, "residual stream")
+    if h.dtype != torch.float32 or h.dim() != 2:
+        raise KernelError(f"residual stream must be float32 [T, H], is {h.dtype} {tuple(h.shape)}")
+    width = h.shape[1]
+    if gain.dtype != torch.float32 or gain.numel() != width:
+        raise KernelError(f"norm gain must be float32 [{width}], is {gain.dtype} {tuple(gain.shape)}")
+    _dev(gain, "norm gain")
+    dcode = F32
+    if delta is not None:
+        _dev(delta, "sublayer output")
+        if delta.shape != h.shape:
+            raise KernelError(f"sublayer output {tuple(delta.shape)} does not match the stream {tuple(h.shape)}")
+        dcode = _code(delta, "sublayer output")
+    n = h.shape[0]
+    if rows is not None:
+        _i32(rows, "row index")
+        n = rows.numel()
+    x = torch.empty((n, width), dtype=out_dtype, device=h.device)
+    check(lib().psb_add_rmsnorm(h.data_ptr(), _ptr(delta), dcode, gain.data_ptr(), _ptr(rows), x.data_ptr(),
+                                _code(x, "norm output"), n, width, float(eps), 0 if rows is not None else 1, _stream()),
+          "add_rmsnorm")
+    return x
+
+
+def gemm_nt_simt(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, out: torch.Tensor | None = None,
+                 accumulate: bool = False) -> torch.Tensor:
+    """a[M,K] @ w[N,K]^T with float32 multiply-adds on the CUDA cores."""
+    _dev(a, "left operand")
+    _dev(w, "weight")
+    if a.dim() != 2 or w.dim() != 2 or a.shape[1] != w.shape[1]:
+        raise KernelError(f"cannot multiply {tuple(a.shape)} by the transpose of {tuple(w.shape)}")
+    m, k = a.shape
+    n = w.shape[0]
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+    check(lib().psb_gemm_nt(a.data_ptr(), _code(a, "left operand"), w.data_ptr(), _code(w, "weight"), out.data_ptr(),
+                            _code(out, "product"), m, n, k, k, k, n, 1 if accumulate else 0, _stream()), "gemm_nt")
+    return out
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """x[M,K] @ w[N,K]^T, accumulated in float32.
+
+    bfloat16 x bfloat16 goes to the tensor-core path; every other mix (all of
+    the 32-bit path, and weights a checkpoint stores in float32) goes to the
+    float32 CUDA-core kernel, so that path never touches a reduced-precision
+    matrix mode.
+    """
+    out_dtype = out_dtype or x.dtype
+    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+        from .tensorcore import linear_bf16
+        return linear_bf16(x, w, out_dtype)
+    return gemm_nt_simt(x, w, out_dtype)
+
+
+def rope_append(qkv: torch.Tensor, positions: torch.Tensor, token_item: torch.Tensor, cos: torch.Tensor | None,
+                sin: torch.Tensor | None, table: torch.Tensor | None, kv: torch.Tensor | None, *, num_heads: int,
+                num_kv_heads: int, head_dim: int, page_size: int, write_kv: bool) -> torch.Tensor:
+    """Rotates queries (and keys); stores rotated keys and values in the pages. Returns q [T, hq, D]."""
+    _dev(qkv, "projection output")
+    t = qkv.shape[0]
+    hkv_in = num_kv_heads if write_kv else 0
+    want = (num_heads + 2 * hkv_in) * head_dim
+    if qkv.dim() != 2 or qkv.shape[1] != want:
+        raise KernelError(f"projection output must be [T, {want}], is {tuple(qkv.shape)}")
+    _i32(positions, "positions")
+    _i32(token_item, "token-to-item map")
+    rotate = cos is not None
+    max_pos = 0
+    if rotate:
+        assert sin is not None
+        _dev(cos, "cos table"), _dev(sin, "sin table")
+        if cos.dtype != torch.float32 or cos.shape != sin.shape or cos.dim() != 2 or cos.shape[1] != head_dim // 2:
+            raise KernelError(f"angle tables must be float32 [positions, {head_dim // 2}], are {cos.dtype} {tuple(cos.shape)}")
+        max_pos = cos.shape[0]
+    width = num_pages = 0
+    kv_code = _code(qkv, "projection output")
+    if write_kv:
+        if kv is None or table is None:
+            raise KernelError("appending to the cache needs the cache entry and the page table")
+        _dev(kv, "cache entry"), _i32(table, "page table")
+        if kv.dim() != 5 or tuple(kv.shape[1:]) != (2, num_kv_heads, page_size, head_dim):
+            raise KernelError(f"cache entry must be [pages, 2, {num_kv_heads}, {page_size}, {head_dim}], is {tuple(kv.shape)}")
+        num_pages, width, kv_code = kv.shape[0], table.shape[1], _code(kv, "cache entry")
+    q = torch.empty((t, num_heads, head_dim), dtype=qkv.dtype, device=qkv.device)
+    check(lib().psb_rope_append(qkv.data_ptr(), _code(qkv, "projection output"), positions.data_ptr(),
+                                token_item.data_ptr(), _ptr(cos), _ptr(sin), _ptr(table) if write_kv else None, width,
+                                _ptr(kv) if write_kv else None, kv_code, q.data_ptr(), t, num_heads, hkv_in, head_dim,
+                                page_size, num_pages, max_pos, 1 if rotate else 0, 1 if write_kv else 0, _stream()),
+          "rope_append")
+    return q
+
+
+def attention_generic(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, positions: torch.Tensor,
+                      token_item: torch.Tensor, *, window: int | None, scale: float) -> torch.Tensor:
+    _dev(q, "queries"), _dev(kv, "cache entry")
+    _i32(table, "page table"), _i32(positions, "positions"), _i32(token_item, "token-to-item map")
+    t, hq, d = q.shape
+    _, two, hkv, page, dk = kv.shape
+    if two != 2 or dk != d:
+        raise KernelError(f"cache entry {tuple(kv.shape)} does not fit queries {tuple(q.shape)}")
+    out = torch.empty((t, hq * d), dtype=q.dtype, device=q.device)
+    check(lib().psb_attention_generic(q.data_ptr(), _code(q, "queries"), kv.data_ptr(), _code(kv, "cache entry"),
+                                      table.data_ptr(), table.shape[1], positions.data_ptr(), token_item.data_ptr(),
+                                      out.data_ptr(), t, hq, hkv, d, page, int(window or 0), float(scale), _stream()),
+          "attention")
+    return out
+
+
+def attention(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, positions: torch.Tensor,
+              token_item: torch.Tensor, *, window: int | None = None, scale: float | None = None,
+              ctx=None) -> torch.Tensor:
+    """Causal grouped-query attention of the step's tokens over their requests' pages -> [T, hq*D]."""
+    if scale is None:
+        scale = 1.0 / math.sqrt(q.shape[-1])
+    if q.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16 and ctx is not None:
+        from .tensorcore import attention_bf16
+        fast = attention_bf16(q, kv, table, positions, token_item, window=window, scale=scale, ctx=ctx)
+        if fast is not None:
+            return fast
+    return attention_generic(q, kv, table, positions, token_item, window=window, scale=scale)
+
+
+def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    """[T, 2I] -> silu(first half) * second half, [T, I]."""
+    _dev(gate_up, "gate/up projection")
+    t, two_i = gate_up.shape
+    if two_i % 2:
+        raise KernelError(f"gate/up projection must have an even width, has {two_i}")
+    out = torch.empty((t, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+    check(lib().psb_silu_mul(gate_up.data_ptr(), _code(gate_up, "gate/up projection"), out.data_ptr(), t, two_i // 2,
+                             _stream()), "silu_mul")
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor | None = None, seed: torch.Tensor | None = None,
+           position: torch.Tensor | None = None) -> torch.Tensor:
+    """Arg max (temperature absent or 0) or Gumbel-max sampling per row -> int32 [S]."""
+    _dev(logits, "logits")
+    if logits.dtype != torch.float32 or logits.dim() != 2:
+        raise KernelError(f"logits must be float32 [S, V], are {logits.dtype} {tuple(logits.shape)}")
+    s, v = logits.shape
+    if temperature is not None:
+        if seed is None or position is None:
+            raise KernelError("temperature sampling needs seed and position per row")
+        _dev(temperature, "temperature"), _dev(seed, "seed"), _i32(position, "position")
+        if temperature.dtype != torch.float32 or seed.dtype != torch.int64:
+            raise KernelError("temperature must be float32 and seed int64")
+        if temperature.numel() != s or seed.numel() != s or position.numel() != s:
+            raise KernelError("temperature, seed and position need one entry per logits row")
+    out = torch.empty((s,), dtype=torch.int32, device=logits.device)
+    check(lib().psb_sample(logits.data_ptr(), _ptr(temperature), _ptr(seed), _ptr(position), out.data_ptr(), s, v,
+                           _stream()), "sample")
+    return out

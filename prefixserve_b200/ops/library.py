@@ -1,0 +1,71 @@
+"""Loads the CUDA kernel library and declares its C entry points.
+
+There is no fallback: if the library cannot be built or loaded, or no CUDA
+device is present, importing an op raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_int64, c_void_p
+
+from ..build import ensure_kernels
+
+
+class KernelError(RuntimeError):
+    """A kernel refused its arguments or the launch failed."""
+
+
+_lib: ctypes.CDLL | None = None
+
+P, I, L, F = c_void_p, c_int, c_int64, c_float
+
+# name -> argument types (every entry point returns an int status, 0 = ok)
+_SIGNATURES: dict[str, list] = {
+    # (ids, table, table_dtype, out_f32, T, H, V, stream)
+    "psb_embedding": [P, P, I, P, I, I, I, P],
+    # (h, delta, delta_dtype, weight, rows, x, x_dtype, n_rows, H, eps, update_h, stream)
+    "psb_add_rmsnorm": [P, P, I, P, P, P, I, I, I, F, I, P],
+    # (a, a_dtype, w, w_dtype, c, c_dtype, M, N, K, lda, ldw, ldc, accumulate, stream)
+    "psb_gemm_nt": [P, I, P, I, P, I, I, I, I, L, L, L, I, P],
+    # (qkv, dtype, positions, token_item, cos, sin, table, table_width, kv, kv_dtype, q_out,
+    #  T, hq, hkv, D, page_size, num_pages, max_positions, rotate, write_kv, stream)
+    "psb_rope_append": [P, I, P, P, P, P, P, I, P, I, P, I, I, I, I, I, I, I, I, I, P],
+    # (q, dtype, kv, kv_dtype, table, table_width, positions, token_item, out, T, hq, hkv, D, page_size, window,
+    #  scale, stream)
+    "psb_attention_generic": [P, I, P, I, P, I, P, P, P, I, I, I, I, I, I, F, P],
+    # (gate_up, dtype, out, T, I, stream)
+    "psb_silu_mul": [P, I, P, I, I, P],
+    # (logits, temperature, seed, position, out, S, V, stream)
+    "psb_sample": [P, P, P, P, P, I, I, P],
+}
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        path = ensure_kernels()
+        handle = ctypes.CDLL(str(path))
+        for name, argtypes in _SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.argtypes = argtypes
+            fn.restype = c_int
+        handle.psb_last_error.restype = ctypes.c_char_p
+        handle.psb_last_error.argtypes = []
+        _lib = handle
+    return _lib
+
+
+def declare(name: str, argtypes: list) -> None:
+    """Adds an entry point (used by kernels that arrive in later files)."""
+    _SIGNATURES[name] = argtypes
+    if _lib is not None:
+        fn = getattr(_lib, name)
+        fn.argtypes = argtypes
+        fn.restype = c_int
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        detail = lib().psb_last_error().decode(errors="replace")
+        raise KernelError(f"{what}: {detail} (status {status})")

@@ -1,0 +1,81 @@
+"""A decoder assembled from a ``ModelSpec``: embedding, blocks run in the order
+of the run list, final norm on the wanted rows, LM head."""
+
+from __future__ import annotations
+
+from typing import Callable, Mapping
+
+import torch
+
+from ..config.spec import ModelSpec
+from .base import CacheNeed, CacheView, ParamSpec, StepContext
+from .block import Block
+from .registry import make
+
+
+class DecoderModel:
+    def __init__(self, spec: ModelSpec):
+        self.spec = spec
+        self.embedding = make("embedding", spec.embedding)
+        self.blocks = [Block(layer) for layer in spec.layers]
+        self.final_norm = make("norm", spec.final_norm)
+        self.head = make("head", spec.head)
+        self.compute_dtype: torch.dtype | None = None
+
+    # ---- tensors ---------------------------------------------------------
+    def named_parts(self):
+        yield "embedding", self.embedding
+        for i, block in enumerate(self.blocks):
+            for name, p in block.named_parts():
+                yield f"layers.{i}.{name}", p
+        yield "final_norm", self.final_norm
+        yield "head", self.head
+
+    def param_table(self) -> dict[str, ParamSpec]:
+        """part path -> wanted tensor, in a fixed order (the random-weights mode draws in this order)."""
+        table: dict[str, ParamSpec] = {}
+        for prefix, p in self.named_parts():
+            for local, ps in p.param_specs().items():
+                table[f"{prefix}.{local}"] = ps
+        return table
+
+    def load(self, tensors: Mapping[str, torch.Tensor], *, compute_dtype: torch.dtype, device: torch.device,
+             max_positions: int) -> None:
+        for prefix, p in self.named_parts():
+            mine = {local: tensors[f"{prefix}.{local}"] for local in p.param_specs()}
+            p.load(mine, compute_dtype=compute_dtype, device=device)
+            p.prepare(max_positions=max_positions, compute_dtype=compute_dtype, device=device)
+        if getattr(self.head, "tied", False):
+            self.head.tie(self.embedding.table)
+        self.compute_dtype = compute_dtype
+
+    # ---- cache -----------------------------------------------------------
+    def cache_needs(self) -> list[CacheNeed]:
+        """What each cache entry must hold (entry index -> need of the call that writes it)."""
+        needs: list[CacheNeed | None] = [None] * self.spec.num_cache_entries
+        for call in self.spec.schedule:
+            need = self.blocks[call.layer].mixer.cache_need()
+            if call.writes_cache:
+                needs[call.cache] = need
+        for call in self.spec.schedule:
+            if not call.writes_cache:
+                need = self.blocks[call.layer].mixer.cache_need()
+                if needs[call.cache] != need:
+                    raise ValueError(f"layer {call.layer} reads cache entry {call.cache} but needs {need}, entry holds {needs[call.cache]}")
+        return [n if n is not None else CacheNeed() for n in needs]
+
+    # ---- one step ----------------------------------------------------------
+    def forward(self, ctx: StepContext, cache_view: Callable[[int, bool], CacheView], rows: torch.Tensor) -> torch.Tensor:
+        """Runs the step's tokens; returns float32 logits [len(rows), vocab] for the wanted flat rows."""
+        h = self.embedding.forward(ctx.token_ids)
+        pending = None
+        for call in self.spec.schedule:
+            h, pending = self.blocks[call.layer].forward(h, pending, ctx, cache_view(call.cache, call.writes_cache))
+        if rows.numel() == 0:
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=h.device)
+        x = self.final_norm.forward(h, pending, ctx, rows=rows)
+        return self.head.forward(x)
+
+
+def build_model(spec: ModelSpec) -> DecoderModel:
+    return DecoderModel(spec)
