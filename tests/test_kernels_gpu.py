@@ -1,0 +1,286 @@
+"""Each kernel alone against a plain float32 torch restatement, at sizes other than the engine's."""
+
+import math
+
+import pytest
+import torch
+
+import plain_model
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+
+
+@pytest.fixture(autouse=True)
+def _seed():
+    torch.manual_seed(0)
+    torch.backends.cuda.matmul.allow_tf32 = False
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("vocab,hidden", [(37, 24), (1000, 2056)])
+def test_embedding(dtype, vocab, hidden):
+    from prefixserve_b200 import ops
+    table = torch.randn(vocab, hidden, device=DEV).to(dtype)
+    ids = torch.randint(0, vocab, (19,), device=DEV, dtype=torch.int32)
+    out = ops.embedding(ids, table)
+    assert out.dtype == torch.float32
+    assert torch.equal(out, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,hidden,eps", [(7, 24, 1e-5), (33, 1000, 1e-6), (3, 5120, 3e-2)])
+def test_add_rmsnorm(dtype, rows, hidden, eps):
+    from prefixserve_b200 import ops
+    h = torch.randn(rows, hidden, device=DEV) * 3
+    delta = torch.randn(rows, hidden, device=DEV).to(dtype)
+    gain = 1 + 0.1 * torch.randn(hidden, device=DEV)
+    total = h + delta.float()
+    want = plain_model.rms_norm(total, gain, eps)
+    h1 = h.clone()
+    x = ops.add_rmsnorm(h1, delta, gain, eps, dtype)
+    assert torch.allclose(h1, total, rtol=0, atol=0)  # the residual sum is float32 and exact
+    assert torch.allclose(x.float(), want, **tol(dtype))
+    # no pending output: plain norm, stream untouched
+    h2 = h.clone()
+    x2 = ops.add_rmsnorm(h2, None, gain, eps, dtype)
+    assert torch.equal(h2, h)
+    assert torch.allclose(x2.float(), plain_model.rms_norm(h, gain, eps), **tol(dtype))
+    # chosen rows only: stream untouched, rows gathered
+    idx = torch.tensor([rows - 1, 0, rows // 2], device=DEV, dtype=torch.int32)
+    h3 = h.clone()
+    x3 = ops.add_rmsnorm(h3, delta, gain, eps, dtype, rows=idx)
+    assert torch.equal(h3, h)
+    assert torch.allclose(x3.float(), want[idx.long()], **tol(dtype))
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 1, 1), (5, 70, 33), (64, 64, 16), (130, 333, 257), (3, 1000, 2048)])
+@pytest.mark.parametrize("a_dtype,w_dtype,c_dtype", [
+    (torch.float32, torch.float32, torch.float32),
+    (torch.bfloat16, torch.bfloat16, torch.bfloat16),
+    (torch.bfloat16, torch.float32, torch.bfloat16),
+    (torch.bfloat16, torch.bfloat16, torch.float32),
+])
+def test_gemm_simt(m, n, k, a_dtype, w_dtype, c_dtype):
+    from prefixserve_b200.ops.kernels import gemm_nt_simt
+    a = torch.randn(m, k, device=DEV).to(a_dtype)
+    w = torch.randn(n, k, device=DEV).to(w_dtype)
+    want = a.double() @ w.double().t()
+    got = gemm_nt_simt(a, w, c_dtype)
+    scale = math.sqrt(k)
+    if c_dtype == torch.float32:
+        assert torch.allclose(got.double(), want, rtol=1e-5, atol=2e-6 * scale * 10)
+    else:
+        assert torch.allclose(got.double(), want, rtol=1e-2, atol=1e-2 * scale)
+
+
+def test_gemm_simt_rows_do_not_depend_on_the_batch():
+    """A row's product is bit-identical whether it is computed alone or among others."""
+    from prefixserve_b200.ops.kernels import gemm_nt_simt
+    a = torch.randn(77, 300, device=DEV)
+    w = torch.randn(190, 300, device=DEV)
+    full = gemm_nt_simt(a, w, torch.float32)
+    for r in (0, 13, 76):
+        assert torch.equal(gemm_nt_simt(a[r:r + 1].contiguous(), w, torch.float32)[0], full[r])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_linear_matches_float64(dtype):
+    from prefixserve_b200 import ops
+    a = torch.randn(50, 96, device=DEV).to(dtype)
+    w = torch.randn(72, 96, device=DEV).to(dtype)
+    got = ops.linear(a, w, out_dtype=torch.float32)
+    want = a.double() @ w.double().t()
+    assert torch.allclose(got.double(), want, rtol=2e-2 if dtype == torch.bfloat16 else 1e-5, atol=0.15 if dtype == torch.bfloat16 else 1e-4)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("t,inter", [(5, 7), (40, 1000)])
+def test_silu_mul(dtype, t, inter):
+    from prefixserve_b200 import ops
+    gu = (torch.randn(t, 2 * inter, device=DEV) * 3).to(dtype)
+    got = ops.silu_mul(gu)
+    g, u = gu.float()[:, :inter], gu.float()[:, inter:]
+    assert torch.allclose(got.float(), torch.nn.functional.silu(g) * u, **tol(dtype))
+
+
+def _paged_setup(dtype, lens_new, lens_old, hq, hkv, d, page, seed=0, shuffle=True):
+    """Random q/k/v for items with ``old`` cached tokens and ``new`` tokens this step; pages in random order."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    b = len(lens_new)
+    total_pages = sum(-(-(o + n) // page) for o, n in zip(lens_old, lens_new)) + 3
+    perm = torch.randperm(total_pages, generator=g) if shuffle else torch.arange(total_pages)
+    width = max(-(-(o + n) // page) for o, n in zip(lens_old, lens_new))
+    table = torch.full((b, width), -1, dtype=torch.int32)
+    at = 0
+    for i, (o, n) in enumerate(zip(lens_old, lens_new)):
+        np_ = -(-(o + n) // page)
+        table[i, :np_] = perm[at:at + np_].to(torch.int32)
+        at += np_
+    seqs = []
+    for o, n in zip(lens_old, lens_new):
+        tot = o + n
+        seqs.append(dict(q=torch.randn(tot, hq, d, generator=g), k=torch.randn(tot, hkv, d, generator=g),
+                         v=torch.randn(tot, hkv, d, generator=g)))
+    return table, seqs, total_pages
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hq,hkv,d,page", [(4, 2, 16, 16), (3, 1, 32, 16), (5, 5, 48, 8), (8, 2, 64, 16), (2, 1, 128, 32)])
+@pytest.mark.parametrize("window", [None, 19])
+def test_rope_append_then_attention(dtype, hq, hkv, d, page, window):
+    """rope+append writes the pages bit-exactly where they belong; attention over cached prefix + new tokens
+    matches plain attention of the whole sequence.  Covers decode at a page edge, a portion over a cached
+    prefix, a fresh prompt, and page tables in random order."""
+    from prefixserve_b200 import ops
+    lens_old = [32, 33, 0, 15, 100]
+    lens_new = [1, 1, 37, 18, 2]
+    table, seqs, num_pages = _paged_setup(dtype, lens_new, lens_old, hq, hkv, d, page)
+    kv = torch.full((num_pages, 2, hkv, page, d), float("nan"), dtype=dtype, device=DEV)  # poison: unread pages
+    inv = 1.0 / (10000.0 ** (torch.arange(0, d, 2).float() / d))
+    max_pos = 256
+    ang = torch.outer(torch.arange(max_pos).float(), inv)
+    cos, sin = ang.cos().to(DEV), ang.sin().to(DEV)
+
+    def rot(x, pos):  # float32 rotation of x [n, h, d] at positions pos
+        c = torch.cat([ang[pos].cos()] * 2, -1)[:, None, :]
+        s = torch.cat([ang[pos].sin()] * 2, -1)[:, None, :]
+        return plain_model.apply_rope(x, c, s)
+
+    table_dev = table.to(DEV)
+    # 1. the cached prefixes arrive through the same kernel in an earlier "step"
+    for phase in ("old", "new"):
+        qkv_rows, positions, items = [], [], []
+        for i, (s, o, n) in enumerate(zip(seqs, lens_old, lens_new)):
+            lo, hi = (0, o) if phase == "old" else (o, o + n)
+            if hi == lo:
+                continue
+            qkv_rows.append(torch.cat([s["q"][lo:hi].reshape(hi - lo, -1), s["k"][lo:hi].reshape(hi - lo, -1),
+                                       s["v"][lo:hi].reshape(hi - lo, -1)], dim=1))
+            positions += list(range(lo, hi))
+            items += [i] * (hi - lo)
+        qkv = torch.cat(qkv_rows).to(dtype).to(DEV)
+        pos_dev = torch.tensor(positions, dtype=torch.int32, device=DEV)
+        item_dev = torch.tensor(items, dtype=torch.int32, device=DEV)
+        q_rot = ops.rope_append(qkv, pos_dev, item_dev, cos, sin, table_dev, kv, num_heads=hq, num_kv_heads=hkv,
+                                head_dim=d, page_size=page, write_kv=True)
+    # pages hold exactly the rotated keys / raw values, rounded once
+    for i, (s, o, n) in enumerate(zip(seqs, lens_old, lens_new)):
+        tot = o + n
+        k_want = rot(s["k"].to(dtype).float(), torch.arange(tot)).to(dtype)
+        v_want = s["v"].to(dtype)
+        for p in range(tot):
+            pg = int(table[i, p // page])
+            assert torch.equal(kv[pg, 1, :, p % page, :].cpu(), v_want[p]), "values must be stored bit-exactly"
+            assert torch.allclose(kv[pg, 0, :, p % page, :].cpu().float(), k_want[p].float(), **tol(dtype))
+    # 2. attention of the new tokens
+    out = ops.attention(q_rot, kv, table_dev, pos_dev, item_dev, window=window)
+    at = 0
+    for i, (s, o, n) in enumerate(zip(seqs, lens_old, lens_new)):
+        tot = o + n
+        qf = rot(s["q"].to(dtype).float(), torch.arange(tot)).to(dtype).float()
+        kf = rot(s["k"].to(dtype).float(), torch.arange(tot)).to(dtype).float()
+        want = plain_model.causal_attention(qf, kf, s["v"].to(dtype).float(), window=window)[o:].reshape(n, hq * d)
+        got = out[at:at + n].float().cpu()
+        assert torch.isfinite(got).all(), "attention read a page it should not have (poison leaked)"
+        assert torch.allclose(got, want, **tol(dtype)), f"item {i}: {(got - want).abs().max()}"
+        at += n
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_one_far_key(dtype):
+    """One key among hundreds is made to dominate; the output must be (almost) its value."""
+    from prefixserve_b200 import ops
+    hq, hkv, d, page, n_ctx = 4, 2, 32, 16, 700
+    needle = 123
+    q = torch.zeros(1, hq, d)
+    q[..., 0] = 40.0
+    k = torch.randn(n_ctx, hkv, d) * 0.1
+    k[needle, :, 0] = 40.0
+    v = torch.randn(n_ctx, hkv, d)
+    pages = -(-n_ctx // page)
+    table = torch.randperm(pages + 5)[:pages].to(torch.int32)[None, :].to(DEV)
+    kv = torch.full((pages + 5, 2, hkv, page, d), float("nan"), dtype=dtype, device=DEV)
+    for p in range(n_ctx):
+        kv[table[0, p // page], 0, :, p % page] = k[p].to(dtype).to(DEV)
+        kv[table[0, p // page], 1, :, p % page] = v[p].to(dtype).to(DEV)
+    out = ops.attention(q.to(dtype).to(DEV), kv, table, torch.tensor([n_ctx - 1], dtype=torch.int32, device=DEV),
+                        torch.zeros(1, dtype=torch.int32, device=DEV))
+    want = v[needle].to(dtype).float().repeat_interleave(hq // hkv, dim=0).reshape(1, -1)
+    assert torch.allclose(out.float().cpu(), want, atol=2e-2, rtol=2e-2)
+    # with a window that ends just after the needle, it must vanish from the result
+    out_w = ops.attention(q.to(dtype).to(DEV), kv, table, torch.tensor([n_ctx - 1], dtype=torch.int32, device=DEV),
+                          torch.zeros(1, dtype=torch.int32, device=DEV), window=n_ctx - 1 - needle)
+    assert not torch.allclose(out_w.float().cpu(), want, atol=0.2, rtol=0)
+    out_w2 = ops.attention(q.to(dtype).to(DEV), kv, table, torch.tensor([n_ctx - 1], dtype=torch.int32, device=DEV),
+                           torch.zeros(1, dtype=torch.int32, device=DEV), window=n_ctx - needle)
+    assert torch.allclose(out_w2.float().cpu(), want, atol=2e-2, rtol=2e-2)
+
+
+def test_sampling_greedy_and_ties():
+    from prefixserve_b200 import ops
+    logits = torch.randn(6, 1001, device=DEV)
+    logits[2, 77] = logits[2, 500] = 50.0  # a tie: the lower index wins
+    logits[3] = 0.0
+    got = ops.sample(logits)
+    want = torch.argmax(logits, dim=-1)
+    want[2], want[3] = 77, 0
+    assert got.tolist() == want.tolist()
+
+
+def test_sampling_temperature_follows_the_stated_rule():
+    from prefixserve_b200 import ops
+    vocab = 300
+    logits = torch.randn(4, vocab, device=DEV)
+    temps = torch.tensor([0.7, 0.0, 1.3, 0.7], device=DEV)
+    seeds = torch.tensor([5, 5, 2**40 + 3, 5], dtype=torch.int64, device=DEV)
+    poss = torch.tensor([9, 9, 0, 10], dtype=torch.int32, device=DEV)
+    got = ops.sample(logits, temps, seeds, poss).tolist()
+    for row in range(4):
+        if float(temps[row]) == 0:
+            assert got[row] == int(torch.argmax(logits[row]))
+            continue
+        u = plain_model.gumbel_uniform(int(seeds[row]), int(poss[row]), vocab)
+        score = logits[row].cpu() / float(temps[row]) - torch.log(-torch.log(u))
+        assert got[row] == int(torch.argmax(score)), row
+    # same (seed, position) -> same draw, whatever the batch
+    alone = ops.sample(logits[:1].contiguous(), temps[:1].contiguous(), seeds[:1].contiguous(), poss[:1].contiguous())
+    assert alone.tolist()[0] == got[0]
+
+
+def test_sampling_distribution():
+    """Over many positions the draws follow softmax(logits / T)."""
+    from prefixserve_b200 import ops
+    vocab, n = 8, 20000
+    row = torch.tensor([2.0, 1.0, 0.5, 0.0, -1.0, -2.0, 1.5, 0.2], device=DEV)
+    logits = row.repeat(n, 1).contiguous()
+    t = 0.8
+    got = ops.sample(logits, torch.full((n,), t, device=DEV), torch.full((n,), 17, dtype=torch.int64, device=DEV),
+                     torch.arange(n, dtype=torch.int32, device=DEV))
+    freq = torch.bincount(got.long(), minlength=vocab).float().cpu() / n
+    want = torch.softmax(row.cpu() / t, dim=-1)
+    assert float((freq - want).abs().max()) < 0.015
+
+
+def test_kernels_refuse_what_they_cannot_run():
+    from prefixserve_b200 import ops
+    from prefixserve_b200.ops import KernelError
+    with pytest.raises(KernelError):
+        ops.embedding(torch.zeros(3, dtype=torch.int32), torch.zeros(4, 4))  # CPU tensors
+    with pytest.raises(KernelError):
+        ops.silu_mul(torch.zeros(2, 7, device=DEV))  # odd width
+    with pytest.raises(KernelError):
+        q = torch.zeros(1, 3, 16, device=DEV)
+        kv = torch.zeros(2, 2, 2, 16, 16, device=DEV)  # 3 query heads over 2 kv heads
+        ops.attention(q, kv, torch.zeros(1, 1, dtype=torch.int32, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV),
+                      torch.zeros(1, dtype=torch.int32, device=DEV))
+    with pytest.raises(KernelError):
+        q = torch.zeros(1, 2, 512, device=DEV)  # head size beyond the kernels' limit
+        kv = torch.zeros(2, 2, 2, 16, 512, device=DEV)
+        ops.attention(q, kv, torch.zeros(1, 1, dtype=torch.int32, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV),
+                      torch.zeros(1, dtype=torch.int32, device=DEV))

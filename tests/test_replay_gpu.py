@@ -1,0 +1,132 @@
+"""Trace replay against the plain implementation: every cutting of the work, float32 and bfloat16."""
+
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import plain_model
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parents[1]
+
+LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 16, 40, 70, 131], "C": [3, 48, 97]}
+TRACES = {
+    "whole": helpers.trace_whole,
+    "tail_decode": helpers.trace_tail_decode,
+    "portions": helpers.trace_portions,
+    "mixed": helpers.trace_mixed,
+}
+
+
+def sequences(which):
+    vocab = helpers.TINY[which]["cfg"].vocab_size
+    return {f"r{i}": helpers.random_tokens(vocab, n, seed=100 + i) for i, n in enumerate(LENGTHS[which])}
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    return {w: helpers.make_folder(tmp_path_factory.mktemp(f"tiny{w}"), w) for w in helpers.TINY}
+
+
+@pytest.fixture(scope="module")
+def truth(folders):
+    """float32 plain logits of every sequence, whole."""
+    out = {}
+    for which, folder in folders.items():
+        cfg, tensors = plain_model.read_folder(folder)
+        out[which] = {rid: plain_model.forward(cfg, tensors, toks) for rid, toks in sequences(which).items()}
+    return out
+
+
+def replay(folder, dtype, steps, max_tokens=None):
+    from prefixserve_b200.engine.replay import Replayer
+    rp = Replayer(folder, dtype, max_tokens or helpers.peak_tokens(steps))
+    outputs = {}
+    for st in steps:
+        out = rp.run_step(st)
+        if out is not None:
+            outputs[st["step"]] = torch.from_numpy(out.copy())
+    rp.cache.check()
+    assert rp.cache.free_pages(0) == rp.cache.num_pages(0), "pages were not all given back"
+    return helpers.collect(steps, outputs)
+
+
+@pytest.mark.parametrize("which", ["A", "B", "C"])
+@pytest.mark.parametrize("kind", list(TRACES))
+def test_float32_matches_plain(folders, truth, which, kind):
+    seqs = sequences(which)
+    steps = TRACES[kind](seqs)
+    rows = replay(folders[which], "float32", steps)
+    assert len(rows) == sum(len(t) for t in seqs.values())
+    for (rid, pos), got in sorted(rows.items()):
+        want = truth[which][rid][pos]
+        tol = 1e-4 * float(want.abs().max())
+        err = float((got - want).abs().max())
+        assert err <= tol, f"{which}/{kind}: request {rid} position {pos}: |diff| {err:.3e} > {tol:.3e}"
+
+
+@pytest.mark.parametrize("which", ["A", "B", "C"])
+@pytest.mark.parametrize("kind", list(TRACES))
+def test_bfloat16_close_to_float32_truth(folders, truth, which, kind):
+    """bfloat16 engine vs float32 truth, judged against a plain bfloat16 run of the same weights."""
+    seqs = sequences(which)
+    steps = TRACES[kind](seqs)
+    rows = replay(folders[which], "bfloat16", steps)
+    cfg, tensors = plain_model.read_folder(folders[which])
+    for rid, toks in seqs.items():
+        want = truth[which][rid]
+        got = torch.stack([rows[(rid, p)] for p in range(len(toks))])
+        plain_bf16 = plain_model.forward(cfg, tensors, toks, dtype=torch.bfloat16)
+        ours, theirs = helpers.rel_err(got, want), helpers.rel_err(plain_bf16, want)
+        assert ours < 0.15 and ours <= 1.5 * theirs + 1e-3, f"{which}/{kind}/{rid}: engine {ours:.4f}, plain bf16 {theirs:.4f}"
+
+
+def test_cuttings_agree_in_float32(folders):
+    """The same request cut four ways gives the same logits up to rounding."""
+    seqs = sequences("B")
+    base = replay(folders["B"], "float32", helpers.trace_whole(seqs))
+    for kind in ("tail_decode", "portions", "mixed"):
+        other = replay(folders["B"], "float32", TRACES[kind](seqs))
+        for key, row in base.items():
+            assert float((row - other[key]).abs().max()) <= 2e-5 * float(row.abs().max()), (kind, key)
+
+
+def test_pages_are_reused_in_mixed_trace(folders):
+    seqs = sequences("B")
+    steps = helpers.trace_mixed(seqs, max_live=2, seed=3)
+    total = sum(-(-len(t) // 64) * 64 for t in seqs.values())
+    assert helpers.peak_tokens(steps) < total  # the pool is smaller than all requests together
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_program_from_the_command_line(folders, truth, tmp_path, dtype):
+    """bin/trace_run as a user runs it: stdin lines, done lines, .f32 files."""
+    seqs = sequences("A")
+    steps = helpers.trace_mixed(seqs, seed=5)
+    out = tmp_path / "out"
+    cmd = [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folders["A"]), "--dtype", dtype, "--out", str(out),
+           "--max-tokens", str(helpers.peak_tokens(steps))]
+    proc = subprocess.run(cmd, input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    done = [line for line in proc.stdout.splitlines() if line.startswith("done ")]
+    assert done == [f"done {s['step']}" for s in steps]
+    vocab = helpers.TINY["A"]["cfg"].vocab_size
+    outputs = {}
+    for s in steps:
+        f = out / f"{s['step']}.f32"
+        wanted = sum(len(e["want"]) for e in s["entries"])
+        assert f.exists() == (wanted > 0)
+        if wanted:
+            outputs[s["step"]] = torch.from_numpy(np.fromfile(f, dtype="<f4").reshape(wanted, vocab).copy())
+    rows = helpers.collect(steps, outputs)
+    tol = 1e-4 if dtype == "float32" else 5e-2
+    for (rid, pos), got in rows.items():
+        want = truth["A"][rid][pos]
+        assert float((got - want).abs().max()) <= tol * float(want.abs().max()), (rid, pos)
