@@ -1,0 +1,422 @@
+"""Decode and prefill throughput of the engine on one B200, Llama-3.2-1B sizes, random weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
+
+One JSON line on stdout.  ``value`` is decoded tokens per second at batch 8
+with every request's context ending at 4,096 tokens, timed on the device with
+CUDA events around exactly K decode steps of the step function (sampling
+kernel included, no host read-back inside the region).  ``e2e`` is the same
+workload through the Python entry point (scheduler -> engine.step -> commit):
+every step copies its inputs from pinned host memory and reads the sampled
+tokens back.  ``prefill`` is one 2,048-token prompt in one step; ``roofline``
+relates the decode step to the bytes it must read; ``points`` holds decode at
+batch 1 and 64.  Weights (2.47 GB) exceed the L2 cache, so every step streams
+them from HBM again.
+
+``--impl reference`` runs PrefixServe itself (installed under baseline/_ref)
+on the same model folder and workload through its own scheduler and engine.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+MODEL = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "vocab_size": 128256, "hidden_size": 2048,
+    "intermediate_size": 8192, "num_hidden_layers": 16, "num_attention_heads": 32, "num_key_value_heads": 8,
+    "head_dim": 64, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "max_position_embeddings": 131072, "tie_word_embeddings": True, "attention_bias": False, "mlp_bias": False,
+}
+FULL_LAYERS = 16
+CONTEXT = 4096
+PREFILL_TOKENS = 2048
+PAGE = 16
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def peaks() -> dict:
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        try:
+            raw = json.loads(f.read_text())
+            out = {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"]), "source": "measured"}
+            if "bf16_tflops_sustained" in raw:
+                out["bf16_tflops_sustained"] = float(raw["bf16_tflops_sustained"])
+            return out
+        except (KeyError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+# ------------------------------------------------------------------ model folder
+def write_model_folder(folder: Path, layers: int, seed: int = 0) -> None:
+    """config.json + model.safetensors with N(0, 0.02) bfloat16 weights, written with torch and safetensors only
+    (both arms read this folder through their own loaders)."""
+    import torch
+    from safetensors.torch import save_file
+
+    cfg = dict(MODEL, num_hidden_layers=layers)
+    h, i, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    q = cfg["num_attention_heads"] * cfg["head_dim"]
+    kv = cfg["num_key_value_heads"] * cfg["head_dim"]
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(seed)
+
+    def mat(*shape):
+        return (torch.randn(shape, device="cuda", generator=gen, dtype=torch.float32) * 0.02).to(torch.bfloat16).cpu()
+
+    tensors = {"model.embed_tokens.weight": mat(v, h), "model.norm.weight": torch.ones(h, dtype=torch.bfloat16)}
+    for n in range(layers):
+        p = f"model.layers.{n}."
+        tensors[p + "input_layernorm.weight"] = torch.ones(h, dtype=torch.bfloat16)
+        tensors[p + "post_attention_layernorm.weight"] = torch.ones(h, dtype=torch.bfloat16)
+        tensors[p + "self_attn.q_proj.weight"] = mat(q, h)
+        tensors[p + "self_attn.k_proj.weight"] = mat(kv, h)
+        tensors[p + "self_attn.v_proj.weight"] = mat(kv, h)
+        tensors[p + "self_attn.o_proj.weight"] = mat(h, q)
+        tensors[p + "mlp.gate_proj.weight"] = mat(i, h)
+        tensors[p + "mlp.up_proj.weight"] = mat(i, h)
+        tensors[p + "mlp.down_proj.weight"] = mat(h, i)
+    folder.mkdir(parents=True, exist_ok=True)
+    save_file(tensors, str(folder / "model.safetensors"), metadata={"format": "pt"})
+    (folder / "config.json").write_text(json.dumps(cfg))
+
+
+def weight_bytes(layers: int) -> int:
+    h, i, v = MODEL["hidden_size"], MODEL["intermediate_size"], MODEL["vocab_size"]
+    q = MODEL["num_attention_heads"] * MODEL["head_dim"]
+    kv = MODEL["num_key_value_heads"] * MODEL["head_dim"]
+    per_layer = (q + 2 * kv) * h + h * q + 3 * h * i + 2 * h
+    return 2 * (v * h + layers * per_layer + h)  # the tied table is read once (as the LM head)
+
+
+def kv_bytes_per_token(layers: int) -> int:
+    return layers * 2 * MODEL["num_key_value_heads"] * MODEL["head_dim"] * 2
+
+
+def prefill_flops(t: int, layers: int) -> float:
+    h, i, v = MODEL["hidden_size"], MODEL["intermediate_size"], MODEL["vocab_size"]
+    q = MODEL["num_attention_heads"] * MODEL["head_dim"]
+    kv = MODEL["num_key_value_heads"] * MODEL["head_dim"]
+    gemm = 2.0 * t * layers * (h * (q + 2 * kv) + q * h + 3 * h * i) + 2.0 * h * v  # logits for the last row only
+    attn = layers * 2.0 * t * (t + 1) * MODEL["head_dim"] * MODEL["num_attention_heads"]  # QK^T and PV, causal
+    return gemm + attn
+
+
+# ------------------------------------------------------------------------ clocks
+class ClockSampler:
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self) -> None:
+        self.samples: list[list[str]] = []
+        self._stop = threading.Event()
+        self._proc = None
+        self._thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self) -> None:
+        try:
+            self._proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                           "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            for line in self._proc.stdout:
+                if self._stop.is_set():
+                    break
+                self.samples.append([c.strip() for c in line.split(",")])
+        except OSError:
+            pass
+
+    def __enter__(self) -> "ClockSampler":
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self._stop.set()
+        if self._proc is not None:
+            self._proc.terminate()
+
+    def summary(self) -> dict:
+        mhz = sorted(int(s[0]) for s in self.samples if s and s[0].isdigit())
+        reasons = set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            for name, val in zip(names, s[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        mx = [int(s[1]) for s in self.samples if len(s) > 1 and s[1].isdigit()]
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+# ----------------------------------------------------------------------- own arm
+def run_own(args) -> dict:
+    import numpy as np
+    import torch
+
+    from prefixserve_b200.engine import Engine, EngineConfig, Scheduler, StepItem
+    from prefixserve_b200.ops import library
+    from prefixserve_b200.sampling import SamplingParams
+    from prefixserve_b200.sampling.sampler import choose_tokens
+
+    pk = peaks()
+    layers = args.layers
+    work = Path(tempfile.mkdtemp(prefix="psb200-bench-"))
+    try:
+        write_model_folder(work, layers)
+        rng = np.random.RandomState(0)
+        vocab = MODEL["vocab_size"]
+        max_b = max(args.batch, 64 if not args.skip_points else args.batch)
+        pool = max_b * (CONTEXT // PAGE) + 64
+        engine = Engine(EngineConfig(model_path=work, dtype=torch.bfloat16, max_num_seqs=max_b, max_prefill_tokens=PREFILL_TOKENS,
+                                     max_seq_len=CONTEXT, num_blocks=pool, page_size=PAGE, enable_prefix_cache=False))
+        runner, cache = engine.runner, engine.cache
+        greedy = SamplingParams()
+
+        def fill(batch: int, upto: int) -> list[int]:
+            """Opens ``batch`` requests and prefills each to ``upto`` tokens through the step function."""
+            slots = []
+            for _ in range(batch):
+                slot = cache.open()
+                at = 0
+                while at < upto:
+                    n = min(PREFILL_TOKENS, upto - at)
+                    cache.reserve(slot, at + n)
+                    runner.step([StepItem(slot, at, rng.randint(0, vocab, size=n).astype(np.int32), ())])
+                    cache.advance(slot, at + n)
+                    at += n
+                slots.append(slot)
+            return slots
+
+        def decode_steps(slots: list[int], n: int) -> None:
+            for _ in range(n):
+                items = []
+                for s in slots:
+                    p = cache.position(s)
+                    cache.reserve(s, p + 1)
+                    items.append(StepItem(s, p, rng.randint(0, vocab, size=1).astype(np.int32), (0,)))
+                logits = runner.step(items)
+                choose_tokens(logits, [greedy] * len(items), [it.start + 1 for it in items])
+                for it in items:
+                    cache.advance(it.slot, it.start + 1)
+
+        def time_decode(batch: int, steps: int, warmup: int) -> tuple[float, int, float]:
+            """ms per step (device), launches of this library's kernels in the timed region, mean context."""
+            slots = fill(batch, CONTEXT - steps - warmup)
+            decode_steps(slots, warmup)
+            ctx_sum = sum(cache.position(s) + 1 for s in slots) * steps + batch * steps * (steps - 1) // 2
+            torch.cuda.synchronize()
+            before = library.launches
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            decode_steps(slots, steps)
+            t1.record()
+            torch.cuda.synchronize()
+            launched = library.launches - before
+            for s in slots:
+                cache.close(s)
+            return t0.elapsed_time(t1) / steps, launched, ctx_sum / (batch * steps)
+
+        # ---- headline: decode at the default batch, device-timed, clocks sampled meanwhile
+        with ClockSampler() as clocks:
+            time.sleep(0.3)
+            ms_step, launches, mean_ctx = time_decode(args.batch, args.steps, args.warmup)
+            time.sleep(0.3)
+        value = args.batch / (ms_step * 1e-3)
+        step_bytes = weight_bytes(layers) + args.batch * mean_ctx * kv_bytes_per_token(layers)
+        achieved = step_bytes / (ms_step * 1e-3) / 1e9
+
+        # ---- end to end through the scheduler and engine.step (host tokens in and out)
+        sched = Scheduler(cache, chunk_size=PREFILL_TOKENS, stop_token_ids=())
+        total = args.steps + args.warmup
+        for r in range(args.batch):
+            sched.add_request(f"e2e-{r}", rng.randint(0, vocab, size=CONTEXT - total), total, ignore_eos=True)
+        decoding = 0
+        t_start = None
+        h2d = []
+        produced = 0
+        while sched.has_work():
+            batch = sched.schedule_step(PREFILL_TOKENS, args.batch)
+            is_decode = all(w.end - w.start == 1 for w in batch.work) and len(batch.work) == args.batch
+            if is_decode:
+                decoding += 1
+                if decoding == args.warmup + 1:
+                    torch.cuda.synchronize()
+                    t_start = time.perf_counter()
+            out = engine.step(batch)
+            if t_start is not None and is_decode:
+                produced += len(out)
+                h2d.append(runner.last_h2d_bytes)
+            sched.commit(batch, out)
+        torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t_start
+        e2e_steps = produced // args.batch
+        e2e = {"value": round(produced / e2e_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(sum(h2d) / max(len(h2d), 1)),
+               "d2h_bytes_per_step": 4 * args.batch, "steps": e2e_steps, "ms_per_step": round(1e3 * e2e_s / max(e2e_steps, 1), 4)}
+
+        # ---- prefill: one 2,048-token prompt in one step
+        def one_prefill() -> float:
+            slot = cache.open()
+            cache.reserve(slot, PREFILL_TOKENS)
+            toks = rng.randint(0, vocab, size=PREFILL_TOKENS).astype(np.int32)
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            t0.record()
+            logits = runner.step([StepItem(slot, 0, toks, (PREFILL_TOKENS - 1,))])
+            choose_tokens(logits, [greedy], [PREFILL_TOKENS])
+            t1.record()
+            torch.cuda.synchronize()
+            cache.close(slot)
+            return t0.elapsed_time(t1)
+
+        for _ in range(3):
+            one_prefill()
+        pf = sorted(one_prefill() for _ in range(10))
+        pf_ms = pf[len(pf) // 2]
+        flops = prefill_flops(PREFILL_TOKENS, layers)
+        prefill = {"value": round(PREFILL_TOKENS / (pf_ms * 1e-3), 1), "tokens": PREFILL_TOKENS, "ms": round(pf_ms, 4),
+                   "frac": round(flops / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4), "peak": f"{pk['bf16_tflops']} TFLOP/s of {pk['source']}"}
+
+        # ---- further points
+        points = {}
+        if not args.skip_points:
+            for b in (1, 64):
+                ms_b, _, _ = time_decode(b, min(args.steps, 64), 3)
+                points[f"decode_b{b}"] = round(b / (ms_b * 1e-3), 1)
+
+        return {
+            "metric": "decode tokens/s at batch 8, context 4096 (Llama-3.2-1B sizes, random weights)",
+            "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic: seeded uniform-random token ids, N(0,0.02) random weights",
+            "config": {
+                "model": "Llama-3.2-1B sizes", "layers": layers, "layers_full": FULL_LAYERS, "hidden": MODEL["hidden_size"],
+                "heads": MODEL["num_attention_heads"], "kv_heads": MODEL["num_key_value_heads"], "head_dim": MODEL["head_dim"],
+                "intermediate": MODEL["intermediate_size"], "vocab": MODEL["vocab_size"], "tied": True,
+                "global_batch": args.batch, "seq_len": CONTEXT, "page_size": PAGE, "prefill_tokens": PREFILL_TOKENS,
+                "parallelism": "single-gpu", "l2": "inputs larger than L2 (every step reads 2.47 GB of weights)",
+            },
+            "e2e": e2e,
+            "prefill": prefill,
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                         "frac": round(achieved / pk["hbm_gbs"], 4), "of": pk["source"], "bytes_per_step": int(step_bytes)},
+            "points": points,
+            "clocks": clocks.summary(),
+            "gpu_launches": launches,
+        }
+    finally:
+        shutil.rmtree(work, ignore_errors=True)
+
+
+# ----------------------------------------------------------------- reference arm
+def run_reference(args) -> dict:
+    ref = ROOT / "baseline" / "_ref"
+    if not (ref / "prefixserve").is_dir():
+        return {"impl": "reference", "unavailable": "baseline/_ref holds no install of the reference"}
+    sys.path.insert(0, str(ref))
+    try:
+        import numpy as np
+        import torch
+        from prefixserve.llama_engine import EngineConfig, LlamaEngine
+        from prefixserve.scheduler import Scheduler
+    except Exception as e:  # noqa: BLE001
+        return {"impl": "reference", "unavailable": f"the reference does not import here: {type(e).__name__}: {e}"[:300]}
+
+    work = Path(tempfile.mkdtemp(prefix="psb200-bench-ref-"))
+    try:
+        write_model_folder(work, FULL_LAYERS)
+        rng = np.random.RandomState(0)
+        vocab = MODEL["vocab_size"]
+        pool = args.batch * (CONTEXT // PAGE) + 64
+        engine, attention, why = None, None, []
+        for attention in ("flashinfer", "torch"):  # its default first, then its own other backend
+            try:
+                engine = LlamaEngine(EngineConfig(model_path=work, dtype=torch.bfloat16, attention=attention,
+                                                  max_num_seqs=args.batch, max_prefill_tokens=PREFILL_TOKENS,
+                                                  max_seq_len=CONTEXT, num_blocks=pool))
+                sched = Scheduler(engine.num_blocks, chunk_size=PREFILL_TOKENS, enable_prefix_cache=False)
+                sched.add_request("probe", rng.randint(0, vocab, size=40), 2, ignore_eos=True)
+                while sched.has_work():
+                    b = sched.schedule_step(PREFILL_TOKENS, args.batch)
+                    sched.commit(b, engine.step(b))
+                break
+            except Exception as e:  # noqa: BLE001
+                why.append(f"{attention}: {type(e).__name__}: {str(e)[:120]}")
+                engine = None
+        if engine is None:
+            return {"impl": "reference", "unavailable": "; ".join(why)[:400]}
+
+        total = args.steps + args.warmup
+        sched = Scheduler(engine.num_blocks, chunk_size=PREFILL_TOKENS, enable_prefix_cache=False)
+        for r in range(args.batch):
+            sched.add_request(f"r{r}", rng.randint(0, vocab, size=CONTEXT - total), total, ignore_eos=True)
+        decoding = produced = 0
+        t_start = None
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler() as clocks:
+            while sched.has_work():
+                batch = sched.schedule_step(PREFILL_TOKENS, args.batch)
+                is_decode = all(w.end - w.start == 1 for w in batch.work) and len(batch.work) == args.batch
+                if is_decode:
+                    decoding += 1
+                    if decoding == args.warmup + 1:
+                        torch.cuda.synchronize()
+                        e0.record()
+                        t_start = time.perf_counter()
+                out = engine.step(batch)
+                if t_start is not None and is_decode:
+                    produced += len(out)
+                sched.commit(batch, out)
+            e1.record()
+            torch.cuda.synchronize()
+            wall = time.perf_counter() - t_start
+        dev_ms = e0.elapsed_time(e1)
+        steps = produced // args.batch
+        return {
+            "impl": "reference", "metric": "decode tokens/s at batch 8, context 4096 (Llama-3.2-1B sizes, random weights)",
+            "value": round(produced / (dev_ms * 1e-3), 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": args.warmup,
+            "ms_per_step": round(dev_ms / max(steps, 1), 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic: seeded uniform-random token ids, N(0,0.02) random weights",
+            "config": {"model": "Llama-3.2-1B sizes", "layers": FULL_LAYERS, "global_batch": args.batch, "seq_len": CONTEXT,
+                       "attention_backend": attention, "parallelism": "single-gpu"},
+            "e2e": {"value": round(produced / wall, 1), "unit": "tokens/s", "h2d_bytes_per_step": None, "d2h_bytes_per_step": 8 * args.batch},
+            "clocks": clocks.summary(), "notes": "; ".join(why),
+        }
+    finally:
+        shutil.rmtree(work, ignore_errors=True)
+
+
+def main() -> int:
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=128)
+    p.add_argument("--warmup", type=int, default=8)
+    p.add_argument("--impl", choices=["own", "reference"], default="own")
+    p.add_argument("--batch", type=int, default=8)
+    p.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the full model (recorded in config)")
+    p.add_argument("--skip-points", action="store_true", help="leave out the batch-1 and batch-64 points")
+    args = p.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"unsupported": f"this engine runs on one GPU; --gpus {args.gpus} is not built", "n_gpus": args.gpus}))
+        return 2
+    result = run_reference(args) if args.impl == "reference" else run_own(args)
+    print(json.dumps(result))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

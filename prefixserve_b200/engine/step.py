@@ -52,6 +52,7 @@ class ModelRunner:
         self._copied = torch.cuda.Event()
         self._copy_pending = False
         self.steps_run = 0
+        self.last_h2d_bytes = 0  # size of the last step's single host-to-device copy
 
     # ------------------------------------------------------------------ checks
     def _check(self, items: Sequence[StepItem]) -> None:
@@ -141,6 +142,7 @@ class ModelRunner:
             at += b * w
 
         dev = host[:total].to(self.device, non_blocking=True)
+        self.last_h2d_bytes = 4 * total
         self._copied.record()
         self._copy_pending = True
 

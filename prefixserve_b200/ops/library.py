@@ -65,7 +65,12 @@ def declare(name: str, argtypes: list) -> None:
         fn.restype = c_int
 
 
+launches = 0  # kernels of this library launched so far (benchmarks report the difference over a timed region)
+
+
 def check(status: int, what: str) -> None:
+    global launches
+    launches += 1
     if status != 0:
         detail = lib().psb_last_error().decode(errors="replace")
         raise KernelError(f"{what}: {detail} (status {status})")

@@ -1,0 +1,183 @@
+"""Generation through the Python entry point, the scheduler and the command line (GPU)."""
+
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import plain_model
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parents[1]
+
+
+@pytest.fixture(scope="module")
+def sharp(tmp_path_factory):
+    """Tiny B with large weights: clear arg max, so token-exact comparison is meaningful."""
+    from prefixserve_b200.weights import write_random_model
+    folder = tmp_path_factory.mktemp("sharpB")
+    write_random_model(folder, helpers.TINY_B["cfg"], seed=11, std=0.2, gain_noise=0.1, dtype=torch.float32)
+    return folder, plain_model.read_folder(folder)
+
+
+def prompts_b():
+    vocab = helpers.TINY_B["cfg"].vocab_size
+    shared = helpers.random_tokens(vocab, 32, seed=1)
+    return [shared[:1], shared[:16], shared + helpers.random_tokens(vocab, 8, 2), shared + helpers.random_tokens(vocab, 38, 3)]
+
+
+def test_greedy_generation_matches_plain_in_float32(sharp):
+    from prefixserve_b200 import LLM, SamplingParams
+    folder, (cfg, tensors) = sharp
+    prompts = prompts_b()
+    llm = LLM(folder, dtype="float32", max_seq_len=256, num_blocks=24, max_running_requests=3, chunked_prefill_size=24)
+    got = llm.generate(prompts, SamplingParams(max_tokens=12, ignore_eos=True))
+    want = [plain_model.greedy(cfg, tensors, p, 12) for p in prompts]
+    assert got == want
+    llm.engine.cache.check()
+    st = llm.stats()
+    assert st.num_running == 0 and st.free_blocks + st.cached_blocks == 24
+    # the same prompts again: now the shared prefix is found in the cache, tokens unchanged
+    again = llm.generate(prompts, SamplingParams(max_tokens=12, ignore_eos=True))
+    assert again == want and llm.stats().cached_prompt_tokens > 0
+
+
+def test_preemption_and_recompute_keep_the_tokens(sharp):
+    from prefixserve_b200 import LLM, SamplingParams
+    folder, (cfg, tensors) = sharp
+    vocab = helpers.TINY_B["cfg"].vocab_size
+    prompts = [helpers.random_tokens(vocab, n, seed=40 + n) for n in (50, 45, 40)]
+    need = -(-(50 + 30) // 16)
+    llm = LLM(folder, dtype="float32", max_seq_len=256, num_blocks=need + 3, max_running_requests=3, chunked_prefill_size=32)
+    got = llm.generate(prompts, SamplingParams(max_tokens=30, ignore_eos=True))
+    assert llm.stats().preemptions > 0
+    assert got == [plain_model.greedy(cfg, tensors, p, 30) for p in prompts]
+    llm.engine.cache.check()
+
+
+def test_bfloat16_generation_teacher_forced(sharp):
+    """bfloat16 logits along the float32 path's own tokens stay close to float32 truth (the reference's criterion,
+    tests/gpu/test_engine_flashinfer.py:86-108 of PrefixServe)."""
+    from prefixserve_b200.engine import Engine, EngineConfig, Scheduler
+    folder, (cfg, tensors) = sharp
+    prompts = prompts_b()
+    truth_tokens = [plain_model.greedy(cfg, tensors, p, 10) for p in prompts]
+    engine = Engine(EngineConfig(model_path=folder, dtype=torch.bfloat16, max_num_seqs=4, max_prefill_tokens=24,
+                                 max_seq_len=256, num_blocks=32))
+    engine.capture_logits = True
+    sched = Scheduler(engine.cache, chunk_size=24)
+    for i, p in enumerate(prompts):
+        sched.add_request(f"r{i}", p, 10, ignore_eos=True)
+    rows = {f"r{i}": [] for i in range(len(prompts))}
+    while sched.has_work():
+        batch = sched.schedule_step(24, 4)
+        engine.step(batch)
+        forced = {}
+        for w in batch.work:
+            if w.samples:
+                rid = w.req.req_id
+                rows[rid].append(engine.last_logits[rid])
+                forced[rid] = truth_tokens[int(rid[1:])][len(w.req.output)]
+        sched.commit(batch, forced)
+    for i, p in enumerate(prompts):
+        seq = p + truth_tokens[i]
+        want = plain_model.forward(cfg, tensors, seq)[len(p) - 1: len(seq) - 1]
+        plain_bf16 = plain_model.forward(cfg, tensors, seq, dtype=torch.bfloat16)[len(p) - 1: len(seq) - 1]
+        got = torch.stack(rows[f"r{i}"])
+        ours, theirs = helpers.rel_err(got, want), helpers.rel_err(plain_bf16, want)
+        assert ours < 0.15 and ours <= 1.5 * theirs + 1e-3, (i, ours, theirs)
+
+
+def test_stop_ids_and_cached_pages_are_never_written(sharp):
+    from prefixserve_b200.engine import Engine, EngineConfig, Scheduler
+    folder, (cfg, tensors) = sharp
+    prompt = helpers.random_tokens(helpers.TINY_B["cfg"].vocab_size, 20, seed=9)
+    first = plain_model.greedy(cfg, tensors, prompt, 3)
+    engine = Engine(EngineConfig(model_path=folder, dtype=torch.float32, max_num_seqs=2, max_prefill_tokens=16,
+                                 max_seq_len=128, num_blocks=16))
+    sched = Scheduler(engine.cache, chunk_size=16, stop_token_ids=[first[2]])
+    sched.add_request("a", prompt, 10)
+    out = []
+    while sched.has_work():
+        batch = sched.schedule_step(16, 2)
+        for w in batch.work:  # a step never writes a position whose page the prefix cache owns
+            table = sched.block_table(w.req)
+            for pos in range(w.start, w.end):
+                assert not engine.cache.is_cached(table[pos // 16])
+        res = sched.commit(batch, engine.step(batch))
+        out += list(res.new_tokens.values())
+    assert out == first[: first.index(first[2]) + 1]  # the stop token is kept, nothing after it
+
+
+def test_long_decode_and_first_tokens(sharp):
+    """A request decoded for hundreds of steps, and the logits of the very first tokens of a sequence."""
+    from prefixserve_b200.engine.replay import Replayer
+    folder, (cfg, tensors) = sharp
+    toks = helpers.random_tokens(helpers.TINY_B["cfg"].vocab_size, 300, seed=77)
+    rp = Replayer(folder, "float32", 320)
+    rows = []
+    for i, t in enumerate(toks):
+        rows.append(torch.from_numpy(rp.run_step({"step": i, "entries": [{"id": "x", "tokens": [t], "want": [0]}], "end": []})[0].copy()))
+    got = torch.stack(rows)
+    want = plain_model.forward(cfg, tensors, toks)
+    for pos in (0, 1, 2, 15, 16, 17, 299):
+        assert float((got[pos] - want[pos]).abs().max()) <= 1e-4 * float(want[pos].abs().max()), pos
+    assert float((got - want).abs().max()) <= 1e-4 * float(want.abs().max())
+
+
+def test_temperature_sampling_is_reproducible_and_batch_independent(sharp):
+    from prefixserve_b200 import LLM, SamplingParams
+    folder, _ = sharp
+    prompts = prompts_b()
+    sp = SamplingParams(temperature=0.9, seed=123, max_tokens=8, ignore_eos=True)
+    llm = LLM(folder, dtype="float32", max_seq_len=256, num_blocks=32, max_running_requests=4, chunked_prefill_size=24)
+    together = llm.generate(prompts, sp)
+    alone = [llm.generate([p], sp)[0] for p in prompts]
+    assert together == alone
+    assert together != llm.generate(prompts, SamplingParams(max_tokens=8, ignore_eos=True))
+    other_seed = llm.generate(prompts, SamplingParams(temperature=0.9, seed=124, max_tokens=8, ignore_eos=True))
+    assert other_seed != together
+
+
+def test_command_line(sharp, tmp_path):
+    folder, (cfg, tensors) = sharp
+    prompt = [3, 1, 4, 1, 5, 9, 2, 6]
+    cmd = [sys.executable, "-m", "prefixserve_b200", "--model", str(folder), "--dtype", "float32", "--max-seq-len", "128",
+           "--num-blocks", "16", "--max-running-requests", "2", "--chunked-prefill-size", "16", "--max-tokens", "5",
+           "--ignore-eos", "--prompt-ids", ",".join(map(str, prompt))]
+    proc = subprocess.run(cmd, capture_output=True, text=True, cwd=ROOT, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = [json.loads(ln) for ln in proc.stdout.splitlines() if ln.startswith("{")]
+    assert lines[0]["output_ids"] == plain_model.greedy(cfg, tensors, prompt, 5)
+    assert lines[1]["stats"]["num_running"] == 0
+
+
+def test_engine_refuses_what_it_cannot_run(sharp):
+    from prefixserve_b200.engine import Engine, EngineConfig, EngineError, StepItem
+    folder, _ = sharp
+    engine = Engine(EngineConfig(model_path=folder, dtype=torch.float32, max_num_seqs=2, max_prefill_tokens=16,
+                                 max_seq_len=64, num_blocks=8))
+    cache, runner = engine.cache, engine.runner
+    slot = cache.open()
+    toks = np.arange(5, dtype=np.int32)
+    with pytest.raises(EngineError, match="no pages"):
+        runner.step([StepItem(slot, 0, toks, (4,))])
+    cache.reserve(slot, 5)
+    with pytest.raises(EngineError, match="start at"):
+        runner.step([StepItem(slot, 3, toks, ())])
+    with pytest.raises(EngineError, match="token id"):
+        runner.step([StepItem(slot, 0, toks + 100000, ())])
+    with pytest.raises(EngineError, match="wanted offset"):
+        runner.step([StepItem(slot, 0, toks, (5,))])
+    with pytest.raises(EngineError, match="twice"):
+        runner.step([StepItem(slot, 0, toks, ()), StepItem(slot, 0, toks, ())])
+    with pytest.raises(EngineError, match="not open"):
+        runner.step([StepItem(1, 0, toks, ())])
+    assert runner.step([StepItem(slot, 0, toks, (0, 4))]).shape == (2, helpers.TINY_B["cfg"].vocab_size)
+    with pytest.raises(ValueError, match="max_seq_len"):
+        Engine(EngineConfig(model_path=folder, dtype=torch.float32, max_seq_len=100000, num_blocks=8))

@@ -1,0 +1,310 @@
+"""Each part alone, and models put together from parts in ways Llama does not use: a run list that names a layer
+twice, a layer that reads another layer's cache, a windowed attention group beside a full one, and a toy mixer with
+a state of its own that is defined and registered here, without any change to the package (GPU)."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import plain_model
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda")
+
+
+def close(got, want, dtype):
+    tol = 1e-4 if dtype == torch.float32 else 3e-2
+    scale = float(want.abs().max())
+    assert float((got.float().cpu() - want.float().cpu()).abs().max()) <= tol * max(scale, 1e-6), \
+        (float((got.float().cpu() - want.float().cpu()).abs().max()), scale)
+
+
+def fake_ctx(dtype, t=1):
+    from prefixserve_b200.parts import StepContext
+    z = torch.zeros(t, dtype=torch.int32, device=DEV)
+    return StepContext(num_tokens=t, num_items=1, compute_dtype=dtype, device=DEV, items=[], token_ids=z, positions=z,
+                       token_item=z, item_start=z, kv_len=z, slots=z, block_tables={}, max_new_tokens=t, max_kv_len=t,
+                       all_decode=False)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_part(dtype):
+    from prefixserve_b200.parts import make
+    from prefixserve_b200.config import part
+    norm = make("norm", part("rms", size=72, eps=1e-4))
+    assert list(norm.param_specs()) == ["weight"] and norm.param_specs()["weight"].role == "vector"
+    gain = 1 + 0.2 * torch.randn(72)
+    norm.load({"weight": gain.to(DEV)}, compute_dtype=dtype, device=DEV)
+    h = torch.randn(9, 72, device=DEV)
+    delta = torch.randn(9, 72, device=DEV).to(dtype)
+    want = plain_model.rms_norm((h + delta.float()).cpu(), gain, 1e-4)
+    x = norm.forward(h, delta, fake_ctx(dtype, 9))
+    assert x.dtype == dtype
+    close(x, want, dtype)
+
+
+def test_position_part_matches_plain_tables():
+    from prefixserve_b200.parts import make
+    from prefixserve_b200.config import part
+    cfg = {"num_attention_heads": 2, "hidden_size": 64, "head_dim": 32, "rope_theta": 500000.0,
+           "rope_scaling": {"rope_type": "llama3", "factor": 4.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                            "original_max_position_embeddings": 64}}
+    pos = make("position", part("rope", head_dim=32, theta=500000.0, layout="half",
+                                scaling={"kind": "llama3", "factor": 4.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                                         "original_max_positions": 64}))
+    pos.prepare(max_positions=300, compute_dtype=torch.float32, device=DEV)
+    cos, sin = plain_model.rope_tables(cfg, torch.arange(300), torch.float32)
+    assert torch.equal(pos.cos.cpu(), cos[:, :16]) and torch.equal(pos.sin.cpu(), sin[:, :16])
+    assert pos.cos.dtype == torch.float32
+    none = make("position", part("none"))
+    assert none.cos is None and not none.rotates
+    with pytest.raises(ValueError):
+        make("position", part("rope", head_dim=32, theta=1.0, layout="interleaved"))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_ffn_embedding_and_head_parts(dtype):
+    from prefixserve_b200.parts import make
+    from prefixserve_b200.config import part
+    ffn = make("ffn", part("gated_mlp", hidden_size=40, intermediate_size=56, activation="silu"))
+    w = {k: (0.3 * torch.randn(*s.shape)).to(dtype) for k, s in ffn.param_specs().items()}
+    ffn.load({k: v.to(DEV) for k, v in w.items()}, compute_dtype=dtype, device=DEV)
+    x = torch.randn(11, 40).to(dtype)
+    want = plain_model.gated_mlp(x.float(), w["gate_proj"].float(), w["up_proj"].float(), w["down_proj"].float())
+    close(ffn.forward(x.to(DEV), fake_ctx(dtype, 11)), want, dtype)
+    with pytest.raises(ValueError):
+        make("ffn", part("gated_mlp", hidden_size=4, intermediate_size=4, activation="gelu"))
+
+    emb = make("embedding", part("token_embedding", vocab_size=33, hidden_size=40))
+    table = torch.randn(33, 40).to(dtype)
+    emb.load({"weight": table.to(DEV)}, compute_dtype=dtype, device=DEV)
+    ids = torch.tensor([0, 32, 5, 5], dtype=torch.int32, device=DEV)
+    assert torch.equal(emb.forward(ids).cpu(), table[[0, 32, 5, 5]].float())
+
+    head = make("head", part("lm_head", vocab_size=33, hidden_size=40, tied=True))
+    assert head.param_specs() == {}
+    head.tie(emb.table)
+    logits = head.forward(x[:3].to(DEV))
+    assert logits.dtype == torch.float32
+    close(logits, x[:3].float() @ table.float().t(), dtype)
+
+
+# ---- whole models from parts -------------------------------------------------------------------------
+
+def build(spec, dtype, seed=0, pages=64, std=0.15):
+    from prefixserve_b200.cache import CacheManager
+    from prefixserve_b200.engine import ModelRunner
+    from prefixserve_b200.parts import build_model
+    from prefixserve_b200.weights import convert_tensors, random_tensors
+    model = build_model(spec)
+    table = model.param_table()
+    raw = random_tensors(table, seed, std=std, gain_noise=0.1, dtype=torch.float32)
+    model.load(convert_tensors(raw, table, compute_dtype=dtype, device=DEV), compute_dtype=dtype, device=DEV, max_positions=512)
+    cache = CacheManager(model.cache_needs(), num_pages=pages, num_slots=4, max_seq_len=512, dtype=dtype, device=DEV,
+                         enable_prefix_cache=False)
+    return model, raw, cache, ModelRunner(model, cache, device=DEV)
+
+
+def run_cut(runner, cache, tokens, cuts):
+    """Feeds one request in portions; returns logits of every position."""
+    from prefixserve_b200.engine import StepItem
+    slot = cache.open()
+    rows, at = [], 0
+    for n in cuts:
+        n = min(n, len(tokens) - at)
+        if n <= 0:
+            break
+        assert cache.reserve(slot, at + n)
+        rows.append(runner.step([StepItem(slot, at, np.asarray(tokens[at:at + n], dtype=np.int32), tuple(range(n)))]).cpu())
+        cache.advance(slot, at + n)
+        at += n
+    cache.close(slot)
+    cache.check()
+    return torch.cat(rows)
+
+
+def attn_spec(h, hq, hkv, d, window=None, own_kv=True, rope=True):
+    from prefixserve_b200.config import part
+    position = part("rope", head_dim=d, theta=10000.0, scaling=None, layout="half") if rope else part("none")
+    return part("attention", hidden_size=h, num_heads=hq, num_kv_heads=hkv, head_dim=d, position=position, window=window,
+                own_kv=own_kv)
+
+
+def plain_attention_layer(x, w, prefix, hq, hkv, d, window, kv_from=None, rope=True):
+    """Returns (output, (k, v)); with kv_from the layer has no key/value projection and reads the given ones."""
+    t = x.shape[0]
+    q = (x @ w[prefix + "q_proj"].t()).view(t, hq, d)
+    cfg = {"num_attention_heads": hq, "hidden_size": hq * d, "head_dim": d, "rope_theta": 10000.0}
+    cos, sin = plain_model.rope_tables(cfg, torch.arange(t), torch.float32)
+    cos, sin = cos[:, None, :], sin[:, None, :]
+    if rope:
+        q = plain_model.apply_rope(q, cos, sin)
+    if kv_from is None:
+        k = (x @ w[prefix + "k_proj"].t()).view(t, hkv, d)
+        if rope:
+            k = plain_model.apply_rope(k, cos, sin)
+        v = (x @ w[prefix + "v_proj"].t()).view(t, hkv, d)
+    else:
+        k, v = kv_from
+    o = plain_model.causal_attention(q, k, v, window=window)
+    return o.reshape(t, hq * d) @ w[prefix + "o_proj"].t(), (k, v)
+
+
+def plain_forward(spec, w, tokens, mixers):
+    """Whole-sequence float32 forward of a model given as a run list; ``mixers[layer]`` computes that layer's mixer."""
+    x_ids = torch.tensor(tokens)
+    h = w["embedding.weight"][x_ids]
+    kept = {}
+    for call in spec.schedule:
+        p = f"layers.{call.layer}."
+        layer = spec.layers[call.layer]
+        x = plain_model.rms_norm(h, w[p + "mixer_norm.weight"], layer.mixer_norm["eps"])
+        out, keep = mixers[call.layer](x, w, p + "mixer.", kept.get(call.cache) if not call.writes_cache else None)
+        if call.writes_cache:
+            kept[call.cache] = keep
+        h = h + out
+        x = plain_model.rms_norm(h, w[p + "ffn_norm.weight"], layer.ffn_norm["eps"])
+        h = h + plain_model.gated_mlp(x, w[p + "ffn.gate_proj"], w[p + "ffn.up_proj"], w[p + "ffn.down_proj"])
+    h = plain_model.rms_norm(h, w["final_norm.weight"], spec.final_norm["eps"])
+    head = w["embedding.weight"] if spec.head["tied"] else w["head.weight"]
+    return h @ head.t()
+
+
+def toy_model_spec(layers, schedule, h=48, vocab=97):
+    from prefixserve_b200.config import ModelSpec, part
+    return ModelSpec(architecture="ToyFromParts", vocab_size=vocab, hidden_size=h, max_positions=512,
+                     embedding=part("token_embedding", vocab_size=vocab, hidden_size=h), layers=tuple(layers),
+                     schedule=tuple(schedule), final_norm=part("rms", size=h, eps=1e-5),
+                     head=part("lm_head", vocab_size=vocab, hidden_size=h, tied=False))
+
+
+def layer_of(mixer, h=48, inter=64, eps=1e-5):
+    from prefixserve_b200.config import LayerSpec, part
+    return LayerSpec(mixer=mixer, ffn=part("gated_mlp", hidden_size=h, intermediate_size=inter, activation="silu"),
+                     mixer_norm=part("rms", size=h, eps=eps), ffn_norm=part("rms", size=h, eps=eps * 3))
+
+
+CUTS = [[200], [150] + [1] * 50, [7, 2, 16, 3, 2, 5, 17, 2, 31, 4] * 3]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_run_list_with_shared_weights_shared_cache_and_a_window(dtype):
+    """Layer 0 (full attention) runs twice with a cache entry each; layer 1 (window 24, no rotation) has a group of
+    pages of its own; layer 2 has no key/value projection and reads the cache entry layer 0 wrote first."""
+    from prefixserve_b200.config import LayerCall
+    h, hq, hkv, d = 48, 3, 1, 16
+    layers = [layer_of(attn_spec(h, hq, hkv, d)), layer_of(attn_spec(h, 2, 2, 32, window=24, rope=False)),
+              layer_of(attn_spec(h, hq, hkv, d, own_kv=False))]
+    schedule = [LayerCall(0, 0), LayerCall(1, 1), LayerCall(0, 2), LayerCall(2, 0, writes_cache=False)]
+    spec = toy_model_spec(layers, schedule)
+    model, raw, cache, runner = build(spec, dtype)
+    assert len(cache.groups) == 2 and cache.entry_group == [0, 1, 0]
+    assert "layers.2.mixer.k_proj" not in model.param_table()
+    mixers = {
+        0: lambda x, w, p, kv: plain_attention_layer(x, w, p, hq, hkv, d, None),
+        1: lambda x, w, p, kv: plain_attention_layer(x, w, p, 2, 2, 32, 24, rope=False),
+        2: lambda x, w, p, kv: plain_attention_layer(x, w, p, hq, hkv, d, None, kv_from=kv),
+    }
+    tokens = helpers.random_tokens(97, 200, seed=5)
+    want = plain_forward(spec, raw, tokens, mixers)
+    for cuts in CUTS:
+        got = run_cut(runner, cache, tokens, cuts)
+        if dtype == torch.float32:
+            close(got, want, dtype)
+        else:
+            assert helpers.rel_err(got, want) < 0.05
+    assert cache.free_pages(0) == 64 and cache.free_pages(1) == 64
+
+
+# ---- a toy mixer with a state of its own, defined here ---------------------------------------------------
+
+DECAY = 0.6
+
+
+def register_toy():
+    from prefixserve_b200 import ops
+    from prefixserve_b200.parts import CacheNeed, FixedState, Mixer, ParamSpec, register_mixer
+
+    class DecayingSum(Mixer):
+        """s_t = DECAY * s_(t-1) + x_t per request (float32 state [H] in the request's slot); y_t = s_t W^T."""
+
+        def __init__(self, params):
+            super().__init__(params)
+            self.h = int(params["hidden_size"])
+
+        def param_specs(self):
+            return {"mix": ParamSpec((self.h, self.h))}
+
+        def cache_need(self):
+            return CacheNeed(state=FixedState((self.h,), torch.float32))
+
+        def load(self, tensors, *, compute_dtype, device):
+            self.w = tensors["mix"].contiguous()
+
+        def forward(self, x, ctx, cache):
+            s_all = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+            for item in ctx.items:  # a state is carried from where the request's last step left it
+                s = cache.state[item.slot]
+                n = item.end - item.start
+                for j in range(n):
+                    s = DECAY * s + x[item.first_token + j].float()
+                    s_all[item.first_token + j] = s
+                cache.state[item.slot] = s
+            return ops.linear(s_all.to(x.dtype), self.w)
+
+    register_mixer("decaying_sum", DecayingSum, replace=True)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_toy_mixer_with_state_is_registered_built_and_stepped(dtype):
+    from prefixserve_b200.config import LayerCall, part
+    from prefixserve_b200.engine import StepItem
+    register_toy()
+    h = 48
+    layers = [layer_of(attn_spec(h, 3, 3, 16)), layer_of(part("decaying_sum", hidden_size=h))]
+    spec = toy_model_spec(layers, [LayerCall(0, 0), LayerCall(1, 1)])
+    model, raw, cache, runner = build(spec, dtype, seed=4, std=0.1)
+    assert cache.entry_group == [0, None] and cache.state[1].shape == (4, h) and not cache.prefix_cache_possible
+
+    def toy(x, w, p, kv):
+        s = torch.zeros(h)
+        out = []
+        for t in range(x.shape[0]):
+            s = DECAY * s + x[t]
+            out.append(s)
+        return torch.stack(out) @ w[p + "mix"].t(), None
+
+    mixers = {0: lambda x, w, p, kv: plain_attention_layer(x, w, p, 3, 3, 16, None), 1: toy}
+    seqs = [helpers.random_tokens(97, n, seed=20 + n) for n in (60, 45)]
+    wants = [plain_forward(spec, raw, s, mixers) for s in seqs]
+    for cuts in ([60], [40] + [1] * 20, [7, 2, 16, 3, 2, 5, 17, 2, 6]):
+        for toks, want in zip(seqs, wants):
+            got = run_cut(runner, cache, toks, cuts)  # the slot is reused: its state must start from zero again
+            if dtype == torch.float32:
+                close(got, want, dtype)
+            else:
+                assert helpers.rel_err(got, want) < 0.05
+    # two requests interleaved in one batch keep their states apart
+    a, b = cache.open(), cache.open()
+    rows = {a: [], b: []}
+    pa = pb = 0
+    for na, nb in ((5, 1), (1, 9), (20, 1), (1, 1), (33, 33)):
+        items = []
+        for slot, toks, at, n in ((a, seqs[0], pa, na), (b, seqs[1], pb, nb)):
+            n = min(n, len(toks) - at)
+            cache.reserve(slot, at + n)
+            items.append(StepItem(slot, at, np.asarray(toks[at:at + n], dtype=np.int32), tuple(range(n))))
+        out = runner.step(items).cpu()
+        rows[a].append(out[: len(items[0].tokens)])
+        rows[b].append(out[len(items[0].tokens):])
+        pa, pb = pa + len(items[0].tokens), pb + len(items[1].tokens)
+        cache.advance(a, pa), cache.advance(b, pb)
+    for slot, want in ((a, wants[0]), (b, wants[1])):
+        got = torch.cat(rows[slot])
+        if dtype == torch.float32:
+            close(got, want[: got.shape[0]], dtype)
+        else:
+            assert helpers.rel_err(got, want[: got.shape[0]]) < 0.05
