@@ -242,12 +242,13 @@ def run_own(args) -> dict:
         sched = Scheduler(cache, chunk_size=PREFILL_TOKENS, stop_token_ids=())
         total = args.steps + args.warmup
         for r in range(args.batch):
-            sched.add_request(f"e2e-{r}", rng.randint(0, vocab, size=CONTEXT - total), total, ignore_eos=True)
-        decoding = 0
+            # prompts end so that the timed steps finish at CONTEXT; the staggered prefill costs a few decode steps
+            sched.add_request(f"e2e-{r}", rng.randint(0, vocab, size=CONTEXT - total - args.batch - 2),
+                              total + args.batch + 2, ignore_eos=True)
+        decoding = produced = e2e_steps = 0
         t_start = None
         h2d = []
-        produced = 0
-        while sched.has_work():
+        while sched.has_work() and e2e_steps < args.steps:
             batch = sched.schedule_step(PREFILL_TOKENS, args.batch)
             is_decode = all(w.end - w.start == 1 for w in batch.work) and len(batch.work) == args.batch
             if is_decode:
@@ -256,13 +257,15 @@ def run_own(args) -> dict:
                     torch.cuda.synchronize()
                     t_start = time.perf_counter()
             out = engine.step(batch)
-            if t_start is not None and is_decode:
+            if t_start is not None:
                 produced += len(out)
+                e2e_steps += 1
                 h2d.append(runner.last_h2d_bytes)
             sched.commit(batch, out)
         torch.cuda.synchronize()
         e2e_s = time.perf_counter() - t_start
-        e2e_steps = produced // args.batch
+        for r in range(args.batch):
+            sched.free_request(f"e2e-{r}")
         e2e = {"value": round(produced / e2e_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(sum(h2d) / max(len(h2d), 1)),
                "d2h_bytes_per_step": 4 * args.batch, "steps": e2e_steps, "ms_per_step": round(1e3 * e2e_s / max(e2e_steps, 1), 4)}
 
@@ -361,12 +364,13 @@ def run_reference(args) -> dict:
         total = args.steps + args.warmup
         sched = Scheduler(engine.num_blocks, chunk_size=PREFILL_TOKENS, enable_prefix_cache=False)
         for r in range(args.batch):
-            sched.add_request(f"r{r}", rng.randint(0, vocab, size=CONTEXT - total), total, ignore_eos=True)
-        decoding = produced = 0
+            sched.add_request(f"r{r}", rng.randint(0, vocab, size=CONTEXT - total - args.batch - 2),
+                              total + args.batch + 2, ignore_eos=True)
+        decoding = produced = steps = 0
         t_start = None
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with ClockSampler() as clocks:
-            while sched.has_work():
+            while sched.has_work() and steps < args.steps:
                 batch = sched.schedule_step(PREFILL_TOKENS, args.batch)
                 is_decode = all(w.end - w.start == 1 for w in batch.work) and len(batch.work) == args.batch
                 if is_decode:
@@ -376,14 +380,14 @@ def run_reference(args) -> dict:
                         e0.record()
                         t_start = time.perf_counter()
                 out = engine.step(batch)
-                if t_start is not None and is_decode:
+                if t_start is not None:
                     produced += len(out)
+                    steps += 1
                 sched.commit(batch, out)
             e1.record()
             torch.cuda.synchronize()
             wall = time.perf_counter() - t_start
         dev_ms = e0.elapsed_time(e1)
-        steps = produced // args.batch
         return {
             "impl": "reference", "metric": "decode tokens/s at batch 8, context 4096 (Llama-3.2-1B sizes, random weights)",
             "value": round(produced / (dev_ms * 1e-3), 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": args.warmup,

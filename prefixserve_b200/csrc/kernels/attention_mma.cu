@@ -1,0 +1,485 @@
+// bfloat16 attention over the paged cache on the tensor cores (mma.sync m16n8k16,
+// float32 accumulation, float32 online softmax), for prefill portions and for
+// decode.  Keys and values go from global memory straight into MMA operand
+// registers with 16-byte loads: no shared-memory staging.  That works because a
+// dot product does not care about the order of its terms:
+//  * QK^T: lane (g, t) of a quad-row loads 8 consecutive head dims of key g; the
+//    query fragment is loaded with the same permutation of head dims.
+//  * PV: lane (g, t) loads, for tokens {2t, 2t+1, 2t+8, 2t+9} of a 16-key tile, the
+//    D/8 consecutive head dims starting at g*D/8; output column n of d-tile j is
+//    then head dim n*D/8 + j, so each lane ends up owning D/4 consecutive dims.
+// A warp therefore reads whole 64..256-byte runs of each key/value row, coalesced.
+//
+// Rows of the score matrix are (token, query head in the group) pairs of ONE
+// key/value head, so keys and values are read once per group of query heads.
+//
+// Two kernels:
+//  * prefill: a CTA owns 128 rows of one item (4 warps x 32 rows), each warp walks
+//    the keys its rows may see (causal, optional window);
+//  * decode: a CTA owns one (item, key/value head, key range); its 4 warps take
+//    16-key tiles in turn and merge at the end; key ranges of one item are merged
+//    by a second small kernel (split-KV).  Only items that bring exactly one token.
+//
+// Math as in the generic kernel (prefixserve/model/attention.py:68-121 of
+// PrefixServe): scores * scale, key j visible to position p iff j <= p (and
+// j > p - window), softmax in float32, probabilities rounded to bfloat16 before
+// the PV product (as the reference's probs.to(dtype), :119).
+//
+// Cache layout of one entry: [num_pages, 2, hkv, page_size, D], page_size a multiple of 16.
+#include <cfloat>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int WARPS = 4;
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ uint4 ldg16(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+
+// One 16-key tile in operand order.
+template <int D>
+struct KVTile {
+  uint4 k[2][D / 32];  // [key half (keys g and g+8)][chunk of 32 head dims]
+  uint4 v[4][D / 64];  // [token slot 2t, 2t+1, 2t+8, 2t+9][16-byte piece of this lane's D/8 dims]
+};
+
+// kp/vp point at key 0 of the tile for this key/value head; rows are D apart.
+// Keys at index >= valid (counted from the tile's first key) are read as zeros.
+template <int D>
+__device__ __forceinline__ void load_tile(KVTile<D>& tile, const __nv_bfloat16* kp, const __nv_bfloat16* vp, int valid,
+                                          int g, int t) {
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int key = half * 8 + g;
+#pragma unroll
+    for (int c = 0; c < D / 32; ++c) tile.k[half][c] = key < valid ? ldg16(kp + key * D + c * 32 + t * 8) : zero;
+  }
+#pragma unroll
+  for (int s = 0; s < 4; ++s) {
+    const int key = 2 * t + (s & 1) + (s >> 1) * 8;
+#pragma unroll
+    for (int c = 0; c < D / 64; ++c) tile.v[s][c] = key < valid ? ldg16(vp + key * D + g * (D / 8) + c * 8) : zero;
+  }
+}
+
+// Query fragments of one 16-row tile, permuted like the keys.  row0/row1: pointers to the rows g and g+8 (or null).
+template <int D>
+__device__ __forceinline__ void load_q(uint32_t (&qa)[D / 16][4], const __nv_bfloat16* row0, const __nv_bfloat16* row1, int t) {
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+  for (int c = 0; c < D / 32; ++c) {
+    const uint4 x = row0 ? ldg16(row0 + c * 32 + t * 8) : zero;
+    const uint4 z = row1 ? ldg16(row1 + c * 32 + t * 8) : zero;
+    qa[2 * c][0] = x.x; qa[2 * c][1] = z.x; qa[2 * c][2] = x.y; qa[2 * c][3] = z.y;
+    qa[2 * c + 1][0] = x.z; qa[2 * c + 1][1] = z.z; qa[2 * c + 1][2] = x.w; qa[2 * c + 1][3] = z.w;
+  }
+}
+
+// Running softmax state of the two rows (g, g+8) this lane sees of a 16-row tile.
+template <int D>
+struct RowState {
+  float m[2];          // running maximum, in the scaled log2 domain
+  float l[2];          // this lane's part of the running sum
+  float o[D / 8][4];   // output accumulators, d-tile j: {row g: n=2t, 2t+1; row g+8: n=2t, 2t+1}
+  __device__ __forceinline__ void init() {
+    m[0] = m[1] = -INFINITY;
+    l[0] = l[1] = 0.f;
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+  }
+};
+
+// Scores of 16 rows x 16 keys; s[half][0..1] row g, s[half][2..3] row g+8; key = half*8 + 2t + (i&1).
+template <int D>
+__device__ __forceinline__ void scores(float (&s)[2][4], const uint32_t (&qa)[D / 16][4], const KVTile<D>& tile) {
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    s[half][0] = s[half][1] = s[half][2] = s[half][3] = 0.f;
+#pragma unroll
+    for (int c = 0; c < D / 32; ++c) {
+      mma_bf16(s[half], qa[2 * c], tile.k[half][c].x, tile.k[half][c].y);
+      mma_bf16(s[half], qa[2 * c + 1], tile.k[half][c].z, tile.k[half][c].w);
+    }
+  }
+}
+
+// Folds one tile's (already masked: -inf where hidden) scores into the running state and accumulates P.V.
+template <int D>
+__device__ __forceinline__ void fold(RowState<D>& st, float (&s)[2][4], const KVTile<D>& tile, float sl2) {
+  float p[2][4];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    float mx = fmaxf(fmaxf(s[0][2 * r], s[0][2 * r + 1]), fmaxf(s[1][2 * r], s[1][2 * r + 1]));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(st.m[r], mx * sl2);
+    const float m_safe = m_new == -INFINITY ? 0.f : m_new;  // a row that has seen nothing yet
+    const float alpha = exp2f(st.m[r] - m_safe);
+    st.m[r] = m_new;
+    float sum = 0.f;
+#pragma unroll
+    for (int half = 0; half < 2; ++half)
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const float e = exp2f(fmaf(s[half][2 * r + i], sl2, -m_safe));
+        p[half][2 * r + i] = e;
+        sum += e;
+      }
+    st.l[r] = st.l[r] * alpha + sum;
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) {
+      st.o[j][2 * r] *= alpha;
+      st.o[j][2 * r + 1] *= alpha;
+    }
+  }
+  uint32_t pa[4];
+  pa[0] = pack_bf16(p[0][0], p[0][1]);
+  pa[1] = pack_bf16(p[0][2], p[0][3]);
+  pa[2] = pack_bf16(p[1][0], p[1][1]);
+  pa[3] = pack_bf16(p[1][2], p[1][3]);
+  const uint32_t* v0 = reinterpret_cast<const uint32_t*>(&tile.v[0][0]);
+  const uint32_t* v1 = reinterpret_cast<const uint32_t*>(&tile.v[1][0]);
+  const uint32_t* v2 = reinterpret_cast<const uint32_t*>(&tile.v[2][0]);
+  const uint32_t* v3 = reinterpret_cast<const uint32_t*>(&tile.v[3][0]);
+#pragma unroll
+  for (int j = 0; j < D / 8; ++j) {
+    const uint32_t sel = (j & 1) ? 0x7632u : 0x5410u;
+    const uint32_t b0 = __byte_perm(v0[j >> 1], v1[j >> 1], sel);
+    const uint32_t b1 = __byte_perm(v2[j >> 1], v3[j >> 1], sel);
+    mma_bf16(st.o[j], pa, b0, b1);
+  }
+}
+
+// Hides keys the row may not see.  key0: absolute position of the tile's first key; pos[r]/lo[r]: the row's own
+// position and its lowest visible key.
+__device__ __forceinline__ void mask_tile(float (&s)[2][4], int key0, int t, const int (&pos)[2], const int (&lo)[2]) {
+#pragma unroll
+  for (int half = 0; half < 2; ++half)
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int key = key0 + half * 8 + 2 * t + i;
+        if (key > pos[r] || key < lo[r]) s[half][2 * r + i] = -INFINITY;
+      }
+}
+
+__device__ __forceinline__ const __nv_bfloat16* tile_ptr(const __nv_bfloat16* kv, const int32_t* pages, int key0, int page_size,
+                                                          int hkv, int h, int D) {
+  const int page = pages[key0 / page_size];
+  return kv + ((size_t)page * 2 * hkv + h) * (size_t)page_size * D + (size_t)(key0 % page_size) * D;
+}
+
+// --------------------------------------------------------------------------------------------- prefill
+// PREFILL_MT: 16-row tiles per warp (2 at head size 64; 1 at 128, where two would spill registers).
+template <int D, int PREFILL_MT>
+__global__ void __launch_bounds__(WARPS * 32)
+attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kv,
+                         const int32_t* __restrict__ table, int table_width, const int32_t* __restrict__ item_start,
+                         const int32_t* __restrict__ kv_len, __nv_bfloat16* __restrict__ out, int num_items, int hq, int hkv,
+                         int page_size, int window, float scale, int skip_single) {
+  constexpr int PREFILL_ROWS = WARPS * 16 * PREFILL_MT;  // rows per CTA
+  const int G = hq / hkv;
+  const int h = blockIdx.y;
+  // which item and which of its row tiles is this CTA?
+  int item = -1, tile = 0, n = 0;
+  {
+    int left = blockIdx.x;
+    for (int i = 0; i < num_items; ++i) {
+      const int ni = item_start[i + 1] - item_start[i];
+      if (skip_single && ni == 1) continue;
+      const int tiles = (ni * G + PREFILL_ROWS - 1) / PREFILL_ROWS;
+      if (left < tiles) { item = i; tile = left; n = ni; break; }
+      left -= tiles;
+    }
+  }
+  if (item < 0) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int t0 = item_start[item];
+  const int kvl = kv_len[item];
+  const int first_pos = kvl - n;  // position of the item's first new token
+  const int32_t* pages = table + (size_t)item * table_width;
+  const float sl2 = scale * LOG2E;
+  const size_t v_off = (size_t)hkv * page_size * D;
+
+  const int rows = n * G;
+  const int r_base = tile * PREFILL_ROWS + warp * 16 * PREFILL_MT;
+  if (r_base >= rows) return;
+
+  uint32_t qa[PREFILL_MT][D / 16][4];
+  RowState<D> st[PREFILL_MT];
+  int pos[PREFILL_MT][2], lo[PREFILL_MT][2], tok[PREFILL_MT][2], head[PREFILL_MT][2];
+  int max_pos = -1, min_pos = 0x7fffffff, min_lo = 0x7fffffff, max_lo = 0;
+#pragma unroll
+  for (int mt = 0; mt < PREFILL_MT; ++mt) {
+    const __nv_bfloat16* rp[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = r_base + mt * 16 + g + 8 * r;
+      if (row < rows) {
+        tok[mt][r] = row / G;
+        head[mt][r] = h * G + row % G;
+        pos[mt][r] = first_pos + tok[mt][r];
+        lo[mt][r] = (window > 0 && pos[mt][r] - window + 1 > 0) ? pos[mt][r] - window + 1 : 0;
+        rp[r] = q + ((size_t)(t0 + tok[mt][r]) * hq + head[mt][r]) * D;
+      } else {
+        tok[mt][r] = -1; head[mt][r] = 0; pos[mt][r] = -1; lo[mt][r] = 0x7fffffff;
+        rp[r] = nullptr;
+      }
+    }
+    load_q<D>(qa[mt], rp[0], rp[1], t);
+    st[mt].init();
+  }
+  // the warp's key range: every lane must agree, so reduce over the warp
+#pragma unroll
+  for (int mt = 0; mt < PREFILL_MT; ++mt)
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+      if (tok[mt][r] >= 0) {
+        max_pos = max(max_pos, pos[mt][r]);
+        min_pos = min(min_pos, pos[mt][r]);
+        min_lo = min(min_lo, lo[mt][r]);
+        max_lo = max(max_lo, lo[mt][r]);
+      }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    max_pos = max(max_pos, __shfl_xor_sync(0xffffffffu, max_pos, o));
+    min_pos = min(min_pos, __shfl_xor_sync(0xffffffffu, min_pos, o));
+    min_lo = min(min_lo, __shfl_xor_sync(0xffffffffu, min_lo, o));
+    max_lo = max(max_lo, __shfl_xor_sync(0xffffffffu, max_lo, o));
+  }
+
+  const int k_first = min_lo & ~15;
+  KVTile<D> cur, nxt;
+  {
+    const __nv_bfloat16* kp = tile_ptr(kv, pages, k_first, page_size, hkv, h, D);
+    load_tile<D>(cur, kp, kp + v_off, kvl - k_first, g, t);
+  }
+  for (int key0 = k_first; key0 <= max_pos; key0 += 16) {
+    const int next0 = key0 + 16;
+    if (next0 <= max_pos) {  // fetch the next tile while this one is used
+      const __nv_bfloat16* kp = tile_ptr(kv, pages, next0, page_size, hkv, h, D);
+      load_tile<D>(nxt, kp, kp + v_off, kvl - next0, g, t);
+    }
+    const bool needs_mask = key0 + 15 > min_pos || key0 < max_lo;
+#pragma unroll
+    for (int mt = 0; mt < PREFILL_MT; ++mt) {
+      float s[2][4];
+      scores<D>(s, qa[mt], cur);
+      if (needs_mask) mask_tile(s, key0, t, pos[mt], lo[mt]);
+      fold<D>(st[mt], s, cur, sl2);
+    }
+    if (next0 <= max_pos) cur = nxt;
+  }
+#pragma unroll
+  for (int mt = 0; mt < PREFILL_MT; ++mt)
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      float l = st[mt].l[r];
+      l += __shfl_xor_sync(0xffffffffu, l, 1);
+      l += __shfl_xor_sync(0xffffffffu, l, 2);
+      if (tok[mt][r] < 0) continue;
+      const float inv = 1.f / l;
+      __nv_bfloat16* orow = out + ((size_t)(t0 + tok[mt][r]) * hq + head[mt][r]) * D;
+      // this lane owns dims [2t*D/8, (2t+2)*D/8): n = 2t -> first half, n = 2t+1 -> second half
+#pragma unroll
+      for (int j = 0; j < D / 8; ++j) {
+        orow[(2 * t) * (D / 8) + j] = __float2bfloat16_rn(st[mt].o[j][2 * r] * inv);
+        orow[(2 * t + 1) * (D / 8) + j] = __float2bfloat16_rn(st[mt].o[j][2 * r + 1] * inv);
+      }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------- decode
+// grid (splits, hkv, items).  Partial results (float32): part_o[item][head][split][D], part_ml[item][head][split][2].
+template <int D>
+__global__ void __launch_bounds__(WARPS * 32)
+attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kv,
+                        const int32_t* __restrict__ table, int table_width, const int32_t* __restrict__ item_start,
+                        const int32_t* __restrict__ kv_len, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
+                        float* __restrict__ part_ml, int hq, int hkv, int page_size, int window, float scale, int chunk,
+                        int max_splits) {
+  __shared__ float sh_m[WARPS][16];
+  __shared__ float sh_l[WARPS][16];
+  __shared__ float sh_o[WARPS][16][D + 4];
+  const int item = blockIdx.z, h = blockIdx.y, split = blockIdx.x;
+  const int t0 = item_start[item];
+  if (item_start[item + 1] - t0 != 1) return;  // not a decode item: the prefill kernel has it
+  const int G = hq / hkv;
+  const int kvl = kv_len[item];
+  const int p = kvl - 1;
+  const int lo_key = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+  const int k_begin = (lo_key & ~15) + split * chunk;
+  if (k_begin >= kvl) return;  // the merge kernel knows how many splits this item has
+  const int k_end = min(k_begin + chunk, kvl);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int32_t* pages = table + (size_t)item * table_width;
+  const float sl2 = scale * LOG2E;
+  const size_t v_off = (size_t)hkv * page_size * D;
+
+  uint32_t qa[D / 16][4];
+  {
+    const __nv_bfloat16* r0 = g < G ? q + ((size_t)t0 * hq + h * G + g) * D : nullptr;
+    const __nv_bfloat16* r1 = g + 8 < G ? q + ((size_t)t0 * hq + h * G + g + 8) * D : nullptr;
+    load_q<D>(qa, r0, r1, t);
+  }
+  RowState<D> st;
+  st.init();
+  const int pos[2] = {p, p};
+  const int lo[2] = {lo_key, lo_key};
+
+  KVTile<D> cur, nxt;
+  int key0 = k_begin + warp * 16;
+  if (key0 < k_end) {
+    const __nv_bfloat16* kp = tile_ptr(kv, pages, key0, page_size, hkv, h, D);
+    load_tile<D>(cur, kp, kp + v_off, kvl - key0, g, t);
+  }
+  for (; key0 < k_end; key0 += WARPS * 16) {
+    const int next0 = key0 + WARPS * 16;
+    if (next0 < k_end) {
+      const __nv_bfloat16* kp = tile_ptr(kv, pages, next0, page_size, hkv, h, D);
+      load_tile<D>(nxt, kp, kp + v_off, kvl - next0, g, t);
+    }
+    float s[2][4];
+    scores<D>(s, qa, cur);
+    if (key0 + 15 > p || key0 < lo_key) mask_tile(s, key0, t, pos, lo);
+    fold<D>(st, s, cur, sl2);
+    if (next0 < k_end) cur = nxt;
+  }
+  // merge the four warps' states through shared memory
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    float l = st.l[r];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    const int row = g + 8 * r;
+    if (t == 0) { sh_m[warp][row] = st.m[r]; sh_l[warp][row] = l; }
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) {
+      sh_o[warp][row][(2 * t) * (D / 8) + j] = st.o[j][2 * r];
+      sh_o[warp][row][(2 * t + 1) * (D / 8) + j] = st.o[j][2 * r + 1];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * D; idx += WARPS * 32) {
+    const int row = idx / D, d = idx - row * D;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) m = fmaxf(m, sh_m[w][row]);
+    const float m_safe = m == -INFINITY ? 0.f : m;
+    float l = 0.f, o = 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) {
+      const float a = exp2f(sh_m[w][row] - m_safe);
+      l += a * sh_l[w][row];
+      o += a * sh_o[w][row][d];
+    }
+    const int head = h * G + row;
+    if (max_splits == 1) {
+      out[((size_t)t0 * hq + head) * D + d] = __float2bfloat16_rn(o / l);
+    } else {
+      const size_t slot = ((size_t)item * hq + head) * max_splits + split;
+      part_o[slot * D + d] = o;
+      if (d == 0) { part_ml[slot * 2] = m; part_ml[slot * 2 + 1] = l; }
+    }
+  }
+}
+
+// grid (hq, items), D threads: combines the key ranges of one (item, head).
+template <int D>
+__global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                       const int32_t* __restrict__ item_start, const int32_t* __restrict__ kv_len,
+                                       __nv_bfloat16* __restrict__ out, int hq, int window, int chunk, int max_splits) {
+  const int item = blockIdx.y, head = blockIdx.x, d = threadIdx.x;
+  const int t0 = item_start[item];
+  if (item_start[item + 1] - t0 != 1) return;
+  const int kvl = kv_len[item];
+  const int p = kvl - 1;
+  const int lo_key = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+  const int splits = (kvl - (lo_key & ~15) + chunk - 1) / chunk;
+  const size_t base = ((size_t)item * hq + head) * max_splits;
+  float m = -INFINITY;
+  for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(base + s) * 2]);
+  const float m_safe = m == -INFINITY ? 0.f : m;
+  float l = 0.f, o = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float a = exp2f(part_ml[(base + s) * 2] - m_safe);
+    l += a * part_ml[(base + s) * 2 + 1];
+    o += a * part_o[(base + s) * D + d];
+  }
+  out[((size_t)t0 * hq + head) * D + d] = __float2bfloat16_rn(o / l);
+}
+
+int check_common(const char* who, int hq, int hkv, int D, int page_size, int table_width, int window) {
+  if (hq < 1 || hkv < 1 || hq % hkv) PSB_REFUSE("%s: %d query heads cannot share %d key/value heads", who, hq, hkv);
+  if (D != 64 && D != 128) PSB_REFUSE("%s: head size %d is not built for the tensor-core path (64 or 128)", who, D);
+  if (page_size < 16 || page_size % 16) PSB_REFUSE("%s: page size %d is not a multiple of 16", who, page_size);
+  if (table_width < 1 || window < 0) PSB_REFUSE("%s: bad table width %d or window %d", who, table_width, window);
+  return 0;
+}
+
+}  // namespace
+
+PSB_API int psb_attention_prefill_bf16(const void* q, const void* kv, const void* table, int table_width,
+                                       const void* item_start, const void* kv_len, void* out, int num_items, int num_tiles,
+                                       int hq, int hkv, int D, int page_size, int window, float scale, int skip_single,
+                                       cudaStream_t stream) {
+  if (int rc = check_common("attention_prefill", hq, hkv, D, page_size, table_width, window)) return rc;
+  if (num_items < 0 || num_tiles < 0) PSB_REFUSE("attention_prefill: negative sizes");
+  if (num_items == 0 || num_tiles == 0) return 0;
+  if (hkv > 65535) PSB_REFUSE("attention_prefill: too many key/value heads");
+  dim3 grid(num_tiles, hkv);
+#define PSB_PREFILL(DD, MT)                                                                                          \
+  attention_prefill_kernel<DD, MT><<<grid, WARPS * 32, 0, stream>>>(                                                     \
+      (const __nv_bfloat16*)q, (const __nv_bfloat16*)kv, (const int32_t*)table, table_width, (const int32_t*)item_start, \
+      (const int32_t*)kv_len, (__nv_bfloat16*)out, num_items, hq, hkv, page_size, window, scale, skip_single)
+  if (D == 64) PSB_PREFILL(64, 2); else PSB_PREFILL(128, 1);
+#undef PSB_PREFILL
+  PSB_LAUNCH_CHECK("attention_prefill");
+  return 0;
+}
+
+// rows of (token, head-in-group) pairs one CTA of the prefill kernel owns, by head size
+PSB_API int psb_attention_prefill_rows_per_cta(int D) { return D == 64 ? WARPS * 16 * 2 : WARPS * 16; }
+
+PSB_API int psb_attention_decode_bf16(const void* q, const void* kv, const void* table, int table_width,
+                                      const void* item_start, const void* kv_len, void* out, void* part_o, void* part_ml,
+                                      int num_items, int hq, int hkv, int D, int page_size, int window, float scale, int chunk,
+                                      int max_splits, cudaStream_t stream) {
+  if (int rc = check_common("attention_decode", hq, hkv, D, page_size, table_width, window)) return rc;
+  if (hq / hkv > 16) PSB_REFUSE("attention_decode: groups of more than 16 query heads are not built");
+  if (chunk < WARPS * 16 || chunk % (WARPS * 16)) PSB_REFUSE("attention_decode: key range %d is not a multiple of %d", chunk, WARPS * 16);
+  if (max_splits < 1 || (max_splits > 1 && (!part_o || !part_ml))) PSB_REFUSE("attention_decode: scratch for %d key ranges missing", max_splits);
+  if (num_items <= 0) return 0;
+  if (num_items > 65535 || hkv > 65535) PSB_REFUSE("attention_decode: batch too large");
+  dim3 grid(max_splits, hkv, num_items);
+#define PSB_DECODE(DD)                                                                                               \
+  do {                                                                                                               \
+    attention_decode_kernel<DD><<<grid, WARPS * 32, 0, stream>>>(                                                    \
+        (const __nv_bfloat16*)q, (const __nv_bfloat16*)kv, (const int32_t*)table, table_width, (const int32_t*)item_start, \
+        (const int32_t*)kv_len, (__nv_bfloat16*)out, (float*)part_o, (float*)part_ml, hq, hkv, page_size, window, scale, \
+        chunk, max_splits);                                                                                          \
+    if (max_splits > 1)                                                                                              \
+      attention_merge_kernel<DD><<<dim3(hq, num_items), DD, 0, stream>>>(                                            \
+          (const float*)part_o, (const float*)part_ml, (const int32_t*)item_start, (const int32_t*)kv_len,           \
+          (__nv_bfloat16*)out, hq, window, chunk, max_splits);                                                       \
+  } while (0)
+  if (D == 64) PSB_DECODE(64); else PSB_DECODE(128);
+#undef PSB_DECODE
+  PSB_LAUNCH_CHECK("attention_decode");
+  return 0;
+}

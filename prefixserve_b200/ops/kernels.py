@@ -177,7 +177,11 @@ def attention(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, positions:
         scale = 1.0 / math.sqrt(q.shape[-1])
     if q.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16 and ctx is not None:
         from .tensorcore import attention_bf16
-        fast = attention_bf16(q, kv, table, positions, token_item, window=window, scale=scale, ctx=ctx)
+        _dev(q, "queries"), _dev(kv, "cache entry"), _i32(table, "page table")
+        if q.shape[1] % kv.shape[2] or kv.shape[4] != q.shape[2] or kv.shape[1] != 2:
+            raise KernelError(f"cache entry {tuple(kv.shape)} does not fit queries {tuple(q.shape)}")
+        fast = attention_bf16(q, kv, table, ctx.item_start, ctx.kv_len, [it.end - it.start for it in ctx.items],
+                              [it.end for it in ctx.items], window=window, scale=scale)
         if fast is not None:
             return fast
     return attention_generic(q, kv, table, positions, token_item, window=window, scale=scale)

@@ -36,6 +36,14 @@ _SIGNATURES: dict[str, list] = {
     "psb_attention_generic": [P, I, P, I, P, I, P, P, P, I, I, I, I, I, I, F, P],
     # (gate_up, dtype, out, T, I, stream)
     "psb_silu_mul": [P, I, P, I, I, P],
+    # (q, kv, table, table_width, item_start, kv_len, out, num_items, num_tiles, hq, hkv, D, page_size, window, scale,
+    #  skip_single, stream)
+    "psb_attention_prefill_bf16": [P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P],
+    # (D) -> rows per CTA
+    "psb_attention_prefill_rows_per_cta": [I],
+    # (q, kv, table, table_width, item_start, kv_len, out, part_o, part_ml, num_items, hq, hkv, D, page_size, window,
+    #  scale, chunk, max_splits, stream)
+    "psb_attention_decode_bf16": [P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
     # (logits, temperature, seed, position, out, S, V, stream)
     "psb_sample": [P, P, P, P, P, I, I, P],
 }

@@ -2,7 +2,11 @@
 
 from __future__ import annotations
 
+from typing import Sequence
+
 import torch
+
+from .library import check, lib
 
 
 def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
@@ -15,6 +19,68 @@ def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> tor
     return y if out_dtype == y.dtype else y.to(out_dtype)
 
 
-def attention_bf16(q, kv, table, positions, token_item, *, window, scale, ctx):
-    """Returns None when no tensor-core kernel takes this shape (the caller falls back)."""
-    return None
+_sm_count: dict[int, int] = {}
+_scratch: dict[tuple[int, str], torch.Tensor] = {}
+
+
+def _sms(device: torch.device) -> int:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _sm_count:
+        _sm_count[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _sm_count[idx]
+
+
+def _scratch_buffer(device: torch.device, name: str, numel: int) -> torch.Tensor:
+    """A float32 buffer that lives as long as the process and only ever grows (split-KV partial results)."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(), name)
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() < numel:
+        buf = torch.empty(max(numel, 1 << 16), dtype=torch.float32, device=device)
+        _scratch[key] = buf
+    return buf
+
+
+def attention_bf16_supported(head_dim: int, page_size: int) -> bool:
+    return head_dim in (64, 128) and page_size >= 16 and page_size % 16 == 0
+
+
+def attention_bf16(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, item_start: torch.Tensor, kv_len: torch.Tensor,
+                   new_tokens: Sequence[int], kv_lens: Sequence[int], *, window: int | None, scale: float) -> torch.Tensor | None:
+    """Tensor-core attention for a step.  ``new_tokens``/``kv_lens`` are the host copies of what ``item_start`` and
+    ``kv_len`` hold on the device.  Returns None when no kernel here takes the shape (the caller falls back)."""
+    t, hq, d = q.shape
+    _, _, hkv, page, _ = kv.shape
+    if not attention_bf16_supported(d, page):
+        return None
+    group = hq // hkv
+    out = torch.empty((t, hq * d), dtype=torch.bfloat16, device=q.device)
+    stream = torch.cuda.current_stream().cuda_stream
+    b = len(new_tokens)
+    w = int(window or 0)
+    singles = [kvl for n, kvl in zip(new_tokens, kv_lens) if n == 1]
+    use_decode = bool(singles) and group <= 16
+    if use_decode:
+        def span(kvl: int) -> int:  # keys a decode item reads, from the 16-aligned start of its window
+            lo = max(0, kvl - w) if w else 0
+            return kvl - (lo // 16) * 16
+        longest = max(span(kvl) for kvl in singles)
+        want = max(1, (4 * _sms(q.device)) // max(1, b * hkv))
+        splits = max(1, min(want, -(-longest // 64)))
+        chunk = -(-(-(-longest // splits)) // 64) * 64
+        max_splits = -(-longest // chunk)
+        part_o = part_ml = None
+        if max_splits > 1:
+            part_o = _scratch_buffer(q.device, "attn_o", b * hq * max_splits * d)
+            part_ml = _scratch_buffer(q.device, "attn_ml", b * hq * max_splits * 2)
+        check(lib().psb_attention_decode_bf16(
+            q.data_ptr(), kv.data_ptr(), table.data_ptr(), table.shape[1], item_start.data_ptr(), kv_len.data_ptr(),
+            out.data_ptr(), part_o.data_ptr() if part_o is not None else None,
+            part_ml.data_ptr() if part_ml is not None else None, b, hq, hkv, d, page, w, float(scale), chunk, max_splits,
+            stream), "attention_decode")
+    rows = lib().psb_attention_prefill_rows_per_cta(d)
+    tiles = sum(-(-(n * group) // rows) for n in new_tokens if not (use_decode and n == 1))
+    if tiles:
+        check(lib().psb_attention_prefill_bf16(
+            q.data_ptr(), kv.data_ptr(), table.data_ptr(), table.shape[1], item_start.data_ptr(), kv_len.data_ptr(),
+            out.data_ptr(), b, tiles, hq, hkv, d, page, w, float(scale), 1 if use_decode else 0, stream), "attention_prefill")
+    return out

@@ -284,3 +284,95 @@ def test_kernels_refuse_what_they_cannot_run():
         kv = torch.zeros(2, 2, 2, 16, 512, device=DEV)
         ops.attention(q, kv, torch.zeros(1, 1, dtype=torch.int32, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV),
                       torch.zeros(1, dtype=torch.int32, device=DEV))
+
+
+# ---- the bfloat16 tensor-core attention kernels (prefill portions, split-KV decode) -----------------------
+
+class _Batch:
+    """What ops.attention reads of a step: device offsets/lengths and the host copy of the items."""
+
+    def __init__(self, lens_old, lens_new):
+        from prefixserve_b200.parts import ItemView
+        starts = [0]
+        for n in lens_new:
+            starts.append(starts[-1] + n)
+        self.item_start = torch.tensor(starts, dtype=torch.int32, device=DEV)
+        self.kv_len = torch.tensor([o + n for o, n in zip(lens_old, lens_new)], dtype=torch.int32, device=DEV)
+        self.items = [ItemView(slot=i, start=o, end=o + n, first_token=s)
+                      for i, (o, n, s) in enumerate(zip(lens_old, lens_new, starts))]
+
+
+def _fill_pages(seqs, table, lens, hkv, d, page, num_pages):
+    """Pages with every position written (keys as given, already 'rotated'), everything else NaN."""
+    kv = torch.full((num_pages, 2, hkv, page, d), float("nan"), dtype=torch.bfloat16)
+    for i, (s, tot) in enumerate(zip(seqs, lens)):
+        for p in range(tot):
+            pg = int(table[i, p // page])
+            kv[pg, 0, :, p % page] = s["k"][p].to(torch.bfloat16)
+            kv[pg, 1, :, p % page] = s["v"][p].to(torch.bfloat16)
+    return kv.to(DEV)
+
+
+@pytest.mark.parametrize("hq,hkv,d,page", [(8, 2, 64, 16), (4, 4, 64, 32), (16, 2, 128, 16), (6, 2, 64, 16), (32, 1, 64, 16)])
+@pytest.mark.parametrize("window", [None, 100])
+@pytest.mark.parametrize("mix", ["decode", "prefill", "mixed"])
+def test_attention_tensor_cores(hq, hkv, d, page, window, mix):
+    from prefixserve_b200 import ops
+    lens_old, lens_new = {
+        "decode": ([31, 32, 15, 700, 0, 2999], [1, 1, 1, 1, 1, 1]),           # page edges, first token, long context (split)
+        "prefill": ([0, 64, 33, 0], [150, 37, 2, 1]),                         # fresh prompt, portions over cached prefixes
+        "mixed": ([500, 0, 17, 250, 47], [1, 70, 1, 9, 1]),
+    }[mix]
+    table, seqs, num_pages = _paged_setup(torch.bfloat16, lens_new, lens_old, hq, hkv, d, page, seed=3)
+    totals = [o + n for o, n in zip(lens_old, lens_new)]
+    kv = _fill_pages(seqs, table, totals, hkv, d, page, num_pages)
+    batch = _Batch(lens_old, lens_new)
+    q = torch.cat([s["q"][o:] for s, o in zip(seqs, lens_old)]).to(torch.bfloat16).to(DEV)
+    positions = torch.cat([torch.arange(o, o + n) for o, n in zip(lens_old, lens_new)]).to(torch.int32).to(DEV)
+    token_item = torch.cat([torch.full((n,), i) for i, n in enumerate(lens_new)]).to(torch.int32).to(DEV)
+    table_dev = table.to(DEV)
+    out = ops.attention(q, kv, table_dev, positions, token_item, window=window, ctx=batch)
+    slow = ops.attention(q, kv, table_dev, positions, token_item, window=window)  # the generic kernel, same inputs
+    at = 0
+    for i, (s, o, n) in enumerate(zip(seqs, lens_old, lens_new)):
+        bf = lambda x: x.to(torch.bfloat16).float()  # noqa: E731
+        want = plain_model.causal_attention(bf(s["q"]), bf(s["k"]), bf(s["v"]), window=window)[o:].reshape(n, hq * d)
+        got = out[at:at + n].float().cpu()
+        assert torch.isfinite(got).all(), f"item {i}: read an unwritten slot"
+        assert torch.allclose(got, want, atol=2e-2, rtol=2e-2), f"item {i}: {(got - want).abs().max()}"
+        assert torch.allclose(got, slow[at:at + n].float().cpu(), atol=2e-2, rtol=2e-2)
+        at += n
+
+
+def test_attention_tensor_cores_find_one_far_key():
+    """Decode over 3,000 keys split into ranges: one early key dominates; and a prompt portion whose rows each have
+    their own dominant key."""
+    from prefixserve_b200 import ops
+    hq, hkv, d, page, n_ctx = 8, 2, 64, 16, 3000
+    g = torch.Generator().manual_seed(0)
+    k = torch.randn(n_ctx, hkv, d, generator=g) * 0.1
+    v = torch.randn(n_ctx, hkv, d, generator=g)
+    q = torch.randn(n_ctx, hq, d, generator=g) * 0.1
+    needles = {n_ctx - 1: 77}
+    for row in range(n_ctx - 40, n_ctx - 1):
+        needles[row] = (row * 37) % (row + 1)  # any earlier (or own) position
+    for row, key in needles.items():
+        q[row, :, row % d] = 30.0
+        k[key, :, row % d] += 30.0
+    pages = -(-n_ctx // page)
+    table = torch.randperm(pages + 7, generator=g)[:pages].to(torch.int32)[None, :]
+    kv = _fill_pages([dict(k=k, v=v)], table, [n_ctx], hkv, d, page, pages + 7)
+    bf = lambda x: x.to(torch.bfloat16).float()  # noqa: E731
+    want = plain_model.causal_attention(bf(q), bf(k), bf(v)).reshape(n_ctx, hq * d)
+    for old, new in ((n_ctx - 1, 1), (n_ctx - 40, 40)):
+        batch = _Batch([old], [new])
+        out = ops.attention(q[old:].to(torch.bfloat16).to(DEV), kv, table.to(DEV),
+                            torch.arange(old, n_ctx, dtype=torch.int32, device=DEV),
+                            torch.zeros(new, dtype=torch.int32, device=DEV), ctx=batch)
+        assert torch.allclose(out.float().cpu(), want[old:], atol=3e-2, rtol=3e-2), (old, new)
+
+
+def test_attention_shapes_outside_the_tensor_core_kernels_fall_back():
+    from prefixserve_b200.ops.tensorcore import attention_bf16_supported
+    assert attention_bf16_supported(64, 16) and attention_bf16_supported(128, 64)
+    assert not attention_bf16_supported(48, 16) and not attention_bf16_supported(64, 8) and not attention_bf16_supported(64, 24)
