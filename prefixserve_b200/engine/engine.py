@@ -40,6 +40,7 @@ class EngineConfig:
     reserve_bytes: int = 1 << 30     # left free after the pool
     page_size: int = 16
     enable_prefix_cache: bool = True
+    use_cuda_graphs: bool = True     # capture pure-decode steps per batch size and replay them
 
 
 class Engine:
@@ -58,7 +59,7 @@ class Engine:
         self.bytes_per_block = CacheManager.bytes_per_page(self.needs, cfg.page_size, dtype)
         num_blocks = cfg.num_blocks if cfg.num_blocks is not None else self._size_pool()
         self.cache = self._make_cache(num_blocks)
-        self.runner = ModelRunner(self.model, self.cache, device=self.device)
+        self.runner = ModelRunner(self.model, self.cache, device=self.device, use_graphs=cfg.use_cuda_graphs)
         self.capture_logits = False
         self.last_logits: dict[str, torch.Tensor] = {}
         log.info("cache: %d pages of %d tokens (%.2f GB)", num_blocks, cfg.page_size, num_blocks * self.bytes_per_block / 1e9)
@@ -112,7 +113,7 @@ class Engine:
         torch.cuda.reset_peak_memory_stats()
         before = torch.cuda.memory_allocated()
         cache = self._make_cache(trial_pages)
-        runner = ModelRunner(self.model, cache, device=self.device)
+        runner = ModelRunner(self.model, cache, device=self.device, use_graphs=False)
         held = torch.cuda.memory_allocated() - before
         items = []
         for i in range(cfg.max_num_seqs):

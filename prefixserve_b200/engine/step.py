@@ -36,10 +36,27 @@ class StepItem:
     want: Sequence[int] = field(default_factory=tuple)  # offsets into tokens whose logits are wanted
 
 
-class ModelRunner:
-    """Owns the per-step staging buffers and runs ``DecoderModel.forward`` on the cache."""
+@dataclass
+class _DecodeGraph:
+    """A captured pure-decode step for one batch size: fixed input buffer, fixed output, the graph."""
 
-    def __init__(self, model: DecoderModel, cache: CacheManager, *, device: torch.device | str) -> None:
+    inputs: torch.Tensor
+    logits: torch.Tensor
+    graph: torch.cuda.CUDAGraph
+
+
+class ModelRunner:
+    """Owns the per-step staging buffers and runs ``DecoderModel.forward`` on the cache.
+
+    Steps in which every item brings one token and wants its logits are
+    launch-bound (some hundred small kernels); they are captured once per
+    batch size as a CUDA graph over a fixed input buffer and replayed.  The
+    logits of such a step live in the graph's own memory and are valid until
+    the next step of the same batch size.
+    """
+
+    def __init__(self, model: DecoderModel, cache: CacheManager, *, device: torch.device | str,
+                 use_graphs: bool = True) -> None:
         if model.compute_dtype is None:
             raise EngineError("the model has no weights yet")
         self.model = model
@@ -53,6 +70,10 @@ class ModelRunner:
         self._copy_pending = False
         self.steps_run = 0
         self.last_h2d_bytes = 0  # size of the last step's single host-to-device copy
+        # graphs need every part to do the same device work for the same shapes, whatever the host-side item list says
+        self.use_graphs = use_graphs and all(getattr(p, "graph_safe", False) for _, p in model.named_parts())
+        self._graphs: dict[int, _DecodeGraph] = {}
+        self.graph_replays = 0
 
     # ------------------------------------------------------------------ checks
     def _check(self, items: Sequence[StepItem]) -> None:
@@ -103,7 +124,12 @@ class ModelRunner:
         b, t = len(items), sum(lens)
         s = sum(len(it.want) for it in items)
         page = self.cache.page_size
-        widths = {gi: max(pages_for(it.start + n, page) for it, n in zip(items, lens)) for gi in range(len(self.cache.groups))}
+        static = self.use_graphs and t == b and all(tuple(it.want) == (0,) for it in items)
+        if static:  # the shapes of a captured step may not depend on the step: full-width page tables
+            widths = {gi: self.cache.max_pages_per_seq for gi in range(len(self.cache.groups))}
+        else:
+            widths = {gi: max(pages_for(it.start + n, page) for it, n in zip(items, lens))
+                      for gi in range(len(self.cache.groups))}
         tables = self.cache.tables_for([it.slot for it in items], widths)
         self._check_tables(items, tables)
 
@@ -141,8 +167,21 @@ class ModelRunner:
             table_at[gi] = (at, w)
             at += b * w
 
-        dev = host[:total].to(self.device, non_blocking=True)
         self.last_h2d_bytes = 4 * total
+        held = self._graphs.get(b) if static else None
+        if held is not None:
+            held.inputs.copy_(host[:total], non_blocking=True)
+            self._copied.record()
+            self._copy_pending = True
+            held.graph.replay()
+            self.steps_run += 1
+            self.graph_replays += 1
+            return held.logits
+        if static:
+            dev = torch.empty(total, dtype=torch.int32, device=self.device)
+            dev.copy_(host[:total], non_blocking=True)
+        else:
+            dev = host[:total].to(self.device, non_blocking=True)
         self._copied.record()
         self._copy_pending = True
 
@@ -163,9 +202,18 @@ class ModelRunner:
             max_kv_len=max(it.start + n for it, n in zip(items, lens)),
             all_decode=all(n == 1 for n in lens),
         )
+        if static:
+            ctx.extras["static_kv_len"] = self.cache.max_seq_len
         rows = dev[o_rows: o_rows + s]
-        logits = self.model.forward(ctx, self.cache.view, rows)
+        logits = self.model.forward(ctx, self.cache.view, rows)  # this step's result, computed eagerly
         self.steps_run += 1
+        if static:
+            # Capture the same launches for later steps of this batch size.  Nothing runs during capture; the eager
+            # run above has already sized every scratch buffer the kernels use.
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                static_logits = self.model.forward(ctx, self.cache.view, rows)
+            self._graphs[b] = _DecodeGraph(inputs=dev, logits=static_logits, graph=graph)
         return logits
 
     def _staging(self, words: int) -> torch.Tensor:

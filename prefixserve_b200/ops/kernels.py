@@ -181,7 +181,8 @@ def attention(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, positions:
         if q.shape[1] % kv.shape[2] or kv.shape[4] != q.shape[2] or kv.shape[1] != 2:
             raise KernelError(f"cache entry {tuple(kv.shape)} does not fit queries {tuple(q.shape)}")
         fast = attention_bf16(q, kv, table, ctx.item_start, ctx.kv_len, [it.end - it.start for it in ctx.items],
-                              [it.end for it in ctx.items], window=window, scale=scale)
+                              [it.end for it in ctx.items], window=window, scale=scale,
+                              static_kv_len=getattr(ctx, "extras", {}).get("static_kv_len"))
         if fast is not None:
             return fast
     return attention_generic(q, kv, table, positions, token_item, window=window, scale=scale)

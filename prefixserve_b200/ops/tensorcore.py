@@ -45,9 +45,13 @@ def attention_bf16_supported(head_dim: int, page_size: int) -> bool:
 
 
 def attention_bf16(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, item_start: torch.Tensor, kv_len: torch.Tensor,
-                   new_tokens: Sequence[int], kv_lens: Sequence[int], *, window: int | None, scale: float) -> torch.Tensor | None:
+                   new_tokens: Sequence[int], kv_lens: Sequence[int], *, window: int | None, scale: float,
+                   static_kv_len: int | None = None) -> torch.Tensor | None:
     """Tensor-core attention for a step.  ``new_tokens``/``kv_lens`` are the host copies of what ``item_start`` and
-    ``kv_len`` hold on the device.  Returns None when no kernel here takes the shape (the caller falls back)."""
+    ``kv_len`` hold on the device.  Returns None when no kernel here takes the shape (the caller falls back).
+
+    With ``static_kv_len`` (a step that is being captured for replay) the launch shapes are derived from that
+    length instead of the items' own, so they are the same for every later step of the same batch size."""
     t, hq, d = q.shape
     _, _, hkv, page, _ = kv.shape
     if not attention_bf16_supported(d, page):
@@ -58,13 +62,15 @@ def attention_bf16(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, item_
     b = len(new_tokens)
     w = int(window or 0)
     singles = [kvl for n, kvl in zip(new_tokens, kv_lens) if n == 1]
+    if static_kv_len is not None:
+        singles = [static_kv_len] * b
     use_decode = bool(singles) and group <= 16
     if use_decode:
         def span(kvl: int) -> int:  # keys a decode item reads, from the 16-aligned start of its window
             lo = max(0, kvl - w) if w else 0
             return kvl - (lo // 16) * 16
         longest = max(span(kvl) for kvl in singles)
-        want = max(1, (4 * _sms(q.device)) // max(1, b * hkv))
+        want = max(1, (8 * _sms(q.device)) // max(1, b * hkv))  # enough CTAs to fill the GPU a few times over
         splits = max(1, min(want, -(-longest // 64)))
         chunk = -(-(-(-longest // splits)) // 64) * 64
         max_splits = -(-longest // chunk)

@@ -21,6 +21,8 @@ from .registry import make, register_mixer
 
 
 class Attention(Mixer):
+    graph_safe = True  # device work depends only on tensor shapes and device-side inputs
+
     def __init__(self, params):
         super().__init__(params)
         self.hidden = int(params["hidden_size"])

@@ -97,6 +97,11 @@ class StepContext:
 class Part:
     """Base class; subclasses override what they need."""
 
+    # True when forward() launches the same device work for the same tensor shapes, reading everything that varies
+    # from device memory (then a decode step can be captured once and replayed).  A part that loops over
+    # ``ctx.items`` on the host must leave this False.
+    graph_safe = False
+
     def __init__(self, spec_params: Mapping[str, Any]) -> None:
         self.params = dict(spec_params)
 

@@ -15,6 +15,8 @@ from .registry import register_embedding, register_head
 
 
 class TokenEmbedding(Part):
+    graph_safe = True  # device work depends only on tensor shapes and device-side inputs
+
     def __init__(self, params):
         super().__init__(params)
         self.vocab = int(params["vocab_size"])
@@ -32,6 +34,8 @@ class TokenEmbedding(Part):
 
 
 class LMHead(Part):
+    graph_safe = True  # device work depends only on tensor shapes and device-side inputs
+
     def __init__(self, params):
         super().__init__(params)
         self.vocab = int(params["vocab_size"])

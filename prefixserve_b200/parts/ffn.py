@@ -11,6 +11,8 @@ from .registry import register_ffn
 
 
 class GatedMLP(FeedForward):
+    graph_safe = True  # device work depends only on tensor shapes and device-side inputs
+
     def __init__(self, params):
         super().__init__(params)
         self.hidden = int(params["hidden_size"])

@@ -16,6 +16,8 @@ from .registry import register_norm
 
 
 class RMSNorm(Norm):
+    graph_safe = True  # device work depends only on tensor shapes and device-side inputs
+
     def __init__(self, params):
         super().__init__(params)
         self.size = int(params["size"])
