@@ -21,6 +21,7 @@ import torch
 
 from ..cache.manager import CacheManager, pages_for
 from ..parts.base import ItemView, StepContext
+from ..ops import library
 from ..parts.model import DecoderModel
 
 
@@ -43,6 +44,7 @@ class _DecodeGraph:
     inputs: torch.Tensor
     logits: torch.Tensor
     graph: torch.cuda.CUDAGraph
+    kernels: int = 0  # launches of this library's kernels recorded in the graph
 
 
 class ModelRunner:
@@ -174,6 +176,7 @@ class ModelRunner:
             self._copied.record()
             self._copy_pending = True
             held.graph.replay()
+            library.launches += held.kernels  # this library's kernels inside the replayed graph
             self.steps_run += 1
             self.graph_replays += 1
             return held.logits
@@ -211,9 +214,11 @@ class ModelRunner:
             # Capture the same launches for later steps of this batch size.  Nothing runs during capture; the eager
             # run above has already sized every scratch buffer the kernels use.
             graph = torch.cuda.CUDAGraph()
+            before = library.launches
             with torch.cuda.graph(graph):
                 static_logits = self.model.forward(ctx, self.cache.view, rows)
-            self._graphs[b] = _DecodeGraph(inputs=dev, logits=static_logits, graph=graph)
+            self._graphs[b] = _DecodeGraph(inputs=dev, logits=static_logits, graph=graph, kernels=library.launches - before)
+            library.launches = before  # recorded, not run
         return logits
 
     def _staging(self, words: int) -> torch.Tensor:

@@ -7,6 +7,7 @@ from .kernels import (  # noqa: F401
     add_rmsnorm,
     attention,
     embedding,
+    gated_linear,
     linear,
     rope_append,
     sample,

@@ -115,6 +115,17 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
     return gemm_nt_simt(x, w, out_dtype)
 
 
+def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(x Wg^T) * (x Wu^T) for W = [gate rows; up rows]: fused for few bfloat16 rows, else product then activation."""
+    if x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16:
+        from .tensorcore import gated_linear_bf16
+        _dev(x, "left operand"), _dev(w_gate_up, "weight")
+        act = gated_linear_bf16(x, w_gate_up)
+        if act is not None:
+            return act
+    return silu_mul(linear(x, w_gate_up))
+
+
 def rope_append(qkv: torch.Tensor, positions: torch.Tensor, token_item: torch.Tensor, cos: torch.Tensor | None,
                 sin: torch.Tensor | None, table: torch.Tensor | None, kv: torch.Tensor | None, *, num_heads: int,
                 num_kv_heads: int, head_dim: int, page_size: int, write_kv: bool) -> torch.Tensor:

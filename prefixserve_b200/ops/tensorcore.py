@@ -9,14 +9,41 @@ import torch
 from .library import check, lib
 
 
+SMALL_M = 64        # rows up to which the weight-streaming kernel is used instead of the library product
+SMALL_M_GATED = 32  # same for the gate/up product with the fused activation
+_OUT_CODE = {torch.float32: 0, torch.bfloat16: 1}
+
+
+def small_m_ok(m: int, k: int, limit: int) -> bool:
+    return 0 < m <= limit and k >= 32 and k % 32 == 0
+
+
 def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     """x[M,K] @ w[N,K]^T for bfloat16 operands, float32 accumulation.
 
-    The library product (cuBLAS through torch) stands here exactly where the
-    reference calls F.linear (prefixserve/model/llama.py:113-126).
+    Few rows (decode): the weight-streaming tensor-core kernel of this library.  Many rows: the library product
+    (cuBLAS through torch), exactly where the reference calls F.linear (prefixserve/model/llama.py:113-126).
     """
+    m, k = x.shape
+    if small_m_ok(m, k, SMALL_M) and out_dtype in _OUT_CODE and x.is_contiguous() and w.is_contiguous():
+        y = torch.empty((m, w.shape[0]), dtype=out_dtype, device=x.device)
+        check(lib().psb_gemm_small_m(x.data_ptr(), w.data_ptr(), y.data_ptr(), _OUT_CODE[out_dtype], m, w.shape[0], k,
+                                     torch.cuda.current_stream().cuda_stream), "gemm_small_m")
+        return y
     y = torch.nn.functional.linear(x, w)
     return y if out_dtype == y.dtype else y.to(out_dtype)
+
+
+def gated_linear_bf16(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor | None:
+    """silu(x Wg^T) * (x Wu^T) in one kernel for few rows; None when the fused kernel does not take the shape."""
+    m, k = x.shape
+    if not (small_m_ok(m, k, SMALL_M_GATED) and w_gate_up.shape[0] % 2 == 0 and x.is_contiguous() and w_gate_up.is_contiguous()):
+        return None
+    inter = w_gate_up.shape[0] // 2
+    act = torch.empty((m, inter), dtype=torch.bfloat16, device=x.device)
+    check(lib().psb_gemm_small_m_gated(x.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(), m, inter, k,
+                                       torch.cuda.current_stream().cuda_stream), "gemm_small_m_gated")
+    return act
 
 
 _sm_count: dict[int, int] = {}

@@ -37,8 +37,7 @@ class GatedMLP(FeedForward):
         self.w_down = tensors["down_proj"].contiguous()
 
     def forward(self, x, ctx: StepContext):
-        act = ops.silu_mul(ops.linear(x, self.w_gate_up))
-        return ops.linear(act, self.w_down)
+        return ops.linear(ops.gated_linear(x, self.w_gate_up), self.w_down)
 
 
 register_ffn("gated_mlp", GatedMLP, replace=True)

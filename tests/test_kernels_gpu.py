@@ -376,3 +376,37 @@ def test_attention_shapes_outside_the_tensor_core_kernels_fall_back():
     from prefixserve_b200.ops.tensorcore import attention_bf16_supported
     assert attention_bf16_supported(64, 16) and attention_bf16_supported(128, 64)
     assert not attention_bf16_supported(48, 16) and not attention_bf16_supported(64, 8) and not attention_bf16_supported(64, 24)
+
+
+# ---- the weight-streaming product for few rows ---------------------------------------------------------------
+
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 31, 32, 33, 64])
+@pytest.mark.parametrize("n,k", [(48, 64), (333, 96), (1000, 2048), (16, 8192)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_small_m(m, n, k, out_dtype):
+    from prefixserve_b200.ops.tensorcore import linear_bf16
+    x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = torch.randn(n, k, device=DEV).to(torch.bfloat16)
+    got = linear_bf16(x, w, out_dtype)
+    want = x.double() @ w.double().t()
+    assert got.dtype == out_dtype and got.shape == (m, n)
+    if out_dtype == torch.float32:
+        assert torch.allclose(got.double(), want, rtol=1e-4, atol=1e-3 * math.sqrt(k))
+    else:
+        assert torch.allclose(got.double(), want, rtol=1e-2, atol=1e-2 * math.sqrt(k))
+    # a row alone gives bit-identical results: its sum order does not depend on the batch
+    alone = linear_bf16(x[m - 1:].contiguous(), w, out_dtype)
+    assert torch.equal(alone[0], got[m - 1])
+
+
+@pytest.mark.parametrize("m", [1, 8, 13, 32, 40])
+@pytest.mark.parametrize("inter,k", [(40, 64), (112, 96), (1000, 2048)])
+def test_gated_linear(m, inter, k):
+    from prefixserve_b200 import ops
+    x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(2 * inter, k, device=DEV) / math.sqrt(k)).to(torch.bfloat16)
+    got = ops.gated_linear(x, w)
+    y = x.double() @ w.double().t()
+    want = torch.nn.functional.silu(y[:, :inter]) * y[:, inter:]
+    assert got.shape == (m, inter)
+    assert torch.allclose(got.double(), want, rtol=3e-2, atol=3e-2)
