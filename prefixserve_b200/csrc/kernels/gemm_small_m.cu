@@ -20,7 +20,6 @@
 
 namespace {
 
-constexpr int GW = 8;  // warps per CTA
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
@@ -38,8 +37,8 @@ __device__ __forceinline__ uint4 ld_stream(const void* p) {
 }
 __device__ __forceinline__ uint4 ld_cached(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
 
-// MT: 8-row tiles of x (M <= 8*MT).  U: k chunks in flight per warp.  TILES: 1 plain, 2 gate+up.
-template <int MT, int U, int TILES, typename TOut>
+// MT: 8-row tiles of x (M <= 8*MT).  U: k chunks in flight per warp.  TILES: 1 plain, 2 gate+up.  GW: warps per CTA.
+template <int MT, int U, int TILES, int GW, typename TOut>
 __global__ void __launch_bounds__(GW * 32)
 gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ W, TOut* __restrict__ y, int M, int N,
                     int K, int ldy, int up_offset) {
@@ -138,22 +137,28 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
   }
 }
 
-template <int MT, int U, int TILES, typename TOut>
+template <int MT, int U, int TILES, int GW, typename TOut>
 void launch(const void* x, const void* W, void* y, int M, int N, int K, int ldy, int up_offset, cudaStream_t stream) {
   const int tiles = (N + 15) / 16;
-  gemm_small_m_kernel<MT, U, TILES, TOut><<<tiles, GW * 32, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)W,
-                                                                         (TOut*)y, M, N, K, ldy, up_offset);
+  gemm_small_m_kernel<MT, U, TILES, GW, TOut><<<tiles, GW * 32, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)W,
+                                                                             (TOut*)y, M, N, K, ldy, up_offset);
 }
 
+// wide: 16 warps per CTA split K (few row tiles: more of the matrix in flight at once), else 8.
 template <int TILES, typename TOut>
-int dispatch_m(const void* x, const void* W, void* y, int M, int N, int K, int ldy, int up_offset, cudaStream_t stream) {
-  if (M <= 8) launch<1, 4, TILES, TOut>(x, W, y, M, N, K, ldy, up_offset, stream);
-  else if (M <= 16) launch<2, 4, TILES, TOut>(x, W, y, M, N, K, ldy, up_offset, stream);
-  else if (M <= 32) launch<4, 2, TILES, TOut>(x, W, y, M, N, K, ldy, up_offset, stream);
+int dispatch_m(const void* x, const void* W, void* y, int M, int N, int K, int ldy, int up_offset, int wide,
+               cudaStream_t stream) {
+  if (M <= 8) {
+    if (wide) launch<1, 4, TILES, 16, TOut>(x, W, y, M, N, K, ldy, up_offset, stream);
+    else launch<1, 4, TILES, 8, TOut>(x, W, y, M, N, K, ldy, up_offset, stream);
+  } else if (M <= 16) {
+    if (wide) launch<2, 4, TILES, 16, TOut>(x, W, y, M, N, K, ldy, up_offset, stream);
+    else launch<2, 4, TILES, 8, TOut>(x, W, y, M, N, K, ldy, up_offset, stream);
+  } else if (M <= 32) launch<4, 2, TILES, 8, TOut>(x, W, y, M, N, K, ldy, up_offset, stream);
   else if (M <= 64) {
     // the gated variant's two partial tiles per warp would not fit in shared memory at this width
     if (TILES == 2) PSB_REFUSE("gemm_small_m_gated: M=%d is beyond this kernel (at most 32 rows)", M);
-    launch<8, 2, 1, TOut>(x, W, y, M, N, K, ldy, up_offset, stream);
+    launch<8, 2, 1, 8, TOut>(x, W, y, M, N, K, ldy, up_offset, stream);
   } else PSB_REFUSE("gemm_small_m: M=%d is beyond this kernel (at most 64 rows)", M);
   return 0;
 }
@@ -161,12 +166,13 @@ int dispatch_m(const void* x, const void* W, void* y, int M, int N, int K, int l
 }  // namespace
 
 // y[M,N] = x[M,K] W[N,K]^T.  out_dtype: PSB_BF16 or PSB_F32.
-PSB_API int psb_gemm_small_m(const void* x, const void* W, void* y, int out_dtype, int M, int N, int K, cudaStream_t stream) {
+PSB_API int psb_gemm_small_m(const void* x, const void* W, void* y, int out_dtype, int M, int N, int K, int wide,
+                             cudaStream_t stream) {
   if (M < 0 || N < 1 || K < 32 || K % 32) PSB_REFUSE("gemm_small_m: needs K a positive multiple of 32 (M=%d N=%d K=%d)", M, N, K);
   if (M == 0) return 0;
   int rc;
-  if (out_dtype == PSB_F32) rc = dispatch_m<1, float>(x, W, y, M, N, K, N, 0, stream);
-  else if (out_dtype == PSB_BF16) rc = dispatch_m<1, __nv_bfloat16>(x, W, y, M, N, K, N, 0, stream);
+  if (out_dtype == PSB_F32) rc = dispatch_m<1, float>(x, W, y, M, N, K, N, 0, wide, stream);
+  else if (out_dtype == PSB_BF16) rc = dispatch_m<1, __nv_bfloat16>(x, W, y, M, N, K, N, 0, wide, stream);
   else PSB_REFUSE("gemm_small_m: unknown output dtype %d", out_dtype);
   if (rc) return rc;
   PSB_LAUNCH_CHECK("gemm_small_m");
@@ -174,10 +180,11 @@ PSB_API int psb_gemm_small_m(const void* x, const void* W, void* y, int out_dtyp
 }
 
 // act[M,I] = silu(x W[0:I]^T) * (x W[I:2I]^T), W = [2I, K] (gate rows, then up rows), bfloat16 output.
-PSB_API int psb_gemm_small_m_gated(const void* x, const void* W, void* act, int M, int I, int K, cudaStream_t stream) {
+PSB_API int psb_gemm_small_m_gated(const void* x, const void* W, void* act, int M, int I, int K, int wide,
+                                   cudaStream_t stream) {
   if (M < 0 || I < 1 || K < 32 || K % 32) PSB_REFUSE("gemm_small_m_gated: needs K a positive multiple of 32 (M=%d I=%d K=%d)", M, I, K);
   if (M == 0) return 0;
-  if (int rc = dispatch_m<2, __nv_bfloat16>(x, W, act, M, I, K, I, I, stream)) return rc;
+  if (int rc = dispatch_m<2, __nv_bfloat16>(x, W, act, M, I, K, I, I, wide, stream)) return rc;
   PSB_LAUNCH_CHECK("gemm_small_m_gated");
   return 0;
 }

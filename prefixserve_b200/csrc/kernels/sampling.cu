@@ -27,27 +27,32 @@ __device__ __forceinline__ float uniform01(uint64_t seed, uint32_t position, uin
   return ((float)(uint32_t)(r >> 40) + 0.5f) * (1.0f / 16777216.0f);
 }
 
+// Stage 1: block (row, part) scans its slice of the row and leaves its winner in part_v/part_i.
+// Stage 2 (parts == 1 and final != nullptr in one launch, or a second launch over the winners): same reduction.
 __global__ void sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
                               const int64_t* __restrict__ seed, const int32_t* __restrict__ position,
-                              int32_t* __restrict__ out, int V) {
+                              int32_t* __restrict__ out, float* __restrict__ part_v, int32_t* __restrict__ part_i, int V,
+                              int parts) {
   __shared__ float best_v[32];
   __shared__ int best_i[32];
-  const int row = blockIdx.x;
+  const int row = blockIdx.x, part = blockIdx.y;
   const float* x = logits + (size_t)row * V;
   const float tau = temperature ? temperature[row] : 0.f;
+  const int per = (V + parts - 1) / parts;
+  const int lo = part * per, hi = min(V, lo + per);
   float bv = -FLT_MAX;
   int bi = 0x7fffffff;
   if (tau > 0.f) {
     const uint64_t sd = (uint64_t)seed[row];
     const uint32_t pos = (uint32_t)position[row];
     const float inv_tau = 1.f / tau;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
       const float u = uniform01(sd, pos, (uint32_t)i);
       const float v = x[i] * inv_tau - logf(-logf(u));
       if (v > bv) { bv = v; bi = i; }   // strided scan keeps the lowest index of equal values
     }
   } else {
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
       const float v = x[i];
       if (v > bv) { bv = v; bi = i; }
     }
@@ -71,21 +76,65 @@ __global__ void sample_kernel(const float* __restrict__ logits, const float* __r
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
       if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
     }
-    // a row of NaNs (or of -FLT_MAX) never beats the initial value: answer 0 rather than an invalid id
-    if (lane == 0) out[row] = bi == 0x7fffffff ? 0 : bi;
+    if (lane == 0) {
+      if (parts == 1) {
+        // a row of NaNs (or of -FLT_MAX) never beats the initial value: answer 0 rather than an invalid id
+        out[row] = bi == 0x7fffffff ? 0 : bi;
+      } else {
+        part_v[row * parts + part] = bv;
+        part_i[row * parts + part] = bi;
+      }
+    }
   }
+}
+
+// One warp per row picks the winner among the parts (lowest index among equal values).
+__global__ void sample_finish_kernel(const float* __restrict__ part_v, const int32_t* __restrict__ part_i,
+                                     int32_t* __restrict__ out, int parts) {
+  const int row = blockIdx.x, lane = threadIdx.x;
+  float bv = -FLT_MAX;
+  int bi = 0x7fffffff;
+  for (int p = lane; p < parts; p += 32) {
+    const float v = part_v[row * parts + p];
+    const int i = part_i[row * parts + p];
+    if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+  if (lane == 0) out[row] = bi == 0x7fffffff ? 0 : bi;
 }
 
 }  // namespace
 
+// Rows of a large vocabulary are scanned by several blocks each; their winners go through ``scratch``
+// (S * parts floats followed by S * parts int32; psb_sample_scratch_bytes tells how much).
+PSB_API int psb_sample_parts(int S, int V) {
+  if (V < 32768 || S < 1) return 1;
+  int parts = 1184 / S;  // a few blocks per SM in total
+  parts = parts < 1 ? 1 : (parts > 64 ? 64 : parts);
+  return parts;
+}
+
+PSB_API long long psb_sample_scratch_bytes(int S, int V) { return (long long)S * psb_sample_parts(S, V) * 8; }
+
 PSB_API int psb_sample(const void* logits, const void* temperature, const void* seed, const void* position, void* out,
-                       int S, int V, cudaStream_t stream) {
+                       void* scratch, int S, int V, cudaStream_t stream) {
   if (S < 0 || V < 1) PSB_REFUSE("sample: bad sizes S=%d V=%d", S, V);
   if (temperature && (!seed || !position)) PSB_REFUSE("sample: temperature given without seed and position");
   if (S == 0) return 0;
-  const int threads = V >= 16384 ? 1024 : (V >= 1024 ? 256 : 64);
-  sample_kernel<<<S, threads, 0, stream>>>((const float*)logits, (const float*)temperature, (const int64_t*)seed,
-                                          (const int32_t*)position, (int32_t*)out, V);
+  const int parts = psb_sample_parts(S, V);
+  if (parts > 1 && !scratch) PSB_REFUSE("sample: scratch for %d parts per row missing", parts);
+  const int per = (V + parts - 1) / parts;
+  const int threads = per >= 16384 ? 1024 : (per >= 1024 ? 256 : 64);
+  float* part_v = (float*)scratch;
+  int32_t* part_i = (int32_t*)(part_v + (size_t)S * parts);
+  sample_kernel<<<dim3(S, parts), threads, 0, stream>>>((const float*)logits, (const float*)temperature, (const int64_t*)seed,
+                                                       (const int32_t*)position, (int32_t*)out, part_v, part_i, V, parts);
+  if (parts > 1) sample_finish_kernel<<<S, 32, 0, stream>>>(part_v, part_i, (int32_t*)out, parts);
   PSB_LAUNCH_CHECK("sample");
   return 0;
 }

@@ -227,6 +227,8 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor | None = None, seed: 
         if temperature.numel() != s or seed.numel() != s or position.numel() != s:
             raise KernelError("temperature, seed and position need one entry per logits row")
     out = torch.empty((s,), dtype=torch.int32, device=logits.device)
-    check(lib().psb_sample(logits.data_ptr(), _ptr(temperature), _ptr(seed), _ptr(position), out.data_ptr(), s, v,
-                           _stream()), "sample")
+    need = lib().psb_sample_scratch_bytes(s, v)
+    scratch = torch.empty((need,), dtype=torch.uint8, device=logits.device) if need else None
+    check(lib().psb_sample(logits.data_ptr(), _ptr(temperature), _ptr(seed), _ptr(position), out.data_ptr(),
+                           _ptr(scratch), s, v, _stream()), "sample")
     return out

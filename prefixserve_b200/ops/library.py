@@ -44,14 +44,16 @@ _SIGNATURES: dict[str, list] = {
     # (q, kv, table, table_width, item_start, kv_len, out, part_o, part_ml, num_items, hq, hkv, D, page_size, window,
     #  scale, chunk, max_splits, stream)
     "psb_attention_decode_bf16": [P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
-    # (x, W, y, out_dtype, M, N, K, stream)
-    "psb_gemm_small_m": [P, P, P, I, I, I, I, P],
-    # (x, W, act, M, I, K, stream)
-    "psb_gemm_small_m_gated": [P, P, P, I, I, I, P],
+    # (x, W, y, out_dtype, M, N, K, wide, stream)
+    "psb_gemm_small_m": [P, P, P, I, I, I, I, I, P],
+    # (x, W, act, M, I, K, wide, stream)
+    "psb_gemm_small_m_gated": [P, P, P, I, I, I, I, P],
     # (gated) -> most rows of x
     "psb_gemm_small_m_max_rows": [I],
-    # (logits, temperature, seed, position, out, S, V, stream)
-    "psb_sample": [P, P, P, P, P, I, I, P],
+    # (logits, temperature, seed, position, out, scratch, S, V, stream)
+    "psb_sample": [P, P, P, P, P, P, I, I, P],
+    # (S, V) -> bytes of scratch psb_sample wants
+    "psb_sample_scratch_bytes": [I, I],
 }
 
 
@@ -64,6 +66,7 @@ def lib() -> ctypes.CDLL:
             fn = getattr(handle, name)
             fn.argtypes = argtypes
             fn.restype = c_int
+        handle.psb_sample_scratch_bytes.restype = ctypes.c_longlong
         handle.psb_last_error.restype = ctypes.c_char_p
         handle.psb_last_error.argtypes = []
         _lib = handle

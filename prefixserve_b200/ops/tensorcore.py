@@ -9,13 +9,28 @@ import torch
 from .library import check, lib
 
 
-SMALL_M = 64        # rows up to which the weight-streaming kernel is used instead of the library product
-SMALL_M_GATED = 32  # same for the gate/up product with the fused activation
+# Tuning, set from measurements on B200 at Llama-1B sizes (the library product wins from 9 rows on):
+SMALL_M = 8         # rows up to which the weight-streaming kernel is used instead of the library product
+SMALL_M_GATED = 8   # same for the gate/up product with the fused activation
+WIDE_BELOW_TILES = 600   # matrices with fewer 16-row tiles than this get 16 warps per CTA instead of 8
+DECODE_CTAS_PER_SM = 8   # split-KV: key ranges are sized so that about this many CTAs per SM exist
 _OUT_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
 
 def small_m_ok(m: int, k: int, limit: int) -> bool:
     return 0 < m <= limit and k >= 32 and k % 32 == 0
+
+
+def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, wide: bool | None = None) -> torch.Tensor:
+    """The weight-streaming kernel itself (at most 64 rows, K a multiple of 32)."""
+    m, k = x.shape
+    n = w.shape[0]
+    if wide is None:
+        wide = (n + 15) // 16 < WIDE_BELOW_TILES and k // 32 >= 32
+    y = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    check(lib().psb_gemm_small_m(x.data_ptr(), w.data_ptr(), y.data_ptr(), _OUT_CODE[out_dtype], m, n, k, 1 if wide else 0,
+                                 torch.cuda.current_stream().cuda_stream), "gemm_small_m")
+    return y
 
 
 def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
@@ -26,22 +41,20 @@ def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> tor
     """
     m, k = x.shape
     if small_m_ok(m, k, SMALL_M) and out_dtype in _OUT_CODE and x.is_contiguous() and w.is_contiguous():
-        y = torch.empty((m, w.shape[0]), dtype=out_dtype, device=x.device)
-        check(lib().psb_gemm_small_m(x.data_ptr(), w.data_ptr(), y.data_ptr(), _OUT_CODE[out_dtype], m, w.shape[0], k,
-                                     torch.cuda.current_stream().cuda_stream), "gemm_small_m")
-        return y
+        return gemm_small_m(x, w, out_dtype)
     y = torch.nn.functional.linear(x, w)
     return y if out_dtype == y.dtype else y.to(out_dtype)
 
 
-def gated_linear_bf16(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor | None:
+def gated_linear_bf16(x: torch.Tensor, w_gate_up: torch.Tensor, limit: int | None = None) -> torch.Tensor | None:
     """silu(x Wg^T) * (x Wu^T) in one kernel for few rows; None when the fused kernel does not take the shape."""
     m, k = x.shape
-    if not (small_m_ok(m, k, SMALL_M_GATED) and w_gate_up.shape[0] % 2 == 0 and x.is_contiguous() and w_gate_up.is_contiguous()):
+    if not (small_m_ok(m, k, SMALL_M_GATED if limit is None else limit) and w_gate_up.shape[0] % 2 == 0 and x.is_contiguous() and w_gate_up.is_contiguous()):
         return None
     inter = w_gate_up.shape[0] // 2
     act = torch.empty((m, inter), dtype=torch.bfloat16, device=x.device)
-    check(lib().psb_gemm_small_m_gated(x.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(), m, inter, k,
+    wide = 1 if (inter + 15) // 16 < WIDE_BELOW_TILES and k // 32 >= 32 else 0
+    check(lib().psb_gemm_small_m_gated(x.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(), m, inter, k, wide,
                                        torch.cuda.current_stream().cuda_stream), "gemm_small_m_gated")
     return act
 
@@ -97,7 +110,7 @@ def attention_bf16(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, item_
             lo = max(0, kvl - w) if w else 0
             return kvl - (lo // 16) * 16
         longest = max(span(kvl) for kvl in singles)
-        want = max(1, (8 * _sms(q.device)) // max(1, b * hkv))  # enough CTAs to fill the GPU a few times over
+        want = max(1, (DECODE_CTAS_PER_SM * _sms(q.device)) // max(1, b * hkv))
         splits = max(1, min(want, -(-longest // 64)))
         chunk = -(-(-(-longest // splits)) // 64) * 64
         max_splits = -(-longest // chunk)

@@ -253,6 +253,24 @@ def test_sampling_temperature_follows_the_stated_rule():
     assert alone.tolist()[0] == got[0]
 
 
+def test_sampling_large_vocabulary_uses_several_blocks_per_row():
+    from prefixserve_b200 import ops
+    vocab = 50021
+    logits = torch.randn(3, vocab, device=DEV)
+    logits[1, 40000] = logits[1, 123] = 30.0  # a tie across blocks: the lower index wins
+    got = ops.sample(logits).tolist()
+    assert got == [int(torch.argmax(logits[0])), 123, int(torch.argmax(logits[2]))]
+    temps = torch.tensor([0.5, 0.0, 2.0], device=DEV)
+    seeds = torch.tensor([1, 2, 3], dtype=torch.int64, device=DEV)
+    poss = torch.tensor([4, 5, 6], dtype=torch.int32, device=DEV)
+    got = ops.sample(logits, temps, seeds, poss).tolist()
+    for row in (0, 2):
+        u = plain_model.gumbel_uniform(int(seeds[row]), int(poss[row]), vocab)
+        score = logits[row].cpu() / float(temps[row]) - torch.log(-torch.log(u))
+        assert got[row] == int(torch.argmax(score))
+    assert got[1] == 123
+
+
 def test_sampling_distribution():
     """Over many positions the draws follow softmax(logits / T)."""
     from prefixserve_b200 import ops
@@ -383,8 +401,10 @@ def test_attention_shapes_outside_the_tensor_core_kernels_fall_back():
 @pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 31, 32, 33, 64])
 @pytest.mark.parametrize("n,k", [(48, 64), (333, 96), (1000, 2048), (16, 8192)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-def test_gemm_small_m(m, n, k, out_dtype):
-    from prefixserve_b200.ops.tensorcore import linear_bf16
+@pytest.mark.parametrize("wide", [False, True])
+def test_gemm_small_m(m, n, k, out_dtype, wide):
+    from prefixserve_b200.ops.tensorcore import gemm_small_m
+    linear_bf16 = lambda a, b, c: gemm_small_m(a, b, c, wide=wide)  # noqa: E731
     x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
     w = torch.randn(n, k, device=DEV).to(torch.bfloat16)
     got = linear_bf16(x, w, out_dtype)
@@ -403,9 +423,11 @@ def test_gemm_small_m(m, n, k, out_dtype):
 @pytest.mark.parametrize("inter,k", [(40, 64), (112, 96), (1000, 2048)])
 def test_gated_linear(m, inter, k):
     from prefixserve_b200 import ops
+    from prefixserve_b200.ops.tensorcore import gated_linear_bf16
     x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
     w = (torch.randn(2 * inter, k, device=DEV) / math.sqrt(k)).to(torch.bfloat16)
-    got = ops.gated_linear(x, w)
+    got = gated_linear_bf16(x, w, limit=32) if m <= 32 else ops.gated_linear(x, w)
+    assert torch.allclose(got.float(), ops.gated_linear(x, w).float(), rtol=3e-2, atol=3e-2)
     y = x.double() @ w.double().t()
     want = torch.nn.functional.silu(y[:, :inter]) * y[:, inter:]
     assert got.shape == (m, inter)
