@@ -306,6 +306,62 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
 
 // ---------------------------------------------------------------------------------------------- decode
 // grid (splits, hkv, items).  Partial results (float32): part_o[item][head][split][D], part_ml[item][head][split][2].
+//
+// Each lane streams the 16-byte pieces it will need (the same ones load_tile reads) through a ring of its own in
+// shared memory with cp.async: slot = ((warp*STAGES + stage)*PIECES + piece)*32 + lane.  A lane only ever touches
+// its own slots, so the ring needs no barrier, only cp.async group counting, and it keeps STAGES-1 tiles per warp in
+// flight without holding them in registers.
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src, bool valid) {
+  const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  const int bytes = valid ? 16 : 0;  // 0: nothing is read, the slot is filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem_src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+template <int D>
+struct DecodeShape {
+  static constexpr int PIECES = 2 * (D / 32) + 4 * (D / 64);  // 16-byte pieces per lane per tile
+  static constexpr int STAGES = D == 64 ? 4 : 3;
+  static constexpr int RING_BYTES = WARPS * STAGES * PIECES * 32 * 16;
+  static constexpr int MERGE_BYTES = WARPS * 16 * (D + 4 + 2) * 4;
+  static constexpr int SMEM_BYTES = RING_BYTES > MERGE_BYTES ? RING_BYTES : MERGE_BYTES;
+};
+
+template <int D>
+__device__ __forceinline__ void issue_tile(uint4* ring_slot, const __nv_bfloat16* kp, const __nv_bfloat16* vp, int valid, int g,
+                                           int t) {
+  int piece = 0;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int key = half * 8 + g;
+    const bool ok = key < valid;
+#pragma unroll
+    for (int c = 0; c < D / 32; ++c, ++piece) cp_async16(ring_slot + piece * 32, kp + (ok ? key : 0) * D + c * 32 + t * 8, ok);
+  }
+#pragma unroll
+  for (int sl = 0; sl < 4; ++sl) {
+    const int key = 2 * t + (sl & 1) + (sl >> 1) * 8;
+    const bool ok = key < valid;
+#pragma unroll
+    for (int c = 0; c < D / 64; ++c, ++piece) cp_async16(ring_slot + piece * 32, vp + (ok ? key : 0) * D + g * (D / 8) + c * 8, ok);
+  }
+}
+
+template <int D>
+__device__ __forceinline__ void read_tile(KVTile<D>& tile, const uint4* ring_slot) {
+  int piece = 0;
+#pragma unroll
+  for (int half = 0; half < 2; ++half)
+#pragma unroll
+    for (int c = 0; c < D / 32; ++c, ++piece) tile.k[half][c] = ring_slot[piece * 32];
+#pragma unroll
+  for (int sl = 0; sl < 4; ++sl)
+#pragma unroll
+    for (int c = 0; c < D / 64; ++c, ++piece) tile.v[sl][c] = ring_slot[piece * 32];
+}
+
 template <int D>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kv,
@@ -313,9 +369,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         const int32_t* __restrict__ kv_len, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
                         float* __restrict__ part_ml, int hq, int hkv, int page_size, int window, float scale, int chunk,
                         int max_splits) {
-  __shared__ float sh_m[WARPS][16];
-  __shared__ float sh_l[WARPS][16];
-  __shared__ float sh_o[WARPS][16][D + 4];
+  using Shape = DecodeShape<D>;
+  constexpr int STAGES = Shape::STAGES, PIECES = Shape::PIECES;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
   const int item = blockIdx.z, h = blockIdx.y, split = blockIdx.x;
   const int t0 = item_start[item];
   if (item_start[item + 1] - t0 != 1) return;  // not a decode item: the prefill kernel has it
@@ -331,6 +387,21 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   const float sl2 = scale * LOG2E;
   const size_t v_off = (size_t)hkv * page_size * D;
 
+  // this warp's tiles: first keys k_begin + (warp + WARPS*i) * 16
+  const int first = k_begin + warp * 16;
+  const int n_tiles = first < k_end ? (k_end - first + WARPS * 16 - 1) / (WARPS * 16) : 0;
+  uint4* ring = reinterpret_cast<uint4*>(smem_raw) + (size_t)warp * STAGES * PIECES * 32 + lane;
+  auto issue = [&](int i) {
+    const int key0 = first + i * WARPS * 16;
+    const __nv_bfloat16* kp = tile_ptr(kv, pages, key0, page_size, hkv, h, D);
+    issue_tile<D>(ring + (size_t)(i % STAGES) * PIECES * 32, kp, kp + v_off, kvl - key0, g, t);
+  };
+#pragma unroll
+  for (int i = 0; i < STAGES - 1; ++i) {
+    if (i < n_tiles) issue(i);
+    cp_async_commit();
+  }
+
   uint32_t qa[D / 16][4];
   {
     const __nv_bfloat16* r0 = g < G ? q + ((size_t)t0 * hq + h * G + g) * D : nullptr;
@@ -342,25 +413,24 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   const int pos[2] = {p, p};
   const int lo[2] = {lo_key, lo_key};
 
-  KVTile<D> cur, nxt;
-  int key0 = k_begin + warp * 16;
-  if (key0 < k_end) {
-    const __nv_bfloat16* kp = tile_ptr(kv, pages, key0, page_size, hkv, h, D);
-    load_tile<D>(cur, kp, kp + v_off, kvl - key0, g, t);
-  }
-  for (; key0 < k_end; key0 += WARPS * 16) {
-    const int next0 = key0 + WARPS * 16;
-    if (next0 < k_end) {
-      const __nv_bfloat16* kp = tile_ptr(kv, pages, next0, page_size, hkv, h, D);
-      load_tile<D>(nxt, kp, kp + v_off, kvl - next0, g, t);
-    }
+  for (int i = 0; i < n_tiles; ++i) {
+    if (i + STAGES - 1 < n_tiles) issue(i + STAGES - 1);
+    cp_async_commit();
+    cp_async_wait<STAGES - 1>();  // everything but the newest STAGES-1 groups has landed: tile i is there
+    KVTile<D> cur;
+    read_tile<D>(cur, ring + (size_t)(i % STAGES) * PIECES * 32);
+    const int key0 = first + i * WARPS * 16;
     float s[2][4];
     scores<D>(s, qa, cur);
     if (key0 + 15 > p || key0 < lo_key) mask_tile(s, key0, t, pos, lo);
     fold<D>(st, s, cur, sl2);
-    if (next0 < k_end) cur = nxt;
   }
-  // merge the four warps' states through shared memory
+  cp_async_wait<0>();
+  __syncthreads();  // every warp is done with its ring: the same memory now carries the merge
+
+  float(*sh_m)[16] = reinterpret_cast<float(*)[16]>(smem_raw);
+  float(*sh_l)[16] = reinterpret_cast<float(*)[16]>(smem_raw + WARPS * 16 * 4);
+  float(*sh_o)[16][D + 4] = reinterpret_cast<float(*)[16][D + 4]>(smem_raw + 2 * WARPS * 16 * 4);
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     float l = st.l[r];
@@ -399,12 +469,14 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   }
 }
 
-// grid (hq, items), D threads: combines the key ranges of one (item, head).
+// grid (hq, items), one warp: combines the key ranges of one (item, head).  Lanes first share out the ranges
+// (maximum and weights), then the head dims.
 template <int D>
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        const int32_t* __restrict__ item_start, const int32_t* __restrict__ kv_len,
                                        __nv_bfloat16* __restrict__ out, int hq, int window, int chunk, int max_splits) {
-  const int item = blockIdx.y, head = blockIdx.x, d = threadIdx.x;
+  __shared__ float weight[1024];
+  const int item = blockIdx.y, head = blockIdx.x, lane = threadIdx.x;
   const int t0 = item_start[item];
   if (item_start[item + 1] - t0 != 1) return;
   const int kvl = kv_len[item];
@@ -413,15 +485,26 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
   const int splits = (kvl - (lo_key & ~15) + chunk - 1) / chunk;
   const size_t base = ((size_t)item * hq + head) * max_splits;
   float m = -INFINITY;
-  for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(base + s) * 2]);
+  for (int s = lane; s < splits; s += 32) m = fmaxf(m, part_ml[(base + s) * 2]);
+  m = warp_max(m);
   const float m_safe = m == -INFINITY ? 0.f : m;
-  float l = 0.f, o = 0.f;
-  for (int s = 0; s < splits; ++s) {
+  float l = 0.f;
+  for (int s = lane; s < splits; s += 32) {
     const float a = exp2f(part_ml[(base + s) * 2] - m_safe);
+    weight[s] = a;
     l += a * part_ml[(base + s) * 2 + 1];
-    o += a * part_o[(base + s) * D + d];
   }
-  out[((size_t)t0 * hq + head) * D + d] = __float2bfloat16_rn(o / l);
+  l = warp_sum(l);
+  __syncwarp();
+  const float inv = 1.f / l;
+#pragma unroll
+  for (int i = 0; i < D / 32; ++i) {
+    const int d = lane + 32 * i;
+    float o = 0.f;
+#pragma unroll 4
+    for (int s = 0; s < splits; ++s) o = fmaf(weight[s], part_o[(base + s) * D + d], o);
+    out[((size_t)t0 * hq + head) * D + d] = __float2bfloat16_rn(o * inv);
+  }
 }
 
 int check_common(const char* who, int hq, int hkv, int D, int page_size, int table_width, int window) {
@@ -463,18 +546,26 @@ PSB_API int psb_attention_decode_bf16(const void* q, const void* kv, const void*
   if (int rc = check_common("attention_decode", hq, hkv, D, page_size, table_width, window)) return rc;
   if (hq / hkv > 16) PSB_REFUSE("attention_decode: groups of more than 16 query heads are not built");
   if (chunk < WARPS * 16 || chunk % (WARPS * 16)) PSB_REFUSE("attention_decode: key range %d is not a multiple of %d", chunk, WARPS * 16);
-  if (max_splits < 1 || (max_splits > 1 && (!part_o || !part_ml))) PSB_REFUSE("attention_decode: scratch for %d key ranges missing", max_splits);
+  if (max_splits < 1 || max_splits > 1024 || (max_splits > 1 && (!part_o || !part_ml)))
+    PSB_REFUSE("attention_decode: %d key ranges (at most 1024), or their scratch is missing", max_splits);
   if (num_items <= 0) return 0;
   if (num_items > 65535 || hkv > 65535) PSB_REFUSE("attention_decode: batch too large");
   dim3 grid(max_splits, hkv, num_items);
 #define PSB_DECODE(DD)                                                                                               \
   do {                                                                                                               \
-    attention_decode_kernel<DD><<<grid, WARPS * 32, 0, stream>>>(                                                    \
+    static bool configured = false; /* more than 48 KB of dynamic shared memory has to be asked for once */           \
+    if (!configured) {                                                                                               \
+      cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<DD>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                           DecodeShape<DD>::SMEM_BYTES);                                             \
+      if (e != cudaSuccess) PSB_REFUSE("attention_decode: cannot reserve shared memory: %s", cudaGetErrorString(e)); \
+      configured = true;                                                                                             \
+    }                                                                                                                \
+    attention_decode_kernel<DD><<<grid, WARPS * 32, DecodeShape<DD>::SMEM_BYTES, stream>>>(                                                    \
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)kv, (const int32_t*)table, table_width, (const int32_t*)item_start, \
         (const int32_t*)kv_len, (__nv_bfloat16*)out, (float*)part_o, (float*)part_ml, hq, hkv, page_size, window, scale, \
         chunk, max_splits);                                                                                          \
     if (max_splits > 1)                                                                                              \
-      attention_merge_kernel<DD><<<dim3(hq, num_items), DD, 0, stream>>>(                                            \
+      attention_merge_kernel<DD><<<dim3(hq, num_items), 32, 0, stream>>>(                                            \
           (const float*)part_o, (const float*)part_ml, (const int32_t*)item_start, (const int32_t*)kv_len,           \
           (__nv_bfloat16*)out, hq, window, chunk, max_splits);                                                       \
   } while (0)

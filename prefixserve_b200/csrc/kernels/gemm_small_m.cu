@@ -191,3 +191,190 @@ PSB_API int psb_gemm_small_m_gated(const void* x, const void* W, void* act, int 
 
 // most rows of x the plain (gated = 0) or the gated (gated = 1) variant takes
 PSB_API int psb_gemm_small_m_max_rows(int gated) { return gated ? 32 : 64; }
+
+// ------------------------------------------------------------------------------------------------------------------
+// Streaming variant for at most 16 rows of x: persistent CTAs (one per SM) of 16 warps that split K; every lane feeds
+// the 16-byte pieces it will need through a ring of its own in shared memory with cp.async, so the loads of the next
+// row tile are already in flight while the current one is reduced and stored.  Same operand layout and the same
+// fixed-order reduction as above.
+namespace {
+
+constexpr int SW = 16;  // warps per CTA
+
+__device__ __forceinline__ void cp_async16_cg(void* smem_dst, const void* gmem_src, bool valid) {
+  const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem_src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async16_ca(void* smem_dst, const void* gmem_src, bool valid) {
+  const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem_src), "r"(bytes) : "memory");
+}
+
+template <int MT, int TILES>
+struct StreamShape {
+  static constexpr int PIECES = 2 * TILES + MT;                 // per lane per k chunk
+  static constexpr int STAGES = PIECES <= 3 ? 8 : (PIECES == 4 ? 6 : (PIECES == 5 ? 4 : 3));  // ring + partials <= 227 KB
+  static constexpr int RING_BYTES = SW * STAGES * PIECES * 32 * 16;
+  static constexpr int PART_BYTES = 2 * SW * TILES * 16 * (8 * MT + 1) * 4;  // two buffers of partial tiles
+  static constexpr int SMEM_BYTES = RING_BYTES + PART_BYTES;
+};
+
+template <int MT, int TILES, typename TOut>
+__global__ void __launch_bounds__(SW * 32, 1)
+gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ W, TOut* __restrict__ y, int M, int N,
+                   int K, int ldy, int up_offset) {
+  using Shape = StreamShape<MT, TILES>;
+  constexpr int STAGES = Shape::STAGES, PIECES = Shape::PIECES;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  uint4* ring = reinterpret_cast<uint4*>(smem_raw) + (size_t)warp * STAGES * PIECES * 32 + lane;
+  typedef float PartTile[TILES][16][8 * MT + 1];
+  PartTile* part = reinterpret_cast<PartTile*>(smem_raw + Shape::RING_BYTES);  // [2][SW]
+
+  const int tiles = (N + 15) / 16;
+  const int my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const int chunks = K / 32;
+  const int per = chunks / SW, extra = chunks % SW;
+  const int c_begin = warp * per + min(warp, extra);
+  const int cpw = per + (warp < extra ? 1 : 0);  // chunks of every tile that fall to this warp
+  const int units = my_tiles * cpw;
+
+  const __nv_bfloat16* xrow[MT];
+  bool xlive[MT];
+#pragma unroll
+  for (int j = 0; j < MT; ++j) {
+    const int m = 8 * j + g;
+    xlive[j] = m < M;
+    xrow[j] = x + (size_t)(xlive[j] ? m : 0) * K + t * 8;
+  }
+  auto issue = [&](int u) {
+    const int ti = u / cpw, c = c_begin + u % cpw;
+    const int row0 = (blockIdx.x + ti * gridDim.x) * 16;
+    uint4* slot = ring + (size_t)(u % STAGES) * PIECES * 32;
+    int piece = 0;
+#pragma unroll
+    for (int tl = 0; tl < TILES; ++tl)
+#pragma unroll
+      for (int r = 0; r < 2; ++r, ++piece) {
+        int row = row0 + g + 8 * r;
+        row = row < N ? row : N - 1;
+        cp_async16_cg(slot + piece * 32, W + (size_t)(row + tl * up_offset) * K + c * 32 + t * 8, true);
+      }
+#pragma unroll
+    for (int j = 0; j < MT; ++j, ++piece) cp_async16_ca(slot + piece * 32, xrow[j] + c * 32, xlive[j]);
+  };
+#pragma unroll
+  for (int u = 0; u < STAGES - 1; ++u) {
+    if (u < units) issue(u);
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  }
+
+  int u = 0;
+  for (int ti = 0; ti < my_tiles; ++ti) {
+    float acc[TILES][MT][4];
+#pragma unroll
+    for (int tl = 0; tl < TILES; ++tl)
+#pragma unroll
+      for (int j = 0; j < MT; ++j) acc[tl][j][0] = acc[tl][j][1] = acc[tl][j][2] = acc[tl][j][3] = 0.f;
+    for (int cc = 0; cc < cpw; ++cc, ++u) {
+      if (u + STAGES - 1 < units) issue(u + STAGES - 1);
+      asm volatile("cp.async.commit_group;\n" ::: "memory");
+      asm volatile("cp.async.wait_group %0;\n" ::"n"(STAGES - 1) : "memory");
+      const uint4* slot = ring + (size_t)(u % STAGES) * PIECES * 32;
+      uint4 wv[TILES][2], xv[MT];
+#pragma unroll
+      for (int tl = 0; tl < TILES; ++tl) {
+        wv[tl][0] = slot[(2 * tl) * 32];
+        wv[tl][1] = slot[(2 * tl + 1) * 32];
+      }
+#pragma unroll
+      for (int j = 0; j < MT; ++j) xv[j] = slot[(2 * TILES + j) * 32];
+#pragma unroll
+      for (int tl = 0; tl < TILES; ++tl)
+#pragma unroll
+        for (int j = 0; j < MT; ++j) {
+          mma_bf16(acc[tl][j], wv[tl][0].x, wv[tl][1].x, wv[tl][0].y, wv[tl][1].y, xv[j].x, xv[j].y);
+          mma_bf16(acc[tl][j], wv[tl][0].z, wv[tl][1].z, wv[tl][0].w, wv[tl][1].w, xv[j].z, xv[j].w);
+        }
+    }
+    PartTile* mine = part + (size_t)(ti & 1) * SW;
+#pragma unroll
+    for (int tl = 0; tl < TILES; ++tl)
+#pragma unroll
+      for (int j = 0; j < MT; ++j) {
+        mine[warp][tl][g][8 * j + 2 * t] = acc[tl][j][0];
+        mine[warp][tl][g][8 * j + 2 * t + 1] = acc[tl][j][1];
+        mine[warp][tl][g + 8][8 * j + 2 * t] = acc[tl][j][2];
+        mine[warp][tl][g + 8][8 * j + 2 * t + 1] = acc[tl][j][3];
+      }
+    __syncthreads();  // one barrier per tile: the two buffers alternate
+    const int row0 = (blockIdx.x + ti * gridDim.x) * 16;
+    for (int idx = threadIdx.x; idx < 16 * 8 * MT; idx += SW * 32) {
+      const int r = idx & 15, m = idx >> 4;
+      const int row = row0 + r;
+      if (m >= M || row >= N) continue;
+      float v[TILES];
+#pragma unroll
+      for (int tl = 0; tl < TILES; ++tl) {
+        float sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < SW; ++w) sum += mine[w][tl][r][m];
+        v[tl] = sum;
+      }
+      float out;
+      if (TILES == 2) {
+        const float gate = __bfloat162float(__float2bfloat16_rn(v[0]));
+        const float up = __bfloat162float(__float2bfloat16_rn(v[TILES - 1]));
+        out = gate / (1.f + expf(-gate)) * up;
+      } else {
+        out = v[0];
+      }
+      y[(size_t)m * ldy + row] = from_float<TOut>(out);
+    }
+  }
+  asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+}
+
+template <int MT, int TILES, typename TOut>
+int launch_stream(const void* x, const void* W, void* y, int M, int N, int K, int ldy, int up_offset, int sms, cudaStream_t stream) {
+  using Shape = StreamShape<MT, TILES>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_stream_kernel<MT, TILES, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Shape::SMEM_BYTES);
+    if (e != cudaSuccess) PSB_REFUSE("gemm_stream: cannot reserve %d bytes of shared memory: %s", Shape::SMEM_BYTES, cudaGetErrorString(e));
+    configured = true;
+  }
+  const int tiles = (N + 15) / 16;
+  const int grid = tiles < sms ? tiles : sms;
+  gemm_stream_kernel<MT, TILES, TOut><<<grid, SW * 32, Shape::SMEM_BYTES, stream>>>(
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)W, (TOut*)y, M, N, K, ldy, up_offset);
+  return 0;
+}
+
+}  // namespace
+
+// y[M,N] = x[M,K] W[N,K]^T for M <= 16 with the streaming kernel; sms: CTAs to launch at most (the SM count).
+PSB_API int psb_gemm_stream(const void* x, const void* W, void* y, int out_dtype, int M, int N, int K, int sms, cudaStream_t stream) {
+  if (M < 0 || M > 16 || N < 1 || K < 32 || K % 32 || sms < 1) PSB_REFUSE("gemm_stream: needs M <= 16 and K a multiple of 32 (M=%d N=%d K=%d)", M, N, K);
+  if (M == 0) return 0;
+  int rc;
+  if (out_dtype == PSB_F32) rc = M <= 8 ? launch_stream<1, 1, float>(x, W, y, M, N, K, N, 0, sms, stream) : launch_stream<2, 1, float>(x, W, y, M, N, K, N, 0, sms, stream);
+  else if (out_dtype == PSB_BF16) rc = M <= 8 ? launch_stream<1, 1, __nv_bfloat16>(x, W, y, M, N, K, N, 0, sms, stream) : launch_stream<2, 1, __nv_bfloat16>(x, W, y, M, N, K, N, 0, sms, stream);
+  else PSB_REFUSE("gemm_stream: unknown output dtype %d", out_dtype);
+  if (rc) return rc;
+  PSB_LAUNCH_CHECK("gemm_stream");
+  return 0;
+}
+
+PSB_API int psb_gemm_stream_gated(const void* x, const void* W, void* act, int M, int I, int K, int sms, cudaStream_t stream) {
+  if (M < 0 || M > 16 || I < 1 || K < 32 || K % 32 || sms < 1) PSB_REFUSE("gemm_stream_gated: needs M <= 16 and K a multiple of 32 (M=%d I=%d K=%d)", M, I, K);
+  if (M == 0) return 0;
+  const int rc = M <= 8 ? launch_stream<1, 2, __nv_bfloat16>(x, W, act, M, I, K, I, I, sms, stream)
+                        : launch_stream<2, 2, __nv_bfloat16>(x, W, act, M, I, K, I, I, sms, stream);
+  if (rc) return rc;
+  PSB_LAUNCH_CHECK("gemm_stream_gated");
+  return 0;
+}

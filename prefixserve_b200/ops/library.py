@@ -50,6 +50,10 @@ _SIGNATURES: dict[str, list] = {
     "psb_gemm_small_m_gated": [P, P, P, I, I, I, I, P],
     # (gated) -> most rows of x
     "psb_gemm_small_m_max_rows": [I],
+    # (x, W, y, out_dtype, M, N, K, sms, stream)
+    "psb_gemm_stream": [P, P, P, I, I, I, I, I, P],
+    # (x, W, act, M, I, K, sms, stream)
+    "psb_gemm_stream_gated": [P, P, P, I, I, I, I, P],
     # (logits, temperature, seed, position, out, scratch, S, V, stream)
     "psb_sample": [P, P, P, P, P, P, I, I, P],
     # (S, V) -> bytes of scratch psb_sample wants

@@ -9,8 +9,9 @@ import torch
 from .library import check, lib
 
 
-# Tuning, set from measurements on B200 at Llama-1B sizes (the library product wins from 9 rows on):
-SMALL_M = 8         # rows up to which the weight-streaming kernel is used instead of the library product
+# Tuning, set from measurements on B200 at Llama-1B sizes:
+STREAM_M = 16       # rows up to which the persistent streaming kernel is used (its limit is 16)
+SMALL_M = 8         # rows up to which the one-tile-per-CTA kernel is used when the streaming kernel is not
 SMALL_M_GATED = 8   # same for the gate/up product with the fused activation
 WIDE_BELOW_TILES = 600   # matrices with fewer 16-row tiles than this get 16 warps per CTA instead of 8
 DECODE_CTAS_PER_SM = 8   # split-KV: key ranges are sized so that about this many CTAs per SM exist
@@ -33,6 +34,25 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, wide:
     return y
 
 
+def gemm_stream(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """The persistent streaming kernel itself (at most 16 rows, K a multiple of 32)."""
+    m, k = x.shape
+    n = w.shape[0]
+    y = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    check(lib().psb_gemm_stream(x.data_ptr(), w.data_ptr(), y.data_ptr(), _OUT_CODE[out_dtype], m, n, k, _sms(x.device),
+                                torch.cuda.current_stream().cuda_stream), "gemm_stream")
+    return y
+
+
+def gemm_stream_gated(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    m, k = x.shape
+    inter = w_gate_up.shape[0] // 2
+    act = torch.empty((m, inter), dtype=torch.bfloat16, device=x.device)
+    check(lib().psb_gemm_stream_gated(x.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(), m, inter, k, _sms(x.device),
+                                      torch.cuda.current_stream().cuda_stream), "gemm_stream_gated")
+    return act
+
+
 def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     """x[M,K] @ w[N,K]^T for bfloat16 operands, float32 accumulation.
 
@@ -40,8 +60,11 @@ def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> tor
     (cuBLAS through torch), exactly where the reference calls F.linear (prefixserve/model/llama.py:113-126).
     """
     m, k = x.shape
-    if small_m_ok(m, k, SMALL_M) and out_dtype in _OUT_CODE and x.is_contiguous() and w.is_contiguous():
-        return gemm_small_m(x, w, out_dtype)
+    if out_dtype in _OUT_CODE and x.is_contiguous() and w.is_contiguous():
+        if small_m_ok(m, k, min(STREAM_M, 16)):
+            return gemm_stream(x, w, out_dtype)
+        if small_m_ok(m, k, SMALL_M):
+            return gemm_small_m(x, w, out_dtype)
     y = torch.nn.functional.linear(x, w)
     return y if out_dtype == y.dtype else y.to(out_dtype)
 
@@ -49,6 +72,9 @@ def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> tor
 def gated_linear_bf16(x: torch.Tensor, w_gate_up: torch.Tensor, limit: int | None = None) -> torch.Tensor | None:
     """silu(x Wg^T) * (x Wu^T) in one kernel for few rows; None when the fused kernel does not take the shape."""
     m, k = x.shape
+    if (limit is None and small_m_ok(m, k, min(STREAM_M, 16)) and w_gate_up.shape[0] % 2 == 0 and x.is_contiguous()
+            and w_gate_up.is_contiguous()):
+        return gemm_stream_gated(x, w_gate_up)
     if not (small_m_ok(m, k, SMALL_M_GATED if limit is None else limit) and w_gate_up.shape[0] % 2 == 0 and x.is_contiguous() and w_gate_up.is_contiguous()):
         return None
     inter = w_gate_up.shape[0] // 2

@@ -415,8 +415,10 @@ def test_gemm_small_m(m, n, k, out_dtype, wide):
     else:
         assert torch.allclose(got.double(), want, rtol=1e-2, atol=1e-2 * math.sqrt(k))
     # a row alone gives bit-identical results: its sum order does not depend on the batch
+    # (the 16-warp split exists for up to 16 rows; beyond that both settings use 8 warps)
     alone = linear_bf16(x[m - 1:].contiguous(), w, out_dtype)
-    assert torch.equal(alone[0], got[m - 1])
+    if m <= 16 or not wide:
+        assert torch.equal(alone[0], got[m - 1])
 
 
 @pytest.mark.parametrize("m", [1, 8, 13, 32, 40])
@@ -431,4 +433,34 @@ def test_gated_linear(m, inter, k):
     y = x.double() @ w.double().t()
     want = torch.nn.functional.silu(y[:, :inter]) * y[:, inter:]
     assert got.shape == (m, inter)
+    assert torch.allclose(got.double(), want, rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("m", [1, 5, 8, 9, 16])
+@pytest.mark.parametrize("n,k", [(48, 64), (333, 96), (1000, 2048), (16, 8192), (5000, 512)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_stream(m, n, k, out_dtype):
+    from prefixserve_b200.ops.tensorcore import gemm_stream
+    x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = torch.randn(n, k, device=DEV).to(torch.bfloat16)
+    got = gemm_stream(x, w, out_dtype)
+    want = x.double() @ w.double().t()
+    if out_dtype == torch.float32:
+        assert torch.allclose(got.double(), want, rtol=1e-4, atol=1e-3 * math.sqrt(k))
+    else:
+        assert torch.allclose(got.double(), want, rtol=1e-2, atol=1e-2 * math.sqrt(k))
+    alone = gemm_stream(x[m - 1:].contiguous(), w, out_dtype)
+    if m <= 8:
+        assert torch.equal(alone[0], got[m - 1])  # a row's sum order does not depend on the batch
+
+
+@pytest.mark.parametrize("m", [1, 8, 13])
+@pytest.mark.parametrize("inter,k", [(40, 64), (112, 96), (5000, 2048)])
+def test_gemm_stream_gated(m, inter, k):
+    from prefixserve_b200.ops.tensorcore import gemm_stream_gated
+    x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(2 * inter, k, device=DEV) / math.sqrt(k)).to(torch.bfloat16)
+    got = gemm_stream_gated(x, w)
+    y = x.double() @ w.double().t()
+    want = torch.nn.functional.silu(y[:, :inter]) * y[:, inter:]
     assert torch.allclose(got.double(), want, rtol=3e-2, atol=3e-2)
