@@ -47,6 +47,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// 2^x by the hardware approximation (ex2.approx: relative error about 2^-22; -inf gives 0)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ uint4 ldg16(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
 
 // One 16-key tile in operand order.
@@ -128,14 +135,14 @@ __device__ __forceinline__ void fold(RowState<D>& st, float (&s)[2][4], const KV
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
     const float m_new = fmaxf(st.m[r], mx * sl2);
     const float m_safe = m_new == -INFINITY ? 0.f : m_new;  // a row that has seen nothing yet
-    const float alpha = exp2f(st.m[r] - m_safe);
+    const float alpha = fast_exp2(st.m[r] - m_safe);
     st.m[r] = m_new;
     float sum = 0.f;
 #pragma unroll
     for (int half = 0; half < 2; ++half)
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
-        const float e = exp2f(fmaf(s[half][2 * r + i], sl2, -m_safe));
+        const float e = fast_exp2(fmaf(s[half][2 * r + i], sl2, -m_safe));
         p[half][2 * r + i] = e;
         sum += e;
       }
@@ -311,11 +318,6 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
 // shared memory with cp.async: slot = ((warp*STAGES + stage)*PIECES + piece)*32 + lane.  A lane only ever touches
 // its own slots, so the ring needs no barrier, only cp.async group counting, and it keeps STAGES-1 tiles per warp in
 // flight without holding them in registers.
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src, bool valid) {
-  const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
-  const int bytes = valid ? 16 : 0;  // 0: nothing is read, the slot is filled with zeros
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem_src), "r"(bytes) : "memory");
-}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
@@ -323,58 +325,42 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 template <int D>
 struct DecodeShape {
   static constexpr int PIECES = 2 * (D / 32) + 4 * (D / 64);  // 16-byte pieces per lane per tile
-  static constexpr int STAGES = D == 64 ? 4 : 3;
-  static constexpr int RING_BYTES = WARPS * STAGES * PIECES * 32 * 16;
+  static constexpr int STAGES = 3;
+  static constexpr int STAGE_BYTES = PIECES * 32 * 16;
+  static constexpr int RING_BYTES = WARPS * STAGES * STAGE_BYTES;
   static constexpr int MERGE_BYTES = WARPS * 16 * (D + 4 + 2) * 4;
   static constexpr int SMEM_BYTES = RING_BYTES > MERGE_BYTES ? RING_BYTES : MERGE_BYTES;
 };
 
-template <int D>
-__device__ __forceinline__ void issue_tile(uint4* ring_slot, const __nv_bfloat16* kp, const __nv_bfloat16* vp, int valid, int g,
-                                           int t) {
-  int piece = 0;
-#pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const int key = half * 8 + g;
-    const bool ok = key < valid;
-#pragma unroll
-    for (int c = 0; c < D / 32; ++c, ++piece) cp_async16(ring_slot + piece * 32, kp + (ok ? key : 0) * D + c * 32 + t * 8, ok);
-  }
-#pragma unroll
-  for (int sl = 0; sl < 4; ++sl) {
-    const int key = 2 * t + (sl & 1) + (sl >> 1) * 8;
-    const bool ok = key < valid;
-#pragma unroll
-    for (int c = 0; c < D / 64; ++c, ++piece) cp_async16(ring_slot + piece * 32, vp + (ok ? key : 0) * D + g * (D / 8) + c * 8, ok);
-  }
+__device__ __forceinline__ void cp16_cg(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp16_cg_zfill(uint32_t dst, const void* src, int bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint4 lds16(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
 }
 
-template <int D>
-__device__ __forceinline__ void read_tile(KVTile<D>& tile, const uint4* ring_slot) {
-  int piece = 0;
-#pragma unroll
-  for (int half = 0; half < 2; ++half)
-#pragma unroll
-    for (int c = 0; c < D / 32; ++c, ++piece) tile.k[half][c] = ring_slot[piece * 32];
-#pragma unroll
-  for (int sl = 0; sl < 4; ++sl)
-#pragma unroll
-    for (int c = 0; c < D / 64; ++c, ++piece) tile.v[sl][c] = ring_slot[piece * 32];
-}
-
+// all_single: every item of the step brings one token (then item i's token is row i and item_start need not be read).
 template <int D>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kv,
                         const int32_t* __restrict__ table, int table_width, const int32_t* __restrict__ item_start,
                         const int32_t* __restrict__ kv_len, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
-                        float* __restrict__ part_ml, int hq, int hkv, int page_size, int window, float scale, int chunk,
-                        int max_splits) {
+                        float* __restrict__ part_ml, int hq, int hkv, int page_shift, int window, float scale, int chunk,
+                        int max_splits, int all_single) {
   using Shape = DecodeShape<D>;
-  constexpr int STAGES = Shape::STAGES, PIECES = Shape::PIECES;
+  constexpr int STAGES = Shape::STAGES, PIECES = Shape::PIECES, KP = 2 * (D / 32);
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int item = blockIdx.z, h = blockIdx.y, split = blockIdx.x;
-  const int t0 = item_start[item];
-  if (item_start[item + 1] - t0 != 1) return;  // not a decode item: the prefill kernel has it
+  int t0 = item;
+  if (!all_single) {
+    t0 = item_start[item];
+    if (item_start[item + 1] - t0 != 1) return;  // not a decode item: the prefill kernel has it
+  }
   const int G = hq / hkv;
   const int kvl = kv_len[item];
   const int p = kvl - 1;
@@ -385,20 +371,58 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int32_t* pages = table + (size_t)item * table_width;
   const float sl2 = scale * LOG2E;
-  const size_t v_off = (size_t)hkv * page_size * D;
+  const int page_size = 1 << page_shift;
+  const size_t page_elems = (size_t)2 * hkv * page_size * D;
+  const __nv_bfloat16* kv_head = kv + (size_t)h * page_size * D;
+  const int v_off = hkv * page_size * D;
+
+  // element offsets of this lane's pieces from the first key of a tile, and the key each piece belongs to
+  int off[PIECES], key_of[PIECES];
+  {
+    int piece = 0;
+#pragma unroll
+    for (int half = 0; half < 2; ++half)
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c, ++piece) {
+        key_of[piece] = half * 8 + g;
+        off[piece] = key_of[piece] * D + c * 32 + t * 8;
+      }
+#pragma unroll
+    for (int sl = 0; sl < 4; ++sl)
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c, ++piece) {
+        key_of[piece] = 2 * t + (sl & 1) + (sl >> 1) * 8;
+        off[piece] = v_off + key_of[piece] * D + g * (D / 8) + c * 8;
+      }
+  }
 
   // this warp's tiles: first keys k_begin + (warp + WARPS*i) * 16
   const int first = k_begin + warp * 16;
   const int n_tiles = first < k_end ? (k_end - first + WARPS * 16 - 1) / (WARPS * 16) : 0;
-  uint4* ring = reinterpret_cast<uint4*>(smem_raw) + (size_t)warp * STAGES * PIECES * 32 + lane;
-  auto issue = [&](int i) {
-    const int key0 = first + i * WARPS * 16;
-    const __nv_bfloat16* kp = tile_ptr(kv, pages, key0, page_size, hkv, h, D);
-    issue_tile<D>(ring + (size_t)(i % STAGES) * PIECES * 32, kp, kp + v_off, kvl - key0, g, t);
+  const uint32_t ring0 = (uint32_t)__cvta_generic_to_shared(smem_raw) + (uint32_t)warp * STAGES * Shape::STAGE_BYTES + lane * 16;
+  int issue_key = first, issued = 0, issue_stage = 0;
+  auto issue = [&]() {
+    const int page = pages[issue_key >> page_shift];
+    const __nv_bfloat16* base = kv_head + (size_t)page * page_elems + (size_t)(issue_key & (page_size - 1)) * D;
+    const uint32_t slot = ring0 + issue_stage * Shape::STAGE_BYTES;
+    const int valid = kvl - issue_key;
+    if (valid >= 16) {
+#pragma unroll
+      for (int i = 0; i < PIECES; ++i) cp16_cg(slot + i * 512, base + off[i]);
+    } else {  // the last tile: keys that do not exist yet are read as zeros
+#pragma unroll
+      for (int i = 0; i < PIECES; ++i) {
+        const bool ok = key_of[i] < valid;
+        cp16_cg_zfill(slot + i * 512, ok ? base + off[i] : base, ok ? 16 : 0);
+      }
+    }
+    issue_key += WARPS * 16;
+    ++issued;
+    if (++issue_stage == STAGES) issue_stage = 0;
   };
 #pragma unroll
   for (int i = 0; i < STAGES - 1; ++i) {
-    if (i < n_tiles) issue(i);
+    if (issued < n_tiles) issue();
     cp_async_commit();
   }
 
@@ -413,13 +437,22 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   const int pos[2] = {p, p};
   const int lo[2] = {lo_key, lo_key};
 
-  for (int i = 0; i < n_tiles; ++i) {
-    if (i + STAGES - 1 < n_tiles) issue(i + STAGES - 1);
+  int read_stage = 0, key0 = first;
+  for (int i = 0; i < n_tiles; ++i, key0 += WARPS * 16) {
+    if (issued < n_tiles) issue();
     cp_async_commit();
     cp_async_wait<STAGES - 1>();  // everything but the newest STAGES-1 groups has landed: tile i is there
     KVTile<D> cur;
-    read_tile<D>(cur, ring + (size_t)(i % STAGES) * PIECES * 32);
-    const int key0 = first + i * WARPS * 16;
+    {
+      const uint32_t slot = ring0 + read_stage * Shape::STAGE_BYTES;
+      uint4* kp = &cur.k[0][0];
+      uint4* vp = &cur.v[0][0];
+#pragma unroll
+      for (int j = 0; j < KP; ++j) kp[j] = lds16(slot + j * 512);
+#pragma unroll
+      for (int j = 0; j < PIECES - KP; ++j) vp[j] = lds16(slot + (KP + j) * 512);
+      if (++read_stage == STAGES) read_stage = 0;
+    }
     float s[2][4];
     scores<D>(s, qa, cur);
     if (key0 + 15 > p || key0 < lo_key) mask_tile(s, key0, t, pos, lo);
@@ -437,11 +470,13 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     l += __shfl_xor_sync(0xffffffffu, l, 1);
     l += __shfl_xor_sync(0xffffffffu, l, 2);
     const int row = g + 8 * r;
-    if (t == 0) { sh_m[warp][row] = st.m[r]; sh_l[warp][row] = l; }
+    if (row < G) {
+      if (t == 0) { sh_m[warp][row] = st.m[r]; sh_l[warp][row] = l; }
 #pragma unroll
-    for (int j = 0; j < D / 8; ++j) {
-      sh_o[warp][row][(2 * t) * (D / 8) + j] = st.o[j][2 * r];
-      sh_o[warp][row][(2 * t + 1) * (D / 8) + j] = st.o[j][2 * r + 1];
+      for (int j = 0; j < D / 8; ++j) {
+        sh_o[warp][row][(2 * t) * (D / 8) + j] = st.o[j][2 * r];
+        sh_o[warp][row][(2 * t + 1) * (D / 8) + j] = st.o[j][2 * r + 1];
+      }
     }
   }
   __syncthreads();
@@ -454,7 +489,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     float l = 0.f, o = 0.f;
 #pragma unroll
     for (int w = 0; w < WARPS; ++w) {
-      const float a = exp2f(sh_m[w][row] - m_safe);
+      const float a = fast_exp2(sh_m[w][row] - m_safe);
       l += a * sh_l[w][row];
       o += a * sh_o[w][row][d];
     }
@@ -474,11 +509,15 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 template <int D>
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        const int32_t* __restrict__ item_start, const int32_t* __restrict__ kv_len,
-                                       __nv_bfloat16* __restrict__ out, int hq, int window, int chunk, int max_splits) {
+                                       __nv_bfloat16* __restrict__ out, int hq, int window, int chunk, int max_splits,
+                                       int all_single) {
   __shared__ float weight[1024];
   const int item = blockIdx.y, head = blockIdx.x, lane = threadIdx.x;
-  const int t0 = item_start[item];
-  if (item_start[item + 1] - t0 != 1) return;
+  int t0 = item;
+  if (!all_single) {
+    t0 = item_start[item];
+    if (item_start[item + 1] - t0 != 1) return;
+  }
   const int kvl = kv_len[item];
   const int p = kvl - 1;
   const int lo_key = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
@@ -490,7 +529,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
   const float m_safe = m == -INFINITY ? 0.f : m;
   float l = 0.f;
   for (int s = lane; s < splits; s += 32) {
-    const float a = exp2f(part_ml[(base + s) * 2] - m_safe);
+    const float a = fast_exp2(part_ml[(base + s) * 2] - m_safe);
     weight[s] = a;
     l += a * part_ml[(base + s) * 2 + 1];
   }
@@ -542,14 +581,17 @@ PSB_API int psb_attention_prefill_rows_per_cta(int D) { return D == 64 ? WARPS *
 PSB_API int psb_attention_decode_bf16(const void* q, const void* kv, const void* table, int table_width,
                                       const void* item_start, const void* kv_len, void* out, void* part_o, void* part_ml,
                                       int num_items, int hq, int hkv, int D, int page_size, int window, float scale, int chunk,
-                                      int max_splits, cudaStream_t stream) {
+                                      int max_splits, int all_single, cudaStream_t stream) {
   if (int rc = check_common("attention_decode", hq, hkv, D, page_size, table_width, window)) return rc;
   if (hq / hkv > 16) PSB_REFUSE("attention_decode: groups of more than 16 query heads are not built");
   if (chunk < WARPS * 16 || chunk % (WARPS * 16)) PSB_REFUSE("attention_decode: key range %d is not a multiple of %d", chunk, WARPS * 16);
   if (max_splits < 1 || max_splits > 1024 || (max_splits > 1 && (!part_o || !part_ml)))
     PSB_REFUSE("attention_decode: %d key ranges (at most 1024), or their scratch is missing", max_splits);
+  if (page_size & (page_size - 1)) PSB_REFUSE("attention_decode: page size %d is not a power of two", page_size);
   if (num_items <= 0) return 0;
   if (num_items > 65535 || hkv > 65535) PSB_REFUSE("attention_decode: batch too large");
+  int page_shift = 0;
+  while ((1 << page_shift) < page_size) ++page_shift;
   dim3 grid(max_splits, hkv, num_items);
 #define PSB_DECODE(DD)                                                                                               \
   do {                                                                                                               \
@@ -562,12 +604,12 @@ PSB_API int psb_attention_decode_bf16(const void* q, const void* kv, const void*
     }                                                                                                                \
     attention_decode_kernel<DD><<<grid, WARPS * 32, DecodeShape<DD>::SMEM_BYTES, stream>>>(                                                    \
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)kv, (const int32_t*)table, table_width, (const int32_t*)item_start, \
-        (const int32_t*)kv_len, (__nv_bfloat16*)out, (float*)part_o, (float*)part_ml, hq, hkv, page_size, window, scale, \
-        chunk, max_splits);                                                                                          \
+        (const int32_t*)kv_len, (__nv_bfloat16*)out, (float*)part_o, (float*)part_ml, hq, hkv, page_shift, window, scale, \
+        chunk, max_splits, all_single);                                                                              \
     if (max_splits > 1)                                                                                              \
       attention_merge_kernel<DD><<<dim3(hq, num_items), 32, 0, stream>>>(                                            \
           (const float*)part_o, (const float*)part_ml, (const int32_t*)item_start, (const int32_t*)kv_len,           \
-          (__nv_bfloat16*)out, hq, window, chunk, max_splits);                                                       \
+          (__nv_bfloat16*)out, hq, window, chunk, max_splits, all_single);                                           \
   } while (0)
   if (D == 64) PSB_DECODE(64); else PSB_DECODE(128);
 #undef PSB_DECODE

@@ -221,15 +221,29 @@ struct StreamShape {
   static constexpr int SMEM_BYTES = RING_BYTES + PART_BYTES;
 };
 
+__device__ __forceinline__ void cp16_cg(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp16_ca_zfill(uint32_t dst, const void* src, int bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint4 lds16(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
 template <int MT, int TILES, typename TOut>
 __global__ void __launch_bounds__(SW * 32, 1)
 gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ W, TOut* __restrict__ y, int M, int N,
                    int K, int ldy, int up_offset) {
   using Shape = StreamShape<MT, TILES>;
   constexpr int STAGES = Shape::STAGES, PIECES = Shape::PIECES;
+  constexpr uint32_t STAGE_BYTES = PIECES * 32 * 16;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  uint4* ring = reinterpret_cast<uint4*>(smem_raw) + (size_t)warp * STAGES * PIECES * 32 + lane;
+  // this lane's ring: slot(stage, piece) = ring0 + stage*STAGE_BYTES + piece*512
+  const uint32_t ring0 = (uint32_t)__cvta_generic_to_shared(smem_raw) + (uint32_t)warp * STAGES * STAGE_BYTES + lane * 16;
   typedef float PartTile[TILES][16][8 * MT + 1];
   PartTile* part = reinterpret_cast<PartTile*>(smem_raw + Shape::RING_BYTES);  // [2][SW]
 
@@ -241,56 +255,72 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   const int cpw = per + (warp < extra ? 1 : 0);  // chunks of every tile that fall to this warp
   const int units = my_tiles * cpw;
 
-  const __nv_bfloat16* xrow[MT];
-  bool xlive[MT];
+  // sources, advanced as units are issued (no divisions in the loop)
+  const __nv_bfloat16* xsrc[MT];
+  int xbytes[MT];
 #pragma unroll
   for (int j = 0; j < MT; ++j) {
     const int m = 8 * j + g;
-    xlive[j] = m < M;
-    xrow[j] = x + (size_t)(xlive[j] ? m : 0) * K + t * 8;
+    xbytes[j] = m < M ? 16 : 0;  // rows past M are zero-filled
+    xsrc[j] = x + (size_t)(m < M ? m : 0) * K + c_begin * 32 + t * 8;
   }
-  auto issue = [&](int u) {
-    const int ti = u / cpw, c = c_begin + u % cpw;
+  const __nv_bfloat16* wsrc[2];   // rows g and g+8 of the tile being issued (first of the TILES row groups)
+  auto tile_rows = [&](int ti) {
     const int row0 = (blockIdx.x + ti * gridDim.x) * 16;
-    uint4* slot = ring + (size_t)(u % STAGES) * PIECES * 32;
-    int piece = 0;
 #pragma unroll
-    for (int tl = 0; tl < TILES; ++tl)
+    for (int r = 0; r < 2; ++r) {
+      int row = row0 + g + 8 * r;
+      row = row < N ? row : N - 1;  // rows past N are computed on a copy of the last row and never stored
+      wsrc[r] = W + (size_t)row * K + c_begin * 32 + t * 8;
+    }
+  };
+  const size_t up_elems = (size_t)up_offset * K;
+  int issued = 0, issue_c = 0, issue_ti = 0;
+  uint32_t issue_slot = ring0;
+  int issue_stage = 0;
+  if (units > 0) tile_rows(0);
+  auto issue = [&]() {
 #pragma unroll
-      for (int r = 0; r < 2; ++r, ++piece) {
-        int row = row0 + g + 8 * r;
-        row = row < N ? row : N - 1;
-        cp_async16_cg(slot + piece * 32, W + (size_t)(row + tl * up_offset) * K + c * 32 + t * 8, true);
-      }
+    for (int tl = 0; tl < TILES; ++tl) {
+      cp16_cg(issue_slot + (2 * tl) * 512, wsrc[0] + tl * up_elems + issue_c * 32);
+      cp16_cg(issue_slot + (2 * tl + 1) * 512, wsrc[1] + tl * up_elems + issue_c * 32);
+    }
 #pragma unroll
-    for (int j = 0; j < MT; ++j, ++piece) cp_async16_ca(slot + piece * 32, xrow[j] + c * 32, xlive[j]);
+    for (int j = 0; j < MT; ++j) cp16_ca_zfill(issue_slot + (2 * TILES + j) * 512, xsrc[j] + issue_c * 32, xbytes[j]);
+    ++issued;
+    if (++issue_c == cpw) {
+      issue_c = 0;
+      if (++issue_ti < my_tiles) tile_rows(issue_ti);
+    }
+    if (++issue_stage == STAGES) { issue_stage = 0; issue_slot = ring0; } else issue_slot += STAGE_BYTES;
   };
 #pragma unroll
   for (int u = 0; u < STAGES - 1; ++u) {
-    if (u < units) issue(u);
+    if (issued < units) issue();
     asm volatile("cp.async.commit_group;\n" ::: "memory");
   }
 
-  int u = 0;
+  uint32_t read_slot = ring0;
+  int read_stage = 0;
   for (int ti = 0; ti < my_tiles; ++ti) {
     float acc[TILES][MT][4];
 #pragma unroll
     for (int tl = 0; tl < TILES; ++tl)
 #pragma unroll
       for (int j = 0; j < MT; ++j) acc[tl][j][0] = acc[tl][j][1] = acc[tl][j][2] = acc[tl][j][3] = 0.f;
-    for (int cc = 0; cc < cpw; ++cc, ++u) {
-      if (u + STAGES - 1 < units) issue(u + STAGES - 1);
+    for (int cc = 0; cc < cpw; ++cc) {
+      if (issued < units) issue();
       asm volatile("cp.async.commit_group;\n" ::: "memory");
       asm volatile("cp.async.wait_group %0;\n" ::"n"(STAGES - 1) : "memory");
-      const uint4* slot = ring + (size_t)(u % STAGES) * PIECES * 32;
       uint4 wv[TILES][2], xv[MT];
 #pragma unroll
       for (int tl = 0; tl < TILES; ++tl) {
-        wv[tl][0] = slot[(2 * tl) * 32];
-        wv[tl][1] = slot[(2 * tl + 1) * 32];
+        wv[tl][0] = lds16(read_slot + (2 * tl) * 512);
+        wv[tl][1] = lds16(read_slot + (2 * tl + 1) * 512);
       }
 #pragma unroll
-      for (int j = 0; j < MT; ++j) xv[j] = slot[(2 * TILES + j) * 32];
+      for (int j = 0; j < MT; ++j) xv[j] = lds16(read_slot + (2 * TILES + j) * 512);
+      if (++read_stage == STAGES) { read_stage = 0; read_slot = ring0; } else read_slot += STAGE_BYTES;
 #pragma unroll
       for (int tl = 0; tl < TILES; ++tl)
 #pragma unroll

@@ -42,8 +42,8 @@ _SIGNATURES: dict[str, list] = {
     # (D) -> rows per CTA
     "psb_attention_prefill_rows_per_cta": [I],
     # (q, kv, table, table_width, item_start, kv_len, out, part_o, part_ml, num_items, hq, hkv, D, page_size, window,
-    #  scale, chunk, max_splits, stream)
-    "psb_attention_decode_bf16": [P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
+    #  scale, chunk, max_splits, all_single, stream)
+    "psb_attention_decode_bf16": [P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P],
     # (x, W, y, out_dtype, M, N, K, wide, stream)
     "psb_gemm_small_m": [P, P, P, I, I, I, I, I, P],
     # (x, W, act, M, I, K, wide, stream)

@@ -107,7 +107,7 @@ def _scratch_buffer(device: torch.device, name: str, numel: int) -> torch.Tensor
 
 
 def attention_bf16_supported(head_dim: int, page_size: int) -> bool:
-    return head_dim in (64, 128) and page_size >= 16 and page_size % 16 == 0
+    return head_dim in (64, 128) and page_size >= 16 and page_size & (page_size - 1) == 0
 
 
 def attention_bf16(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, item_start: torch.Tensor, kv_len: torch.Tensor,
@@ -148,7 +148,7 @@ def attention_bf16(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, item_
             q.data_ptr(), kv.data_ptr(), table.data_ptr(), table.shape[1], item_start.data_ptr(), kv_len.data_ptr(),
             out.data_ptr(), part_o.data_ptr() if part_o is not None else None,
             part_ml.data_ptr() if part_ml is not None else None, b, hq, hkv, d, page, w, float(scale), chunk, max_splits,
-            stream), "attention_decode")
+            1 if len(singles) == b else 0, stream), "attention_decode")
     rows = lib().psb_attention_prefill_rows_per_cta(d)
     tiles = sum(-(-(n * group) // rows) for n in new_tokens if not (use_decode and n == 1))
     if tiles:

@@ -393,7 +393,7 @@ def test_attention_tensor_cores_find_one_far_key():
 def test_attention_shapes_outside_the_tensor_core_kernels_fall_back():
     from prefixserve_b200.ops.tensorcore import attention_bf16_supported
     assert attention_bf16_supported(64, 16) and attention_bf16_supported(128, 64)
-    assert not attention_bf16_supported(48, 16) and not attention_bf16_supported(64, 8) and not attention_bf16_supported(64, 24)
+    assert not attention_bf16_supported(48, 16) and not attention_bf16_supported(64, 8) and not attention_bf16_supported(64, 48)
 
 
 # ---- the weight-streaming product for few rows ---------------------------------------------------------------
