@@ -271,15 +271,29 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
   }
 
   const int k_first = min_lo & ~15;
+  // page ids of 32 tiles at a time, one per lane, handed out by shuffle (a table load per tile would stall the warp)
+  const size_t head_off = (size_t)h * page_size * D;
+  const size_t page_elems = (size_t)2 * hkv * page_size * D;
+  auto fetch_pages = [&](int key) {  // ids of the pages holding keys key, key+16, ... (one per lane)
+    const int k = key + 16 * lane;
+    return k <= max_pos ? pages[k / page_size] : 0;
+  };
+  int page_ids = fetch_pages(k_first);
+  int page_base = k_first;  // key of lane 0's tile in page_ids
+  auto tile_at = [&](int key) {
+    if (key - page_base >= 512) { page_base = key; page_ids = fetch_pages(key); }
+    const int page = __shfl_sync(0xffffffffu, page_ids, (key - page_base) >> 4);
+    return kv + (size_t)page * page_elems + head_off + (size_t)(key % page_size) * D;
+  };
   KVTile<D> cur, nxt;
   {
-    const __nv_bfloat16* kp = tile_ptr(kv, pages, k_first, page_size, hkv, h, D);
+    const __nv_bfloat16* kp = tile_at(k_first);
     load_tile<D>(cur, kp, kp + v_off, kvl - k_first, g, t);
   }
   for (int key0 = k_first; key0 <= max_pos; key0 += 16) {
     const int next0 = key0 + 16;
     if (next0 <= max_pos) {  // fetch the next tile while this one is used
-      const __nv_bfloat16* kp = tile_ptr(kv, pages, next0, page_size, hkv, h, D);
+      const __nv_bfloat16* kp = tile_at(next0);
       load_tile<D>(nxt, kp, kp + v_off, kvl - next0, g, t);
     }
     const bool needs_mask = key0 + 15 > min_pos || key0 < max_lo;
@@ -400,9 +414,17 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   const int first = k_begin + warp * 16;
   const int n_tiles = first < k_end ? (k_end - first + WARPS * 16 - 1) / (WARPS * 16) : 0;
   const uint32_t ring0 = (uint32_t)__cvta_generic_to_shared(smem_raw) + (uint32_t)warp * STAGES * Shape::STAGE_BYTES + lane * 16;
+  // Page ids are fetched 32 tiles at a time, one per lane, and handed out by shuffle: a load in the issue path
+  // would stall the warp for a full memory latency on every tile.
+  auto fetch_pages = [&](int first_tile) {
+    const int i = first_tile + lane;
+    return i < n_tiles ? pages[(first + i * WARPS * 16) >> page_shift] : 0;
+  };
+  int page_ids = fetch_pages(0);
   int issue_key = first, issued = 0, issue_stage = 0;
   auto issue = [&]() {
-    const int page = pages[issue_key >> page_shift];
+    if ((issued & 31) == 0 && issued > 0) page_ids = fetch_pages(issued);
+    const int page = __shfl_sync(0xffffffffu, page_ids, issued & 31);
     const __nv_bfloat16* base = kv_head + (size_t)page * page_elems + (size_t)(issue_key & (page_size - 1)) * D;
     const uint32_t slot = ring0 + issue_stage * Shape::STAGE_BYTES;
     const int valid = kvl - issue_key;
@@ -528,10 +550,10 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
   m = warp_max(m);
   const float m_safe = m == -INFINITY ? 0.f : m;
   float l = 0.f;
-  for (int s = lane; s < splits; s += 32) {
-    const float a = fast_exp2(part_ml[(base + s) * 2] - m_safe);
+  for (int s = lane; s < max_splits; s += 32) {
+    const float a = s < splits ? fast_exp2(part_ml[(base + s) * 2] - m_safe) : 0.f;
     weight[s] = a;
-    l += a * part_ml[(base + s) * 2 + 1];
+    if (s < splits) l += a * part_ml[(base + s) * 2 + 1];
   }
   l = warp_sum(l);
   __syncwarp();
@@ -540,8 +562,14 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
   for (int i = 0; i < D / 32; ++i) {
     const int d = lane + 32 * i;
     float o = 0.f;
-#pragma unroll 4
-    for (int s = 0; s < splits; ++s) o = fmaf(weight[s], part_o[(base + s) * D + d], o);
+    // eight ranges per round, all loads issued before any is used; ranges past the item's own are skipped by weight
+    for (int s0 = 0; s0 < splits; s0 += 8) {
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = s0 + j < splits ? part_o[(base + s0 + j) * D + d] : 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o = fmaf(s0 + j < splits ? weight[s0 + j] : 0.f, v[j], o);
+    }
     out[((size_t)t0 * hq + head) * D + d] = __float2bfloat16_rn(o * inv);
   }
 }

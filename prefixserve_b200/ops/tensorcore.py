@@ -11,6 +11,8 @@ from .library import check, lib
 
 # Tuning, set from measurements on B200 at Llama-1B sizes:
 STREAM_M = 16       # rows up to which the persistent streaming kernel is used (its limit is 16)
+STREAM_MIN_TILES = 300   # ... for matrices with at least this many 16-row tiles (about two per SM); smaller ones
+                         # balance better over one CTA per tile
 SMALL_M = 8         # rows up to which the one-tile-per-CTA kernel is used when the streaming kernel is not
 SMALL_M_GATED = 8   # same for the gate/up product with the fused activation
 WIDE_BELOW_TILES = 600   # matrices with fewer 16-row tiles than this get 16 warps per CTA instead of 8
@@ -61,7 +63,7 @@ def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> tor
     """
     m, k = x.shape
     if out_dtype in _OUT_CODE and x.is_contiguous() and w.is_contiguous():
-        if small_m_ok(m, k, min(STREAM_M, 16)):
+        if small_m_ok(m, k, min(STREAM_M, 16)) and ((w.shape[0] + 15) // 16 >= STREAM_MIN_TILES or m > SMALL_M):
             return gemm_stream(x, w, out_dtype)
         if small_m_ok(m, k, SMALL_M):
             return gemm_small_m(x, w, out_dtype)
