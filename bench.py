@@ -248,6 +248,7 @@ def run_own(args) -> dict:
         decoding = produced = e2e_steps = 0
         t_start = None
         h2d = []
+        marks = []
         while sched.has_work() and e2e_steps < args.steps:
             batch = sched.schedule_step(PREFILL_TOKENS, args.batch)
             is_decode = all(w.end - w.start == 1 for w in batch.work) and len(batch.work) == args.batch
@@ -262,12 +263,15 @@ def run_own(args) -> dict:
                 e2e_steps += 1
                 h2d.append(runner.last_h2d_bytes)
             sched.commit(batch, out)
+            if t_start is not None:
+                marks.append(time.perf_counter())
         torch.cuda.synchronize()
         e2e_s = time.perf_counter() - t_start
         for r in range(args.batch):
             sched.free_request(f"e2e-{r}")
         e2e = {"value": round(produced / e2e_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(sum(h2d) / max(len(h2d), 1)),
-               "d2h_bytes_per_step": 4 * args.batch, "steps": e2e_steps, "ms_per_step": round(1e3 * e2e_s / max(e2e_steps, 1), 4)}
+               "d2h_bytes_per_step": 4 * args.batch, "steps": e2e_steps, "ms_per_step": round(1e3 * e2e_s / max(e2e_steps, 1), 4),
+               "ms_per_step_p50": round(1e3 * float(np.median(np.diff(marks))), 4) if len(marks) > 2 else None}
 
         # ---- prefill: one 2,048-token prompt in one step
         def one_prefill() -> float:

@@ -30,6 +30,8 @@ attention_generic_kernel(const T* __restrict__ q, const TKV* __restrict__ kv, co
                          int table_width, const int32_t* __restrict__ positions, const int32_t* __restrict__ token_item,
                          T* __restrict__ out, int T_tokens, int hq, int hkv, int D, int page_size, int window, float scale) {
   __shared__ float qs[WARPS][MAX_D];
+  pdl_trigger();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long unit = (long long)blockIdx.x * WARPS + warp;
   if (unit >= (long long)T_tokens * hq) return;
@@ -110,7 +112,7 @@ PSB_API int psb_attention_generic(const void* q, int dtype, const void* kv, int 
   if (blocks > 0x7fffffffLL) PSB_REFUSE("attention: batch too large");
   PSB_DISPATCH_DTYPE(dtype, T_, {
     PSB_DISPATCH_DTYPE(kv_dtype, TKV, {
-      attention_generic_kernel<T_, TKV><<<(unsigned)blocks, WARPS * 32, 0, stream>>>(
+      psb_launch(attention_generic_kernel<T_, TKV>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream,
           (const T_*)q, (const TKV*)kv, (const int32_t*)table, table_width, (const int32_t*)positions,
           (const int32_t*)token_item, (T_*)out, T, hq, hkv, D, page_size, window, scale);
     });

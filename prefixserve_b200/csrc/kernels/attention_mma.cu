@@ -200,6 +200,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                          const int32_t* __restrict__ kv_len, __nv_bfloat16* __restrict__ out, int num_items, int hq, int hkv,
                          int page_size, int window, float scale, int skip_single) {
   constexpr int PREFILL_ROWS = WARPS * 16 * PREFILL_MT;  // rows per CTA
+  pdl_trigger();
+  pdl_wait();
   const int G = hq / hkv;
   const int h = blockIdx.y;
   // which item and which of its row tiles is this CTA?
@@ -369,18 +371,24 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   using Shape = DecodeShape<D>;
   constexpr int STAGES = Shape::STAGES, PIECES = Shape::PIECES, KP = 2 * (D / 32);
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  // Lengths and page tables are inputs of the step: they may be read before the preceding kernel has finished.
+  pdl_trigger();
   const int item = blockIdx.z, h = blockIdx.y, split = blockIdx.x;
   int t0 = item;
+  bool mine = true;
   if (!all_single) {
     t0 = item_start[item];
-    if (item_start[item + 1] - t0 != 1) return;  // not a decode item: the prefill kernel has it
+    mine = item_start[item + 1] - t0 == 1;  // otherwise not a decode item: the prefill kernel has it
   }
   const int G = hq / hkv;
   const int kvl = kv_len[item];
   const int p = kvl - 1;
   const int lo_key = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
   const int k_begin = (lo_key & ~15) + split * chunk;
-  if (k_begin >= kvl) return;  // the merge kernel knows how many splits this item has
+  if (!mine || k_begin >= kvl) {  // the merge kernel knows how many splits this item has
+    pdl_wait();
+    return;
+  }
   const int k_end = min(k_begin + chunk, kvl);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int32_t* pages = table + (size_t)item * table_width;
@@ -421,6 +429,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     return i < n_tiles ? pages[(first + i * WARPS * 16) >> page_shift] : 0;
   };
   int page_ids = fetch_pages(0);
+  pdl_wait();  // from here on: queries and the keys and values the preceding kernels wrote
   int issue_key = first, issued = 0, issue_stage = 0;
   auto issue = [&]() {
     if ((issued & 31) == 0 && issued > 0) page_ids = fetch_pages(issued);
@@ -534,13 +543,17 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
                                        __nv_bfloat16* __restrict__ out, int hq, int window, int chunk, int max_splits,
                                        int all_single) {
   __shared__ float weight[1024];
+  pdl_trigger();
   const int item = blockIdx.y, head = blockIdx.x, lane = threadIdx.x;
   int t0 = item;
+  bool mine = true;
   if (!all_single) {
     t0 = item_start[item];
-    if (item_start[item + 1] - t0 != 1) return;
+    mine = item_start[item + 1] - t0 == 1;
   }
   const int kvl = kv_len[item];
+  pdl_wait();
+  if (!mine) return;
   const int p = kvl - 1;
   const int lo_key = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
   const int splits = (kvl - (lo_key & ~15) + chunk - 1) / chunk;
@@ -594,7 +607,7 @@ PSB_API int psb_attention_prefill_bf16(const void* q, const void* kv, const void
   if (hkv > 65535) PSB_REFUSE("attention_prefill: too many key/value heads");
   dim3 grid(num_tiles, hkv);
 #define PSB_PREFILL(DD, MT)                                                                                          \
-  attention_prefill_kernel<DD, MT><<<grid, WARPS * 32, 0, stream>>>(                                                     \
+  psb_launch(attention_prefill_kernel<DD, MT>, grid, dim3(WARPS * 32), 0, stream, \
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)kv, (const int32_t*)table, table_width, (const int32_t*)item_start, \
       (const int32_t*)kv_len, (__nv_bfloat16*)out, num_items, hq, hkv, page_size, window, scale, skip_single)
   if (D == 64) PSB_PREFILL(64, 2); else PSB_PREFILL(128, 1);
@@ -630,12 +643,12 @@ PSB_API int psb_attention_decode_bf16(const void* q, const void* kv, const void*
       if (e != cudaSuccess) PSB_REFUSE("attention_decode: cannot reserve shared memory: %s", cudaGetErrorString(e)); \
       configured = true;                                                                                             \
     }                                                                                                                \
-    attention_decode_kernel<DD><<<grid, WARPS * 32, DecodeShape<DD>::SMEM_BYTES, stream>>>(                                                    \
+    psb_launch(attention_decode_kernel<DD>, grid, dim3(WARPS * 32), (size_t)DecodeShape<DD>::SMEM_BYTES, stream, \
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)kv, (const int32_t*)table, table_width, (const int32_t*)item_start, \
         (const int32_t*)kv_len, (__nv_bfloat16*)out, (float*)part_o, (float*)part_ml, hq, hkv, page_shift, window, scale, \
         chunk, max_splits, all_single);                                                                              \
     if (max_splits > 1)                                                                                              \
-      attention_merge_kernel<DD><<<dim3(hq, num_items), 32, 0, stream>>>(                                            \
+      psb_launch(attention_merge_kernel<DD>, dim3(hq, num_items), dim3(32), 0, stream, \
           (const float*)part_o, (const float*)part_ml, (const int32_t*)item_start, (const int32_t*)kv_len,           \
           (__nv_bfloat16*)out, hq, window, chunk, max_splits, all_single);                                           \
   } while (0)

@@ -31,6 +31,36 @@ void psb_set_error(const char* fmt, ...);
     }                                                                            \
   } while (0)
 
+// ---- programmatic dependent launch ---------------------------------------------------------------------------
+// A decode step is a chain of some hundred short kernels, each waiting for the one before.  Launched with the
+// programmatic-serialization attribute, a kernel may start while its predecessor is still draining: everything
+// before pdl_wait() (index arithmetic, loads of weights and of the step's read-only inputs) overlaps with the
+// predecessor; nothing the predecessor writes is read, and nothing is written, before pdl_wait() returns (it
+// returns once the whole predecessor grid has finished and its writes are visible).  Every thread executes
+// pdl_wait() before it exits, so that "this grid finished" always implies "its predecessor finished".  Without the
+// launch attribute both instructions do nothing.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+extern int psb_pdl_enabled;  // set through psb_set_pdl()
+
+template <typename Kernel, typename... Args>
+inline cudaError_t psb_launch(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (psb_pdl_enabled) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 template <typename T>
 __device__ __forceinline__ float to_float(T v);
 template <>

@@ -12,6 +12,8 @@ namespace {
 template <typename TT>
 __global__ void embedding_kernel(const int32_t* __restrict__ ids, const TT* __restrict__ table,
                                  float* __restrict__ out, int H, int V) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   int id = ids[t];
   // ids are validated on the host; clamp so that a bad one can never read outside the table
@@ -39,6 +41,8 @@ template <typename TD, typename TX>
 __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ delta, const float* __restrict__ gain,
                                    const int32_t* __restrict__ rows, TX* __restrict__ x, int H, float eps, int update_h) {
   __shared__ float scratch[32];
+  pdl_trigger();
+  pdl_wait();
   const int i = blockIdx.x;
   const int r = rows ? rows[i] : i;
   float* hr = h + (size_t)r * H;
@@ -62,6 +66,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
 
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
+  pdl_trigger();
+  pdl_wait();
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const size_t t = idx / (size_t)I;
@@ -80,7 +86,7 @@ PSB_API int psb_embedding(const void* ids, const void* table, int table_dtype, v
   if (T == 0) return 0;
   const int threads = H >= 1024 ? 256 : 128;
   PSB_DISPATCH_DTYPE(table_dtype, TT, {
-    embedding_kernel<TT><<<T, threads, 0, stream>>>((const int32_t*)ids, (const TT*)table, (float*)out, H, V);
+    psb_launch(embedding_kernel<TT>, dim3(T), dim3(threads), 0, stream, (const int32_t*)ids, (const TT*)table, (float*)out, H, V);
   });
   PSB_LAUNCH_CHECK("embedding");
   return 0;
@@ -94,7 +100,7 @@ PSB_API int psb_add_rmsnorm(void* h, const void* delta, int delta_dtype, const v
   const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
   PSB_DISPATCH_DTYPE(delta_dtype, TD, {
     PSB_DISPATCH_DTYPE(x_dtype, TX, {
-      add_rmsnorm_kernel<TD, TX><<<n_rows, threads, 0, stream>>>((float*)h, (const TD*)delta, (const float*)gain,
+      psb_launch(add_rmsnorm_kernel<TD, TX>, dim3(n_rows), dim3(threads), 0, stream, (float*)h, (const TD*)delta, (const float*)gain,
                                                                  (const int32_t*)rows, (TX*)x, H, eps, update_h);
     });
   });
@@ -110,7 +116,7 @@ PSB_API int psb_silu_mul(const void* gate_up, int dtype, void* out, int T, int I
   const size_t blocks = (total + threads - 1) / threads;
   if (blocks > 0x7fffffffull) PSB_REFUSE("silu_mul: too many elements");
   PSB_DISPATCH_DTYPE(dtype, T_, {
-    silu_mul_kernel<T_><<<(unsigned)blocks, threads, 0, stream>>>((const T_*)gate_up, (T_*)out, I, total);
+    psb_launch(silu_mul_kernel<T_>, dim3((unsigned)blocks), dim3(threads), 0, stream, (const T_*)gate_up, (T_*)out, I, total);
   });
   PSB_LAUNCH_CHECK("silu_mul");
   return 0;

@@ -23,6 +23,8 @@ gemm_nt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TC* __restric
                int64_t lda, int64_t ldw, int64_t ldc, int accumulate) {
   __shared__ float sa[BK][TILE + 4];
   __shared__ float sw[BK][TILE + 4];
+  pdl_trigger();
+  pdl_wait();
   const int m0 = blockIdx.y * TILE, n0 = blockIdx.x * TILE;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   float acc[4][4] = {};
@@ -74,7 +76,7 @@ int launch_c(const void* a, const void* w, void* c, int c_dtype, int M, int N, i
   dim3 grid((N + TILE - 1) / TILE, (M + TILE - 1) / TILE);
   if (grid.y > 65535) PSB_REFUSE("gemm_nt: M=%d is too large for this kernel", M);
   PSB_DISPATCH_DTYPE(c_dtype, TC, {
-    gemm_nt_kernel<TA, TW, TC><<<grid, THREADS, 0, stream>>>((const TA*)a, (const TW*)w, (TC*)c, M, N, K, lda, ldw, ldc, accumulate);
+    psb_launch(gemm_nt_kernel<TA, TW, TC>, grid, dim3(THREADS), 0, stream, (const TA*)a, (const TW*)w, (TC*)c, M, N, K, lda, ldw, ldc, accumulate);
   });
   return 0;
 }

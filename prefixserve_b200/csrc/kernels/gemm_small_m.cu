@@ -68,6 +68,8 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
   for (int tl = 0; tl < TILES; ++tl)
 #pragma unroll
     for (int j = 0; j < MT; ++j) acc[tl][j][0] = acc[tl][j][1] = acc[tl][j][2] = acc[tl][j][3] = 0.f;
+  pdl_trigger();
+  pdl_wait();
 
   // this warp's share of the K/32 chunks
   const int chunks = K / 32;
@@ -140,7 +142,7 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
 template <int MT, int U, int TILES, int GW, typename TOut>
 void launch(const void* x, const void* W, void* y, int M, int N, int K, int ldy, int up_offset, cudaStream_t stream) {
   const int tiles = (N + 15) / 16;
-  gemm_small_m_kernel<MT, U, TILES, GW, TOut><<<tiles, GW * 32, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)W,
+  psb_launch(gemm_small_m_kernel<MT, U, TILES, GW, TOut>, dim3(tiles), dim3(GW * 32), 0, stream, (const __nv_bfloat16*)x, (const __nv_bfloat16*)W,
                                                                              (TOut*)y, M, N, K, ldy, up_offset);
 }
 
@@ -279,14 +281,19 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   uint32_t issue_slot = ring0;
   int issue_stage = 0;
   if (units > 0) tile_rows(0);
-  auto issue = [&]() {
+  // with_x false: only the weights (they never change; x comes from the preceding kernel and must wait for it)
+  auto issue = [&](bool with_w, bool with_x) {
+    if (with_w) {
 #pragma unroll
-    for (int tl = 0; tl < TILES; ++tl) {
-      cp16_cg(issue_slot + (2 * tl) * 512, wsrc[0] + tl * up_elems + issue_c * 32);
-      cp16_cg(issue_slot + (2 * tl + 1) * 512, wsrc[1] + tl * up_elems + issue_c * 32);
+      for (int tl = 0; tl < TILES; ++tl) {
+        cp16_cg(issue_slot + (2 * tl) * 512, wsrc[0] + tl * up_elems + issue_c * 32);
+        cp16_cg(issue_slot + (2 * tl + 1) * 512, wsrc[1] + tl * up_elems + issue_c * 32);
+      }
     }
+    if (with_x) {
 #pragma unroll
-    for (int j = 0; j < MT; ++j) cp16_ca_zfill(issue_slot + (2 * TILES + j) * 512, xsrc[j] + issue_c * 32, xbytes[j]);
+      for (int j = 0; j < MT; ++j) cp16_ca_zfill(issue_slot + (2 * TILES + j) * 512, xsrc[j] + issue_c * 32, xbytes[j]);
+    }
     ++issued;
     if (++issue_c == cpw) {
       issue_c = 0;
@@ -294,9 +301,18 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     }
     if (++issue_stage == STAGES) { issue_stage = 0; issue_slot = ring0; } else issue_slot += STAGE_BYTES;
   };
+  // The ring is primed in two passes over the same first STAGES-1 units: weights before the dependency wait,
+  // x after it.  All of it lands in the first commit groups, which the first wait_group covers.
+  pdl_trigger();
+#pragma unroll
+  for (int u = 0; u < STAGES - 1; ++u)
+    if (issued < units) issue(true, false);
+  pdl_wait();
+  issued = 0; issue_c = 0; issue_ti = 0; issue_slot = ring0; issue_stage = 0;
+  if (units > 0) tile_rows(0);
 #pragma unroll
   for (int u = 0; u < STAGES - 1; ++u) {
-    if (issued < units) issue();
+    if (issued < units) issue(false, true);
     asm volatile("cp.async.commit_group;\n" ::: "memory");
   }
 
@@ -309,7 +325,7 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 #pragma unroll
       for (int j = 0; j < MT; ++j) acc[tl][j][0] = acc[tl][j][1] = acc[tl][j][2] = acc[tl][j][3] = 0.f;
     for (int cc = 0; cc < cpw; ++cc) {
-      if (issued < units) issue();
+      if (issued < units) issue(true, true);
       asm volatile("cp.async.commit_group;\n" ::: "memory");
       asm volatile("cp.async.wait_group %0;\n" ::"n"(STAGES - 1) : "memory");
       uint4 wv[TILES][2], xv[MT];
@@ -379,7 +395,7 @@ int launch_stream(const void* x, const void* W, void* y, int M, int N, int K, in
   }
   const int tiles = (N + 15) / 16;
   const int grid = tiles < sms ? tiles : sms;
-  gemm_stream_kernel<MT, TILES, TOut><<<grid, SW * 32, Shape::SMEM_BYTES, stream>>>(
+  psb_launch(gemm_stream_kernel<MT, TILES, TOut>, dim3(grid), dim3(SW * 32), (size_t)Shape::SMEM_BYTES, stream,
       (const __nv_bfloat16*)x, (const __nv_bfloat16*)W, (TOut*)y, M, N, K, ldy, up_offset);
   return 0;
 }

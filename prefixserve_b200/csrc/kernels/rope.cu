@@ -24,6 +24,8 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, const int32_t* __r
                                    const float* __restrict__ sin_t, const int32_t* __restrict__ table, int table_width,
                                    TKV* __restrict__ kv, T* __restrict__ q_out, int hq, int hkv, int D, int page_size,
                                    int num_pages, int max_positions, int rotate, int write_kv) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int half = D >> 1;
   const int pos = positions[t];
@@ -91,7 +93,7 @@ PSB_API int psb_rope_append(const void* qkv, int dtype, const void* positions, c
   const int threads = work >= 1024 ? 256 : 128;
   PSB_DISPATCH_DTYPE(dtype, T_, {
     PSB_DISPATCH_DTYPE(kv_dtype, TKV, {
-      rope_append_kernel<T_, TKV><<<T, threads, 0, stream>>>(
+      psb_launch(rope_append_kernel<T_, TKV>, dim3(T), dim3(threads), 0, stream,
           (const T_*)qkv, (const int32_t*)positions, (const int32_t*)token_item, (const float*)cos_t, (const float*)sin_t,
           (const int32_t*)table, table_width, (TKV*)kv, (T_*)q_out, hq, hkv, D, page_size, num_pages, max_positions, rotate,
           write_kv);

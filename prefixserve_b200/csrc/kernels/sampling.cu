@@ -35,6 +35,8 @@ __global__ void sample_kernel(const float* __restrict__ logits, const float* __r
                               int parts) {
   __shared__ float best_v[32];
   __shared__ int best_i[32];
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x, part = blockIdx.y;
   const float* x = logits + (size_t)row * V;
   const float tau = temperature ? temperature[row] : 0.f;
@@ -91,6 +93,8 @@ __global__ void sample_kernel(const float* __restrict__ logits, const float* __r
 // One warp per row picks the winner among the parts (lowest index among equal values).
 __global__ void sample_finish_kernel(const float* __restrict__ part_v, const int32_t* __restrict__ part_i,
                                      int32_t* __restrict__ out, int parts) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x, lane = threadIdx.x;
   float bv = -FLT_MAX;
   int bi = 0x7fffffff;
@@ -132,9 +136,9 @@ PSB_API int psb_sample(const void* logits, const void* temperature, const void* 
   const int threads = per >= 16384 ? 1024 : (per >= 1024 ? 256 : 64);
   float* part_v = (float*)scratch;
   int32_t* part_i = (int32_t*)(part_v + (size_t)S * parts);
-  sample_kernel<<<dim3(S, parts), threads, 0, stream>>>((const float*)logits, (const float*)temperature, (const int64_t*)seed,
+  psb_launch(sample_kernel, dim3(S, parts), dim3(threads), 0, stream, (const float*)logits, (const float*)temperature, (const int64_t*)seed,
                                                        (const int32_t*)position, (int32_t*)out, part_v, part_i, V, parts);
-  if (parts > 1) sample_finish_kernel<<<S, 32, 0, stream>>>(part_v, part_i, (int32_t*)out, parts);
+  if (parts > 1) psb_launch(sample_finish_kernel, dim3(S), dim3(32), 0, stream, (const float*)part_v, (const int32_t*)part_i, (int32_t*)out, parts);
   PSB_LAUNCH_CHECK("sample");
   return 0;
 }

@@ -7,6 +7,7 @@ device is present, importing an op raises.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_int64, c_void_p
 
 from ..build import ensure_kernels
@@ -73,8 +74,24 @@ def lib() -> ctypes.CDLL:
         handle.psb_sample_scratch_bytes.restype = ctypes.c_longlong
         handle.psb_last_error.restype = ctypes.c_char_p
         handle.psb_last_error.argtypes = []
+        handle.psb_set_pdl.argtypes = [c_int]
+        handle.psb_set_pdl.restype = None
+        handle.psb_get_pdl.argtypes = []
+        handle.psb_get_pdl.restype = c_int
+        if os.environ.get("PSB200_PDL", "1") == "0":  # plain stream order between kernels (for comparisons)
+            handle.psb_set_pdl(0)
         _lib = handle
     return _lib
+
+
+def set_pdl(on: bool) -> None:
+    """Whether kernels are launched so that each may overlap its start with the end of its predecessor
+    (programmatic dependent launch).  Graphs captured earlier keep the mode they were captured with."""
+    lib().psb_set_pdl(1 if on else 0)
+
+
+def pdl_enabled() -> bool:
+    return bool(lib().psb_get_pdl())
 
 
 def declare(name: str, argtypes: list) -> None:

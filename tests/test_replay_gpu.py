@@ -130,3 +130,22 @@ def test_program_from_the_command_line(folders, truth, tmp_path, dtype):
     for (rid, pos), got in rows.items():
         want = truth["A"][rid][pos]
         assert float((got - want).abs().max()) <= tol * float(want.abs().max()), (rid, pos)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_overlapped_launches_change_nothing(folders, dtype):
+    """With and without programmatic dependent launch (each kernel starting while its predecessor drains) the logits
+    are bit-identical: the overlap only moves work that does not depend on the predecessor."""
+    from prefixserve_b200.ops import library
+    seqs = sequences("B")
+    steps = helpers.trace_mixed(seqs, seed=9) + [dict(s, step=s["step"] + 1000) for s in helpers.trace_tail_decode(seqs)]
+    assert library.pdl_enabled()
+    try:
+        with_overlap = replay(folders["B"], dtype, steps)
+        library.set_pdl(False)
+        without = replay(folders["B"], dtype, steps)
+    finally:
+        library.set_pdl(True)
+    assert with_overlap.keys() == without.keys()
+    for key, row in with_overlap.items():
+        assert torch.equal(row, without[key]), key
