@@ -11,8 +11,9 @@ from .library import check, lib
 
 # Tuning, set from measurements on B200 at Llama-1B sizes:
 STREAM_M = 16       # rows up to which the persistent streaming kernel is used (its limit is 16)
-STREAM_MIN_TILES = 300   # ... for matrices with at least this many 16-row tiles (about two per SM); smaller ones
-                         # balance better over one CTA per tile
+STREAM_MIN_TILES = 0     # ... for matrices with at least this many 16-row tiles.  0: always.  The streaming kernel holds
+                         # one CTA per SM by its shared memory, so kernels that start early (programmatic dependent
+                         # launch) cannot pile up on the SMs that free up first, which the one-tile-per-CTA kernel does.
 SMALL_M = 8         # rows up to which the one-tile-per-CTA kernel is used when the streaming kernel is not
 SMALL_M_GATED = 8   # same for the gate/up product with the fused activation
 WIDE_BELOW_TILES = 600   # matrices with fewer 16-row tiles than this get 16 warps per CTA instead of 8
