@@ -657,3 +657,43 @@ PSB_API int psb_attention_decode_bf16(const void* q, const void* kv, const void*
   PSB_LAUNCH_CHECK("attention_decode");
   return 0;
 }
+
+// ---- the same, with the scratch inside the library (see no_alloc.h: for callers that cannot allocate) -----------
+#include "no_alloc.h"
+
+namespace {
+// Partial results of the key ranges.  File scope, so the memory exists from the moment the library is loaded on a
+// device until the process ends.  In host code this name is only a handle for cudaGetSymbolAddress, never a pointer.
+static __device__ __align__(256) float g_decode_scratch[PSB_STATIC_SCRATCH_FLOATS];
+constexpr int MAX_DEVICES = 64;
+float* g_decode_scratch_addr[MAX_DEVICES] = {};  // device address of the array, per device, looked up on first use
+}  // namespace
+
+PSB_API int psb_attention_decode_bf16_static(const void* q, const void* kv, const void* table, int table_width,
+                                             const void* item_start, const void* kv_len, void* out, int num_items, int hq,
+                                             int hkv, int D, int page_size, int window, float scale, int chunk,
+                                             int max_splits, int all_single, cudaStream_t stream) {
+  if (num_items < 0 || hq < 1 || D < 1 || max_splits < 1) PSB_REFUSE("attention_decode_static: bad sizes");
+  const unsigned long long ranges = (unsigned long long)num_items * hq * max_splits;
+  const unsigned long long need = ranges * (unsigned long long)(D + 2);
+  if (need > PSB_STATIC_SCRATCH_FLOATS)
+    PSB_REFUSE("attention_decode_static: %d items x %d heads x %d key ranges x (%d + 2) floats = %llu exceed the built-in "
+               "scratch of %u floats; use fewer key ranges or the entry point that takes a scratch buffer",
+               num_items, hq, max_splits, D, need, (unsigned)PSB_STATIC_SCRATCH_FLOATS);
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) PSB_REFUSE("attention_decode_static: cudaGetDevice failed: %s", cudaGetErrorString(e));
+  if (device < 0 || device >= MAX_DEVICES) PSB_REFUSE("attention_decode_static: device index %d is out of range", device);
+  if (g_decode_scratch_addr[device] == nullptr) {
+    // once per device, with that device current; not inside a stream capture
+    float* addr = nullptr;
+    e = cudaGetSymbolAddress((void**)&addr, g_decode_scratch);
+    if (e != cudaSuccess || addr == nullptr)
+      PSB_REFUSE("attention_decode_static: cannot find the built-in scratch on device %d: %s", device, cudaGetErrorString(e));
+    g_decode_scratch_addr[device] = addr;
+  }
+  float* part_o = g_decode_scratch_addr[device];
+  float* part_ml = part_o + ranges * (unsigned long long)D;
+  return psb_attention_decode_bf16(q, kv, table, table_width, item_start, kv_len, out, part_o, part_ml, num_items, hq, hkv, D,
+                                   page_size, window, scale, chunk, max_splits, all_single, stream);
+}
