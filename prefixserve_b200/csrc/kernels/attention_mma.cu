@@ -14,8 +14,9 @@
 // key/value head, so keys and values are read once per group of query heads.
 //
 // Two kernels:
-//  * prefill: a CTA owns 128 rows of one item (4 warps x 32 rows), each warp walks
-//    the keys its rows may see (causal, optional window);
+//  * prefill: a CTA owns 128 rows of one item (4 warps x 32 rows) and walks the keys
+//    they may see (causal, optional window) in blocks of 64 shared through a ring
+//    in shared memory;
 //  * decode: a CTA owns one (item, key/value head, key range); its 4 warps take
 //    16-key tiles in turn and merge at the end; key ranges of one item are merged
 //    by a second small kernel (split-KV).  Only items that bring exactly one token.
@@ -191,142 +192,6 @@ __device__ __forceinline__ const __nv_bfloat16* tile_ptr(const __nv_bfloat16* kv
   return kv + ((size_t)page * 2 * hkv + h) * (size_t)page_size * D + (size_t)(key0 % page_size) * D;
 }
 
-// --------------------------------------------------------------------------------------------- prefill
-// PREFILL_MT: 16-row tiles per warp (2 at head size 64; 1 at 128, where two would spill registers).
-template <int D, int PREFILL_MT>
-__global__ void __launch_bounds__(WARPS * 32)
-attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kv,
-                         const int32_t* __restrict__ table, int table_width, const int32_t* __restrict__ item_start,
-                         const int32_t* __restrict__ kv_len, __nv_bfloat16* __restrict__ out, int num_items, int hq, int hkv,
-                         int page_size, int window, float scale, int skip_single) {
-  constexpr int PREFILL_ROWS = WARPS * 16 * PREFILL_MT;  // rows per CTA
-  pdl_trigger();
-  pdl_wait();
-  const int G = hq / hkv;
-  const int h = blockIdx.y;
-  // which item and which of its row tiles is this CTA?
-  int item = -1, tile = 0, n = 0;
-  {
-    int left = blockIdx.x;
-    for (int i = 0; i < num_items; ++i) {
-      const int ni = item_start[i + 1] - item_start[i];
-      if (skip_single && ni == 1) continue;
-      const int tiles = (ni * G + PREFILL_ROWS - 1) / PREFILL_ROWS;
-      if (left < tiles) { item = i; tile = left; n = ni; break; }
-      left -= tiles;
-    }
-  }
-  if (item < 0) return;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int t0 = item_start[item];
-  const int kvl = kv_len[item];
-  const int first_pos = kvl - n;  // position of the item's first new token
-  const int32_t* pages = table + (size_t)item * table_width;
-  const float sl2 = scale * LOG2E;
-  const size_t v_off = (size_t)hkv * page_size * D;
-
-  const int rows = n * G;
-  const int r_base = tile * PREFILL_ROWS + warp * 16 * PREFILL_MT;
-  if (r_base >= rows) return;
-
-  uint32_t qa[PREFILL_MT][D / 16][4];
-  RowState<D> st[PREFILL_MT];
-  int pos[PREFILL_MT][2], lo[PREFILL_MT][2], tok[PREFILL_MT][2], head[PREFILL_MT][2];
-  int max_pos = -1, min_pos = 0x7fffffff, min_lo = 0x7fffffff, max_lo = 0;
-#pragma unroll
-  for (int mt = 0; mt < PREFILL_MT; ++mt) {
-    const __nv_bfloat16* rp[2];
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      const int row = r_base + mt * 16 + g + 8 * r;
-      if (row < rows) {
-        tok[mt][r] = row / G;
-        head[mt][r] = h * G + row % G;
-        pos[mt][r] = first_pos + tok[mt][r];
-        lo[mt][r] = (window > 0 && pos[mt][r] - window + 1 > 0) ? pos[mt][r] - window + 1 : 0;
-        rp[r] = q + ((size_t)(t0 + tok[mt][r]) * hq + head[mt][r]) * D;
-      } else {
-        tok[mt][r] = -1; head[mt][r] = 0; pos[mt][r] = -1; lo[mt][r] = 0x7fffffff;
-        rp[r] = nullptr;
-      }
-    }
-    load_q<D>(qa[mt], rp[0], rp[1], t);
-    st[mt].init();
-  }
-  // the warp's key range: every lane must agree, so reduce over the warp
-#pragma unroll
-  for (int mt = 0; mt < PREFILL_MT; ++mt)
-#pragma unroll
-    for (int r = 0; r < 2; ++r)
-      if (tok[mt][r] >= 0) {
-        max_pos = max(max_pos, pos[mt][r]);
-        min_pos = min(min_pos, pos[mt][r]);
-        min_lo = min(min_lo, lo[mt][r]);
-        max_lo = max(max_lo, lo[mt][r]);
-      }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    max_pos = max(max_pos, __shfl_xor_sync(0xffffffffu, max_pos, o));
-    min_pos = min(min_pos, __shfl_xor_sync(0xffffffffu, min_pos, o));
-    min_lo = min(min_lo, __shfl_xor_sync(0xffffffffu, min_lo, o));
-    max_lo = max(max_lo, __shfl_xor_sync(0xffffffffu, max_lo, o));
-  }
-
-  const int k_first = min_lo & ~15;
-  // page ids of 32 tiles at a time, one per lane, handed out by shuffle (a table load per tile would stall the warp)
-  const size_t head_off = (size_t)h * page_size * D;
-  const size_t page_elems = (size_t)2 * hkv * page_size * D;
-  auto fetch_pages = [&](int key) {  // ids of the pages holding keys key, key+16, ... (one per lane)
-    const int k = key + 16 * lane;
-    return k <= max_pos ? pages[k / page_size] : 0;
-  };
-  int page_ids = fetch_pages(k_first);
-  int page_base = k_first;  // key of lane 0's tile in page_ids
-  auto tile_at = [&](int key) {
-    if (key - page_base >= 512) { page_base = key; page_ids = fetch_pages(key); }
-    const int page = __shfl_sync(0xffffffffu, page_ids, (key - page_base) >> 4);
-    return kv + (size_t)page * page_elems + head_off + (size_t)(key % page_size) * D;
-  };
-  KVTile<D> cur, nxt;
-  {
-    const __nv_bfloat16* kp = tile_at(k_first);
-    load_tile<D>(cur, kp, kp + v_off, kvl - k_first, g, t);
-  }
-  for (int key0 = k_first; key0 <= max_pos; key0 += 16) {
-    const int next0 = key0 + 16;
-    if (next0 <= max_pos) {  // fetch the next tile while this one is used
-      const __nv_bfloat16* kp = tile_at(next0);
-      load_tile<D>(nxt, kp, kp + v_off, kvl - next0, g, t);
-    }
-    const bool needs_mask = key0 + 15 > min_pos || key0 < max_lo;
-#pragma unroll
-    for (int mt = 0; mt < PREFILL_MT; ++mt) {
-      float s[2][4];
-      scores<D>(s, qa[mt], cur);
-      if (needs_mask) mask_tile(s, key0, t, pos[mt], lo[mt]);
-      fold<D>(st[mt], s, cur, sl2);
-    }
-    if (next0 <= max_pos) cur = nxt;
-  }
-#pragma unroll
-  for (int mt = 0; mt < PREFILL_MT; ++mt)
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      float l = st[mt].l[r];
-      l += __shfl_xor_sync(0xffffffffu, l, 1);
-      l += __shfl_xor_sync(0xffffffffu, l, 2);
-      if (tok[mt][r] < 0) continue;
-      const float inv = 1.f / l;
-      __nv_bfloat16* orow = out + ((size_t)(t0 + tok[mt][r]) * hq + head[mt][r]) * D;
-      // this lane owns dims [2t*D/8, (2t+2)*D/8): n = 2t -> first half, n = 2t+1 -> second half
-#pragma unroll
-      for (int j = 0; j < D / 8; ++j) {
-        orow[(2 * t) * (D / 8) + j] = __float2bfloat16_rn(st[mt].o[j][2 * r] * inv);
-        orow[(2 * t + 1) * (D / 8) + j] = __float2bfloat16_rn(st[mt].o[j][2 * r + 1] * inv);
-      }
-    }
-}
-
 // ---------------------------------------------------------------------------------------------- decode
 // grid (splits, hkv, items).  Partial results (float32): part_o[item][head][split][D], part_ml[item][head][split][2].
 //
@@ -358,6 +223,286 @@ __device__ __forceinline__ uint4 lds16(uint32_t addr) {
   uint4 v;
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
   return v;
+}
+
+// --------------------------------------------------------------------------------------------- prefill
+// A CTA owns 64*MT rows ((token, head-in-group) pairs of one key/value head of one item); its 4 warps own 16*MT rows
+// each.  Keys are walked in blocks of 64 (four 16-key tiles): warp w brings tile w of every block into a ring in
+// shared memory with cp.async, laid out piece-by-piece exactly as lanes will read them ((tile*PIECES + piece)*32 +
+// lane), so every warp reads every tile without bank conflicts and each key/value is fetched once per CTA.  Scores
+// of a whole block are held in registers and folded into the running softmax once per block.
+template <int D>
+struct PrefillShape {
+  static constexpr int PIECES = 2 * (D / 32) + 4 * (D / 64);
+  static constexpr int STAGES = 3;
+  static constexpr int TILE_BYTES = PIECES * 32 * 16;
+  static constexpr int STAGE_BYTES = WARPS * TILE_BYTES;  // one 64-key block
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES;
+};
+
+template <int D, int MT>
+__global__ void __launch_bounds__(WARPS * 32)
+attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kv,
+                         const int32_t* __restrict__ table, int table_width, const int32_t* __restrict__ item_start,
+                         const int32_t* __restrict__ kv_len, __nv_bfloat16* __restrict__ out, int num_items, int hq, int hkv,
+                         int page_shift, int window, float scale, int skip_single) {
+  using Shape = PrefillShape<D>;
+  constexpr int STAGES = Shape::STAGES, PIECES = Shape::PIECES, KP = 2 * (D / 32);
+  constexpr int ROWS = WARPS * 16 * MT;  // rows per CTA
+  constexpr int BLOCK = WARPS * 16;      // keys per block
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  pdl_trigger();
+  const int G = hq / hkv;
+  const int h = blockIdx.y;
+  // which item and which of its row tiles is this CTA?  (lengths are inputs of the step: readable before the wait)
+  int item = -1, tile = 0, n = 0;
+  {
+    int left = blockIdx.x;  // block 0 takes the last (longest) row tile of the last item
+    for (int i = num_items - 1; i >= 0; --i) {
+      const int ni = item_start[i + 1] - item_start[i];
+      if (skip_single && ni == 1) continue;
+      const int tiles = (ni * G + ROWS - 1) / ROWS;
+      if (left < tiles) { item = i; tile = tiles - 1 - left; n = ni; break; }
+      left -= tiles;
+    }
+  }
+  pdl_wait();
+  if (item < 0) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int t0 = item_start[item];
+  const int kvl = kv_len[item];
+  const int first_pos = kvl - n;  // position of the item's first new token
+  const int32_t* pages = table + (size_t)item * table_width;
+  const float sl2 = scale * LOG2E;
+  const int page_size = 1 << page_shift;
+  const size_t page_elems = (size_t)2 * hkv * page_size * D;
+  const __nv_bfloat16* kv_head = kv + (size_t)h * page_size * D;
+  const int v_off = hkv * page_size * D;
+  const int rows = n * G;
+
+  // ---- this warp's rows
+  const int r_base = tile * ROWS + warp * 16 * MT;
+  uint32_t qa[MT][D / 16][4];
+  int pos[MT][2], lo[MT][2], tok[MT][2], head[MT][2];
+  int w_max_pos = -1, w_min_pos = 0x7fffffff, w_min_lo = 0x7fffffff, w_max_lo = 0;
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) {
+    const __nv_bfloat16* rp[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = r_base + mt * 16 + g + 8 * r;
+      if (row < rows) {
+        tok[mt][r] = row / G;
+        head[mt][r] = h * G + row % G;
+        pos[mt][r] = first_pos + tok[mt][r];
+        lo[mt][r] = (window > 0 && pos[mt][r] - window + 1 > 0) ? pos[mt][r] - window + 1 : 0;
+        rp[r] = q + ((size_t)(t0 + tok[mt][r]) * hq + head[mt][r]) * D;
+        w_max_pos = max(w_max_pos, pos[mt][r]);
+        w_min_pos = min(w_min_pos, pos[mt][r]);
+        w_min_lo = min(w_min_lo, lo[mt][r]);
+        w_max_lo = max(w_max_lo, lo[mt][r]);
+      } else {
+        tok[mt][r] = -1; head[mt][r] = 0; pos[mt][r] = -1; lo[mt][r] = 0x7fffffff;
+        rp[r] = nullptr;
+      }
+    }
+    load_q<D>(qa[mt], rp[0], rp[1], t);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    w_max_pos = max(w_max_pos, __shfl_xor_sync(0xffffffffu, w_max_pos, o));
+    w_min_pos = min(w_min_pos, __shfl_xor_sync(0xffffffffu, w_min_pos, o));
+    w_min_lo = min(w_min_lo, __shfl_xor_sync(0xffffffffu, w_min_lo, o));
+    w_max_lo = max(w_max_lo, __shfl_xor_sync(0xffffffffu, w_max_lo, o));
+  }
+  // ---- the CTA's key range: rows of the tile are consecutive, so its first and last row bound everything
+  const int first_row = tile * ROWS, last_row = min(rows, first_row + ROWS) - 1;
+  const int cta_max_pos = first_pos + last_row / G;
+  const int cta_first_pos = first_pos + first_row / G;
+  const int cta_min_lo = (window > 0 && cta_first_pos - window + 1 > 0) ? cta_first_pos - window + 1 : 0;
+  const int k_first = cta_min_lo & ~(BLOCK - 1);
+  const int n_blocks = (cta_max_pos - k_first) / BLOCK + 1;
+
+  // ---- ring: warp w copies tile w of each block
+  int off[PIECES], key_of[PIECES];
+  {
+    int piece = 0;
+#pragma unroll
+    for (int half = 0; half < 2; ++half)
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c, ++piece) {
+        key_of[piece] = half * 8 + g;
+        off[piece] = key_of[piece] * D + c * 32 + t * 8;
+      }
+#pragma unroll
+    for (int sl = 0; sl < 4; ++sl)
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c, ++piece) {
+        key_of[piece] = 2 * t + (sl & 1) + (sl >> 1) * 8;
+        off[piece] = v_off + key_of[piece] * D + g * (D / 8) + c * 8;
+      }
+  }
+  const uint32_t smem0 = (uint32_t)__cvta_generic_to_shared(smem_raw);
+  const uint32_t my_slot0 = smem0 + warp * Shape::TILE_BYTES + lane * 16;  // where this lane writes (stage 0)
+  const uint32_t rd0 = smem0 + lane * 16;                                   // where this lane reads (stage 0, tile 0)
+  auto fetch_pages = [&](int first_block) {  // page ids of this warp's tile in blocks first_block + lane
+    const int key = k_first + (first_block + lane) * BLOCK + warp * 16;
+    return (first_block + lane < n_blocks && key <= cta_max_pos) ? pages[key >> page_shift] : 0;
+  };
+  int page_ids = fetch_pages(0);
+  int issued = 0, issue_stage = 0;
+  auto issue = [&]() {
+    if ((issued & 31) == 0 && issued > 0) page_ids = fetch_pages(issued);
+    const int page = __shfl_sync(0xffffffffu, page_ids, issued & 31);
+    const int key0 = k_first + issued * BLOCK + warp * 16;
+    const uint32_t slot = my_slot0 + issue_stage * Shape::STAGE_BYTES;
+    int valid = min(kvl, cta_max_pos + 1) - key0;  // keys of this tile anybody in the CTA may see
+    const __nv_bfloat16* base = kv_head + (size_t)page * page_elems + (size_t)(key0 & (page_size - 1)) * D;
+    if (valid >= 16) {
+#pragma unroll
+      for (int i = 0; i < PIECES; ++i) cp16_cg(slot + i * 512, base + off[i]);
+    } else {  // keys nobody may see (or that do not exist) are filled with zeros, never read from memory
+#pragma unroll
+      for (int i = 0; i < PIECES; ++i) {
+        const bool ok = key_of[i] < valid;
+        cp16_cg_zfill(slot + i * 512, ok ? base + off[i] : kv, ok ? 16 : 0);
+      }
+    }
+    ++issued;
+    if (++issue_stage == STAGES) issue_stage = 0;
+  };
+#pragma unroll
+  for (int i = 0; i < STAGES - 1; ++i) {
+    if (issued < n_blocks) issue();
+    cp_async_commit();
+  }
+
+  RowState<D> st[MT];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) st[mt].init();
+  const bool warp_live = r_base < rows;
+
+  int read_stage = 0;
+  for (int b = 0; b < n_blocks; ++b) {
+    cp_async_wait<STAGES - 2>();  // this thread's copies of block b have landed
+    __syncthreads();              // ... and everybody's; and everybody is done with block b-1
+    if (issued < n_blocks) issue();  // block b + STAGES - 1 goes where block b - 1 was
+    cp_async_commit();
+    const int key_b = k_first + b * BLOCK;
+    const uint32_t rd = rd0 + read_stage * Shape::STAGE_BYTES;
+    if (++read_stage == STAGES) read_stage = 0;
+    if (!warp_live || key_b > w_max_pos || key_b + BLOCK <= w_min_lo) continue;  // nothing here for this warp's rows
+
+    float s[MT][2 * WARPS][4];
+#pragma unroll
+    for (int tl = 0; tl < WARPS; ++tl) {
+      uint4 kf[KP];
+#pragma unroll
+      for (int j = 0; j < KP; ++j) kf[j] = lds16(rd + tl * Shape::TILE_BYTES + j * 512);
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          float(&acc)[4] = s[mt][2 * tl + half];
+          acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            const uint4 kk = kf[half * (D / 32) + c];
+            mma_bf16(acc, qa[mt][2 * c], kk.x, kk.y);
+            mma_bf16(acc, qa[mt][2 * c + 1], kk.z, kk.w);
+          }
+        }
+    }
+    const bool needs_mask = key_b + BLOCK - 1 > w_min_pos || key_b < w_max_lo;
+    uint32_t pa[MT][WARPS][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      if (needs_mask) {
+#pragma unroll
+        for (int nt = 0; nt < 2 * WARPS; ++nt)
+#pragma unroll
+          for (int r = 0; r < 2; ++r)
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              const int key = key_b + nt * 8 + 2 * t + i;
+              if (key > pos[mt][r] || key < lo[mt][r]) s[mt][nt][2 * r + i] = -INFINITY;
+            }
+      }
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 2 * WARPS; ++nt) mx = fmaxf(mx, fmaxf(s[mt][nt][2 * r], s[mt][nt][2 * r + 1]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(st[mt].m[r], mx * sl2);
+        const float m_safe = m_new == -INFINITY ? 0.f : m_new;
+        const float alpha = fast_exp2(st[mt].m[r] - m_safe);
+        st[mt].m[r] = m_new;
+        float sum = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 2 * WARPS; ++nt)
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            const float e = fast_exp2(fmaf(s[mt][nt][2 * r + i], sl2, -m_safe));
+            s[mt][nt][2 * r + i] = e;
+            sum += e;
+          }
+        st[mt].l[r] = st[mt].l[r] * alpha + sum;
+#pragma unroll
+        for (int j = 0; j < D / 8; ++j) {
+          st[mt].o[j][2 * r] *= alpha;
+          st[mt].o[j][2 * r + 1] *= alpha;
+        }
+      }
+#pragma unroll
+      for (int tl = 0; tl < WARPS; ++tl) {
+        pa[mt][tl][0] = pack_bf16(s[mt][2 * tl][0], s[mt][2 * tl][1]);
+        pa[mt][tl][1] = pack_bf16(s[mt][2 * tl][2], s[mt][2 * tl][3]);
+        pa[mt][tl][2] = pack_bf16(s[mt][2 * tl + 1][0], s[mt][2 * tl + 1][1]);
+        pa[mt][tl][3] = pack_bf16(s[mt][2 * tl + 1][2], s[mt][2 * tl + 1][3]);
+      }
+    }
+#pragma unroll
+    for (int tl = 0; tl < WARPS; ++tl) {
+      uint4 vf[PIECES - KP];
+#pragma unroll
+      for (int j = 0; j < PIECES - KP; ++j) vf[j] = lds16(rd + tl * Shape::TILE_BYTES + (KP + j) * 512);
+      const uint32_t* v0 = reinterpret_cast<const uint32_t*>(&vf[0 * (D / 64)]);
+      const uint32_t* v1 = reinterpret_cast<const uint32_t*>(&vf[1 * (D / 64)]);
+      const uint32_t* v2 = reinterpret_cast<const uint32_t*>(&vf[2 * (D / 64)]);
+      const uint32_t* v3 = reinterpret_cast<const uint32_t*>(&vf[3 * (D / 64)]);
+#pragma unroll
+      for (int j = 0; j < D / 8; ++j) {
+        const uint32_t sel = (j & 1) ? 0x7632u : 0x5410u;
+        const uint32_t b0 = __byte_perm(v0[j >> 1], v1[j >> 1], sel);
+        const uint32_t b1 = __byte_perm(v2[j >> 1], v3[j >> 1], sel);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) mma_bf16(st[mt].o[j], pa[mt][tl], b0, b1);
+      }
+    }
+  }
+  cp_async_wait<0>();
+  if (!warp_live) return;
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      float l = st[mt].l[r];
+      l += __shfl_xor_sync(0xffffffffu, l, 1);
+      l += __shfl_xor_sync(0xffffffffu, l, 2);
+      if (tok[mt][r] < 0) continue;
+      const float inv = 1.f / l;
+      __nv_bfloat16* orow = out + ((size_t)(t0 + tok[mt][r]) * hq + head[mt][r]) * D;
+      // this lane owns dims [2t*D/8, (2t+2)*D/8): accumulator column 2t is the first half, 2t+1 the second
+#pragma unroll
+      for (int j = 0; j < D / 8; j += 2) {
+        *reinterpret_cast<uint32_t*>(orow + (2 * t) * (D / 8) + j) =
+            pack_bf16(st[mt].o[j][2 * r] * inv, st[mt].o[j + 1][2 * r] * inv);
+        *reinterpret_cast<uint32_t*>(orow + (2 * t + 1) * (D / 8) + j) =
+            pack_bf16(st[mt].o[j][2 * r + 1] * inv, st[mt].o[j + 1][2 * r + 1] * inv);
+      }
+    }
 }
 
 // all_single: every item of the step brings one token (then item i's token is row i and item_start need not be read).
@@ -605,11 +750,24 @@ PSB_API int psb_attention_prefill_bf16(const void* q, const void* kv, const void
   if (num_items < 0 || num_tiles < 0) PSB_REFUSE("attention_prefill: negative sizes");
   if (num_items == 0 || num_tiles == 0) return 0;
   if (hkv > 65535) PSB_REFUSE("attention_prefill: too many key/value heads");
+  if (page_size & (page_size - 1)) PSB_REFUSE("attention_prefill: page size %d is not a power of two", page_size);
+  int page_shift = 0;
+  while ((1 << page_shift) < page_size) ++page_shift;
   dim3 grid(num_tiles, hkv);
 #define PSB_PREFILL(DD, MT)                                                                                          \
-  psb_launch(attention_prefill_kernel<DD, MT>, grid, dim3(WARPS * 32), 0, stream, \
-      (const __nv_bfloat16*)q, (const __nv_bfloat16*)kv, (const int32_t*)table, table_width, (const int32_t*)item_start, \
-      (const int32_t*)kv_len, (__nv_bfloat16*)out, num_items, hq, hkv, page_size, window, scale, skip_single)
+  do {                                                                                                               \
+    static bool configured = false; /* more than 48 KB of dynamic shared memory has to be asked for once */           \
+    if (!configured) {                                                                                               \
+      cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<DD, MT>,                                         \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, PrefillShape<DD>::SMEM_BYTES); \
+      if (e != cudaSuccess) PSB_REFUSE("attention_prefill: cannot reserve shared memory: %s", cudaGetErrorString(e)); \
+      configured = true;                                                                                             \
+    }                                                                                                                \
+    psb_launch(attention_prefill_kernel<DD, MT>, grid, dim3(WARPS * 32), (size_t)PrefillShape<DD>::SMEM_BYTES, stream, \
+        (const __nv_bfloat16*)q, (const __nv_bfloat16*)kv, (const int32_t*)table, table_width,                       \
+        (const int32_t*)item_start, (const int32_t*)kv_len, (__nv_bfloat16*)out, num_items, hq, hkv, page_shift,     \
+        window, scale, skip_single);                                                                                 \
+  } while (0)
   if (D == 64) PSB_PREFILL(64, 2); else PSB_PREFILL(128, 1);
 #undef PSB_PREFILL
   PSB_LAUNCH_CHECK("attention_prefill");
