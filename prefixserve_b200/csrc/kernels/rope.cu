@@ -18,6 +18,39 @@
 
 namespace {
 
+template <typename T>
+__device__ __forceinline__ void load8v(const T* p, float (&o)[8]);
+template <>
+__device__ __forceinline__ void load8v<float>(const float* p, float (&o)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8v<__nv_bfloat16>(const __nv_bfloat16* p, float (&o)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 f = __bfloat1622float2(h2[k]);
+    o[2 * k] = f.x; o[2 * k + 1] = f.y;
+  }
+}
+template <typename T>
+__device__ __forceinline__ void store8v(T* p, const float (&v)[8]);
+template <>
+__device__ __forceinline__ void store8v<float>(float* p, const float (&v)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <>
+__device__ __forceinline__ void store8v<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[8]) {
+  uint4 raw;
+  __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) h2[k] = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
+  *reinterpret_cast<uint4*>(p) = raw;
+}
+
 template <typename T, typename TKV>
 __global__ void rope_append_kernel(const T* __restrict__ qkv, const int32_t* __restrict__ positions,
                                    const int32_t* __restrict__ token_item, const float* __restrict__ cos_t,
@@ -78,6 +111,75 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, const int32_t* __r
   }
 }
 
+// Eight pairs per thread: 16/32-byte loads of both halves of a head and of the angle tables.  Needs (D/2) % 8 == 0.
+template <typename T, typename TKV>
+__global__ void rope_append_vec_kernel(const T* __restrict__ qkv, const int32_t* __restrict__ positions,
+                                       const int32_t* __restrict__ token_item, const float* __restrict__ cos_t,
+                                       const float* __restrict__ sin_t, const int32_t* __restrict__ table, int table_width,
+                                       TKV* __restrict__ kv, T* __restrict__ q_out, int hq, int hkv, int D, int page_size,
+                                       int num_pages, int max_positions, int rotate, int write_kv) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int half = D >> 1;
+  const int pos = positions[t];
+  const int heads_in = hq + 2 * hkv;
+  const T* row = qkv + (size_t)t * heads_in * D;
+  const int safe_pos = pos < 0 ? 0 : (pos >= max_positions ? max_positions - 1 : pos);
+  const float* c = cos_t + (size_t)safe_pos * half;
+  const float* s = sin_t + (size_t)safe_pos * half;
+  TKV* kdst = nullptr;
+  TKV* vdst = nullptr;
+  if (write_kv) {
+    const int item = token_item[t];
+    const int page = table[(size_t)item * table_width + pos / page_size];
+    if (page >= 0 && page < num_pages) {
+      const size_t page_elems = (size_t)2 * hkv * page_size * D;
+      kdst = kv + (size_t)page * page_elems + (size_t)(pos % page_size) * D;
+      vdst = kdst + (size_t)hkv * page_size * D;
+    }
+  }
+  const int rot_heads = write_kv ? hq + hkv : hq;
+  const int vec_per_head = half >> 3;
+  for (int idx = threadIdx.x; idx < rot_heads * vec_per_head; idx += blockDim.x) {
+    const int head = idx / vec_per_head, j = (idx - head * vec_per_head) << 3;
+    float x1[8], x2[8], o1[8], o2[8];
+    load8v<T>(row + head * D + j, x1);
+    load8v<T>(row + head * D + j + half, x2);
+    if (rotate) {
+      float cs[8], sn[8];
+      load8v<float>(c + j, cs);
+      load8v<float>(s + j, sn);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        o1[k] = x1[k] * cs[k] - x2[k] * sn[k];
+        o2[k] = x2[k] * cs[k] + x1[k] * sn[k];
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) { o1[k] = x1[k]; o2[k] = x2[k]; }
+    }
+    if (head < hq) {
+      T* qo = q_out + ((size_t)t * hq + head) * D;
+      store8v<T>(qo + j, o1);
+      store8v<T>(qo + j + half, o2);
+    } else if (kdst) {
+      TKV* k = kdst + (size_t)(head - hq) * page_size * D;
+      store8v<TKV>(k + j, o1);
+      store8v<TKV>(k + j + half, o2);
+    }
+  }
+  if (vdst) {
+    const T* vrow = row + (size_t)(hq + hkv) * D;
+    for (int idx = threadIdx.x; idx < hkv * (D >> 3); idx += blockDim.x) {
+      const int head = idx / (D >> 3), j = (idx - head * (D >> 3)) << 3;
+      float v[8];
+      load8v<T>(vrow + head * D + j, v);
+      store8v<TKV>(vdst + (size_t)head * page_size * D + j, v);
+    }
+  }
+}
+
 }  // namespace
 
 PSB_API int psb_rope_append(const void* qkv, int dtype, const void* positions, const void* token_item, const void* cos_t,
@@ -90,6 +192,19 @@ PSB_API int psb_rope_append(const void* qkv, int dtype, const void* positions, c
   if (rotate && (!cos_t || !sin_t || max_positions < 1)) PSB_REFUSE("rope_append: angle tables missing");
   if (T == 0) return 0;
   const int work = (hq + hkv) * (D / 2);
+  if (D % 16 == 0) {  // every 8-element run is aligned: vector accesses
+    const int threads = work / 8 >= 256 ? 256 : (work / 8 >= 128 ? 128 : 64);
+    PSB_DISPATCH_DTYPE(dtype, T_, {
+      PSB_DISPATCH_DTYPE(kv_dtype, TKV, {
+        psb_launch(rope_append_vec_kernel<T_, TKV>, dim3(T), dim3(threads), 0, stream,
+            (const T_*)qkv, (const int32_t*)positions, (const int32_t*)token_item, (const float*)cos_t, (const float*)sin_t,
+            (const int32_t*)table, table_width, (TKV*)kv, (T_*)q_out, hq, hkv, D, page_size, num_pages, max_positions, rotate,
+            write_kv);
+      });
+    });
+    PSB_LAUNCH_CHECK("rope_append");
+    return 0;
+  }
   const int threads = work >= 1024 ? 256 : 128;
   PSB_DISPATCH_DTYPE(dtype, T_, {
     PSB_DISPATCH_DTYPE(kv_dtype, TKV, {
