@@ -76,6 +76,10 @@ class ModelRunner:
         self.use_graphs = use_graphs and all(getattr(p, "graph_safe", False) for _, p in model.named_parts())
         self._graphs: dict[int, _DecodeGraph] = {}
         self.graph_replays = 0
+        # Test-only, after the reference's EngineConfig.inject_bug (prefixserve/llama_engine.py:62-63, :192, :202-203):
+        # "rope_relative" numbers every portion's positions from 0; "kv_len_short" reports one key too few.
+        # The test suite proves with these that it notices such faults.
+        self.inject_bug: str | None = None
 
     # ------------------------------------------------------------------ checks
     def _check(self, items: Sequence[StepItem]) -> None:
@@ -151,9 +155,10 @@ class ModelRunner:
         buf[o_start] = 0
         for i, (it, n) in enumerate(zip(items, lens)):
             buf[o_ids + tok: o_ids + tok + n] = it.tokens
-            buf[o_pos + tok: o_pos + tok + n] = np.arange(it.start, it.start + n, dtype=np.int32)  # absolute
+            first = 0 if self.inject_bug == "rope_relative" else it.start
+            buf[o_pos + tok: o_pos + tok + n] = np.arange(first, first + n, dtype=np.int32)  # absolute positions
             buf[o_item + tok: o_item + tok + n] = i
-            buf[o_kvlen + i] = it.start + n
+            buf[o_kvlen + i] = it.start + n - (1 if self.inject_bug == "kv_len_short" and it.start + n > n else 0)
             buf[o_slot + i] = it.slot
             for w in it.want:
                 buf[o_rows + ri] = tok + w

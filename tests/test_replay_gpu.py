@@ -149,3 +149,23 @@ def test_overlapped_launches_change_nothing(folders, dtype):
     assert with_overlap.keys() == without.keys()
     for key, row in with_overlap.items():
         assert torch.equal(row, without[key]), key
+
+
+@pytest.mark.parametrize("dtype,bug", [("float32", "rope_relative"), ("bfloat16", "rope_relative"), ("bfloat16", "kv_len_short")])
+def test_injected_faults_are_noticed(folders, truth, dtype, bug):
+    """The comparison used above must fail when the step function is given relative positions or a short key count
+    (the faults PrefixServe injects in tests/test_llama_exact.py:227-241 to prove its own suite)."""
+    from prefixserve_b200.engine.replay import Replayer
+    seqs = {"r0": sequences("C")["r2"]}
+    steps = helpers.trace_portions(seqs)
+    rp = Replayer(folders["C"], dtype, helpers.peak_tokens(steps))
+    rp.runner.inject_bug = bug
+    outputs = {}
+    for st in steps:
+        out = rp.run_step(st)
+        if out is not None:
+            outputs[st["step"]] = torch.from_numpy(out.copy())
+    rows = helpers.collect(steps, outputs)
+    want = truth["C"]["r0"]
+    got = torch.stack([rows[("r0", p)] for p in range(len(seqs["r0"]))])
+    assert helpers.rel_err(got[20:], want[20:]) > 0.15, "the injected fault went unnoticed"
