@@ -18,9 +18,8 @@
 //    they may see (causal, optional window) in blocks of 64 shared through a ring
 //    in shared memory;
 //  * decode: a CTA owns one (item, key/value head, key range); its 4 warps take
-//    16-key tiles in turn and merge at the end; the CTA that finishes last among the
-//    key ranges of an (item, key/value head) combines them (split-KV without a second
-//    kernel).  Only items that bring exactly one token.
+//    16-key tiles in turn and merge at the end; key ranges of one item are merged
+//    by a second small kernel (split-KV).  Only items that bring exactly one token.
 //
 // Math as in the generic kernel (prefixserve/model/attention.py:68-121 of
 // PrefixServe): scores * scale, key j visible to position p iff j <= p (and
@@ -194,8 +193,7 @@ __device__ __forceinline__ const __nv_bfloat16* tile_ptr(const __nv_bfloat16* kv
 }
 
 // ---------------------------------------------------------------------------------------------- decode
-// grid (splits, hkv, items).  Partial results (float32): part_o[item][head][split][D], part_ml[item][head][split][2],
-// then one int32 counter per (item, key/value head), zero between launches.
+// grid (splits, hkv, items).  Partial results (float32): part_o[item][head][split][D], part_ml[item][head][split][2].
 //
 // Each lane streams the 16-byte pieces it will need (the same ones load_tile reads) through a ring of its own in
 // shared memory with cp.async: slot = ((warp*STAGES + stage)*PIECES + piece)*32 + lane.  A lane only ever touches
@@ -212,10 +210,7 @@ struct DecodeShape {
   static constexpr int STAGE_BYTES = PIECES * 32 * 16;
   static constexpr int RING_BYTES = WARPS * STAGES * STAGE_BYTES;
   static constexpr int MERGE_BYTES = WARPS * 16 * (D + 4 + 2) * 4;
-  static constexpr int MAX_SPLITS = 256;                       // weights of the final merge: 16 * MAX_SPLITS floats
-  static constexpr int FINAL_BYTES = 16 * (MAX_SPLITS + 1) * 4;
-  static constexpr int SMEM_A = RING_BYTES > MERGE_BYTES ? RING_BYTES : MERGE_BYTES;
-  static constexpr int SMEM_BYTES = SMEM_A > FINAL_BYTES ? SMEM_A : FINAL_BYTES;
+  static constexpr int SMEM_BYTES = RING_BYTES > MERGE_BYTES ? RING_BYTES : MERGE_BYTES;
 };
 
 __device__ __forceinline__ void cp16_cg(uint32_t dst, const void* src) {
@@ -516,8 +511,8 @@ __global__ void __launch_bounds__(WARPS * 32)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kv,
                         const int32_t* __restrict__ table, int table_width, const int32_t* __restrict__ item_start,
                         const int32_t* __restrict__ kv_len, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
-                        float* __restrict__ part_ml, int* __restrict__ tickets, int hq, int hkv, int page_shift, int window,
-                        float scale, int chunk, int max_splits, int all_single) {
+                        float* __restrict__ part_ml, int hq, int hkv, int page_shift, int window, float scale, int chunk,
+                        int max_splits, int all_single) {
   using Shape = DecodeShape<D>;
   constexpr int STAGES = Shape::STAGES, PIECES = Shape::PIECES, KP = 2 * (D / 32);
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -689,52 +684,57 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
       if (d == 0) { part_ml[slot * 2] = m; part_ml[slot * 2 + 1] = l; }
     }
   }
-  if (max_splits == 1) return;
+}
 
-  // The CTA that finishes last among the key ranges of this (item, key/value head) combines them.  Every CTA
-  // publishes its partial results, then takes a ticket; the one drawing the last ticket sees all of them.
-  __shared__ int last_one;
-  __threadfence();
-  __syncthreads();
+// grid (hq, items), one warp: combines the key ranges of one (item, head).  Lanes first share out the ranges
+// (maximum and weights), then the head dims.
+template <int D>
+__global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                       const int32_t* __restrict__ item_start, const int32_t* __restrict__ kv_len,
+                                       __nv_bfloat16* __restrict__ out, int hq, int window, int chunk, int max_splits,
+                                       int all_single) {
+  __shared__ float weight[1024];
+  pdl_trigger();
+  const int item = blockIdx.y, head = blockIdx.x, lane = threadIdx.x;
+  int t0 = item;
+  bool mine = true;
+  if (!all_single) {
+    t0 = item_start[item];
+    mine = item_start[item + 1] - t0 == 1;
+  }
+  const int kvl = kv_len[item];
+  pdl_wait();
+  if (!mine) return;
+  const int p = kvl - 1;
+  const int lo_key = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
   const int splits = (kvl - (lo_key & ~15) + chunk - 1) / chunk;
-  if (threadIdx.x == 0) {
-    int* ticket = tickets + item * hkv + h;
-    const int drawn = atomicAdd(ticket, 1);
-    last_one = drawn == splits - 1;
-    if (last_one) *ticket = 0;  // left at zero for the next launch
+  const size_t base = ((size_t)item * hq + head) * max_splits;
+  float m = -INFINITY;
+  for (int s = lane; s < splits; s += 32) m = fmaxf(m, part_ml[(base + s) * 2]);
+  m = warp_max(m);
+  const float m_safe = m == -INFINITY ? 0.f : m;
+  float l = 0.f;
+  for (int s = lane; s < max_splits; s += 32) {
+    const float a = s < splits ? fast_exp2(part_ml[(base + s) * 2] - m_safe) : 0.f;
+    weight[s] = a;
+    if (s < splits) l += a * part_ml[(base + s) * 2 + 1];
   }
-  __syncthreads();
-  if (!last_one) return;
-  __threadfence();
-  float* w_sh = reinterpret_cast<float*>(smem_raw);  // [G][max_splits] weights, then [G] inverse sums
-  for (int row = warp; row < G; row += WARPS) {
-    const size_t base = ((size_t)item * hq + h * G + row) * max_splits;
-    float mx = -INFINITY;
-    for (int s2 = lane; s2 < splits; s2 += 32) mx = fmaxf(mx, __ldcg(part_ml + (base + s2) * 2));
-    mx = warp_max(mx);
-    const float m_safe = mx == -INFINITY ? 0.f : mx;
-    float lsum = 0.f;
-    for (int s2 = lane; s2 < splits; s2 += 32) {
-      const float a = fast_exp2(__ldcg(part_ml + (base + s2) * 2) - m_safe);
-      w_sh[row * max_splits + s2] = a;
-      lsum += a * __ldcg(part_ml + (base + s2) * 2 + 1);
-    }
-    lsum = warp_sum(lsum);
-    if (lane == 0) w_sh[G * max_splits + row] = 1.f / lsum;
-  }
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < G * D; idx += WARPS * 32) {
-    const int row = idx / D, d = idx - row * D;
-    const size_t base = ((size_t)item * hq + h * G + row) * max_splits;
+  l = warp_sum(l);
+  __syncwarp();
+  const float inv = 1.f / l;
+#pragma unroll
+  for (int i = 0; i < D / 32; ++i) {
+    const int d = lane + 32 * i;
     float o = 0.f;
+    // eight ranges per round, all loads issued before any is used; ranges past the item's own are skipped by weight
     for (int s0 = 0; s0 < splits; s0 += 8) {
       float v[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = s0 + j < splits ? __ldcg(part_o + (base + s0 + j) * D + d) : 0.f;
+      for (int j = 0; j < 8; ++j) v[j] = s0 + j < splits ? part_o[(base + s0 + j) * D + d] : 0.f;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) o = fmaf(s0 + j < splits ? w_sh[row * max_splits + s0 + j] : 0.f, v[j], o);
+      for (int j = 0; j < 8; ++j) o = fmaf(s0 + j < splits ? weight[s0 + j] : 0.f, v[j], o);
     }
-    out[((size_t)t0 * hq + h * G + row) * D + d] = __float2bfloat16_rn(o * w_sh[G * max_splits + row]);
+    out[((size_t)t0 * hq + head) * D + d] = __float2bfloat16_rn(o * inv);
   }
 }
 
@@ -780,11 +780,6 @@ PSB_API int psb_attention_prefill_bf16(const void* q, const void* kv, const void
   return 0;
 }
 
-// floats of scratch behind part_ml: sums and maxima of every (item, head, range), then the (item, kv head) counters
-PSB_API long long psb_attention_decode_ml_floats(int num_items, int hq, int hkv, int max_splits) {
-  return (long long)num_items * hq * max_splits * 2 + (long long)num_items * hkv;
-}
-
 // rows of (token, head-in-group) pairs one CTA of the prefill kernel owns, by head size
 PSB_API int psb_attention_prefill_rows_per_cta(int D) { return D == 64 ? WARPS * 16 * 2 : WARPS * 16; }
 
@@ -795,17 +790,14 @@ PSB_API int psb_attention_decode_bf16(const void* q, const void* kv, const void*
   if (int rc = check_common("attention_decode", hq, hkv, D, page_size, table_width, window)) return rc;
   if (hq / hkv > 16) PSB_REFUSE("attention_decode: groups of more than 16 query heads are not built");
   if (chunk < WARPS * 16 || chunk % (WARPS * 16)) PSB_REFUSE("attention_decode: key range %d is not a multiple of %d", chunk, WARPS * 16);
-  if (max_splits < 1 || max_splits > 256 || (max_splits > 1 && (!part_o || !part_ml)))
-    PSB_REFUSE("attention_decode: %d key ranges (at most 256), or their scratch is missing", max_splits);
+  if (max_splits < 1 || max_splits > 1024 || (max_splits > 1 && (!part_o || !part_ml)))
+    PSB_REFUSE("attention_decode: %d key ranges (at most 1024), or their scratch is missing", max_splits);
   if (page_size & (page_size - 1)) PSB_REFUSE("attention_decode: page size %d is not a power of two", page_size);
   if (num_items <= 0) return 0;
   if (num_items > 65535 || hkv > 65535) PSB_REFUSE("attention_decode: batch too large");
   int page_shift = 0;
   while ((1 << page_shift) < page_size) ++page_shift;
   dim3 grid(max_splits, hkv, num_items);
-  // one counter per (item, key/value head) sits behind the sums: part_ml holds num_items*hq*max_splits*2 floats, then
-  // num_items*hkv int32 that must be zero before the first launch and are left at zero by every launch
-  int* tickets = max_splits > 1 ? reinterpret_cast<int*>((float*)part_ml + (size_t)num_items * hq * max_splits * 2) : nullptr;
 #define PSB_DECODE(DD)                                                                                               \
   do {                                                                                                               \
     static bool configured = false; /* more than 48 KB of dynamic shared memory has to be asked for once */           \
@@ -817,8 +809,12 @@ PSB_API int psb_attention_decode_bf16(const void* q, const void* kv, const void*
     }                                                                                                                \
     psb_launch(attention_decode_kernel<DD>, grid, dim3(WARPS * 32), (size_t)DecodeShape<DD>::SMEM_BYTES, stream, \
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)kv, (const int32_t*)table, table_width, (const int32_t*)item_start, \
-        (const int32_t*)kv_len, (__nv_bfloat16*)out, (float*)part_o, (float*)part_ml, tickets, hq, hkv, page_shift, \
-        window, scale, chunk, max_splits, all_single);                                                               \
+        (const int32_t*)kv_len, (__nv_bfloat16*)out, (float*)part_o, (float*)part_ml, hq, hkv, page_shift, window, scale, \
+        chunk, max_splits, all_single);                                                                              \
+    if (max_splits > 1)                                                                                              \
+      psb_launch(attention_merge_kernel<DD>, dim3(hq, num_items), dim3(32), 0, stream, \
+          (const float*)part_o, (const float*)part_ml, (const int32_t*)item_start, (const int32_t*)kv_len,           \
+          (__nv_bfloat16*)out, hq, window, chunk, max_splits, all_single);                                           \
   } while (0)
   if (D == 64) PSB_DECODE(64); else PSB_DECODE(128);
 #undef PSB_DECODE
@@ -843,7 +839,7 @@ PSB_API int psb_attention_decode_bf16_static(const void* q, const void* kv, cons
                                              int max_splits, int all_single, cudaStream_t stream) {
   if (num_items < 0 || hq < 1 || D < 1 || max_splits < 1) PSB_REFUSE("attention_decode_static: bad sizes");
   const unsigned long long ranges = (unsigned long long)num_items * hq * max_splits;
-  const unsigned long long need = ranges * (unsigned long long)(D + 2) + (unsigned long long)num_items * hkv;
+  const unsigned long long need = ranges * (unsigned long long)(D + 2);
   if (need > PSB_STATIC_SCRATCH_FLOATS)
     PSB_REFUSE("attention_decode_static: %d items x %d heads x %d key ranges x (%d + 2) floats = %llu exceed the built-in "
                "scratch of %u floats; use fewer key ranges or the entry point that takes a scratch buffer",

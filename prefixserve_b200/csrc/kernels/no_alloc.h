@@ -15,16 +15,14 @@
 //
 //   * Size: PSB_STATIC_SCRATCH_FLOATS floats (4 MiB).  Every GPU that loads the library holds
 //     this much until the process exits.  A call that would need more, i.e.
-//     items * heads * max_splits * (head_dim + 2) + items * kv_heads > PSB_STATIC_SCRATCH_FLOATS, is
-//     refused with status 1 and a message in psb_last_error(); nothing is launched.
+//     items * heads * max_splits * (head_dim + 2) > PSB_STATIC_SCRATCH_FLOATS, is refused with
+//     status 1 and a message in psb_last_error(); nothing is launched.
 //   * The first call on each device looks up the array's device address (cudaGetSymbolAddress,
 //     with that device current).  Make that first call outside of any stream capture; later calls
 //     on the same device only launch kernels.
 //   * It calls no cudaMalloc, cudaFree or any allocating library routine.
-//   * All calls share the one array.  The partial results need no clearing: every range that the
-//     merge step reads was written by the same call just before.  The per-(item, kv head) counters
-//     that elect the merging block must be zero when a call starts; the array starts zeroed and
-//     every call puts its counters back to zero.  But two calls that overlap on
+//   * All calls share the one array.  Nothing in it has to start at zero: every range that the
+//     merge step reads was written by the same call just before.  But two calls that overlap on
 //     the GPU (different streams, or graphs replayed concurrently) overwrite each other's
 //     partial results: serialise them.
 //

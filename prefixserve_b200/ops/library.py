@@ -55,8 +55,6 @@ _SIGNATURES: dict[str, list] = {
     "psb_gemm_stream": [P, P, P, I, I, I, I, I, P],
     # (x, W, act, M, I, K, sms, stream)
     "psb_gemm_stream_gated": [P, P, P, I, I, I, I, P],
-    # (num_items, hq, hkv, max_splits) -> floats behind part_ml
-    "psb_attention_decode_ml_floats": [I, I, I, I],
     # (logits, temperature, seed, position, out, scratch, S, V, stream)
     "psb_sample": [P, P, P, P, P, P, I, I, P],
     # (S, V) -> bytes of scratch psb_sample wants
@@ -74,7 +72,6 @@ def lib() -> ctypes.CDLL:
             fn.argtypes = argtypes
             fn.restype = c_int
         handle.psb_sample_scratch_bytes.restype = ctypes.c_longlong
-        handle.psb_attention_decode_ml_floats.restype = ctypes.c_longlong
         handle.psb_last_error.restype = ctypes.c_char_p
         handle.psb_last_error.argtypes = []
         handle.psb_set_pdl.argtypes = [c_int]

@@ -100,12 +100,11 @@ def _sms(device: torch.device) -> int:
 
 
 def _scratch_buffer(device: torch.device, name: str, numel: int) -> torch.Tensor:
-    """A float32 buffer that lives as long as the process and only ever grows (split-KV partial results).  It starts
-    zeroed: the counters that elect the merging block rely on that, and every launch leaves them at zero."""
+    """A float32 buffer that lives as long as the process and only ever grows (split-KV partial results)."""
     key = (device.index if device.index is not None else torch.cuda.current_device(), name)
     buf = _scratch.get(key)
     if buf is None or buf.numel() < numel:
-        buf = torch.zeros(max(numel, 1 << 16), dtype=torch.float32, device=device)
+        buf = torch.empty(max(numel, 1 << 16), dtype=torch.float32, device=device)
         _scratch[key] = buf
     return buf
 
@@ -141,13 +140,13 @@ def attention_bf16(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, item_
             return kvl - (lo // 16) * 16
         longest = max(span(kvl) for kvl in singles)
         want = max(1, (DECODE_CTAS_PER_SM * _sms(q.device)) // max(1, b * hkv))
-        splits = max(1, min(want, -(-longest // 64), 256))
+        splits = max(1, min(want, -(-longest // 64)))
         chunk = -(-(-(-longest // splits)) // 64) * 64
         max_splits = -(-longest // chunk)
         part_o = part_ml = None
         if max_splits > 1:
             part_o = _scratch_buffer(q.device, "attn_o", b * hq * max_splits * d)
-            part_ml = _scratch_buffer(q.device, "attn_ml", lib().psb_attention_decode_ml_floats(b, hq, hkv, max_splits))
+            part_ml = _scratch_buffer(q.device, "attn_ml", b * hq * max_splits * 2)
         check(lib().psb_attention_decode_bf16(
             q.data_ptr(), kv.data_ptr(), table.data_ptr(), table.shape[1], item_start.data_ptr(), kv_len.data_ptr(),
             out.data_ptr(), part_o.data_ptr() if part_o is not None else None,

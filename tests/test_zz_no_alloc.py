@@ -60,7 +60,7 @@ def _run(lib, pr, chunk, static):
     else:
         n = pr["b"] * pr["hq"] * max_splits
         part_o = torch.empty(n * pr["d"], dtype=torch.float32, device=DEV)
-        part_ml = torch.zeros(n * 2 + pr["b"] * pr["hkv"], dtype=torch.float32, device=DEV)  # sums, then zeroed counters
+        part_ml = torch.empty(n * 2, dtype=torch.float32, device=DEV)
         rc = lib.psb_attention_decode_bf16(*head, part_o.data_ptr(), part_ml.data_ptr(), *common_tail)
     assert rc == 0, lib.psb_last_error().decode()
     torch.cuda.synchronize()
