@@ -17,7 +17,7 @@ STREAM_MIN_TILES = 0     # ... for matrices with at least this many 16-row tiles
 SMALL_M = 8         # rows up to which the one-tile-per-CTA kernel is used when the streaming kernel is not
 SMALL_M_GATED = 8   # same for the gate/up product with the fused activation
 WIDE_BELOW_TILES = 600   # matrices with fewer 16-row tiles than this get 16 warps per CTA instead of 8
-DECODE_CTAS_PER_SM = 8   # split-KV: key ranges are sized so that about this many CTAs per SM exist
+DECODE_CTAS_PER_SM = 4   # split-KV: key ranges are sized so that about this many CTAs per SM exist
 _OUT_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
 

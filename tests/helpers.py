@@ -26,7 +26,14 @@ TINY_C = dict(
                     rope_scaling=Llama3RopeScaling(8.0, 1.0, 2.0, 16), max_position_embeddings=300,
                     tie_word_embeddings=False),
     seed=2, std=0.2, gain_noise=0.2)
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# head size 64: the size at which the bfloat16 path runs the tensor-core attention kernels
+TINY_D = dict(
+    cfg=LlamaConfig(vocab_size=300, hidden_size=128, intermediate_size=160, num_layers=2, num_heads=4, num_kv_heads=2,
+                    head_dim=64, rms_norm_eps=1e-5, rope_theta=50000.0,
+                    rope_scaling=Llama3RopeScaling(2.0, 1.0, 4.0, 32), max_position_embeddings=1024,
+                    tie_word_embeddings=True),
+    seed=3, std=0.08, gain_noise=0.1)
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
 
 
 def make_folder(tmp, which: str, dtype=torch.float32):

@@ -16,7 +16,7 @@ import plain_model
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parents[1]
 
-LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 16, 40, 70, 131], "C": [3, 48, 97]}
+LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 16, 40, 70, 131], "C": [3, 48, 97], "D": [2, 64, 129, 300]}
 TRACES = {
     "whole": helpers.trace_whole,
     "tail_decode": helpers.trace_tail_decode,
@@ -58,7 +58,7 @@ def replay(folder, dtype, steps, max_tokens=None):
     return helpers.collect(steps, outputs)
 
 
-@pytest.mark.parametrize("which", ["A", "B", "C"])
+@pytest.mark.parametrize("which", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("kind", list(TRACES))
 def test_float32_matches_plain(folders, truth, which, kind):
     seqs = sequences(which)
@@ -72,7 +72,7 @@ def test_float32_matches_plain(folders, truth, which, kind):
         assert err <= tol, f"{which}/{kind}: request {rid} position {pos}: |diff| {err:.3e} > {tol:.3e}"
 
 
-@pytest.mark.parametrize("which", ["A", "B", "C"])
+@pytest.mark.parametrize("which", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("kind", list(TRACES))
 def test_bfloat16_close_to_float32_truth(folders, truth, which, kind):
     """bfloat16 engine vs float32 truth, judged against a plain bfloat16 run of the same weights."""
@@ -156,9 +156,9 @@ def test_injected_faults_are_noticed(folders, truth, dtype, bug):
     """The comparison used above must fail when the step function is given relative positions or a short key count
     (the faults PrefixServe injects in tests/test_llama_exact.py:227-241 to prove its own suite)."""
     from prefixserve_b200.engine.replay import Replayer
-    seqs = {"r0": sequences("C")["r2"]}
+    seqs = {"r0": sequences("D")["r2"]}
     steps = helpers.trace_portions(seqs)
-    rp = Replayer(folders["C"], dtype, helpers.peak_tokens(steps))
+    rp = Replayer(folders["D"], dtype, helpers.peak_tokens(steps))
     rp.runner.inject_bug = bug
     outputs = {}
     for st in steps:
@@ -166,6 +166,13 @@ def test_injected_faults_are_noticed(folders, truth, dtype, bug):
         if out is not None:
             outputs[st["step"]] = torch.from_numpy(out.copy())
     rows = helpers.collect(steps, outputs)
-    want = truth["C"]["r0"]
+    want = truth["D"]["r2"]  # the sequence replayed here under the name r0
     got = torch.stack([rows[("r0", p)] for p in range(len(seqs["r0"]))])
-    assert helpers.rel_err(got[20:], want[20:]) > 0.15, "the injected fault went unnoticed"
+    # the acceptance rule of the tests above must reject this run
+    ours = helpers.rel_err(got[20:], want[20:])
+    if dtype == "float32":
+        assert float((got - want).abs().max()) > 1e-2 * float(want.abs().max()), "the injected fault went unnoticed"
+    else:
+        cfg, tensors = plain_model.read_folder(folders["D"])
+        theirs = helpers.rel_err(plain_model.forward(cfg, tensors, seqs["r0"], dtype=torch.bfloat16)[20:], want[20:])
+        assert ours > 1.5 * theirs + 1e-3, f"the injected fault went unnoticed ({ours:.4f} vs plain bf16 {theirs:.4f})"
