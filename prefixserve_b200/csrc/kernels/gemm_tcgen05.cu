@@ -1,0 +1,384 @@
+// C[M,N] = A[M,K] * W[N,K]^T in bfloat16 on the 5th-generation tensor cores, for many rows (prefill).
+//
+// Persistent, warp-specialised CTAs (one per SM), 192 threads:
+//   warp 0      producer: one lane issues TMA loads (cp.async.bulk.tensor.2d) of a 128x64 tile of A and two 128x64
+//               tiles of W per stage into 128-byte-swizzled shared memory; completion by mbarrier transaction bytes;
+//   warp 1      MMA: one lane issues tcgen05.mma (cta_group::1, kind::f16, M=128, N=256, K=16; four per stage) with
+//               shared-memory matrix descriptors; accumulators are float32 in tensor memory (two buffers of 256
+//               columns, so the epilogue of one tile overlaps the main loop of the next); tcgen05.commit hands stages
+//               back to the producer and finished accumulators to the epilogue;
+//   warps 2..5  epilogue: tcgen05.ld (32 lanes x 32 columns per instruction) -> registers -> bfloat16 -> global.
+// The two W tiles of a stage are rows [n0, n0+128) and [n1, n1+128): for a plain product n1 = n0 + 128; for the
+// gated feed-forward n0 indexes the gate rows and n1 the matching up rows, and the epilogue writes
+// silu(gate) * up, so the [T, 2I] intermediate never exists (prefixserve/model/llama.py:120-121 of PrefixServe;
+// F.linear at :113, :117).
+//
+// Rows of A past M, rows of W past N and columns past K are filled with zeros by the TMA unit (K only needs to be a
+// multiple of 8: a 16-byte row pitch).  No cluster, no multicast: every CTA loads its own tiles.
+//
+// Every wait on an mbarrier is bounded.  If one runs out, the CTA raises a flag that all its warps poll, stops
+// issuing work, pauses long enough for copies in flight to land, frees its tensor memory and returns; the host finds
+// a non-zero status word (psb_tcgen05_status) and raises.  That path has never been taken in testing; it exists so
+// that a defect cannot hang the GPU.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128, BN_HALF = 128, BN = 2 * BN_HALF, BK = 64;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;        // 16 KB
+constexpr int B_BYTES = BN * BK * 2;        // 32 KB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int THREADS = 192;
+constexpr int TMEM_COLS = 512;              // two accumulator buffers of BN float32 columns
+constexpr uint32_t SPIN_LIMIT = 1u << 22;
+
+// shared memory: [stages][A | B] (1024-byte aligned), then barriers and the tensor-memory address
+struct Barriers {
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  uint32_t abort;
+};
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + (int)sizeof(Barriers);
+
+__device__ int g_tcgen05_status = 0;  // 0 ok; otherwise which wait gave up (1 producer, 2 mma, 3 epilogue, 4 mma/acc)
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+// Bounded: false when the barrier did not complete within SPIN_LIMIT polls or another warp has raised the abort flag.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort, int who) {
+  for (uint32_t spin = 0; spin < SPIN_LIMIT; ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort) return false;
+  }
+  *abort = 1;
+  atomicCAS(&g_tcgen05_status, 0, who);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+
+// K-major operand tile with 128-byte swizzle: rows of 128 bytes, 8 rows (1024 bytes) per swizzle atom.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3fff);        // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                       // leading byte offset: unused with swizzled K-major tiles
+  d |= (uint64_t)(1024 >> 4) << 32;             // stride byte offset: 8 rows of 128 bytes
+  d |= (uint64_t)1 << 46;                       // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;                       // 128-byte swizzle
+  return d;
+}
+// kind::f16: bfloat16 A and B, float32 accumulate, both K-major, M=128, N=256
+constexpr uint32_t INSTR_DESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+__device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(INSTR_DESC), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// gated: 0 plain (C[M, N], tile columns [n0, n0+128) and [n0+128, n0+256)); 1 gated (C[M, I], W = [gate; up], tile
+// columns [n0, n0+128) of the gate and the same of the up rows).
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                    __nv_bfloat16* __restrict__ C, int M, int N_out, int K, int ldc, int up_offset, int gated) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  Barriers* bars = reinterpret_cast<Barriers*>(tiles + STAGES * STAGE_BYTES);
+  volatile uint32_t* abort = &bars->abort;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const int n_span = gated ? BN_HALF : BN;  // output columns one tile covers
+  const int m_blocks = (M + BM - 1) / BM;
+  const int n_blocks = (N_out + n_span - 1) / n_span;
+  const int tiles_total = m_blocks * n_blocks;
+  const int k_blocks = (K + BK - 1) / BK;
+
+  pdl_trigger();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars->acc_full[b], 1);
+      mbar_init(&bars->acc_empty[b], 4);  // one arrival per epilogue warp
+    }
+    bars->abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {  // one warp allocates (and later frees) the tensor memory
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+  pdl_wait();  // A is the preceding kernel's output
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < tiles_total; tile += gridDim.x) {
+        const int m0 = (tile % m_blocks) * BM;
+        const int n0 = (tile / m_blocks) * n_span;
+        const int n1 = gated ? up_offset + n0 : n0 + BN_HALF;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          ok = mbar_wait(&bars->empty[stage], phase ^ 1, abort, 1);
+          if (!ok) break;
+          unsigned char* a_dst = tiles + stage * STAGE_BYTES;
+          unsigned char* b_dst = a_dst + A_BYTES;
+          mbar_expect_tx(&bars->full[stage], STAGE_BYTES);
+          tma_load_2d(a_dst, &map_a, kb * BK, m0, &bars->full[stage]);
+          tma_load_2d(b_dst, &map_w, kb * BK, n0, &bars->full[stage]);
+          tma_load_2d(b_dst + BN_HALF * BK * 2, &map_w, kb * BK, n1, &bars->full[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ----------------------------------------------------------------------- MMA
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0, local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < tiles_total; tile += gridDim.x, ++local) {
+        const uint32_t buf = local & 1, use = local >> 1;  // accumulator buffer and how often it has been used
+        ok = mbar_wait(&bars->acc_empty[buf], (use & 1) ^ 1, abort, 4);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t acc = tmem_base + buf * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          ok = mbar_wait(&bars->full[stage], phase, abort, 2);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(tiles + stage * STAGE_BYTES);
+          const uint32_t b_addr = a_addr + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            // 16 elements = 32 bytes further along K inside the swizzled 128-byte rows
+            mma_f16(acc, smem_desc(a_addr + k * 32), smem_desc(b_addr + k * 32), (kb | k) != 0);
+          }
+          mma_commit(&bars->empty[stage]);  // arrives when the MMAs that read this stage are done
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) mma_commit(&bars->acc_full[buf]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;  // a warp may only read tensor-memory lanes [32*(warp%4), +32)
+    uint32_t local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < tiles_total; tile += gridDim.x, ++local) {
+      const uint32_t buf = local & 1, use = local >> 1;
+      const int m0 = (tile % m_blocks) * BM;
+      const int n0 = (tile / m_blocks) * n_span;
+      ok = mbar_wait(&bars->acc_full[buf], use & 1, abort, 3);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
+      __nv_bfloat16* crow = C + (size_t)row * ldc;
+      if (gated) {
+#pragma unroll 1
+        for (int c = 0; c < BN_HALF; c += 32) {
+          uint32_t g[32], u[32];
+          tmem_ld32(taddr + c, g);
+          tmem_ld32(taddr + BN_HALF + c, u);
+          tmem_ld_wait();
+          if (row < M) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              const int col = n0 + c + j;
+              uint32_t packed[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                // the reference rounds both projections to bfloat16 before the activation
+                const float g0 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(g[j + 2 * q])));
+                const float g1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(g[j + 2 * q + 1])));
+                const float u0 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[j + 2 * q])));
+                const float u1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[j + 2 * q + 1])));
+                packed[q] = pack2(g0 / (1.f + __expf(-g0)) * u0, g1 / (1.f + __expf(-g1)) * u1);
+              }
+              if (col + 8 <= N_out && (ldc & 7) == 0) {
+                *reinterpret_cast<uint4*>(crow + col) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+              } else {
+                const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(packed);
+                for (int q = 0; q < 8; ++q)
+                  if (col + q < N_out) crow[col + q] = e[q];
+              }
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(taddr + c, v);
+          tmem_ld_wait();
+          if (row < M) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              const int col = n0 + c + j;
+              uint32_t packed[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) packed[q] = pack2(__uint_as_float(v[j + 2 * q]), __uint_as_float(v[j + 2 * q + 1]));
+              if (col + 8 <= N_out && (ldc & 7) == 0) {
+                *reinterpret_cast<uint4*>(crow + col) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+              } else {
+                const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(packed);
+                for (int q = 0; q < 8; ++q)
+                  if (col + q < N_out) crow[col + q] = e[q];
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->acc_empty[buf]);  // this warp has read its part of the buffer
+    }
+  }
+
+  if (*abort) {
+    // something gave up: give copies in flight time to land before the shared memory is handed to another CTA
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ---- host side -----------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// row-major [rows, K] bfloat16 matrix, box of 64 columns x box_rows rows, 128-byte swizzle, zero fill outside
+int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn) PSB_REFUSE("gemm_tcgen05: the driver does not export cuTensorMapEncodeTiled");
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) PSB_REFUSE("gemm_tcgen05: cuTensorMapEncodeTiled failed with code %d (rows=%d K=%d)", (int)r, rows, K);
+  return 0;
+}
+
+int launch(const void* a, const void* w, void* c, int M, int w_rows, int N_out, int K, int up_offset, int gated, int sms,
+           cudaStream_t stream) {
+  if (M < 1 || N_out < 1 || K < 8 || K % 8) PSB_REFUSE("gemm_tcgen05: needs K a multiple of 8 (M=%d N=%d K=%d)", M, N_out, K);
+  if (((uintptr_t)a | (uintptr_t)w | (uintptr_t)c) & 15) PSB_REFUSE("gemm_tcgen05: operands must be 16-byte aligned");
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) PSB_REFUSE("gemm_tcgen05: cannot reserve %d bytes of shared memory: %s", SMEM_BYTES, cudaGetErrorString(e));
+    configured = true;
+  }
+  CUtensorMap map_a, map_w;
+  if (int rc = make_map(&map_a, a, M, K, BM)) return rc;
+  if (int rc = make_map(&map_w, w, w_rows, K, BN_HALF)) return rc;
+  const int n_span = gated ? BN_HALF : BN;
+  const int tiles = ((M + BM - 1) / BM) * ((N_out + n_span - 1) / n_span);
+  const int grid = tiles < sms ? tiles : sms;
+  psb_launch(gemm_tcgen05_kernel, dim3(grid), dim3(THREADS), (size_t)SMEM_BYTES, stream, map_a, map_w, (__nv_bfloat16*)c, M,
+             N_out, K, N_out, up_offset, gated);
+  PSB_LAUNCH_CHECK("gemm_tcgen05");
+  return 0;
+}
+
+}  // namespace
+
+// C[M,N] = A[M,K] W[N,K]^T, all bfloat16 row-major, K % 8 == 0.  sms: CTAs to launch at most (the SM count).
+PSB_API int psb_gemm_tcgen05(const void* a, const void* w, void* c, int M, int N, int K, int sms, cudaStream_t stream) {
+  return launch(a, w, c, M, N, N, K, 0, 0, sms, stream);
+}
+
+// act[M,I] = silu(A Wg^T) * (A Wu^T) for W = [Wg; Wu] of shape [2I, K].
+PSB_API int psb_gemm_tcgen05_gated(const void* a, const void* w, void* act, int M, int I, int K, int sms, cudaStream_t stream) {
+  return launch(a, w, act, M, 2 * I, I, K, I, 1, sms, stream);
+}
+
+// 0 while no bounded wait has ever run out on the current device; reading it synchronises with the device.
+PSB_API int psb_tcgen05_status() {
+  int v = -1;
+  if (cudaMemcpyFromSymbol(&v, g_tcgen05_status, sizeof(int)) != cudaSuccess) return -1;
+  return v;
+}

@@ -55,6 +55,12 @@ _SIGNATURES: dict[str, list] = {
     "psb_gemm_stream": [P, P, P, I, I, I, I, I, P],
     # (x, W, act, M, I, K, sms, stream)
     "psb_gemm_stream_gated": [P, P, P, I, I, I, I, P],
+    # (a, w, c, M, N, K, sms, stream)
+    "psb_gemm_tcgen05": [P, P, P, I, I, I, I, P],
+    # (a, w, act, M, I, K, sms, stream)
+    "psb_gemm_tcgen05_gated": [P, P, P, I, I, I, I, P],
+    # () -> 0 while no bounded wait of the tcgen05 kernel has ever run out
+    "psb_tcgen05_status": [],
     # (logits, temperature, seed, position, out, scratch, S, V, stream)
     "psb_sample": [P, P, P, P, P, P, I, I, P],
     # (S, V) -> bytes of scratch psb_sample wants
@@ -92,6 +98,11 @@ def set_pdl(on: bool) -> None:
 
 def pdl_enabled() -> bool:
     return bool(lib().psb_get_pdl())
+
+
+def tcgen05_status() -> int:
+    """0 unless a bounded wait inside the tcgen05 product ever gave up (then its results are void). Synchronises."""
+    return int(lib().psb_tcgen05_status())
 
 
 def declare(name: str, argtypes: list) -> None:

@@ -16,6 +16,7 @@ STREAM_MIN_TILES = 0     # ... for matrices with at least this many 16-row tiles
                          # launch) cannot pile up on the SMs that free up first, which the one-tile-per-CTA kernel does.
 SMALL_M = 8         # rows up to which the one-tile-per-CTA kernel is used when the streaming kernel is not
 SMALL_M_GATED = 8   # same for the gate/up product with the fused activation
+USE_TCGEN05 = True  # products with more rows than STREAM_M: this library's tcgen05/TMEM/TMA kernel (else cuBLAS)
 WIDE_BELOW_TILES = 600   # matrices with fewer 16-row tiles than this get 16 warps per CTA instead of 8
 DECODE_CTAS_PER_SM = 4   # split-KV: key ranges are sized so that about this many CTAs per SM exist
 _OUT_CODE = {torch.float32: 0, torch.bfloat16: 1}
@@ -56,6 +57,31 @@ def gemm_stream_gated(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     return act
 
 
+def _tcgen05_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (USE_TCGEN05 and x.shape[1] % 8 == 0 and x.shape[1] >= 8 and x.is_contiguous() and w.is_contiguous()
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """x[M,K] @ w[N,K]^T -> bfloat16, on tcgen05 tensor cores with TMEM accumulators, operands fed by TMA."""
+    m, k = x.shape
+    n = w.shape[0]
+    y = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+    check(lib().psb_gemm_tcgen05(x.data_ptr(), w.data_ptr(), y.data_ptr(), m, n, k, _sms(x.device),
+                                 torch.cuda.current_stream().cuda_stream), "gemm_tcgen05")
+    return y
+
+
+def gemm_tcgen05_gated(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(x Wg^T) * (x Wu^T) -> bfloat16 [M, I], the activation applied in the product's epilogue."""
+    m, k = x.shape
+    inter = w_gate_up.shape[0] // 2
+    act = torch.empty((m, inter), dtype=torch.bfloat16, device=x.device)
+    check(lib().psb_gemm_tcgen05_gated(x.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(), m, inter, k, _sms(x.device),
+                                       torch.cuda.current_stream().cuda_stream), "gemm_tcgen05_gated")
+    return act
+
+
 def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     """x[M,K] @ w[N,K]^T for bfloat16 operands, float32 accumulation.
 
@@ -68,6 +94,8 @@ def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> tor
             return gemm_stream(x, w, out_dtype)
         if small_m_ok(m, k, SMALL_M):
             return gemm_small_m(x, w, out_dtype)
+        if out_dtype == torch.bfloat16 and m > 0 and _tcgen05_ok(x, w):
+            return gemm_tcgen05(x, w)
     y = torch.nn.functional.linear(x, w)
     return y if out_dtype == y.dtype else y.to(out_dtype)
 
@@ -78,6 +106,8 @@ def gated_linear_bf16(x: torch.Tensor, w_gate_up: torch.Tensor, limit: int | Non
     if (limit is None and small_m_ok(m, k, min(STREAM_M, 16)) and w_gate_up.shape[0] % 2 == 0 and x.is_contiguous()
             and w_gate_up.is_contiguous()):
         return gemm_stream_gated(x, w_gate_up)
+    if limit is None and m > max(STREAM_M, SMALL_M_GATED) and w_gate_up.shape[0] % 2 == 0 and _tcgen05_ok(x, w_gate_up):
+        return gemm_tcgen05_gated(x, w_gate_up)
     if not (small_m_ok(m, k, SMALL_M_GATED if limit is None else limit) and w_gate_up.shape[0] % 2 == 0 and x.is_contiguous() and w_gate_up.is_contiguous()):
         return None
     inter = w_gate_up.shape[0] // 2

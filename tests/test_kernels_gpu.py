@@ -464,3 +464,37 @@ def test_gemm_stream_gated(m, inter, k):
     y = x.double() @ w.double().t()
     want = torch.nn.functional.silu(y[:, :inter]) * y[:, inter:]
     assert torch.allclose(got.double(), want, rtol=3e-2, atol=3e-2)
+
+
+# ---- the tcgen05 / TMEM / TMA product for many rows -----------------------------------------------------------------
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (17, 40, 8), (130, 333, 264), (2048, 3072, 2048), (300, 2048, 8192),
+                                   (1000, 1000, 1000), (129, 128256 // 16, 96)])
+def test_gemm_tcgen05(m, n, k):
+    from prefixserve_b200.ops import library
+    from prefixserve_b200.ops.tensorcore import gemm_tcgen05
+    x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = torch.randn(n, k, device=DEV).to(torch.bfloat16)
+    got = gemm_tcgen05(x, w)
+    assert library.tcgen05_status() == 0, "a bounded wait in the kernel gave up"
+    want = x.double() @ w.double().t()
+    assert got.shape == (m, n) and got.dtype == torch.bfloat16
+    assert torch.allclose(got.double(), want, rtol=1e-2, atol=1e-2 * math.sqrt(k)), float((got.double() - want).abs().max())
+    # the same rows inside another batch give the same bits (tile-local sums, fixed k order)
+    if m >= 130:
+        part = gemm_tcgen05(x[:129].contiguous(), w)
+        assert torch.equal(part, got[:129])
+
+
+@pytest.mark.parametrize("m,inter,k", [(128, 128, 64), (50, 40, 24), (257, 333, 264), (2048, 8192, 2048)])
+def test_gemm_tcgen05_gated(m, inter, k):
+    from prefixserve_b200.ops import library
+    from prefixserve_b200.ops.tensorcore import gemm_tcgen05_gated
+    x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(2 * inter, k, device=DEV) / math.sqrt(k)).to(torch.bfloat16)
+    got = gemm_tcgen05_gated(x, w)
+    assert library.tcgen05_status() == 0
+    y = (x.double() @ w.double().t()).to(torch.bfloat16).double()  # the reference rounds the projections first
+    want = torch.nn.functional.silu(y[:, :inter]) * y[:, inter:]
+    assert got.shape == (m, inter)
+    assert torch.allclose(got.double(), want, rtol=3e-2, atol=3e-2), float((got.double() - want).abs().max())
