@@ -239,6 +239,7 @@ def run_own(args) -> dict:
         achieved = step_bytes / (ms_step * 1e-3) / 1e9
 
         # ---- end to end through the scheduler and engine.step (host tokens in and out)
+        engine.capture_decode_graphs(range(1, args.batch + 1))  # as the entry point does at start-up
         sched = Scheduler(cache, chunk_size=PREFILL_TOKENS, stop_token_ids=())
         total = args.steps + args.warmup
         for r in range(args.batch):

@@ -101,6 +101,30 @@ class Engine:
             self.last_logits = {w.req.req_id: logits[i].cpu() for i, w in enumerate(sampling)}
         return {w.req.req_id: tok for w, tok in zip(sampling, tokens.tolist())}  # the step's one device-to-host read
 
+    def capture_decode_graphs(self, batch_sizes) -> int:
+        """Captures the pure-decode step for the given batch sizes now, so that no request pays for a capture
+        (a few milliseconds each) in the middle of serving.  Needs the cache to have that many free slots and pages.
+        Returns how many graphs were captured."""
+        if not self.runner.use_graphs:
+            return 0
+        done = 0
+        for b in sorted(set(int(x) for x in batch_sizes)):
+            if b < 1 or b > self.cfg.max_num_seqs or b in self.runner._graphs:
+                continue
+            if self.cache.slots.num_free < b or self.cache.free_pages(0) < b:
+                break
+            slots = []
+            for _ in range(b):
+                slot = self.cache.open()
+                self.cache.reserve(slot, 1)
+                slots.append(slot)
+            self.runner.step([StepItem(s, 0, np.zeros(1, dtype=np.int32), (0,)) for s in slots])  # runs, then captures
+            for s in slots:
+                self.cache.close(s)
+            done += 1
+        torch.cuda.synchronize()
+        return done
+
     # ---- pool sizing ----------------------------------------------------------
     def _size_pool(self) -> int:
         """Pages that fit beside the weights and the activations of a worst-case step."""

@@ -25,7 +25,7 @@ class LLM:
     def __init__(self, model: str | Path, *, dtype: str | torch.dtype = "bfloat16", max_seq_len: int = 8192,
                  num_blocks: int | None = None, max_running_requests: int = 64, chunked_prefill_size: int = 512,
                  enable_prefix_cache: bool = True, max_waiting: int = 1024, page_size: int = 16,
-                 device: str = "cuda") -> None:
+                 device: str = "cuda", warm_up: bool = True) -> None:
         self.engine = Engine(EngineConfig(
             model_path=Path(model), dtype=parse_dtype(dtype), device=device, max_num_seqs=max_running_requests,
             max_prefill_tokens=chunked_prefill_size, max_seq_len=max_seq_len, num_blocks=num_blocks,
@@ -35,6 +35,8 @@ class LLM:
         self.max_running_requests = max_running_requests
         self.chunked_prefill_size = chunked_prefill_size
         self._counter = 0
+        if warm_up:  # capture the decode step for every batch size up front instead of at its first use
+            self.engine.capture_decode_graphs(range(1, max_running_requests + 1))
 
     def generate(self, prompts: Sequence[Sequence[int]], sampling: SamplingParams | Sequence[SamplingParams] | None = None
                  ) -> list[list[int]]:
