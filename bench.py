@@ -180,8 +180,11 @@ def run_own(args) -> dict:
         vocab = MODEL["vocab_size"]
         max_b = max(args.batch, 64 if not args.skip_points else args.batch)
         pool = max_b * (CONTEXT // PAGE) + 64
+        if args.only != "all":
+            args.skip_points = True
         engine = Engine(EngineConfig(model_path=work, dtype=torch.bfloat16, max_num_seqs=max_b, max_prefill_tokens=PREFILL_TOKENS,
-                                     max_seq_len=CONTEXT, num_blocks=pool, page_size=PAGE, enable_prefix_cache=False))
+                                     max_seq_len=CONTEXT, num_blocks=pool, page_size=PAGE, enable_prefix_cache=False,
+                                     use_cuda_graphs=not args.no_graphs))
         runner, cache = engine.runner, engine.cache
         greedy = SamplingParams()
 
@@ -229,6 +232,15 @@ def run_own(args) -> dict:
                 cache.close(s)
             return t0.elapsed_time(t1) / steps, launched, ctx_sum / (batch * steps)
 
+        if args.only == "prefill":
+            torch.cuda.synchronize()
+            slot = cache.open()
+            cache.reserve(slot, PREFILL_TOKENS)
+            for _ in range(max(args.steps, 1)):
+                runner.step([StepItem(slot, 0, rng.randint(0, vocab, size=PREFILL_TOKENS).astype(np.int32), (PREFILL_TOKENS - 1,))])
+            torch.cuda.synchronize()
+            return {"only": "prefill", "steps": args.steps, "layers": layers}
+
         # ---- headline: decode at the default batch, device-timed, clocks sampled meanwhile
         with ClockSampler() as clocks:
             time.sleep(0.3)
@@ -237,6 +249,9 @@ def run_own(args) -> dict:
         value = args.batch / (ms_step * 1e-3)
         step_bytes = weight_bytes(layers) + args.batch * mean_ctx * kv_bytes_per_token(layers)
         achieved = step_bytes / (ms_step * 1e-3) / 1e9
+        if args.only == "decode":
+            return {"only": "decode", "value": round(value, 1), "ms_per_step": round(ms_step, 4), "layers": layers,
+                    "batch": args.batch, "gpu_launches": launches}
 
         # ---- end to end through the scheduler and engine.step (host tokens in and out)
         engine.capture_decode_graphs(range(1, args.batch + 1))  # as the entry point does at start-up
@@ -416,6 +431,9 @@ def main() -> int:
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the full model (recorded in config)")
     p.add_argument("--skip-points", action="store_true", help="leave out the batch-1 and batch-64 points")
+    p.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
+                   help="decode: only the device-timed decode steps; prefill: only the 2,048-token prefill (for profilers)")
+    p.add_argument("--no-graphs", action="store_true", help="run decode steps without CUDA graphs (kernel launch lists)")
     args = p.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:

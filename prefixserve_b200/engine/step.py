@@ -75,6 +75,7 @@ class ModelRunner:
         # graphs need every part to do the same device work for the same shapes, whatever the host-side item list says
         self.use_graphs = use_graphs and all(getattr(p, "graph_safe", False) for _, p in model.named_parts())
         self._graphs: dict[int, _DecodeGraph] = {}
+        self._graph_pool = None  # one memory pool for all captured steps: only one of them runs at a time
         self.graph_replays = 0
         # Test-only, after the reference's EngineConfig.inject_bug (prefixserve/llama_engine.py:62-63, :192, :202-203):
         # "rope_relative" numbers every portion's positions from 0; "kv_len_short" reports one key too few.
@@ -219,8 +220,10 @@ class ModelRunner:
             # Capture the same launches for later steps of this batch size.  Nothing runs during capture; the eager
             # run above has already sized every scratch buffer the kernels use.
             graph = torch.cuda.CUDAGraph()
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
             before = library.launches
-            with torch.cuda.graph(graph):
+            with torch.cuda.graph(graph, pool=self._graph_pool):
                 static_logits = self.model.forward(ctx, self.cache.view, rows)
             self._graphs[b] = _DecodeGraph(inputs=dev, logits=static_logits, graph=graph, kernels=library.launches - before)
             library.launches = before  # recorded, not run

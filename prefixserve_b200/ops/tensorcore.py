@@ -17,6 +17,8 @@ STREAM_MIN_TILES = 0     # ... for matrices with at least this many 16-row tiles
 SMALL_M = 8         # rows up to which the one-tile-per-CTA kernel is used when the streaming kernel is not
 SMALL_M_GATED = 8   # same for the gate/up product with the fused activation
 USE_TCGEN05 = True  # products with more rows than STREAM_M: this library's tcgen05/TMEM/TMA kernel (else cuBLAS)
+TCGEN05_MIN_TILES = 120  # ... when the product has at least this many 128x256 output tiles; smaller ones (a few
+                         # dozen rows against a narrow matrix) leave most SMs idle without split-K and go to cuBLAS
 WIDE_BELOW_TILES = 600   # matrices with fewer 16-row tiles than this get 16 warps per CTA instead of 8
 DECODE_CTAS_PER_SM = 4   # split-KV: key ranges are sized so that about this many CTAs per SM exist
 _OUT_CODE = {torch.float32: 0, torch.bfloat16: 1}
@@ -57,8 +59,10 @@ def gemm_stream_gated(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     return act
 
 
-def _tcgen05_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
-    return (USE_TCGEN05 and x.shape[1] % 8 == 0 and x.shape[1] >= 8 and x.is_contiguous() and w.is_contiguous()
+def _tcgen05_ok(x: torch.Tensor, w: torch.Tensor, n_span: int = 256) -> bool:
+    n_out = w.shape[0] if n_span == 256 else w.shape[0] // 2
+    tiles = -(-x.shape[0] // 128) * -(-n_out // n_span)
+    return (USE_TCGEN05 and tiles >= TCGEN05_MIN_TILES and x.shape[1] % 8 == 0 and x.shape[1] >= 8 and x.is_contiguous() and w.is_contiguous()
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
@@ -106,7 +110,7 @@ def gated_linear_bf16(x: torch.Tensor, w_gate_up: torch.Tensor, limit: int | Non
     if (limit is None and small_m_ok(m, k, min(STREAM_M, 16)) and w_gate_up.shape[0] % 2 == 0 and x.is_contiguous()
             and w_gate_up.is_contiguous()):
         return gemm_stream_gated(x, w_gate_up)
-    if limit is None and m > max(STREAM_M, SMALL_M_GATED) and w_gate_up.shape[0] % 2 == 0 and _tcgen05_ok(x, w_gate_up):
+    if limit is None and m > max(STREAM_M, SMALL_M_GATED) and w_gate_up.shape[0] % 2 == 0 and _tcgen05_ok(x, w_gate_up, 128):
         return gemm_tcgen05_gated(x, w_gate_up)
     if not (small_m_ok(m, k, SMALL_M_GATED if limit is None else limit) and w_gate_up.shape[0] % 2 == 0 and x.is_contiguous() and w_gate_up.is_contiguous()):
         return None
