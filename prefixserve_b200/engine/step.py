@@ -126,6 +126,9 @@ class ModelRunner:
         in the order of the items and of each item's ``want``."""
         if not items:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
+        held = self._graphs.get(len(items)) if self.use_graphs else None
+        if held is not None and all(len(it.tokens) == 1 and tuple(it.want) == (0,) for it in items):
+            return self._replay(items, held)
         self._check(items)
         lens = [len(it.tokens) for it in items]
         b, t = len(items), sum(lens)
@@ -176,16 +179,6 @@ class ModelRunner:
             at += b * w
 
         self.last_h2d_bytes = 4 * total
-        held = self._graphs.get(b) if static else None
-        if held is not None:
-            held.inputs.copy_(host[:total], non_blocking=True)
-            self._copied.record()
-            self._copy_pending = True
-            held.graph.replay()
-            library.launches += held.kernels  # this library's kernels inside the replayed graph
-            self.steps_run += 1
-            self.graph_replays += 1
-            return held.logits
         if static:
             dev = torch.empty(total, dtype=torch.int32, device=self.device)
             dev.copy_(host[:total], non_blocking=True)
@@ -228,6 +221,64 @@ class ModelRunner:
             self._graphs[b] = _DecodeGraph(inputs=dev, logits=static_logits, graph=graph, kernels=library.launches - before)
             library.launches = before  # recorded, not run
         return logits
+
+    def _replay(self, items: Sequence[StepItem], held: _DecodeGraph) -> torch.Tensor:
+        """A pure-decode step of a batch size that has been captured: the same checks and the same buffer layout as
+        the general path, written with array operations instead of per-item loops, then one copy and one replay."""
+        cache = self.cache
+        b = len(items)
+        slots = np.fromiter((it.slot for it in items), dtype=np.int32, count=b)
+        starts = np.fromiter((it.start for it in items), dtype=np.int64, count=b)
+        toks = np.fromiter((it.tokens[0] for it in items), dtype=np.int64, count=b)
+        if len(set(slots.tolist())) != b:
+            raise EngineError("a slot appears twice in one step")
+        if slots.min() < 0 or slots.max() >= cache.num_slots or not all(cache.slots.taken(int(s)) for s in slots):
+            raise EngineError("a slot of the step is not open")
+        if not np.array_equal(starts, cache._position[slots]):
+            raise EngineError("tokens do not start where the cache ends for some slot of the step")
+        if starts.max() + 1 > cache.max_seq_len:
+            raise EngineError(f"a position exceeds max_seq_len {cache.max_seq_len}")
+        if toks.min() < 0 or toks.max() >= self.vocab_size:
+            raise EngineError(f"token id outside [0, {self.vocab_size})")
+        page = cache.page_size
+        need = (starts + page) // page  # pages that must be held to cover position `start`
+        width = cache.max_pages_per_seq
+        t = s = b
+        o_ids, o_pos, o_item, o_start = 0, t, 2 * t, 3 * t
+        o_kvlen = o_start + b + 1
+        o_slot = o_kvlen + b
+        o_rows = o_slot + b
+        o_tab = o_rows + s
+        total = o_tab + len(cache.groups) * b * width
+        host = self._staging(total)
+        buf = host.numpy()
+        cols = np.arange(width)[None, :]
+        at = o_tab
+        for gi, g in enumerate(cache.groups):
+            table = buf[at: at + b * width].reshape(b, width)
+            g.tables.gather(slots, width, table)
+            first = 0 if g.window is None else np.maximum(0, starts - g.window + 1)[:, None] // page
+            live = (cols >= first) & (cols < need[:, None])
+            if (live & ((table < 0) | (table >= g.pool.num_blocks))).any():
+                raise EngineError(f"a page table of group {gi} lacks a page or names one outside the pool")
+            at += b * width
+        ramp = np.arange(b + 1, dtype=np.int32)
+        buf[o_ids: o_ids + b] = toks
+        buf[o_pos: o_pos + b] = 0 if self.inject_bug == "rope_relative" else starts
+        buf[o_item: o_item + b] = ramp[:b]
+        buf[o_start: o_start + b + 1] = ramp
+        buf[o_kvlen: o_kvlen + b] = starts + 1 - (1 if self.inject_bug == "kv_len_short" else 0) * (starts > 0)
+        buf[o_slot: o_slot + b] = slots
+        buf[o_rows: o_rows + b] = ramp[:b]
+        self.last_h2d_bytes = 4 * total
+        held.inputs.copy_(host[:total], non_blocking=True)
+        self._copied.record()
+        self._copy_pending = True
+        held.graph.replay()
+        library.launches += held.kernels  # this library's kernels inside the replayed graph
+        self.steps_run += 1
+        self.graph_replays += 1
+        return held.logits
 
     def _staging(self, words: int) -> torch.Tensor:
         # the previous step's copy must have left the buffer before it is overwritten

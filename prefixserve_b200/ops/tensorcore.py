@@ -174,7 +174,7 @@ def attention_bf16(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, item_
             return kvl - (lo // 16) * 16
         longest = max(span(kvl) for kvl in singles)
         want = max(1, (DECODE_CTAS_PER_SM * _sms(q.device)) // max(1, b * hkv))
-        splits = max(1, min(want, -(-longest // 64)))
+        splits = max(1, min(want, -(-longest // 128)))  # ranges shorter than 128 keys cost more to merge than they save
         chunk = -(-(-(-longest // splits)) // 64) * 64
         max_splits = -(-longest // chunk)
         part_o = part_ml = None
