@@ -424,3 +424,294 @@ PSB_API int psb_gemm_stream_gated(const void* x, const void* W, void* act, int M
   PSB_LAUNCH_CHECK("gemm_stream_gated");
   return 0;
 }
+
+// ------------------------------------------------------------------------------------------------------------------
+// The streaming product with the preceding residual add + RMSNorm folded in (decode):
+//   v = h[rows[m]] + pending[rows[m]]        (float32; written to h_out by CTA 0 when pending is given and rows is not)
+//   y[m, n] = rsqrt(mean(v^2) + eps) * sum_k W[n, k] * bf16(v[k] * gain[k])
+// A warp's share of K is the same for every row tile it visits, so it computes its bfloat16 operand fragments of
+// v * gain once, keeps them in registers, and the ring in shared memory carries weights only.  Each warp also adds up
+// the squares of its share of v; the 16 partial sums per row meet in shared memory at the first tile's barrier and
+// the scale is applied to the finished sums.  (RMSNorm: prefixserve/model/llama.py:63-69 of PrefixServe; the
+// reference rounds the normalised row to bfloat16 and multiplies by the gain, this rounds v * gain and scales after
+// the product: the same number of roundings.)
+namespace {
+
+template <int MT, int TILES>
+struct NormStreamShape {
+  static constexpr int PIECES = 2 * TILES;
+  static constexpr int STAGES = TILES == 1 ? 8 : (MT == 1 ? 5 : 4);
+  static constexpr int RING_BYTES = SW * STAGES * PIECES * 32 * 16;
+  static constexpr int PART_BYTES = 2 * SW * TILES * 16 * (8 * MT + 1) * 4;
+  static constexpr int SSQ_BYTES = SW * 8 * MT * 4;
+  static constexpr int SMEM_BYTES = RING_BYTES + PART_BYTES + SSQ_BYTES;
+  static_assert(SMEM_BYTES <= 227 * 1024, "beyond a CTA's shared memory");
+};
+
+template <typename TP>
+__device__ __forceinline__ void load8_any(const TP* p, float (&o)[8]);
+template <>
+__device__ __forceinline__ void load8_any<float>(const float* p, float (&o)[8]) {
+  const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p + 4));
+  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8_any<__nv_bfloat16>(const __nv_bfloat16* p, float (&o)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 f = __bfloat1622float2(h2[k]);
+    o[2 * k] = f.x; o[2 * k + 1] = f.y;
+  }
+}
+
+// CPW: most k chunks (of 32) a warp may own (K <= 512 * CPW).
+template <int MT, int TILES, int CPW, typename TOut>
+__global__ void __launch_bounds__(SW * 32, 1)
+gemm_stream_norm_kernel(const float* __restrict__ h_in, const __nv_bfloat16* __restrict__ pending, const float* __restrict__ gain,
+                        const int32_t* __restrict__ rows, float* __restrict__ h_out, const __nv_bfloat16* __restrict__ W,
+                        TOut* __restrict__ y, int M, int N, int K, int ldy, int up_offset, float eps) {
+  using Shape = NormStreamShape<MT, TILES>;
+  constexpr int STAGES = Shape::STAGES, PIECES = Shape::PIECES;
+  constexpr uint32_t STAGE_BYTES = PIECES * 32 * 16;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const uint32_t ring0 = (uint32_t)__cvta_generic_to_shared(smem_raw) + (uint32_t)warp * STAGES * STAGE_BYTES + lane * 16;
+  typedef float PartTile[TILES][16][8 * MT + 1];
+  PartTile* part = reinterpret_cast<PartTile*>(smem_raw + Shape::RING_BYTES);  // [2][SW]
+  float(*ssq_part)[8 * MT] = reinterpret_cast<float(*)[8 * MT]>(smem_raw + Shape::RING_BYTES + Shape::PART_BYTES);  // [SW]
+
+  const int tiles = (N + 15) / 16;
+  const int my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const int chunks = K / 32;
+  const int per = chunks / SW, extra = chunks % SW;
+  const int c_begin = warp * per + min(warp, extra);
+  const int cpw = per + (warp < extra ? 1 : 0);
+  const int units = my_tiles * cpw;
+
+  const __nv_bfloat16* wsrc[2];
+  auto tile_rows = [&](int ti) {
+    const int row0 = (blockIdx.x + ti * gridDim.x) * 16;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      int row = row0 + g + 8 * r;
+      row = row < N ? row : N - 1;
+      wsrc[r] = W + (size_t)row * K + c_begin * 32 + t * 8;
+    }
+  };
+  const size_t up_elems = (size_t)up_offset * K;
+  int issued = 0, issue_c = 0, issue_ti = 0, issue_stage = 0;
+  uint32_t issue_slot = ring0;
+  if (units > 0) tile_rows(0);
+  auto issue = [&]() {
+#pragma unroll
+    for (int tl = 0; tl < TILES; ++tl) {
+      cp16_cg(issue_slot + (2 * tl) * 512, wsrc[0] + tl * up_elems + issue_c * 32);
+      cp16_cg(issue_slot + (2 * tl + 1) * 512, wsrc[1] + tl * up_elems + issue_c * 32);
+    }
+    ++issued;
+    if (++issue_c == cpw) {
+      issue_c = 0;
+      if (++issue_ti < my_tiles) tile_rows(issue_ti);
+    }
+    if (++issue_stage == STAGES) { issue_stage = 0; issue_slot = ring0; } else issue_slot += STAGE_BYTES;
+  };
+  // weights never change: prime the ring before waiting for the preceding kernel
+  pdl_trigger();
+#pragma unroll
+  for (int u = 0; u < STAGES - 1; ++u) {
+    if (issued < units) issue();
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  }
+  pdl_wait();
+
+  // ---- this warp's operand fragments of v * gain, and its share of sum(v^2)
+  uint4 xf[CPW][MT];
+  {
+    float ssq[MT];
+#pragma unroll
+    for (int j = 0; j < MT; ++j) ssq[j] = 0.f;
+#pragma unroll
+    for (int cc = 0; cc < CPW; ++cc) {
+#pragma unroll
+      for (int j = 0; j < MT; ++j) {
+        const int m = 8 * j + g;
+        uint4 packed = make_uint4(0u, 0u, 0u, 0u);
+        if (cc < cpw && m < M) {
+          const int src = rows ? rows[m] : m;
+          const size_t at = (size_t)src * K + (size_t)(c_begin + cc) * 32 + t * 8;
+          float v[8], gn[8];
+          load8_any<float>(h_in + at, v);
+          if (pending) {
+            float p[8];
+            load8_any<__nv_bfloat16>(pending + at, p);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[k] += p[k];
+            if (h_out && blockIdx.x == 0) {
+              *reinterpret_cast<float4*>(h_out + at) = make_float4(v[0], v[1], v[2], v[3]);
+              *reinterpret_cast<float4*>(h_out + at + 4) = make_float4(v[4], v[5], v[6], v[7]);
+            }
+          }
+          load8_any<float>(gain + (size_t)(c_begin + cc) * 32 + t * 8, gn);
+          __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            ssq[j] += v[2 * k] * v[2 * k] + v[2 * k + 1] * v[2 * k + 1];
+            o2[k] = __floats2bfloat162_rn(v[2 * k] * gn[2 * k], v[2 * k + 1] * gn[2 * k + 1]);
+          }
+        }
+        xf[cc][j] = packed;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < MT; ++j) {
+      float s = ssq[j];
+      s += __shfl_xor_sync(0xffffffffu, s, 1);
+      s += __shfl_xor_sync(0xffffffffu, s, 2);
+      if (t == 0) ssq_part[warp][8 * j + g] = s;
+    }
+  }
+
+  uint32_t read_slot = ring0;
+  int read_stage = 0;
+  for (int ti = 0; ti < my_tiles; ++ti) {
+    float acc[TILES][MT][4];
+#pragma unroll
+    for (int tl = 0; tl < TILES; ++tl)
+#pragma unroll
+      for (int j = 0; j < MT; ++j) acc[tl][j][0] = acc[tl][j][1] = acc[tl][j][2] = acc[tl][j][3] = 0.f;
+#pragma unroll
+    for (int cc = 0; cc < CPW; ++cc) {
+      if (cc < cpw) {
+        if (issued < units) issue();
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(STAGES - 1) : "memory");
+        uint4 wv[TILES][2];
+#pragma unroll
+        for (int tl = 0; tl < TILES; ++tl) {
+          wv[tl][0] = lds16(read_slot + (2 * tl) * 512);
+          wv[tl][1] = lds16(read_slot + (2 * tl + 1) * 512);
+        }
+        if (++read_stage == STAGES) { read_stage = 0; read_slot = ring0; } else read_slot += STAGE_BYTES;
+#pragma unroll
+        for (int tl = 0; tl < TILES; ++tl)
+#pragma unroll
+          for (int j = 0; j < MT; ++j) {
+            mma_bf16(acc[tl][j], wv[tl][0].x, wv[tl][1].x, wv[tl][0].y, wv[tl][1].y, xf[cc][j].x, xf[cc][j].y);
+            mma_bf16(acc[tl][j], wv[tl][0].z, wv[tl][1].z, wv[tl][0].w, wv[tl][1].w, xf[cc][j].z, xf[cc][j].w);
+          }
+      }
+    }
+    PartTile* mine = part + (size_t)(ti & 1) * SW;
+#pragma unroll
+    for (int tl = 0; tl < TILES; ++tl)
+#pragma unroll
+      for (int j = 0; j < MT; ++j) {
+        mine[warp][tl][g][8 * j + 2 * t] = acc[tl][j][0];
+        mine[warp][tl][g][8 * j + 2 * t + 1] = acc[tl][j][1];
+        mine[warp][tl][g + 8][8 * j + 2 * t] = acc[tl][j][2];
+        mine[warp][tl][g + 8][8 * j + 2 * t + 1] = acc[tl][j][3];
+      }
+    __syncthreads();  // also makes every warp's sum of squares visible (written before the first of these barriers)
+    const int row0 = (blockIdx.x + ti * gridDim.x) * 16;
+    for (int idx = threadIdx.x; idx < 16 * 8 * MT; idx += SW * 32) {
+      const int r = idx & 15, m = idx >> 4;
+      const int row = row0 + r;
+      if (m >= M || row >= N) continue;
+      float total = 0.f;
+#pragma unroll
+      for (int w = 0; w < SW; ++w) total += ssq_part[w][m];
+      const float inv = rsqrtf(total / (float)K + eps);
+      float v[TILES];
+#pragma unroll
+      for (int tl = 0; tl < TILES; ++tl) {
+        float sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < SW; ++w) sum += mine[w][tl][r][m];
+        v[tl] = sum * inv;
+      }
+      float out;
+      if (TILES == 2) {
+        const float gate = __bfloat162float(__float2bfloat16_rn(v[0]));
+        const float up = __bfloat162float(__float2bfloat16_rn(v[TILES - 1]));
+        out = gate / (1.f + expf(-gate)) * up;
+      } else {
+        out = v[0];
+      }
+      y[(size_t)m * ldy + row] = from_float<TOut>(out);
+    }
+  }
+  asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+}
+
+template <int MT, int TILES, int CPW, typename TOut>
+int launch_norm_stream(const void* h_in, const void* pending, const void* gain, const void* rows, void* h_out, const void* W,
+                       void* y, int M, int N, int K, int ldy, int up_offset, float eps, int sms, cudaStream_t stream) {
+  using Shape = NormStreamShape<MT, TILES>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_stream_norm_kernel<MT, TILES, CPW, TOut>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Shape::SMEM_BYTES);
+    if (e != cudaSuccess) PSB_REFUSE("gemm_stream_norm: cannot reserve %d bytes of shared memory: %s", Shape::SMEM_BYTES, cudaGetErrorString(e));
+    configured = true;
+  }
+  const int tiles = (N + 15) / 16;
+  const int grid = tiles < sms ? tiles : sms;
+  psb_launch(gemm_stream_norm_kernel<MT, TILES, CPW, TOut>, dim3(grid), dim3(SW * 32), (size_t)Shape::SMEM_BYTES, stream,
+             (const float*)h_in, (const __nv_bfloat16*)pending, (const float*)gain, (const int32_t*)rows, (float*)h_out,
+             (const __nv_bfloat16*)W, (TOut*)y, M, N, K, ldy, up_offset, eps);
+  return 0;
+}
+
+template <int TILES, typename TOut>
+int dispatch_norm_stream(const void* h_in, const void* pending, const void* gain, const void* rows, void* h_out, const void* W,
+                         void* y, int M, int N, int K, int ldy, int up_offset, float eps, int sms, cudaStream_t stream) {
+  const int cpw = (K / 32 + SW - 1) / SW;  // the most chunks any warp owns
+#define PSB_NS(MT, CPW) launch_norm_stream<MT, TILES, CPW, TOut>(h_in, pending, gain, rows, h_out, W, y, M, N, K, ldy, up_offset, eps, sms, stream)
+  if (M <= 8) {
+    if (cpw <= 4) return PSB_NS(1, 4);
+    if (cpw <= 8) return PSB_NS(1, 8);
+    if (cpw <= 16) return PSB_NS(1, 16);
+  } else if (M <= 16) {
+    if (cpw <= 4) return PSB_NS(2, 4);
+    if (cpw <= 8) return PSB_NS(2, 8);
+  }
+#undef PSB_NS
+  PSB_REFUSE("gemm_stream_norm: M=%d K=%d is beyond this kernel (M <= 8 with K <= 8192, or M <= 16 with K <= 4096)", M, K);
+}
+
+}  // namespace
+
+// 1 if psb_gemm_stream_norm takes the shape, else 0.
+PSB_API int psb_gemm_stream_norm_supported(int M, int K) {
+  if (M < 1 || K < 32 || K % 32) return 0;
+  const int cpw = (K / 32 + SW - 1) / SW;
+  return (M <= 8 && cpw <= 16) || (M <= 16 && cpw <= 8) ? 1 : 0;
+}
+
+// y[M,N] = rmsnorm(h_in[rows] + pending[rows]; gain, eps) W[N,K]^T; h_out (optional, rows absent) receives the sum.
+PSB_API int psb_gemm_stream_norm(const void* h_in, const void* pending, const void* gain, const void* rows, void* h_out,
+                                 const void* W, void* y, int out_dtype, int M, int N, int K, float eps, int sms,
+                                 cudaStream_t stream) {
+  if (!psb_gemm_stream_norm_supported(M, K) || N < 1 || sms < 1) PSB_REFUSE("gemm_stream_norm: shape M=%d N=%d K=%d is not taken", M, N, K);
+  if (rows && h_out) PSB_REFUSE("gemm_stream_norm: the stream cannot be updated through a row selection");
+  if (!(eps > 0.f)) PSB_REFUSE("gemm_stream_norm: eps must be positive");
+  int rc;
+  if (out_dtype == PSB_F32) rc = dispatch_norm_stream<1, float>(h_in, pending, gain, rows, h_out, W, y, M, N, K, N, 0, eps, sms, stream);
+  else if (out_dtype == PSB_BF16) rc = dispatch_norm_stream<1, __nv_bfloat16>(h_in, pending, gain, rows, h_out, W, y, M, N, K, N, 0, eps, sms, stream);
+  else PSB_REFUSE("gemm_stream_norm: unknown output dtype %d", out_dtype);
+  if (rc) return rc;
+  PSB_LAUNCH_CHECK("gemm_stream_norm");
+  return 0;
+}
+
+// act[M,I] = silu(x Wg^T) * (x Wu^T) with x = rmsnorm(h_in + pending) as above, W = [Wg; Wu].
+PSB_API int psb_gemm_stream_norm_gated(const void* h_in, const void* pending, const void* gain, void* h_out, const void* W,
+                                       void* act, int M, int I, int K, float eps, int sms, cudaStream_t stream) {
+  if (!psb_gemm_stream_norm_supported(M, K) || I < 1 || sms < 1) PSB_REFUSE("gemm_stream_norm_gated: shape M=%d I=%d K=%d is not taken", M, I, K);
+  if (!(eps > 0.f)) PSB_REFUSE("gemm_stream_norm_gated: eps must be positive");
+  if (int rc = dispatch_norm_stream<2, __nv_bfloat16>(h_in, pending, gain, nullptr, h_out, W, act, M, I, K, I, I, eps, sms, stream)) return rc;
+  PSB_LAUNCH_CHECK("gemm_stream_norm_gated");
+  return 0;
+}

@@ -2,6 +2,7 @@
 the host and raises ``KernelError`` instead of launching on arguments a kernel
 was not written for."""
 
+from .deferred import NormedRows  # noqa: F401
 from .kernels import (  # noqa: F401
     KernelError,
     add_rmsnorm,

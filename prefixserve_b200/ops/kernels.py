@@ -10,6 +10,7 @@ import math
 
 import torch
 
+from .deferred import NormedRows
 from .library import KernelError, check, lib
 
 F32, BF16 = 0, 1
@@ -108,6 +109,13 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
     float32 CUDA-core kernel, so that path never touches a reduced-precision
     matrix mode.
     """
+    if isinstance(x, NormedRows):
+        if x.fusable and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+            from .tensorcore import norm_linear_bf16
+            y = norm_linear_bf16(x, w, out_dtype or x.dtype)
+            if y is not None:
+                return y
+        x = x.tensor()
     out_dtype = out_dtype or x.dtype
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
         from .tensorcore import linear_bf16
@@ -117,6 +125,13 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
 
 def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     """silu(x Wg^T) * (x Wu^T) for W = [gate rows; up rows]: fused for few bfloat16 rows, else product then activation."""
+    if isinstance(x, NormedRows):
+        if x.fusable and x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16:
+            from .tensorcore import norm_gated_linear_bf16
+            act = norm_gated_linear_bf16(x, w_gate_up)
+            if act is not None:
+                return act
+        x = x.tensor()
     if x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16:
         from .tensorcore import gated_linear_bf16
         _dev(x, "left operand"), _dev(w_gate_up, "weight")

@@ -55,6 +55,12 @@ _SIGNATURES: dict[str, list] = {
     "psb_gemm_stream": [P, P, P, I, I, I, I, I, P],
     # (x, W, act, M, I, K, sms, stream)
     "psb_gemm_stream_gated": [P, P, P, I, I, I, I, P],
+    # (M, K) -> 1 if the norm-fused streaming product takes the shape
+    "psb_gemm_stream_norm_supported": [I, I],
+    # (h_in, pending, gain, rows, h_out, W, y, out_dtype, M, N, K, eps, sms, stream)
+    "psb_gemm_stream_norm": [P, P, P, P, P, P, P, I, I, I, I, F, I, P],
+    # (h_in, pending, gain, h_out, W, act, M, I, K, eps, sms, stream)
+    "psb_gemm_stream_norm_gated": [P, P, P, P, P, P, I, I, I, F, I, P],
     # (a, w, c, M, N, K, sms, stream)
     "psb_gemm_tcgen05": [P, P, P, I, I, I, I, P],
     # (a, w, act, M, I, K, sms, stream)

@@ -59,6 +59,53 @@ def gemm_stream_gated(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     return act
 
 
+FUSE_NORM = True    # few rows: fold the residual sum and the RMSNorm in front of a product into the streaming kernel
+
+
+def _norm_fusable(x, w: torch.Tensor) -> bool:
+    m, k = x.shape
+    pending = x.pending
+    return (FUSE_NORM and w.is_contiguous() and w.shape[1] == k and x.h.is_contiguous() and x.h.dtype == torch.float32
+            and (pending is None or (pending.dtype == torch.bfloat16 and pending.is_contiguous() and pending.shape == x.h.shape))
+            and k % 32 == 0 and 0 < m <= 16 and bool(lib().psb_gemm_stream_norm_supported(m, k)))
+
+
+def norm_linear_bf16(x, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor | None:
+    """rmsnorm(h + pending) @ w^T in the streaming kernel; None when that kernel does not take the shape.
+
+    ``x`` is an ``ops.NormedRows`` that nobody has turned into a tensor yet.  The float32 stream after the sum goes to
+    a new tensor (other CTAs still read the old one while the first CTA writes), which ``x`` is told of.
+    """
+    if out_dtype not in _OUT_CODE or not _norm_fusable(x, w):
+        return None
+    m, k = x.shape
+    n = w.shape[0]
+    y = torch.empty((m, n), dtype=out_dtype, device=w.device)
+    new_h = torch.empty_like(x.h) if (x.pending is not None and x.rows is None) else None
+    check(lib().psb_gemm_stream_norm(x.h.data_ptr(), None if x.pending is None else x.pending.data_ptr(), x.gain.data_ptr(),
+                                     None if x.rows is None else x.rows.data_ptr(), None if new_h is None else new_h.data_ptr(),
+                                     w.data_ptr(), y.data_ptr(), _OUT_CODE[out_dtype], m, n, k, x.eps, _sms(w.device),
+                                     torch.cuda.current_stream().cuda_stream), "gemm_stream_norm")
+    x.fused(new_h)
+    return y
+
+
+def norm_gated_linear_bf16(x, w_gate_up: torch.Tensor) -> torch.Tensor | None:
+    """silu(x Wg^T) * (x Wu^T) with x = rmsnorm(h + pending), all in the streaming kernel; None when it does not fit."""
+    if w_gate_up.shape[0] % 2 or x.rows is not None or not _norm_fusable(x, w_gate_up):
+        return None
+    m, k = x.shape
+    inter = w_gate_up.shape[0] // 2
+    act = torch.empty((m, inter), dtype=torch.bfloat16, device=w_gate_up.device)
+    new_h = torch.empty_like(x.h) if x.pending is not None else None
+    check(lib().psb_gemm_stream_norm_gated(x.h.data_ptr(), None if x.pending is None else x.pending.data_ptr(), x.gain.data_ptr(),
+                                           None if new_h is None else new_h.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(),
+                                           m, inter, k, x.eps, _sms(w_gate_up.device),
+                                           torch.cuda.current_stream().cuda_stream), "gemm_stream_norm_gated")
+    x.fused(new_h)
+    return act
+
+
 def _tcgen05_ok(x: torch.Tensor, w: torch.Tensor, n_span: int = 256) -> bool:
     n_out = w.shape[0] if n_span == 256 else w.shape[0] // 2
     tiles = -(-x.shape[0] // 128) * -(-n_out // n_span)

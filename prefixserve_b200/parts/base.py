@@ -97,6 +97,10 @@ class StepContext:
 class Part:
     """Base class; subclasses override what they need."""
 
+    # A mixer, feed-forward or head that hands its input straight to ``ops.linear`` / ``ops.gated_linear`` sets this
+    # and then receives an ``ops.NormedRows`` instead of a tensor (see ``Norm.defer``).
+    takes_deferred_input = False
+
     # True when forward() launches the same device work for the same tensor shapes, reading everything that varies
     # from device memory (then a decode step can be captured once and replayed).  A part that loops over
     # ``ctx.items`` on the host must leave this False.
@@ -138,6 +142,13 @@ class Norm(Part):
         h is left untouched (last use of the stream).
         """
         raise NotImplementedError
+
+    def defer(self, h: torch.Tensor, delta: torch.Tensor | None, ctx: StepContext, rows: torch.Tensor | None = None):
+        """Same, for a consumer that declares ``takes_deferred_input``: returns an ``ops.NormedRows``, which the
+        consumer passes to ``ops.linear`` / ``ops.gated_linear`` (they may do the norm inside the product) or turns
+        into a tensor with ``.tensor()``.  A norm without a deferred form computes now and wraps the result."""
+        from ..ops import NormedRows
+        return NormedRows.ready(self.forward(h, delta, ctx, rows), h)
 
 
 class PositionEncoding(Part):

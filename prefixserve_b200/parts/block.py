@@ -26,8 +26,16 @@ class Block:
         return (("mixer_norm", self.mixer_norm), ("mixer", self.mixer), ("ffn_norm", self.ffn_norm), ("ffn", self.ffn))
 
     def forward(self, h, pending, ctx: StepContext, cache: CacheView):
-        x = self.mixer_norm.forward(h, pending, ctx)
-        pending = self.mixer.forward(x, ctx, cache)
-        x = self.ffn_norm.forward(h, pending, ctx)
-        pending = self.ffn.forward(x, ctx)
+        h, pending = _sublayer(self.mixer_norm, self.mixer, h, pending, ctx, cache)
+        h, pending = _sublayer(self.ffn_norm, self.ffn, h, pending, ctx)
         return h, pending
+
+
+def _sublayer(norm, part, h, pending, ctx, *more):
+    """(stream after adding ``pending``, the part's output).  A part that takes a deferred input may have the sum
+    and the norm done inside its first product, which then writes the summed stream to a new tensor."""
+    if part.takes_deferred_input:
+        x = norm.defer(h, pending, ctx)
+        out = part.forward(x, ctx, *more)
+        return x.residual(), out
+    return h, part.forward(norm.forward(h, pending, ctx), ctx, *more)

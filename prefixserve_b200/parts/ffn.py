@@ -12,6 +12,7 @@ from .registry import register_ffn
 
 class GatedMLP(FeedForward):
     graph_safe = True  # device work depends only on tensor shapes and device-side inputs
+    takes_deferred_input = True  # x goes to one product only, which may do the norm in front of it itself
 
     def __init__(self, params):
         super().__init__(params)

@@ -73,8 +73,9 @@ class DecoderModel:
             h, pending = self.blocks[call.layer].forward(h, pending, ctx, cache_view(call.cache, call.writes_cache))
         if rows.numel() == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=h.device)
-        x = self.final_norm.forward(h, pending, ctx, rows=rows)
-        return self.head.forward(x)
+        if self.head.takes_deferred_input:
+            return self.head.forward(self.final_norm.defer(h, pending, ctx, rows=rows))
+        return self.head.forward(self.final_norm.forward(h, pending, ctx, rows=rows))
 
 
 def build_model(spec: ModelSpec) -> DecoderModel:

@@ -33,5 +33,8 @@ class RMSNorm(Norm):
     def forward(self, h, delta, ctx: StepContext, rows=None):
         return ops.add_rmsnorm(h, delta, self.gain, self.eps, ctx.compute_dtype, rows)
 
+    def defer(self, h, delta, ctx: StepContext, rows=None):
+        return ops.NormedRows(h, delta, self.gain, self.eps, ctx.compute_dtype, rows)
+
 
 register_norm("rms", RMSNorm, replace=True)

@@ -466,6 +466,82 @@ def test_gemm_stream_gated(m, inter, k):
     assert torch.allclose(got.double(), want, rtol=3e-2, atol=3e-2)
 
 
+# ---- the streaming product with the residual sum and the RMSNorm in front of it folded in ---------------------------
+
+def _plain_normed(h, pending, gain, eps, rows=None):
+    v = h.double() + (0 if pending is None else pending.double())
+    if rows is not None:
+        v = v[rows.long()]
+    return v, v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps) * gain.double()
+
+
+@pytest.mark.parametrize("m", [1, 5, 8, 11, 16])
+@pytest.mark.parametrize("n,k,eps", [(40, 64, 1e-5), (1000, 96, 1e-6), (3072, 2048, 1e-5), (520, 3104, 2e-3), (96, 8192, 1e-5)])
+@pytest.mark.parametrize("with_pending", [True, False])
+def test_norm_fused_linear(m, n, k, eps, with_pending):
+    from prefixserve_b200 import ops
+    from prefixserve_b200.ops.tensorcore import norm_linear_bf16
+    h = torch.randn(m, k, device=DEV) * 3.0
+    pending = torch.randn(m, k, device=DEV).to(torch.bfloat16) if with_pending else None
+    gain = 1.0 + 0.3 * torch.randn(k, device=DEV)
+    w = (torch.randn(n, k, device=DEV) / math.sqrt(k)).to(torch.bfloat16)
+    x = ops.NormedRows(h.clone(), pending, gain, eps, torch.bfloat16)
+    got = norm_linear_bf16(x, w, torch.float32)
+    if m > 8 and k > 4096:
+        assert got is None  # beyond the kernel: the caller takes the unfused way
+        got = ops.linear(x, w, out_dtype=torch.float32)
+    v, normed = _plain_normed(h, pending, gain, eps)
+    want = normed @ w.double().t()
+    assert float((got.double() - want).abs().max()) <= 2e-2 * float(want.abs().max()) + 1e-3
+    assert torch.allclose(x.residual().double(), v, rtol=0, atol=1e-6)   # the float32 stream after the sum: exact
+    # the unfused way, through the norm's own kernel, for comparison of the error against float64
+    y = ops.NormedRows(h.clone(), pending, gain, eps, torch.bfloat16)
+    unfused = ops.linear(y.tensor(), w, out_dtype=torch.float32)
+    err_fused, err_unfused = float((got.double() - want).abs().max()), float((unfused.double() - want).abs().max())
+    assert err_fused <= 2.0 * err_unfused + 1e-3 * float(want.abs().max())
+
+
+def test_norm_fused_linear_on_chosen_rows_and_gated():
+    from prefixserve_b200 import ops
+    from prefixserve_b200.ops.tensorcore import norm_gated_linear_bf16, norm_linear_bf16
+    t, k, n, eps = 37, 160, 1031, 1e-5
+    h = torch.randn(t, k, device=DEV)
+    pending = torch.randn(t, k, device=DEV).to(torch.bfloat16)
+    gain = 1.0 + 0.3 * torch.randn(k, device=DEV)
+    w = (torch.randn(n, k, device=DEV) / math.sqrt(k)).to(torch.bfloat16)
+    rows = torch.tensor([36, 0, 7, 7, 19], dtype=torch.int32, device=DEV)
+    before = h.clone()
+    x = ops.NormedRows(h, pending, gain, eps, torch.bfloat16, rows)
+    got = norm_linear_bf16(x, w, torch.float32)
+    assert got is not None and torch.equal(h, before)           # a row selection leaves the stream alone
+    _, normed = _plain_normed(before, pending, gain, eps, rows)
+    want = normed @ w.double().t()
+    assert float((got.double() - want).abs().max()) <= 2e-2 * float(want.abs().max())
+    assert torch.equal(got[2], got[3])
+    for m, inter, kk in [(3, 72, 64), (16, 1000, 2048), (8, 333, 4128)]:
+        h = torch.randn(m, kk, device=DEV)
+        pending = torch.randn(m, kk, device=DEV).to(torch.bfloat16)
+        gain = 1.0 + 0.3 * torch.randn(kk, device=DEV)
+        w = (torch.randn(2 * inter, kk, device=DEV) / math.sqrt(kk)).to(torch.bfloat16)
+        x = ops.NormedRows(h.clone(), pending, gain, eps, torch.bfloat16)
+        act = norm_gated_linear_bf16(x, w)
+        assert act is not None and act.dtype == torch.bfloat16
+        v, normed = _plain_normed(h, pending, gain, eps)
+        y = (normed @ w.double().t()).to(torch.bfloat16).double()
+        want = torch.nn.functional.silu(y[:, :inter]) * y[:, inter:]
+        assert float((act.double() - want).abs().max()) <= 3e-2 * float(want.abs().max()) + 3e-2
+        assert torch.allclose(x.residual().double(), v, rtol=0, atol=1e-6)
+
+
+def test_normed_rows_nobody_consumed_still_update_the_stream():
+    from prefixserve_b200 import ops
+    h = torch.randn(4, 64, device=DEV)
+    pending = torch.randn(4, 64, device=DEV).to(torch.bfloat16)
+    x = ops.NormedRows(h.clone(), pending, torch.ones(64, device=DEV), 1e-5, torch.bfloat16)
+    assert torch.allclose(x.residual(), h + pending.float())
+    assert torch.allclose(x.residual(), h + pending.float())  # and only once
+
+
 # ---- the tcgen05 / TMEM / TMA product for many rows -----------------------------------------------------------------
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (17, 40, 8), (130, 333, 264), (2048, 3072, 2048), (300, 2048, 8192),
