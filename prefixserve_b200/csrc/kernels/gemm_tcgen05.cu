@@ -20,9 +20,7 @@
 // issuing work, pauses long enough for copies in flight to land, frees its tensor memory and returns; the host finds
 // a non-zero status word (psb_tcgen05_status) and raises.  That path has never been taken in testing; it exists so
 // that a defect cannot hang the GPU.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace {
 
@@ -33,7 +31,6 @@ constexpr int B_BYTES = BN * BK * 2;        // 32 KB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int THREADS = 192;
 constexpr int TMEM_COLS = 512;              // two accumulator buffers of BN float32 columns
-constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
 // shared memory: [stages][A | B] (1024-byte aligned), then barriers and the tensor-memory address
 struct Barriers {
@@ -46,92 +43,9 @@ struct Barriers {
 };
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + (int)sizeof(Barriers);
 
-__device__ int g_tcgen05_status = 0;  // 0 ok; otherwise which wait gave up (1 producer, 2 mma, 3 epilogue, 4 mma/acc)
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(done)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return done != 0;
-}
-// Bounded: false when the barrier did not complete within SPIN_LIMIT polls or another warp has raised the abort flag.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort, int who) {
-  for (uint32_t spin = 0; spin < SPIN_LIMIT; ++spin) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (*abort) return false;
-  }
-  *abort = 1;
-  atomicCAS(&g_tcgen05_status, 0, who);
-  return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
-      : "memory");
-}
-
-// K-major operand tile with 128-byte swizzle: rows of 128 bytes, 8 rows (1024 bytes) per swizzle atom.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr >> 4) & 0x3fff);        // start address, 16-byte units
-  d |= (uint64_t)1 << 16;                       // leading byte offset: unused with swizzled K-major tiles
-  d |= (uint64_t)(1024 >> 4) << 32;             // stride byte offset: 8 rows of 128 bytes
-  d |= (uint64_t)1 << 46;                       // descriptor version of this architecture
-  d |= (uint64_t)2 << 61;                       // 128-byte swizzle
-  return d;
-}
-// kind::f16: bfloat16 A and B, float32 accumulate, both K-major, M=128, N=256
-constexpr uint32_t INSTR_DESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-
-__device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(INSTR_DESC), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void mma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
+// status word: 0 ok; otherwise which wait gave up (1 producer, 2 mma, 3 epilogue, 4 mma/acc)
+using namespace tc;
+constexpr uint32_t INSTR_DESC = instr_desc(BM, BN, false);  // M=128, N=256, both operands K-major
 
 // gated: 0 plain (C[M, N], tile columns [n0, n0+128) and [n0+128, n0+256)); 1 gated (C[M, I], W = [gate; up], tile
 // columns [n0, n0+128) of the gate and the same of the up rows).
@@ -164,12 +78,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 2) {  // one warp allocates (and later frees) the tensor memory
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)), "r"(TMEM_COLS) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    tmem_alloc(&bars->tmem_base, TMEM_COLS);
   }
-  tc_fence_before();
+  fence_before();
   __syncthreads();
-  tc_fence_after();
+  fence_after();
   const uint32_t tmem_base = bars->tmem_base;
   pdl_wait();  // A is the preceding kernel's output
 
@@ -204,18 +117,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const uint32_t buf = local & 1, use = local >> 1;  // accumulator buffer and how often it has been used
         ok = mbar_wait(&bars->acc_empty[buf], (use & 1) ^ 1, abort, 4);
         if (!ok) break;
-        tc_fence_after();
+        fence_after();
         const uint32_t acc = tmem_base + buf * BN;
         for (int kb = 0; kb < k_blocks; ++kb) {
           ok = mbar_wait(&bars->full[stage], phase, abort, 2);
           if (!ok) break;
-          tc_fence_after();
+          fence_after();
           const uint32_t a_addr = smem_u32(tiles + stage * STAGE_BYTES);
           const uint32_t b_addr = a_addr + A_BYTES;
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
             // 16 elements = 32 bytes further along K inside the swizzled 128-byte rows
-            mma_f16(acc, smem_desc(a_addr + k * 32), smem_desc(b_addr + k * 32), (kb | k) != 0);
+            mma_f16(acc, smem_desc(a_addr + k * 32), smem_desc(b_addr + k * 32), INSTR_DESC, (kb | k) != 0);
           }
           mma_commit(&bars->empty[stage]);  // arrives when the MMAs that read this stage are done
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -234,7 +147,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int n0 = (tile / m_blocks) * n_span;
       ok = mbar_wait(&bars->acc_full[buf], use & 1, abort, 3);
       if (!ok) break;
-      tc_fence_after();
+      fence_after();
       const int row = m0 + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
       __nv_bfloat16* crow = C + (size_t)row * ldc;
@@ -293,7 +206,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           }
         }
       }
-      tc_fence_before();
+      fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->acc_empty[buf]);  // this warp has read its part of the buffer
     }
@@ -303,42 +216,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     // something gave up: give copies in flight time to land before the shared memory is handed to another CTA
     for (int i = 0; i < 200; ++i) __nanosleep(1000);
   }
-  tc_fence_before();
+  fence_before();
   __syncthreads();
   if (warp == 2) {
-    tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    fence_after();
+    tmem_free(tmem_base, TMEM_COLS);
   }
 }
 
 // ---- host side -----------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
-  return fn;
-}
-
-// row-major [rows, K] bfloat16 matrix, box of 64 columns x box_rows rows, 128-byte swizzle, zero fill outside
+// row-major [rows, K] bfloat16 matrix, box of 64 columns x box_rows rows
 int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
-  EncodeTiledFn fn = encode_tiled();
-  if (!fn) PSB_REFUSE("gemm_tcgen05: the driver does not export cuTensorMapEncodeTiled");
-  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-  const cuuint32_t elem[2] = {1, 1};
-  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) PSB_REFUSE("gemm_tcgen05: cuTensorMapEncodeTiled failed with code %d (rows=%d K=%d)", (int)r, rows, K);
+  const int r = make_map_bf16(map, base, (uint64_t)rows, (uint64_t)K, (uint64_t)K, box_rows);
+  if (r == -1) PSB_REFUSE("gemm_tcgen05: the driver does not export cuTensorMapEncodeTiled");
+  if (r != 0) PSB_REFUSE("gemm_tcgen05: cuTensorMapEncodeTiled failed with code %d (rows=%d K=%d)", r, rows, K);
   return 0;
 }
 
@@ -378,7 +269,5 @@ PSB_API int psb_gemm_tcgen05_gated(const void* a, const void* w, void* act, int 
 
 // 0 while no bounded wait has ever run out on the current device; reading it synchronises with the device.
 PSB_API int psb_tcgen05_status() {
-  int v = -1;
-  if (cudaMemcpyFromSymbol(&v, g_tcgen05_status, sizeof(int)) != cudaSuccess) return -1;
-  return v;
+  return tc::read_status();
 }

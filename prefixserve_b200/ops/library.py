@@ -42,6 +42,15 @@ _SIGNATURES: dict[str, list] = {
     "psb_attention_prefill_bf16": [P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P],
     # (D) -> rows per CTA
     "psb_attention_prefill_rows_per_cta": [I],
+    # (D, page_size) -> 1 if the tcgen05 prefill attention takes them
+    "psb_attention_prefill_tcgen05_supported": [I, I],
+    # () -> rows per CTA
+    "psb_attention_prefill_tcgen05_rows_per_cta": [],
+    # (q, kv, table, table_width, item_start, kv_len, out, num_items, num_pairs, T, hq, hkv, D, page_size, num_pages,
+    #  window, scale, skip_single, stream)
+    "psb_attention_prefill_tcgen05": [P, P, P, I, P, P, P, I, I, I, I, I, I, I, L, I, F, I, P],
+    # () -> 0 while no bounded wait of the tcgen05 attention kernel has ever run out
+    "psb_attention_tcgen05_status": [],
     # (q, kv, table, table_width, item_start, kv_len, out, part_o, part_ml, num_items, hq, hkv, D, page_size, window,
     #  scale, chunk, max_splits, all_single, stream)
     "psb_attention_decode_bf16": [P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P],
@@ -107,8 +116,10 @@ def pdl_enabled() -> bool:
 
 
 def tcgen05_status() -> int:
-    """0 unless a bounded wait inside the tcgen05 product ever gave up (then its results are void). Synchronises."""
-    return int(lib().psb_tcgen05_status())
+    """0 unless a bounded wait inside a tcgen05 kernel ever gave up (then its results are void). Synchronises.
+
+    The product's code sits in the low byte, prefill attention's in the next."""
+    return int(lib().psb_tcgen05_status()) | (int(lib().psb_attention_tcgen05_status()) << 8)
 
 
 def declare(name: str, argtypes: list) -> None:

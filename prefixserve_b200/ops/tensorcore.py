@@ -20,6 +20,8 @@ USE_TCGEN05 = True  # products with more rows than STREAM_M: this library's tcge
 TCGEN05_MIN_TILES = 120  # ... when the product has at least this many 128x256 output tiles; smaller ones (a few
                          # dozen rows against a narrow matrix) leave most SMs idle without split-K and go to cuBLAS
 WIDE_BELOW_TILES = 600   # matrices with fewer 16-row tiles than this get 16 warps per CTA instead of 8
+TCGEN05_PREFILL_MIN_TOKENS = 64   # steps whose longest prompt portion has at least this many tokens run prefill attention
+                                  # on the tcgen05 kernel (tiles of 128 rows); shorter portions fill too little of a tile
 DECODE_CTAS_PER_SM = 4   # split-KV: key ranges are sized so that about this many CTAs per SM exist
 _OUT_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -233,6 +235,15 @@ def attention_bf16(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, item_
             out.data_ptr(), part_o.data_ptr() if part_o is not None else None,
             part_ml.data_ptr() if part_ml is not None else None, b, hq, hkv, d, page, w, float(scale), chunk, max_splits,
             1 if len(singles) == b else 0, stream), "attention_decode")
+    portions = [n for n in new_tokens if not (use_decode and n == 1)]
+    if (USE_TCGEN05 and portions and max(portions) >= TCGEN05_PREFILL_MIN_TOKENS
+            and lib().psb_attention_prefill_tcgen05_supported(d, page) and q.is_contiguous() and kv.is_contiguous()):
+        per_cta = lib().psb_attention_prefill_tcgen05_rows_per_cta()
+        check(lib().psb_attention_prefill_tcgen05(
+            q.data_ptr(), kv.data_ptr(), table.data_ptr(), table.shape[1], item_start.data_ptr(), kv_len.data_ptr(),
+            out.data_ptr(), b, sum(-(-n // per_cta) for n in portions), t, hq, hkv, d, page, kv.shape[0], w, float(scale),
+            1 if use_decode else 0, stream), "attention_prefill_tcgen05")
+        return out
     rows = lib().psb_attention_prefill_rows_per_cta(d)
     tiles = sum(-(-(n * group) // rows) for n in new_tokens if not (use_decode and n == 1))
     if tiles:

@@ -390,6 +390,60 @@ def test_attention_tensor_cores_find_one_far_key():
         assert torch.allclose(out.float().cpu(), want[old:], atol=3e-2, rtol=3e-2), (old, new)
 
 
+@pytest.mark.parametrize("hq,hkv,d,page", [(8, 2, 64, 16), (4, 4, 64, 64), (6, 2, 128, 16), (3, 1, 128, 32), (2, 1, 64, 128)])
+@pytest.mark.parametrize("window", [None, 100, 300])
+def test_attention_prefill_tcgen05(hq, hkv, d, page, window, monkeypatch):
+    """Prompt portions of every shape on the tcgen05 kernel: whole tiles and ragged ones, over cached prefixes that end
+    inside a page and inside a key block, next to two-token portions and decode tokens."""
+    from prefixserve_b200 import ops
+    from prefixserve_b200.ops import library, tensorcore
+    monkeypatch.setattr(tensorcore, "TCGEN05_PREFILL_MIN_TOKENS", 2)
+    lens_old = [0, 200, 1000, 77, 3, 640, 0]
+    lens_new = [300, 513, 256, 2, 129, 1, 128]
+    table, seqs, num_pages = _paged_setup(torch.bfloat16, lens_new, lens_old, hq, hkv, d, page, seed=5)
+    totals = [o + n for o, n in zip(lens_old, lens_new)]
+    kv = _fill_pages(seqs, table, totals, hkv, d, page, num_pages)
+    batch = _Batch(lens_old, lens_new)
+    q = torch.cat([s["q"][o:] for s, o in zip(seqs, lens_old)]).to(torch.bfloat16).to(DEV)
+    positions = torch.cat([torch.arange(o, o + n) for o, n in zip(lens_old, lens_new)]).to(torch.int32).to(DEV)
+    token_item = torch.cat([torch.full((n,), i) for i, n in enumerate(lens_new)]).to(torch.int32).to(DEV)
+    out = ops.attention(q, kv, table.to(DEV), positions, token_item, window=window, ctx=batch)
+    assert library.tcgen05_status() == 0, "a bounded wait in the kernel gave up"
+    at = 0
+    for i, (s, o, n) in enumerate(zip(seqs, lens_old, lens_new)):
+        bf = lambda x: x.to(torch.bfloat16).float()  # noqa: E731
+        want = plain_model.causal_attention(bf(s["q"]), bf(s["k"]), bf(s["v"]), window=window)[o:].reshape(n, hq * d)
+        got = out[at:at + n].float().cpu()
+        assert torch.isfinite(got).all(), f"item {i}: read an unwritten slot"
+        assert torch.allclose(got, want, atol=2e-2, rtol=2e-2), f"item {i}: {(got - want).abs().max()}"
+        at += n
+
+
+def test_attention_prefill_tcgen05_every_row_finds_its_own_key():
+    """600 new rows over 1,500 cached keys; each row has one key, anywhere before it, that must win."""
+    from prefixserve_b200 import ops
+    from prefixserve_b200.ops import library
+    hq, hkv, d, page, n_ctx, old = 4, 2, 64, 16, 2100, 1500
+    g = torch.Generator().manual_seed(1)
+    k = torch.randn(n_ctx, hkv, d, generator=g) * 0.1
+    v = torch.randn(n_ctx, hkv, d, generator=g)
+    q = torch.randn(n_ctx, hq, d, generator=g) * 0.1
+    for row in range(old, n_ctx):
+        key = (row * 7919) % (row + 1)
+        q[row, :, row % d] = 30.0
+        k[key, :, row % d] += 30.0
+    pages = -(-n_ctx // page)
+    table = torch.randperm(pages + 7, generator=g)[:pages].to(torch.int32)[None, :]
+    kv = _fill_pages([dict(k=k, v=v)], table, [n_ctx], hkv, d, page, pages + 7)
+    bf = lambda x: x.to(torch.bfloat16).float()  # noqa: E731
+    want = plain_model.causal_attention(bf(q), bf(k), bf(v)).reshape(n_ctx, hq * d)
+    new = n_ctx - old
+    out = ops.attention(q[old:].to(torch.bfloat16).to(DEV), kv, table.to(DEV), torch.arange(old, n_ctx, dtype=torch.int32, device=DEV),
+                        torch.zeros(new, dtype=torch.int32, device=DEV), ctx=_Batch([old], [new]))
+    assert library.tcgen05_status() == 0
+    assert torch.allclose(out.float().cpu(), want[old:], atol=3e-2, rtol=3e-2)
+
+
 def test_attention_shapes_outside_the_tensor_core_kernels_fall_back():
     from prefixserve_b200.ops.tensorcore import attention_bf16_supported
     assert attention_bf16_supported(64, 16) and attention_bf16_supported(128, 64)
