@@ -1,15 +1,17 @@
 // Causal grouped-query attention of prompt portions over the paged cache on the 5th-generation tensor cores.
 //
 // One CTA owns up to 256 consecutive new tokens of one request for one query head, as two tiles of 128 rows, and walks
-// the keys they may see in blocks of KB keys (128 for a head size of 64, 64 for 128).  320 threads:
+// the keys they may see in blocks of KB keys (128 for a head size of 64, 64 for 128).  576 threads:
 //   warp 0      producer: TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle) of the two Q tiles once, and per block of
 //               the pages that hold its keys and values, one box per page, into rings of three stages each;
 //   warp 1      MMA: one lane issues tcgen05.mma (cta_group::1, kind::f16, M=128):  S = Q K^T  (A and B K-major, N=KB)
-//               into tensor memory, and  O_block = P V  (A = P K-major from shared memory, B = V MN-major exactly as the
+//               into tensor memory, and  O += P V  (A = P from tensor memory, B = V MN-major exactly as the
 //               cache stores it: keys x head dim, N = head dim);
-//   warps 2..5  softmax of tile 0, warps 6..9 of tile 1: one thread per row.  tcgen05.ld of the row of S, masks, running
-//               maximum and sum in float32, P as bfloat16 into swizzled shared memory, then tcgen05.ld of O_block,
-//               which is added into the row's float32 accumulator in registers scaled by exp(old max - new max).
+//   warps 2..9  softmax of tile 0, warps 10..17 of tile 1: two threads per row, each with half of the block's keys.
+//               tcgen05.ld of the row of S, masks, maximum (agreed between the two through shared memory) and sum in
+//               float32, P as bfloat16 into tensor memory over the scores it came from.  O accumulates in tensor memory over
+//               the blocks; the row's reference maximum only follows the true one when that has grown by more than
+//               2^8, and only then is the row of O rescaled (tcgen05.ld, multiply, tcgen05.st), which is rare.
 // The two tiles alternate on the tensor cores: while one tile's rows are in the softmax, the other's products run.
 // Rows are [token, head*D] of the rotated queries (prefixserve/model/llama.py:113-116 of PrefixServe computes the same
 // attention with a library kernel, prefixserve/model/attention.py:58-104); keys and values come from the pages named
@@ -25,7 +27,7 @@ using namespace tc;
 constexpr int TILE_M = 128;
 constexpr int TILES = 2;
 constexpr int ROWS_PER_CTA = TILE_M * TILES;
-constexpr int THREADS = 32 * (2 + 4 * TILES);
+constexpr int THREADS = 32 * (2 + 8 * TILES);  // producer, MMA, and two softmax threads per row
 constexpr int STAGES = 3;
 constexpr int TMEM_COLS = 512;
 constexpr float LOG2E_F = 1.4426950408889634f;
@@ -38,22 +40,22 @@ struct Shape {
   static constexpr int Q_SUB_BYTES = TILE_M * 128;        // one [128 x 64] sub-tile
   static constexpr int KV_STAGE_BYTES = KB * D * 2;
   static constexpr int KV_SUB_BYTES = KB * 128;           // one [KB x 64] sub-tile
-  static constexpr int P_TILE_BYTES = TILE_M * KB * 2;
   static constexpr int Q_OFF = 0;
   static constexpr int K_OFF = Q_OFF + TILES * Q_TILE_BYTES;
   static constexpr int V_OFF = K_OFF + STAGES * KV_STAGE_BYTES;
-  static constexpr int P_OFF = V_OFF + STAGES * KV_STAGE_BYTES;
-  static constexpr int BAR_OFF = P_OFF + TILES * P_TILE_BYTES;
-  static constexpr int S_COL = 0;                         // S of tile t: columns [t*KB, +KB)
-  static constexpr int O_COL = TILES * KB;                // O_block of tile t: columns [O_COL + t*D, +D)
+  static constexpr int BAR_OFF = V_OFF + STAGES * KV_STAGE_BYTES;
+  static constexpr int S_BUFS = 3;                        // S buffers, used in turn by the tiles' blocks
+  static constexpr int S_COL = 0;                         // S buffer j: columns [j*KB, +KB)
+  static constexpr int O_COL = S_BUFS * KB;               // O of tile t: columns [O_COL + t*D, +D)
   static_assert(O_COL + TILES * D <= TMEM_COLS, "tensor memory");
-  static_assert(Q_TILE_BYTES % 1024 == 0 && KV_STAGE_BYTES % 1024 == 0 && P_TILE_BYTES % 1024 == 0, "swizzle atoms");
+  static_assert(Q_TILE_BYTES % 1024 == 0 && KV_STAGE_BYTES % 1024 == 0, "swizzle atoms");
 };
 
 struct Barriers {
   uint64_t q_full;
   uint64_t k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
-  uint64_t s_full[TILES], p_ready[TILES], o_full[TILES];
+  uint64_t s_full[3], p_ready[TILES], o_full[TILES], row_max[TILES];
+  float exchange[2][TILES][2][TILE_M];  // [block parity][tile][half of the row][row]: maxima, at the end sums
   uint32_t tmem_base;
   uint32_t abort;
 };
@@ -80,7 +82,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   Barriers* bars = reinterpret_cast<Barriers*>(smem + Sh::BAR_OFF);
   volatile uint32_t* abort = &bars->abort;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = uniform_warp_index(), lane = threadIdx.x & 31;  // the warp's role is the same for all its lanes
 
   pdl_trigger();
   // which request and which 256 rows of it?  (lengths are inputs of the step: readable before the wait)
@@ -106,9 +108,10 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       mbar_init(&bars->v_full[s], 1);
       mbar_init(&bars->v_empty[s], 1);
     }
+    for (int j = 0; j < 3; ++j) mbar_init(&bars->s_full[j], 1);
     for (int t = 0; t < TILES; ++t) {
-      mbar_init(&bars->s_full[t], 1);
-      mbar_init(&bars->p_ready[t], TILE_M);  // every softmax thread of the tile arrives
+      mbar_init(&bars->p_ready[t], 8);  // one arrival per softmax warp of the tile (arrivals on one barrier serialise)
+      mbar_init(&bars->row_max[t], 8);
       mbar_init(&bars->o_full[t], 1);
     }
     bars->abort = 0;
@@ -137,6 +140,12 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const int b0 = lo_key / KB;
   const int nblk = bend[ntiles - 1] - b0 + 1;
   const int kvh = head / (hq / hkv);
+  // The tiles' blocks in the order their S is computed: (0,0) (1,0) (0,1) (1,1) ... while tile 0 still has blocks (n0 of
+  // them), then tile 1's remaining ones.  The e-th of them uses S buffer e % 3, so S of a block is computed while the
+  // softmax of the two blocks before it is still running.
+  const int n0 = bend[0] - b0 + 1;
+  const int total = ntiles == 2 ? n0 + nblk : n0;
+  auto seq_of = [&](int t, int i) { return ntiles == 1 ? i : (i < n0 ? 2 * i + t : n0 + i); };
 
   pdl_wait();  // queries and this step's keys and values are the preceding kernel's output
 
@@ -185,89 +194,103 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     }
   } else if (warp == 1) {
     // --------------------------------------------------------------------------------------------------- MMA
-    // All lanes follow the barriers; lane 0 issues.  The others only work on the block that holds the request's last
+    // All lanes follow the barriers; an elected lane issues each instruction (tcgen05.cuh says why).  All of them work on
+    // the block that holds the request's last
     // key: value rows behind it were never written by this request, and 0 x (whatever an earlier owner of the page
     // left there) must be 0, so those rows are cleared in shared memory before P V runs.
-    const bool issuer = lane == 0;
     constexpr uint32_t IDESC_S = instr_desc(TILE_M, KB, false);
     constexpr uint32_t IDESC_O = instr_desc(TILE_M, D, true);
-    const uint32_t q_addr = smem_u32(smem + Sh::Q_OFF), k_addr = smem_u32(smem + Sh::K_OFF);
-    const uint32_t v_addr = smem_u32(smem + Sh::V_OFF), p_addr = smem_u32(smem + Sh::P_OFF);
-    auto issue_s = [&](int t, uint32_t ks) {
-      const uint32_t a = q_addr + t * Sh::Q_TILE_BYTES, bk = k_addr + ks * Sh::KV_STAGE_BYTES;
+    // descriptors: low words (address field in 16-byte units, leading byte offset) of the operands' first tiles; the high
+    // word is the same for all of them
+    const uint64_t d_q = smem_desc(smem_u32(smem + Sh::Q_OFF)), d_k = smem_desc(smem_u32(smem + Sh::K_OFF));
+    const uint64_t d_v = smem_desc_mn(smem_u32(smem + Sh::V_OFF), Sh::KV_SUB_BYTES);
+    const uint32_t hi = (uint32_t)(d_q >> 32);  // stride byte offset, version, swizzle: equal in all three
+    const uint32_t q_lo = (uint32_t)d_q, k_lo = (uint32_t)d_k, v_lo = (uint32_t)d_v;
+    auto issue_s = [&](int t, uint32_t ks, int buf) {
+      const uint32_t a = q_lo + t * (Sh::Q_TILE_BYTES >> 4), bk = k_lo + ks * (Sh::KV_STAGE_BYTES >> 4);
+      const uint32_t dst = tmem_base + Sh::S_COL + buf * KB;
 #pragma unroll
       for (int j = 0; j < Sh::DS; ++j)
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          mma_f16(tmem_base + Sh::S_COL + t * KB, smem_desc(a + j * Sh::Q_SUB_BYTES + k * 32),
-                  smem_desc(bk + j * Sh::KV_SUB_BYTES + k * 32), IDESC_S, (j | k) != 0);
+          if (elect_one())
+            mma_f16_split(dst, a + ((j * Sh::Q_SUB_BYTES + k * 32) >> 4), hi, bk + ((j * Sh::KV_SUB_BYTES + k * 32) >> 4), hi, IDESC_S,
+                          (j | k) != 0);
     };
-    auto issue_pv = [&](int t, uint32_t vs) {
-      const uint32_t a = p_addr + t * Sh::P_TILE_BYTES, bv = v_addr + vs * Sh::KV_STAGE_BYTES;
+    // P of a block lies in the S buffer it was computed from: the 32 keys [32c, +32) of the block as 16 columns of two
+    // bfloat16 at columns [32c, +16) (see the softmax warps); one MMA takes 16 keys, 8 columns
+    auto issue_pv = [&](int t, uint32_t vs, int buf, int accumulate) {
+      const uint32_t bv = v_lo + vs * (Sh::KV_STAGE_BYTES >> 4);
+      const uint32_t dst = tmem_base + Sh::O_COL + t * D, src = tmem_base + Sh::S_COL + buf * KB;
+      if (elect_one()) {
 #pragma unroll
-      for (int kk = 0; kk < KB / 16; ++kk)
-        mma_f16(tmem_base + Sh::O_COL + t * D, smem_desc(a + (kk >> 2) * Sh::Q_SUB_BYTES + (kk & 3) * 32),
-                smem_desc_mn(bv + kk * 2048, Sh::KV_SUB_BYTES), IDESC_O, kk != 0);
+        for (int kk = 0; kk < KB / 16; ++kk)
+          mma_f16_tmem_a(dst, src + (kk >> 1) * 32 + (kk & 1) * 8, bv + ((kk * 2048) >> 4), hi, IDESC_O, (accumulate | kk) != 0);
+      }
+      __syncwarp();
     };
-    uint32_t ks = 0, kph = 0, vs = 0, vph = 0;
-    bool ok = mbar_wait(&bars->q_full, 0, abort, 2) && mbar_wait(&bars->k_full[0], 0, abort, 2);
+    bool ok = mbar_wait(&bars->q_full, 0, abort, 2);
     ok = __all_sync(0xffffffffu, ok);
-    if (ok) {
-      fence_after();
-      if (issuer) {
-        for (int t = 0; t < ntiles; ++t) {
-          issue_s(t, 0);
-          mma_commit(&bars->s_full[t]);
-        }
-        mma_commit(&bars->k_empty[0]);
-      }
-      ks = 1;
-    }
-    for (int i = 0; ok && i < nblk; ++i) {
-      const int b = b0 + i;
-      const bool next = i + 1 < nblk;
-      ok = mbar_wait(&bars->v_full[vs], vph, abort, 2);
-      if (ok && next) ok = mbar_wait(&bars->k_full[ks], kph, abort, 2);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      const int written = kvl - b * KB;  // rows of this block that hold the request's values
-      if (written < KB) {
-        unsigned char* stage = smem + Sh::V_OFF + vs * Sh::KV_STAGE_BYTES;
-        const int first = written > 0 ? written : 0;
-        for (int idx = first * 8 * Sh::DS + lane; idx < KB * 8 * Sh::DS; idx += 32) {
-          const int row = idx / (8 * Sh::DS), rest = idx % (8 * Sh::DS);
-          *reinterpret_cast<uint4*>(stage + (rest >> 3) * Sh::KV_SUB_BYTES + row * 128 + (rest & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
-        }
-        fence_async_smem();
-        __syncwarp();
+    int k_seen = 0, v_seen = 0;  // blocks (from b0) whose keys / values have been waited for
+    auto s_of = [&](int e) {     // computes S of the e-th (tile, block); false if a wait gave up
+      const int t = ntiles == 1 ? 0 : (e < 2 * n0 ? (e & 1) : 1);
+      const int i = ntiles == 1 ? e : (e < 2 * n0 ? (e >> 1) : e - n0);
+      while (k_seen <= i) {
+        bool got = mbar_wait(&bars->k_full[k_seen % STAGES], (k_seen / STAGES) & 1, abort, 2);
+        got = __all_sync(0xffffffffu, got);
+        if (!got) return false;
+        ++k_seen;
       }
       fence_after();
-      for (int t = 0; t < ntiles; ++t) {
-        if (b > bend[t]) continue;
-        ok = mbar_wait(&bars->p_ready[t], i & 1, abort, 2);
+      issue_s(t, i % STAGES, e % 3);
+      if (elect_one()) {
+        mma_commit(&bars->s_full[e % 3]);
+        if (t == ntiles - 1) mma_commit(&bars->k_empty[i % STAGES]);  // the last tile to use this block's keys
+      }
+      __syncwarp();
+      return true;
+    };
+    for (int e = 0; ok && e < 3 && e < total; ++e) ok = s_of(e);
+    for (int e = 0; ok && e < total; ++e) {
+      const int t = ntiles == 1 ? 0 : (e < 2 * n0 ? (e & 1) : 1);
+      const int i = ntiles == 1 ? e : (e < 2 * n0 ? (e >> 1) : e - n0);
+      while (ok && v_seen <= i) {
+        ok = mbar_wait(&bars->v_full[v_seen % STAGES], (v_seen / STAGES) & 1, abort, 2);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        fence_after();
-        if (issuer) {
-          issue_pv(t, vs);
-          mma_commit(&bars->o_full[t]);
-          if (next && b + 1 <= bend[t]) {
-            issue_s(t, ks);
-            mma_commit(&bars->s_full[t]);
+        const int written = kvl - (b0 + v_seen) * KB;  // rows of this block that hold the request's values
+        if (written < KB) {
+          unsigned char* stage = smem + Sh::V_OFF + (v_seen % STAGES) * Sh::KV_STAGE_BYTES;
+          const int first = written > 0 ? written : 0;
+          for (int idx = first * 8 * Sh::DS + lane; idx < KB * 8 * Sh::DS; idx += 32) {
+            const int row = idx / (8 * Sh::DS), rest = idx % (8 * Sh::DS);
+            *reinterpret_cast<uint4*>(stage + (rest >> 3) * Sh::KV_SUB_BYTES + row * 128 + (rest & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
           }
+          fence_async_smem();
+          __syncwarp();
         }
+        ++v_seen;
       }
       if (!ok) break;
-      if (issuer) mma_commit(&bars->v_empty[vs]);
-      if (++vs == STAGES) { vs = 0; vph ^= 1; }
-      if (next) {
-        if (issuer) mma_commit(&bars->k_empty[ks]);
-        if (++ks == STAGES) { ks = 0; kph ^= 1; }
+      ok = mbar_wait(&bars->p_ready[t], i & 1, abort, 2);  // P of this block is written (over its S)
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      fence_after();
+      issue_pv(t, i % STAGES, e % 3, i);
+      if (elect_one()) {
+        mma_commit(&bars->o_full[t]);
+        if (t == ntiles - 1) mma_commit(&bars->v_empty[i % STAGES]);
       }
+      __syncwarp();
+      if (e + 3 < total) ok = s_of(e + 3);
     }
   } else {
     // ----------------------------------------------------------------------------------------------- softmax
-    const int t = (warp - 2) >> 2;
+    // Two threads per row (one in each of two warps that share a tensor-memory lane quarter): each owns half of the
+    // row's keys of a block and half of the head dim of O.  They agree on the row's maximum through shared memory.
+    constexpr int HC = KB / 2, HD = D / 2;
+    const int sw = warp - 2;
+    const int t = sw >> 3, half = (sw >> 2) & 1;
     const int quarter = warp & 3;  // a warp may only touch tensor-memory lanes [32*(warp%4), +32)
     const int r = quarter * 32 + lane;
     if (t < ntiles) {
@@ -278,98 +301,143 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       const bool partial = row0 + TILE_M * (t + 1) > n;
       const float c = scale * LOG2E_F;
       const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-      const uint32_t s_addr = lane_addr + Sh::S_COL + t * KB, o_addr = lane_addr + Sh::O_COL + t * D;
-      unsigned char* p_row = smem + Sh::P_OFF + t * Sh::P_TILE_BYTES + r * 128;
-      float o[D];
-#pragma unroll
-      for (int d = 0; d < D; ++d) o[d] = 0.f;
+      const uint32_t o_addr = lane_addr + Sh::O_COL + t * D + half * HD;
+      float* mine = &bars->exchange[0][t][half][r];
+      const float* theirs = &bars->exchange[0][t][half ^ 1][r];
+      constexpr int XCH = TILES * 2 * TILE_M;            // floats per parity of the exchange buffer
+      // m_run is the maximum the row's exponentials refer to.  It follows the true maximum only when that has grown by
+      // more than 2^8 (in the exponent), so that the accumulator in tensor memory is rescaled rarely; sums and
+      // products use the same reference, and the quotient at the end does not depend on it.
       float m_run = -INFINITY, l_run = 0.f;
       bool ok = true;
       const int my_blocks = bend[t] - b0 + 1;
       for (int i = 0; i < my_blocks; ++i) {
-        const int key0 = (b0 + i) * KB;
-        ok = mbar_wait(&bars->s_full[t], i & 1, abort, 3);
+        const int key0 = (b0 + i) * KB + half * HC;
+        const int e = seq_of(t, i);
+        ok = mbar_wait(&bars->s_full[e % 3], (e / 3) & 1, abort, 3);
+        ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         fence_after();
-        const bool need_mask = partial || key0 + KB - 1 > p_first[t] || (window > 0 && key0 < p_last[t] - window + 1);
-        // pass 1: the row's maximum over this block
-        float mx = -INFINITY;
-#pragma unroll 1
-        for (int cc = 0; cc < KB / 32; ++cc) {
-          uint32_t v[32];
-          tmem_ld32(s_addr + cc * 32, v);
+        const uint32_t s_addr = lane_addr + Sh::S_COL + (e % 3) * KB + half * HC;
+        const bool need_mask = partial || key0 + HC - 1 > p_first[t] || (window > 0 && key0 < p_last[t] - window + 1);
+        // 32 keys at a time: the maximum first, over all of this thread's keys; the last chunk stays in registers
+        // and the others are read from tensor memory again for the exponentials
+        constexpr int NCH = HC / 32;
+        float sv[32];
+        auto load_chunk = [&](int cc) {
+          tmem_ld32(s_addr + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
           tmem_ld_wait();
           if (need_mask) {
 #pragma unroll
             for (int e = 0; e < 32; ++e) {
               const int key = key0 + cc * 32 + e;
-              if (key <= pr && key >= lo_r) mx = fmaxf(mx, __uint_as_float(v[e]));
+              if (key > pr || key < lo_r) sv[e] = -INFINITY;
             }
-          } else {
+          }
+        };
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-            for (int e = 0; e < 32; e += 2) mx = fmaxf(mx, fmaxf(__uint_as_float(v[e]), __uint_as_float(v[e + 1])));
+        for (int cc = 0; cc < NCH; ++cc) {
+          load_chunk(cc);
+#pragma unroll
+          for (int e = 0; e < 32; e += 4) {
+            mx0 = fmaxf(mx0, sv[e]); mx1 = fmaxf(mx1, sv[e + 1]); mx2 = fmaxf(mx2, sv[e + 2]); mx3 = fmaxf(mx3, sv[e + 3]);
           }
         }
-        const float m_new = fmaxf(m_run, mx);
-        const float m_ref = m_new == -INFINITY ? 0.f : m_new;   // a row that has seen nothing yet
-        const float alpha = ex2((m_run - m_ref) * c);           // 0 while m_run is -inf
-        const float mc = m_ref * c;
-        // pass 2: P = exp(S - max) as bfloat16 into the swizzled operand tile, and its sum
-        float sum = 0.f;
-#pragma unroll 1
-        for (int cc = 0; cc < KB / 32; ++cc) {
-          uint32_t v[32];
-          tmem_ld32(s_addr + cc * 32, v);
-          tmem_ld_wait();
-          float p[32];
-          if (need_mask) {
-#pragma unroll
-            for (int e = 0; e < 32; ++e) {
-              const int key = key0 + cc * 32 + e;
-              p[e] = (key <= pr && key >= lo_r) ? ex2(fmaf(__uint_as_float(v[e]), c, -mc)) : 0.f;
-            }
-          } else {
-#pragma unroll
-            for (int e = 0; e < 32; ++e) p[e] = ex2(fmaf(__uint_as_float(v[e]), c, -mc));
-          }
-#pragma unroll
-          for (int e = 0; e < 32; ++e) sum += p[e];
-          // keys [cc*32, +32) of the block: sub-tile (cc*32)/64, 16-byte chunks (cc*32 % 64)/8 .. +4 of the 128-byte row
-          unsigned char* sub = p_row + ((cc * 32) >> 6) * Sh::Q_SUB_BYTES;
-          const int chunk0 = ((cc * 32) & 63) >> 3;
-#pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            const uint4 packed = make_uint4(pack2(p[q4 * 8 + 0], p[q4 * 8 + 1]), pack2(p[q4 * 8 + 2], p[q4 * 8 + 3]),
-                                            pack2(p[q4 * 8 + 4], p[q4 * 8 + 5]), pack2(p[q4 * 8 + 6], p[q4 * 8 + 7]));
-            *reinterpret_cast<uint4*>(sub + (((chunk0 + q4) ^ (r & 7)) << 4)) = packed;
-          }
-        }
-        l_run = l_run * alpha + sum;
-        m_run = m_new;
-        fence_async_smem();   // P is read by the tensor cores
-        fence_before();       // S has been read
-        mbar_arrive(&bars->p_ready[t]);
-        // O_block = P V of this block, added into the row's accumulator
-        ok = mbar_wait(&bars->o_full[t], i & 1, abort, 3);
+        float m_new = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        mine[(i & 1) * XCH] = m_new;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->row_max[t]);
+        ok = mbar_wait(&bars->row_max[t], i & 1, abort, 3);
+        ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        fence_after();
+        m_new = fmaxf(m_new, theirs[(i & 1) * XCH]);
+        const bool grow = (m_new - m_run) * c > 8.f;  // false while the row has seen nothing (-inf - -inf)
+        // Each phase of o_full (P V of this tile's block i-1 has finished) is waited for exactly once, during block i:
+        // a parity wait can only tell the phase in progress from the one before it.  Early if O has to be rescaled,
+        // otherwise at the end of the block, when it has long completed.
+        bool waited = i == 0;
+        if (__any_sync(0xffffffffu, grow)) {
+          // tensor-memory loads and stores are warp-wide: every lane takes part, with a factor of 1 where nothing grew
+          const float alpha = grow ? ex2((m_run - m_new) * c) : 1.f;  // 0 from -inf
+          if (grow) { m_run = m_new; l_run *= alpha; }
+          if (i > 0) {
+            ok = mbar_wait(&bars->o_full[t], (i - 1) & 1, abort, 3);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            waited = true;
+            fence_after();
+#pragma unroll 1
+            for (int cc = 0; cc < HD / 32; ++cc) {
+              uint32_t v[32];
+              tmem_ld32(o_addr + cc * 32, v);
+              tmem_ld_wait();
 #pragma unroll
-        for (int cc = 0; cc < D / 32; ++cc) {
+              for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * alpha);
+              tmem_st32(o_addr + cc * 32, v);
+            }
+            tmem_st_wait();
+          }
+        }
+        const float mc = (m_run == -INFINITY ? 0.f : m_run) * c;
+        // P as bfloat16 over the S it came from: keys [32c, +32) of this thread's half become 16 columns at the start of
+        // the 32 columns their scores occupied (the chunk is in registers by then, and nobody else reads those columns)
+        float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+        for (int cc = NCH - 1; cc >= 0; --cc) {
+          if (cc != NCH - 1) load_chunk(cc);
+          uint32_t packed[16];
+#pragma unroll
+          for (int e2 = 0; e2 < 32; e2 += 2) {
+            const float p0 = ex2(fmaf(sv[e2], c, -mc));          // masked entries are -inf: 0
+            const float p1 = ex2(fmaf(sv[e2 + 1], c, -mc));
+            sum0 += p0;
+            sum1 += p1;
+            packed[e2 >> 1] = pack2(p0, p1);
+          }
+          tmem_st16(s_addr + cc * 32, packed);
+        }
+        tmem_st_wait();
+        l_run += sum0 + sum1;
+        if (!waited) {
+          ok = mbar_wait(&bars->o_full[t], (i - 1) & 1, abort, 3);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+        }
+        fence_before();       // P written, O rescaled
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->p_ready[t]);
+      }
+      // the quotient: the two halves of a row add up their sums, then each scales its half of O
+      if (ok) {
+        mine[(my_blocks & 1) * XCH] = l_run;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->row_max[t]);
+        ok = mbar_wait(&bars->row_max[t], my_blocks & 1, abort, 3);
+        if (ok) ok = mbar_wait(&bars->o_full[t], (my_blocks - 1) & 1, abort, 3);
+        ok = __all_sync(0xffffffffu, ok);
+      }
+      if (ok) {
+        fence_after();
+        const float l_row = l_run + theirs[(my_blocks & 1) * XCH];
+        const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
+        __nv_bfloat16* dst = out + ((size_t)(t0 + row) * hq + head) * D + half * HD;
+#pragma unroll 1
+        for (int cc = 0; cc < HD / 32; ++cc) {
           uint32_t v[32];
           tmem_ld32(o_addr + cc * 32, v);
           tmem_ld_wait();
+          if (valid) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) o[cc * 32 + e] = fmaf(o[cc * 32 + e], alpha, __uint_as_float(v[e]));
+            for (int e = 0; e < 32; e += 8)
+              *reinterpret_cast<uint4*>(dst + cc * 32 + e) =
+                  make_uint4(pack2(__uint_as_float(v[e]) * inv, __uint_as_float(v[e + 1]) * inv),
+                             pack2(__uint_as_float(v[e + 2]) * inv, __uint_as_float(v[e + 3]) * inv),
+                             pack2(__uint_as_float(v[e + 4]) * inv, __uint_as_float(v[e + 5]) * inv),
+                             pack2(__uint_as_float(v[e + 6]) * inv, __uint_as_float(v[e + 7]) * inv));
+          }
         }
         fence_before();
-      }
-      if (ok && valid) {
-        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-        __nv_bfloat16* dst = out + ((size_t)(t0 + row) * hq + head) * D;
-#pragma unroll
-        for (int d = 0; d < D; d += 8)
-          *reinterpret_cast<uint4*>(dst + d) = make_uint4(pack2(o[d] * inv, o[d + 1] * inv), pack2(o[d + 2] * inv, o[d + 3] * inv),
-                                                          pack2(o[d + 4] * inv, o[d + 5] * inv), pack2(o[d + 6] * inv, o[d + 7] * inv));
       }
     }
   }

@@ -56,7 +56,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   Barriers* bars = reinterpret_cast<Barriers*>(tiles + STAGES * STAGE_BYTES);
   volatile uint32_t* abort = &bars->abort;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = uniform_warp_index(), lane = threadIdx.x & 31;  // the warp's role is the same for all its lanes
 
   const int n_span = gated ? BN_HALF : BN;  // output columns one tile covers
   const int m_blocks = (M + BM - 1) / BM;
@@ -88,7 +88,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
-    if (lane == 0) {
+    if (elect_one()) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < tiles_total; tile += gridDim.x) {
@@ -110,30 +110,35 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
   } else if (warp == 1) {
     // ----------------------------------------------------------------------- MMA
-    if (lane == 0) {
+    // The whole warp runs this loop and waits on the barriers; each tensor-core instruction is issued by one elected
+    // lane (tcgen05.cuh says why).
+    {
       uint32_t stage = 0, phase = 0, local = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < tiles_total; tile += gridDim.x, ++local) {
         const uint32_t buf = local & 1, use = local >> 1;  // accumulator buffer and how often it has been used
         ok = mbar_wait(&bars->acc_empty[buf], (use & 1) ^ 1, abort, 4);
+        ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         fence_after();
         const uint32_t acc = tmem_base + buf * BN;
         for (int kb = 0; kb < k_blocks; ++kb) {
           ok = mbar_wait(&bars->full[stage], phase, abort, 2);
+          ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           fence_after();
-          const uint32_t a_addr = smem_u32(tiles + stage * STAGE_BYTES);
-          const uint32_t b_addr = a_addr + A_BYTES;
+          const uint64_t da = smem_desc(smem_u32(tiles + stage * STAGE_BYTES));
+          const uint64_t db = smem_desc(smem_u32(tiles + stage * STAGE_BYTES + A_BYTES));
+          const uint32_t hi = (uint32_t)(da >> 32), a_lo = (uint32_t)da, b_lo = (uint32_t)db;
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
-            // 16 elements = 32 bytes further along K inside the swizzled 128-byte rows
-            mma_f16(acc, smem_desc(a_addr + k * 32), smem_desc(b_addr + k * 32), INSTR_DESC, (kb | k) != 0);
+            // 16 elements = 32 bytes further along K inside the swizzled 128-byte rows: 2 in the address field
+            if (elect_one()) mma_f16_split(acc, a_lo + 2 * k, hi, b_lo + 2 * k, hi, INSTR_DESC, (kb | k) != 0);
           }
-          mma_commit(&bars->empty[stage]);  // arrives when the MMAs that read this stage are done
+          if (elect_one()) mma_commit(&bars->empty[stage]);  // arrives when the MMAs that read this stage are done
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
-        if (ok) mma_commit(&bars->acc_full[buf]);
+        if (ok && elect_one()) mma_commit(&bars->acc_full[buf]);
       }
     }
   } else {
