@@ -3,7 +3,7 @@
 // One CTA owns up to 256 consecutive new tokens of one request for one query head, as two tiles of 128 rows, and walks
 // the keys they may see in blocks of KB keys (128 for a head size of 64, 64 for 128).  576 threads:
 //   warp 0      producer: TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle) of the two Q tiles once, and per block of
-//               the pages that hold its keys and values, one box per page, into rings of three stages each;
+//               the pages that hold its keys and values, one box per page, into a ring of four stages;
 //   warp 1      MMA: one lane issues tcgen05.mma (cta_group::1, kind::f16, M=128):  S = Q K^T  (A and B K-major, N=KB)
 //               into tensor memory, and  O += P V  (A = P from tensor memory, B = V MN-major exactly as the
 //               cache stores it: keys x head dim, N = head dim);
@@ -28,7 +28,7 @@ constexpr int TILE_M = 128;
 constexpr int TILES = 2;
 constexpr int ROWS_PER_CTA = TILE_M * TILES;
 constexpr int THREADS = 32 * (2 + 8 * TILES);  // producer, MMA, and two softmax threads per row
-constexpr int STAGES = 3;
+constexpr int STAGES = 4;  // blocks of keys and values in shared memory at a time: S runs up to three blocks ahead of P V
 constexpr int TMEM_COLS = 512;
 constexpr float LOG2E_F = 1.4426950408889634f;
 
@@ -53,7 +53,7 @@ struct Shape {
 
 struct Barriers {
   uint64_t q_full;
-  uint64_t k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
+  uint64_t k_full[STAGES], v_full[STAGES], kv_empty[STAGES];
   uint64_t s_full[3], p_ready[TILES], o_full[TILES], row_max[TILES];
   float exchange[2][TILES][2][TILE_M];  // [block parity][tile][half of the row][row]: maxima, at the end sums
   uint32_t tmem_base;
@@ -104,9 +104,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     mbar_init(&bars->q_full, 1);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&bars->k_full[s], 1);
-      mbar_init(&bars->k_empty[s], 1);
       mbar_init(&bars->v_full[s], 1);
-      mbar_init(&bars->v_empty[s], 1);
+      mbar_init(&bars->kv_empty[s], 1);
     }
     for (int j = 0; j < 3; ++j) mbar_init(&bars->s_full[j], 1);
     for (int t = 0; t < TILES; ++t) {
@@ -175,19 +174,21 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         row_k = ((pid * 2) * hkv + kvh) * page;
       }
       const int row_v = row_k + hkv * page;
+      ok = mbar_wait(&bars->kv_empty[stage], phase ^ 1, abort, 1);  // P V of the block that used this stage has finished
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      if (lane == 0) {
+        mbar_expect_tx(&bars->k_full[stage], (uint32_t)Sh::KV_STAGE_BYTES);
+        mbar_expect_tx(&bars->v_full[stage], (uint32_t)Sh::KV_STAGE_BYTES);
+      }
+      __syncwarp();
+      if (lane < pages_per_block) {
 #pragma unroll
-      for (int which = 0; which < 2; ++which) {
-        uint64_t* empty = which ? &bars->v_empty[stage] : &bars->k_empty[stage];
-        uint64_t* full = which ? &bars->v_full[stage] : &bars->k_full[stage];
-        ok = mbar_wait(empty, phase ^ 1, abort, 1);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        if (lane == 0) mbar_expect_tx(full, (uint32_t)Sh::KV_STAGE_BYTES);
-        __syncwarp();
-        if (lane < pages_per_block) {
+        for (int which = 0; which < 2; ++which) {
           unsigned char* dst = smem + (which ? Sh::V_OFF : Sh::K_OFF) + stage * Sh::KV_STAGE_BYTES + lane * page * 128;
 #pragma unroll
-          for (int j = 0; j < Sh::DS; ++j) tma_load_2d(dst + j * Sh::KV_SUB_BYTES, &map_kv, 64 * j, which ? row_v : row_k, full);
+          for (int j = 0; j < Sh::DS; ++j)
+            tma_load_2d(dst + j * Sh::KV_SUB_BYTES, &map_kv, 64 * j, which ? row_v : row_k, which ? &bars->v_full[stage] : &bars->k_full[stage]);
         }
       }
       if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -213,47 +214,42 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       for (int j = 0; j < Sh::DS; ++j)
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          if (elect_one())
-            mma_f16_split(dst, a + ((j * Sh::Q_SUB_BYTES + k * 32) >> 4), hi, bk + ((j * Sh::KV_SUB_BYTES + k * 32) >> 4), hi, IDESC_S,
-                          (j | k) != 0);
+          mma_f16_split(dst, a + ((j * Sh::Q_SUB_BYTES + k * 32) >> 4), hi, bk + ((j * Sh::KV_SUB_BYTES + k * 32) >> 4), hi, IDESC_S,
+                        (j | k) != 0);
     };
     // P of a block lies in the S buffer it was computed from: the 32 keys [32c, +32) of the block as 16 columns of two
     // bfloat16 at columns [32c, +16) (see the softmax warps); one MMA takes 16 keys, 8 columns
     auto issue_pv = [&](int t, uint32_t vs, int buf, int accumulate) {
       const uint32_t bv = v_lo + vs * (Sh::KV_STAGE_BYTES >> 4);
       const uint32_t dst = tmem_base + Sh::O_COL + t * D, src = tmem_base + Sh::S_COL + buf * KB;
-      if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < KB / 16; ++kk)
-          mma_f16_tmem_a(dst, src + (kk >> 1) * 32 + (kk & 1) * 8, bv + ((kk * 2048) >> 4), hi, IDESC_O, (accumulate | kk) != 0);
-      }
-      __syncwarp();
+      for (int kk = 0; kk < KB / 16; ++kk)
+        mma_f16_tmem_a(dst, src + (kk >> 1) * 32 + (kk & 1) * 8, bv + ((kk * 2048) >> 4), hi, IDESC_O, (accumulate | kk) != 0);
     };
     bool ok = mbar_wait(&bars->q_full, 0, abort, 2);
     ok = __all_sync(0xffffffffu, ok);
     int k_seen = 0, v_seen = 0;  // blocks (from b0) whose keys / values have been waited for
-    auto s_of = [&](int e) {     // computes S of the e-th (tile, block); false if a wait gave up
-      const int t = ntiles == 1 ? 0 : (e < 2 * n0 ? (e & 1) : 1);
-      const int i = ntiles == 1 ? e : (e < 2 * n0 ? (e >> 1) : e - n0);
+    auto tile_of = [&](int e) { return ntiles == 1 ? 0 : (e < 2 * n0 ? (e & 1) : 1); };
+    auto block_of = [&](int e) { return ntiles == 1 ? e : (e < 2 * n0 ? (e >> 1) : e - n0); };
+    auto keys_ready = [&](int i) {  // waits (once) for the keys of every block up to i
       while (k_seen <= i) {
         bool got = mbar_wait(&bars->k_full[k_seen % STAGES], (k_seen / STAGES) & 1, abort, 2);
         got = __all_sync(0xffffffffu, got);
         if (!got) return false;
         ++k_seen;
       }
-      fence_after();
-      issue_s(t, i % STAGES, e % 3);
-      if (elect_one()) {
-        mma_commit(&bars->s_full[e % 3]);
-        if (t == ntiles - 1) mma_commit(&bars->k_empty[i % STAGES]);  // the last tile to use this block's keys
-      }
-      __syncwarp();
       return true;
     };
-    for (int e = 0; ok && e < 3 && e < total; ++e) ok = s_of(e);
+    for (int e = 0; ok && e < 3 && e < total; ++e) {
+      ok = keys_ready(block_of(e));
+      if (ok && elect_one()) {
+        issue_s(tile_of(e), block_of(e) % STAGES, e % 3);
+        mma_commit(&bars->s_full[e % 3]);
+      }
+      __syncwarp();
+    }
     for (int e = 0; ok && e < total; ++e) {
-      const int t = ntiles == 1 ? 0 : (e < 2 * n0 ? (e & 1) : 1);
-      const int i = ntiles == 1 ? e : (e < 2 * n0 ? (e >> 1) : e - n0);
+      const int t = tile_of(e), i = block_of(e);
       while (ok && v_seen <= i) {
         ok = mbar_wait(&bars->v_full[v_seen % STAGES], (v_seen / STAGES) & 1, abort, 2);
         ok = __all_sync(0xffffffffu, ok);
@@ -271,18 +267,23 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         }
         ++v_seen;
       }
+      const bool ahead = e + 3 < total;  // S of the block three steps on goes out together with this P V
+      if (ok && ahead) ok = keys_ready(block_of(e + 3));
       if (!ok) break;
       ok = mbar_wait(&bars->p_ready[t], i & 1, abort, 2);  // P of this block is written (over its S)
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       fence_after();
-      issue_pv(t, i % STAGES, e % 3, i);
       if (elect_one()) {
+        issue_pv(t, i % STAGES, e % 3, i);
         mma_commit(&bars->o_full[t]);
-        if (t == ntiles - 1) mma_commit(&bars->v_empty[i % STAGES]);
+        if (t == ntiles - 1) mma_commit(&bars->kv_empty[i % STAGES]);  // the last tile to use this block
+        if (ahead) {
+          issue_s(tile_of(e + 3), block_of(e + 3) % STAGES, (e + 3) % 3);
+          mma_commit(&bars->s_full[(e + 3) % 3]);
+        }
       }
       __syncwarp();
-      if (e + 3 < total) ok = s_of(e + 3);
     }
   } else {
     // ----------------------------------------------------------------------------------------------- softmax
