@@ -265,22 +265,33 @@ def run_own(args) -> dict:
         t_start = None
         h2d = []
         marks = []
-        while sched.has_work() and e2e_steps < args.steps:
-            batch = sched.schedule_step(PREFILL_TOKENS, args.batch)
+        # the loop of the entry point (LLM.generate): while a step runs, the one after it is scheduled and launched
+        # if that can be done without its tokens; every step's tokens are read back before its commit
+        pending = None
+        while (pending is not None or sched.has_work()) and e2e_steps < args.steps:
+            if pending is None:
+                pending = engine.launch(sched.schedule_step(PREFILL_TOKENS, args.batch))
+                first_h2d = runner.last_h2d_bytes
+            ahead = sched.schedule_ahead(args.batch)
+            following = engine.launch(ahead, feed=pending) if ahead is not None else None
+            batch = pending.batch
             is_decode = all(w.end - w.start == 1 for w in batch.work) and len(batch.work) == args.batch
             if is_decode:
                 decoding += 1
                 if decoding == args.warmup + 1:
                     torch.cuda.synchronize()
                     t_start = time.perf_counter()
-            out = engine.step(batch)
+            out = engine.finish(pending)
             if t_start is not None:
                 produced += len(out)
                 e2e_steps += 1
-                h2d.append(runner.last_h2d_bytes)
+                h2d.append(runner.last_h2d_bytes if following is not None else first_h2d)
             sched.commit(batch, out)
             if t_start is not None:
                 marks.append(time.perf_counter())
+            pending = following
+        if pending is not None:
+            sched.commit(pending.batch, engine.finish(pending))
         torch.cuda.synchronize()
         e2e_s = time.perf_counter() - t_start
         for r in range(args.batch):

@@ -43,6 +43,17 @@ class EngineConfig:
     use_cuda_graphs: bool = True     # capture pure-decode steps per batch size and replay them
 
 
+@dataclass
+class PendingStep:
+    """A step that has been put on the device: what ``Engine.finish`` needs to hand out its tokens, and what a step
+    launched right behind it needs to take its input tokens from."""
+    batch: Batch
+    sampling: list                       # the work items that sample, in the order of the tokens
+    tokens_dev: torch.Tensor | None      # int32 [len(sampling)] on the device
+    host: torch.Tensor | None            # the same in pinned host memory once ``done`` has passed
+    done: torch.cuda.Event | None
+
+
 class Engine:
     def __init__(self, cfg: EngineConfig) -> None:
         self.cfg = cfg
@@ -62,6 +73,11 @@ class Engine:
         self.runner = ModelRunner(self.model, self.cache, device=self.device, use_graphs=cfg.use_cuda_graphs)
         self.capture_logits = False
         self.last_logits: dict[str, torch.Tensor] = {}
+        # sampled tokens come back through pinned host memory; two buffers, because a step may be launched while the
+        # one before it has not been read yet
+        self._token_buffers = [torch.empty(cfg.max_num_seqs, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._token_turn = 0
+        self.launched_ahead = 0  # steps launched before the step in front of them had been read
         log.info("cache: %d pages of %d tokens (%.2f GB)", num_blocks, cfg.page_size, num_blocks * self.bytes_per_block / 1e9)
 
     def _make_cache(self, num_blocks: int) -> CacheManager:
@@ -85,21 +101,53 @@ class Engine:
     @torch.inference_mode()
     def step(self, batch: Batch) -> dict[str, int]:
         """Runs one batch of the scheduler; returns request id -> next token for the items that sample."""
+        return self.finish(self.launch(batch))
+
+    @torch.inference_mode()
+    def launch(self, batch: Batch, feed: "PendingStep | None" = None) -> "PendingStep":
+        """Puts one batch on the device (forward, sampling, copy of the tokens to pinned host memory) and returns
+        without waiting for it.  ``feed``: the step launched just before, not finished yet, whose sampled tokens are
+        this batch's input tokens (a batch from ``Scheduler.schedule_ahead``); they go from its output to this step's
+        input on the device."""
         work = batch.work
         if not work:
-            return {}
+            return PendingStep(batch, [], None, None, None)
         if len(work) > self.cfg.max_num_seqs or batch.num_tokens > self.cfg.max_prefill_tokens + self.cfg.max_num_seqs:
             raise EngineError(f"batch of {len(work)} requests / {batch.num_tokens} tokens is over the engine's limits")
-        items = [StepItem(w.req.slot, w.start, w.req.tokens(w.start, w.end), (w.end - w.start - 1,) if w.samples else ())
-                 for w in work]
-        logits = self.runner.step(items)
+        ahead = any(w.ahead for w in work)
+        device_ids = None
+        if ahead:
+            if feed is None or feed.tokens_dev is None or not all(w.ahead for w in work) or \
+                    [w.req for w in work] != [w.req for w in feed.sampling]:
+                raise EngineError("a batch scheduled ahead must follow, request by request, the step that feeds it")
+            device_ids = feed.tokens_dev
+            self.launched_ahead += 1
+            placeholder = np.zeros(1, dtype=np.int32)
+            items = [StepItem(w.req.slot, w.start, placeholder, (0,)) for w in work]
+        else:
+            items = [StepItem(w.req.slot, w.start, w.req.tokens(w.start, w.end), (w.end - w.start - 1,) if w.samples else ())
+                     for w in work]
+        in_flight = [w.end - w.start for w in feed.sampling] if ahead else None
+        logits = self.runner.step(items, device_ids=device_ids, in_flight=in_flight)
         sampling = [w for w in work if w.samples]
         if not sampling:
-            return {}  # nothing to read back: the host runs ahead
+            return PendingStep(batch, [], None, None, None)  # nothing to read back: the host runs ahead
         tokens = choose_tokens(logits, [w.req.sampling for w in sampling], [w.end for w in sampling])
         if self.capture_logits:
             self.last_logits = {w.req.req_id: logits[i].cpu() for i, w in enumerate(sampling)}
-        return {w.req.req_id: tok for w, tok in zip(sampling, tokens.tolist())}  # the step's one device-to-host read
+        host = self._token_buffers[self._token_turn % len(self._token_buffers)][: len(sampling)]
+        self._token_turn += 1
+        host.copy_(tokens, non_blocking=True)  # the step's one device-to-host read
+        done = torch.cuda.Event()
+        done.record()
+        return PendingStep(batch, sampling, tokens, host, done)
+
+    def finish(self, pending: "PendingStep") -> dict[str, int]:
+        """Waits for a launched step; returns request id -> next token for the items that sample."""
+        if pending.done is None:
+            return {}
+        pending.done.synchronize()
+        return {w.req.req_id: tok for w, tok in zip(pending.sampling, pending.host.tolist())}
 
     def capture_decode_graphs(self, batch_sizes) -> int:
         """Captures the pure-decode step for the given batch sizes now, so that no request pays for a capture

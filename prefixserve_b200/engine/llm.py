@@ -58,11 +58,17 @@ class LLM:
             ids.append(rid)
         outputs: dict[str, list[int]] = {rid: [] for rid in ids}
         sched, engine = self.scheduler, self.engine
-        while sched.has_work():
-            batch = sched.schedule_step(self.chunked_prefill_size, self.max_running_requests)
-            result = sched.commit(batch, engine.step(batch))
+        pending = None  # the step on the device whose tokens have not been read yet
+        while pending is not None or sched.has_work():
+            if pending is None:
+                pending = engine.launch(sched.schedule_step(self.chunked_prefill_size, self.max_running_requests))
+            # while that step runs: decide and launch the one after it, if that can be done without its tokens
+            ahead = sched.schedule_ahead(self.max_running_requests)
+            following = engine.launch(ahead, feed=pending) if ahead is not None else None
+            result = sched.commit(pending.batch, engine.finish(pending))
             for rid, tok in result.new_tokens.items():
                 outputs[rid].append(tok)
+            pending = following
         return [outputs[rid] for rid in ids]
 
     def stats(self) -> SchedulerStats:

@@ -111,10 +111,11 @@ class WorkItem:
     req: Request
     start: int
     end: int
+    ahead: bool = False  # scheduled before the step in front of it was committed: its one token is not known yet
 
     @property
     def samples(self) -> bool:
-        return self.end == self.req.seq_len
+        return self.ahead or self.end == self.req.seq_len
 
 
 @dataclass(frozen=True)
@@ -182,6 +183,7 @@ class Scheduler:
         self._waiting: deque[Request] = deque()
         self._running: list[Request] = []  # by arrival, newest last
         self._inflight: Batch | None = None
+        self._ahead: Batch | None = None  # scheduled after _inflight, before its commit (schedule_ahead)
         self._abort_at_commit: list[Request] = []
         self._arrivals = 0
         self._n_prompt = self._n_prompt_cached = self._n_preempt = self._n_rejected = 0
@@ -238,19 +240,51 @@ class Scheduler:
 
         batch = Batch(work, preempted)
         self._inflight = batch
+        self._ahead = None
         took = time.perf_counter() - t0
         if took > SLOW_STEP_SECONDS:
             log.debug("schedule_step took %.2f ms", took * 1e3)
         return batch
 
+    def schedule_ahead(self, max_decode_seqs: int | None = None) -> Batch | None:
+        """The step after the one in flight, decided before that one's tokens are known, so that the device need not
+        wait for the host between two decode steps.
+
+        Possible when every request of the batch in flight gets a token from it and goes on afterwards whatever that
+        token is, except that it may be a stop token: then the request's share of the step ahead is thrown away at its
+        commit.  Returns None whenever the ordinary way is needed instead: a request reaches its length limit, an abort
+        is pending, someone waits and could be admitted (``max_decode_seqs`` as for schedule_step; None: anyone waiting
+        counts), or pages would have to be taken from another request.
+        """
+        cur = self._inflight
+        if cur is None or self._ahead is not None or not cur.work or self._abort_at_commit:
+            return None
+        if self._waiting and (max_decode_seqs is None or len(self._running) < max_decode_seqs):
+            return None
+        for w in cur.work:
+            req = w.req
+            if req.state is not ReqState.RUNNING:
+                return None  # it ended with the step before: the step in flight carries it for nothing, the next must not
+            if not w.samples or req.abort_pending or len(req.output) + 1 >= req.max_tokens or w.end + 1 > self.cache.max_seq_len:
+                return None
+        work = []
+        for w in cur.work:
+            if not self._take_pages(w.req, w.end + 1):
+                return None  # pages taken for the requests before this one stay theirs: they need them next step anyway
+            work.append(WorkItem(w.req, w.end, w.end + 1, ahead=True))
+        self._ahead = Batch(work, [])
+        return self._ahead
+
     def commit(self, batch: Batch, sampled: Mapping[str, int]) -> StepResult:
         if batch is not self._inflight:
             raise SchedulerError("commit() was given a batch that is not the one in flight")
-        self._inflight = None
+        self._inflight, self._ahead = self._ahead, None  # a step scheduled ahead is the one in flight from now on
         new_tokens: dict[str, int] = {}
         finished: dict[str, FinishReason] = {}
         for w in batch.work:
             req = w.req
+            if w.ahead and req.state is not ReqState.RUNNING:
+                continue  # it ended with the step before (a stop token): what this step computed for it is dropped
             if req.num_computed != w.start:
                 raise SchedulerError(f"{req.req_id}: the batch is stale")
             samples = w.samples

@@ -83,9 +83,9 @@ class ModelRunner:
         self.inject_bug: str | None = None
 
     # ------------------------------------------------------------------ checks
-    def _check(self, items: Sequence[StepItem]) -> None:
+    def _check(self, items: Sequence[StepItem], ahead: np.ndarray | None = None) -> None:
         seen: set[int] = set()
-        for it in items:
+        for at, it in enumerate(items):
             n = len(it.tokens)
             if n < 1:
                 raise EngineError(f"slot {it.slot}: an item needs at least one token")
@@ -94,7 +94,7 @@ class ModelRunner:
             seen.add(it.slot)
             if not self.cache.slots.taken(it.slot):
                 raise EngineError(f"slot {it.slot} is not open")
-            if it.start != self.cache.position(it.slot):
+            if it.start != self.cache.position(it.slot) + (0 if ahead is None else int(ahead[at])):
                 raise EngineError(f"slot {it.slot}: tokens start at {it.start} but the cache holds {self.cache.position(it.slot)}")
             end = it.start + n
             if end > self.cache.max_seq_len:
@@ -121,15 +121,27 @@ class ModelRunner:
 
     # ------------------------------------------------------------------- step
     @torch.inference_mode()
-    def step(self, items: Sequence[StepItem]) -> torch.Tensor:
+    def step(self, items: Sequence[StepItem], device_ids: torch.Tensor | None = None,
+             in_flight: Sequence[int] | None = None) -> torch.Tensor:
         """Runs the batch. Returns float32 logits [number of wanted positions, vocab] on the device,
-        in the order of the items and of each item's ``want``."""
+        in the order of the items and of each item's ``want``.
+
+        ``device_ids`` (int32 [len(items)] on the device): the items are single tokens that follow a step which has been
+        launched but whose result the host has not seen; their token ids are taken from this tensor on the device (the
+        items' own ``tokens`` are placeholders); ``in_flight[i]`` is how many tokens that step computes for item i's
+        request, which the cache manager does not record before its commit."""
         if not items:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
+        ahead = None
+        if device_ids is not None:
+            if any(len(it.tokens) != 1 for it in items) or device_ids.numel() != len(items) or device_ids.dtype != torch.int32 \
+                    or not device_ids.is_cuda or in_flight is None or len(in_flight) != len(items):
+                raise EngineError("token ids from the device: one int32 per item, every item a single token")
+            ahead = np.asarray(in_flight, dtype=np.int64)
         held = self._graphs.get(len(items)) if self.use_graphs else None
         if held is not None and all(len(it.tokens) == 1 and tuple(it.want) == (0,) for it in items):
-            return self._replay(items, held)
-        self._check(items)
+            return self._replay(items, held, device_ids, ahead)
+        self._check(items, ahead)
         lens = [len(it.tokens) for it in items]
         b, t = len(items), sum(lens)
         s = sum(len(it.want) for it in items)
@@ -186,6 +198,8 @@ class ModelRunner:
             dev = host[:total].to(self.device, non_blocking=True)
         self._copied.record()
         self._copy_pending = True
+        if device_ids is not None:
+            dev[o_ids: o_ids + t].copy_(device_ids)
 
         ctx = StepContext(
             num_tokens=t,
@@ -222,7 +236,8 @@ class ModelRunner:
             library.launches = before  # recorded, not run
         return logits
 
-    def _replay(self, items: Sequence[StepItem], held: _DecodeGraph) -> torch.Tensor:
+    def _replay(self, items: Sequence[StepItem], held: _DecodeGraph, device_ids: torch.Tensor | None = None,
+                ahead: np.ndarray | None = None) -> torch.Tensor:
         """A pure-decode step of a batch size that has been captured: the same checks and the same buffer layout as
         the general path, written with array operations instead of per-item loops, then one copy and one replay."""
         cache = self.cache
@@ -234,7 +249,7 @@ class ModelRunner:
             raise EngineError("a slot appears twice in one step")
         if slots.min() < 0 or slots.max() >= cache.num_slots or not all(cache.slots.taken(int(s)) for s in slots):
             raise EngineError("a slot of the step is not open")
-        if not np.array_equal(starts, cache._position[slots]):
+        if not np.array_equal(starts, cache._position[slots] + (0 if ahead is None else ahead)):
             raise EngineError("tokens do not start where the cache ends for some slot of the step")
         if starts.max() + 1 > cache.max_seq_len:
             raise EngineError(f"a position exceeds max_seq_len {cache.max_seq_len}")
@@ -274,6 +289,8 @@ class ModelRunner:
         held.inputs.copy_(host[:total], non_blocking=True)
         self._copied.record()
         self._copy_pending = True
+        if device_ids is not None:
+            held.inputs[o_ids: o_ids + b].copy_(device_ids)
         held.graph.replay()
         library.launches += held.kernels  # this library's kernels inside the replayed graph
         self.steps_run += 1

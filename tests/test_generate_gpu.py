@@ -114,6 +114,47 @@ def test_stop_ids_and_cached_pages_are_never_written(sharp):
     assert out == first[: first.index(first[2]) + 1]  # the stop token is kept, nothing after it
 
 
+def test_steps_launched_ahead_give_the_same_tokens(sharp):
+    """The entry point launches a decode step before it has read the tokens of the one before; a loop that waits for
+    every step must produce the same, with greedy and with seeded sampling, and when a stop token ends a request
+    one step before the host finds out."""
+    from prefixserve_b200 import LLM, SamplingParams
+    from prefixserve_b200.engine import Engine, EngineConfig, Scheduler
+    folder, (cfg, tensors) = sharp
+    vocab = helpers.TINY_B["cfg"].vocab_size
+    prompts = [helpers.random_tokens(vocab, n, seed=70 + n) for n in (5, 33, 18)]
+    want = [plain_model.greedy(cfg, tensors, p, 20) for p in prompts]
+    stop = want[1][7]                                        # ends request 1 early (and whoever else meets it)
+    for dtype in ("float32", "bfloat16"):
+        for params in (SamplingParams(max_tokens=20), SamplingParams(max_tokens=20, temperature=0.8, seed=5)):
+            engine = Engine(EngineConfig(model_path=folder, dtype=helpers_dtype(dtype), max_num_seqs=3, max_prefill_tokens=16,
+                                         max_seq_len=128, num_blocks=24))
+            sched = Scheduler(engine.cache, chunk_size=16, stop_token_ids=[stop])
+            for i, p in enumerate(prompts):
+                sched.add_request(f"r{i}", p, params.max_tokens, sampling=params)
+            waited = {f"r{i}": [] for i in range(3)}
+            while sched.has_work():
+                batch = sched.schedule_step(16, 3)
+                for rid, tok in sched.commit(batch, engine.step(batch)).new_tokens.items():
+                    waited[rid].append(tok)
+            del engine, sched
+            llm = LLM(folder, dtype=dtype, max_seq_len=128, num_blocks=24, max_running_requests=3, chunked_prefill_size=16)
+            llm.scheduler._stop = frozenset([stop])
+            before = llm.engine.launched_ahead
+            got = llm.generate(prompts, params)
+            assert got == [waited[f"r{i}"] for i in range(3)], (dtype, params)
+            assert llm.engine.launched_ahead - before >= 8   # the path under test was taken
+            llm.engine.cache.check()
+            if dtype == "float32" and params.temperature == 0:
+                cut = [w[: w.index(stop) + 1] if stop in w else w for w in want]
+                assert got == cut
+            del llm
+
+
+def helpers_dtype(name):
+    return {"float32": torch.float32, "bfloat16": torch.bfloat16}[name]
+
+
 def test_long_decode_and_first_tokens(sharp):
     """A request decoded for hundreds of steps, and the logits of the very first tokens of a sequence."""
     from prefixserve_b200.engine.replay import Replayer

@@ -270,3 +270,113 @@ def test_cache_given_or_made():
     _, batches = drive(s)
     assert batches[:3] == [[("a", 0, 8)], [("a", 8, 16)], [("a", 16, 20)]]
     assert s.stats().cached_blocks == 2  # pages of 8 tokens
+
+
+# ---- scheduling one step ahead of the commit ------------------------------------------------------------------------
+
+def drive_ahead(s, budget=512, seqs=64, token=lambda rid, n: 1000 + n):
+    """The loop of the entry point with a fake device: a step is 'launched' when it is scheduled and its tokens are
+    only made up when it is finished, after the next step has been scheduled ahead if that was possible."""
+    out, kinds = {}, []
+    pending = None
+    while pending is not None or s.has_work():
+        if pending is None:
+            pending = s.schedule_step(budget, seqs)
+            kinds.append("plain")
+        ahead = s.schedule_ahead(seqs)
+        if ahead is not None:
+            kinds.append("ahead")
+            assert [w.req for w in ahead.work] == [w.req for w in pending.work if w.samples]
+            assert all(w.ahead and w.samples and w.end - w.start == 1 for w in ahead.work)
+        counts = {w.req.req_id: len(w.req.output) for w in pending.work}
+        sampled = {w.req.req_id: token(w.req.req_id, counts[w.req.req_id]) for w in pending.work
+                   if w.samples and w.req.req_id in s._by_id}
+        res = s.commit(pending, sampled)
+        for rid, tok in res.new_tokens.items():
+            out.setdefault(rid, []).append(tok)
+        s.cache.check()
+        pending = ahead
+    return out, kinds
+
+
+def test_ahead_gives_the_same_tokens_and_is_used_for_plain_decoding():
+    def build():
+        s = Scheduler(64, stop_token_ids=[1003])
+        s.add_request("a", prompt(20), 9, ignore_eos=True)
+        s.add_request("b", prompt(7, 100), 30)            # stops at its fourth token (1003), found out one step late
+        s.add_request("c", prompt(40, 200), 6, ignore_eos=True)
+        return s
+    plain, _ = drive(build())
+    ahead, kinds = drive_ahead(build())
+    assert ahead == plain
+    assert plain["b"] == [1000, 1001, 1002, 1003] and len(plain["a"]) == 9 and len(plain["c"]) == 6
+    assert kinds.count("ahead") >= 4 and kinds[0] == "plain"
+
+
+def test_ahead_is_refused_where_the_next_step_depends_on_this_one():
+    s = Scheduler(16)
+    assert s.schedule_ahead() is None                       # nothing in flight
+    s.add_request("a", prompt(40), 3, ignore_eos=True)
+    b = s.schedule_step(16, 4)                              # a prompt portion that samples nothing
+    assert s.schedule_ahead() is None
+    s.commit(b, {})
+    b = s.schedule_step(16, 4)
+    s.commit(b, {})
+    b = s.schedule_step(16, 4)                              # the last portion: samples token 1 of 3
+    assert [w.samples for w in b.work] == [True]
+    nxt = s.schedule_ahead()
+    assert nxt is not None and [(w.start, w.end) for w in nxt.work] == [(40, 41)]
+    assert s.schedule_ahead() is None                       # only one step ahead
+    with pytest.raises(SchedulerError):
+        s.schedule_step(16, 4)
+    s.commit(b, {"a": 5})
+    last = s.schedule_ahead()                               # the step in flight yields token 2 of 3, this one the third
+    assert last is not None and [(w.start, w.end) for w in last.work] == [(41, 42)]
+    with pytest.raises(SchedulerError):
+        s.commit(b, {"a": 5})
+    res = s.commit(nxt, {"a": 6})
+    assert res.new_tokens == {"a": 6} and not res.finished
+    assert s.schedule_ahead() is None                       # nothing follows the last token
+    res = s.commit(last, {"a": 7})
+    assert res.finished == {"a": FinishReason.LENGTH} and not s.has_work()
+    # someone waiting who could be admitted, an abort, and a lack of pages all send the caller the ordinary way
+    s = Scheduler(8)
+    assert s.add_request("x", prompt(30), 50, ignore_eos=True) is AddResult.ACCEPTED
+    b = s.schedule_step(64, 1)
+    s.add_request("y", prompt(3), 5)
+    assert s.schedule_ahead(2) is None and s.schedule_ahead() is None
+    assert s.schedule_ahead(1) is not None                  # y cannot be admitted anyway: x holds the only seat
+    s = Scheduler(4, enable_prefix_cache=False)
+    for rid in ("x", "y"):
+        assert s.add_request(rid, prompt(31), 20, ignore_eos=True) is AddResult.ACCEPTED
+    b = s.schedule_step(64, 2)                              # 31 tokens each: two pages each, the pool is used up
+    nxt = s.schedule_ahead()
+    assert nxt is not None                                  # position 31 still lies in the second page
+    s.commit(b, {"x": 1, "y": 1})
+    assert s.schedule_ahead() is None                       # position 32 needs a third page: someone has to go, which
+    s.commit(nxt, {"x": 2, "y": 2})                         # only the ordinary way decides
+    b = s.schedule_step(64, 2)
+    assert b.preempted == ["y"] and [w.req.req_id for w in b.work] == ["x"]
+    s.commit(b, {"x": 3})
+    s = Scheduler(16)
+    s.add_request("x", prompt(5), 50, ignore_eos=True)
+    b = s.schedule_step(64, 1)
+    s.free_request("x")
+    assert s.schedule_ahead() is None
+    assert s.commit(b, {"x": 1}).finished == {"x": FinishReason.ABORT}
+
+
+def test_abort_while_two_steps_are_out():
+    s = Scheduler(16)
+    s.add_request("x", prompt(5), 50, ignore_eos=True)
+    s.add_request("y", prompt(6, 50), 50, ignore_eos=True)
+    b = s.schedule_step(64, 4)
+    nxt = s.schedule_ahead()
+    assert nxt is not None
+    assert s.free_request("x")                              # both steps may still write into its pages
+    res = s.commit(b, {"x": 1, "y": 2})
+    assert res.finished == {"x": FinishReason.ABORT}
+    res = s.commit(nxt, {"x": 3, "y": 4})                   # what the step ahead computed for x is dropped
+    assert res.new_tokens == {"y": 4} and not res.finished
+    s.cache.check()
+    assert s.stats().num_running == 1
