@@ -123,10 +123,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         fence_after();
         const uint32_t acc = tmem_base + buf * BN;
         for (int kb = 0; kb < k_blocks; ++kb) {
-          ok = mbar_wait(&bars->full[stage], phase, abort, 2);
-          ok = __all_sync(0xffffffffu, ok);
+          ok = mbar_wait(&bars->full[stage], phase, abort, 2);  // filled by TMA: no tensor-memory fence needed
           if (!ok) break;
-          fence_after();
           const uint64_t da = smem_desc(smem_u32(tiles + stage * STAGE_BYTES));
           const uint64_t db = smem_desc(smem_u32(tiles + stage * STAGE_BYTES + A_BYTES));
           const uint32_t hi = (uint32_t)(da >> 32), a_lo = (uint32_t)da, b_lo = (uint32_t)db;

@@ -70,15 +70,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return false;
 }
 
-// The same for a whole (converged) warp: one lane polls, the others wait for it.  An mbarrier operation is carried out
-// lane by lane, so 32 lanes polling cost 32 times one.  The warp barrier orders the polling lane's acquire before what
-// the other lanes do next.
-__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile uint32_t* abort, int who) {
-  int ok = 1;
-  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort, who) ? 1 : 0;
-  __syncwarp();
-  return __shfl_sync(0xffffffffu, ok, 0) != 0;
-}
+// A converged warp that waits together calls mbar_wait in all its lanes: measured on B200, that costs about 120
+// clocks on a completed barrier, while one polling lane followed by a warp barrier and a broadcast costs about 260.
 
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
   asm volatile(

@@ -149,6 +149,15 @@ class Engine:
         pending.done.synchronize()
         return {w.req.req_id: tok for w, tok in zip(pending.sampling, pending.host.tolist())}
 
+    def check_device_status(self) -> None:
+        """Raises if a bounded wait inside a tensor-core kernel ever gave up on this device: the results of that launch
+        (and possibly of later ones) are void.  Reading the status waits for the device, so callers do it where they
+        wait anyway: at the end of a generate call, at the end of a replay."""
+        from ..ops import library
+        status = library.tcgen05_status()
+        if status:
+            raise EngineError(f"a tcgen05 kernel gave up waiting on a barrier (status {status:#x}); results are void")
+
     def capture_decode_graphs(self, batch_sizes) -> int:
         """Captures the pure-decode step for the given batch sizes now, so that no request pays for a capture
         (a few milliseconds each) in the middle of serving.  Needs the cache to have that many free slots and pages.

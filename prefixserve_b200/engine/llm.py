@@ -69,6 +69,7 @@ class LLM:
             for rid, tok in result.new_tokens.items():
                 outputs[rid].append(tok)
             pending = following
+        engine.check_device_status()
         return [outputs[rid] for rid in ids]
 
     def stats(self) -> SchedulerStats:

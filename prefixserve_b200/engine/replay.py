@@ -31,6 +31,7 @@ import numpy as np
 import torch
 
 from ..cache.manager import CacheManager, pages_for
+from ..ops import library
 from .loading import load_model, parse_dtype
 from .step import EngineError, ModelRunner, StepItem
 
@@ -76,6 +77,10 @@ class Replayer:
         out = None
         if logits is not None and logits.shape[0] > 0:
             out = logits.to("cpu").numpy().astype("<f4", copy=False)
+            if self.dtype == torch.bfloat16:  # the device has just been waited for: see whether a bounded wait gave up
+                status = library.tcgen05_status()
+                if status:
+                    raise EngineError(f"a tcgen05 kernel gave up waiting on a barrier (status {status:#x}); results are void")
         for rid in record.get("end", []):
             slot = self.slot_of.pop(str(rid), None)
             if slot is not None:
