@@ -444,6 +444,37 @@ def test_attention_prefill_tcgen05_every_row_finds_its_own_key():
     assert torch.allclose(out.float().cpu(), want[old:], atol=3e-2, rtol=3e-2)
 
 
+@pytest.mark.parametrize("seed", range(12))
+def test_attention_tensor_cores_random_steps_agree_with_the_generic_kernel(seed, monkeypatch):
+    """Random steps (head counts, page sizes, windows, cached lengths, portion lengths from 1 to 700 tokens) through
+    the tensor-core kernels and through the generic one-warp-per-row kernel on the same pages."""
+    from prefixserve_b200 import ops
+    from prefixserve_b200.ops import library, tensorcore
+    import random
+    rnd = random.Random(seed)
+    d = rnd.choice([64, 128])
+    hkv = rnd.choice([1, 2, 3])
+    hq = hkv * rnd.choice([1, 2, 4, 7])
+    page = rnd.choice([16, 32, 64])
+    window = rnd.choice([None, None, 17, 130, 500])
+    monkeypatch.setattr(tensorcore, "TCGEN05_PREFILL_MIN_TOKENS", rnd.choice([2, 64, 64]))
+    n_items = rnd.randint(1, 5)
+    lens_new = [rnd.choice([1, 1, 2, rnd.randint(3, 130), rnd.randint(120, 700)]) for _ in range(n_items)]
+    lens_old = [rnd.choice([0, rnd.randint(1, 40), rnd.randint(100, 900)]) for _ in range(n_items)]
+    table, seqs, num_pages = _paged_setup(torch.bfloat16, lens_new, lens_old, hq, hkv, d, page, seed=100 + seed)
+    totals = [o + n for o, n in zip(lens_old, lens_new)]
+    kv = _fill_pages(seqs, table, totals, hkv, d, page, num_pages)
+    q = torch.cat([s["q"][o:] for s, o in zip(seqs, lens_old)]).to(torch.bfloat16).to(DEV)
+    positions = torch.cat([torch.arange(o, o + n) for o, n in zip(lens_old, lens_new)]).to(torch.int32).to(DEV)
+    token_item = torch.cat([torch.full((n,), i) for i, n in enumerate(lens_new)]).to(torch.int32).to(DEV)
+    fast = ops.attention(q, kv, table.to(DEV), positions, token_item, window=window, ctx=_Batch(lens_old, lens_new))
+    slow = ops.attention(q, kv, table.to(DEV), positions, token_item, window=window)
+    assert library.tcgen05_status() == 0
+    what = (d, hq, hkv, page, window, lens_old, lens_new)
+    assert torch.isfinite(fast.float()).all(), what
+    assert torch.allclose(fast.float(), slow.float(), atol=2e-2, rtol=2e-2), (what, float((fast.float() - slow.float()).abs().max()))
+
+
 def test_attention_shapes_outside_the_tensor_core_kernels_fall_back():
     from prefixserve_b200.ops.tensorcore import attention_bf16_supported
     assert attention_bf16_supported(64, 16) and attention_bf16_supported(128, 64)
