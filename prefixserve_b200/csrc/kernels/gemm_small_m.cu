@@ -466,12 +466,28 @@ __device__ __forceinline__ void load8_any<__nv_bfloat16>(const __nv_bfloat16* p,
   }
 }
 
-// CPW: most k chunks (of 32) a warp may own (K <= 512 * CPW).
-template <int MT, int TILES, int CPW, typename TOut>
+// What the fused projection needs to finish the job of the rotary kernel (rope.cu) in its own epilogue: W is the
+// [queries; keys; values] matrix with the rows of every query and key head reordered so that a 16-row tile holds
+// 8 elements of the head's first half and the 8 elements they are rotated with (stored index 16b+j <-> natural
+// index 8b+j, stored 16b+8+j <-> natural D/2+8b+j).  Queries go to q_out [M, hq, D] and keys to the cache in that
+// stored order (a dot product does not care, as long as both sides agree); values in natural order.
+struct RopeArgs {
+  const int32_t* positions;   // [M] absolute position of each token
+  const int32_t* token_item;  // [M] row of the page table
+  const int32_t* table;       // [items, table_width] page ids
+  const float* cos_t;         // [max_positions, D/2], null: no rotation
+  const float* sin_t;
+  __nv_bfloat16* kv;          // [num_pages, 2, hkv, page_size, D]
+  __nv_bfloat16* q_out;       // [M, hq, D]
+  int table_width, hq, hkv, D, page_shift, num_pages, max_positions;
+};
+
+// CPW: most k chunks (of 32) a warp may own (K <= 512 * CPW).  ROPE: the epilogue rotates and appends (TILES == 1).
+template <int MT, int TILES, int CPW, typename TOut, bool ROPE = false>
 __global__ void __launch_bounds__(SW * 32, 1)
 gemm_stream_norm_kernel(const float* __restrict__ h_in, const __nv_bfloat16* __restrict__ pending, const float* __restrict__ gain,
                         const int32_t* __restrict__ rows, float* __restrict__ h_out, const __nv_bfloat16* __restrict__ W,
-                        TOut* __restrict__ y, int M, int N, int K, int ldy, int up_offset, float eps) {
+                        TOut* __restrict__ y, int M, int N, int K, int ldy, int up_offset, float eps, RopeArgs rope) {
   using Shape = NormStreamShape<MT, TILES>;
   constexpr int STAGES = Shape::STAGES, PIECES = Shape::PIECES;
   constexpr uint32_t STAGE_BYTES = PIECES * 32 * 16;
@@ -615,6 +631,57 @@ gemm_stream_norm_kernel(const float* __restrict__ h_in, const __nv_bfloat16* __r
       }
     __syncthreads();  // also makes every warp's sum of squares visible (written before the first of these barriers)
     const int row0 = (blockIdx.x + ti * gridDim.x) * 16;
+    if constexpr (ROPE) {
+      // a thread takes one pair (rows j and j+8 of the tile) of one token
+      for (int idx = threadIdx.x; idx < 8 * 8 * MT; idx += SW * 32) {
+        const int j = idx & 7, m = idx >> 3;
+        if (m >= M || row0 >= N) continue;
+        float total = 0.f;
+#pragma unroll
+        for (int w = 0; w < SW; ++w) total += ssq_part[w][m];
+        const float inv = rsqrtf(total / (float)K + eps);
+        float lo = 0.f, hi = 0.f;
+#pragma unroll
+        for (int w = 0; w < SW; ++w) { lo += mine[w][0][j][m]; hi += mine[w][0][j + 8][m]; }
+        // what a separate projection would have stored in bfloat16 before the rotary kernel read it
+        lo = __bfloat162float(__float2bfloat16_rn(lo * inv));
+        hi = __bfloat162float(__float2bfloat16_rn(hi * inv));
+        const int D = rope.D, q_cols = rope.hq * D, k_cols = rope.hkv * D;
+        const int pos = rope.positions[m];
+        if (row0 < q_cols + k_cols) {
+          const int within = row0 < q_cols ? row0 : row0 - q_cols;
+          const int head = within / D, block = (within - head * D) >> 4;
+          if (rope.cos_t) {
+            const int safe = pos < 0 ? 0 : (pos >= rope.max_positions ? rope.max_positions - 1 : pos);
+            const float cs = rope.cos_t[(size_t)safe * (D >> 1) + block * 8 + j], sn = rope.sin_t[(size_t)safe * (D >> 1) + block * 8 + j];
+            const float a = lo * cs - hi * sn, b = hi * cs + lo * sn;
+            lo = a; hi = b;
+          }
+          __nv_bfloat16* dst = nullptr;
+          if (row0 < q_cols) {
+            dst = rope.q_out + ((size_t)m * rope.hq + head) * D;
+          } else {
+            const int page = rope.table[(size_t)rope.token_item[m] * rope.table_width + (pos >> rope.page_shift)];
+            if (page >= 0 && page < rope.num_pages)  // the host checks tables before launch; a bad id is skipped
+              dst = rope.kv + ((((size_t)page * 2) * rope.hkv + head) << rope.page_shift) * D + (size_t)(pos & ((1 << rope.page_shift) - 1)) * D;
+          }
+          if (dst) {
+            dst[block * 16 + j] = __float2bfloat16_rn(lo);
+            dst[block * 16 + 8 + j] = __float2bfloat16_rn(hi);
+          }
+        } else {
+          const int within = row0 - q_cols - k_cols;
+          const int head = within / D, d0 = within - head * D;
+          const int page = rope.table[(size_t)rope.token_item[m] * rope.table_width + (pos >> rope.page_shift)];
+          if (page >= 0 && page < rope.num_pages) {
+            __nv_bfloat16* dst = rope.kv + ((((size_t)page * 2 + 1) * rope.hkv + head) << rope.page_shift) * D +
+                                 (size_t)(pos & ((1 << rope.page_shift) - 1)) * D;
+            dst[d0 + j] = __float2bfloat16_rn(lo);
+            dst[d0 + 8 + j] = __float2bfloat16_rn(hi);
+          }
+        }
+      }
+    } else {
     for (int idx = threadIdx.x; idx < 16 * 8 * MT; idx += SW * 32) {
       const int r = idx & 15, m = idx >> 4;
       const int row = row0 + r;
@@ -641,26 +708,28 @@ gemm_stream_norm_kernel(const float* __restrict__ h_in, const __nv_bfloat16* __r
       }
       y[(size_t)m * ldy + row] = from_float<TOut>(out);
     }
+    }
   }
   asm volatile("cp.async.wait_group 0;\n" ::: "memory");
 }
 
-template <int MT, int TILES, int CPW, typename TOut>
+template <int MT, int TILES, int CPW, typename TOut, bool ROPE = false>
 int launch_norm_stream(const void* h_in, const void* pending, const void* gain, const void* rows, void* h_out, const void* W,
-                       void* y, int M, int N, int K, int ldy, int up_offset, float eps, int sms, cudaStream_t stream) {
+                       void* y, int M, int N, int K, int ldy, int up_offset, float eps, int sms, cudaStream_t stream,
+                       const RopeArgs& rope = RopeArgs{}) {
   using Shape = NormStreamShape<MT, TILES>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_stream_norm_kernel<MT, TILES, CPW, TOut>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_stream_norm_kernel<MT, TILES, CPW, TOut, ROPE>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Shape::SMEM_BYTES);
     if (e != cudaSuccess) PSB_REFUSE("gemm_stream_norm: cannot reserve %d bytes of shared memory: %s", Shape::SMEM_BYTES, cudaGetErrorString(e));
     configured = true;
   }
   const int tiles = (N + 15) / 16;
   const int grid = tiles < sms ? tiles : sms;
-  psb_launch(gemm_stream_norm_kernel<MT, TILES, CPW, TOut>, dim3(grid), dim3(SW * 32), (size_t)Shape::SMEM_BYTES, stream,
+  psb_launch(gemm_stream_norm_kernel<MT, TILES, CPW, TOut, ROPE>, dim3(grid), dim3(SW * 32), (size_t)Shape::SMEM_BYTES, stream,
              (const float*)h_in, (const __nv_bfloat16*)pending, (const float*)gain, (const int32_t*)rows, (float*)h_out,
-             (const __nv_bfloat16*)W, (TOut*)y, M, N, K, ldy, up_offset, eps);
+             (const __nv_bfloat16*)W, (TOut*)y, M, N, K, ldy, up_offset, eps, rope);
   return 0;
 }
 
@@ -679,6 +748,22 @@ int dispatch_norm_stream(const void* h_in, const void* pending, const void* gain
   }
 #undef PSB_NS
   PSB_REFUSE("gemm_stream_norm: M=%d K=%d is beyond this kernel (M <= 8 with K <= 8192, or M <= 16 with K <= 4096)", M, K);
+}
+
+int dispatch_norm_stream_rope(const void* h_in, const void* pending, const void* gain, void* h_out, const void* W, int M, int N,
+                              int K, float eps, int sms, cudaStream_t stream, const RopeArgs& rope) {
+  const int cpw = (K / 32 + SW - 1) / SW;
+#define PSB_NSR(MT, CPW) launch_norm_stream<MT, 1, CPW, __nv_bfloat16, true>(h_in, pending, gain, nullptr, h_out, W, nullptr, M, N, K, N, 0, eps, sms, stream, rope)
+  if (M <= 8) {
+    if (cpw <= 4) return PSB_NSR(1, 4);
+    if (cpw <= 8) return PSB_NSR(1, 8);
+    if (cpw <= 16) return PSB_NSR(1, 16);
+  } else if (M <= 16) {
+    if (cpw <= 4) return PSB_NSR(2, 4);
+    if (cpw <= 8) return PSB_NSR(2, 8);
+  }
+#undef PSB_NSR
+  PSB_REFUSE("gemm_stream_norm_rope: M=%d K=%d is beyond this kernel (M <= 8 with K <= 8192, or M <= 16 with K <= 4096)", M, K);
 }
 
 }  // namespace
@@ -713,5 +798,31 @@ PSB_API int psb_gemm_stream_norm_gated(const void* h_in, const void* pending, co
   if (!(eps > 0.f)) PSB_REFUSE("gemm_stream_norm_gated: eps must be positive");
   if (int rc = dispatch_norm_stream<2, __nv_bfloat16>(h_in, pending, gain, nullptr, h_out, W, act, M, I, K, I, I, eps, sms, stream)) return rc;
   PSB_LAUNCH_CHECK("gemm_stream_norm_gated");
+  return 0;
+}
+
+// The fused projection of an attention layer for few tokens: rmsnorm(h_in + pending) W^T with W = [queries; keys;
+// values] in the pair-interleaved row order described at RopeArgs, queries rotated into q_out [M, hq, D], keys rotated
+// and values as they are stored at the tokens' positions in the pages (what psb_gemm_stream_norm followed by
+// psb_rope_append in its paired form would do, in one kernel).  cos_t/sin_t null: no rotation.
+PSB_API int psb_gemm_stream_norm_rope(const void* h_in, const void* pending, const void* gain, void* h_out, const void* W, int M,
+                                      int K, float eps, int sms, const void* positions, const void* token_item, const void* table,
+                                      int table_width, const void* cos_t, const void* sin_t, void* kv, void* q_out, int hq, int hkv,
+                                      int D, int page_size, int num_pages, int max_positions, cudaStream_t stream) {
+  const int N = (hq + 2 * hkv) * D;
+  if (!psb_gemm_stream_norm_supported(M, K) || sms < 1) PSB_REFUSE("gemm_stream_norm_rope: shape M=%d K=%d is not taken", M, K);
+  if (hq < 1 || hkv < 1 || D < 16 || D % 16) PSB_REFUSE("gemm_stream_norm_rope: needs a head size that is a multiple of 16 (hq=%d hkv=%d D=%d)", hq, hkv, D);
+  if (page_size < 1 || (page_size & (page_size - 1)) || num_pages < 1 || table_width < 1) PSB_REFUSE("gemm_stream_norm_rope: page size %d must be a power of two (pages=%d, width=%d)", page_size, num_pages, table_width);
+  if (!positions || !token_item || !table || !kv || !q_out) PSB_REFUSE("gemm_stream_norm_rope: cache arguments missing");
+  if ((cos_t == nullptr) != (sin_t == nullptr) || (cos_t && max_positions < 1)) PSB_REFUSE("gemm_stream_norm_rope: angle tables incomplete");
+  if (!(eps > 0.f)) PSB_REFUSE("gemm_stream_norm_rope: eps must be positive");
+  RopeArgs rope;
+  rope.positions = (const int32_t*)positions; rope.token_item = (const int32_t*)token_item; rope.table = (const int32_t*)table;
+  rope.cos_t = (const float*)cos_t; rope.sin_t = (const float*)sin_t; rope.kv = (__nv_bfloat16*)kv; rope.q_out = (__nv_bfloat16*)q_out;
+  rope.table_width = table_width; rope.hq = hq; rope.hkv = hkv; rope.D = D; rope.num_pages = num_pages; rope.max_positions = max_positions;
+  rope.page_shift = 0;
+  while ((1 << rope.page_shift) < page_size) ++rope.page_shift;
+  if (int rc = dispatch_norm_stream_rope(h_in, pending, gain, h_out, W, M, N, K, eps, sms, stream, rope)) return rc;
+  PSB_LAUNCH_CHECK("gemm_stream_norm_rope");
   return 0;
 }

@@ -14,6 +14,12 @@
 // (prefixserve/model/attention.py:14-16, :95-106).
 //
 // Cache layout of one entry: [num_pages, 2, hkv, page_size, D].
+//
+// ``paired`` (head sizes that are multiples of 16): the elements of every query and key head arrive in the order the
+// attention part gives its projection rows, 8 elements of the first half followed by the 8 they are rotated with
+// (stored index 16b+j <-> natural index 8b+j, stored 16b+8+j <-> natural D/2+8b+j), and queries and keys leave in
+// that same order: scores do not depend on the order of a head's elements as long as both sides share it.  Values
+// are always in natural order.
 #include "common.cuh"
 
 namespace {
@@ -117,7 +123,7 @@ __global__ void rope_append_vec_kernel(const T* __restrict__ qkv, const int32_t*
                                        const int32_t* __restrict__ token_item, const float* __restrict__ cos_t,
                                        const float* __restrict__ sin_t, const int32_t* __restrict__ table, int table_width,
                                        TKV* __restrict__ kv, T* __restrict__ q_out, int hq, int hkv, int D, int page_size,
-                                       int num_pages, int max_positions, int rotate, int write_kv) {
+                                       int num_pages, int max_positions, int rotate, int write_kv, int paired) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
@@ -142,10 +148,11 @@ __global__ void rope_append_vec_kernel(const T* __restrict__ qkv, const int32_t*
   const int rot_heads = write_kv ? hq + hkv : hq;
   const int vec_per_head = half >> 3;
   for (int idx = threadIdx.x; idx < rot_heads * vec_per_head; idx += blockDim.x) {
-    const int head = idx / vec_per_head, j = (idx - head * vec_per_head) << 3;
+    const int head = idx / vec_per_head, j = (idx - head * vec_per_head) << 3;  // j: first of 8 angles
+    const int at1 = paired ? 2 * j : j, at2 = paired ? 2 * j + 8 : j + half;     // where the two runs of 8 elements lie
     float x1[8], x2[8], o1[8], o2[8];
-    load8v<T>(row + head * D + j, x1);
-    load8v<T>(row + head * D + j + half, x2);
+    load8v<T>(row + head * D + at1, x1);
+    load8v<T>(row + head * D + at2, x2);
     if (rotate) {
       float cs[8], sn[8];
       load8v<float>(c + j, cs);
@@ -161,12 +168,12 @@ __global__ void rope_append_vec_kernel(const T* __restrict__ qkv, const int32_t*
     }
     if (head < hq) {
       T* qo = q_out + ((size_t)t * hq + head) * D;
-      store8v<T>(qo + j, o1);
-      store8v<T>(qo + j + half, o2);
+      store8v<T>(qo + at1, o1);
+      store8v<T>(qo + at2, o2);
     } else if (kdst) {
       TKV* k = kdst + (size_t)(head - hq) * page_size * D;
-      store8v<TKV>(k + j, o1);
-      store8v<TKV>(k + j + half, o2);
+      store8v<TKV>(k + at1, o1);
+      store8v<TKV>(k + at2, o2);
     }
   }
   if (vdst) {
@@ -185,11 +192,12 @@ __global__ void rope_append_vec_kernel(const T* __restrict__ qkv, const int32_t*
 PSB_API int psb_rope_append(const void* qkv, int dtype, const void* positions, const void* token_item, const void* cos_t,
                             const void* sin_t, const void* table, int table_width, void* kv, int kv_dtype, void* q_out,
                             int T, int hq, int hkv, int D, int page_size, int num_pages, int max_positions, int rotate,
-                            int write_kv, cudaStream_t stream) {
+                            int write_kv, int paired, cudaStream_t stream) {
   if (T < 0 || hq < 1 || hkv < 0 || D < 2 || (D & 1)) PSB_REFUSE("rope_append: bad sizes T=%d hq=%d hkv=%d D=%d", T, hq, hkv, D);
   if (write_kv && (page_size < 1 || num_pages < 1 || table_width < 1 || !kv || !table || hkv < 1))
     PSB_REFUSE("rope_append: cache arguments missing (page_size=%d num_pages=%d width=%d)", page_size, num_pages, table_width);
   if (rotate && (!cos_t || !sin_t || max_positions < 1)) PSB_REFUSE("rope_append: angle tables missing");
+  if (paired && D % 16) PSB_REFUSE("rope_append: the paired element order needs a head size that is a multiple of 16, not %d", D);
   if (T == 0) return 0;
   const int work = (hq + hkv) * (D / 2);
   if (D % 16 == 0) {  // every 8-element run is aligned: vector accesses
@@ -199,7 +207,7 @@ PSB_API int psb_rope_append(const void* qkv, int dtype, const void* positions, c
         psb_launch(rope_append_vec_kernel<T_, TKV>, dim3(T), dim3(threads), 0, stream,
             (const T_*)qkv, (const int32_t*)positions, (const int32_t*)token_item, (const float*)cos_t, (const float*)sin_t,
             (const int32_t*)table, table_width, (TKV*)kv, (T_*)q_out, hq, hkv, D, page_size, num_pages, max_positions, rotate,
-            write_kv);
+            write_kv, paired);
       });
     });
     PSB_LAUNCH_CHECK("rope_append");

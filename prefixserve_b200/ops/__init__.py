@@ -10,6 +10,8 @@ from .kernels import (  # noqa: F401
     embedding,
     gated_linear,
     linear,
+    pair_interleaved_order,
+    qkv_rope_append,
     rope_append,
     sample,
     silu_mul,

@@ -143,8 +143,11 @@ def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
 
 def rope_append(qkv: torch.Tensor, positions: torch.Tensor, token_item: torch.Tensor, cos: torch.Tensor | None,
                 sin: torch.Tensor | None, table: torch.Tensor | None, kv: torch.Tensor | None, *, num_heads: int,
-                num_kv_heads: int, head_dim: int, page_size: int, write_kv: bool) -> torch.Tensor:
-    """Rotates queries (and keys); stores rotated keys and values in the pages. Returns q [T, hq, D]."""
+                num_kv_heads: int, head_dim: int, page_size: int, write_kv: bool, paired: bool = False) -> torch.Tensor:
+    """Rotates queries (and keys); stores rotated keys and values in the pages. Returns q [T, hq, D].
+
+    ``paired``: every query and key head comes (and goes) with its elements in the pair-interleaved order of
+    ``pair_interleaved_order``; the rotary kernel's header says why that is harmless."""
     _dev(qkv, "projection output")
     t = qkv.shape[0]
     hkv_in = num_kv_heads if write_kv else 0
@@ -174,9 +177,42 @@ def rope_append(qkv: torch.Tensor, positions: torch.Tensor, token_item: torch.Te
     check(lib().psb_rope_append(qkv.data_ptr(), _code(qkv, "projection output"), positions.data_ptr(),
                                 token_item.data_ptr(), _ptr(cos), _ptr(sin), _ptr(table) if write_kv else None, width,
                                 _ptr(kv) if write_kv else None, kv_code, q.data_ptr(), t, num_heads, hkv_in, head_dim,
-                                page_size, num_pages, max_pos, 1 if rotate else 0, 1 if write_kv else 0, _stream()),
+                                page_size, num_pages, max_pos, 1 if rotate else 0, 1 if write_kv else 0, 1 if paired else 0,
+                                _stream()),
           "rope_append")
     return q
+
+
+def pair_interleaved_order(head_dim: int) -> list[int]:
+    """For a head size that is a multiple of 16: natural element index for each stored index when 8 elements of the
+    first half are followed by the 8 elements they are rotated with (split-half rotation pairs d with d + D/2)."""
+    if head_dim % 16:
+        raise KernelError(f"a head size of {head_dim} cannot be pair-interleaved (multiples of 16 only)")
+    order: list[int] = []
+    for block in range(head_dim // 16):
+        order += list(range(8 * block, 8 * block + 8)) + list(range(head_dim // 2 + 8 * block, head_dim // 2 + 8 * block + 8))
+    return order
+
+
+def qkv_rope_append(x: NormedRows, w_qkv: torch.Tensor, positions: torch.Tensor, token_item: torch.Tensor,
+                    cos: torch.Tensor | None, sin: torch.Tensor | None, table: torch.Tensor, kv: torch.Tensor, *,
+                    num_heads: int, num_kv_heads: int, head_dim: int, page_size: int) -> torch.Tensor | None:
+    """rmsnorm(h + pending) @ w_qkv^T, rotation and append to the pages in one kernel, for few bfloat16 tokens and a
+    projection whose query and key rows are pair-interleaved.  Returns q [T, hq, D], or None when the kernel does not
+    take the case (the caller then runs the product and ``rope_append(..., paired=True)``)."""
+    from .tensorcore import norm_qkv_rope_bf16
+    if not (x.fusable and x.rows is None and x.dtype == torch.bfloat16 and w_qkv.dtype == torch.bfloat16
+            and kv.dtype == torch.bfloat16 and head_dim % 16 == 0 and page_size & (page_size - 1) == 0):
+        return None
+    _i32(positions, "positions"), _i32(token_item, "token-to-item map"), _i32(table, "page table"), _dev(kv, "cache entry")
+    if kv.dim() != 5 or tuple(kv.shape[1:]) != (2, num_kv_heads, page_size, head_dim):
+        raise KernelError(f"cache entry must be [pages, 2, {num_kv_heads}, {page_size}, {head_dim}], is {tuple(kv.shape)}")
+    if w_qkv.shape[0] != (num_heads + 2 * num_kv_heads) * head_dim:
+        raise KernelError(f"projection has {w_qkv.shape[0]} rows, not {(num_heads + 2 * num_kv_heads) * head_dim}")
+    if cos is not None and (sin is None or cos.dtype != torch.float32 or cos.shape != sin.shape or cos.dim() != 2
+                            or cos.shape[1] != head_dim // 2):
+        raise KernelError(f"angle tables must be float32 [positions, {head_dim // 2}]")
+    return norm_qkv_rope_bf16(x, w_qkv, positions, token_item, cos, sin, table, kv, num_heads, num_kv_heads, head_dim, page_size)
 
 
 def attention_generic(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, positions: torch.Tensor,

@@ -30,8 +30,11 @@ _SIGNATURES: dict[str, list] = {
     # (a, a_dtype, w, w_dtype, c, c_dtype, M, N, K, lda, ldw, ldc, accumulate, stream)
     "psb_gemm_nt": [P, I, P, I, P, I, I, I, I, L, L, L, I, P],
     # (qkv, dtype, positions, token_item, cos, sin, table, table_width, kv, kv_dtype, q_out,
-    #  T, hq, hkv, D, page_size, num_pages, max_positions, rotate, write_kv, stream)
-    "psb_rope_append": [P, I, P, P, P, P, P, I, P, I, P, I, I, I, I, I, I, I, I, I, P],
+    #  T, hq, hkv, D, page_size, num_pages, max_positions, rotate, write_kv, paired, stream)
+    "psb_rope_append": [P, I, P, P, P, P, P, I, P, I, P, I, I, I, I, I, I, I, I, I, I, P],
+    # (h_in, pending, gain, h_out, W, M, K, eps, sms, positions, token_item, table, table_width, cos, sin, kv, q_out,
+    #  hq, hkv, D, page_size, num_pages, max_positions, stream)
+    "psb_gemm_stream_norm_rope": [P, P, P, P, P, I, I, F, I, P, P, P, I, P, P, P, P, I, I, I, I, I, I, P],
     # (q, dtype, kv, kv_dtype, table, table_width, positions, token_item, out, T, hq, hkv, D, page_size, window,
     #  scale, stream)
     "psb_attention_generic": [P, I, P, I, P, I, P, P, P, I, I, I, I, I, I, F, P],

@@ -22,6 +22,7 @@ TCGEN05_MIN_TILES = 120  # ... when the product has at least this many 128x256 o
 WIDE_BELOW_TILES = 600   # matrices with fewer 16-row tiles than this get 16 warps per CTA instead of 8
 TCGEN05_PREFILL_MIN_TOKENS = 64   # steps whose longest prompt portion has at least this many tokens run prefill attention
                                   # on the tcgen05 kernel (tiles of 128 rows); shorter portions fill too little of a tile
+MIN_KEY_RANGE = 128       # split-KV: no key range shorter than this
 DECODE_CTAS_PER_SM = 4   # split-KV: key ranges are sized so that about this many CTAs per SM exist
 _OUT_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -92,6 +93,24 @@ def norm_linear_bf16(x, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor
     return y
 
 
+def norm_qkv_rope_bf16(x, w_qkv, positions, token_item, cos, sin, table, kv, hq, hkv, d, page_size) -> torch.Tensor | None:
+    """The streaming kernel with the residual sum and norm in front and rotation and append behind; None when it does
+    not take the shape."""
+    if not _norm_fusable(x, w_qkv):
+        return None
+    m, k = x.shape
+    q = torch.empty((m, hq, d), dtype=torch.bfloat16, device=w_qkv.device)
+    new_h = torch.empty_like(x.h) if x.pending is not None else None
+    check(lib().psb_gemm_stream_norm_rope(
+        x.h.data_ptr(), None if x.pending is None else x.pending.data_ptr(), x.gain.data_ptr(),
+        None if new_h is None else new_h.data_ptr(), w_qkv.data_ptr(), m, k, x.eps, _sms(w_qkv.device), positions.data_ptr(),
+        token_item.data_ptr(), table.data_ptr(), table.shape[1], None if cos is None else cos.data_ptr(),
+        None if sin is None else sin.data_ptr(), kv.data_ptr(), q.data_ptr(), hq, hkv, d, page_size, kv.shape[0],
+        0 if cos is None else cos.shape[0], torch.cuda.current_stream().cuda_stream), "gemm_stream_norm_rope")
+    x.fused(new_h)
+    return q
+
+
 def norm_gated_linear_bf16(x, w_gate_up: torch.Tensor) -> torch.Tensor | None:
     """silu(x Wg^T) * (x Wu^T) with x = rmsnorm(h + pending), all in the streaming kernel; None when it does not fit."""
     if w_gate_up.shape[0] % 2 or x.rows is not None or not _norm_fusable(x, w_gate_up):
@@ -138,8 +157,10 @@ def gemm_tcgen05_gated(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor
 def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     """x[M,K] @ w[N,K]^T for bfloat16 operands, float32 accumulation.
 
-    Few rows (decode): the weight-streaming tensor-core kernel of this library.  Many rows: the library product
-    (cuBLAS through torch), exactly where the reference calls F.linear (prefixserve/model/llama.py:113-126).
+    Up to 16 rows (decode): the weight-streaming kernel of this library.  Prefill-sized products with bfloat16
+    output: its tcgen05 kernel.  What lies between (and outputs in float32 with many rows) goes to the library
+    product (cuBLAS through torch), which is where the reference calls F.linear for everything
+    (prefixserve/model/llama.py:113-126).
     """
     m, k = x.shape
     if out_dtype in _OUT_CODE and x.is_contiguous() and w.is_contiguous():
@@ -223,7 +244,7 @@ def attention_bf16(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, item_
             return kvl - (lo // 16) * 16
         longest = max(span(kvl) for kvl in singles)
         want = max(1, (DECODE_CTAS_PER_SM * _sms(q.device)) // max(1, b * hkv))
-        splits = max(1, min(want, -(-longest // 128)))  # ranges shorter than 128 keys cost more to merge than they save
+        splits = max(1, min(want, -(-longest // MIN_KEY_RANGE)))  # shorter ranges cost more to merge than they save
         chunk = -(-(-(-longest // splits)) // 64) * 64
         max_splits = -(-longest // chunk)
         part_o = part_ml = None

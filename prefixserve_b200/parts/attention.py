@@ -57,7 +57,19 @@ class Attention(Mixer):
             pieces += [tensors["k_proj"], tensors["v_proj"]]
         # one matrix for the three projections (rows: queries, keys, values)
         dtype = torch.float32 if any(p.dtype == torch.float32 for p in pieces) else pieces[0].dtype
-        self.w_qkv = torch.cat([p.to(dtype) for p in pieces], dim=0).contiguous()
+        pieces = [p.to(dtype) for p in pieces]
+        # With head sizes that are multiples of 16 the rows of every query and key head are reordered so that each run
+        # of 16 holds 8 elements of the head's first half and the 8 they are rotated with: the decode kernel that
+        # computes a 16-row tile of this product can then rotate and store it itself.  Queries and keys keep that
+        # element order all the way (scores do not depend on it); every attention part does this, rotating or not, so
+        # that a layer which reads another layer's keys meets the order it uses itself.
+        self.paired = self.d % 16 == 0
+        if self.paired:
+            order = torch.tensor(ops.pair_interleaved_order(self.d), device=pieces[0].device)
+            for at in range(2 if self.own_kv else 1):
+                heads = pieces[at].shape[0] // self.d
+                pieces[at] = pieces[at].view(heads, self.d, -1)[:, order, :].reshape(heads * self.d, -1)
+        self.w_qkv = torch.cat(pieces, dim=0).contiguous()
         self.w_o = tensors["o_proj"].contiguous()
 
     def prepare(self, *, max_positions, compute_dtype, device):
@@ -67,10 +79,16 @@ class Attention(Mixer):
         if cache.writes != self.own_kv:
             raise RuntimeError("an attention part with its own keys and values must write its cache entry, and only such a part may")
         table = ctx.block_tables[cache.group]
-        qkv = ops.linear(x, self.w_qkv)
-        q = ops.rope_append(qkv, ctx.positions, ctx.token_item, self.position.cos, self.position.sin, table, cache.kv,
-                            num_heads=self.hq, num_kv_heads=self.hkv, head_dim=self.d, page_size=cache.page_size,
-                            write_kv=self.own_kv)
+        q = None
+        if self.paired and self.own_kv and isinstance(x, ops.NormedRows):  # few tokens: projection, rotation, append in one
+            q = ops.qkv_rope_append(x, self.w_qkv, ctx.positions, ctx.token_item, self.position.cos, self.position.sin, table,
+                                    cache.kv, num_heads=self.hq, num_kv_heads=self.hkv, head_dim=self.d,
+                                    page_size=cache.page_size)
+        if q is None:
+            qkv = ops.linear(x, self.w_qkv)
+            q = ops.rope_append(qkv, ctx.positions, ctx.token_item, self.position.cos, self.position.sin, table, cache.kv,
+                                num_heads=self.hq, num_kv_heads=self.hkv, head_dim=self.d, page_size=cache.page_size,
+                                write_kv=self.own_kv, paired=self.paired)
         o = ops.attention(q, cache.kv, table, ctx.positions, ctx.token_item, window=self.window, scale=self.scale, ctx=ctx)
         return ops.linear(o, self.w_o)
 

@@ -627,6 +627,67 @@ def test_normed_rows_nobody_consumed_still_update_the_stream():
     assert torch.allclose(x.residual(), h + pending.float())  # and only once
 
 
+# ---- the pair-interleaved element order, and projection + rotation + append in one kernel -----------------------------
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hq,hkv,d,page", [(4, 2, 16, 16), (3, 1, 48, 8), (8, 2, 64, 16), (2, 2, 128, 32)])
+def test_rope_append_in_paired_order(dtype, hq, hkv, d, page):
+    from prefixserve_b200 import ops
+    lens_old, lens_new = [0, 37, 5], [9, 1, 30]
+    table, seqs, num_pages = _paged_setup(dtype, lens_new, lens_old, hq, hkv, d, page, seed=7)
+    t = sum(lens_new)
+    g = torch.Generator().manual_seed(2)
+    qkv = torch.randn(t, (hq + 2 * hkv) * d, generator=g).to(dtype)
+    positions = torch.cat([torch.arange(o, o + n) for o, n in zip(lens_old, lens_new)]).to(torch.int32).to(DEV)
+    token_item = torch.cat([torch.full((n,), i) for i, n in enumerate(lens_new)]).to(torch.int32).to(DEV)
+    angles = torch.outer(torch.arange(80).float(), 1.0 / (10000.0 ** (torch.arange(0, d, 2).float() / d)))
+    cos, sin = angles.cos().to(DEV).contiguous(), angles.sin().to(DEV).contiguous()
+    order = torch.tensor(ops.pair_interleaved_order(d))
+    assert sorted(order.tolist()) == list(range(d))
+    # the same projection output with the elements of every query and key head reordered
+    heads = qkv.view(t, hq + 2 * hkv, d).clone()
+    heads[:, : hq + hkv] = heads[:, : hq + hkv][:, :, order]
+    results = []
+    for data, paired in ((qkv, False), (heads.reshape(t, -1).contiguous(), True)):
+        kv = torch.zeros(num_pages, 2, hkv, page, d, dtype=dtype, device=DEV)
+        q = ops.rope_append(data.to(DEV), positions, token_item, cos, sin, table.to(DEV), kv, num_heads=hq, num_kv_heads=hkv,
+                            head_dim=d, page_size=page, write_kv=True, paired=paired)
+        results.append((q.cpu(), kv.cpu()))
+    (q_nat, kv_nat), (q_par, kv_par) = results
+    assert torch.equal(q_par, q_nat[:, :, order])
+    assert torch.equal(kv_par[:, 0], kv_nat[:, 0][..., order]) and torch.equal(kv_par[:, 1], kv_nat[:, 1])
+
+
+@pytest.mark.parametrize("m", [1, 5, 8, 13, 16])
+@pytest.mark.parametrize("hq,hkv,d,page,k", [(8, 2, 64, 16, 512), (3, 1, 48, 8, 96), (4, 4, 128, 32, 2048), (32, 8, 64, 16, 2048)])
+@pytest.mark.parametrize("rotate", [True, False])
+def test_projection_rotation_and_append_in_one_kernel(m, hq, hkv, d, page, k, rotate):
+    """Bit for bit what the norm-folded projection followed by the rotary kernel (paired order) produces."""
+    from prefixserve_b200 import ops
+    g = torch.Generator().manual_seed(m + d)
+    lens_old = [int(x) for x in torch.randint(0, 60, (m,), generator=g)]
+    table, _, num_pages = _paged_setup(torch.bfloat16, [1] * m, lens_old, hq, hkv, d, page, seed=11)
+    positions = torch.tensor(lens_old, dtype=torch.int32, device=DEV)
+    token_item = torch.arange(m, dtype=torch.int32, device=DEV)
+    h = torch.randn(m, k, generator=g).to(DEV) * 2
+    pending = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    gain = (1.0 + 0.2 * torch.randn(k, generator=g)).to(DEV)
+    w = (torch.randn((hq + 2 * hkv) * d, k, generator=g) / math.sqrt(k)).to(torch.bfloat16).to(DEV)
+    angles = torch.outer(torch.arange(80).float(), 1.0 / (10000.0 ** (torch.arange(0, d, 2).float() / d)))
+    cos, sin = (angles.cos().to(DEV).contiguous(), angles.sin().to(DEV).contiguous()) if rotate else (None, None)
+    args = dict(num_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page)
+    x = ops.NormedRows(h.clone(), pending, gain, 1e-5, torch.bfloat16)
+    kv_two = torch.zeros(num_pages, 2, hkv, page, d, dtype=torch.bfloat16, device=DEV)
+    q_two = ops.rope_append(ops.linear(x, w), positions, token_item, cos, sin, table.to(DEV), kv_two, write_kv=True, paired=True, **args)
+    y = ops.NormedRows(h.clone(), pending, gain, 1e-5, torch.bfloat16)
+    kv_one = torch.zeros_like(kv_two)
+    q_one = ops.qkv_rope_append(y, w, positions, token_item, cos, sin, table.to(DEV), kv_one, **args)
+    assert q_one is not None
+    assert torch.equal(q_one, q_two) and torch.equal(kv_one, kv_two)
+    assert torch.equal(y.residual(), x.residual())
+    assert float(kv_one.float().abs().sum()) > 0
+
+
 # ---- the tcgen05 / TMEM / TMA product for many rows -----------------------------------------------------------------
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (17, 40, 8), (130, 333, 264), (2048, 3072, 2048), (300, 2048, 8192),
