@@ -63,13 +63,13 @@ def peaks() -> dict:
 
 
 # ------------------------------------------------------------------ model folder
-def write_model_folder(folder: Path, layers: int, seed: int = 0) -> None:
+def write_model_folder(folder: Path, layers: int, seed: int = 0, model: dict | None = None) -> None:
     """config.json + model.safetensors with N(0, 0.02) bfloat16 weights, written with torch and safetensors only
-    (both arms read this folder through their own loaders)."""
+    (both arms read this folder through their own loaders).  ``model``: config.json contents (default: the 1B sizes)."""
     import torch
     from safetensors.torch import save_file
 
-    cfg = dict(MODEL, num_hidden_layers=layers)
+    cfg = dict(model or MODEL, num_hidden_layers=layers)
     h, i, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
     q = cfg["num_attention_heads"] * cfg["head_dim"]
     kv = cfg["num_key_value_heads"] * cfg["head_dim"]
@@ -91,6 +91,8 @@ def write_model_folder(folder: Path, layers: int, seed: int = 0) -> None:
         tensors[p + "mlp.gate_proj.weight"] = mat(i, h)
         tensors[p + "mlp.up_proj.weight"] = mat(i, h)
         tensors[p + "mlp.down_proj.weight"] = mat(h, i)
+    if not cfg.get("tie_word_embeddings", False):
+        tensors["lm_head.weight"] = mat(v, h)
     folder.mkdir(parents=True, exist_ok=True)
     save_file(tensors, str(folder / "model.safetensors"), metadata={"format": "pt"})
     (folder / "config.json").write_text(json.dumps(cfg))
@@ -354,6 +356,162 @@ def run_own(args) -> dict:
         shutil.rmtree(work, ignore_errors=True)
 
 
+# --------------------------------------------------------------- further workloads
+SIZES = {"1b": "llama-3.2-1b", "3b": "llama-3.2-3b", "8b": "llama-3.1-8b"}
+
+
+def _model_config(size: str) -> tuple[dict, int]:
+    from prefixserve_b200.config.presets import PRESETS
+    cfg = dict(PRESETS[SIZES[size]], architectures=["LlamaForCausalLM"])
+    return cfg, int(cfg["num_hidden_layers"])
+
+
+def run_shared_prefix(args) -> dict:
+    """The multi-tenant workload the reference is named for: requests whose prompts start with one of a few long system
+    prefixes, through the Python entry point (scheduler, prefix tree, chunked prefill, decode), once with the prefix
+    cache and once without.  Output tokens per second of wall-clock makespan, as the reference's simulator counts."""
+    import numpy as np
+    import torch
+
+    from prefixserve_b200 import LLM, SamplingParams
+
+    cfg, full_layers = _model_config(args.model)
+    layers = args.layers or full_layers
+    requests, tenants, prefix_len, decode_tokens = args.requests, 4, 1024, 256
+    rng = np.random.RandomState(0)
+    vocab = cfg["vocab_size"]
+    prefixes = [rng.randint(0, vocab, size=prefix_len).tolist() for _ in range(tenants)]
+    prompts = [prefixes[r % tenants] + rng.randint(0, vocab, size=int(rng.randint(64, 513))).tolist() for r in range(requests)]
+    work = Path(tempfile.mkdtemp(prefix="psb200-bench-"))
+    try:
+        write_model_folder(work, layers, model=cfg)
+        pages = requests * (-(-(prefix_len + 512 + decode_tokens) // PAGE)) + 256
+        runs = {}
+        for name, enabled in (("prefix_cache", True), ("no_prefix_cache", False)):
+            llm = LLM(work, dtype="bfloat16", max_seq_len=8192, num_blocks=pages, max_running_requests=min(requests, 64),
+                      chunked_prefill_size=2048, enable_prefix_cache=enabled)
+            llm.generate([prompts[0][:64]], SamplingParams(max_tokens=4, ignore_eos=True))  # first-use costs stay outside
+            base = llm.stats()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            outs = llm.generate(prompts, SamplingParams(max_tokens=decode_tokens, ignore_eos=True))
+            torch.cuda.synchronize()
+            wall = time.perf_counter() - t0
+            st = llm.stats()
+            prompt_tokens = st.prompt_tokens - base.prompt_tokens
+            cached = st.cached_prompt_tokens - base.cached_prompt_tokens
+            runs[name] = {"output_tokens_per_s": round(sum(len(o) for o in outs) / wall, 1), "makespan_s": round(wall, 3),
+                          "prompt_tokens": int(prompt_tokens), "prompt_tokens_computed": int(prompt_tokens - cached),
+                          "prefix_hit_rate": round(cached / max(prompt_tokens, 1), 4),
+                          "preemptions": int(st.preemptions - base.preemptions),
+                          "steps_launched_ahead": int(llm.engine.launched_ahead)}
+            del llm
+            torch.cuda.empty_cache()
+        on, off = runs["prefix_cache"], runs["no_prefix_cache"]
+        return {
+            "metric": "output tokens/s of makespan, multi-tenant shared-prefix workload through the entry point",
+            "value": on["output_tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "higher_is_better": True, "dtype": "bf16",
+            "data": "synthetic: seeded uniform-random token ids, N(0,0.02) random weights",
+            "config": {"model": SIZES[args.model] + " sizes", "layers": layers, "layers_full": full_layers, "requests": requests,
+                       "system_prefixes": tenants, "prefix_tokens": prefix_len, "suffix_tokens": "64-512", "decoded_tokens": decode_tokens,
+                       "max_seq_len": 8192, "page_size": PAGE, "pages": pages, "chunk_budget": 2048},
+            "prefix_cache": on, "no_prefix_cache": off,
+            "speedup_from_prefix_cache": round(on["output_tokens_per_s"] / max(off["output_tokens_per_s"], 1e-9), 3),
+        }
+    finally:
+        shutil.rmtree(work, ignore_errors=True)
+
+
+def run_mixed(args) -> dict:
+    """Steps that carry a 512-token prompt portion beside single decoded tokens of 64 requests at a long context:
+    the step function's general path (no graph), device-timed."""
+    import numpy as np
+    import torch
+
+    from prefixserve_b200.engine import Engine, EngineConfig, StepItem
+    from prefixserve_b200.sampling import SamplingParams
+    from prefixserve_b200.sampling.sampler import choose_tokens
+
+    pk = peaks()
+    cfg, full_layers = _model_config(args.model)
+    layers = args.layers or full_layers
+    decodes, chunk, context = args.batch if args.batch != 8 else 64, 512, args.context
+    rng = np.random.RandomState(0)
+    vocab = cfg["vocab_size"]
+    work = Path(tempfile.mkdtemp(prefix="psb200-bench-"))
+    try:
+        write_model_folder(work, layers, model=cfg)
+        steps, warmup = min(args.steps, 16), 3
+        pages = (decodes + 1) * (context // PAGE) + 64
+        engine = Engine(EngineConfig(model_path=work, dtype=torch.bfloat16, max_num_seqs=decodes + 1, max_prefill_tokens=2048,
+                                     max_seq_len=context, num_blocks=pages, page_size=PAGE, enable_prefix_cache=False))
+        runner, cache = engine.runner, engine.cache
+        start = context - (steps + warmup) - 1
+        slots = []
+        for _ in range(decodes):  # the decoding requests, prefilled through the step function
+            slot, at = cache.open(), 0
+            while at < start:
+                n = min(2048, start - at)
+                cache.reserve(slot, at + n)
+                runner.step([StepItem(slot, at, rng.randint(0, vocab, size=n).astype(np.int32), ())])
+                cache.advance(slot, at + n)
+                at += n
+            slots.append(slot)
+        prompt = cache.open()  # the request whose prompt arrives in portions; it starts over when it is full
+        greedy = SamplingParams()
+
+        def one_step() -> None:
+            nonlocal prompt
+            at = cache.position(prompt)
+            if at + chunk > context:
+                cache.close(prompt)
+                prompt, at = cache.open(), 0
+            items = [StepItem(prompt, at, rng.randint(0, vocab, size=chunk).astype(np.int32), ())]
+            cache.reserve(prompt, at + chunk)
+            for s in slots:
+                p = cache.position(s)
+                cache.reserve(s, p + 1)
+                items.append(StepItem(s, p, rng.randint(0, vocab, size=1).astype(np.int32), (0,)))
+            logits = runner.step(items)
+            choose_tokens(logits, [greedy] * decodes, [it.start + 1 for it in items[1:]])
+            for it in items:
+                cache.advance(it.slot, it.start + len(it.tokens))
+
+        for _ in range(warmup):
+            one_step()
+        torch.cuda.synchronize()
+        portion_context = cache.position(prompt)
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        w0 = time.perf_counter()
+        t0.record()
+        for _ in range(steps):
+            one_step()
+        t1.record()
+        torch.cuda.synchronize()
+        wall_ms = (time.perf_counter() - w0) * 1e3 / steps
+        ms = t0.elapsed_time(t1) / steps
+        h, i = cfg["hidden_size"], cfg["intermediate_size"]
+        q, kv = cfg["num_attention_heads"] * cfg["head_dim"], cfg["num_key_value_heads"] * cfg["head_dim"]
+        per_layer = (q + 2 * kv) * h + h * q + 3 * h * i
+        weights = 2 * (vocab * h + layers * per_layer)
+        kv_token = layers * 2 * kv * 2
+        bytes_step = weights + decodes * (context - steps // 2) * kv_token
+        flops = 2.0 * chunk * layers * per_layer + layers * 4.0 * chunk * (portion_context + chunk / 2) * q
+        bound_ms = max(bytes_step / (pk["hbm_gbs"] * 1e9), flops / (pk["bf16_tflops"] * 1e12)) * 1e3
+        return {
+            "metric": "tokens/s of steps that mix a 512-token prompt portion with single decoded tokens",
+            "value": round((decodes + chunk) / (ms * 1e-3), 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+            "ms_per_step": round(ms, 3), "ms_per_step_wall": round(wall_ms, 3), "higher_is_better": True, "dtype": "bf16",
+            "data": "synthetic: seeded uniform-random token ids, N(0,0.02) random weights",
+            "config": {"model": SIZES[args.model] + " sizes", "layers": layers, "layers_full": full_layers, "decoding_requests": decodes,
+                       "portion_tokens": chunk, "context": context, "page_size": PAGE},
+            "roofline": {"bound": "max(bytes/hbm, portion flops/peak)", "ms": round(bound_ms, 3), "frac": round(bound_ms / ms, 4),
+                         "of": pk["source"], "bytes_per_step": int(bytes_step), "flops_per_step": flops},
+        }
+    finally:
+        shutil.rmtree(work, ignore_errors=True)
+
+
 # ----------------------------------------------------------------- reference arm
 def run_reference(args) -> dict:
     ref = ROOT / "baseline" / "_ref"
@@ -445,13 +603,27 @@ def main() -> int:
     p.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
                    help="decode: only the device-timed decode steps; prefill: only the 2,048-token prefill (for profilers)")
     p.add_argument("--no-graphs", action="store_true", help="run decode steps without CUDA graphs (kernel launch lists)")
+    p.add_argument("--workload", choices=["decode", "shared-prefix", "mixed"], default="decode",
+                   help="decode: the headline line.  shared-prefix: 64 requests over 4 system prefixes through the entry "
+                        "point, prefix cache on and off.  mixed: steps of one 512-token prompt portion beside 64 decoded tokens")
+    p.add_argument("--model", choices=sorted(SIZES), default=None, help="layer sizes for --workload shared-prefix (8b) / mixed (3b)")
+    p.add_argument("--requests", type=int, default=64, help="requests of --workload shared-prefix")
+    p.add_argument("--context", type=int, default=8192, help="context of --workload mixed")
     args = p.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
         if int(os.environ.get("RANK", "0")) == 0:
             print(json.dumps({"unsupported": f"this engine runs on one GPU; --gpus {args.gpus} is not built", "n_gpus": args.gpus}))
         return 2
-    result = run_reference(args) if args.impl == "reference" else run_own(args)
+    if args.workload != "decode":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the reference arm runs the headline workload only"}))
+            return 0
+        args.model = args.model or ("8b" if args.workload == "shared-prefix" else "3b")
+        args.layers = None if args.layers == FULL_LAYERS and "--layers" not in sys.argv else args.layers
+        result = run_shared_prefix(args) if args.workload == "shared-prefix" else run_mixed(args)
+    else:
+        result = run_reference(args) if args.impl == "reference" else run_own(args)
     print(json.dumps(result))
     return 0
 

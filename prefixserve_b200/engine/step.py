@@ -221,7 +221,8 @@ class ModelRunner:
         if static:
             ctx.extras["static_kv_len"] = self.cache.max_seq_len
         rows = dev[o_rows: o_rows + s]
-        logits = self.model.forward(ctx, self.cache.view, rows)  # this step's result, computed eagerly
+        with library.pinned_stream():  # one look-up of the stream for the step's hundred-odd launches
+            logits = self.model.forward(ctx, self.cache.view, rows)  # this step's result, computed eagerly
         self.steps_run += 1
         if static:
             # Capture the same launches for later steps of this batch size.  Nothing runs during capture; the eager
@@ -231,7 +232,8 @@ class ModelRunner:
                 self._graph_pool = torch.cuda.graph_pool_handle()
             before = library.launches
             with torch.cuda.graph(graph, pool=self._graph_pool):
-                static_logits = self.model.forward(ctx, self.cache.view, rows)
+                with library.pinned_stream():  # the capture's own stream
+                    static_logits = self.model.forward(ctx, self.cache.view, rows)
             self._graphs[b] = _DecodeGraph(inputs=dev, logits=static_logits, graph=graph, kernels=library.launches - before)
             library.launches = before  # recorded, not run
         return logits

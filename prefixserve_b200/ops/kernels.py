@@ -11,7 +11,7 @@ import math
 import torch
 
 from .deferred import NormedRows
-from .library import KernelError, check, lib
+from .library import KernelError, check, lib, stream_handle
 
 F32, BF16 = 0, 1
 _CODES = {torch.float32: F32, torch.bfloat16: BF16}
@@ -39,7 +39,7 @@ def _i32(t: torch.Tensor, what: str) -> torch.Tensor:
 
 
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    return stream_handle()
 
 
 def _ptr(t: torch.Tensor | None) -> int | None:

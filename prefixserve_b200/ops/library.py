@@ -10,6 +10,8 @@ import ctypes
 import os
 from ctypes import c_float, c_int, c_int64, c_void_p
 
+import torch
+
 from ..build import ensure_kernels
 
 
@@ -116,6 +118,32 @@ def set_pdl(on: bool) -> None:
 
 def pdl_enabled() -> bool:
     return bool(lib().psb_get_pdl())
+
+
+_pinned_stream: int | None = None
+
+
+def stream_handle() -> int:
+    """The raw handle of the stream kernels are launched on: torch's current stream, looked up on every call unless a
+    step has pinned it (``pinned_stream``): the lookup costs more host time than the launch it serves."""
+    if _pinned_stream is not None:
+        return _pinned_stream
+    return torch.cuda.current_stream().cuda_stream
+
+
+class pinned_stream:
+    """Within the block, ``stream_handle()`` is torch's current stream as it was at entry.  For code that launches many
+    kernels on one stream and does not switch streams itself (a step of the engine, the capture of one)."""
+
+    def __enter__(self):
+        global _pinned_stream
+        self._before = _pinned_stream
+        _pinned_stream = torch.cuda.current_stream().cuda_stream
+        return self
+
+    def __exit__(self, *exc):
+        global _pinned_stream
+        _pinned_stream = self._before
 
 
 def tcgen05_status() -> int:

@@ -6,7 +6,7 @@ from typing import Sequence
 
 import torch
 
-from .library import check, lib
+from .library import check, lib, stream_handle
 
 
 # Tuning, set from measurements on B200 at Llama-1B sizes:
@@ -39,7 +39,7 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, wide:
         wide = (n + 15) // 16 < WIDE_BELOW_TILES and k // 32 >= 32
     y = torch.empty((m, n), dtype=out_dtype, device=x.device)
     check(lib().psb_gemm_small_m(x.data_ptr(), w.data_ptr(), y.data_ptr(), _OUT_CODE[out_dtype], m, n, k, 1 if wide else 0,
-                                 torch.cuda.current_stream().cuda_stream), "gemm_small_m")
+                                 stream_handle()), "gemm_small_m")
     return y
 
 
@@ -49,7 +49,7 @@ def gemm_stream(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> tor
     n = w.shape[0]
     y = torch.empty((m, n), dtype=out_dtype, device=x.device)
     check(lib().psb_gemm_stream(x.data_ptr(), w.data_ptr(), y.data_ptr(), _OUT_CODE[out_dtype], m, n, k, _sms(x.device),
-                                torch.cuda.current_stream().cuda_stream), "gemm_stream")
+                                stream_handle()), "gemm_stream")
     return y
 
 
@@ -58,7 +58,7 @@ def gemm_stream_gated(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     inter = w_gate_up.shape[0] // 2
     act = torch.empty((m, inter), dtype=torch.bfloat16, device=x.device)
     check(lib().psb_gemm_stream_gated(x.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(), m, inter, k, _sms(x.device),
-                                      torch.cuda.current_stream().cuda_stream), "gemm_stream_gated")
+                                      stream_handle()), "gemm_stream_gated")
     return act
 
 
@@ -88,7 +88,7 @@ def norm_linear_bf16(x, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor
     check(lib().psb_gemm_stream_norm(x.h.data_ptr(), None if x.pending is None else x.pending.data_ptr(), x.gain.data_ptr(),
                                      None if x.rows is None else x.rows.data_ptr(), None if new_h is None else new_h.data_ptr(),
                                      w.data_ptr(), y.data_ptr(), _OUT_CODE[out_dtype], m, n, k, x.eps, _sms(w.device),
-                                     torch.cuda.current_stream().cuda_stream), "gemm_stream_norm")
+                                     stream_handle()), "gemm_stream_norm")
     x.fused(new_h)
     return y
 
@@ -106,7 +106,7 @@ def norm_qkv_rope_bf16(x, w_qkv, positions, token_item, cos, sin, table, kv, hq,
         None if new_h is None else new_h.data_ptr(), w_qkv.data_ptr(), m, k, x.eps, _sms(w_qkv.device), positions.data_ptr(),
         token_item.data_ptr(), table.data_ptr(), table.shape[1], None if cos is None else cos.data_ptr(),
         None if sin is None else sin.data_ptr(), kv.data_ptr(), q.data_ptr(), hq, hkv, d, page_size, kv.shape[0],
-        0 if cos is None else cos.shape[0], torch.cuda.current_stream().cuda_stream), "gemm_stream_norm_rope")
+        0 if cos is None else cos.shape[0], stream_handle()), "gemm_stream_norm_rope")
     x.fused(new_h)
     return q
 
@@ -122,7 +122,7 @@ def norm_gated_linear_bf16(x, w_gate_up: torch.Tensor) -> torch.Tensor | None:
     check(lib().psb_gemm_stream_norm_gated(x.h.data_ptr(), None if x.pending is None else x.pending.data_ptr(), x.gain.data_ptr(),
                                            None if new_h is None else new_h.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(),
                                            m, inter, k, x.eps, _sms(w_gate_up.device),
-                                           torch.cuda.current_stream().cuda_stream), "gemm_stream_norm_gated")
+                                           stream_handle()), "gemm_stream_norm_gated")
     x.fused(new_h)
     return act
 
@@ -140,7 +140,7 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     n = w.shape[0]
     y = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
     check(lib().psb_gemm_tcgen05(x.data_ptr(), w.data_ptr(), y.data_ptr(), m, n, k, _sms(x.device),
-                                 torch.cuda.current_stream().cuda_stream), "gemm_tcgen05")
+                                 stream_handle()), "gemm_tcgen05")
     return y
 
 
@@ -150,7 +150,7 @@ def gemm_tcgen05_gated(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor
     inter = w_gate_up.shape[0] // 2
     act = torch.empty((m, inter), dtype=torch.bfloat16, device=x.device)
     check(lib().psb_gemm_tcgen05_gated(x.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(), m, inter, k, _sms(x.device),
-                                       torch.cuda.current_stream().cuda_stream), "gemm_tcgen05_gated")
+                                       stream_handle()), "gemm_tcgen05_gated")
     return act
 
 
@@ -188,12 +188,12 @@ def gated_linear_bf16(x: torch.Tensor, w_gate_up: torch.Tensor, limit: int | Non
     act = torch.empty((m, inter), dtype=torch.bfloat16, device=x.device)
     wide = 1 if (inter + 15) // 16 < WIDE_BELOW_TILES and k // 32 >= 32 else 0
     check(lib().psb_gemm_small_m_gated(x.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(), m, inter, k, wide,
-                                       torch.cuda.current_stream().cuda_stream), "gemm_small_m_gated")
+                                       stream_handle()), "gemm_small_m_gated")
     return act
 
 
 _sm_count: dict[int, int] = {}
-_scratch: dict[tuple[int, str], torch.Tensor] = {}
+_scratch: dict[tuple[int, str], list[torch.Tensor]] = {}
 
 
 def _sms(device: torch.device) -> int:
@@ -204,13 +204,13 @@ def _sms(device: torch.device) -> int:
 
 
 def _scratch_buffer(device: torch.device, name: str, numel: int) -> torch.Tensor:
-    """A float32 buffer that lives as long as the process and only ever grows (split-KV partial results)."""
+    """A float32 buffer that lives as long as the process (split-KV partial results).  When a larger one is needed a
+    new one is made and the old ones are KEPT: captured steps have their address baked in and go on using them."""
     key = (device.index if device.index is not None else torch.cuda.current_device(), name)
-    buf = _scratch.get(key)
-    if buf is None or buf.numel() < numel:
-        buf = torch.empty(max(numel, 1 << 16), dtype=torch.float32, device=device)
-        _scratch[key] = buf
-    return buf
+    held = _scratch.setdefault(key, [])
+    if not held or held[-1].numel() < numel:
+        held.append(torch.empty(max(numel, 1 << 16), dtype=torch.float32, device=device))
+    return held[-1]
 
 
 def attention_bf16_supported(head_dim: int, page_size: int) -> bool:
@@ -231,7 +231,7 @@ def attention_bf16(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, item_
         return None
     group = hq // hkv
     out = torch.empty((t, hq * d), dtype=torch.bfloat16, device=q.device)
-    stream = torch.cuda.current_stream().cuda_stream
+    stream = stream_handle()
     b = len(new_tokens)
     w = int(window or 0)
     singles = [kvl for n, kvl in zip(new_tokens, kv_lens) if n == 1]

@@ -155,6 +155,31 @@ def helpers_dtype(name):
     return {"float32": torch.float32, "bfloat16": torch.bfloat16}[name]
 
 
+def test_captured_steps_keep_their_split_scratch_when_later_captures_need_more(tmp_path):
+    """Many heads and a long maximum length: the split-KV scratch of the batch-1 step is larger than the buffer's
+    first size, and the captures for larger batches need more still.  The steps captured first keep the address they
+    were captured with, so that buffer has to stay alive (capturing empties the allocator's cache, which unmaps what
+    was freed): the batch-1 step must still run, and give what a fresh engine without the other captures gives."""
+    from prefixserve_b200 import LLM, SamplingParams
+    from prefixserve_b200.config import LlamaConfig
+    from prefixserve_b200.ops import tensorcore
+    from prefixserve_b200.weights import write_random_model
+    cfg = LlamaConfig(vocab_size=200, hidden_size=64, intermediate_size=96, num_layers=1, num_heads=32, num_kv_heads=8,
+                      head_dim=64, rms_norm_eps=1e-5, rope_theta=10000.0, rope_scaling=None, max_position_embeddings=8192,
+                      tie_word_embeddings=True)
+    folder = write_random_model(tmp_path / "wide", cfg, seed=2, std=0.2, gain_noise=0.1, dtype=torch.bfloat16)
+    prompt = helpers.random_tokens(200, 40, seed=4)
+    params = SamplingParams(max_tokens=12, ignore_eos=True)
+    alone = LLM(folder, dtype="bfloat16", max_seq_len=8192, num_blocks=64, max_running_requests=1)
+    want = alone.generate([prompt], params)
+    del alone
+    generations = len(next(iter(tensorcore._scratch.values()), []))
+    many = LLM(folder, dtype="bfloat16", max_seq_len=8192, num_blocks=64, max_running_requests=8)
+    assert len(next(iter(tensorcore._scratch.values()))) > max(generations, 1)   # the scratch did grow in between
+    assert many.generate([prompt], params) == want
+    many.engine.check_device_status()
+
+
 def test_long_decode_and_first_tokens(sharp):
     """A request decoded for hundreds of steps, and the logits of the very first tokens of a sequence."""
     from prefixserve_b200.engine.replay import Replayer

@@ -659,7 +659,8 @@ def test_rope_append_in_paired_order(dtype, hq, hkv, d, page):
 
 
 @pytest.mark.parametrize("m", [1, 5, 8, 13, 16])
-@pytest.mark.parametrize("hq,hkv,d,page,k", [(8, 2, 64, 16, 512), (3, 1, 48, 8, 96), (4, 4, 128, 32, 2048), (32, 8, 64, 16, 2048)])
+@pytest.mark.parametrize("hq,hkv,d,page,k", [(8, 2, 64, 16, 512), (3, 1, 48, 8, 96), (4, 4, 128, 32, 2048), (32, 8, 64, 16, 2048),
+                                              (32, 8, 128, 16, 4096), (6, 2, 128, 16, 3072)])
 @pytest.mark.parametrize("rotate", [True, False])
 def test_projection_rotation_and_append_in_one_kernel(m, hq, hkv, d, page, k, rotate):
     """Bit for bit what the norm-folded projection followed by the rotary kernel (paired order) produces."""
