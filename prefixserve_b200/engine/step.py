@@ -101,12 +101,13 @@ class ModelRunner:
                 raise EngineError(f"slot {it.slot}: position {end} exceeds max_seq_len {self.cache.max_seq_len}")
             if self.cache.shortfall(it.slot, end):
                 raise EngineError(f"slot {it.slot}: no pages reserved for positions up to {end}")
-            toks = np.asarray(it.tokens)
-            if toks.min() < 0 or toks.max() >= self.vocab_size:
-                raise EngineError(f"slot {it.slot}: token id outside [0, {self.vocab_size})")
             for w in it.want:
                 if not 0 <= w < n:
                     raise EngineError(f"slot {it.slot}: wanted offset {w} outside its {n} tokens")
+        every = np.concatenate([np.asarray(it.tokens).reshape(-1) for it in items])  # one pass instead of one per item
+        if every.min() < 0 or every.max() >= self.vocab_size:
+            bad = next(it.slot for it in items if np.min(it.tokens) < 0 or np.max(it.tokens) >= self.vocab_size)
+            raise EngineError(f"slot {bad}: token id outside [0, {self.vocab_size})")
 
     def _check_tables(self, items: Sequence[StepItem], tables: dict[int, np.ndarray]) -> None:
         page = self.cache.page_size

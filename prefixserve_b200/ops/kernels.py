@@ -242,9 +242,10 @@ def attention(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, positions:
         _dev(q, "queries"), _dev(kv, "cache entry"), _i32(table, "page table")
         if q.shape[1] % kv.shape[2] or kv.shape[4] != q.shape[2] or kv.shape[1] != 2:
             raise KernelError(f"cache entry {tuple(kv.shape)} does not fit queries {tuple(q.shape)}")
-        fast = attention_bf16(q, kv, table, ctx.item_start, ctx.kv_len, [it.end - it.start for it in ctx.items],
-                              [it.end for it in ctx.items], window=window, scale=scale,
-                              static_kv_len=getattr(ctx, "extras", {}).get("static_kv_len"))
+        extras = getattr(ctx, "extras", None)
+        fast = attention_bf16(q, kv, table, ctx.item_start, ctx.kv_len, None, None, window=window, scale=scale,
+                              static_kv_len=extras.get("static_kv_len") if extras is not None else None,
+                              plans=extras, items=ctx.items)
         if fast is not None:
             return fast
     return attention_generic(q, kv, table, positions, token_item, window=window, scale=scale)

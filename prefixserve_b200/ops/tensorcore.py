@@ -217,11 +217,44 @@ def attention_bf16_supported(head_dim: int, page_size: int) -> bool:
     return head_dim in (64, 128) and page_size >= 16 and page_size & (page_size - 1) == 0
 
 
+def _attention_plan(new_tokens: Sequence[int], kv_lens: Sequence[int], window: int, group: int, hkv: int, d: int, page: int,
+                    sms: int, static_kv_len: int | None) -> dict:
+    """Launch shapes of a step's attention, from the host copies of the items' lengths.  The same for every layer with
+    the same head counts and window, so a step works it out once."""
+    b = len(new_tokens)
+    singles = [kvl for n, kvl in zip(new_tokens, kv_lens) if n == 1]
+    if static_kv_len is not None:
+        singles = [static_kv_len] * b
+    plan = {"b": b, "use_decode": bool(singles) and group <= 16}
+    if plan["use_decode"]:
+        if window:  # keys a decode item reads, from the 16-aligned start of its window
+            longest = max(kvl - (max(0, kvl - window) // 16) * 16 for kvl in singles)
+        else:
+            longest = max(singles)
+        want = max(1, (DECODE_CTAS_PER_SM * sms) // max(1, b * hkv))
+        splits = max(1, min(want, -(-longest // MIN_KEY_RANGE)))  # shorter ranges cost more to merge than they save
+        plan["chunk"] = -(-(-(-longest // splits)) // 64) * 64
+        plan["max_splits"] = -(-longest // plan["chunk"])
+        plan["all_single"] = 1 if len(singles) == b else 0
+    portions = [n for n in new_tokens if not (plan["use_decode"] and n == 1)]
+    plan["tcgen05"] = bool(USE_TCGEN05 and portions and max(portions) >= TCGEN05_PREFILL_MIN_TOKENS
+                           and lib().psb_attention_prefill_tcgen05_supported(d, page))
+    if plan["tcgen05"]:
+        per_cta = lib().psb_attention_prefill_tcgen05_rows_per_cta()
+        plan["pairs"] = sum(-(-n // per_cta) for n in portions)
+    else:
+        rows = lib().psb_attention_prefill_rows_per_cta(d)
+        plan["tiles"] = sum(-(-(n * group) // rows) for n in portions)
+    return plan
+
+
 def attention_bf16(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, item_start: torch.Tensor, kv_len: torch.Tensor,
-                   new_tokens: Sequence[int], kv_lens: Sequence[int], *, window: int | None, scale: float,
-                   static_kv_len: int | None = None) -> torch.Tensor | None:
+                   new_tokens: Sequence[int] | None, kv_lens: Sequence[int] | None, *, window: int | None, scale: float,
+                   static_kv_len: int | None = None, plans: dict | None = None, items=None) -> torch.Tensor | None:
     """Tensor-core attention for a step.  ``new_tokens``/``kv_lens`` are the host copies of what ``item_start`` and
-    ``kv_len`` hold on the device.  Returns None when no kernel here takes the shape (the caller falls back).
+    ``kv_len`` hold on the device (or ``items`` with ``.start``/``.end``, read only when no plan is cached yet).
+    Returns None when no kernel here takes the shape (the caller falls back).  ``plans``: a dict that lives as long as
+    the step; layers with the same shape reuse the launch plan the first of them worked out.
 
     With ``static_kv_len`` (a step that is being captured for replay) the launch shapes are derived from that
     length instead of the items' own, so they are the same for every later step of the same batch size."""
@@ -230,23 +263,20 @@ def attention_bf16(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, item_
     if not attention_bf16_supported(d, page):
         return None
     group = hq // hkv
+    w = int(window or 0)
+    key = ("attention plan", w, hq, hkv, d, page)
+    plan = plans.get(key) if plans is not None else None
+    if plan is None:
+        if new_tokens is None:
+            new_tokens, kv_lens = [it.end - it.start for it in items], [it.end for it in items]
+        plan = _attention_plan(new_tokens, kv_lens, w, group, hkv, d, page, _sms(q.device), static_kv_len)
+        if plans is not None:
+            plans[key] = plan
     out = torch.empty((t, hq * d), dtype=torch.bfloat16, device=q.device)
     stream = stream_handle()
-    b = len(new_tokens)
-    w = int(window or 0)
-    singles = [kvl for n, kvl in zip(new_tokens, kv_lens) if n == 1]
-    if static_kv_len is not None:
-        singles = [static_kv_len] * b
-    use_decode = bool(singles) and group <= 16
-    if use_decode:
-        def span(kvl: int) -> int:  # keys a decode item reads, from the 16-aligned start of its window
-            lo = max(0, kvl - w) if w else 0
-            return kvl - (lo // 16) * 16
-        longest = max(span(kvl) for kvl in singles)
-        want = max(1, (DECODE_CTAS_PER_SM * _sms(q.device)) // max(1, b * hkv))
-        splits = max(1, min(want, -(-longest // MIN_KEY_RANGE)))  # shorter ranges cost more to merge than they save
-        chunk = -(-(-(-longest // splits)) // 64) * 64
-        max_splits = -(-longest // chunk)
+    b = plan["b"]
+    if plan["use_decode"]:
+        chunk, max_splits = plan["chunk"], plan["max_splits"]
         part_o = part_ml = None
         if max_splits > 1:
             part_o = _scratch_buffer(q.device, "attn_o", b * hq * max_splits * d)
@@ -255,20 +285,20 @@ def attention_bf16(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, item_
             q.data_ptr(), kv.data_ptr(), table.data_ptr(), table.shape[1], item_start.data_ptr(), kv_len.data_ptr(),
             out.data_ptr(), part_o.data_ptr() if part_o is not None else None,
             part_ml.data_ptr() if part_ml is not None else None, b, hq, hkv, d, page, w, float(scale), chunk, max_splits,
-            1 if len(singles) == b else 0, stream), "attention_decode")
-    portions = [n for n in new_tokens if not (use_decode and n == 1)]
-    if (USE_TCGEN05 and portions and max(portions) >= TCGEN05_PREFILL_MIN_TOKENS
-            and lib().psb_attention_prefill_tcgen05_supported(d, page) and q.is_contiguous() and kv.is_contiguous()):
-        per_cta = lib().psb_attention_prefill_tcgen05_rows_per_cta()
+            plan["all_single"], stream), "attention_decode")
+    if plan["tcgen05"] and q.is_contiguous() and kv.is_contiguous():
         check(lib().psb_attention_prefill_tcgen05(
             q.data_ptr(), kv.data_ptr(), table.data_ptr(), table.shape[1], item_start.data_ptr(), kv_len.data_ptr(),
-            out.data_ptr(), b, sum(-(-n // per_cta) for n in portions), t, hq, hkv, d, page, kv.shape[0], w, float(scale),
-            1 if use_decode else 0, stream), "attention_prefill_tcgen05")
+            out.data_ptr(), b, plan["pairs"], t, hq, hkv, d, page, kv.shape[0], w, float(scale),
+            1 if plan["use_decode"] else 0, stream), "attention_prefill_tcgen05")
         return out
-    rows = lib().psb_attention_prefill_rows_per_cta(d)
-    tiles = sum(-(-(n * group) // rows) for n in new_tokens if not (use_decode and n == 1))
+    tiles = plan.get("tiles")
+    if tiles is None:  # planned for the tcgen05 kernel, which these tensors' layout rules out
+        rows = lib().psb_attention_prefill_rows_per_cta(d)
+        new_tokens = new_tokens if new_tokens is not None else [it.end - it.start for it in items]
+        tiles = sum(-(-(n * group) // rows) for n in new_tokens if not (plan["use_decode"] and n == 1))
     if tiles:
         check(lib().psb_attention_prefill_bf16(
             q.data_ptr(), kv.data_ptr(), table.data_ptr(), table.shape[1], item_start.data_ptr(), kv_len.data_ptr(),
-            out.data_ptr(), b, tiles, hq, hkv, d, page, w, float(scale), 1 if use_decode else 0, stream), "attention_prefill")
+            out.data_ptr(), b, tiles, hq, hkv, d, page, w, float(scale), 1 if plan["use_decode"] else 0, stream), "attention_prefill")
     return out
