@@ -61,6 +61,14 @@ inline cudaError_t psb_launch(Kernel kernel, dim3 grid, dim3 block, size_t smem,
   return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
+// (x1, x2) turned by the angle whose cosine and sine are given.  Written with explicit roundings, so that every
+// kernel that rotates (the rotary kernels, the projection that rotates in its epilogue) rounds alike whatever the
+// compiler would make of the plain expression around it.
+__device__ __forceinline__ void rotate_pair(float x1, float x2, float cs, float sn, float& o1, float& o2) {
+  o1 = __fmaf_rn(x1, cs, -__fmul_rn(x2, sn));
+  o2 = __fmaf_rn(x2, cs, __fmul_rn(x1, sn));
+}
+
 template <typename T>
 __device__ __forceinline__ float to_float(T v);
 template <>

@@ -540,6 +540,18 @@ gemm_stream_norm_kernel(const float* __restrict__ h_in, const __nv_bfloat16* __r
     if (issued < units) issue();
     asm volatile("cp.async.commit_group;\n" ::: "memory");
   }
+  // So are the step's own inputs: the thread that will rotate and store pair j of token m (see the epilogue) looks up
+  // the token's position and page now, and the angles of each tile while the tile's products run.
+  int ep_pos = 0, ep_page = -1;
+  float ep_cos = 1.f, ep_sin = 0.f;
+  const bool ep_thread = ROPE && threadIdx.x < 8 * 8 * MT && (int)(threadIdx.x >> 3) < M;
+  if constexpr (ROPE) {
+    if (ep_thread) {
+      const int m = threadIdx.x >> 3;
+      ep_pos = rope.positions[m];
+      ep_page = rope.table[(size_t)rope.token_item[m] * rope.table_width + (ep_pos >> rope.page_shift)];
+    }
+  }
   pdl_wait();
 
   // ---- this warp's operand fragments of v * gain, and its share of sum(v^2)
@@ -592,6 +604,15 @@ gemm_stream_norm_kernel(const float* __restrict__ h_in, const __nv_bfloat16* __r
   uint32_t read_slot = ring0;
   int read_stage = 0;
   for (int ti = 0; ti < my_tiles; ++ti) {
+    if constexpr (ROPE) {
+      const int row0 = (blockIdx.x + ti * gridDim.x) * 16;
+      if (ep_thread && rope.cos_t && row0 < (rope.hq + rope.hkv) * rope.D) {
+        const int block = (row0 % rope.D) >> 4, j = threadIdx.x & 7;
+        const int safe = ep_pos < 0 ? 0 : (ep_pos >= rope.max_positions ? rope.max_positions - 1 : ep_pos);
+        ep_cos = rope.cos_t[(size_t)safe * (rope.D >> 1) + block * 8 + j];
+        ep_sin = rope.sin_t[(size_t)safe * (rope.D >> 1) + block * 8 + j];
+      }
+    }
     float acc[TILES][MT][4];
 #pragma unroll
     for (int tl = 0; tl < TILES; ++tl)
@@ -632,10 +653,9 @@ gemm_stream_norm_kernel(const float* __restrict__ h_in, const __nv_bfloat16* __r
     __syncthreads();  // also makes every warp's sum of squares visible (written before the first of these barriers)
     const int row0 = (blockIdx.x + ti * gridDim.x) * 16;
     if constexpr (ROPE) {
-      // a thread takes one pair (rows j and j+8 of the tile) of one token
-      for (int idx = threadIdx.x; idx < 8 * 8 * MT; idx += SW * 32) {
-        const int j = idx & 7, m = idx >> 3;
-        if (m >= M || row0 >= N) continue;
+      // a thread takes one pair (rows j and j+8 of the tile) of one token (8 * 8 * MT <= the CTA's threads)
+      if (ep_thread && row0 < N) {
+        const int j = threadIdx.x & 7, m = threadIdx.x >> 3;
         float total = 0.f;
 #pragma unroll
         for (int w = 0; w < SW; ++w) total += ssq_part[w][m];
@@ -647,21 +667,19 @@ gemm_stream_norm_kernel(const float* __restrict__ h_in, const __nv_bfloat16* __r
         lo = __bfloat162float(__float2bfloat16_rn(lo * inv));
         hi = __bfloat162float(__float2bfloat16_rn(hi * inv));
         const int D = rope.D, q_cols = rope.hq * D, k_cols = rope.hkv * D;
-        const int pos = rope.positions[m];
+        const int pos = ep_pos, page = ep_page;
         if (row0 < q_cols + k_cols) {
           const int within = row0 < q_cols ? row0 : row0 - q_cols;
           const int head = within / D, block = (within - head * D) >> 4;
           if (rope.cos_t) {
-            const int safe = pos < 0 ? 0 : (pos >= rope.max_positions ? rope.max_positions - 1 : pos);
-            const float cs = rope.cos_t[(size_t)safe * (D >> 1) + block * 8 + j], sn = rope.sin_t[(size_t)safe * (D >> 1) + block * 8 + j];
-            const float a = lo * cs - hi * sn, b = hi * cs + lo * sn;
+            float a, b;
+            rotate_pair(lo, hi, ep_cos, ep_sin, a, b);
             lo = a; hi = b;
           }
           __nv_bfloat16* dst = nullptr;
           if (row0 < q_cols) {
             dst = rope.q_out + ((size_t)m * rope.hq + head) * D;
           } else {
-            const int page = rope.table[(size_t)rope.token_item[m] * rope.table_width + (pos >> rope.page_shift)];
             if (page >= 0 && page < rope.num_pages)  // the host checks tables before launch; a bad id is skipped
               dst = rope.kv + ((((size_t)page * 2) * rope.hkv + head) << rope.page_shift) * D + (size_t)(pos & ((1 << rope.page_shift) - 1)) * D;
           }
@@ -672,7 +690,6 @@ gemm_stream_norm_kernel(const float* __restrict__ h_in, const __nv_bfloat16* __r
         } else {
           const int within = row0 - q_cols - k_cols;
           const int head = within / D, d0 = within - head * D;
-          const int page = rope.table[(size_t)rope.token_item[m] * rope.table_width + (pos >> rope.page_shift)];
           if (page >= 0 && page < rope.num_pages) {
             __nv_bfloat16* dst = rope.kv + ((((size_t)page * 2 + 1) * rope.hkv + head) << rope.page_shift) * D +
                                  (size_t)(pos & ((1 << rope.page_shift) - 1)) * D;

@@ -95,8 +95,7 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, const int32_t* __r
     float o1 = x1, o2 = x2;
     if (rotate) {
       const float cs = c[j], sn = s[j];
-      o1 = x1 * cs - x2 * sn;
-      o2 = x2 * cs + x1 * sn;
+      rotate_pair(x1, x2, cs, sn, o1, o2);
     }
     if (head < hq) {
       T* q = q_out + ((size_t)t * hq + head) * D;
@@ -159,8 +158,7 @@ __global__ void rope_append_vec_kernel(const T* __restrict__ qkv, const int32_t*
       load8v<float>(s + j, sn);
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
-        o1[k] = x1[k] * cs[k] - x2[k] * sn[k];
-        o2[k] = x2[k] * cs[k] + x1[k] * sn[k];
+        rotate_pair(x1[k], x2[k], cs[k], sn[k], o1[k], o2[k]);
       }
     } else {
 #pragma unroll
