@@ -709,6 +709,13 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
   const int lo_key = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
   const int splits = (kvl - (lo_key & ~15) + chunk - 1) / chunk;
   const size_t base = ((size_t)item * hq + head) * max_splits;
+  // The first eight ranges' partial outputs are asked for together with the maxima: where they lie does not depend on
+  // the weights, and this kernel is nothing but the latency of its loads.
+  float first[D / 32][8];
+#pragma unroll
+  for (int i = 0; i < D / 32; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) first[i][j] = j < splits ? part_o[(base + j) * D + lane + 32 * i] : 0.f;
   float m = -INFINITY;
   for (int s = lane; s < splits; s += 32) m = fmaxf(m, part_ml[(base + s) * 2]);
   m = warp_max(m);
@@ -726,8 +733,10 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
   for (int i = 0; i < D / 32; ++i) {
     const int d = lane + 32 * i;
     float o = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o = fmaf(j < splits ? weight[j] : 0.f, first[i][j], o);
     // eight ranges per round, all loads issued before any is used; ranges past the item's own are skipped by weight
-    for (int s0 = 0; s0 < splits; s0 += 8) {
+    for (int s0 = 8; s0 < splits; s0 += 8) {
       float v[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) v[j] = s0 + j < splits ? part_o[(base + s0 + j) * D + d] : 0.f;

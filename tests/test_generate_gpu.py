@@ -170,14 +170,21 @@ def test_captured_steps_keep_their_split_scratch_when_later_captures_need_more(t
     folder = write_random_model(tmp_path / "wide", cfg, seed=2, std=0.2, gain_noise=0.1, dtype=torch.bfloat16)
     prompt = helpers.random_tokens(200, 40, seed=4)
     params = SamplingParams(max_tokens=12, ignore_eos=True)
-    alone = LLM(folder, dtype="bfloat16", max_seq_len=8192, num_blocks=64, max_running_requests=1)
-    want = alone.generate([prompt], params)
-    del alone
-    generations = len(next(iter(tensorcore._scratch.values()), []))
-    many = LLM(folder, dtype="bfloat16", max_seq_len=8192, num_blocks=64, max_running_requests=8)
-    assert len(next(iter(tensorcore._scratch.values()))) > max(generations, 1)   # the scratch did grow in between
-    assert many.generate([prompt], params) == want
-    many.engine.check_device_status()
+    # start from no scratch at all, whatever ran before in this process; what earlier engines captured stays alive here
+    earlier = {key: list(held) for key, held in tensorcore._scratch.items()}
+    tensorcore._scratch.clear()
+    try:
+        alone = LLM(folder, dtype="bfloat16", max_seq_len=8192, num_blocks=64, max_running_requests=1)
+        want = alone.generate([prompt], params)
+        del alone
+        generations = len(next(iter(tensorcore._scratch.values()), []))
+        many = LLM(folder, dtype="bfloat16", max_seq_len=8192, num_blocks=64, max_running_requests=8)
+        assert len(next(iter(tensorcore._scratch.values()))) > max(generations, 1)   # the scratch did grow in between
+        assert many.generate([prompt], params) == want
+        many.engine.check_device_status()
+    finally:
+        for key, held in earlier.items():
+            tensorcore._scratch[key] = held + tensorcore._scratch.get(key, [])
 
 
 def test_long_decode_and_first_tokens(sharp):
