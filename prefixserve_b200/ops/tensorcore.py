@@ -170,6 +170,8 @@ def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> tor
             return gemm_small_m(x, w, out_dtype)
         if out_dtype == torch.bfloat16 and m > 0 and _tcgen05_ok(x, w):
             return gemm_tcgen05(x, w)
+    if out_dtype == torch.float32:  # logits of many rows: the sums leave the library in float32, never rounded to bfloat16
+        return torch.mm(x, w.t(), out_dtype=torch.float32)
     y = torch.nn.functional.linear(x, w)
     return y if out_dtype == y.dtype else y.to(out_dtype)
 

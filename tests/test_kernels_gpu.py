@@ -551,6 +551,20 @@ def test_gemm_stream_gated(m, inter, k):
     assert torch.allclose(got.double(), want, rtol=3e-2, atol=3e-2)
 
 
+@pytest.mark.parametrize("m", [1, 16, 17, 40, 200])
+def test_float32_outputs_of_bfloat16_products_are_never_rounded_to_bfloat16(m):
+    """Logits: whatever the number of rows, and so whichever kernel or library call does the product, the float32
+    result carries the float32 sums (a detour through a bfloat16 result would cost 8 bits)."""
+    from prefixserve_b200 import ops
+    n, k = 1000, 512
+    x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=DEV) / math.sqrt(k)).to(torch.bfloat16)
+    got = ops.linear(x, w, out_dtype=torch.float32)
+    want = x.double() @ w.double().t()
+    assert got.dtype == torch.float32
+    assert float((got.double() - want).abs().max()) <= 2e-5 * float(want.abs().max())
+
+
 # ---- the streaming product with the residual sum and the RMSNorm in front of it folded in ---------------------------
 
 def _plain_normed(h, pending, gain, eps, rows=None):
