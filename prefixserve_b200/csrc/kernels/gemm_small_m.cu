@@ -466,22 +466,6 @@ __device__ __forceinline__ void load8_any<__nv_bfloat16>(const __nv_bfloat16* p,
   }
 }
 
-// What the fused projection needs to finish the job of the rotary kernel (rope.cu) in its own epilogue: W is the
-// [queries; keys; values] matrix with the rows of every query and key head reordered so that a 16-row tile holds
-// 8 elements of the head's first half and the 8 elements they are rotated with (stored index 16b+j <-> natural
-// index 8b+j, stored 16b+8+j <-> natural D/2+8b+j).  Queries go to q_out [M, hq, D] and keys to the cache in that
-// stored order (a dot product does not care, as long as both sides agree); values in natural order.
-struct RopeArgs {
-  const int32_t* positions;   // [M] absolute position of each token
-  const int32_t* token_item;  // [M] row of the page table
-  const int32_t* table;       // [items, table_width] page ids
-  const float* cos_t;         // [max_positions, D/2], null: no rotation
-  const float* sin_t;
-  __nv_bfloat16* kv;          // [num_pages, 2, hkv, page_size, D]
-  __nv_bfloat16* q_out;       // [M, hq, D]
-  int table_width, hq, hkv, D, page_shift, num_pages, max_positions;
-};
-
 // CPW: most k chunks (of 32) a warp may own (K <= 512 * CPW).  ROPE: the epilogue rotates and appends (TILES == 1).
 template <int MT, int TILES, int CPW, typename TOut, bool ROPE = false>
 __global__ void __launch_bounds__(SW * 32, 1)

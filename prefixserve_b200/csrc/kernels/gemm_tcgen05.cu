@@ -47,11 +47,94 @@ constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + (
 using namespace tc;
 constexpr uint32_t INSTR_DESC = instr_desc(BM, BN, false);  // M=128, N=256, both operands K-major
 
-// gated: 0 plain (C[M, N], tile columns [n0, n0+128) and [n0+128, n0+256)); 1 gated (C[M, I], W = [gate; up], tile
-// columns [n0, n0+128) of the gate and the same of the up rows).
+// mode: 0 plain (C[M, N], tile columns [n0, n0+128) and [n0+128, n0+256)); 1 gated (C[M, I], W = [gate; up], tile
+// columns [n0, n0+128) of the gate and the same of the up rows); 2 the projection of an attention layer (columns as in
+// 0; the epilogue rotates queries and keys and stores queries, keys and values where RopeArgs says, C is not used).
+enum : int { MODE_PLAIN = 0, MODE_GATED = 1, MODE_ROPE = 2 };
+
+// One thread's row of a 128x256 tile of sums, for the projection of an attention layer: 16 columns are 8 pairs of one
+// head (first-half elements, then the ones they are rotated with), so the job of the rotary kernel is done on the sums
+// while they are in registers.  Each value is first rounded to bfloat16, which is what a separate projection would have
+// stored for the rotary kernel to read.  HB > 0: a head is HB blocks of 16 columns and the caller holds the angles of
+// the row's position in registers (cs, sn); HB == 0: any head size, angles fetched block by block.
+template <int HB>
+__device__ __forceinline__ void rope_store_row(uint32_t taddr, int row, int M, int n0, int N_out, const RopeArgs& rope, int pos,
+                                               int page, const float (&cs)[HB > 0 ? HB : 1][8],
+                                               const float (&sn)[HB > 0 ? HB : 1][8]) {
+  static_assert(HB % 2 == 0 && BN % (16 * (HB > 0 ? HB : 1)) == 0, "tiles must start at a head's first column");
+  constexpr int SPAN = HB > 0 ? 16 * HB : 32;  // columns per round: one head, or one load from tensor memory
+  const int D = rope.D, q_cols = rope.hq * D, k_cols = rope.hkv * D;
+  const int safe = pos < 0 ? 0 : (pos >= rope.max_positions ? rope.max_positions - 1 : pos);
+  const bool page_ok = page >= 0 && page < rope.num_pages;  // the host checks tables before launch; a bad id is skipped
+  const size_t in_page = (size_t)(pos & ((1 << rope.page_shift) - 1)) * D;
+#pragma unroll 1
+  for (int c0 = 0; c0 < BN; c0 += SPAN) {
+#pragma unroll
+    for (int cc = 0; cc < SPAN; cc += 32) {
+      uint32_t v[32];
+      tmem_ld32(taddr + c0 + cc, v);
+      tmem_ld_wait();
+      if (row >= M) continue;
+#pragma unroll
+      for (int b = 0; b < 2; ++b) {
+        const int col = n0 + c0 + cc + 16 * b;
+        if (col >= N_out) continue;
+        float lo[8], hi[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          lo[j] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[16 * b + j])));
+          hi[j] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[16 * b + 8 + j])));
+        }
+        __nv_bfloat16* dst = nullptr;
+        if (col < q_cols + k_cols) {
+          const int within = col < q_cols ? col : col - q_cols;
+          const int head = within / D;
+          const int blk = HB > 0 ? cc / 16 + b : (within - head * D) >> 4;
+          if (rope.cos_t) {
+            if constexpr (HB > 0) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                float a, r;
+                rotate_pair(lo[j], hi[j], cs[cc / 16 + b][j], sn[cc / 16 + b][j], a, r);
+                lo[j] = a; hi[j] = r;
+              }
+            } else {
+              const float4* cp = reinterpret_cast<const float4*>(rope.cos_t + (size_t)safe * (D >> 1) + blk * 8);
+              const float4* sp = reinterpret_cast<const float4*>(rope.sin_t + (size_t)safe * (D >> 1) + blk * 8);
+              const float4 c0v = __ldg(cp), c1v = __ldg(cp + 1), s0v = __ldg(sp), s1v = __ldg(sp + 1);
+              const float cv[8] = {c0v.x, c0v.y, c0v.z, c0v.w, c1v.x, c1v.y, c1v.z, c1v.w};
+              const float sv[8] = {s0v.x, s0v.y, s0v.z, s0v.w, s1v.x, s1v.y, s1v.z, s1v.w};
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                float a, r;
+                rotate_pair(lo[j], hi[j], cv[j], sv[j], a, r);
+                lo[j] = a; hi[j] = r;
+              }
+            }
+          }
+          if (col < q_cols) dst = rope.q_out + ((size_t)row * rope.hq + head) * D + blk * 16;
+          else if (page_ok) dst = rope.kv + ((((size_t)page * 2) * rope.hkv + head) << rope.page_shift) * D + in_page + blk * 16;
+        } else {
+          const int within = col - q_cols - k_cols;
+          const int head = within / D, d0 = within - head * D;
+          if (page_ok) dst = rope.kv + ((((size_t)page * 2 + 1) * rope.hkv + head) << rope.page_shift) * D + in_page + d0;
+        }
+        if (dst) {
+          reinterpret_cast<uint4*>(dst)[0] = make_uint4(pack2(lo[0], lo[1]), pack2(lo[2], lo[3]), pack2(lo[4], lo[5]), pack2(lo[6], lo[7]));
+          reinterpret_cast<uint4*>(dst)[1] = make_uint4(pack2(hi[0], hi[1]), pack2(hi[2], hi[3]), pack2(hi[4], hi[5]), pack2(hi[6], hi[7]));
+        }
+      }
+    }
+  }
+}
+
+// HB: see rope_store_row (0 unless mode is MODE_ROPE and the head size is 16 * HB).
+template <int HB>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                    __nv_bfloat16* __restrict__ C, int M, int N_out, int K, int ldc, int up_offset, int gated) {
+                    __nv_bfloat16* __restrict__ C, int M, int N_out, int K, int ldc, int up_offset, int mode,
+                    const RopeArgs rope) {
+  const bool gated = mode == MODE_GATED;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   Barriers* bars = reinterpret_cast<Barriers*>(tiles + STAGES * STAGE_BYTES);
@@ -148,13 +231,32 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const uint32_t buf = local & 1, use = local >> 1;
       const int m0 = (tile % m_blocks) * BM;
       const int n0 = (tile / m_blocks) * n_span;
+      const int row = m0 + quarter * 32 + lane;
+      int pos = 0, page = -1;
+      float cs[HB > 0 ? HB : 1][8], sn[HB > 0 ? HB : 1][8];  // HB > 0: the angles of this row's position, all of a head's pairs
+      if (mode == MODE_ROPE && row < M) {  // this row's token: where it stands and which page takes it (inputs of the step)
+        pos = rope.positions[row];
+        page = rope.table[(size_t)rope.token_item[row] * rope.table_width + (pos >> rope.page_shift)];
+        if (HB > 0 && rope.cos_t) {
+          const int safe = pos < 0 ? 0 : (pos >= rope.max_positions ? rope.max_positions - 1 : pos);
+          const float4* cp = reinterpret_cast<const float4*>(rope.cos_t + (size_t)safe * (rope.D >> 1));
+          const float4* sp = reinterpret_cast<const float4*>(rope.sin_t + (size_t)safe * (rope.D >> 1));
+#pragma unroll
+          for (int b = 0; b < (HB > 0 ? HB : 1); ++b) {
+            const float4 c0 = __ldg(cp + 2 * b), c1 = __ldg(cp + 2 * b + 1), s0 = __ldg(sp + 2 * b), s1 = __ldg(sp + 2 * b + 1);
+            cs[b][0] = c0.x; cs[b][1] = c0.y; cs[b][2] = c0.z; cs[b][3] = c0.w; cs[b][4] = c1.x; cs[b][5] = c1.y; cs[b][6] = c1.z; cs[b][7] = c1.w;
+            sn[b][0] = s0.x; sn[b][1] = s0.y; sn[b][2] = s0.z; sn[b][3] = s0.w; sn[b][4] = s1.x; sn[b][5] = s1.y; sn[b][6] = s1.z; sn[b][7] = s1.w;
+          }
+        }
+      }
       ok = mbar_wait(&bars->acc_full[buf], use & 1, abort, 3);
       if (!ok) break;
       fence_after();
-      const int row = m0 + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
       __nv_bfloat16* crow = C + (size_t)row * ldc;
-      if (gated) {
+      if (mode == MODE_ROPE) {
+        rope_store_row<HB>(taddr, row, M, n0, N_out, rope, pos, page, cs, sn);
+      } else if (gated) {
 #pragma unroll 1
         for (int c = 0; c < BN_HALF; c += 32) {
           uint32_t g[32], u[32];
@@ -236,24 +338,33 @@ int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) 
   return 0;
 }
 
-int launch(const void* a, const void* w, void* c, int M, int w_rows, int N_out, int K, int up_offset, int gated, int sms,
-           cudaStream_t stream) {
+int launch(const void* a, const void* w, void* c, int M, int w_rows, int N_out, int K, int up_offset, int mode, int sms,
+           cudaStream_t stream, const RopeArgs& rope = RopeArgs{}) {
+  const bool gated = mode == MODE_GATED;
   if (M < 1 || N_out < 1 || K < 8 || K % 8) PSB_REFUSE("gemm_tcgen05: needs K a multiple of 8 (M=%d N=%d K=%d)", M, N_out, K);
   if (((uintptr_t)a | (uintptr_t)w | (uintptr_t)c) & 15) PSB_REFUSE("gemm_tcgen05: operands must be 16-byte aligned");
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    if (e != cudaSuccess) PSB_REFUSE("gemm_tcgen05: cannot reserve %d bytes of shared memory: %s", SMEM_BYTES, cudaGetErrorString(e));
-    configured = true;
-  }
   CUtensorMap map_a, map_w;
   if (int rc = make_map(&map_a, a, M, K, BM)) return rc;
   if (int rc = make_map(&map_w, w, w_rows, K, BN_HALF)) return rc;
   const int n_span = gated ? BN_HALF : BN;
   const int tiles = ((M + BM - 1) / BM) * ((N_out + n_span - 1) / n_span);
   const int grid = tiles < sms ? tiles : sms;
-  psb_launch(gemm_tcgen05_kernel, dim3(grid), dim3(THREADS), (size_t)SMEM_BYTES, stream, map_a, map_w, (__nv_bfloat16*)c, M,
-             N_out, K, N_out, up_offset, gated);
+#define PSB_TCGEN05(HB)                                                                                              \
+  do {                                                                                                               \
+    static bool configured = false; /* more than 48 KB of dynamic shared memory has to be asked for once */           \
+    if (!configured) {                                                                                               \
+      cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<HB>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES); \
+      if (e != cudaSuccess) PSB_REFUSE("gemm_tcgen05: cannot reserve %d bytes of shared memory: %s", SMEM_BYTES, cudaGetErrorString(e)); \
+      configured = true;                                                                                             \
+    }                                                                                                                \
+    psb_launch(gemm_tcgen05_kernel<HB>, dim3(grid), dim3(THREADS), (size_t)SMEM_BYTES, stream, map_a, map_w,          \
+               (__nv_bfloat16*)c, M, N_out, K, N_out, up_offset, mode, rope);                                        \
+  } while (0)
+  // the usual head sizes keep a row's angles in registers; every other multiple of 16 fetches them block by block
+  if (mode == MODE_ROPE && rope.D == 64) PSB_TCGEN05(4);
+  else if (mode == MODE_ROPE && rope.D == 128) PSB_TCGEN05(8);
+  else PSB_TCGEN05(0);
+#undef PSB_TCGEN05
   PSB_LAUNCH_CHECK("gemm_tcgen05");
   return 0;
 }
@@ -262,12 +373,34 @@ int launch(const void* a, const void* w, void* c, int M, int w_rows, int N_out, 
 
 // C[M,N] = A[M,K] W[N,K]^T, all bfloat16 row-major, K % 8 == 0.  sms: CTAs to launch at most (the SM count).
 PSB_API int psb_gemm_tcgen05(const void* a, const void* w, void* c, int M, int N, int K, int sms, cudaStream_t stream) {
-  return launch(a, w, c, M, N, N, K, 0, 0, sms, stream);
+  return launch(a, w, c, M, N, N, K, 0, MODE_PLAIN, sms, stream);
 }
 
 // act[M,I] = silu(A Wg^T) * (A Wu^T) for W = [Wg; Wu] of shape [2I, K].
 PSB_API int psb_gemm_tcgen05_gated(const void* a, const void* w, void* act, int M, int I, int K, int sms, cudaStream_t stream) {
-  return launch(a, w, act, M, 2 * I, I, K, I, 1, sms, stream);
+  return launch(a, w, act, M, 2 * I, I, K, I, MODE_GATED, sms, stream);
+}
+
+// The projection of an attention layer for many tokens: A W^T with W = [queries; keys; values] [(hq + 2 hkv) D, K] in the
+// pair-interleaved row order described at RopeArgs (common.cuh); queries rotated into q_out [M, hq, D], keys rotated
+// and values as they are stored at the tokens' positions in the pages: what psb_gemm_tcgen05 followed by
+// psb_rope_append in its paired form would do, without the [M, (hq + 2 hkv) D] matrix in between.
+PSB_API int psb_gemm_tcgen05_rope(const void* a, const void* w, int M, int K, int sms, const void* positions, const void* token_item,
+                                  const void* table, int table_width, const void* cos_t, const void* sin_t, void* kv, void* q_out,
+                                  int hq, int hkv, int D, int page_size, int num_pages, int max_positions, cudaStream_t stream) {
+  if (hq < 1 || hkv < 1 || D < 16 || D % 16) PSB_REFUSE("gemm_tcgen05_rope: needs a head size that is a multiple of 16 (hq=%d hkv=%d D=%d)", hq, hkv, D);
+  if (page_size < 1 || (page_size & (page_size - 1)) || num_pages < 1 || table_width < 1) PSB_REFUSE("gemm_tcgen05_rope: page size %d must be a power of two (pages=%d, width=%d)", page_size, num_pages, table_width);
+  if (!positions || !token_item || !table || !kv || !q_out) PSB_REFUSE("gemm_tcgen05_rope: cache arguments missing");
+  if ((cos_t == nullptr) != (sin_t == nullptr) || (cos_t && max_positions < 1)) PSB_REFUSE("gemm_tcgen05_rope: angle tables incomplete");
+  if (((uintptr_t)kv | (uintptr_t)q_out | (uintptr_t)cos_t | (uintptr_t)sin_t) & 31) PSB_REFUSE("gemm_tcgen05_rope: cache, queries and angle tables must be 32-byte aligned");
+  RopeArgs rope;
+  rope.positions = (const int32_t*)positions; rope.token_item = (const int32_t*)token_item; rope.table = (const int32_t*)table;
+  rope.cos_t = (const float*)cos_t; rope.sin_t = (const float*)sin_t; rope.kv = (__nv_bfloat16*)kv; rope.q_out = (__nv_bfloat16*)q_out;
+  rope.table_width = table_width; rope.hq = hq; rope.hkv = hkv; rope.D = D; rope.num_pages = num_pages; rope.max_positions = max_positions;
+  rope.page_shift = 0;
+  while ((1 << rope.page_shift) < page_size) ++rope.page_shift;
+  const int N = (hq + 2 * hkv) * D;
+  return launch(a, w, q_out, M, N, N, K, 0, MODE_ROPE, sms, stream, rope);
 }
 
 // 0 while no bounded wait has ever run out on the current device; reading it synchronises with the device.

@@ -197,11 +197,12 @@ def pair_interleaved_order(head_dim: int) -> list[int]:
 def qkv_rope_append(x: NormedRows, w_qkv: torch.Tensor, positions: torch.Tensor, token_item: torch.Tensor,
                     cos: torch.Tensor | None, sin: torch.Tensor | None, table: torch.Tensor, kv: torch.Tensor, *,
                     num_heads: int, num_kv_heads: int, head_dim: int, page_size: int) -> torch.Tensor | None:
-    """rmsnorm(h + pending) @ w_qkv^T, rotation and append to the pages in one kernel, for few bfloat16 tokens and a
-    projection whose query and key rows are pair-interleaved.  Returns q [T, hq, D], or None when the kernel does not
-    take the case (the caller then runs the product and ``rope_append(..., paired=True)``)."""
-    from .tensorcore import norm_qkv_rope_bf16
-    if not (x.fusable and x.rows is None and x.dtype == torch.bfloat16 and w_qkv.dtype == torch.bfloat16
+    """rmsnorm(h + pending) @ w_qkv^T, rotation and append to the pages, for bfloat16 tokens and a projection whose
+    query and key rows are pair-interleaved: one kernel for few tokens (the norm folded in as well), the norm's kernel
+    and one product that rotates and stores in its epilogue for many.  Returns q [T, hq, D], or None when neither kernel
+    takes the case (the caller then runs the product and ``rope_append(..., paired=True)``)."""
+    from .tensorcore import norm_qkv_rope_bf16, tcgen05_qkv_rope_bf16
+    if not (x.rows is None and x.dtype == torch.bfloat16 and w_qkv.dtype == torch.bfloat16
             and kv.dtype == torch.bfloat16 and head_dim % 16 == 0 and page_size & (page_size - 1) == 0):
         return None
     _i32(positions, "positions"), _i32(token_item, "token-to-item map"), _i32(table, "page table"), _dev(kv, "cache entry")
@@ -212,7 +213,12 @@ def qkv_rope_append(x: NormedRows, w_qkv: torch.Tensor, positions: torch.Tensor,
     if cos is not None and (sin is None or cos.dtype != torch.float32 or cos.shape != sin.shape or cos.dim() != 2
                             or cos.shape[1] != head_dim // 2):
         raise KernelError(f"angle tables must be float32 [positions, {head_dim // 2}]")
-    return norm_qkv_rope_bf16(x, w_qkv, positions, token_item, cos, sin, table, kv, num_heads, num_kv_heads, head_dim, page_size)
+    if x.fusable:
+        q = norm_qkv_rope_bf16(x, w_qkv, positions, token_item, cos, sin, table, kv, num_heads, num_kv_heads, head_dim, page_size)
+        if q is not None:
+            return q
+    return tcgen05_qkv_rope_bf16(x.tensor(), w_qkv, positions, token_item, cos, sin, table, kv, num_heads, num_kv_heads,
+                                 head_dim, page_size)
 
 
 def attention_generic(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, positions: torch.Tensor,

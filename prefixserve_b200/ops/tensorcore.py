@@ -154,6 +154,21 @@ def gemm_tcgen05_gated(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor
     return act
 
 
+def tcgen05_qkv_rope_bf16(x: torch.Tensor, w_qkv, positions, token_item, cos, sin, table, kv, hq, hkv, d, page_size) -> torch.Tensor | None:
+    """The projection of an attention layer for many tokens on the tcgen05 kernel, rotation and append to the pages in
+    its epilogue; None when that kernel does not take the shape."""
+    if not (_tcgen05_ok(x, w_qkv) and kv.is_contiguous() and (cos is None or (cos.is_contiguous() and sin.is_contiguous()))):
+        return None
+    m, k = x.shape
+    q = torch.empty((m, hq, d), dtype=torch.bfloat16, device=x.device)
+    check(lib().psb_gemm_tcgen05_rope(
+        x.data_ptr(), w_qkv.data_ptr(), m, k, _sms(x.device), positions.data_ptr(), token_item.data_ptr(), table.data_ptr(),
+        table.shape[1], None if cos is None else cos.data_ptr(), None if sin is None else sin.data_ptr(), kv.data_ptr(),
+        q.data_ptr(), hq, hkv, d, page_size, kv.shape[0], 0 if cos is None else cos.shape[0], stream_handle()),
+        "gemm_tcgen05_rope")
+    return q
+
+
 def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     """x[M,K] @ w[N,K]^T for bfloat16 operands, float32 accumulation.
 

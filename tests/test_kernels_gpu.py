@@ -632,6 +632,41 @@ def test_norm_fused_linear_on_chosen_rows_and_gated():
         assert torch.allclose(x.residual().double(), v, rtol=0, atol=1e-6)
 
 
+@pytest.mark.parametrize("lens_new,lens_old", [([130], [0]), ([64, 1, 70, 3], [5, 40, 0, 17]), ([300, 45], [16, 31])])
+@pytest.mark.parametrize("hq,hkv,d,page,k", [(8, 2, 64, 16, 512), (3, 1, 48, 8, 96), (4, 4, 128, 32, 2048), (6, 2, 128, 16, 520)])
+@pytest.mark.parametrize("rotate", [True, False])
+def test_projection_of_many_tokens_rotates_and_appends_in_its_epilogue(monkeypatch, lens_new, lens_old, hq, hkv, d, page, k, rotate):
+    """The tcgen05 product with the rotary kernel's job in its epilogue: bit for bit what the same product followed by
+    the rotary kernel (paired order) leaves in the queries and in the pages, and nothing anywhere else in the pages."""
+    from prefixserve_b200 import ops
+    from prefixserve_b200.ops import library, tensorcore
+    monkeypatch.setattr(tensorcore, "TCGEN05_MIN_TILES", 1)
+    g = torch.Generator().manual_seed(sum(lens_new) + d)
+    table, _, num_pages = _paged_setup(torch.bfloat16, lens_new, lens_old, hq, hkv, d, page, seed=5)
+    positions = torch.cat([torch.arange(o, o + n) for o, n in zip(lens_old, lens_new)]).to(torch.int32).to(DEV)
+    token_item = torch.cat([torch.full((n,), i) for i, n in enumerate(lens_new)]).to(torch.int32).to(DEV)
+    t = sum(lens_new)
+    h = torch.randn(t, k, generator=g).to(DEV) * 2
+    pending = torch.randn(t, k, generator=g).to(torch.bfloat16).to(DEV)
+    gain = (1.0 + 0.2 * torch.randn(k, generator=g)).to(DEV)
+    w = (torch.randn((hq + 2 * hkv) * d, k, generator=g) / math.sqrt(k)).to(torch.bfloat16).to(DEV)
+    angles = torch.outer(torch.arange(400).float(), 1.0 / (10000.0 ** (torch.arange(0, d, 2).float() / d)))
+    cos, sin = (angles.cos().to(DEV).contiguous(), angles.sin().to(DEV).contiguous()) if rotate else (None, None)
+    args = dict(num_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page)
+    tab = table.to(DEV)
+    x = ops.NormedRows(h.clone(), pending, gain, 1e-5, torch.bfloat16)
+    kv_two = torch.full((num_pages, 2, hkv, page, d), 7.0, dtype=torch.bfloat16, device=DEV)
+    q_two = ops.rope_append(tensorcore.gemm_tcgen05(x.tensor(), w), positions, token_item, cos, sin, tab, kv_two, write_kv=True,
+                            paired=True, **args)
+    y = ops.NormedRows(h.clone(), pending, gain, 1e-5, torch.bfloat16)
+    kv_one = torch.full_like(kv_two, 7.0)
+    q_one = ops.qkv_rope_append(y, w, positions, token_item, cos, sin, tab, kv_one, **args)
+    assert q_one is not None and q_one.shape == (t, hq, d)
+    assert torch.equal(q_one, q_two) and torch.equal(kv_one, kv_two)
+    assert torch.equal(y.residual(), x.residual())
+    assert library.tcgen05_status() == 0
+
+
 def test_normed_rows_nobody_consumed_still_update_the_stream():
     from prefixserve_b200 import ops
     h = torch.randn(4, 64, device=DEV)
