@@ -24,40 +24,51 @@
 
 namespace {
 
-constexpr int BM = 128, BN_HALF = 128, BN = 2 * BN_HALF, BK = 64;
-constexpr int STAGES = 4;
+constexpr int BM = 128, BK = 64;
 constexpr int A_BYTES = BM * BK * 2;        // 16 KB
-constexpr int B_BYTES = BN * BK * 2;        // 32 KB
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int THREADS = 192;
-constexpr int TMEM_COLS = 512;              // two accumulator buffers of BN float32 columns
+constexpr int TMEM_COLS = 512;              // two accumulator buffers, 256 float32 columns apart
+constexpr int ACC_STRIDE = 256;
+constexpr int MAX_STAGES = 5;
+
+// The output tile is 128 rows by BN columns: 256 where that fills the SMs evenly, 192 where it does not (a product of
+// 192 tiles of 256 columns takes 148 CTAs two rounds, as 256 tiles of 192 columns two rounds of three quarters the size).
+template <int BN>
+struct Tile {
+  static_assert(BN == 256 || BN == 192, "tile widths built");
+  static constexpr int HALF = BN / 2;                  // rows of W per TMA load
+  static constexpr int B_BYTES = BN * BK * 2;          // 32 or 24 KB
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = BN == 256 ? 4 : 5;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+  static_assert(STAGES <= MAX_STAGES && SMEM_BYTES <= 227 * 1024, "beyond a CTA's shared memory");
+};
 
 // shared memory: [stages][A | B] (1024-byte aligned), then barriers and the tensor-memory address
 struct Barriers {
-  uint64_t full[STAGES];
-  uint64_t empty[STAGES];
+  uint64_t full[MAX_STAGES];
+  uint64_t empty[MAX_STAGES];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
   uint32_t tmem_base;
   uint32_t abort;
 };
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + (int)sizeof(Barriers);
+static_assert(sizeof(Barriers) <= 256, "room kept for the barriers");
 
 // status word: 0 ok; otherwise which wait gave up (1 producer, 2 mma, 3 epilogue, 4 mma/acc)
 using namespace tc;
-constexpr uint32_t INSTR_DESC = instr_desc(BM, BN, false);  // M=128, N=256, both operands K-major
 
-// mode: 0 plain (C[M, N], tile columns [n0, n0+128) and [n0+128, n0+256)); 1 gated (C[M, I], W = [gate; up], tile
+// mode: 0 plain (C[M, N], tile columns [n0, n0+BN/2) and [n0+BN/2, n0+BN)); 1 gated (C[M, I], W = [gate; up], tile
 // columns [n0, n0+128) of the gate and the same of the up rows); 2 the projection of an attention layer (columns as in
 // 0; the epilogue rotates queries and keys and stores queries, keys and values where RopeArgs says, C is not used).
 enum : int { MODE_PLAIN = 0, MODE_GATED = 1, MODE_ROPE = 2 };
 
-// One thread's row of a 128x256 tile of sums, for the projection of an attention layer: 16 columns are 8 pairs of one
+// One thread's row of a 128 x BN tile of sums, for the projection of an attention layer: 16 columns are 8 pairs of one
 // head (first-half elements, then the ones they are rotated with), so the job of the rotary kernel is done on the sums
 // while they are in registers.  Each value is first rounded to bfloat16, which is what a separate projection would have
 // stored for the rotary kernel to read.  HB > 0: a head is HB blocks of 16 columns and the caller holds the angles of
 // the row's position in registers (cs, sn); HB == 0: any head size, angles fetched block by block.
-template <int HB>
+template <int BN, int HB>
 __device__ __forceinline__ void rope_store_row(uint32_t taddr, int row, int M, int n0, int N_out, const RopeArgs& rope, int pos,
                                                int page, const float (&cs)[HB > 0 ? HB : 1][8],
                                                const float (&sn)[HB > 0 ? HB : 1][8]) {
@@ -128,12 +139,15 @@ __device__ __forceinline__ void rope_store_row(uint32_t taddr, int row, int M, i
   }
 }
 
-// HB: see rope_store_row (0 unless mode is MODE_ROPE and the head size is 16 * HB).
-template <int HB>
+// BN: see Tile.  HB: see rope_store_row (0 unless mode is MODE_ROPE and the head size is 16 * HB).
+template <int BN, int HB>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     __nv_bfloat16* __restrict__ C, int M, int N_out, int K, int ldc, int up_offset, int mode,
                     const RopeArgs rope) {
+  using T = Tile<BN>;
+  constexpr int BN_HALF = T::HALF, STAGES = T::STAGES, STAGE_BYTES = T::STAGE_BYTES;
+  constexpr uint32_t INSTR_DESC = instr_desc(BM, BN, false);  // M=128, N=BN, both operands K-major
   const bool gated = mode == MODE_GATED;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -204,7 +218,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         fence_after();
-        const uint32_t acc = tmem_base + buf * BN;
+        const uint32_t acc = tmem_base + buf * ACC_STRIDE;
         for (int kb = 0; kb < k_blocks; ++kb) {
           ok = mbar_wait(&bars->full[stage], phase, abort, 2);  // filled by TMA: no tensor-memory fence needed
           if (!ok) break;
@@ -252,10 +266,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       ok = mbar_wait(&bars->acc_full[buf], use & 1, abort, 3);
       if (!ok) break;
       fence_after();
-      const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
+      const uint32_t taddr = tmem_base + buf * ACC_STRIDE + ((uint32_t)(quarter * 32) << 16);
       __nv_bfloat16* crow = C + (size_t)row * ldc;
       if (mode == MODE_ROPE) {
-        rope_store_row<HB>(taddr, row, M, n0, N_out, rope, pos, page, cs, sn);
+        rope_store_row<BN, HB>(taddr, row, M, n0, N_out, rope, pos, page, cs, sn);
       } else if (gated) {
 #pragma unroll 1
         for (int c = 0; c < BN_HALF; c += 32) {
@@ -338,32 +352,44 @@ int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) 
   return 0;
 }
 
+int g_forced_width = 0;  // 0: the launcher chooses the tile width; 192 or 256: tests compare the two
+
 int launch(const void* a, const void* w, void* c, int M, int w_rows, int N_out, int K, int up_offset, int mode, int sms,
            cudaStream_t stream, const RopeArgs& rope = RopeArgs{}) {
   const bool gated = mode == MODE_GATED;
   if (M < 1 || N_out < 1 || K < 8 || K % 8) PSB_REFUSE("gemm_tcgen05: needs K a multiple of 8 (M=%d N=%d K=%d)", M, N_out, K);
   if (((uintptr_t)a | (uintptr_t)w | (uintptr_t)c) & 15) PSB_REFUSE("gemm_tcgen05: operands must be 16-byte aligned");
+  // Tile width: 256 columns unless 192 get the product done in fewer or shorter rounds over the SMs (the gated form
+  // and 128-wide heads held in registers need 256).
+  const int m_blocks = (M + BM - 1) / BM;
+  auto rounds_cost = [&](int bn) { return ((m_blocks * ((N_out + bn - 1) / bn) + sms - 1) / sms) * bn; };
+  const bool may_narrow = !gated && !(mode == MODE_ROPE && rope.D == 128);
+  const bool narrow = may_narrow && (g_forced_width ? g_forced_width == 192 : rounds_cost(192) * 10 <= rounds_cost(256) * 9);
+  const int bn = narrow ? 192 : 256;
   CUtensorMap map_a, map_w;
   if (int rc = make_map(&map_a, a, M, K, BM)) return rc;
-  if (int rc = make_map(&map_w, w, w_rows, K, BN_HALF)) return rc;
-  const int n_span = gated ? BN_HALF : BN;
-  const int tiles = ((M + BM - 1) / BM) * ((N_out + n_span - 1) / n_span);
+  if (int rc = make_map(&map_w, w, w_rows, K, bn / 2)) return rc;
+  const int n_span = gated ? bn / 2 : bn;
+  const int tiles = m_blocks * ((N_out + n_span - 1) / n_span);
   const int grid = tiles < sms ? tiles : sms;
-#define PSB_TCGEN05(HB)                                                                                              \
+#define PSB_TCGEN05(BN, HB)                                                                                          \
   do {                                                                                                               \
     static bool configured = false; /* more than 48 KB of dynamic shared memory has to be asked for once */           \
     if (!configured) {                                                                                               \
-      cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<HB>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES); \
-      if (e != cudaSuccess) PSB_REFUSE("gemm_tcgen05: cannot reserve %d bytes of shared memory: %s", SMEM_BYTES, cudaGetErrorString(e)); \
+      cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, HB>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                           Tile<BN>::SMEM_BYTES);                                                    \
+      if (e != cudaSuccess) PSB_REFUSE("gemm_tcgen05: cannot reserve %d bytes of shared memory: %s", Tile<BN>::SMEM_BYTES, cudaGetErrorString(e)); \
       configured = true;                                                                                             \
     }                                                                                                                \
-    psb_launch(gemm_tcgen05_kernel<HB>, dim3(grid), dim3(THREADS), (size_t)SMEM_BYTES, stream, map_a, map_w,          \
-               (__nv_bfloat16*)c, M, N_out, K, N_out, up_offset, mode, rope);                                        \
+    psb_launch(gemm_tcgen05_kernel<BN, HB>, dim3(grid), dim3(THREADS), (size_t)Tile<BN>::SMEM_BYTES, stream, map_a,   \
+               map_w, (__nv_bfloat16*)c, M, N_out, K, N_out, up_offset, mode, rope);                                 \
   } while (0)
   // the usual head sizes keep a row's angles in registers; every other multiple of 16 fetches them block by block
-  if (mode == MODE_ROPE && rope.D == 64) PSB_TCGEN05(4);
-  else if (mode == MODE_ROPE && rope.D == 128) PSB_TCGEN05(8);
-  else PSB_TCGEN05(0);
+  if (mode == MODE_ROPE && rope.D == 128) PSB_TCGEN05(256, 8);
+  else if (mode == MODE_ROPE && rope.D == 64 && narrow) PSB_TCGEN05(192, 4);
+  else if (mode == MODE_ROPE && rope.D == 64) PSB_TCGEN05(256, 4);
+  else if (narrow) PSB_TCGEN05(192, 0);
+  else PSB_TCGEN05(256, 0);
 #undef PSB_TCGEN05
   PSB_LAUNCH_CHECK("gemm_tcgen05");
   return 0;
@@ -401,6 +427,13 @@ PSB_API int psb_gemm_tcgen05_rope(const void* a, const void* w, int M, int K, in
   while ((1 << rope.page_shift) < page_size) ++rope.page_shift;
   const int N = (hq + 2 * hkv) * D;
   return launch(a, w, q_out, M, N, N, K, 0, MODE_ROPE, sms, stream, rope);
+}
+
+// For tests: 192 or 256 makes every later product use that tile width where the shape allows it, 0 gives the choice back.
+PSB_API int psb_gemm_tcgen05_tile_width(int width) {
+  if (width != 0 && width != 192 && width != 256) PSB_REFUSE("gemm_tcgen05: tile widths are 192 and 256, not %d", width);
+  g_forced_width = width;
+  return 0;
 }
 
 // 0 while no bounded wait has ever run out on the current device; reading it synchronises with the device.

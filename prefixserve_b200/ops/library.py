@@ -79,6 +79,7 @@ _SIGNATURES: dict[str, list] = {
     "psb_gemm_tcgen05": [P, P, P, I, I, I, I, P],
     # (a, w, act, M, I, K, sms, stream)
     "psb_gemm_tcgen05_gated": [P, P, P, I, I, I, I, P],
+    "psb_gemm_tcgen05_tile_width": [I],
     "psb_gemm_tcgen05_rope": [P, P, I, I, I, P, P, P, I, P, P, P, P, I, I, I, I, I, I, P],
     # () -> 0 while no bounded wait of the tcgen05 kernel has ever run out
     "psb_tcgen05_status": [],
