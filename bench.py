@@ -591,6 +591,50 @@ def run_reference(args) -> dict:
         shutil.rmtree(work, ignore_errors=True)
 
 
+def run_timeline(args) -> dict:
+    """--only decode|prefill under the torch profiler: when every kernel of the last step started and ended on the
+    device (also inside a replayed CUDA graph, which a launch list under ncu serialises and so cannot show).  A
+    kernel's "serial" time is its end minus the latest end before it: what it adds to the step, waits included."""
+    import re
+    import tempfile as tf
+
+    from torch.profiler import ProfilerActivity, profile
+
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        base = run_own(args)
+    with tf.TemporaryDirectory() as tmp:
+        trace = Path(tmp) / "trace.json"
+        prof.export_chrome_trace(str(trace))
+        events = json.loads(trace.read_text())["traceEvents"]
+    kernels = sorted((e for e in events if e.get("cat") == "kernel"), key=lambda e: e["ts"])
+    first = [i for i, e in enumerate(kernels) if "embedding_kernel" in e["name"]]
+    if not first:
+        return {**base, "timeline": "no step found in the trace"}
+    last = first[-1]
+    if args.only == "decode":  # the timed steps end with the sampling kernels; the last complete step
+        ends = [i for i, e in enumerate(kernels) if "sample_finish" in e["name"]]
+        last = max(i for i in first if any(j > i for j in ends))
+        step = kernels[last: min(j for j in ends if j > last) + 1]
+    else:
+        step = kernels[last:]
+
+    def short(name: str) -> str:
+        m = re.search(r"(\w+_kernel)(<[^>]*>)?", name)
+        return (m.group(1) + (m.group(2) or "")) if m else name[:48]
+
+    t0 = prev_end = step[0]["ts"]
+    rows: dict[str, list] = {}
+    for e in step:
+        end = e["ts"] + e["dur"]
+        row = rows.setdefault(short(e["name"]), [0, 0.0])
+        row[0] += 1
+        row[1] += max(end - prev_end, 0.0)
+        prev_end = max(prev_end, end)
+    table = [{"kernel": k, "launches": n, "serial_us_each": round(t / n, 2), "serial_us_total": round(t, 1)}
+             for k, (n, t) in sorted(rows.items(), key=lambda kv: -kv[1][1])]
+    return {**base, "step_span_us": round(prev_end - t0, 1), "kernels_in_step": len(step), "timeline": table}
+
+
 def main() -> int:
     p = argparse.ArgumentParser()
     p.add_argument("--gpus", type=int, default=1)
@@ -603,6 +647,9 @@ def main() -> int:
     p.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
                    help="decode: only the device-timed decode steps; prefill: only the 2,048-token prefill (for profilers)")
     p.add_argument("--no-graphs", action="store_true", help="run decode steps without CUDA graphs (kernel launch lists)")
+    p.add_argument("--timeline", action="store_true",
+                   help="with --only decode|prefill: start and end of every kernel of the last step, from the torch profiler "
+                        "(numbers of a profiled run are not bench values)")
     p.add_argument("--workload", choices=["decode", "shared-prefix", "mixed"], default="decode",
                    help="decode: the headline line.  shared-prefix: 64 requests over 4 system prefixes through the entry "
                         "point, prefix cache on and off.  mixed: steps of one 512-token prompt portion beside 64 decoded tokens")
@@ -623,7 +670,10 @@ def main() -> int:
         args.layers = None if args.layers == FULL_LAYERS and "--layers" not in sys.argv else args.layers
         result = run_shared_prefix(args) if args.workload == "shared-prefix" else run_mixed(args)
     else:
-        result = run_reference(args) if args.impl == "reference" else run_own(args)
+        if args.timeline and (args.impl != "own" or args.only == "all"):
+            print(json.dumps({"unsupported": "--timeline needs --only decode or --only prefill of this engine"}))
+            return 2
+        result = run_reference(args) if args.impl == "reference" else (run_timeline(args) if args.timeline else run_own(args))
     print(json.dumps(result))
     return 0
 
