@@ -88,6 +88,63 @@ def test_bfloat16_close_to_float32_truth(folders, truth, which, kind):
         assert ours < 0.15 and ours <= 1.5 * theirs + 1e-3, f"{which}/{kind}/{rid}: engine {ours:.4f}, plain bf16 {theirs:.4f}"
 
 
+@pytest.mark.parametrize("which", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("kind", list(TRACES))
+def test_bfloat16_with_weights_stored_in_bfloat16(tmp_path, which, kind):
+    """The same with a checkpoint in bfloat16: every product then runs on the bfloat16 kernels (a tensor that a
+    checkpoint stores in float32 stays float32 and takes the float32 product, which is what the test above sees)."""
+    folder = helpers.make_folder(tmp_path / f"tiny{which}16", which, dtype=torch.bfloat16)
+    cfg, tensors = plain_model.read_folder(folder)
+    assert all(t.dtype == torch.bfloat16 for t in tensors.values())
+    seqs = sequences(which)
+    rows = replay(folder, "bfloat16", TRACES[kind](seqs))
+    for rid, toks in seqs.items():
+        want = plain_model.forward(cfg, tensors, toks)
+        got = torch.stack([rows[(rid, p)] for p in range(len(toks))])
+        plain_bf16 = plain_model.forward(cfg, tensors, toks, dtype=torch.bfloat16)
+        ours, theirs = helpers.rel_err(got, want), helpers.rel_err(plain_bf16, want)
+        assert ours < 0.15 and ours <= 1.5 * theirs + 1e-3, f"{which}/{kind}/{rid}: engine {ours:.4f}, plain bf16 {theirs:.4f}"
+
+
+@pytest.mark.parametrize("kind", list(TRACES))
+def test_bfloat16_with_the_prefill_kernels_on_small_shapes(tmp_path, kind, monkeypatch):
+    """The tcgen05 products (plain, gated, and the projection that rotates and appends in its epilogue) and tcgen05
+    attention normally wait for prompt-sized work.  Here every portion that has their head size takes them, inside
+    the whole engine: cache, portions cut anywhere, other requests in the batch, pages used again.  The weights are
+    stored in bfloat16 (tensors stored in float32 stay so and go to the float32 product)."""
+    from prefixserve_b200.ops import library, tensorcore
+    folder = helpers.make_folder(tmp_path / "tinyD16", "D", dtype=torch.bfloat16)
+    cfg, tensors = plain_model.read_folder(folder)
+    monkeypatch.setattr(tensorcore, "TCGEN05_MIN_TILES", 1)
+    monkeypatch.setattr(tensorcore, "TCGEN05_PREFILL_MIN_TOKENS", 2)
+    taken = {"projection": 0, "gated": 0}
+    projection, gated = tensorcore.tcgen05_qkv_rope_bf16, tensorcore.gemm_tcgen05_gated
+
+    def count_projection(*args, **kwargs):
+        out = projection(*args, **kwargs)
+        taken["projection"] += out is not None
+        return out
+
+    def count_gated(*args, **kwargs):
+        taken["gated"] += 1
+        return gated(*args, **kwargs)
+
+    monkeypatch.setattr(tensorcore, "tcgen05_qkv_rope_bf16", count_projection)
+    monkeypatch.setattr(tensorcore, "gemm_tcgen05_gated", count_gated)
+    before = library.launches
+    seqs = sequences("D")
+    steps = TRACES[kind](seqs)
+    rows = replay(folder, "bfloat16", steps)
+    assert library.launches > before and library.tcgen05_status() == 0
+    assert taken["projection"] > 0 and taken["gated"] > 0, taken   # the paths under test were taken
+    for rid, toks in seqs.items():
+        want = plain_model.forward(cfg, tensors, toks)
+        got = torch.stack([rows[(rid, p)] for p in range(len(toks))])
+        plain_bf16 = plain_model.forward(cfg, tensors, toks, dtype=torch.bfloat16)
+        ours, theirs = helpers.rel_err(got, want), helpers.rel_err(plain_bf16, want)
+        assert ours < 0.15 and ours <= 1.5 * theirs + 1e-3, f"D/{kind}/{rid}: engine {ours:.4f}, plain bf16 {theirs:.4f}"
+
+
 def test_cuttings_agree_in_float32(folders):
     """The same request cut four ways gives the same logits up to rounding."""
     seqs = sequences("B")
