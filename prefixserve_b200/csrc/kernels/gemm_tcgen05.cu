@@ -1,17 +1,20 @@
 // C[M,N] = A[M,K] * W[N,K]^T in bfloat16 on the 5th-generation tensor cores, for many rows (prefill).
 //
-// Persistent, warp-specialised CTAs (one per SM), 192 threads:
-//   warp 0      producer: one lane issues TMA loads (cp.async.bulk.tensor.2d) of a 128x64 tile of A and two 128x64
-//               tiles of W per stage into 128-byte-swizzled shared memory; completion by mbarrier transaction bytes;
-//   warp 1      MMA: one lane issues tcgen05.mma (cta_group::1, kind::f16, M=128, N=256, K=16; four per stage) with
-//               shared-memory matrix descriptors; accumulators are float32 in tensor memory (two buffers of 256
-//               columns, so the epilogue of one tile overlaps the main loop of the next); tcgen05.commit hands stages
-//               back to the producer and finished accumulators to the epilogue;
+// Persistent, warp-specialised CTAs (one per SM), 192 threads, output tiles of 128 rows by BN columns (256 or 192):
+//   warp 0      producer: one lane issues TMA loads (cp.async.bulk.tensor.2d) of a 128x64 tile of A and two
+//               (BN/2)x64 tiles of W per stage into 128-byte-swizzled shared memory; completion by mbarrier
+//               transaction bytes;
+//   warp 1      MMA: an elected lane issues tcgen05.mma (cta_group::1, kind::f16, M=128, N=BN, K=16; four per stage)
+//               with shared-memory matrix descriptors; accumulators are float32 in tensor memory (two buffers 256
+//               columns apart, so the epilogue of one tile overlaps the main loop of the next); tcgen05.commit hands
+//               stages back to the producer and finished accumulators to the epilogue;
 //   warps 2..5  epilogue: tcgen05.ld (32 lanes x 32 columns per instruction) -> registers -> bfloat16 -> global.
-// The two W tiles of a stage are rows [n0, n0+128) and [n1, n1+128): for a plain product n1 = n0 + 128; for the
+// The two W tiles of a stage are rows [n0, n0+BN/2) and [n1, n1+BN/2): for a plain product n1 = n0 + BN/2; for the
 // gated feed-forward n0 indexes the gate rows and n1 the matching up rows, and the epilogue writes
 // silu(gate) * up, so the [T, 2I] intermediate never exists (prefixserve/model/llama.py:120-121 of PrefixServe;
-// F.linear at :113, :117).
+// F.linear at :113, :117).  For the projection of an attention layer the epilogue does the rotary kernel's job
+// (rope.cu) on the sums and stores queries, keys and values where they belong (llama.py:113-116 and
+// prefixserve/model/attention.py:105-106 of PrefixServe), so the [T, (hq + 2 hkv) D] matrix never exists either.
 //
 // Rows of A past M, rows of W past N and columns past K are filled with zeros by the TMA unit (K only needs to be a
 // multiple of 8: a 16-byte row pitch).  No cluster, no multicast: every CTA loads its own tiles.

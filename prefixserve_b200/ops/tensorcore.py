@@ -17,8 +17,9 @@ STREAM_MIN_TILES = 0     # ... for matrices with at least this many 16-row tiles
 SMALL_M = 8         # rows up to which the one-tile-per-CTA kernel is used when the streaming kernel is not
 SMALL_M_GATED = 8   # same for the gate/up product with the fused activation
 USE_TCGEN05 = True  # products with more rows than STREAM_M: this library's tcgen05/TMEM/TMA kernel (else cuBLAS)
-TCGEN05_MIN_TILES = 120  # ... when the product has at least this many 128x256 output tiles; smaller ones (a few
-                         # dozen rows against a narrow matrix) leave most SMs idle without split-K and go to cuBLAS
+TCGEN05_MIN_TILES = 120  # ... when the product has at least this many 128x256 output tiles (the kernel itself may then
+                         # cut it into 128x192 ones); smaller ones (a few dozen rows against a narrow matrix) leave
+                         # most SMs idle without split-K and go to cuBLAS
 WIDE_BELOW_TILES = 600   # matrices with fewer 16-row tiles than this get 16 warps per CTA instead of 8
 TCGEN05_PREFILL_MIN_TOKENS = 64   # steps whose longest prompt portion has at least this many tokens run prefill attention
                                   # on the tcgen05 kernel (tiles of 128 rows); shorter portions fill too little of a tile
