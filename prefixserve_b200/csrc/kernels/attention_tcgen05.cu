@@ -1,17 +1,18 @@
 // Causal grouped-query attention of prompt portions over the paged cache on the 5th-generation tensor cores.
 //
 // One CTA owns up to 256 consecutive new tokens of one request for one query head, as two tiles of 128 rows, and walks
-// the keys they may see in blocks of KB keys (128 for a head size of 64, 64 for 128).  576 threads:
+// the keys they may see in blocks of KB keys (128 for a head size of 64, 64 for 128).  320 threads:
 //   warp 0      producer: TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle) of the two Q tiles once, and per block of
 //               the pages that hold its keys and values, one box per page, into a ring of four stages;
 //   warp 1      MMA: one lane issues tcgen05.mma (cta_group::1, kind::f16, M=128):  S = Q K^T  (A and B K-major, N=KB)
 //               into tensor memory, and  O += P V  (A = P from tensor memory, B = V MN-major exactly as the
 //               cache stores it: keys x head dim, N = head dim);
-//   warps 2..9  softmax of tile 0, warps 10..17 of tile 1: two threads per row, each with half of the block's keys.
-//               tcgen05.ld of the row of S, masks, maximum (agreed between the two through shared memory) and sum in
-//               float32, P as bfloat16 into tensor memory over the scores it came from.  O accumulates in tensor memory over
-//               the blocks; the row's reference maximum only follows the true one when that has grown by more than
-//               2^8, and only then is the row of O rescaled (tcgen05.ld, multiply, tcgen05.st), which is rare.
+//   warps 2..5  softmax of tile 0, warps 6..9 of tile 1: one thread per row.  tcgen05.ld of the row of S, masks,
+//               maximum and sum in float32 (three-input maxima and arithmetic on register pairs: the loop is bound by
+//               the instructions it issues), P as bfloat16 into tensor memory over the scores it came from.  O
+//               accumulates in tensor memory over the blocks; the row's reference maximum only follows the true one
+//               when that has grown by more than 2^8, and only then is the row of O rescaled (tcgen05.ld, multiply,
+//               tcgen05.st), which is rare.
 // The two tiles alternate on the tensor cores: while one tile's rows are in the softmax, the other's products run.
 // Rows are [token, head*D] of the rotated queries (prefixserve/model/llama.py:113-116 of PrefixServe computes the same
 // attention with a library kernel, prefixserve/model/attention.py:58-104); keys and values come from the pages named
@@ -27,7 +28,8 @@ using namespace tc;
 constexpr int TILE_M = 128;
 constexpr int TILES = 2;
 constexpr int ROWS_PER_CTA = TILE_M * TILES;
-constexpr int THREADS = 32 * (2 + 8 * TILES);  // producer, MMA, and two softmax threads per row
+constexpr int SOFTMAX_WARPS = 4;                     // per tile: one thread per row, a warp per quarter of tensor-memory lanes
+constexpr int THREADS = 32 * (2 + SOFTMAX_WARPS * TILES);  // producer, MMA, softmax
 constexpr int STAGES = 4;  // blocks of keys and values in shared memory at a time: S runs up to three blocks ahead of P V
 constexpr int TMEM_COLS = 512;
 constexpr float LOG2E_F = 1.4426950408889634f;
@@ -54,14 +56,39 @@ struct Shape {
 struct Barriers {
   uint64_t q_full;
   uint64_t k_full[STAGES], v_full[STAGES], kv_empty[STAGES];
-  uint64_t s_full[3], p_ready[TILES], o_full[TILES], row_max[TILES];
-  float exchange[2][TILES][2][TILE_M];  // [block parity][tile][half of the row][row]: maxima, at the end sums
+  uint64_t s_full[3], p_ready[TILES], o_full[TILES];
   uint32_t tmem_base;
   uint32_t abort;
 };
 
 template <int D>
 constexpr int smem_bytes() { return Shape<D>::BAR_OFF + 1024 /* alignment slack */ + (int)sizeof(Barriers); }
+
+// The softmax loops are bound by how many instructions they issue; sm_100 has float32 arithmetic on register pairs
+// (one instruction, two results, each rounded as the scalar instruction would) and a maximum of three.
+__device__ __forceinline__ uint64_t pair_of(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void halves_of(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_pair(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add_pair(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -109,8 +136,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     }
     for (int j = 0; j < 3; ++j) mbar_init(&bars->s_full[j], 1);
     for (int t = 0; t < TILES; ++t) {
-      mbar_init(&bars->p_ready[t], 8);  // one arrival per softmax warp of the tile (arrivals on one barrier serialise)
-      mbar_init(&bars->row_max[t], 8);
+      mbar_init(&bars->p_ready[t], SOFTMAX_WARPS);  // one arrival per softmax warp of the tile (arrivals on one barrier serialise)
       mbar_init(&bars->o_full[t], 1);
     }
     bars->abort = 0;
@@ -287,11 +313,15 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     }
   } else {
     // ----------------------------------------------------------------------------------------------- softmax
-    // Two threads per row (one in each of two warps that share a tensor-memory lane quarter): each owns half of the
-    // row's keys of a block and half of the head dim of O.  They agree on the row's maximum through shared memory.
-    constexpr int HC = KB / 2, HD = D / 2;
+    // One thread per row: it reads the row's scores of a block from tensor memory, finds the maximum, writes the
+    // probabilities over the scores and keeps the row's running maximum and sum; nothing is shared between threads.
+    // Per head size (measured): with 128 keys a block the scores alone are 128 registers of the 168 a thread may have
+    // (three warps on a scheduler), and arithmetic on register pairs, which wants them aligned, costs more in spills
+    // than it saves in instructions; with 64 keys a block there is room and it pays.
+    constexpr int KEPT_CHUNKS = 4;
+    constexpr bool PAIRS = D == 128;
     const int sw = warp - 2;
-    const int t = sw >> 3, half = (sw >> 2) & 1;
+    const int t = sw / SOFTMAX_WARPS;
     const int quarter = warp & 3;  // a warp may only touch tensor-memory lanes [32*(warp%4), +32)
     const int r = quarter * 32 + lane;
     if (t < ntiles) {
@@ -302,10 +332,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       const bool partial = row0 + TILE_M * (t + 1) > n;
       const float c = scale * LOG2E_F;
       const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-      const uint32_t o_addr = lane_addr + Sh::O_COL + t * D + half * HD;
-      float* mine = &bars->exchange[0][t][half][r];
-      const float* theirs = &bars->exchange[0][t][half ^ 1][r];
-      constexpr int XCH = TILES * 2 * TILE_M;            // floats per parity of the exchange buffer
+      const uint32_t o_addr = lane_addr + Sh::O_COL + t * D;
       // m_run is the maximum the row's exponentials refer to.  It follows the true maximum only when that has grown by
       // more than 2^8 (in the exponent), so that the accumulator in tensor memory is rescaled rarely; sums and
       // products use the same reference, and the quotient at the end does not depend on it.
@@ -313,46 +340,54 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       bool ok = true;
       const int my_blocks = bend[t] - b0 + 1;
       for (int i = 0; i < my_blocks; ++i) {
-        const int key0 = (b0 + i) * KB + half * HC;
+        const int key0 = (b0 + i) * KB;
         const int e = seq_of(t, i);
         ok = mbar_wait(&bars->s_full[e % 3], (e / 3) & 1, abort, 3);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         fence_after();
-        const uint32_t s_addr = lane_addr + Sh::S_COL + (e % 3) * KB + half * HC;
-        const bool need_mask = partial || key0 + HC - 1 > p_first[t] || (window > 0 && key0 < p_last[t] - window + 1);
-        // 32 keys at a time: the maximum first, over all of this thread's keys; the last chunk stays in registers
-        // and the others are read from tensor memory again for the exponentials
-        constexpr int NCH = HC / 32;
-        float sv[32];
-        auto load_chunk = [&](int cc) {
-          tmem_ld32(s_addr + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
-          tmem_ld_wait();
+        const uint32_t s_addr = lane_addr + Sh::S_COL + (e % 3) * KB;
+        const bool need_mask = partial || key0 + KB - 1 > p_first[t] || (window > 0 && key0 < p_last[t] - window + 1);
+        // The row's scores come in chunks of 32 keys.  The last KEPT chunks stay in registers from the maximum to the
+        // exponentials; earlier ones (a block of 128 keys has one) pass through the first chunk's registers for the
+        // maximum and are read from tensor memory again for the exponentials: 168 registers a thread is what three
+        // warps on one scheduler may have.
+        constexpr int NCH = KB / 32, KEPT = KEPT_CHUNKS < NCH ? KEPT_CHUNKS : NCH, FIRST_KEPT = NCH - KEPT;
+        float sv[KEPT][32];
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+        auto mask_chunk = [&](int cc, float(&x)[32]) {
           if (need_mask) {
 #pragma unroll
-            for (int e = 0; e < 32; ++e) {
-              const int key = key0 + cc * 32 + e;
-              if (key > pr || key < lo_r) sv[e] = -INFINITY;
+            for (int k = 0; k < 32; ++k) {
+              const int key = key0 + cc * 32 + k;
+              if (key > pr || key < lo_r) x[k] = -INFINITY;
             }
           }
         };
-        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+        auto fold_max = [&](const float(&x)[32]) {
 #pragma unroll
-        for (int cc = 0; cc < NCH; ++cc) {
-          load_chunk(cc);
-#pragma unroll
-          for (int e = 0; e < 32; e += 4) {
-            mx0 = fmaxf(mx0, sv[e]); mx1 = fmaxf(mx1, sv[e + 1]); mx2 = fmaxf(mx2, sv[e + 2]); mx3 = fmaxf(mx3, sv[e + 3]);
+          for (int k = 0; k < 32; k += 8) {
+            mx0 = max3(mx0, x[k], x[k + 1]); mx1 = max3(mx1, x[k + 2], x[k + 3]);
+            mx2 = max3(mx2, x[k + 4], x[k + 5]); mx3 = max3(mx3, x[k + 6], x[k + 7]);
           }
+        };
+#pragma unroll
+        for (int cc = 0; cc < FIRST_KEPT; ++cc) {
+          tmem_ld32(s_addr + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[0][0]));
+          tmem_ld_wait();
+          mask_chunk(cc, sv[0]);
+          fold_max(sv[0]);
         }
-        float m_new = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-        mine[(i & 1) * XCH] = m_new;
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->row_max[t]);
-        ok = mbar_wait(&bars->row_max[t], i & 1, abort, 3);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        m_new = fmaxf(m_new, theirs[(i & 1) * XCH]);
+#pragma unroll
+        for (int cc = FIRST_KEPT; cc < NCH; ++cc)  // all on their way before the first is waited for
+          tmem_ld32(s_addr + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[cc - FIRST_KEPT][0]));
+        tmem_ld_wait();
+#pragma unroll
+        for (int cc = FIRST_KEPT; cc < NCH; ++cc) {
+          mask_chunk(cc, sv[cc - FIRST_KEPT]);
+          fold_max(sv[cc - FIRST_KEPT]);
+        }
+        const float m_new = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
         const bool grow = (m_new - m_run) * c > 8.f;  // false while the row has seen nothing (-inf - -inf)
         // Each phase of o_full (P V of this tile's block i-1 has finished) is waited for exactly once, during block i:
         // a parity wait can only tell the phase in progress from the one before it.  Early if O has to be rescaled,
@@ -369,36 +404,53 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             waited = true;
             fence_after();
 #pragma unroll 1
-            for (int cc = 0; cc < HD / 32; ++cc) {
+            for (int cc = 0; cc < D / 32; ++cc) {
               uint32_t v[32];
               tmem_ld32(o_addr + cc * 32, v);
               tmem_ld_wait();
 #pragma unroll
-              for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * alpha);
+              for (int k = 0; k < 32; ++k) v[k] = __float_as_uint(__uint_as_float(v[k]) * alpha);
               tmem_st32(o_addr + cc * 32, v);
             }
             tmem_st_wait();
           }
         }
         const float mc = (m_run == -INFINITY ? 0.f : m_run) * c;
-        // P as bfloat16 over the S it came from: keys [32c, +32) of this thread's half become 16 columns at the start of
-        // the 32 columns their scores occupied (the chunk is in registers by then, and nobody else reads those columns)
+        // P as bfloat16 over the S it came from: keys [32c, +32) of the block become 16 columns at the start of the 32
+        // columns their scores occupied (the chunk is in registers by then, and nobody else reads those columns)
+        const uint64_t c_pair = pair_of(c, c), mc_pair = pair_of(-mc, -mc);
+        uint64_t sum_pair = pair_of(0.f, 0.f);  // even and odd keys add up apart
         float sum0 = 0.f, sum1 = 0.f;
-#pragma unroll
-        for (int cc = NCH - 1; cc >= 0; --cc) {
-          if (cc != NCH - 1) load_chunk(cc);
+        auto emit = [&](int cc, const float(&x)[32]) {
           uint32_t packed[16];
 #pragma unroll
-          for (int e2 = 0; e2 < 32; e2 += 2) {
-            const float p0 = ex2(fmaf(sv[e2], c, -mc));          // masked entries are -inf: 0
-            const float p1 = ex2(fmaf(sv[e2 + 1], c, -mc));
-            sum0 += p0;
-            sum1 += p1;
-            packed[e2 >> 1] = pack2(p0, p1);
+          for (int k = 0; k < 32; k += 2) {
+            float p0, p1;                                        // masked entries are -inf: 0
+            if constexpr (PAIRS) {
+              float x0, x1;
+              halves_of(fma_pair(pair_of(x[k], x[k + 1]), c_pair, mc_pair), x0, x1);
+              p0 = ex2(x0), p1 = ex2(x1);
+              sum_pair = add_pair(sum_pair, pair_of(p0, p1));
+            } else {
+              p0 = ex2(fmaf(x[k], c, -mc)), p1 = ex2(fmaf(x[k + 1], c, -mc));
+              sum0 += p0;
+              sum1 += p1;
+            }
+            packed[k >> 1] = pack2(p0, p1);
           }
           tmem_st16(s_addr + cc * 32, packed);
+        };
+#pragma unroll
+        for (int cc = NCH - 1; cc >= FIRST_KEPT; --cc) emit(cc, sv[cc - FIRST_KEPT]);
+#pragma unroll
+        for (int cc = FIRST_KEPT - 1; cc >= 0; --cc) {
+          tmem_ld32(s_addr + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[0][0]));
+          tmem_ld_wait();
+          mask_chunk(cc, sv[0]);
+          emit(cc, sv[0]);
         }
         tmem_st_wait();
+        if constexpr (PAIRS) halves_of(sum_pair, sum0, sum1);
         l_run += sum0 + sum1;
         if (!waited) {
           ok = mbar_wait(&bars->o_full[t], (i - 1) & 1, abort, 3);
@@ -409,33 +461,28 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->p_ready[t]);
       }
-      // the quotient: the two halves of a row add up their sums, then each scales its half of O
+      // the quotient
       if (ok) {
-        mine[(my_blocks & 1) * XCH] = l_run;
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->row_max[t]);
-        ok = mbar_wait(&bars->row_max[t], my_blocks & 1, abort, 3);
-        if (ok) ok = mbar_wait(&bars->o_full[t], (my_blocks - 1) & 1, abort, 3);
+        ok = mbar_wait(&bars->o_full[t], (my_blocks - 1) & 1, abort, 3);
         ok = __all_sync(0xffffffffu, ok);
       }
       if (ok) {
         fence_after();
-        const float l_row = l_run + theirs[(my_blocks & 1) * XCH];
-        const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
-        __nv_bfloat16* dst = out + ((size_t)(t0 + row) * hq + head) * D + half * HD;
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        __nv_bfloat16* dst = out + ((size_t)(t0 + row) * hq + head) * D;
 #pragma unroll 1
-        for (int cc = 0; cc < HD / 32; ++cc) {
+        for (int cc = 0; cc < D / 32; ++cc) {
           uint32_t v[32];
           tmem_ld32(o_addr + cc * 32, v);
           tmem_ld_wait();
           if (valid) {
 #pragma unroll
-            for (int e = 0; e < 32; e += 8)
-              *reinterpret_cast<uint4*>(dst + cc * 32 + e) =
-                  make_uint4(pack2(__uint_as_float(v[e]) * inv, __uint_as_float(v[e + 1]) * inv),
-                             pack2(__uint_as_float(v[e + 2]) * inv, __uint_as_float(v[e + 3]) * inv),
-                             pack2(__uint_as_float(v[e + 4]) * inv, __uint_as_float(v[e + 5]) * inv),
-                             pack2(__uint_as_float(v[e + 6]) * inv, __uint_as_float(v[e + 7]) * inv));
+            for (int k = 0; k < 32; k += 8)
+              *reinterpret_cast<uint4*>(dst + cc * 32 + k) =
+                  make_uint4(pack2(__uint_as_float(v[k]) * inv, __uint_as_float(v[k + 1]) * inv),
+                             pack2(__uint_as_float(v[k + 2]) * inv, __uint_as_float(v[k + 3]) * inv),
+                             pack2(__uint_as_float(v[k + 4]) * inv, __uint_as_float(v[k + 5]) * inv),
+                             pack2(__uint_as_float(v[k + 6]) * inv, __uint_as_float(v[k + 7]) * inv));
           }
         }
         fence_before();
