@@ -315,10 +315,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     // ----------------------------------------------------------------------------------------------- softmax
     // One thread per row: it reads the row's scores of a block from tensor memory, finds the maximum, writes the
     // probabilities over the scores and keeps the row's running maximum and sum; nothing is shared between threads.
-    // Per head size (measured): with 128 keys a block the scores alone are 128 registers of the 168 a thread may have
+    // Measured per head size: with 128 keys a block the scores alone are 128 registers of the 168 a thread may have
     // (three warps on a scheduler), and arithmetic on register pairs, which wants them aligned, costs more in spills
     // than it saves in instructions; with 64 keys a block there is room and it pays.
-    constexpr int KEPT_CHUNKS = 4;
     constexpr bool PAIRS = D == 128;
     const int sw = warp - 2;
     const int t = sw / SOFTMAX_WARPS;
@@ -339,23 +338,34 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       float m_run = -INFINITY, l_run = 0.f;
       bool ok = true;
       const int my_blocks = bend[t] - b0 + 1;
-      for (int i = 0; i < my_blocks; ++i) {
-        const int key0 = (b0 + i) * KB;
+      // The row's scores of a block, 32 keys a chunk, stay in registers from the maximum to the exponentials.  They are
+      // asked for as early as they can be: a block's scores are computed up to three blocks ahead, so the loads of
+      // block i+1 go out as soon as the exponentials of block i have let go of the registers, and arrive while this
+      // thread waits for its stores and hands block i over.
+      constexpr int NCH = KB / 32;
+      float sv[NCH][32];
+      auto request_scores = [&](int i) {  // false: a wait gave up
         const int e = seq_of(t, i);
-        ok = mbar_wait(&bars->s_full[e % 3], (e / 3) & 1, abort, 3);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
+        bool got = mbar_wait(&bars->s_full[e % 3], (e / 3) & 1, abort, 3);
+        got = __all_sync(0xffffffffu, got);
+        if (!got) return false;
         fence_after();
         const uint32_t s_addr = lane_addr + Sh::S_COL + (e % 3) * KB;
+#pragma unroll
+        for (int cc = 0; cc < NCH; ++cc) tmem_ld32(s_addr + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[cc][0]));
+        return true;
+      };
+      ok = request_scores(0);
+      for (int i = 0; ok && i < my_blocks; ++i) {
+        const int key0 = (b0 + i) * KB;
+        const int e = seq_of(t, i);
+        const uint32_t s_addr = lane_addr + Sh::S_COL + (e % 3) * KB;
         const bool need_mask = partial || key0 + KB - 1 > p_first[t] || (window > 0 && key0 < p_last[t] - window + 1);
-        // The row's scores come in chunks of 32 keys.  The last KEPT chunks stay in registers from the maximum to the
-        // exponentials; earlier ones (a block of 128 keys has one) pass through the first chunk's registers for the
-        // maximum and are read from tensor memory again for the exponentials: 168 registers a thread is what three
-        // warps on one scheduler may have.
-        constexpr int NCH = KB / 32, KEPT = KEPT_CHUNKS < NCH ? KEPT_CHUNKS : NCH, FIRST_KEPT = NCH - KEPT;
-        float sv[KEPT][32];
         float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-        auto mask_chunk = [&](int cc, float(&x)[32]) {
+        tmem_ld_wait();
+#pragma unroll
+        for (int cc = 0; cc < NCH; ++cc) {
+          float(&x)[32] = sv[cc];
           if (need_mask) {
 #pragma unroll
             for (int k = 0; k < 32; ++k) {
@@ -363,29 +373,11 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
               if (key > pr || key < lo_r) x[k] = -INFINITY;
             }
           }
-        };
-        auto fold_max = [&](const float(&x)[32]) {
 #pragma unroll
           for (int k = 0; k < 32; k += 8) {
             mx0 = max3(mx0, x[k], x[k + 1]); mx1 = max3(mx1, x[k + 2], x[k + 3]);
             mx2 = max3(mx2, x[k + 4], x[k + 5]); mx3 = max3(mx3, x[k + 6], x[k + 7]);
           }
-        };
-#pragma unroll
-        for (int cc = 0; cc < FIRST_KEPT; ++cc) {
-          tmem_ld32(s_addr + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[0][0]));
-          tmem_ld_wait();
-          mask_chunk(cc, sv[0]);
-          fold_max(sv[0]);
-        }
-#pragma unroll
-        for (int cc = FIRST_KEPT; cc < NCH; ++cc)  // all on their way before the first is waited for
-          tmem_ld32(s_addr + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[cc - FIRST_KEPT][0]));
-        tmem_ld_wait();
-#pragma unroll
-        for (int cc = FIRST_KEPT; cc < NCH; ++cc) {
-          mask_chunk(cc, sv[cc - FIRST_KEPT]);
-          fold_max(sv[cc - FIRST_KEPT]);
         }
         const float m_new = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
         const bool grow = (m_new - m_run) * c > 8.f;  // false while the row has seen nothing (-inf - -inf)
@@ -441,13 +433,10 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
           tmem_st16(s_addr + cc * 32, packed);
         };
 #pragma unroll
-        for (int cc = NCH - 1; cc >= FIRST_KEPT; --cc) emit(cc, sv[cc - FIRST_KEPT]);
-#pragma unroll
-        for (int cc = FIRST_KEPT - 1; cc >= 0; --cc) {
-          tmem_ld32(s_addr + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[0][0]));
-          tmem_ld_wait();
-          mask_chunk(cc, sv[0]);
-          emit(cc, sv[0]);
+        for (int cc = 0; cc < NCH; ++cc) emit(cc, sv[cc]);
+        if (i + 1 < my_blocks) {  // the registers are free again: the next block's scores may start on their way
+          ok = request_scores(i + 1);
+          if (!ok) break;
         }
         tmem_st_wait();
         if constexpr (PAIRS) halves_of(sum_pair, sum0, sum1);
