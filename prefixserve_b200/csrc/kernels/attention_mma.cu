@@ -186,12 +186,6 @@ __device__ __forceinline__ void mask_tile(float (&s)[2][4], int key0, int t, con
       }
 }
 
-__device__ __forceinline__ const __nv_bfloat16* tile_ptr(const __nv_bfloat16* kv, const int32_t* pages, int key0, int page_size,
-                                                          int hkv, int h, int D) {
-  const int page = pages[key0 / page_size];
-  return kv + ((size_t)page * 2 * hkv + h) * (size_t)page_size * D + (size_t)(key0 % page_size) * D;
-}
-
 // ---------------------------------------------------------------------------------------------- decode
 // grid (splits, hkv, items).  Partial results (float32): part_o[item][head][split][D], part_ml[item][head][split][2].
 //

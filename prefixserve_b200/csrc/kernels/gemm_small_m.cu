@@ -203,17 +203,6 @@ namespace {
 
 constexpr int SW = 16;  // warps per CTA
 
-__device__ __forceinline__ void cp_async16_cg(void* smem_dst, const void* gmem_src, bool valid) {
-  const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
-  const int bytes = valid ? 16 : 0;
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem_src), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async16_ca(void* smem_dst, const void* gmem_src, bool valid) {
-  const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
-  const int bytes = valid ? 16 : 0;
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem_src), "r"(bytes) : "memory");
-}
-
 template <int MT, int TILES>
 struct StreamShape {
   static constexpr int PIECES = 2 * TILES + MT;                 // per lane per k chunk
