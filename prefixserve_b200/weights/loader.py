@@ -15,6 +15,7 @@ On the float32 path everything is widened to float32.
 from __future__ import annotations
 
 import json
+import sys
 from contextlib import ExitStack
 from pathlib import Path
 from typing import Callable, Mapping
@@ -104,9 +105,14 @@ def load_tensors(
             raise WeightLoadError("\n".join(lines))
 
         out: dict[str, torch.Tensor] = {}
+        wide = 0
         for path, spec in wanted.items():
             t: torch.Tensor = where[names[path]].get_tensor(names[path])  # type: ignore[attr-defined]
             out[path] = t.to(device=device, dtype=held_dtype(spec.role, t.dtype, compute_dtype)).contiguous()
+            wide += spec.role != "vector" and t.dim() >= 2 and out[path].dtype == torch.float32 and compute_dtype != torch.float32
+        if wide:  # right, but not what somebody who asked for bfloat16 may expect of the speed
+            print(f"[prefixserve_b200] {wide} matrices of {folder} are stored in 32-bit and stay so: their products run on the "
+                  f"float32 kernel, not on the tensor cores", file=sys.stderr, flush=True)
         return out
 
 
