@@ -128,8 +128,10 @@ def norm_gated_linear_bf16(x, w_gate_up: torch.Tensor) -> torch.Tensor | None:
     return act
 
 
-def _tcgen05_ok(x: torch.Tensor, w: torch.Tensor, n_span: int = 256) -> bool:
+def _tcgen05_ok(x: torch.Tensor, w: torch.Tensor, n_span: int = 256, narrow_ok: bool = True) -> bool:
     n_out = w.shape[0] if n_span == 256 else w.shape[0] // 2
+    if n_span == 256 and narrow_ok:
+        n_span = 192  # the kernel cuts such a product into 128x192 tiles when that fills the SMs better
     tiles = -(-x.shape[0] // 128) * -(-n_out // n_span)
     return (USE_TCGEN05 and tiles >= TCGEN05_MIN_TILES and x.shape[1] % 8 == 0 and x.shape[1] >= 8 and x.is_contiguous() and w.is_contiguous()
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
@@ -158,7 +160,7 @@ def gemm_tcgen05_gated(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor
 def tcgen05_qkv_rope_bf16(x: torch.Tensor, w_qkv, positions, token_item, cos, sin, table, kv, hq, hkv, d, page_size) -> torch.Tensor | None:
     """The projection of an attention layer for many tokens on the tcgen05 kernel, rotation and append to the pages in
     its epilogue; None when that kernel does not take the shape."""
-    if not (_tcgen05_ok(x, w_qkv) and kv.is_contiguous() and (cos is None or (cos.is_contiguous() and sin.is_contiguous()))):
+    if not (_tcgen05_ok(x, w_qkv, narrow_ok=d != 128) and kv.is_contiguous() and (cos is None or (cos.is_contiguous() and sin.is_contiguous()))):
         return None
     m, k = x.shape
     q = torch.empty((m, hq, d), dtype=torch.bfloat16, device=x.device)
