@@ -128,10 +128,11 @@ def norm_gated_linear_bf16(x, w_gate_up: torch.Tensor) -> torch.Tensor | None:
     return act
 
 
-def _tcgen05_ok(x: torch.Tensor, w: torch.Tensor, n_span: int = 256, narrow_ok: bool = True) -> bool:
+def _tcgen05_ok(x: torch.Tensor, w: torch.Tensor, n_span: int = 256, narrow_ok: bool = False) -> bool:
     n_out = w.shape[0] if n_span == 256 else w.shape[0] // 2
     if n_span == 256 and narrow_ok:
-        n_span = 192  # the kernel cuts such a product into 128x192 tiles when that fills the SMs better
+        n_span = 192  # the projection with rotation in its epilogue: counted in the 128x192 tiles the kernel may cut it
+                      # into (it replaces two kernels; the plain products of this size are the library's: measured)
     tiles = -(-x.shape[0] // 128) * -(-n_out // n_span)
     return (USE_TCGEN05 and tiles >= TCGEN05_MIN_TILES and x.shape[1] % 8 == 0 and x.shape[1] >= 8 and x.is_contiguous() and w.is_contiguous()
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
