@@ -213,7 +213,7 @@ def run_own(args) -> dict:
                     cache.reserve(s, p + 1)
                     items.append(StepItem(s, p, rng.randint(0, vocab, size=1).astype(np.int32), (0,)))
                 logits = runner.step(items)
-                choose_tokens(logits, [greedy] * len(items), [it.start + 1 for it in items])
+                choose_tokens(logits, cache.records_dev, runner.last_row_slots)
                 for it in items:
                     cache.advance(it.slot, it.start + 1)
 
@@ -311,7 +311,7 @@ def run_own(args) -> dict:
             torch.cuda.synchronize()
             t0.record()
             logits = runner.step([StepItem(slot, 0, toks, (PREFILL_TOKENS - 1,))])
-            choose_tokens(logits, [greedy], [PREFILL_TOKENS])
+            choose_tokens(logits, cache.records_dev, runner.last_row_slots)
             t1.record()
             torch.cuda.synchronize()
             cache.close(slot)
@@ -473,7 +473,7 @@ def run_mixed(args) -> dict:
                 cache.reserve(s, p + 1)
                 items.append(StepItem(s, p, rng.randint(0, vocab, size=1).astype(np.int32), (0,)))
             logits = runner.step(items)
-            choose_tokens(logits, [greedy] * decodes, [it.start + 1 for it in items[1:]])
+            choose_tokens(logits, cache.records_dev, runner.last_row_slots)
             for it in items:
                 cache.advance(it.slot, it.start + len(it.tokens))
 

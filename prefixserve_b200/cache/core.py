@@ -31,5 +31,6 @@ BlockManager = _core.BlockManager
 RadixTree = _core.RadixTree
 SlotPool = _core.SlotPool
 SeqTables = _core.SeqTables
+SlotRecords = _core.SlotRecords
 
-__all__ = ["BLOCK_SIZE", "BlockManager", "CoreError", "RadixTree", "SeqTables", "SlotPool"]
+__all__ = ["BLOCK_SIZE", "BlockManager", "CoreError", "RadixTree", "SeqTables", "SlotPool", "SlotRecords"]

@@ -19,6 +19,13 @@ request (csrc/block_manager.hpp, csrc/radix_tree.hpp,
 prefixserve/scheduler.py:370-451, prefixserve/llama_engine.py:110-117); here
 one object owns ids, tables, slots and the device tensors.
 Cache layout of an entry: [num_pages, 2 (key, value), kv_heads, page_size, head_dim].
+
+What a step needs to know about a request stays on the device in one int32
+array (``resident``): a record per slot (position, sampling temperature and
+seed) followed by every group's page table rows [num_slots, max_pages].  The
+C++ side holds the mirror and logs which words changed; ``drain_deltas`` hands
+a step the (index, value) pairs to send, and nothing else of the tables
+travels.
 """
 
 from __future__ import annotations
@@ -30,7 +37,7 @@ import numpy as np
 import torch
 
 from ..parts.base import CacheNeed, CacheView
-from .core import BlockManager, CoreError, RadixTree, SeqTables, SlotPool
+from .core import BlockManager, CoreError, RadixTree, SeqTables, SlotPool, SlotRecords
 
 
 class CacheError(RuntimeError):
@@ -93,7 +100,16 @@ class CacheManager:
             self.entry_group.append(g)
 
         self.slots = SlotPool(num_slots)
-        self._position = np.zeros(num_slots, dtype=np.int64)  # tokens computed, per slot (host mirror)
+        self.records = SlotRecords(num_slots)          # host mirror of the per-slot records, owned by the C++ side
+        self._position = self.records.view()[:, 0]     # tokens computed, per slot (a view of the mirror)
+        self.record_words = SlotRecords.WORDS
+        # where each mirrored array starts in the device's resident array
+        self._table_base: list[int] = []
+        at = num_slots * self.record_words
+        for _ in self.groups:
+            self._table_base.append(at)
+            at += num_slots * self.max_pages_per_seq
+        self.resident_words = at
 
         has_state = any(n.state is not None for n in self.needs)
         self.prefix_cache_possible = len(self.groups) == 1 and self.groups[0].window is None and not has_state
@@ -104,7 +120,15 @@ class CacheManager:
         # device tensors
         self.kv: list[torch.Tensor | None] = [None] * len(self.needs)
         self.state: list[torch.Tensor | None] = [None] * len(self.needs)
+        self.resident: torch.Tensor | None = None
+        self.records_dev: torch.Tensor | None = None
+        self.tables_dev: list[torch.Tensor] = []
         if self.device is not None:
+            self.resident = torch.full((self.resident_words,), -1, dtype=torch.int32, device=self.device)
+            self.records_dev = self.resident[: num_slots * self.record_words].view(num_slots, self.record_words)
+            self.records_dev.zero_()
+            self.tables_dev = [self.resident[b: b + num_slots * self.max_pages_per_seq].view(num_slots, self.max_pages_per_seq)
+                               for b in self._table_base]
             for i, need in enumerate(self.needs):
                 if need.paged is not None:
                     g = self.groups[self.entry_group[i]]
@@ -156,6 +180,29 @@ class CacheManager:
 
     def position(self, slot: int) -> int:
         return int(self._position[slot])
+
+    def set_sampling(self, slot: int, temperature: float, seed: int) -> None:
+        """Notes how the slot's request samples; the sampling kernel reads it from the slot's record on the device."""
+        self.records.set_sampling(slot, float(temperature), int(seed) & 0xFFFFFFFFFFFFFFFF)
+
+    # ----------------------------------------------------- what the device holds
+    def pending_deltas(self) -> int:
+        """Words of the resident array (records, page tables) that changed since the device last saw them."""
+        return self.records.pending + sum(g.tables.pending for g in self.groups)
+
+    def drain_deltas(self, out: np.ndarray, at: int) -> int:
+        """Writes the changed words as (index into ``resident``, value) pairs into the int32 array ``out`` from word
+        ``at`` on (2 * pending_deltas() words) and forgets them.  Returns the number of pairs."""
+        n = self.records.drain(0, out, at)
+        for base, g in zip(self._table_base, self.groups):
+            n += g.tables.drain(base, out, at + 2 * n)
+        return n
+
+    def covered(self, group: int, slots: np.ndarray, first: np.ndarray, upto: np.ndarray) -> int:
+        """Index of the first of ``slots`` whose row in ``group`` lacks a valid page at some page index in
+        [first, upto); -1 when every row is whole."""
+        g = self.groups[group]
+        return int(g.tables.covered(slots, first, upto, g.pool.num_blocks))
 
     # ------------------------------------------------------------------ pages
     def _first_needed_page(self, g: _Group, upto_start: int) -> int:

@@ -167,6 +167,35 @@ PYBIND11_MODULE(_core, m) {
       .def_property_readonly("num_free", &SlotPool::num_free)
       .def_property_readonly("num_slots", &SlotPool::num_slots);
 
+  py::class_<SlotRecords>(m, "SlotRecords")
+      .def(py::init([](int64_t n) {
+             if (n < 1 || n > (1 << 24)) throw py::value_error("num_slots must be in [1, 2**24]");
+             return std::make_unique<SlotRecords>(static_cast<int32_t>(n));
+           }),
+           py::arg("num_slots"))
+      .def_property_readonly("num_slots", &SlotRecords::num_slots)
+      .def_property_readonly_static("WORDS", [](py::object) { return SlotRecords::kWords; })
+      .def("view",
+           [](py::object self) {
+             auto& r = self.cast<SlotRecords&>();
+             // int32 [num_slots, WORDS] over the records themselves; the array keeps the object alive
+             return py::array_t<int32_t>({static_cast<py::ssize_t>(r.num_slots()), static_cast<py::ssize_t>(SlotRecords::kWords)},
+                                         r.data(), self);
+           })
+      .def("set_sampling",
+           [](SlotRecords& r, int64_t s, double temperature, uint64_t seed) {
+             if (!r.slot_ok(static_cast<int32_t>(s))) throw py::value_error("slot out of range");
+             r.set_sampling(static_cast<int32_t>(s), static_cast<float>(temperature), seed);
+           },
+           py::arg("slot"), py::arg("temperature"), py::arg("seed"))
+      .def_property_readonly("pending", &SlotRecords::pending)
+      .def("drain",
+           [](SlotRecords& r, int64_t base, py::array_t<int32_t, py::array::c_style> out, int64_t at) {
+             if (at < 0 || out.size() < at + 2 * static_cast<int64_t>(r.pending())) throw py::value_error("output array is too small");
+             return r.drain(static_cast<int32_t>(base), out.mutable_data() + at);
+           },
+           py::arg("base"), py::arg("out"), py::arg("at"));
+
   py::class_<SeqTables>(m, "SeqTables")
       .def(py::init([](int64_t slots, int64_t pages) {
              if (slots < 1 || pages < 1 || slots * pages > (int64_t{1} << 31)) throw py::value_error("bad table shape");
@@ -220,6 +249,28 @@ PYBIND11_MODULE(_core, m) {
              return out;
            },
            py::arg("slot"))
+      .def_property_readonly("pending", &SeqTables::pending)
+      .def("drain",
+           [](SeqTables& t, int64_t base, py::array_t<int32_t, py::array::c_style> out, int64_t at) {
+             if (at < 0 || out.size() < at + 2 * static_cast<int64_t>(t.pending())) throw py::value_error("output array is too small");
+             return t.drain(static_cast<int32_t>(base), out.mutable_data() + at);
+           },
+           py::arg("base"), py::arg("out"), py::arg("at"))
+      .def("covered",
+           [](const SeqTables& t, const IntArray& slots, const IntArray& first, const IntArray& upto, int64_t num_pages) {
+             // index of the first slot whose row lacks a valid page id somewhere in [first, upto); -1 when all are whole
+             int64_t n = 0, nf = 0, nu = 0;
+             const int32_t* s = flat(slots, "slots", &n);
+             const int32_t* f = flat(first, "first", &nf);
+             const int32_t* u = flat(upto, "upto", &nu);
+             if (nf != n || nu != n) throw py::value_error("slots, first and upto must have one entry per item");
+             for (int64_t i = 0; i < n; ++i) {
+               if (!t.slot_ok(s[i])) throw py::value_error("slot out of range");
+               if (!t.covered(s[i], f[i], u[i], static_cast<int32_t>(num_pages))) return i;
+             }
+             return int64_t{-1};
+           },
+           py::arg("slots"), py::arg("first"), py::arg("upto"), py::arg("num_pages"))
       .def("gather",
            [](const SeqTables& t, const IntArray& slots, int64_t width, py::array_t<int32_t, py::array::c_style> out) {
              int64_t n = 0;

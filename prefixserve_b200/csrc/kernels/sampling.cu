@@ -29,8 +29,11 @@ __device__ __forceinline__ float uniform01(uint64_t seed, uint32_t position, uin
 
 // Stage 1: block (row, part) scans its slice of the row and leaves its winner in part_v/part_i.
 // Stage 2 (parts == 1 and final != nullptr in one launch, or a second launch over the winners): same reduction.
+// The row's temperature, seed and position come either from three arrays with one entry per row, or (records given)
+// from the record of the row's request slot: int32 words {position, temperature bits, seed low, seed high, ...}.
 __global__ void sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
                               const int64_t* __restrict__ seed, const int32_t* __restrict__ position,
+                              const int32_t* __restrict__ records, const int32_t* __restrict__ row_slot, int record_words,
                               int32_t* __restrict__ out, float* __restrict__ part_v, int32_t* __restrict__ part_i, int V,
                               int parts) {
   __shared__ float best_v[32];
@@ -39,14 +42,15 @@ __global__ void sample_kernel(const float* __restrict__ logits, const float* __r
   pdl_wait();
   const int row = blockIdx.x, part = blockIdx.y;
   const float* x = logits + (size_t)row * V;
-  const float tau = temperature ? temperature[row] : 0.f;
+  const int32_t* rec = records ? records + (size_t)row_slot[row] * record_words : nullptr;
+  const float tau = rec ? __int_as_float(rec[1]) : (temperature ? temperature[row] : 0.f);
   const int per = (V + parts - 1) / parts;
   const int lo = part * per, hi = min(V, lo + per);
   float bv = -FLT_MAX;
   int bi = 0x7fffffff;
   if (tau > 0.f) {
-    const uint64_t sd = (uint64_t)seed[row];
-    const uint32_t pos = (uint32_t)position[row];
+    const uint64_t sd = rec ? ((uint64_t)(uint32_t)rec[2] | ((uint64_t)(uint32_t)rec[3] << 32)) : (uint64_t)seed[row];
+    const uint32_t pos = (uint32_t)(rec ? rec[0] : position[row]);
     const float inv_tau = 1.f / tau;
     for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
       const float u = uniform01(sd, pos, (uint32_t)i);
@@ -137,7 +141,29 @@ PSB_API int psb_sample(const void* logits, const void* temperature, const void* 
   float* part_v = (float*)scratch;
   int32_t* part_i = (int32_t*)(part_v + (size_t)S * parts);
   psb_launch(sample_kernel, dim3(S, parts), dim3(threads), 0, stream, (const float*)logits, (const float*)temperature, (const int64_t*)seed,
-                                                       (const int32_t*)position, (int32_t*)out, part_v, part_i, V, parts);
+             (const int32_t*)position, (const int32_t*)nullptr, (const int32_t*)nullptr, 0, (int32_t*)out, part_v, part_i, V, parts);
+  if (parts > 1) psb_launch(sample_finish_kernel, dim3(S), dim3(32), 0, stream, (const float*)part_v, (const int32_t*)part_i, (int32_t*)out, parts);
+  PSB_LAUNCH_CHECK("sample");
+  return 0;
+}
+
+// The same choice with every row's temperature, seed and position read from the record of its request slot
+// (records: int32 [num_slots, record_words] on the device; row_slot: int32 [S]).  Nothing about the requests is
+// built on the host for a step.
+PSB_API int psb_sample_slots(const void* logits, const void* records, const void* row_slot, int record_words, void* out,
+                             void* scratch, int S, int V, cudaStream_t stream) {
+  if (S < 0 || V < 1) PSB_REFUSE("sample: bad sizes S=%d V=%d", S, V);
+  if (!records || !row_slot || record_words < 4) PSB_REFUSE("sample: slot records of at least 4 words and one slot per row are needed");
+  if (S == 0) return 0;
+  const int parts = psb_sample_parts(S, V);
+  if (parts > 1 && !scratch) PSB_REFUSE("sample: scratch for %d parts per row missing", parts);
+  const int per = (V + parts - 1) / parts;
+  const int threads = per >= 16384 ? 1024 : (per >= 1024 ? 256 : 64);
+  float* part_v = (float*)scratch;
+  int32_t* part_i = (int32_t*)(part_v + (size_t)S * parts);
+  psb_launch(sample_kernel, dim3(S, parts), dim3(threads), 0, stream, (const float*)logits, (const float*)nullptr,
+             (const int64_t*)nullptr, (const int32_t*)nullptr, (const int32_t*)records, (const int32_t*)row_slot, record_words,
+             (int32_t*)out, part_v, part_i, V, parts);
   if (parts > 1) psb_launch(sample_finish_kernel, dim3(S), dim3(32), 0, stream, (const float*)part_v, (const int32_t*)part_i, (int32_t*)out, parts);
   PSB_LAUNCH_CHECK("sample");
   return 0;

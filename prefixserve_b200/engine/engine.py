@@ -132,7 +132,7 @@ class Engine:
         sampling = [w for w in work if w.samples]
         if not sampling:
             return PendingStep(batch, [], None, None, None)  # nothing to read back: the host runs ahead
-        tokens = choose_tokens(logits, [w.req.sampling for w in sampling], [w.end for w in sampling])
+        tokens = choose_tokens(logits, self.cache.records_dev, self.runner.last_row_slots)
         if self.capture_logits:
             self.last_logits = {w.req.req_id: logits[i].cpu() for i, w in enumerate(sampling)}
         host = self._token_buffers[self._token_turn % len(self._token_buffers)][: len(sampling)]

@@ -411,6 +411,7 @@ class Scheduler:
             self.cache.release_pages(pages)
             return None
         req.slot = slot
+        self.cache.set_sampling(slot, req.sampling.temperature, req.sampling.seed)
         if pages:
             self.cache.adopt(slot, pages, matched)
         if not self._take_pages(req, matched + n):

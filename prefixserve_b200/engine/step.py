@@ -9,6 +9,14 @@ all integer inputs are laid out in one pinned buffer and reach the device in a
 single asynchronous copy; page tables and limits are checked on the host
 before anything is launched (prefixserve/llama_engine.py:270-287), so a bad
 table is an exception for one step, not a memory fault.
+
+Unlike the reference, which flattens and uploads every request's page list on
+every step (prefixserve/llama_engine.py:183-209), the page tables and a record
+per request slot (position, sampling temperature and seed) stay on the device.
+A step carries the words of them that changed since the last one as (index,
+value) pairs behind its other inputs; a small kernel puts them in place and
+another turns the rows of the step's slots into the table the layers read.  A
+decode step that appends no page sends four words per request.
 """
 
 from __future__ import annotations
@@ -16,11 +24,14 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Sequence
 
+import os
+
 import numpy as np
 import torch
 
 from ..cache.manager import CacheManager, pages_for
 from ..parts.base import ItemView, StepContext
+from .. import ops
 from ..ops import library
 from ..parts.model import DecoderModel
 
@@ -44,7 +55,30 @@ class _DecodeGraph:
     inputs: torch.Tensor
     logits: torch.Tensor
     graph: torch.cuda.CUDAGraph
+    var_at: int      # where the words that change from step to step begin in ``inputs``
+    pairs_at: int    # where the (index, value) pairs of the resident array begin
+    pairs_room: int  # how many pairs fit
     kernels: int = 0  # launches of this library's kernels recorded in the graph
+
+
+@dataclass
+class _Layout:
+    """Where each input of a step lies in its one int32 buffer.  What never changes between steps of the same shape
+    comes first, what changes next, the changed words of the resident array last."""
+
+    t: int
+    b: int
+    s: int
+    rows_are_items: bool = False  # every item brings one token and wants it: the slot of a row is the slot of its item
+
+    def __post_init__(self) -> None:
+        t, b, s = self.t, self.b, self.s
+        self.item, self.start, self.rows = 0, t, t + b + 1
+        self.var = self.rows + s
+        self.ids, self.pos, self.kvlen = self.var, self.var + t, self.var + 2 * t
+        self.slot = self.kvlen + b
+        self.rowslot = self.slot if self.rows_are_items else self.slot + b
+        self.pairs = self.rowslot + s
 
 
 class ModelRunner:
@@ -72,6 +106,7 @@ class ModelRunner:
         self._copy_pending = False
         self.steps_run = 0
         self.last_h2d_bytes = 0  # size of the last step's single host-to-device copy
+        self.last_row_slots: torch.Tensor | None = None  # int32 [wanted rows]: the request slot of each row of the last logits
         # graphs need every part to do the same device work for the same shapes, whatever the host-side item list says
         self.use_graphs = use_graphs and all(getattr(p, "graph_safe", False) for _, p in model.named_parts())
         self._graphs: dict[int, _DecodeGraph] = {}
@@ -81,6 +116,9 @@ class ModelRunner:
         # "rope_relative" numbers every portion's positions from 0; "kv_len_short" reports one key too few.
         # The test suite proves with these that it notices such faults.
         self.inject_bug: str | None = None
+        # Debug check, after the reference's test harness (tests/test_llama_exact.py:146-151 of PrefixServe): a step
+        # must never write a position whose page the prefix tree owns (another request may be reading it).
+        self.check_writes = os.environ.get("PSB200_DEBUG_CHECKS", "0") == "1"
 
     # ------------------------------------------------------------------ checks
     def _check(self, items: Sequence[StepItem], ahead: np.ndarray | None = None) -> None:
@@ -109,29 +147,91 @@ class ModelRunner:
             bad = next(it.slot for it in items if np.min(it.tokens) < 0 or np.max(it.tokens) >= self.vocab_size)
             raise EngineError(f"slot {bad}: token id outside [0, {self.vocab_size})")
 
-    def _check_tables(self, items: Sequence[StepItem], tables: dict[int, np.ndarray]) -> None:
-        page = self.cache.page_size
-        for gi, table in tables.items():
-            g = self.cache.groups[gi]
-            for row, it in zip(table, items):
-                end = it.start + len(it.tokens)
-                first = self.cache._first_needed_page(g, it.start)
-                live = row[first: pages_for(end, page)]
-                if live.size and (live.min() < 0 or live.max() >= g.pool.num_blocks):
-                    raise EngineError(f"slot {it.slot}: page table of group {gi} names a page outside the pool")
+    def _check_pages(self, slots: np.ndarray, starts: np.ndarray, ends: np.ndarray) -> None:
+        """Every page a step reads or writes must be held and name a page of the pool; with the debug check on, no
+        page it writes may belong to the prefix tree."""
+        cache = self.cache
+        page = cache.page_size
+        upto = ((ends + page - 1) // page).astype(np.int32)
+        for gi, g in enumerate(cache.groups):
+            if g.window is None:
+                first = np.zeros(len(slots), dtype=np.int32)
+            else:
+                first = (np.maximum(0, starts - g.window + 1) // page).astype(np.int32)
+            bad = cache.covered(gi, slots, first, upto)
+            if bad >= 0:
+                raise EngineError(f"slot {int(slots[bad])}: page table of group {gi} lacks a page or names one outside the pool")
+        if self.check_writes and cache.tree is not None:
+            for slot, a, e in zip(slots.tolist(), starts.tolist(), ends.tolist()):
+                row = cache.page_ids(slot)
+                for pi in range(a // page, (e - 1) // page + 1):
+                    if cache.is_cached(row[pi]):
+                        raise EngineError(f"slot {slot}: the step would write position {max(a, pi * page)}, whose page "
+                                          f"{row[pi]} belongs to the prefix cache")
+
+    # -------------------------------------------------------- resident arrays
+    def _send_deltas_alone(self) -> None:
+        """Sends the changed words of the resident array in a copy of their own (when they do not fit behind a
+        captured step's inputs)."""
+        n = self.cache.pending_deltas()
+        if n == 0:
+            return
+        host = self._staging(2 * n)
+        n = self.cache.drain_deltas(host.numpy(), 0)
+        dev = host[: 2 * n].to(self.device, non_blocking=True)
+        self._copied.record()
+        self._copy_pending = True
+        ops.scatter_words(self.cache.resident, dev, n)
+
+    def _device_step(self, lay: _Layout, dev: torch.Tensor, widths: dict[int, int], views, lens, static: bool, rows: torch.Tensor):
+        """The device work of a step whose inputs lie in ``dev``: the step's page tables from the resident rows, the
+        slots' positions, then the model.  The same launches whether run at once or captured."""
+        cache = self.cache
+        t, b = lay.t, lay.b
+        kv_len = dev[lay.kvlen: lay.kvlen + b]
+        slots = dev[lay.slot: lay.slot + b]
+        tables: dict[int, torch.Tensor] = {}
+        noted = False
+        for gi in range(len(cache.groups)):
+            tables[gi] = torch.empty((b, widths[gi]), dtype=torch.int32, device=self.device)
+            ops.step_prepare(None if noted else cache.records_dev, kv_len, slots, cache.tables_dev[gi], tables[gi])
+            noted = True
+        if not noted:
+            ops.step_prepare(cache.records_dev, kv_len, slots, None, None)
+        ctx = StepContext(
+            num_tokens=t,
+            num_items=b,
+            compute_dtype=self.model.compute_dtype,
+            device=self.device,
+            items=views,
+            token_ids=dev[lay.ids: lay.ids + t],
+            positions=dev[lay.pos: lay.pos + t],
+            token_item=dev[lay.item: lay.item + t],
+            item_start=dev[lay.start: lay.start + b + 1],
+            kv_len=kv_len,
+            slots=slots,
+            block_tables=tables,
+            max_new_tokens=max(lens),
+            max_kv_len=max(v.end for v in views),
+            all_decode=all(n == 1 for n in lens),
+        )
+        if static:
+            ctx.extras["static_kv_len"] = cache.max_seq_len
+        return self.model.forward(ctx, cache.view, rows)
 
     # ------------------------------------------------------------------- step
     @torch.inference_mode()
     def step(self, items: Sequence[StepItem], device_ids: torch.Tensor | None = None,
              in_flight: Sequence[int] | None = None) -> torch.Tensor:
         """Runs the batch. Returns float32 logits [number of wanted positions, vocab] on the device,
-        in the order of the items and of each item's ``want``.
+        in the order of the items and of each item's ``want``; ``last_row_slots`` then names the slot of each row.
 
         ``device_ids`` (int32 [len(items)] on the device): the items are single tokens that follow a step which has been
         launched but whose result the host has not seen; their token ids are taken from this tensor on the device (the
         items' own ``tokens`` are placeholders); ``in_flight[i]`` is how many tokens that step computes for item i's
         request, which the cache manager does not record before its commit."""
         if not items:
+            self.last_row_slots = torch.empty(0, dtype=torch.int32, device=self.device)
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
         ahead = None
         if device_ids is not None:
@@ -147,83 +247,57 @@ class ModelRunner:
         b, t = len(items), sum(lens)
         s = sum(len(it.want) for it in items)
         page = self.cache.page_size
+        slots_np = np.fromiter((it.slot for it in items), dtype=np.int32, count=b)
+        starts_np = np.fromiter((it.start for it in items), dtype=np.int64, count=b)
+        ends_np = starts_np + np.asarray(lens, dtype=np.int64)
+        self._check_pages(slots_np, starts_np, ends_np)
         static = self.use_graphs and t == b and all(tuple(it.want) == (0,) for it in items)
         if static:  # the shapes of a captured step may not depend on the step: full-width page tables
             widths = {gi: self.cache.max_pages_per_seq for gi in range(len(self.cache.groups))}
         else:
-            widths = {gi: max(pages_for(it.start + n, page) for it, n in zip(items, lens))
-                      for gi in range(len(self.cache.groups))}
-        tables = self.cache.tables_for([it.slot for it in items], widths)
-        self._check_tables(items, tables)
+            widths = {gi: pages_for(int(ends_np.max()), page) for gi in range(len(self.cache.groups))}
 
-        # layout of the one staging buffer (int32 words)
-        o_ids, o_pos, o_item = 0, t, 2 * t
-        o_start = 3 * t
-        o_kvlen = o_start + b + 1
-        o_slot = o_kvlen + b
-        o_rows = o_slot + b
-        o_tab = o_rows + s
-        total = o_tab + sum(b * w for w in widths.values())
-
+        lay = _Layout(t, b, s, rows_are_items=static)
+        n_pairs = self.cache.pending_deltas()
+        room = max(n_pairs, 4 * b + 64) if static else n_pairs  # a captured step keeps room for later steps' pairs
+        total = lay.pairs + 2 * n_pairs
         host = self._staging(total)
         buf = host.numpy()
         views: list[ItemView] = []
         tok = ri = 0
-        buf[o_start] = 0
+        buf[lay.start] = 0
         for i, (it, n) in enumerate(zip(items, lens)):
-            buf[o_ids + tok: o_ids + tok + n] = it.tokens
+            buf[lay.ids + tok: lay.ids + tok + n] = it.tokens
             first = 0 if self.inject_bug == "rope_relative" else it.start
-            buf[o_pos + tok: o_pos + tok + n] = np.arange(first, first + n, dtype=np.int32)  # absolute positions
-            buf[o_item + tok: o_item + tok + n] = i
-            buf[o_kvlen + i] = it.start + n - (1 if self.inject_bug == "kv_len_short" and it.start + n > n else 0)
-            buf[o_slot + i] = it.slot
+            buf[lay.pos + tok: lay.pos + tok + n] = np.arange(first, first + n, dtype=np.int32)  # absolute positions
+            buf[lay.item + tok: lay.item + tok + n] = i
+            buf[lay.kvlen + i] = it.start + n - (1 if self.inject_bug == "kv_len_short" and it.start + n > n else 0)
+            buf[lay.slot + i] = it.slot
             for w in it.want:
-                buf[o_rows + ri] = tok + w
+                buf[lay.rows + ri] = tok + w
+                buf[lay.rowslot + ri] = it.slot
                 ri += 1
             views.append(ItemView(slot=it.slot, start=it.start, end=it.start + n, first_token=tok))
             tok += n
-            buf[o_start + i + 1] = tok
-        at = o_tab
-        table_at: dict[int, tuple[int, int]] = {}
-        for gi, table in tables.items():
-            w = widths[gi]
-            buf[at: at + b * w] = table.reshape(-1)
-            table_at[gi] = (at, w)
-            at += b * w
+            buf[lay.start + i + 1] = tok
+        n_pairs = self.cache.drain_deltas(buf, lay.pairs)
 
         self.last_h2d_bytes = 4 * total
         if static:
-            dev = torch.empty(total, dtype=torch.int32, device=self.device)
-            dev.copy_(host[:total], non_blocking=True)
+            dev = torch.empty(lay.pairs + 2 * room, dtype=torch.int32, device=self.device)
+            dev[:total].copy_(host[:total], non_blocking=True)
         else:
             dev = host[:total].to(self.device, non_blocking=True)
         self._copied.record()
         self._copy_pending = True
         if device_ids is not None:
-            dev[o_ids: o_ids + t].copy_(device_ids)
-
-        ctx = StepContext(
-            num_tokens=t,
-            num_items=b,
-            compute_dtype=self.model.compute_dtype,
-            device=self.device,
-            items=views,
-            token_ids=dev[o_ids: o_ids + t],
-            positions=dev[o_pos: o_pos + t],
-            token_item=dev[o_item: o_item + t],
-            item_start=dev[o_start: o_start + b + 1],
-            kv_len=dev[o_kvlen: o_kvlen + b],
-            slots=dev[o_slot: o_slot + b],
-            block_tables={gi: dev[a: a + b * w].view(b, w) for gi, (a, w) in table_at.items()},
-            max_new_tokens=max(lens),
-            max_kv_len=max(it.start + n for it, n in zip(items, lens)),
-            all_decode=all(n == 1 for n in lens),
-        )
-        if static:
-            ctx.extras["static_kv_len"] = self.cache.max_seq_len
-        rows = dev[o_rows: o_rows + s]
+            dev[lay.ids: lay.ids + t].copy_(device_ids)
+        rows = dev[lay.rows: lay.rows + s]
+        self.last_row_slots = dev[lay.rowslot: lay.rowslot + s]
         with library.pinned_stream():  # one look-up of the stream for the step's hundred-odd launches
-            logits = self.model.forward(ctx, self.cache.view, rows)  # this step's result, computed eagerly
+            if n_pairs:
+                ops.scatter_words(self.cache.resident, dev[lay.pairs:], n_pairs)
+            logits = self._device_step(lay, dev, widths, views, lens, static, rows)  # this step's result, computed eagerly
         self.steps_run += 1
         if static:
             # Capture the same launches for later steps of this batch size.  Nothing runs during capture; the eager
@@ -234,15 +308,17 @@ class ModelRunner:
             before = library.launches
             with torch.cuda.graph(graph, pool=self._graph_pool):
                 with library.pinned_stream():  # the capture's own stream
-                    static_logits = self.model.forward(ctx, self.cache.view, rows)
-            self._graphs[b] = _DecodeGraph(inputs=dev, logits=static_logits, graph=graph, kernels=library.launches - before)
+                    static_logits = self._device_step(lay, dev, widths, views, lens, static, rows)
+            self._graphs[b] = _DecodeGraph(inputs=dev, logits=static_logits, graph=graph, var_at=lay.var, pairs_at=lay.pairs,
+                                           pairs_room=room, kernels=library.launches - before)
             library.launches = before  # recorded, not run
         return logits
 
     def _replay(self, items: Sequence[StepItem], held: _DecodeGraph, device_ids: torch.Tensor | None = None,
                 ahead: np.ndarray | None = None) -> torch.Tensor:
-        """A pure-decode step of a batch size that has been captured: the same checks and the same buffer layout as
-        the general path, written with array operations instead of per-item loops, then one copy and one replay."""
+        """A pure-decode step of a batch size that has been captured: the same checks as the general path, written
+        with array operations instead of per-item loops, then one copy of the words that change (token, position,
+        length and slot per request, and the resident array's changed words) and one replay."""
         cache = self.cache
         b = len(items)
         slots = np.fromiter((it.slot for it in items), dtype=np.int32, count=b)
@@ -258,42 +334,29 @@ class ModelRunner:
             raise EngineError(f"a position exceeds max_seq_len {cache.max_seq_len}")
         if toks.min() < 0 or toks.max() >= self.vocab_size:
             raise EngineError(f"token id outside [0, {self.vocab_size})")
-        page = cache.page_size
-        need = (starts + page) // page  # pages that must be held to cover position `start`
-        width = cache.max_pages_per_seq
-        t = s = b
-        o_ids, o_pos, o_item, o_start = 0, t, 2 * t, 3 * t
-        o_kvlen = o_start + b + 1
-        o_slot = o_kvlen + b
-        o_rows = o_slot + b
-        o_tab = o_rows + s
-        total = o_tab + len(cache.groups) * b * width
+        self._check_pages(slots, starts, starts + 1)
+        if cache.pending_deltas() > held.pairs_room:
+            self._send_deltas_alone()
+        n_pairs = cache.pending_deltas()
+        total = 4 * b + 2 * n_pairs
         host = self._staging(total)
         buf = host.numpy()
-        cols = np.arange(width)[None, :]
-        at = o_tab
-        for gi, g in enumerate(cache.groups):
-            table = buf[at: at + b * width].reshape(b, width)
-            g.tables.gather(slots, width, table)
-            first = 0 if g.window is None else np.maximum(0, starts - g.window + 1)[:, None] // page
-            live = (cols >= first) & (cols < need[:, None])
-            if (live & ((table < 0) | (table >= g.pool.num_blocks))).any():
-                raise EngineError(f"a page table of group {gi} lacks a page or names one outside the pool")
-            at += b * width
-        ramp = np.arange(b + 1, dtype=np.int32)
-        buf[o_ids: o_ids + b] = toks
-        buf[o_pos: o_pos + b] = 0 if self.inject_bug == "rope_relative" else starts
-        buf[o_item: o_item + b] = ramp[:b]
-        buf[o_start: o_start + b + 1] = ramp
-        buf[o_kvlen: o_kvlen + b] = starts + 1 - (1 if self.inject_bug == "kv_len_short" else 0) * (starts > 0)
-        buf[o_slot: o_slot + b] = slots
-        buf[o_rows: o_rows + b] = ramp[:b]
+        buf[0: b] = toks
+        buf[b: 2 * b] = 0 if self.inject_bug == "rope_relative" else starts
+        buf[2 * b: 3 * b] = starts + 1 - (1 if self.inject_bug == "kv_len_short" else 0) * (starts > 0)
+        buf[3 * b: 4 * b] = slots
+        n_pairs = cache.drain_deltas(buf, 4 * b)
         self.last_h2d_bytes = 4 * total
-        held.inputs.copy_(host[:total], non_blocking=True)
+        # ids, positions, lengths and slots are adjacent in the captured buffer and the pairs follow them
+        held.inputs[held.var_at: held.var_at + total].copy_(host[:total], non_blocking=True)
         self._copied.record()
         self._copy_pending = True
         if device_ids is not None:
-            held.inputs[o_ids: o_ids + b].copy_(device_ids)
+            held.inputs[held.var_at: held.var_at + b].copy_(device_ids)
+        self.last_row_slots = held.inputs[held.var_at + 3 * b: held.var_at + 4 * b]
+        if n_pairs:
+            with library.pinned_stream():
+                ops.scatter_words(cache.resident, held.inputs[held.pairs_at:], n_pairs)
         held.graph.replay()
         library.launches += held.kernels  # this library's kernels inside the replayed graph
         self.steps_run += 1

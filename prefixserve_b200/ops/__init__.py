@@ -14,5 +14,8 @@ from .kernels import (  # noqa: F401
     qkv_rope_append,
     rope_append,
     sample,
+    sample_slots,
+    scatter_words,
+    step_prepare,
     silu_mul,
 )

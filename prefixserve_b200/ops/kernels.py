@@ -290,3 +290,53 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor | None = None, seed: 
     check(lib().psb_sample(logits.data_ptr(), _ptr(temperature), _ptr(seed), _ptr(position), out.data_ptr(),
                            _ptr(scratch), s, v, _stream()), "sample")
     return out
+
+
+def sample_slots(logits: torch.Tensor, records: torch.Tensor, row_slot: torch.Tensor) -> torch.Tensor:
+    """The same choice with each row's temperature, seed and position read on the device from the record of the row's
+    request slot (``records`` int32 [num_slots, words]: position, temperature bits, seed low, seed high) -> int32 [S]."""
+    _dev(logits, "logits"), _i32(records, "slot records"), _i32(row_slot, "slot of each row")
+    if logits.dtype != torch.float32 or logits.dim() != 2:
+        raise KernelError(f"logits must be float32 [S, V], are {logits.dtype} {tuple(logits.shape)}")
+    s, v = logits.shape
+    if records.dim() != 2 or records.shape[1] < 4 or row_slot.numel() != s:
+        raise KernelError(f"slot records must be [slots, >=4] and one slot per logits row is needed, got {tuple(records.shape)}, "
+                          f"{row_slot.numel()} slots for {s} rows")
+    out = torch.empty((s,), dtype=torch.int32, device=logits.device)
+    need = lib().psb_sample_scratch_bytes(s, v)
+    scratch = torch.empty((need,), dtype=torch.uint8, device=logits.device) if need else None
+    check(lib().psb_sample_slots(logits.data_ptr(), records.data_ptr(), row_slot.data_ptr(), records.shape[1], out.data_ptr(),
+                                 _ptr(scratch), s, v, _stream()), "sample")
+    return out
+
+
+def scatter_words(resident: torch.Tensor, pairs: torch.Tensor, count: int) -> None:
+    """resident[pairs[2i]] = pairs[2i+1] for i < count (int32 arrays on the device; every index at most once)."""
+    _i32(resident, "resident array"), _i32(pairs, "index/value pairs")
+    if count < 0 or pairs.numel() < 2 * count:
+        raise KernelError(f"{count} pairs do not fit in {pairs.numel()} words")
+    check(lib().psb_scatter_words(resident.data_ptr(), pairs.data_ptr(), count, resident.numel(), _stream()), "scatter_words")
+
+
+def step_prepare(records: torch.Tensor | None, kv_len: torch.Tensor | None, slots: torch.Tensor, rows: torch.Tensor | None,
+                 out: torch.Tensor | None) -> None:
+    """out[i, :] = rows[slots[i], :width] (the page table of a step from the rows that stay on the device, padded
+    with -1 beyond their width), and records[slots[i]].position = kv_len[i].  Either half may be left out."""
+    _i32(slots, "slots")
+    b = slots.numel()
+    num_slots = record_words = row_width = width = 0
+    if records is not None:
+        _i32(records, "slot records"), _i32(kv_len, "kv_len")
+        if records.dim() != 2 or kv_len.numel() != b:
+            raise KernelError("slot records must be [slots, words] and kv_len needs one entry per item")
+        num_slots, record_words = records.shape
+    if rows is not None:
+        _i32(rows, "resident page table"), _i32(out, "page table of the step")
+        if rows.dim() != 2 or out.dim() != 2 or out.shape[0] != b:
+            raise KernelError(f"page tables must be [slots, pages] and [{b}, width], are {tuple(rows.shape)} and {tuple(out.shape)}")
+        num_slots, row_width = rows.shape
+        width = out.shape[1]
+    if records is None and rows is None:
+        return
+    check(lib().psb_step_prepare(_ptr(records), record_words, _ptr(kv_len), slots.data_ptr(), _ptr(rows), row_width, _ptr(out),
+                                 width, b, num_slots, _stream()), "step_prepare")

@@ -85,6 +85,12 @@ _SIGNATURES: dict[str, list] = {
     "psb_tcgen05_status": [],
     # (logits, temperature, seed, position, out, scratch, S, V, stream)
     "psb_sample": [P, P, P, P, P, P, I, I, P],
+    # (logits, records, row_slot, record_words, out, scratch, S, V, stream)
+    "psb_sample_slots": [P, P, P, I, P, P, I, I, P],
+    # (resident, pairs, n, limit, stream)
+    "psb_scatter_words": [P, P, I, I, P],
+    # (records, record_words, kv_len, slots, rows, row_width, out, width, num_items, num_slots, stream)
+    "psb_step_prepare": [P, I, P, P, P, I, P, I, I, I, P],
     # (S, V) -> bytes of scratch psb_sample wants
     "psb_sample_scratch_bytes": [I, I],
 }

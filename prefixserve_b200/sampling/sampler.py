@@ -2,23 +2,16 @@
 
 from __future__ import annotations
 
-from typing import Sequence
-
 import torch
 
 from .. import ops
-from . import SamplingParams
 
 
-def choose_tokens(logits: torch.Tensor, params: Sequence[SamplingParams], positions: Sequence[int]) -> torch.Tensor:
+def choose_tokens(logits: torch.Tensor, records: torch.Tensor, row_slots: torch.Tensor) -> torch.Tensor:
     """logits float32 [S, V] on the device -> int32 [S] on the device.
 
-    ``positions[i]`` is the absolute position of the token being chosen for row i.
+    ``row_slots[i]`` is the request slot of row i; the row's temperature, seed and the absolute position of the
+    token being chosen are read on the device from that slot's record (``CacheManager.records_dev``), where
+    admission and the step itself have put them.  Nothing is built on the host for a step.
     """
-    if all(p.temperature == 0 for p in params):
-        return ops.sample(logits)
-    dev = logits.device
-    temperature = torch.tensor([p.temperature for p in params], dtype=torch.float32, device=dev)
-    seed = torch.tensor([p.seed for p in params], dtype=torch.int64, device=dev)
-    position = torch.tensor(list(positions), dtype=torch.int32, device=dev)
-    return ops.sample(logits, temperature, seed, position)
+    return ops.sample_slots(logits, records, row_slots)

@@ -120,3 +120,58 @@ def test_random_request_orders_lose_nothing(seed):
         cm.close(s)
     cm.check()
     assert cm.free_pages(0) == 40 and cm.free_pages(1) == 12 and cm.slots.num_free == 5
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_changed_words_reach_a_device_copy_through_every_turn_of_a_slot(seed):
+    """The page tables and slot records stay on the device; a step sends only the words that changed.  Here the
+    "device" is a numpy array that receives nothing but the drained (index, value) pairs, at random moments, while
+    slots open, grow, lose pages to their window, close and are reopened.  After every drain the device copy must
+    name, for every open slot and every page index a step could read, the page the host holds there."""
+    rng = random.Random(seed)
+    cm = CacheManager([FULL, WINDOWED], num_pages={0: 30, 1: 10}, num_slots=4, max_seq_len=200)
+    device = np.full(cm.resident_words, -1, dtype=np.int32)
+    device[: cm.num_slots * cm.record_words] = 0
+    live: dict[int, int] = {}
+    sampling: dict[int, tuple[float, int]] = {}
+
+    def send():
+        n = cm.pending_deltas()
+        out = np.zeros(2 * n + 3, dtype=np.int32)
+        assert cm.drain_deltas(out, 3) == n and cm.pending_deltas() == 0
+        pairs = out[3: 3 + 2 * n].reshape(n, 2)
+        assert len(set(pairs[:, 0].tolist())) == n   # every index at most once: the scatter kernel's threads never meet
+        device[pairs[:, 0]] = pairs[:, 1]
+        for gi, g in enumerate(cm.groups):
+            base = cm._table_base[gi]
+            rows = device[base: base + cm.num_slots * cm.max_pages_per_seq].reshape(cm.num_slots, cm.max_pages_per_seq)
+            for s, upto in live.items():
+                first = cm._first_needed_page(g, upto)   # what the next step of this slot can still read
+                want = cm.page_ids(s, gi)[first:]
+                assert rows[s, first: first + len(want)].tolist() == want and all(p >= 0 for p in want)
+        records = device[: cm.num_slots * cm.record_words].reshape(cm.num_slots, cm.record_words)
+        for s, (temperature, sd) in sampling.items():
+            assert records[s, 1:2].view(np.float32)[0] == np.float32(temperature)
+            assert (int(records[s, 2]) & 0xFFFFFFFF) | ((int(records[s, 3]) & 0xFFFFFFFF) << 32) == sd
+
+    for _ in range(400):
+        r = rng.random()
+        if r < 0.2 and len(live) < 4:
+            s = cm.open()
+            live[s] = 0
+            sampling[s] = (rng.choice([0.0, 0.7, 1.5]), rng.getrandbits(64))
+            cm.set_sampling(s, *sampling[s])
+        elif r < 0.8 and live:
+            s = rng.choice(list(live))
+            upto = min(live[s] + rng.choice([1, 1, 3, 16, 40]), 200)
+            if cm.reserve(s, upto):
+                live[s] = upto
+                cm.advance(s, upto)
+        elif r < 0.9 and live:   # closed (finished or preempted); the slot comes back to a later request
+            s = rng.choice(list(live))
+            cm.close(s)
+            del live[s], sampling[s]
+        if rng.random() < 0.3:
+            send()
+    send()
+    assert cm.pending_deltas() == 0
