@@ -52,6 +52,7 @@ class PendingStep:
     tokens_dev: torch.Tensor | None      # int32 [len(sampling)] on the device
     host: torch.Tensor | None            # the same in pinned host memory once ``done`` has passed
     done: torch.cuda.Event | None
+    logits: torch.Tensor | None = None   # with ``Engine.capture_logits``: float32 [len(sampling), vocab], a copy on the device
 
 
 class Engine:
@@ -104,11 +105,14 @@ class Engine:
         return self.finish(self.launch(batch))
 
     @torch.inference_mode()
-    def launch(self, batch: Batch, feed: "PendingStep | None" = None) -> "PendingStep":
+    def launch(self, batch: Batch, feed: "PendingStep | None" = None,
+               override: "dict[str, int] | None" = None) -> "PendingStep":
         """Puts one batch on the device (forward, sampling, copy of the tokens to pinned host memory) and returns
         without waiting for it.  ``feed``: the step launched just before, not finished yet, whose sampled tokens are
         this batch's input tokens (a batch from ``Scheduler.schedule_ahead``); they go from its output to this step's
-        input on the device."""
+        input on the device.  ``override`` (request id -> token): these tokens stand in for the sampled ones, on the
+        device too, so that a step fed from this one continues with them (teacher forcing, as the reference's tests
+        do at commit: tests/gpu/test_engine_flashinfer.py:50-77 of PrefixServe)."""
         work = batch.work
         if not work:
             return PendingStep(batch, [], None, None, None)
@@ -133,20 +137,29 @@ class Engine:
         if not sampling:
             return PendingStep(batch, [], None, None, None)  # nothing to read back: the host runs ahead
         tokens = choose_tokens(logits, self.cache.records_dev, self.runner.last_row_slots)
-        if self.capture_logits:
-            self.last_logits = {w.req.req_id: logits[i].cpu() for i, w in enumerate(sampling)}
+        if override is not None:
+            given = [override.get(w.req.req_id) for w in sampling]
+            if all(g is not None for g in given):
+                tokens = torch.tensor(given, dtype=torch.int32).to(self.device, non_blocking=True)
+            elif any(g is not None for g in given):
+                mask = torch.tensor([g is not None for g in given]).to(self.device)
+                tokens = torch.where(mask, torch.tensor([g or 0 for g in given], dtype=torch.int32).to(self.device), tokens)
+        kept = logits.clone() if self.capture_logits else None  # a replayed graph's logits last until its next replay
         host = self._token_buffers[self._token_turn % len(self._token_buffers)][: len(sampling)]
         self._token_turn += 1
         host.copy_(tokens, non_blocking=True)  # the step's one device-to-host read
         done = torch.cuda.Event()
         done.record()
-        return PendingStep(batch, sampling, tokens, host, done)
+        return PendingStep(batch, sampling, tokens, host, done, kept)
 
     def finish(self, pending: "PendingStep") -> dict[str, int]:
         """Waits for a launched step; returns request id -> next token for the items that sample."""
         if pending.done is None:
             return {}
         pending.done.synchronize()
+        if pending.logits is not None:
+            rows = pending.logits.cpu()
+            self.last_logits = {w.req.req_id: rows[i] for i, w in enumerate(pending.sampling)}
         return {w.req.req_id: tok for w, tok in zip(pending.sampling, pending.host.tolist())}
 
     def check_device_status(self) -> None:

@@ -59,6 +59,7 @@ class _DecodeGraph:
     pairs_at: int    # where the (index, value) pairs of the resident array begin
     pairs_room: int  # how many pairs fit
     kernels: int = 0  # launches of this library's kernels recorded in the graph
+    by_name: dict | None = None  # the same by entry point
 
 
 @dataclass
@@ -305,13 +306,15 @@ class ModelRunner:
             graph = torch.cuda.CUDAGraph()
             if self._graph_pool is None:
                 self._graph_pool = torch.cuda.graph_pool_handle()
-            before = library.launches
+            before, named = library.launches, library.launch_counts.copy()
             with torch.cuda.graph(graph, pool=self._graph_pool):
                 with library.pinned_stream():  # the capture's own stream
                     static_logits = self._device_step(lay, dev, widths, views, lens, static, rows)
+            recorded = library.launch_counts - named
             self._graphs[b] = _DecodeGraph(inputs=dev, logits=static_logits, graph=graph, var_at=lay.var, pairs_at=lay.pairs,
-                                           pairs_room=room, kernels=library.launches - before)
+                                           pairs_room=room, kernels=library.launches - before, by_name=dict(recorded))
             library.launches = before  # recorded, not run
+            library.launch_counts.subtract(recorded)
         return logits
 
     def _replay(self, items: Sequence[StepItem], held: _DecodeGraph, device_ids: torch.Tensor | None = None,
@@ -359,6 +362,7 @@ class ModelRunner:
                 ops.scatter_words(cache.resident, held.inputs[held.pairs_at:], n_pairs)
         held.graph.replay()
         library.launches += held.kernels  # this library's kernels inside the replayed graph
+        library.launch_counts.update(held.by_name)
         self.steps_run += 1
         self.graph_replays += 1
         return held.logits

@@ -8,6 +8,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+from collections import Counter
 from ctypes import c_float, c_int, c_int64, c_void_p
 
 import torch
@@ -171,11 +172,13 @@ def declare(name: str, argtypes: list) -> None:
 
 
 launches = 0  # kernels of this library launched so far (benchmarks report the difference over a timed region)
+launch_counts: Counter = Counter()  # the same by entry point ("attention_decode", "gemm_tcgen05", ...)
 
 
 def check(status: int, what: str) -> None:
     global launches
     launches += 1
+    launch_counts[what] += 1
     if status != 0:
         detail = lib().psb_last_error().decode(errors="replace")
         raise KernelError(f"{what}: {detail} (status {status})")

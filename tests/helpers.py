@@ -33,7 +33,14 @@ TINY_D = dict(
                     rope_scaling=Llama3RopeScaling(2.0, 1.0, 4.0, 32), max_position_embeddings=1024,
                     tie_word_embeddings=True),
     seed=3, std=0.08, gain_noise=0.1)
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+# head size 128, one key/value head for three query heads: the other size the tensor-core attention kernels are built for
+TINY_E = dict(
+    cfg=LlamaConfig(vocab_size=411, hidden_size=192, intermediate_size=224, num_layers=2, num_heads=3, num_kv_heads=1,
+                    head_dim=128, rms_norm_eps=2e-6, rope_theta=123456.0,
+                    rope_scaling=Llama3RopeScaling(16.0, 1.0, 8.0, 48), max_position_embeddings=2048,
+                    tie_word_embeddings=False),
+    seed=4, std=0.06, gain_noise=0.15)
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
 
 
 def make_folder(tmp, which: str, dtype=torch.float32):
@@ -120,6 +127,35 @@ def trace_mixed(seqs: dict[str, list[int]], max_live: int = 4, seed: int = 0, pr
             if rec[2] == len(toks):
                 ended.append(rid)
         live = [rec for rec in live if rec[2] < len(rec[1])]
+        steps.append({"step": n, "entries": entries, "end": ended})
+        n += 1
+    return steps
+
+
+def trace_many_live(seqs: dict[str, list[int]], tail: int = 12, portion_beside: bool = True):
+    """Every request live at once: request k's prompt (all but its last ``tail`` tokens) arrives in step k in one
+    portion beside single decoded tokens of the requests before it; then all decode together until they end, the
+    shorter ones first.  With dozens of requests the decode steps have dozens of rows."""
+    order = list(seqs.items())
+    at = {rid: 0 for rid, _ in order}
+    steps = []
+    n = 0
+    started = 0
+    while any(at[rid] < len(toks) for rid, toks in order):
+        entries, ended = [], []
+        for k, (rid, toks) in enumerate(order):
+            if k < started and at[rid] < len(toks):
+                entries.append({"id": rid, "tokens": [toks[at[rid]]], "want": [0]})
+                at[rid] += 1
+            elif k == started:
+                head = max(len(toks) - tail, 1)
+                entries.append({"id": rid, "tokens": toks[:head], "want": [head - 1] if portion_beside else list(range(head))})
+                at[rid] = head
+            else:
+                continue
+            if at[rid] == len(toks):
+                ended.append(rid)
+        started = min(started + 1, len(order))
         steps.append({"step": n, "entries": entries, "end": ended})
         n += 1
     return steps

@@ -16,7 +16,7 @@ import plain_model
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parents[1]
 
-LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 16, 40, 70, 131], "C": [3, 48, 97], "D": [2, 64, 129, 300]}
+LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 16, 40, 70, 131], "C": [3, 48, 97], "D": [2, 64, 129, 300], "E": [2, 70, 140, 260]}
 TRACES = {
     "whole": helpers.trace_whole,
     "tail_decode": helpers.trace_tail_decode,
@@ -58,7 +58,7 @@ def replay(folder, dtype, steps, max_tokens=None):
     return helpers.collect(steps, outputs)
 
 
-@pytest.mark.parametrize("which", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("which", ["A", "B", "C", "D", "E"])
 @pytest.mark.parametrize("kind", list(TRACES))
 def test_float32_matches_plain(folders, truth, which, kind):
     seqs = sequences(which)
@@ -72,7 +72,7 @@ def test_float32_matches_plain(folders, truth, which, kind):
         assert err <= tol, f"{which}/{kind}: request {rid} position {pos}: |diff| {err:.3e} > {tol:.3e}"
 
 
-@pytest.mark.parametrize("which", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("which", ["A", "B", "C", "D", "E"])
 @pytest.mark.parametrize("kind", list(TRACES))
 def test_bfloat16_close_to_float32_truth(folders, truth, which, kind):
     """bfloat16 engine vs float32 truth, judged against a plain bfloat16 run of the same weights."""
@@ -88,7 +88,7 @@ def test_bfloat16_close_to_float32_truth(folders, truth, which, kind):
         assert ours < 0.15 and ours <= 1.5 * theirs + 1e-3, f"{which}/{kind}/{rid}: engine {ours:.4f}, plain bf16 {theirs:.4f}"
 
 
-@pytest.mark.parametrize("which", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("which", ["A", "B", "C", "D", "E"])
 @pytest.mark.parametrize("kind", list(TRACES))
 def test_bfloat16_with_weights_stored_in_bfloat16(tmp_path, which, kind):
     """The same with a checkpoint in bfloat16: every product then runs on the bfloat16 kernels (a tensor that a
