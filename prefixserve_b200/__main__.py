@@ -9,7 +9,12 @@ them (prefixserve/server.py:567-581): --model, --dtype, --max-seq-len,
 The reference serves HTTP and tokenises text; this program reads token ids and
 prints token ids (one JSON object per prompt, then the scheduler's counters).
 Without --model, --random-config NAME --seed N first writes a random-weights
-model folder and runs that.
+model folder and runs that.  --max-seq-len defaults to the smaller of the
+reference's 8192 and the model's own position limit.
+
+Two sub-commands hand over to the other programs of the repository:
+``python -m prefixserve_b200 replay ...`` is ``bin/trace_run ...`` and
+``python -m prefixserve_b200 bench ...`` is ``bench.py ...`` of a source checkout.
 """
 
 from __future__ import annotations
@@ -28,7 +33,7 @@ def parse_args(argv=None) -> argparse.Namespace:
     p.add_argument("--seed", type=int, default=0, help="seed of the random weights")
     p.add_argument("--save-model", default=None, help="with --random-config: keep the written folder here")
     p.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
-    p.add_argument("--max-seq-len", type=int, default=8192)
+    p.add_argument("--max-seq-len", type=int, default=None, help="default: min(8192, the model's max_position_embeddings)")
     p.add_argument("--num-blocks", type=int, default=None, help="cache pages; default: sized from free GPU memory")
     p.add_argument("--max-waiting", type=int, default=1024)
     p.add_argument("--max-running-requests", type=int, default=64)
@@ -40,6 +45,9 @@ def parse_args(argv=None) -> argparse.Namespace:
     p.add_argument("--temperature", type=float, default=0.0)
     p.add_argument("--sampling-seed", type=int, default=0)
     p.add_argument("--ignore-eos", action="store_true")
+    p.add_argument("--stop-token-ids", default="", help="comma-separated ids that end a request, beside the model's own")
+    p.add_argument("--cast-float32-weights", action="store_true",
+                   help="round matrices the checkpoint stores in 32-bit to the compute type at load (the reference does)")
     return p.parse_args(argv)
 
 
@@ -54,6 +62,18 @@ def read_prompts(args: argparse.Namespace) -> list[list[int]]:
 
 
 def main(argv=None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if argv and argv[0] == "replay":
+        from .engine.replay import main as replay_main
+        return replay_main(argv[1:])
+    if argv and argv[0] == "bench":
+        import runpy
+        script = Path(__file__).resolve().parents[1] / "bench.py"
+        if not script.exists():
+            raise SystemExit("bench.py lies beside the package in a source checkout; it is not part of an installed package")
+        sys.argv = [str(script)] + argv[1:]
+        runpy.run_path(str(script), run_name="__main__")
+        return 0
     args = parse_args(argv)
     prompts = read_prompts(args)
     if (args.model is None) == (args.random_config is None):
@@ -79,9 +99,11 @@ def main(argv=None) -> int:
     try:
         llm = LLM(model_dir, dtype=args.dtype, max_seq_len=args.max_seq_len, num_blocks=args.num_blocks,
                   max_running_requests=args.max_running_requests, chunked_prefill_size=args.chunked_prefill_size,
-                  enable_prefix_cache=not args.disable_prefix_cache, max_waiting=args.max_waiting)
+                  enable_prefix_cache=not args.disable_prefix_cache, max_waiting=args.max_waiting,
+                  cast_float32_weights=args.cast_float32_weights)
+        stops = tuple(int(t) for t in args.stop_token_ids.replace(",", " ").split())
         sp = SamplingParams(temperature=args.temperature, seed=args.sampling_seed, max_tokens=args.max_tokens,
-                            ignore_eos=args.ignore_eos)
+                            ignore_eos=args.ignore_eos, stop_token_ids=stops)
         outputs = llm.generate(prompts, sp)
         for prompt, out in zip(prompts, outputs):
             print(json.dumps({"prompt_ids": prompt, "output_ids": out}))

@@ -50,6 +50,13 @@ RadixTree::RadixTree(BlockManager& pool, int32_t page_tokens, uint64_t seed)
   heap_.reserve(cap);
   held_back_.reserve(cap);
   owned_.assign(static_cast<size_t>(pool.num_blocks()), 0);
+  // one 32-bit key per token position of a page (an odd page length gets one more for its padding)
+  uint64_t state = seed_;
+  keys_.resize((static_cast<size_t>(page_tokens) + 1) & ~size_t{1});
+  for (uint32_t& k : keys_) {
+    state += 0x9e3779b97f4a7c15ULL;
+    k = static_cast<uint32_t>(scramble(state));
+  }
 }
 
 RadixTree::~RadixTree() {
@@ -58,18 +65,25 @@ RadixTree::~RadixTree() {
   }
 }
 
-// Multiply-and-fold over token pairs, keyed by the seed and the parent, so the
-// same tokens under different parents land in unrelated slots.
+// The NH construction of the reference's tree (csrc/radix_tree.cpp:65-87 of PrefixServe): with one secret 32-bit key
+// per token position, sum over token pairs of (t[i] + k[i]) * (t[i+1] + k[i+1]), the additions wrapping at 32 bits and
+// the products and the sum kept in 64; two different pages collide with probability about 2^-32 whatever the
+// tokens are, because the keys are drawn from the seed and never shown.  The parent goes into the high half before
+// a final scramble, so the same tokens under different parents land in unrelated slots.  An odd page length is
+// padded with a zero token.
 uint64_t RadixTree::edge_hash(Node parent, const int32_t* toks) const noexcept {
-  uint64_t h = seed_ ^ (static_cast<uint64_t>(static_cast<uint32_t>(parent)) * 0x9e3779b97f4a7c15ULL);
+  uint64_t acc = 0;
   int32_t i = 0;
   for (; i + 1 < page_tokens_; i += 2) {
-    const uint64_t pair = (static_cast<uint64_t>(static_cast<uint32_t>(toks[i])) << 32) | static_cast<uint32_t>(toks[i + 1]);
-    h = (h ^ pair) * 0xff51afd7ed558ccdULL;
-    h ^= h >> 29;
+    const uint32_t a = static_cast<uint32_t>(toks[i]) + keys_[static_cast<size_t>(i)];
+    const uint32_t b = static_cast<uint32_t>(toks[i + 1]) + keys_[static_cast<size_t>(i) + 1];
+    acc += static_cast<uint64_t>(a) * static_cast<uint64_t>(b);
   }
-  if (i < page_tokens_) h = (h ^ static_cast<uint32_t>(toks[i])) * 0xc4ceb9fe1a85ec53ULL;
-  return scramble(h);
+  if (i < page_tokens_) {
+    const uint32_t a = static_cast<uint32_t>(toks[i]) + keys_[static_cast<size_t>(i)];
+    acc += static_cast<uint64_t>(a) * static_cast<uint64_t>(keys_[static_cast<size_t>(i) + 1]);
+  }
+  return scramble(acc ^ (static_cast<uint64_t>(static_cast<uint32_t>(parent)) << 32));
 }
 
 int64_t RadixTree::lookup(Node parent, const int32_t* toks, uint64_t h) const noexcept {

@@ -3,8 +3,8 @@
 //
 // Behaviour follows the reference's tree (csrc/radix_tree.hpp:36-144,
 // csrc/radix_tree.cpp:130-290 of PrefixServe):
-//  * children are found by hashing all tokens of the page together with the
-//    parent, and every hit is verified by comparing parent and tokens, so two
+//  * children are found by hashing all tokens of the page (NH: keyed sums of
+//    products of token pairs) together with the parent, and every hit is verified by comparing parent and tokens, so two
 //    siblings that start alike are never confused and correctness never rests
 //    on the hash;
 //  * match_prefix returns the longest cached prefix in whole pages and takes
@@ -100,6 +100,7 @@ class RadixTree {
   std::vector<Node> heap_;
   std::vector<Node> held_back_; // evict() scratch
   std::vector<uint8_t> owned_;  // per page: a node owns it
+  std::vector<uint32_t> keys_;  // per token position: secret key of the page hash
 };
 
 }  // namespace psb200

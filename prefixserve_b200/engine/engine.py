@@ -13,7 +13,7 @@ from __future__ import annotations
 
 import gc
 import logging
-from dataclasses import dataclass
+from dataclasses import dataclass, replace
 from pathlib import Path
 
 import numpy as np
@@ -21,6 +21,7 @@ import torch
 
 from ..cache.manager import CacheManager, pages_for
 from ..sampling.sampler import choose_tokens
+from ..config.registry import read_model_folder
 from .loading import load_model, parse_dtype
 from .scheduler import Batch
 from .step import EngineError, ModelRunner, StepItem
@@ -35,12 +36,13 @@ class EngineConfig:
     device: str = "cuda"
     max_num_seqs: int = 64           # must match the scheduler's max_decode_seqs
     max_prefill_tokens: int = 512    # must match the scheduler's budget
-    max_seq_len: int = 8192
+    max_seq_len: int | None = None   # None: the smaller of 8192 (the reference's default) and the model's positions
     num_blocks: int | None = None    # None: size the pool from free memory
     reserve_bytes: int = 1 << 30     # left free after the pool
     page_size: int = 16
     enable_prefix_cache: bool = True
     use_cuda_graphs: bool = True     # capture pure-decode steps per batch size and replay them
+    cast_float32_weights: bool = False  # round matrices a checkpoint stores in 32-bit to the compute type at load
 
 
 @dataclass
@@ -62,10 +64,15 @@ class Engine:
         if self.device.type != "cuda" or not torch.cuda.is_available():
             raise EngineError("no CUDA device: this engine has no CPU path")
         dtype = parse_dtype(cfg.dtype)
+        arch, model_cfg = read_model_folder(cfg.model_path)
+        positions = arch.to_spec(model_cfg).max_positions
+        if cfg.max_seq_len is None:
+            cfg = self.cfg = replace(cfg, max_seq_len=min(8192, positions))
+        elif cfg.max_seq_len > positions:
+            raise ValueError(f"max_seq_len {cfg.max_seq_len} exceeds the model's {positions} positions")
         self.arch, self.model_cfg, self.model = load_model(cfg.model_path, dtype=dtype, device=self.device,
-                                                           max_positions=cfg.max_seq_len)
-        if cfg.max_seq_len > self.model.spec.max_positions:
-            raise ValueError(f"max_seq_len {cfg.max_seq_len} exceeds the model's {self.model.spec.max_positions} positions")
+                                                           max_positions=cfg.max_seq_len,
+                                                           cast_float32=cfg.cast_float32_weights)
         self.dtype = dtype
         self.needs = self.model.cache_needs()
         self.bytes_per_block = CacheManager.bytes_per_page(self.needs, cfg.page_size, dtype)
@@ -94,6 +101,10 @@ class Engine:
     @property
     def max_seq_len(self) -> int:
         return self.cfg.max_seq_len
+
+    def weight_bytes(self) -> int:
+        """Bytes of the loaded weights, a tied head counted once."""
+        return self.model.num_bytes()
 
     @property
     def stop_token_ids(self) -> frozenset[int]:

@@ -22,14 +22,14 @@ from .scheduler import AddResult, Scheduler, SchedulerStats
 
 
 class LLM:
-    def __init__(self, model: str | Path, *, dtype: str | torch.dtype = "bfloat16", max_seq_len: int = 8192,
+    def __init__(self, model: str | Path, *, dtype: str | torch.dtype = "bfloat16", max_seq_len: int | None = None,
                  num_blocks: int | None = None, max_running_requests: int = 64, chunked_prefill_size: int = 512,
                  enable_prefix_cache: bool = True, max_waiting: int = 1024, page_size: int = 16,
-                 device: str = "cuda", warm_up: bool = True) -> None:
+                 device: str = "cuda", warm_up: bool = True, cast_float32_weights: bool = False) -> None:
         self.engine = Engine(EngineConfig(
             model_path=Path(model), dtype=parse_dtype(dtype), device=device, max_num_seqs=max_running_requests,
             max_prefill_tokens=chunked_prefill_size, max_seq_len=max_seq_len, num_blocks=num_blocks,
-            page_size=page_size, enable_prefix_cache=enable_prefix_cache))
+            page_size=page_size, enable_prefix_cache=enable_prefix_cache, cast_float32_weights=cast_float32_weights))
         self.scheduler = Scheduler(self.engine.cache, max_waiting=max_waiting, chunk_size=chunked_prefill_size,
                                    stop_token_ids=self.engine.stop_token_ids, enable_prefix_cache=enable_prefix_cache)
         self.max_running_requests = max_running_requests
@@ -59,17 +59,25 @@ class LLM:
         outputs: dict[str, list[int]] = {rid: [] for rid in ids}
         sched, engine = self.scheduler, self.engine
         pending = None  # the step on the device whose tokens have not been read yet
-        while pending is not None or sched.has_work():
-            if pending is None:
-                pending = engine.launch(sched.schedule_step(self.chunked_prefill_size, self.max_running_requests))
-            # while that step runs: decide and launch the one after it, if that can be done without its tokens
-            ahead = sched.schedule_ahead(self.max_running_requests)
-            following = engine.launch(ahead, feed=pending) if ahead is not None else None
-            result = sched.commit(pending.batch, engine.finish(pending))
-            for rid, tok in result.new_tokens.items():
-                outputs[rid].append(tok)
-            pending = following
-        engine.check_device_status()
+        try:
+            while pending is not None or sched.has_work():
+                if pending is None:
+                    pending = engine.launch(sched.schedule_step(self.chunked_prefill_size, self.max_running_requests))
+                # while that step runs: decide and launch the one after it, if that can be done without its tokens
+                ahead = sched.schedule_ahead(self.max_running_requests)
+                following = engine.launch(ahead, feed=pending) if ahead is not None else None
+                result = sched.commit(pending.batch, engine.finish(pending))
+                for rid, tok in result.new_tokens.items():
+                    outputs[rid].append(tok)
+                pending = following
+            engine.check_device_status()
+        except BaseException:
+            # nothing of this call may outlive it: the batch in flight is forgotten, every request of the call is
+            # ended and its slot and pages are given back, so that the next call starts clean
+            sched.abandon_inflight()
+            for rid in ids:
+                sched.free_request(rid)
+            raise
         return [outputs[rid] for rid in ids]
 
     def stats(self) -> SchedulerStats:

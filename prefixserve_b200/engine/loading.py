@@ -27,13 +27,13 @@ def parse_dtype(name: str | torch.dtype) -> torch.dtype:
 
 
 def load_model(folder: str | Path, *, dtype: torch.dtype, device: torch.device | str,
-               max_positions: int | None = None) -> tuple[Architecture, Any, DecoderModel]:
+               max_positions: int | None = None, cast_float32: bool = False) -> tuple[Architecture, Any, DecoderModel]:
     """Reads config.json, picks the model by its architecture name, loads the weights by tensor name."""
     arch, config = read_model_folder(folder)
     spec = arch.to_spec(config)
     model = build_model(spec)
     tensors = load_tensors(folder, model.param_table(), arch.tensor_name, lambda n: arch.ignorable(config, n),
-                           compute_dtype=dtype, device=device)
+                           compute_dtype=dtype, device=device, cast_float32=cast_float32)
     limit = spec.max_positions if max_positions is None else min(max_positions, spec.max_positions)
     model.load(tensors, compute_dtype=dtype, device=torch.device(device), max_positions=limit)
     return arch, config, model

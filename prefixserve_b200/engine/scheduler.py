@@ -302,7 +302,7 @@ class Scheduler:
             new_tokens[req.req_id] = token
             if req.abort_pending:
                 continue
-            if token in self._stop and not req.ignore_eos:
+            if (token in self._stop or token in req.sampling.stop_token_ids) and not req.ignore_eos:
                 reason = FinishReason.STOP
             elif len(req.output) >= req.max_tokens:
                 reason = FinishReason.LENGTH
@@ -316,6 +316,15 @@ class Scheduler:
                 finished[req.req_id] = FinishReason.ABORT
         self._abort_at_commit.clear()
         return StepResult(new_tokens, finished)
+
+    def abandon_inflight(self) -> None:
+        """After a step failed on the device: forgets the batch in flight (and one scheduled ahead) without a commit.
+        Requests keep what their last commit recorded; aborts that waited for the commit take effect now."""
+        self._inflight = self._ahead = None
+        for req in self._abort_at_commit:
+            if req.state is ReqState.RUNNING:
+                self._retire(req)
+        self._abort_at_commit.clear()
 
     def free_request(self, req_id: str) -> bool:
         """Aborts a request; harmless for unknown ids and when called twice."""
@@ -374,8 +383,12 @@ class Scheduler:
         if req_id in self._by_id:
             return AddResult.DUPLICATE_ID
         total = int(arr.size) + max_tokens
-        too_many_pages = any(pages_for(total, self.cache.page_size) > g.pool.num_blocks for g in self.cache.groups
-                             if g.window is None)
+        page = self.cache.page_size
+        # what the request holds at its largest: every page in a group of full attention; in a group with a window
+        # the window, the portion being computed and the page the window's start lies in
+        too_many_pages = any(
+            (pages_for(total, page) if g.window is None else min(pages_for(total, page), pages_for(g.window + self._chunk, page) + 1))
+            > g.pool.num_blocks for g in self.cache.groups)
         if too_many_pages or total > self.cache.max_seq_len:
             return AddResult.TOO_LONG
         if len(self._waiting) >= self._max_waiting:

@@ -49,6 +49,19 @@ class DecoderModel:
             self.head.tie(self.embedding.table)
         self.compute_dtype = compute_dtype
 
+    def num_bytes(self) -> int:
+        """Bytes of the weights on the device, every tensor once however many parts use it: a tied head is the
+        embedding's table (prefixserve/model/weights.py:49-59 counts by data pointer in the same way).  Start-up
+        tables that are not in the checkpoint (rotary angles) are not weights and do not count."""
+        seen: set[int] = set()
+        total = 0
+        for _, part in self.named_parts():
+            for value in vars(part).values():
+                if isinstance(value, torch.Tensor) and value.data_ptr() not in seen:
+                    seen.add(value.data_ptr())
+                    total += value.numel() * value.element_size()
+        return total
+
     # ---- cache -----------------------------------------------------------
     def cache_needs(self) -> list[CacheNeed]:
         """What each cache entry must hold (entry index -> need of the call that writes it)."""

@@ -19,12 +19,14 @@ class SamplingParams:
     seed: int = 0
     max_tokens: int = 16
     ignore_eos: bool = False
+    stop_token_ids: tuple[int, ...] = ()   # this request also ends on these (beside the model's own stop ids)
 
     def __post_init__(self) -> None:
         if self.temperature < 0:
             raise ValueError("temperature must be >= 0")
         if self.max_tokens < 1:
             raise ValueError("max_tokens must be >= 1")
+        object.__setattr__(self, "stop_token_ids", tuple(int(t) for t in self.stop_token_ids))
 
 
 GREEDY = SamplingParams()

@@ -9,7 +9,11 @@ unexpected, wrong shape) are reported together in one ``WeightLoadError``.
 Stored types are kept: 16-bit matrices stay bfloat16 on the bfloat16 path, a
 tensor stored in 32-bit stays float32 (the products then take the float32
 kernel), gains are widened to float32 (exact), integer tables become int32.
-On the float32 path everything is widened to float32.
+On the float32 path everything is widened to float32.  With
+``cast_float32=True`` matrices stored in 32-bit are rounded to the compute
+type at load instead, which is what the reference does with every tensor
+(prefixserve/model/weights.py:94-98): a float32 checkpoint then runs on the
+tensor cores like a bfloat16 one.
 """
 
 from __future__ import annotations
@@ -47,13 +51,13 @@ def shard_files(folder: Path) -> list[Path]:
     raise WeightLoadError(f"{folder} holds neither model.safetensors nor model.safetensors.index.json")
 
 
-def held_dtype(role: str, stored: torch.dtype, compute_dtype: torch.dtype) -> torch.dtype:
+def held_dtype(role: str, stored: torch.dtype, compute_dtype: torch.dtype, cast_float32: bool = False) -> torch.dtype:
     """The type a tensor has on the device, from its role, its stored type and the path's compute type."""
     if role == "table_int" or stored in _INT_TYPES:
         return torch.int32
     if compute_dtype == torch.float32 or role == "vector":
         return torch.float32
-    if stored in (torch.float32, torch.float64):
+    if stored in (torch.float32, torch.float64) and not cast_float32:
         return torch.float32  # stored in 32-bit: stays so
     return compute_dtype
 
@@ -66,6 +70,7 @@ def load_tensors(
     *,
     compute_dtype: torch.dtype,
     device: torch.device | str,
+    cast_float32: bool = False,
 ) -> dict[str, torch.Tensor]:
     """part path -> tensor on ``device``.  Raises one WeightLoadError naming every problem."""
     folder = Path(folder)
@@ -108,11 +113,12 @@ def load_tensors(
         wide = 0
         for path, spec in wanted.items():
             t: torch.Tensor = where[names[path]].get_tensor(names[path])  # type: ignore[attr-defined]
-            out[path] = t.to(device=device, dtype=held_dtype(spec.role, t.dtype, compute_dtype)).contiguous()
+            out[path] = t.to(device=device, dtype=held_dtype(spec.role, t.dtype, compute_dtype, cast_float32)).contiguous()
             wide += spec.role != "vector" and t.dim() >= 2 and out[path].dtype == torch.float32 and compute_dtype != torch.float32
         if wide:  # right, but not what somebody who asked for bfloat16 may expect of the speed
             print(f"[prefixserve_b200] {wide} matrices of {folder} are stored in 32-bit and stay so: their products run on the "
-                  f"float32 kernel, not on the tensor cores", file=sys.stderr, flush=True)
+                  f"float32 kernel, not on the tensor cores (cast_float32_weights / --cast-float32-weights rounds them at "
+                  f"load instead)", file=sys.stderr, flush=True)
         return out
 
 

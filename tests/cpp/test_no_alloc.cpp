@@ -8,6 +8,7 @@
 
 #include "block_manager.hpp"
 #include "radix_tree.hpp"
+#include "seq_tables.hpp"
 
 static long g_allocations = 0;
 static bool g_counting = false;
@@ -77,6 +78,28 @@ int main() {
     (void)pool.drop(pages[0]);
     for (int i = 0; i < blocks; ++i) (void)pool.drop(pages[i]);
     if (round % 7 == 0) tree.evict(3);
+  }
+  g_counting = false;
+  CHECK(g_allocations == 0);
+
+  // the slot pool, the page table rows, the slot records and their logs of changed words
+  SlotPool slots(8);
+  SeqTables tables(8, 32);
+  SlotRecords records(8);
+  std::vector<int32_t> pairs(2 * (8 * 32 + 8 * SlotRecords::kWords));
+  PageId given[32];
+  g_counting = true;
+  for (int round = 0; round < 2000; ++round) {
+    rng = rng * 1664525u + 1013904223u;
+    const int32_t s = slots.take();
+    if (s < 0) return 3;
+    records.set_sampling(s, (float)(rng % 7) * 0.25f, rng);
+    const PageId ids[3] = {(PageId)(rng % 64), (PageId)((rng >> 8) % 64), (PageId)((rng >> 16) % 64)};
+    for (int k = 0; k < 1 + (int)(rng % 9); ++k) (void)tables.append(s, ids, 3);
+    (void)tables.release_front(s, (int32_t)(rng % 5), given);
+    if (round % 3 == 0) { (void)tables.drain(0, pairs.data()); (void)records.drain(0, pairs.data()); }
+    (void)tables.clear(s, given);
+    (void)slots.give_back(s);
   }
   g_counting = false;
   CHECK(g_allocations == 0);

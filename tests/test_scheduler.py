@@ -380,3 +380,74 @@ def test_abort_while_two_steps_are_out():
     assert res.new_tokens == {"y": 4} and not res.finished
     s.cache.check()
     assert s.stats().num_running == 1
+
+
+# ---- later additions -------------------------------------------------------------------------------------------------
+
+def test_a_request_may_bring_stop_ids_of_its_own():
+    from prefixserve_b200 import SamplingParams
+    s = Scheduler(64, chunk_size=512, stop_token_ids=[1003])
+    s.add_request("own", prompt(5), 10, sampling=SamplingParams(max_tokens=10, stop_token_ids=(1001,)))
+    s.add_request("model", prompt(5, 50), 10)
+    s.add_request("deaf", prompt(5, 90), 6, ignore_eos=True, sampling=SamplingParams(max_tokens=6, stop_token_ids=(1001,)))
+    out, _ = drive(s)
+    assert out["own"] == [1000, 1001]                 # its own id ends it, the id itself is kept
+    assert out["model"] == [1000, 1001, 1002, 1003]   # the model's id still applies to the others
+    assert len(out["deaf"]) == 6
+
+
+def test_a_windowed_pool_too_small_for_one_portion_is_refused_at_the_door():
+    """A group with a window holds the window, the portion being computed and one page of slack; a request that could
+    never hold that is refused when it is added instead of being preempted by itself for ever."""
+    from prefixserve_b200.cache import CacheManager
+    from prefixserve_b200.parts import CacheNeed, PagedKV
+    needs = [CacheNeed(PagedKV(1, 8)), CacheNeed(PagedKV(1, 8, window=20))]
+    small = CacheManager(needs, num_pages={0: 64, 1: 3}, num_slots=4, max_seq_len=512)
+    s = Scheduler(small, chunk_size=32)   # window 20 + portion 32 = 52 tokens = 4 pages, + 1 of slack
+    assert s.add_request("long", prompt(200), 20) is AddResult.TOO_LONG
+    assert s.add_request("short", prompt(30), 10) is AddResult.ACCEPTED   # 40 tokens never need more than 3 pages
+    enough = CacheManager(needs, num_pages={0: 64, 1: 5}, num_slots=4, max_seq_len=512)
+    s = Scheduler(enough, chunk_size=32)
+    assert s.add_request("long", prompt(200), 20, ignore_eos=True) is AddResult.ACCEPTED
+    out, _ = drive(s)
+    assert len(out["long"]) == 20 and s.stats().preemptions == 0
+
+
+def test_a_failed_step_leaves_nothing_behind():
+    """The entry point's loop with an engine that fails once: the call raises, every request of the call is gone,
+    slots and pages are back, and the next call works."""
+    from prefixserve_b200 import SamplingParams
+    from prefixserve_b200.engine.llm import LLM
+
+    class Pending:
+        def __init__(self, batch):
+            self.batch = batch
+
+    class FlakyEngine:
+        def __init__(self):
+            self.fail_at, self.launched = 3, 0
+
+        def launch(self, batch, feed=None):
+            self.launched += 1
+            if self.launched == self.fail_at:
+                raise RuntimeError("device fault")
+            return Pending(batch)
+
+        def finish(self, pending):
+            return {w.req.req_id: 7 for w in pending.batch.work if w.samples}
+
+        def check_device_status(self):
+            pass
+
+    llm = LLM.__new__(LLM)
+    llm.engine = FlakyEngine()
+    llm.scheduler = Scheduler(host_only_cache(32, num_slots=4), chunk_size=16)
+    llm.max_running_requests, llm.chunked_prefill_size, llm._counter = 4, 16, 0
+    params = SamplingParams(max_tokens=5, ignore_eos=True)
+    with pytest.raises(RuntimeError, match="device fault"):
+        llm.generate([list(range(20)), list(range(40, 50))], params)
+    s = llm.scheduler
+    assert not s.has_work() and s._inflight is None and s._ahead is None
+    s.cache.check()
+    assert s.cache.slots.num_free == 4 and s.cache.free_pages(0) + s.cache.cached_pages() == 32
+    assert llm.generate([list(range(20))], params) == [[7] * 5]   # the next call starts clean

@@ -118,3 +118,32 @@ def test_no_weights_at_all(tmp_path):
     (folder / "model.safetensors").unlink()
     with pytest.raises(WeightLoadError, match="neither"):
         load(folder)
+
+
+def test_float32_checkpoint_can_be_rounded_at_load_as_the_reference_does(tmp_path):
+    """prefixserve/model/weights.py:94-98 casts every tensor to the engine's type; here that is an option."""
+    folder = helpers.make_folder(tmp_path, "A", dtype=torch.float32)
+    arch, cfg = read_model_folder(folder)
+    model = build_model(arch.to_spec(cfg))
+    tensors = load_tensors(folder, model.param_table(), arch.tensor_name, lambda n: arch.ignorable(cfg, n),
+                           compute_dtype=torch.bfloat16, device="cpu", cast_float32=True)
+    assert tensors["embedding.weight"].dtype == torch.bfloat16
+    assert tensors["layers.0.mixer.q_proj"].dtype == torch.bfloat16
+    assert tensors["layers.0.mixer_norm.weight"].dtype == torch.float32   # gains stay wide either way
+    assert held_dtype("matrix", torch.float32, torch.bfloat16, cast_float32=True) == torch.bfloat16
+    assert held_dtype("matrix", torch.float32, torch.float32, cast_float32=True) == torch.float32
+
+
+@pytest.mark.parametrize("which,tied", [("A", True), ("B", False)])
+def test_weight_bytes_count_a_tied_head_once(tmp_path, which, tied):
+    """prefixserve/model/weights.py:49-59: the footprint of the loaded weights, shared tensors once."""
+    folder = helpers.make_folder(tmp_path, which, dtype=torch.bfloat16)
+    tensors, model = load(folder)
+    model.load(tensors, compute_dtype=torch.bfloat16, device=torch.device("cpu"), max_positions=64)
+    cfg = helpers.TINY[which]["cfg"]
+    q, kv = cfg.num_heads * cfg.head_dim, cfg.num_kv_heads * cfg.head_dim
+    matrices = cfg.vocab_size * cfg.hidden_size * (1 if tied else 2) + cfg.num_layers * (
+        (q + 2 * kv) * cfg.hidden_size + cfg.hidden_size * q + 3 * cfg.hidden_size * cfg.intermediate_size)
+    gains = (2 * cfg.num_layers + 1) * cfg.hidden_size
+    assert model.num_bytes() == 2 * matrices + 4 * gains   # bfloat16 matrices, float32 gains
+    assert (model.head.weight.data_ptr() == model.embedding.table.data_ptr()) == tied
