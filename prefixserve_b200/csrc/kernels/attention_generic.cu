@@ -71,13 +71,16 @@ attention_generic_kernel(const T* __restrict__ q, const TKV* __restrict__ kv, co
     const float m_new = fmaxf(m, run_max);
     const float alpha = expf(m - m_new);   // first run: exp(-huge) = 0
     const float pr = live ? expf(s - m_new) : 0.f;
+    // what multiplies the values is rounded to the storage type first (nothing happens in float32), as the reference
+    // rounds its probabilities (prefixserve/model/attention.py:119) and as the tensor-core kernels do; the sum is not
+    const float pv = to_float<T>(from_float<T>(pr));
     l = l * alpha + warp_sum(pr);
     m = m_new;
 #pragma unroll
     for (int i = 0; i < MAX_D / 32; ++i) acc[i] *= alpha;
     const int n_live = min(32, p - base + 1);
     for (int j = 0; j < n_live; ++j) {
-      const float pj = __shfl_sync(0xffffffffu, pr, j);
+      const float pj = __shfl_sync(0xffffffffu, pv, j);
       const long long oj = __shfl_sync(0xffffffffu, off, j);
       if (oj < 0) continue;  // before the window
       const TKV* vrow = kv + oj + v_off;

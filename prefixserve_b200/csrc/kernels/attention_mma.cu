@@ -701,7 +701,8 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
   if (!mine) return;
   const int p = kvl - 1;
   const int lo_key = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
-  const int splits = (kvl - (lo_key & ~15) + chunk - 1) / chunk;
+  // never more ranges than the launch provided scratch for (the host sizes them from the longest span it expects)
+  const int splits = min((kvl - (lo_key & ~15) + chunk - 1) / chunk, max_splits);
   const size_t base = ((size_t)item * hq + head) * max_splits;
   // The first eight ranges' partial outputs are asked for together with the maxima: where they lie does not depend on
   // the weights, and this kernel is nothing but the latency of its loads.
@@ -765,12 +766,12 @@ PSB_API int psb_attention_prefill_bf16(const void* q, const void* kv, const void
   dim3 grid(num_tiles, hkv);
 #define PSB_PREFILL(DD, MT)                                                                                          \
   do {                                                                                                               \
-    static bool configured = false; /* more than 48 KB of dynamic shared memory has to be asked for once */           \
-    if (!configured) {                                                                                               \
+    static PsbPerDevice configured;  /* more than 48 KB of dynamic shared memory has to be asked for once */           \
+    if (!configured.get()) {                                                                                               \
       cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<DD, MT>,                                         \
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, PrefillShape<DD>::SMEM_BYTES); \
       if (e != cudaSuccess) PSB_REFUSE("attention_prefill: cannot reserve shared memory: %s", cudaGetErrorString(e)); \
-      configured = true;                                                                                             \
+      configured.set();                                                                                              \
     }                                                                                                                \
     psb_launch(attention_prefill_kernel<DD, MT>, grid, dim3(WARPS * 32), (size_t)PrefillShape<DD>::SMEM_BYTES, stream, \
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)kv, (const int32_t*)table, table_width,                       \
@@ -803,12 +804,12 @@ PSB_API int psb_attention_decode_bf16(const void* q, const void* kv, const void*
   dim3 grid(max_splits, hkv, num_items);
 #define PSB_DECODE(DD)                                                                                               \
   do {                                                                                                               \
-    static bool configured = false; /* more than 48 KB of dynamic shared memory has to be asked for once */           \
-    if (!configured) {                                                                                               \
+    static PsbPerDevice configured;  /* more than 48 KB of dynamic shared memory has to be asked for once */           \
+    if (!configured.get()) {                                                                                               \
       cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<DD>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                            DecodeShape<DD>::SMEM_BYTES);                                             \
       if (e != cudaSuccess) PSB_REFUSE("attention_decode: cannot reserve shared memory: %s", cudaGetErrorString(e)); \
-      configured = true;                                                                                             \
+      configured.set();                                                                                              \
     }                                                                                                                \
     psb_launch(attention_decode_kernel<DD>, grid, dim3(WARPS * 32), (size_t)DecodeShape<DD>::SMEM_BYTES, stream, \
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)kv, (const int32_t*)table, table_width, (const int32_t*)item_start, \

@@ -495,11 +495,11 @@ template <int D>
 int launch(const CUtensorMap& map_q, const CUtensorMap& map_kv, const void* table, int table_width, const void* item_start,
            const void* kv_len, void* out, int num_items, int num_pairs, int hq, int hkv, int page_shift, int window,
            float scale, int skip_single, cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
+  static PsbPerDevice configured; 
+  if (!configured.get()) {
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<D>());
     if (e != cudaSuccess) PSB_REFUSE("attention_prefill_tcgen05: cannot reserve %d bytes of shared memory: %s", smem_bytes<D>(), cudaGetErrorString(e));
-    configured = true;
+    configured.set(); 
   }
   psb_launch(attention_prefill_tcgen05_kernel<D>, dim3(hq, num_pairs), dim3(THREADS), (size_t)smem_bytes<D>(), stream, map_q, map_kv,
              (const int32_t*)table, table_width, (const int32_t*)item_start, (const int32_t*)kv_len, (__nv_bfloat16*)out,

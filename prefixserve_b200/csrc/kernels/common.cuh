@@ -61,6 +61,26 @@ inline cudaError_t psb_launch(Kernel kernel, dim3 grid, dim3 block, size_t smem,
   return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
+// A function attribute (more than 48 KB of dynamic shared memory) has to be set once on every device that runs the
+// kernel.  One of these per call site: get() is false until set() has been called with the same device current.
+struct PsbPerDevice {
+  static constexpr int kMaxDevices = 64;
+  bool done[kMaxDevices] = {};
+  static int current() {
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= kMaxDevices) return -1;
+    return d;
+  }
+  bool get() const {
+    const int d = current();
+    return d >= 0 && done[d];
+  }
+  void set() {
+    const int d = current();
+    if (d >= 0) done[d] = true;
+  }
+};
+
 // (x1, x2) turned by the angle whose cosine and sine are given.  Written with explicit roundings, so that every
 // kernel that rotates (the rotary kernels, the projection that rotates in its epilogue) rounds alike whatever the
 // compiler would make of the plain expression around it.

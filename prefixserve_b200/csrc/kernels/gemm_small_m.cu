@@ -375,12 +375,12 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 template <int MT, int TILES, typename TOut>
 int launch_stream(const void* x, const void* W, void* y, int M, int N, int K, int ldy, int up_offset, int sms, cudaStream_t stream) {
   using Shape = StreamShape<MT, TILES>;
-  static bool configured = false;
-  if (!configured) {
+  static PsbPerDevice configured; 
+  if (!configured.get()) {
     cudaError_t e = cudaFuncSetAttribute(gemm_stream_kernel<MT, TILES, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Shape::SMEM_BYTES);
     if (e != cudaSuccess) PSB_REFUSE("gemm_stream: cannot reserve %d bytes of shared memory: %s", Shape::SMEM_BYTES, cudaGetErrorString(e));
-    configured = true;
+    configured.set(); 
   }
   const int tiles = (N + 15) / 16;
   const int grid = tiles < sms ? tiles : sms;
@@ -708,12 +708,12 @@ int launch_norm_stream(const void* h_in, const void* pending, const void* gain, 
                        void* y, int M, int N, int K, int ldy, int up_offset, float eps, int sms, cudaStream_t stream,
                        const RopeArgs& rope = RopeArgs{}) {
   using Shape = NormStreamShape<MT, TILES>;
-  static bool configured = false;
-  if (!configured) {
+  static PsbPerDevice configured; 
+  if (!configured.get()) {
     cudaError_t e = cudaFuncSetAttribute(gemm_stream_norm_kernel<MT, TILES, CPW, TOut, ROPE>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Shape::SMEM_BYTES);
     if (e != cudaSuccess) PSB_REFUSE("gemm_stream_norm: cannot reserve %d bytes of shared memory: %s", Shape::SMEM_BYTES, cudaGetErrorString(e));
-    configured = true;
+    configured.set(); 
   }
   const int tiles = (N + 15) / 16;
   const int grid = tiles < sms ? tiles : sms;

@@ -377,12 +377,12 @@ int launch(const void* a, const void* w, void* c, int M, int w_rows, int N_out, 
   const int grid = tiles < sms ? tiles : sms;
 #define PSB_TCGEN05(BN, HB)                                                                                          \
   do {                                                                                                               \
-    static bool configured = false; /* more than 48 KB of dynamic shared memory has to be asked for once */           \
-    if (!configured) {                                                                                               \
+    static PsbPerDevice configured;  /* more than 48 KB of dynamic shared memory has to be asked for once */           \
+    if (!configured.get()) {                                                                                               \
       cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, HB>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                            Tile<BN>::SMEM_BYTES);                                                    \
       if (e != cudaSuccess) PSB_REFUSE("gemm_tcgen05: cannot reserve %d bytes of shared memory: %s", Tile<BN>::SMEM_BYTES, cudaGetErrorString(e)); \
-      configured = true;                                                                                             \
+      configured.set();                                                                                              \
     }                                                                                                                \
     psb_launch(gemm_tcgen05_kernel<BN, HB>, dim3(grid), dim3(THREADS), (size_t)Tile<BN>::SMEM_BYTES, stream, map_a,   \
                map_w, (__nv_bfloat16*)c, M, N_out, K, N_out, up_offset, mode, rope);                                 \

@@ -248,7 +248,11 @@ def _attention_plan(new_tokens: Sequence[int], kv_lens: Sequence[int], window: i
         singles = [static_kv_len] * b
     plan = {"b": b, "use_decode": bool(singles) and group <= 16}
     if plan["use_decode"]:
-        if window:  # keys a decode item reads, from the 16-aligned start of its window
+        if window and static_kv_len is not None:
+            # a captured step serves every length up to static_kv_len: the span from the 16-aligned start of the
+            # window to the newest key depends on (length - window) mod 16 and reaches window + 15
+            longest = min(static_kv_len, window + 15)
+        elif window:  # keys a decode item reads, from the 16-aligned start of its window
             longest = max(kvl - (max(0, kvl - window) // 16) * 16 for kvl in singles)
         else:
             longest = max(singles)

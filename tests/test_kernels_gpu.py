@@ -390,6 +390,43 @@ def test_attention_tensor_cores_find_one_far_key():
         assert torch.allclose(out.float().cpu(), want[old:], atol=3e-2, rtol=3e-2), (old, new)
 
 
+@pytest.mark.parametrize("static_len,window", [(256, 50), (1024, 114), (512, 16), (4096, 300), (300, 290)])
+def test_windowed_decode_with_the_launch_shapes_of_a_captured_step(static_len, window):
+    """A captured decode step is launched with key ranges sized from the engine's longest sequence, not from the
+    step's own lengths.  With a window, the keys an item reads start at the 16-aligned beginning of the window, so
+    their number depends on (length - window) mod 16 and reaches window + 15: the ranges must cover that for every
+    length.  The newest key dominates every query here and the oldest key of the window comes second, so a range
+    that stops short, or a merge that reads another item's partial results, gives another answer."""
+    from prefixserve_b200.ops import tensorcore
+    hq, hkv, d, page = 4, 2, 64, 16
+    lengths = [k for k in range(max(1, window - 20), min(static_len, window + 70) + 1)]
+    g = torch.Generator().manual_seed(1)
+    longest = max(lengths)
+    k = torch.randn(longest, hkv, d, generator=g) * 0.1
+    v = torch.randn(longest, hkv, d, generator=g)
+    pages = -(-longest // page)
+    table = torch.randperm(pages + 5, generator=g)[:pages].to(torch.int32)[None, :]
+    bf = lambda x: x.to(torch.bfloat16).float()  # noqa: E731
+    for kvl in lengths:
+        pos = kvl - 1
+        q = torch.randn(1, hq, d, generator=g) * 0.1
+        kk = k[:kvl].clone()
+        q[0, :, pos % d] = 30.0
+        kk[pos, :, pos % d] += 30.0                          # the newest key
+        kk[max(0, pos - window + 1), :, pos % d] += 29.0     # the oldest key still inside the window
+        if pos - window >= 0:
+            kk[pos - window, :, pos % d] += 40.0             # just outside: must not be seen
+        kv = _fill_pages([dict(k=kk, v=v[:kvl])], table, [kvl], hkv, d, page, pages + 5)
+        batch = _Batch([kvl - 1], [1])
+        out = tensorcore.attention_bf16(q.to(torch.bfloat16).to(DEV), kv, table.to(DEV), batch.item_start, batch.kv_len,
+                                        [1], [kvl], window=window, scale=1.0 / math.sqrt(d), static_kv_len=static_len)
+        scores = torch.einsum("hd,khd->hk", bf(q[0]), bf(kk).repeat_interleave(hq // hkv, dim=1)) / math.sqrt(d)
+        scores[:, : max(0, pos - window + 1)] = float("-inf")
+        want = torch.einsum("hk,khd->hd", torch.softmax(scores, -1), bf(v[:kvl]).repeat_interleave(hq // hkv, dim=1))
+        got = out.float().cpu().view(hq, d)
+        assert torch.allclose(got, want, atol=3e-2, rtol=3e-2), (kvl, float((got - want).abs().max()))
+
+
 @pytest.mark.parametrize("hq,hkv,d,page", [(8, 2, 64, 16), (4, 4, 64, 64), (6, 2, 128, 16), (3, 1, 128, 32), (2, 1, 64, 128)])
 @pytest.mark.parametrize("window", [None, 100, 300])
 def test_attention_prefill_tcgen05(hq, hkv, d, page, window, monkeypatch):

@@ -223,6 +223,33 @@ def test_run_list_with_shared_weights_shared_cache_and_a_window(dtype):
     assert cache.free_pages(0) == 64 and cache.free_pages(1) == 64
 
 
+@pytest.mark.parametrize("window", [50, 114, 16, 33])
+def test_windowed_heads_of_64_decoded_through_captured_steps(window):
+    """A window on the tensor-core decode kernel, token by token through a captured and replayed step: the keys an
+    item reads run from the 16-aligned start of its window, so their number depends on (length - window) mod 16 and
+    the captured launch must have room for the longest such span.  The sweep covers every residue (the kernel alone,
+    with keys that make a short range show, is in the kernel tests)."""
+    from prefixserve_b200.config import LayerCall
+    from prefixserve_b200.ops import library
+    h, hq, hkv, d = 128, 4, 2, 64
+    spec = toy_model_spec([layer_of(attn_spec(h, hq, hkv, d, window=window), h=h, inter=96)], [LayerCall(0, 0)], h=h)
+    model, raw, cache, runner = build(spec, torch.bfloat16, std=0.3)
+    mixers = {0: lambda x, w, p, kv: plain_attention_layer(x, w, p, hq, hkv, d, window)}
+    tokens = helpers.random_tokens(97, window + 70, seed=8)
+    w16 = {k: v.to(torch.bfloat16).float() for k, v in raw.items()}   # the values the engine holds
+    want = plain_forward(spec, w16, tokens, mixers)
+    before = library.launch_counts["attention_decode"]
+    got = run_cut(runner, cache, tokens, [1] * len(tokens))
+    assert runner.graph_replays >= len(tokens) - 2 and library.launch_counts["attention_decode"] - before >= len(tokens) - 1
+    assert helpers.rel_err(got, want) < 0.05
+    # the same token by token without captured steps (launch shapes from each step's own lengths): the same to rounding
+    model2, _, cache2, runner2 = build(spec, torch.bfloat16, std=0.3)
+    runner2.use_graphs = False
+    eager = run_cut(runner2, cache2, tokens, [1] * len(tokens))
+    assert runner2.graph_replays == 0
+    assert float((got - eager).abs().max()) <= 2e-2 * float(want.abs().max())
+
+
 # ---- a toy mixer with a state of its own, defined here ---------------------------------------------------
 
 DECAY = 0.6
