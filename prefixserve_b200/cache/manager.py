@@ -141,8 +141,18 @@ class CacheManager:
     @staticmethod
     def bytes_per_page(needs: Sequence[CacheNeed], page_size: int, dtype: torch.dtype) -> int:
         """Bytes one page id costs over all entries (all groups counted as one, for sizing a single-group model)."""
+        return sum(CacheManager.group_page_bytes(needs, page_size, dtype).values())
+
+    @staticmethod
+    def group_page_bytes(needs: Sequence[CacheNeed], page_size: int, dtype: torch.dtype) -> dict[int | None, int]:
+        """window (None: all keys) -> bytes one page id of that group costs over the group's entries, in the order
+        in which the groups are numbered (first appearance among the entries)."""
         item = torch.empty((), dtype=dtype).element_size()
-        return sum(2 * n.paged.num_kv_heads * page_size * n.paged.head_dim * item for n in needs if n.paged is not None)
+        out: dict[int | None, int] = {}
+        for n in needs:
+            if n.paged is not None:
+                out[n.paged.window] = out.get(n.paged.window, 0) + 2 * n.paged.num_kv_heads * page_size * n.paged.head_dim * item
+        return out
 
     def num_pages(self, group: int = 0) -> int:
         return self.groups[group].pool.num_blocks

@@ -46,13 +46,19 @@ def part(kind: str, **params: Any) -> PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One block: norm -> mixer -> residual, norm -> feed-forward -> residual."""
+    """One block: a mixer, a feed-forward and their norms, put together by the named arrangement
+    (``parts.block``: "pre_norm", "parallel", or one registered there).  ``ffn`` and ``ffn_norm`` may be None: a
+    layer that only mixes."""
 
     mixer: PartSpec
-    ffn: PartSpec
+    ffn: PartSpec | None
     mixer_norm: PartSpec
-    ffn_norm: PartSpec
+    ffn_norm: PartSpec | None
     arrangement: str = "pre_norm"
+
+    def __post_init__(self) -> None:
+        if (self.ffn is None) != (self.ffn_norm is None):
+            raise ValueError("a layer has a feed-forward and its norm, or neither")
 
 
 @dataclass(frozen=True)

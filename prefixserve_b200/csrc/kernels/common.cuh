@@ -105,6 +105,16 @@ struct RopeArgs {
   int table_width, hq, hkv, D, page_shift, num_pages, max_positions;
 };
 
+// The activation of a gated feed-forward, act(gate) * up, by code: SiLU (prefixserve/model/llama.py:121 of
+// PrefixServe, the only one that architecture uses) and the tanh form of GELU.  Every kernel that applies the
+// activation takes the code; entry points refuse codes that are not listed here.
+enum PsbAct : int { PSB_ACT_SILU = 0, PSB_ACT_GELU_TANH = 1 };
+inline bool psb_activation_known(int code) { return code == PSB_ACT_SILU || code == PSB_ACT_GELU_TANH; }
+__device__ __forceinline__ float gate_act(float g, int act) {
+  if (act == PSB_ACT_GELU_TANH) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+  return g / (1.f + expf(-g));
+}
+
 template <typename T>
 __device__ __forceinline__ float to_float(T v);
 template <>

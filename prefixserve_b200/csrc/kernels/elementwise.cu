@@ -64,7 +64,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
   }
 }
 
-template <typename T>
+template <typename T, int ACT>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
   pdl_trigger();
   pdl_wait();
@@ -74,11 +74,11 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
   const int j = (int)(idx - t * (size_t)I);
   const float g = to_float<T>(gu[t * 2 * (size_t)I + j]);
   const float u = to_float<T>(gu[t * 2 * (size_t)I + I + j]);
-  const float s = g / (1.f + expf(-g));
-  out[idx] = from_float<T>(s * u);
+  out[idx] = from_float<T>(gate_act(g, ACT) * u);
 }
 
 // Eight elements per thread (16-byte loads and stores).  Needs I % 8 == 0 and bfloat16.
+template <int ACT>
 __global__ void silu_mul_vec_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int I, size_t vecs) {
   pdl_trigger();
   pdl_wait();
@@ -95,7 +95,7 @@ __global__ void silu_mul_vec_kernel(const __nv_bfloat16* __restrict__ gu, __nv_b
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
-      o2[k] = __floats2bfloat162_rn(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y);
+      o2[k] = __floats2bfloat162_rn(gate_act(g.x, ACT) * u.x, gate_act(g.y, ACT) * u.y);
     }
     *reinterpret_cast<uint4*>(out + t * (size_t)I + j) = o4;
   }
@@ -227,24 +227,54 @@ PSB_API int psb_add_rmsnorm(void* h, const void* delta, int delta_dtype, const v
   return 0;
 }
 
-PSB_API int psb_silu_mul(const void* gate_up, int dtype, void* out, int T, int I, cudaStream_t stream) {
-  if (T < 0 || I < 1) PSB_REFUSE("silu_mul: bad sizes T=%d I=%d", T, I);
-  if (T == 0) return 0;
+// out[T, I] = f(gate_up[:, :I]) * gate_up[:, I:], f the activation named by its code (PsbAct), a template parameter
+// of the kernels.
+template <int ACT>
+static int launch_act_mul(const void* gate_up, int dtype, void* out, int T, int I, cudaStream_t stream) {
   if (dtype == PSB_BF16 && I % 8 == 0) {
     const size_t vecs = (size_t)T * (I / 8);
     const size_t want = (vecs + 255) / 256;
     const unsigned blocks = (unsigned)(want < 148 * 16 ? want : 148 * 16);
-    psb_launch(silu_mul_vec_kernel, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, I, vecs);
-    PSB_LAUNCH_CHECK("silu_mul");
+    psb_launch(silu_mul_vec_kernel<ACT>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, I, vecs);
+    PSB_LAUNCH_CHECK("act_mul");
     return 0;
   }
   const size_t total = (size_t)T * I;
   const int threads = 256;
   const size_t blocks = (total + threads - 1) / threads;
-  if (blocks > 0x7fffffffull) PSB_REFUSE("silu_mul: too many elements");
+  if (blocks > 0x7fffffffull) PSB_REFUSE("act_mul: too many elements");
   PSB_DISPATCH_DTYPE(dtype, T_, {
-    psb_launch(silu_mul_kernel<T_>, dim3((unsigned)blocks), dim3(threads), 0, stream, (const T_*)gate_up, (T_*)out, I, total);
+    psb_launch(silu_mul_kernel<T_, ACT>, dim3((unsigned)blocks), dim3(threads), 0, stream, (const T_*)gate_up, (T_*)out, I, total);
   });
-  PSB_LAUNCH_CHECK("silu_mul");
+  PSB_LAUNCH_CHECK("act_mul");
+  return 0;
+}
+
+PSB_API int psb_silu_mul(const void* gate_up, int dtype, void* out, int T, int I, int activation, cudaStream_t stream) {
+  if (T < 0 || I < 1) PSB_REFUSE("act_mul: bad sizes T=%d I=%d", T, I);
+  if (T == 0) return 0;
+  if (activation == PSB_ACT_SILU) return launch_act_mul<PSB_ACT_SILU>(gate_up, dtype, out, T, I, stream);
+  if (activation == PSB_ACT_GELU_TANH) return launch_act_mul<PSB_ACT_GELU_TANH>(gate_up, dtype, out, T, I, stream);
+  PSB_REFUSE("act_mul: activation code %d is not built", activation);
+}
+
+// h[T, H] (float32) += delta[T, H]: the residual sum on its own, for block arrangements in which no norm follows it.
+template <typename TD>
+__global__ void residual_add_kernel(float* __restrict__ h, const TD* __restrict__ delta, size_t total) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+    h[i] += to_float<TD>(delta[i]);
+}
+
+PSB_API int psb_residual_add(void* h, const void* delta, int delta_dtype, long long total, cudaStream_t stream) {
+  if (total < 0) PSB_REFUSE("residual_add: negative size");
+  if (total == 0) return 0;
+  const size_t want = ((size_t)total + 255) / 256;
+  const unsigned blocks = (unsigned)(want < 148 * 16 ? want : 148 * 16);
+  PSB_DISPATCH_DTYPE(delta_dtype, TD, {
+    psb_launch(residual_add_kernel<TD>, dim3(blocks), dim3(256), 0, stream, (float*)h, (const TD*)delta, (size_t)total);
+  });
+  PSB_LAUNCH_CHECK("residual_add");
   return 0;
 }

@@ -41,7 +41,7 @@ __device__ __forceinline__ uint4 ld_cached(const void* p) { return __ldg(reinter
 template <int MT, int U, int TILES, int GW, typename TOut>
 __global__ void __launch_bounds__(GW * 32)
 gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ W, TOut* __restrict__ y, int M, int N,
-                    int K, int ldy, int up_offset) {
+                    int K, int ldy, int up_offset, int act) {
   __shared__ float part[GW][TILES][16][8 * MT + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int row0 = blockIdx.x * 16;
@@ -131,7 +131,7 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
       // the reference rounds the projection to bfloat16 before the activation
       const float gate = __bfloat162float(__float2bfloat16_rn(v[0]));
       const float up = __bfloat162float(__float2bfloat16_rn(v[TILES - 1]));
-      out = gate / (1.f + expf(-gate)) * up;
+      out = gate_act(gate, act) * up;
     } else {
       out = v[0];
     }
@@ -140,27 +140,27 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
 }
 
 template <int MT, int U, int TILES, int GW, typename TOut>
-void launch(const void* x, const void* W, void* y, int M, int N, int K, int ldy, int up_offset, cudaStream_t stream) {
+void launch(const void* x, const void* W, void* y, int M, int N, int K, int ldy, int up_offset, int act, cudaStream_t stream) {
   const int tiles = (N + 15) / 16;
   psb_launch(gemm_small_m_kernel<MT, U, TILES, GW, TOut>, dim3(tiles), dim3(GW * 32), 0, stream, (const __nv_bfloat16*)x, (const __nv_bfloat16*)W,
-                                                                             (TOut*)y, M, N, K, ldy, up_offset);
+                                                                             (TOut*)y, M, N, K, ldy, up_offset, act);
 }
 
 // wide: 16 warps per CTA split K (few row tiles: more of the matrix in flight at once), else 8.
 template <int TILES, typename TOut>
-int dispatch_m(const void* x, const void* W, void* y, int M, int N, int K, int ldy, int up_offset, int wide,
+int dispatch_m(const void* x, const void* W, void* y, int M, int N, int K, int ldy, int up_offset, int act, int wide,
                cudaStream_t stream) {
   if (M <= 8) {
-    if (wide) launch<1, 4, TILES, 16, TOut>(x, W, y, M, N, K, ldy, up_offset, stream);
-    else launch<1, 4, TILES, 8, TOut>(x, W, y, M, N, K, ldy, up_offset, stream);
+    if (wide) launch<1, 4, TILES, 16, TOut>(x, W, y, M, N, K, ldy, up_offset, act, stream);
+    else launch<1, 4, TILES, 8, TOut>(x, W, y, M, N, K, ldy, up_offset, act, stream);
   } else if (M <= 16) {
-    if (wide) launch<2, 4, TILES, 16, TOut>(x, W, y, M, N, K, ldy, up_offset, stream);
-    else launch<2, 4, TILES, 8, TOut>(x, W, y, M, N, K, ldy, up_offset, stream);
-  } else if (M <= 32) launch<4, 2, TILES, 8, TOut>(x, W, y, M, N, K, ldy, up_offset, stream);
+    if (wide) launch<2, 4, TILES, 16, TOut>(x, W, y, M, N, K, ldy, up_offset, act, stream);
+    else launch<2, 4, TILES, 8, TOut>(x, W, y, M, N, K, ldy, up_offset, act, stream);
+  } else if (M <= 32) launch<4, 2, TILES, 8, TOut>(x, W, y, M, N, K, ldy, up_offset, act, stream);
   else if (M <= 64) {
     // the gated variant's two partial tiles per warp would not fit in shared memory at this width
     if (TILES == 2) PSB_REFUSE("gemm_small_m_gated: M=%d is beyond this kernel (at most 32 rows)", M);
-    launch<8, 2, 1, 8, TOut>(x, W, y, M, N, K, ldy, up_offset, stream);
+    launch<8, 2, 1, 8, TOut>(x, W, y, M, N, K, ldy, up_offset, act, stream);
   } else PSB_REFUSE("gemm_small_m: M=%d is beyond this kernel (at most 64 rows)", M);
   return 0;
 }
@@ -173,20 +173,21 @@ PSB_API int psb_gemm_small_m(const void* x, const void* W, void* y, int out_dtyp
   if (M < 0 || N < 1 || K < 32 || K % 32) PSB_REFUSE("gemm_small_m: needs K a positive multiple of 32 (M=%d N=%d K=%d)", M, N, K);
   if (M == 0) return 0;
   int rc;
-  if (out_dtype == PSB_F32) rc = dispatch_m<1, float>(x, W, y, M, N, K, N, 0, wide, stream);
-  else if (out_dtype == PSB_BF16) rc = dispatch_m<1, __nv_bfloat16>(x, W, y, M, N, K, N, 0, wide, stream);
+  if (out_dtype == PSB_F32) rc = dispatch_m<1, float>(x, W, y, M, N, K, N, 0, 0, wide, stream);
+  else if (out_dtype == PSB_BF16) rc = dispatch_m<1, __nv_bfloat16>(x, W, y, M, N, K, N, 0, 0, wide, stream);
   else PSB_REFUSE("gemm_small_m: unknown output dtype %d", out_dtype);
   if (rc) return rc;
   PSB_LAUNCH_CHECK("gemm_small_m");
   return 0;
 }
 
-// act[M,I] = silu(x W[0:I]^T) * (x W[I:2I]^T), W = [2I, K] (gate rows, then up rows), bfloat16 output.
-PSB_API int psb_gemm_small_m_gated(const void* x, const void* W, void* act, int M, int I, int K, int wide,
+// act[M,I] = f(x W[0:I]^T) * (x W[I:2I]^T), f the activation named by its code (PsbAct),, W = [2I, K] (gate rows, then up rows), bfloat16 output.
+PSB_API int psb_gemm_small_m_gated(const void* x, const void* W, void* act, int M, int I, int K, int wide, int activation,
                                    cudaStream_t stream) {
+  if (!psb_activation_known(activation)) PSB_REFUSE("gemm_small_m_gated: activation code %d is not built", activation);
   if (M < 0 || I < 1 || K < 32 || K % 32) PSB_REFUSE("gemm_small_m_gated: needs K a positive multiple of 32 (M=%d I=%d K=%d)", M, I, K);
   if (M == 0) return 0;
-  if (int rc = dispatch_m<2, __nv_bfloat16>(x, W, act, M, I, K, I, I, wide, stream)) return rc;
+  if (int rc = dispatch_m<2, __nv_bfloat16>(x, W, act, M, I, K, I, I, activation, wide, stream)) return rc;
   PSB_LAUNCH_CHECK("gemm_small_m_gated");
   return 0;
 }
@@ -227,7 +228,7 @@ __device__ __forceinline__ uint4 lds16(uint32_t addr) {
 template <int MT, int TILES, typename TOut>
 __global__ void __launch_bounds__(SW * 32, 1)
 gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ W, TOut* __restrict__ y, int M, int N,
-                   int K, int ldy, int up_offset) {
+                   int K, int ldy, int up_offset, int act) {
   using Shape = StreamShape<MT, TILES>;
   constexpr int STAGES = Shape::STAGES, PIECES = Shape::PIECES;
   constexpr uint32_t STAGE_BYTES = PIECES * 32 * 16;
@@ -362,7 +363,7 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
       if (TILES == 2) {
         const float gate = __bfloat162float(__float2bfloat16_rn(v[0]));
         const float up = __bfloat162float(__float2bfloat16_rn(v[TILES - 1]));
-        out = gate / (1.f + expf(-gate)) * up;
+        out = gate_act(gate, act) * up;
       } else {
         out = v[0];
       }
@@ -373,7 +374,7 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 }
 
 template <int MT, int TILES, typename TOut>
-int launch_stream(const void* x, const void* W, void* y, int M, int N, int K, int ldy, int up_offset, int sms, cudaStream_t stream) {
+int launch_stream(const void* x, const void* W, void* y, int M, int N, int K, int ldy, int up_offset, int act, int sms, cudaStream_t stream) {
   using Shape = StreamShape<MT, TILES>;
   static PsbPerDevice configured; 
   if (!configured.get()) {
@@ -385,7 +386,7 @@ int launch_stream(const void* x, const void* W, void* y, int M, int N, int K, in
   const int tiles = (N + 15) / 16;
   const int grid = tiles < sms ? tiles : sms;
   psb_launch(gemm_stream_kernel<MT, TILES, TOut>, dim3(grid), dim3(SW * 32), (size_t)Shape::SMEM_BYTES, stream,
-      (const __nv_bfloat16*)x, (const __nv_bfloat16*)W, (TOut*)y, M, N, K, ldy, up_offset);
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)W, (TOut*)y, M, N, K, ldy, up_offset, act);
   return 0;
 }
 
@@ -396,19 +397,21 @@ PSB_API int psb_gemm_stream(const void* x, const void* W, void* y, int out_dtype
   if (M < 0 || M > 16 || N < 1 || K < 32 || K % 32 || sms < 1) PSB_REFUSE("gemm_stream: needs M <= 16 and K a multiple of 32 (M=%d N=%d K=%d)", M, N, K);
   if (M == 0) return 0;
   int rc;
-  if (out_dtype == PSB_F32) rc = M <= 8 ? launch_stream<1, 1, float>(x, W, y, M, N, K, N, 0, sms, stream) : launch_stream<2, 1, float>(x, W, y, M, N, K, N, 0, sms, stream);
-  else if (out_dtype == PSB_BF16) rc = M <= 8 ? launch_stream<1, 1, __nv_bfloat16>(x, W, y, M, N, K, N, 0, sms, stream) : launch_stream<2, 1, __nv_bfloat16>(x, W, y, M, N, K, N, 0, sms, stream);
+  if (out_dtype == PSB_F32) rc = M <= 8 ? launch_stream<1, 1, float>(x, W, y, M, N, K, N, 0, 0, sms, stream) : launch_stream<2, 1, float>(x, W, y, M, N, K, N, 0, 0, sms, stream);
+  else if (out_dtype == PSB_BF16) rc = M <= 8 ? launch_stream<1, 1, __nv_bfloat16>(x, W, y, M, N, K, N, 0, 0, sms, stream) : launch_stream<2, 1, __nv_bfloat16>(x, W, y, M, N, K, N, 0, 0, sms, stream);
   else PSB_REFUSE("gemm_stream: unknown output dtype %d", out_dtype);
   if (rc) return rc;
   PSB_LAUNCH_CHECK("gemm_stream");
   return 0;
 }
 
-PSB_API int psb_gemm_stream_gated(const void* x, const void* W, void* act, int M, int I, int K, int sms, cudaStream_t stream) {
+PSB_API int psb_gemm_stream_gated(const void* x, const void* W, void* act, int M, int I, int K, int sms, int activation,
+                                  cudaStream_t stream) {
+  if (!psb_activation_known(activation)) PSB_REFUSE("gemm_stream_gated: activation code %d is not built", activation);
   if (M < 0 || M > 16 || I < 1 || K < 32 || K % 32 || sms < 1) PSB_REFUSE("gemm_stream_gated: needs M <= 16 and K a multiple of 32 (M=%d I=%d K=%d)", M, I, K);
   if (M == 0) return 0;
-  const int rc = M <= 8 ? launch_stream<1, 2, __nv_bfloat16>(x, W, act, M, I, K, I, I, sms, stream)
-                        : launch_stream<2, 2, __nv_bfloat16>(x, W, act, M, I, K, I, I, sms, stream);
+  const int rc = M <= 8 ? launch_stream<1, 2, __nv_bfloat16>(x, W, act, M, I, K, I, I, activation, sms, stream)
+                        : launch_stream<2, 2, __nv_bfloat16>(x, W, act, M, I, K, I, I, activation, sms, stream);
   if (rc) return rc;
   PSB_LAUNCH_CHECK("gemm_stream_gated");
   return 0;
@@ -460,7 +463,7 @@ template <int MT, int TILES, int CPW, typename TOut, bool ROPE = false>
 __global__ void __launch_bounds__(SW * 32, 1)
 gemm_stream_norm_kernel(const float* __restrict__ h_in, const __nv_bfloat16* __restrict__ pending, const float* __restrict__ gain,
                         const int32_t* __restrict__ rows, float* __restrict__ h_out, const __nv_bfloat16* __restrict__ W,
-                        TOut* __restrict__ y, int M, int N, int K, int ldy, int up_offset, float eps, RopeArgs rope) {
+                        TOut* __restrict__ y, int M, int N, int K, int ldy, int up_offset, int act, float eps, RopeArgs rope) {
   using Shape = NormStreamShape<MT, TILES>;
   constexpr int STAGES = Shape::STAGES, PIECES = Shape::PIECES;
   constexpr uint32_t STAGE_BYTES = PIECES * 32 * 16;
@@ -692,7 +695,7 @@ gemm_stream_norm_kernel(const float* __restrict__ h_in, const __nv_bfloat16* __r
       if (TILES == 2) {
         const float gate = __bfloat162float(__float2bfloat16_rn(v[0]));
         const float up = __bfloat162float(__float2bfloat16_rn(v[TILES - 1]));
-        out = gate / (1.f + expf(-gate)) * up;
+        out = gate_act(gate, act) * up;
       } else {
         out = v[0];
       }
@@ -705,7 +708,7 @@ gemm_stream_norm_kernel(const float* __restrict__ h_in, const __nv_bfloat16* __r
 
 template <int MT, int TILES, int CPW, typename TOut, bool ROPE = false>
 int launch_norm_stream(const void* h_in, const void* pending, const void* gain, const void* rows, void* h_out, const void* W,
-                       void* y, int M, int N, int K, int ldy, int up_offset, float eps, int sms, cudaStream_t stream,
+                       void* y, int M, int N, int K, int ldy, int up_offset, int act, float eps, int sms, cudaStream_t stream,
                        const RopeArgs& rope = RopeArgs{}) {
   using Shape = NormStreamShape<MT, TILES>;
   static PsbPerDevice configured; 
@@ -719,15 +722,15 @@ int launch_norm_stream(const void* h_in, const void* pending, const void* gain, 
   const int grid = tiles < sms ? tiles : sms;
   psb_launch(gemm_stream_norm_kernel<MT, TILES, CPW, TOut, ROPE>, dim3(grid), dim3(SW * 32), (size_t)Shape::SMEM_BYTES, stream,
              (const float*)h_in, (const __nv_bfloat16*)pending, (const float*)gain, (const int32_t*)rows, (float*)h_out,
-             (const __nv_bfloat16*)W, (TOut*)y, M, N, K, ldy, up_offset, eps, rope);
+             (const __nv_bfloat16*)W, (TOut*)y, M, N, K, ldy, up_offset, act, eps, rope);
   return 0;
 }
 
 template <int TILES, typename TOut>
 int dispatch_norm_stream(const void* h_in, const void* pending, const void* gain, const void* rows, void* h_out, const void* W,
-                         void* y, int M, int N, int K, int ldy, int up_offset, float eps, int sms, cudaStream_t stream) {
+                         void* y, int M, int N, int K, int ldy, int up_offset, int act, float eps, int sms, cudaStream_t stream) {
   const int cpw = (K / 32 + SW - 1) / SW;  // the most chunks any warp owns
-#define PSB_NS(MT, CPW) launch_norm_stream<MT, TILES, CPW, TOut>(h_in, pending, gain, rows, h_out, W, y, M, N, K, ldy, up_offset, eps, sms, stream)
+#define PSB_NS(MT, CPW) launch_norm_stream<MT, TILES, CPW, TOut>(h_in, pending, gain, rows, h_out, W, y, M, N, K, ldy, up_offset, act, eps, sms, stream)
   if (M <= 8) {
     if (cpw <= 4) return PSB_NS(1, 4);
     if (cpw <= 8) return PSB_NS(1, 8);
@@ -743,7 +746,7 @@ int dispatch_norm_stream(const void* h_in, const void* pending, const void* gain
 int dispatch_norm_stream_rope(const void* h_in, const void* pending, const void* gain, void* h_out, const void* W, int M, int N,
                               int K, float eps, int sms, cudaStream_t stream, const RopeArgs& rope) {
   const int cpw = (K / 32 + SW - 1) / SW;
-#define PSB_NSR(MT, CPW) launch_norm_stream<MT, 1, CPW, __nv_bfloat16, true>(h_in, pending, gain, nullptr, h_out, W, nullptr, M, N, K, N, 0, eps, sms, stream, rope)
+#define PSB_NSR(MT, CPW) launch_norm_stream<MT, 1, CPW, __nv_bfloat16, true>(h_in, pending, gain, nullptr, h_out, W, nullptr, M, N, K, N, 0, 0, eps, sms, stream, rope)
   if (M <= 8) {
     if (cpw <= 4) return PSB_NSR(1, 4);
     if (cpw <= 8) return PSB_NSR(1, 8);
@@ -773,20 +776,21 @@ PSB_API int psb_gemm_stream_norm(const void* h_in, const void* pending, const vo
   if (rows && h_out) PSB_REFUSE("gemm_stream_norm: the stream cannot be updated through a row selection");
   if (!(eps > 0.f)) PSB_REFUSE("gemm_stream_norm: eps must be positive");
   int rc;
-  if (out_dtype == PSB_F32) rc = dispatch_norm_stream<1, float>(h_in, pending, gain, rows, h_out, W, y, M, N, K, N, 0, eps, sms, stream);
-  else if (out_dtype == PSB_BF16) rc = dispatch_norm_stream<1, __nv_bfloat16>(h_in, pending, gain, rows, h_out, W, y, M, N, K, N, 0, eps, sms, stream);
+  if (out_dtype == PSB_F32) rc = dispatch_norm_stream<1, float>(h_in, pending, gain, rows, h_out, W, y, M, N, K, N, 0, 0, eps, sms, stream);
+  else if (out_dtype == PSB_BF16) rc = dispatch_norm_stream<1, __nv_bfloat16>(h_in, pending, gain, rows, h_out, W, y, M, N, K, N, 0, 0, eps, sms, stream);
   else PSB_REFUSE("gemm_stream_norm: unknown output dtype %d", out_dtype);
   if (rc) return rc;
   PSB_LAUNCH_CHECK("gemm_stream_norm");
   return 0;
 }
 
-// act[M,I] = silu(x Wg^T) * (x Wu^T) with x = rmsnorm(h_in + pending) as above, W = [Wg; Wu].
+// act[M,I] = f(x Wg^T) * (x Wu^T), f the activation named by its code, with x = rmsnorm(h_in + pending) as above, W = [Wg; Wu].
 PSB_API int psb_gemm_stream_norm_gated(const void* h_in, const void* pending, const void* gain, void* h_out, const void* W,
-                                       void* act, int M, int I, int K, float eps, int sms, cudaStream_t stream) {
+                                       void* act, int M, int I, int K, float eps, int sms, int activation, cudaStream_t stream) {
+  if (!psb_activation_known(activation)) PSB_REFUSE("gemm_stream_norm_gated: activation code %d is not built", activation);
   if (!psb_gemm_stream_norm_supported(M, K) || I < 1 || sms < 1) PSB_REFUSE("gemm_stream_norm_gated: shape M=%d I=%d K=%d is not taken", M, I, K);
   if (!(eps > 0.f)) PSB_REFUSE("gemm_stream_norm_gated: eps must be positive");
-  if (int rc = dispatch_norm_stream<2, __nv_bfloat16>(h_in, pending, gain, nullptr, h_out, W, act, M, I, K, I, I, eps, sms, stream)) return rc;
+  if (int rc = dispatch_norm_stream<2, __nv_bfloat16>(h_in, pending, gain, nullptr, h_out, W, act, M, I, K, I, I, activation, eps, sms, stream)) return rc;
   PSB_LAUNCH_CHECK("gemm_stream_norm_gated");
   return 0;
 }

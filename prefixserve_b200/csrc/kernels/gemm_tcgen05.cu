@@ -64,7 +64,7 @@ using namespace tc;
 // mode: 0 plain (C[M, N], tile columns [n0, n0+BN/2) and [n0+BN/2, n0+BN)); 1 gated (C[M, I], W = [gate; up], tile
 // columns [n0, n0+128) of the gate and the same of the up rows); 2 the projection of an attention layer (columns as in
 // 0; the epilogue rotates queries and keys and stores queries, keys and values where RopeArgs says, C is not used).
-enum : int { MODE_PLAIN = 0, MODE_GATED = 1, MODE_ROPE = 2 };
+enum : int { MODE_PLAIN = 0, MODE_GATED = 1, MODE_ROPE = 2, MODE_GATED_GELU = 3 };  // gated: SiLU, or the tanh form of GELU
 
 // One thread's row of a 128 x BN tile of sums, for the projection of an attention layer: 16 columns are 8 pairs of one
 // head (first-half elements, then the ones they are rotated with), so the job of the rotary kernel is done on the sums
@@ -151,7 +151,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   using T = Tile<BN>;
   constexpr int BN_HALF = T::HALF, STAGES = T::STAGES, STAGE_BYTES = T::STAGE_BYTES;
   constexpr uint32_t INSTR_DESC = instr_desc(BM, BN, false);  // M=128, N=BN, both operands K-major
-  const bool gated = mode == MODE_GATED;
+  const bool gated = mode == MODE_GATED || mode == MODE_GATED_GELU;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   Barriers* bars = reinterpret_cast<Barriers*>(tiles + STAGES * STAGE_BYTES);
@@ -292,7 +292,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const float g1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(g[j + 2 * q + 1])));
                 const float u0 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[j + 2 * q])));
                 const float u1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[j + 2 * q + 1])));
-                packed[q] = pack2(g0 / (1.f + __expf(-g0)) * u0, g1 / (1.f + __expf(-g1)) * u1);
+                packed[q] = mode == MODE_GATED ? pack2(g0 / (1.f + __expf(-g0)) * u0, g1 / (1.f + __expf(-g1)) * u1)
+                                               : pack2(gate_act(g0, PSB_ACT_GELU_TANH) * u0, gate_act(g1, PSB_ACT_GELU_TANH) * u1);
               }
               if (col + 8 <= N_out && (ldc & 7) == 0) {
                 *reinterpret_cast<uint4*>(crow + col) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
@@ -359,7 +360,7 @@ int g_forced_width = 0;  // 0: the launcher chooses the tile width; 192 or 256: 
 
 int launch(const void* a, const void* w, void* c, int M, int w_rows, int N_out, int K, int up_offset, int mode, int sms,
            cudaStream_t stream, const RopeArgs& rope = RopeArgs{}) {
-  const bool gated = mode == MODE_GATED;
+  const bool gated = mode == MODE_GATED || mode == MODE_GATED_GELU;
   if (M < 1 || N_out < 1 || K < 8 || K % 8) PSB_REFUSE("gemm_tcgen05: needs K a multiple of 8 (M=%d N=%d K=%d)", M, N_out, K);
   if (((uintptr_t)a | (uintptr_t)w | (uintptr_t)c) & 15) PSB_REFUSE("gemm_tcgen05: operands must be 16-byte aligned");
   // Tile width: 256 columns unless 192 get the product done in fewer or shorter rounds over the SMs (the gated form
@@ -405,9 +406,11 @@ PSB_API int psb_gemm_tcgen05(const void* a, const void* w, void* c, int M, int N
   return launch(a, w, c, M, N, N, K, 0, MODE_PLAIN, sms, stream);
 }
 
-// act[M,I] = silu(A Wg^T) * (A Wu^T) for W = [Wg; Wu] of shape [2I, K].
-PSB_API int psb_gemm_tcgen05_gated(const void* a, const void* w, void* act, int M, int I, int K, int sms, cudaStream_t stream) {
-  return launch(a, w, act, M, 2 * I, I, K, I, MODE_GATED, sms, stream);
+// act[M,I] = f(A Wg^T) * (A Wu^T) for W = [Wg; Wu] of shape [2I, K], f the activation named by its code (PsbAct).
+PSB_API int psb_gemm_tcgen05_gated(const void* a, const void* w, void* act, int M, int I, int K, int sms, int activation,
+                                   cudaStream_t stream) {
+  if (!psb_activation_known(activation)) PSB_REFUSE("gemm_tcgen05_gated: activation code %d is not built", activation);
+  return launch(a, w, act, M, 2 * I, I, K, I, activation == PSB_ACT_SILU ? MODE_GATED : MODE_GATED_GELU, sms, stream);
 }
 
 // The projection of an attention layer for many tokens: A W^T with W = [queries; keys; values] [(hq + 2 hkv) D, K] in the

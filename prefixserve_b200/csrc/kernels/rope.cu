@@ -20,6 +20,11 @@
 // (stored index 16b+j <-> natural index 8b+j, stored 16b+8+j <-> natural D/2+8b+j), and queries and keys leave in
 // that same order: scores do not depend on the order of a head's elements as long as both sides share it.  Values
 // are always in natural order.
+//
+// The general kernel also takes a rotation over the first ``rotary_dim`` elements of a head only (the rest pass
+// through; the tables then hold rotary_dim/2 angles per position) and the interleaved pairing, in which element 2j
+// turns with element 2j+1 instead of j with j + rotary_dim/2.  The vector kernel and the fused projections bake in
+// the split-half pairing over the whole head; the host sends every other description here.
 #include "common.cuh"
 
 namespace {
@@ -62,11 +67,12 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, const int32_t* __r
                                    const int32_t* __restrict__ token_item, const float* __restrict__ cos_t,
                                    const float* __restrict__ sin_t, const int32_t* __restrict__ table, int table_width,
                                    TKV* __restrict__ kv, T* __restrict__ q_out, int hq, int hkv, int D, int page_size,
-                                   int num_pages, int max_positions, int rotate, int write_kv) {
+                                   int num_pages, int max_positions, int rotate, int write_kv, int rotary_dim,
+                                   int interleaved) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
-  const int half = D >> 1;
+  const int half = rotary_dim >> 1;  // pairs per head; elements from rotary_dim on pass through
   const int pos = positions[t];
   const int heads_in = hq + 2 * hkv;
   const T* row = qkv + (size_t)t * heads_in * D;
@@ -90,8 +96,9 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, const int32_t* __r
   const int rot_heads = write_kv ? hq + hkv : hq;
   for (int idx = threadIdx.x; idx < rot_heads * half; idx += blockDim.x) {
     const int head = idx / half, j = idx - head * half;
-    const float x1 = to_float<T>(row[head * D + j]);
-    const float x2 = to_float<T>(row[head * D + j + half]);
+    const int e1 = interleaved ? 2 * j : j, e2 = interleaved ? 2 * j + 1 : j + half;  // the two elements of pair j
+    const float x1 = to_float<T>(row[head * D + e1]);
+    const float x2 = to_float<T>(row[head * D + e2]);
     float o1 = x1, o2 = x2;
     if (rotate) {
       const float cs = c[j], sn = s[j];
@@ -99,13 +106,20 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, const int32_t* __r
     }
     if (head < hq) {
       T* q = q_out + ((size_t)t * hq + head) * D;
-      q[j] = from_float<T>(o1);
-      q[j + half] = from_float<T>(o2);
+      q[e1] = from_float<T>(o1);
+      q[e2] = from_float<T>(o2);
     } else if (kdst) {
       TKV* k = kdst + (size_t)(head - hq) * page_size * D;
-      k[j] = from_float<TKV>(o1);
-      k[j + half] = from_float<TKV>(o2);
+      k[e1] = from_float<TKV>(o1);
+      k[e2] = from_float<TKV>(o2);
     }
+  }
+  const int rest = D - rotary_dim;
+  for (int idx = threadIdx.x; idx < rot_heads * rest; idx += blockDim.x) {
+    const int head = idx / rest, e = rotary_dim + (idx - head * rest);
+    const T x = row[head * D + e];
+    if (head < hq) q_out[((size_t)t * hq + head) * D + e] = x;
+    else if (kdst) kdst[(size_t)(head - hq) * page_size * D + e] = from_float<TKV>(to_float<T>(x));
   }
   if (vdst) {
     const T* vrow = row + (size_t)(hq + hkv) * D;
@@ -190,15 +204,18 @@ __global__ void rope_append_vec_kernel(const T* __restrict__ qkv, const int32_t*
 PSB_API int psb_rope_append(const void* qkv, int dtype, const void* positions, const void* token_item, const void* cos_t,
                             const void* sin_t, const void* table, int table_width, void* kv, int kv_dtype, void* q_out,
                             int T, int hq, int hkv, int D, int page_size, int num_pages, int max_positions, int rotate,
-                            int write_kv, int paired, cudaStream_t stream) {
+                            int write_kv, int paired, int rotary_dim, int interleaved, cudaStream_t stream) {
   if (T < 0 || hq < 1 || hkv < 0 || D < 2 || (D & 1)) PSB_REFUSE("rope_append: bad sizes T=%d hq=%d hkv=%d D=%d", T, hq, hkv, D);
+  if (rotary_dim < 2 || rotary_dim > D || (rotary_dim & 1)) PSB_REFUSE("rope_append: rotary_dim %d must be even and in [2, %d]", rotary_dim, D);
+  const bool general = rotary_dim != D || interleaved;
+  if (general && paired) PSB_REFUSE("rope_append: the paired element order is built for the split-half rotation of a whole head only");
   if (write_kv && (page_size < 1 || num_pages < 1 || table_width < 1 || !kv || !table || hkv < 1))
     PSB_REFUSE("rope_append: cache arguments missing (page_size=%d num_pages=%d width=%d)", page_size, num_pages, table_width);
   if (rotate && (!cos_t || !sin_t || max_positions < 1)) PSB_REFUSE("rope_append: angle tables missing");
   if (paired && D % 16) PSB_REFUSE("rope_append: the paired element order needs a head size that is a multiple of 16, not %d", D);
   if (T == 0) return 0;
   const int work = (hq + hkv) * (D / 2);
-  if (D % 16 == 0) {  // every 8-element run is aligned: vector accesses
+  if (D % 16 == 0 && !general) {  // every 8-element run is aligned: vector accesses
     const int threads = work / 8 >= 256 ? 256 : (work / 8 >= 128 ? 128 : 64);
     PSB_DISPATCH_DTYPE(dtype, T_, {
       PSB_DISPATCH_DTYPE(kv_dtype, TKV, {
@@ -217,7 +234,7 @@ PSB_API int psb_rope_append(const void* qkv, int dtype, const void* positions, c
       psb_launch(rope_append_kernel<T_, TKV>, dim3(T), dim3(threads), 0, stream,
           (const T_*)qkv, (const int32_t*)positions, (const int32_t*)token_item, (const float*)cos_t, (const float*)sin_t,
           (const int32_t*)table, table_width, (TKV*)kv, (T_*)q_out, hq, hkv, D, page_size, num_pages, max_positions, rotate,
-          write_kv);
+          write_kv, rotary_dim, interleaved);
     });
   });
   PSB_LAUNCH_CHECK("rope_append");

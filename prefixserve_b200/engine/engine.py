@@ -37,7 +37,7 @@ class EngineConfig:
     max_num_seqs: int = 64           # must match the scheduler's max_decode_seqs
     max_prefill_tokens: int = 512    # must match the scheduler's budget
     max_seq_len: int | None = None   # None: the smaller of 8192 (the reference's default) and the model's positions
-    num_blocks: int | None = None    # None: size the pool from free memory
+    num_blocks: int | None = None    # pages of every cache group; None: size the pools from free memory
     reserve_bytes: int = 1 << 30     # left free after the pool
     page_size: int = 16
     enable_prefix_cache: bool = True
@@ -86,9 +86,9 @@ class Engine:
         self._token_buffers = [torch.empty(cfg.max_num_seqs, dtype=torch.int32, pin_memory=True) for _ in range(2)]
         self._token_turn = 0
         self.launched_ahead = 0  # steps launched before the step in front of them had been read
-        log.info("cache: %d pages of %d tokens (%.2f GB)", num_blocks, cfg.page_size, num_blocks * self.bytes_per_block / 1e9)
+        log.info("cache: %s pages of %d tokens", num_blocks, cfg.page_size)
 
-    def _make_cache(self, num_blocks: int) -> CacheManager:
+    def _make_cache(self, num_blocks) -> CacheManager:
         return CacheManager(self.needs, num_pages=num_blocks, num_slots=self.cfg.max_num_seqs,
                             max_seq_len=self.cfg.max_seq_len, page_size=self.cfg.page_size, dtype=self.dtype,
                             device=self.device, enable_prefix_cache=self.cfg.enable_prefix_cache)
@@ -234,9 +234,24 @@ class Engine:
         torch.cuda.empty_cache()
         free, _ = torch.cuda.mem_get_info()
         usable = free - activations - cfg.reserve_bytes
-        n = int(usable // self.bytes_per_block)
+        # Groups with a window are given what every running request can hold at once (the window, a portion and a
+        # page of slack); what is left goes to the groups that keep all keys, which share it page for page.
+        by_group = CacheManager.group_page_bytes(self.needs, cfg.page_size, self.dtype)
+        sizes: dict[int, int] = {}
+        for gi, (window, cost) in enumerate(by_group.items()):
+            if window is not None:
+                sizes[gi] = cfg.max_num_seqs * (pages_for(min(cfg.max_seq_len, window + prefill), cfg.page_size) + 1)
+                usable -= sizes[gi] * cost
+        full_cost = sum(cost for window, cost in by_group.items() if window is None)
         need = pages_for(cfg.max_seq_len, cfg.page_size)
-        if n < need:
-            raise EngineError(f"only {n} cache pages fit ({usable / 1e9:.2f} GB usable); one request of max_seq_len needs {need}")
-        log.info("trial step: activations %.0f MB, %.2f GB free -> %d pages", activations / 1e6, free / 1e9, n)
-        return n
+        if full_cost:
+            n = int(usable // full_cost)
+            if n < need:
+                raise EngineError(f"only {n} cache pages fit ({usable / 1e9:.2f} GB usable); one request of max_seq_len needs {need}")
+            for gi, window in enumerate(by_group):
+                if window is None:
+                    sizes[gi] = n
+        elif usable < 0:
+            raise EngineError(f"the windowed cache groups alone do not fit ({-usable / 1e9:.2f} GB short)")
+        log.info("trial step: activations %.0f MB, %.2f GB free -> pages per group %s", activations / 1e6, free / 1e9, sizes)
+        return sizes if len(sizes) != 1 else next(iter(sizes.values()))

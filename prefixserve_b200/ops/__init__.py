@@ -4,7 +4,9 @@ was not written for."""
 
 from .deferred import NormedRows  # noqa: F401
 from .kernels import (  # noqa: F401
+    ACTIVATIONS,
     KernelError,
+    act_mul,
     add_rmsnorm,
     attention,
     embedding,
@@ -12,6 +14,7 @@ from .kernels import (  # noqa: F401
     linear,
     pair_interleaved_order,
     qkv_rope_append,
+    residual_add,
     rope_append,
     sample,
     sample_slots,

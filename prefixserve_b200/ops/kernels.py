@@ -123,31 +123,45 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
     return gemm_nt_simt(x, w, out_dtype)
 
 
-def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
-    """silu(x Wg^T) * (x Wu^T) for W = [gate rows; up rows]: fused for few bfloat16 rows, else product then activation."""
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}  # the codes the kernels know (PsbAct in common.cuh)
+
+
+def activation_code(name: str) -> int:
+    try:
+        return ACTIVATIONS[name]
+    except KeyError:
+        raise KernelError(f"activation {name!r} is not built (one of {sorted(ACTIVATIONS)})") from None
+
+
+def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+    """act(x Wg^T) * (x Wu^T) for W = [gate rows; up rows]: fused for bfloat16 rows, else product then activation."""
+    code = activation_code(activation)
     if isinstance(x, NormedRows):
         if x.fusable and x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16:
             from .tensorcore import norm_gated_linear_bf16
-            act = norm_gated_linear_bf16(x, w_gate_up)
+            act = norm_gated_linear_bf16(x, w_gate_up, code)
             if act is not None:
                 return act
         x = x.tensor()
     if x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16:
         from .tensorcore import gated_linear_bf16
         _dev(x, "left operand"), _dev(w_gate_up, "weight")
-        act = gated_linear_bf16(x, w_gate_up)
+        act = gated_linear_bf16(x, w_gate_up, activation=code)
         if act is not None:
             return act
-    return silu_mul(linear(x, w_gate_up))
+    return act_mul(linear(x, w_gate_up), activation)
 
 
 def rope_append(qkv: torch.Tensor, positions: torch.Tensor, token_item: torch.Tensor, cos: torch.Tensor | None,
                 sin: torch.Tensor | None, table: torch.Tensor | None, kv: torch.Tensor | None, *, num_heads: int,
-                num_kv_heads: int, head_dim: int, page_size: int, write_kv: bool, paired: bool = False) -> torch.Tensor:
+                num_kv_heads: int, head_dim: int, page_size: int, write_kv: bool, paired: bool = False,
+                rotary_dim: int | None = None, interleaved: bool = False) -> torch.Tensor:
     """Rotates queries (and keys); stores rotated keys and values in the pages. Returns q [T, hq, D].
 
     ``paired``: every query and key head comes (and goes) with its elements in the pair-interleaved order of
-    ``pair_interleaved_order``; the rotary kernel's header says why that is harmless."""
+    ``pair_interleaved_order``; the rotary kernel's header says why that is harmless.
+    ``rotary_dim``: only the first so many elements of a head turn (default: all; the tables then hold
+    rotary_dim/2 angles); ``interleaved``: element 2j turns with 2j+1 instead of j with j + rotary_dim/2."""
     _dev(qkv, "projection output")
     t = qkv.shape[0]
     hkv_in = num_kv_heads if write_kv else 0
@@ -158,11 +172,16 @@ def rope_append(qkv: torch.Tensor, positions: torch.Tensor, token_item: torch.Te
     _i32(token_item, "token-to-item map")
     rotate = cos is not None
     max_pos = 0
+    rotary_dim = head_dim if rotary_dim is None else int(rotary_dim)
+    if rotary_dim < 2 or rotary_dim > head_dim or rotary_dim % 2:
+        raise KernelError(f"rotary_dim {rotary_dim} must be even and within the head size {head_dim}")
+    if paired and (rotary_dim != head_dim or interleaved):
+        raise KernelError("the paired element order goes with the split-half rotation of a whole head only")
     if rotate:
         assert sin is not None
         _dev(cos, "cos table"), _dev(sin, "sin table")
-        if cos.dtype != torch.float32 or cos.shape != sin.shape or cos.dim() != 2 or cos.shape[1] != head_dim // 2:
-            raise KernelError(f"angle tables must be float32 [positions, {head_dim // 2}], are {cos.dtype} {tuple(cos.shape)}")
+        if cos.dtype != torch.float32 or cos.shape != sin.shape or cos.dim() != 2 or cos.shape[1] != rotary_dim // 2:
+            raise KernelError(f"angle tables must be float32 [positions, {rotary_dim // 2}], are {cos.dtype} {tuple(cos.shape)}")
         max_pos = cos.shape[0]
     width = num_pages = 0
     kv_code = _code(qkv, "projection output")
@@ -178,7 +197,7 @@ def rope_append(qkv: torch.Tensor, positions: torch.Tensor, token_item: torch.Te
                                 token_item.data_ptr(), _ptr(cos), _ptr(sin), _ptr(table) if write_kv else None, width,
                                 _ptr(kv) if write_kv else None, kv_code, q.data_ptr(), t, num_heads, hkv_in, head_dim,
                                 page_size, num_pages, max_pos, 1 if rotate else 0, 1 if write_kv else 0, 1 if paired else 0,
-                                _stream()),
+                                rotary_dim, 1 if interleaved else 0, _stream()),
           "rope_append")
     return q
 
@@ -257,16 +276,30 @@ def attention(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, positions:
     return attention_generic(q, kv, table, positions, token_item, window=window, scale=scale)
 
 
-def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
-    """[T, 2I] -> silu(first half) * second half, [T, I]."""
+def act_mul(gate_up: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+    """[T, 2I] -> act(first half) * second half, [T, I]."""
     _dev(gate_up, "gate/up projection")
     t, two_i = gate_up.shape
     if two_i % 2:
         raise KernelError(f"gate/up projection must have an even width, has {two_i}")
     out = torch.empty((t, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
     check(lib().psb_silu_mul(gate_up.data_ptr(), _code(gate_up, "gate/up projection"), out.data_ptr(), t, two_i // 2,
-                             _stream()), "silu_mul")
+                             activation_code(activation), _stream()), "silu_mul")
     return out
+
+
+def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    """[T, 2I] -> silu(first half) * second half, [T, I]."""
+    return act_mul(gate_up, "silu")
+
+
+def residual_add(h: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+    """h += delta in place (h float32, delta float32 or bfloat16 of the same shape); returns h."""
+    _dev(h, "residual stream"), _dev(delta, "sublayer output")
+    if h.dtype != torch.float32 or delta.shape != h.shape:
+        raise KernelError(f"residual stream must be float32 and the output must match it: {h.dtype} {tuple(h.shape)} vs {tuple(delta.shape)}")
+    check(lib().psb_residual_add(h.data_ptr(), delta.data_ptr(), _code(delta, "sublayer output"), h.numel(), _stream()), "residual_add")
+    return h
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor | None = None, seed: torch.Tensor | None = None,

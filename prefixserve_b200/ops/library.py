@@ -33,16 +33,18 @@ _SIGNATURES: dict[str, list] = {
     # (a, a_dtype, w, w_dtype, c, c_dtype, M, N, K, lda, ldw, ldc, accumulate, stream)
     "psb_gemm_nt": [P, I, P, I, P, I, I, I, I, L, L, L, I, P],
     # (qkv, dtype, positions, token_item, cos, sin, table, table_width, kv, kv_dtype, q_out,
-    #  T, hq, hkv, D, page_size, num_pages, max_positions, rotate, write_kv, paired, stream)
-    "psb_rope_append": [P, I, P, P, P, P, P, I, P, I, P, I, I, I, I, I, I, I, I, I, I, P],
+    #  T, hq, hkv, D, page_size, num_pages, max_positions, rotate, write_kv, paired, rotary_dim, interleaved, stream)
+    "psb_rope_append": [P, I, P, P, P, P, P, I, P, I, P, I, I, I, I, I, I, I, I, I, I, I, I, P],
     # (h_in, pending, gain, h_out, W, M, K, eps, sms, positions, token_item, table, table_width, cos, sin, kv, q_out,
     #  hq, hkv, D, page_size, num_pages, max_positions, stream)
     "psb_gemm_stream_norm_rope": [P, P, P, P, P, I, I, F, I, P, P, P, I, P, P, P, P, I, I, I, I, I, I, P],
     # (q, dtype, kv, kv_dtype, table, table_width, positions, token_item, out, T, hq, hkv, D, page_size, window,
     #  scale, stream)
     "psb_attention_generic": [P, I, P, I, P, I, P, P, P, I, I, I, I, I, I, F, P],
-    # (gate_up, dtype, out, T, I, stream)
-    "psb_silu_mul": [P, I, P, I, I, P],
+    # (gate_up, dtype, out, T, I, activation, stream)
+    "psb_silu_mul": [P, I, P, I, I, I, P],
+    # (h, delta, delta_dtype, total, stream)
+    "psb_residual_add": [P, P, I, L, P],
     # (q, kv, table, table_width, item_start, kv_len, out, num_items, num_tiles, hq, hkv, D, page_size, window, scale,
     #  skip_single, stream)
     "psb_attention_prefill_bf16": [P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P],
@@ -62,24 +64,24 @@ _SIGNATURES: dict[str, list] = {
     "psb_attention_decode_bf16": [P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P],
     # (x, W, y, out_dtype, M, N, K, wide, stream)
     "psb_gemm_small_m": [P, P, P, I, I, I, I, I, P],
-    # (x, W, act, M, I, K, wide, stream)
-    "psb_gemm_small_m_gated": [P, P, P, I, I, I, I, P],
+    # (x, W, act, M, I, K, wide, activation, stream)
+    "psb_gemm_small_m_gated": [P, P, P, I, I, I, I, I, P],
     # (gated) -> most rows of x
     "psb_gemm_small_m_max_rows": [I],
     # (x, W, y, out_dtype, M, N, K, sms, stream)
     "psb_gemm_stream": [P, P, P, I, I, I, I, I, P],
-    # (x, W, act, M, I, K, sms, stream)
-    "psb_gemm_stream_gated": [P, P, P, I, I, I, I, P],
+    # (x, W, act, M, I, K, sms, activation, stream)
+    "psb_gemm_stream_gated": [P, P, P, I, I, I, I, I, P],
     # (M, K) -> 1 if the norm-fused streaming product takes the shape
     "psb_gemm_stream_norm_supported": [I, I],
     # (h_in, pending, gain, rows, h_out, W, y, out_dtype, M, N, K, eps, sms, stream)
     "psb_gemm_stream_norm": [P, P, P, P, P, P, P, I, I, I, I, F, I, P],
-    # (h_in, pending, gain, h_out, W, act, M, I, K, eps, sms, stream)
-    "psb_gemm_stream_norm_gated": [P, P, P, P, P, P, I, I, I, F, I, P],
+    # (h_in, pending, gain, h_out, W, act, M, I, K, eps, sms, activation, stream)
+    "psb_gemm_stream_norm_gated": [P, P, P, P, P, P, I, I, I, F, I, I, P],
     # (a, w, c, M, N, K, sms, stream)
     "psb_gemm_tcgen05": [P, P, P, I, I, I, I, P],
-    # (a, w, act, M, I, K, sms, stream)
-    "psb_gemm_tcgen05_gated": [P, P, P, I, I, I, I, P],
+    # (a, w, act, M, I, K, sms, activation, stream)
+    "psb_gemm_tcgen05_gated": [P, P, P, I, I, I, I, I, P],
     "psb_gemm_tcgen05_tile_width": [I],
     "psb_gemm_tcgen05_rope": [P, P, I, I, I, P, P, P, I, P, P, P, P, I, I, I, I, I, I, P],
     # () -> 0 while no bounded wait of the tcgen05 kernel has ever run out

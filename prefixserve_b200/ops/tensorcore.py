@@ -54,12 +54,12 @@ def gemm_stream(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> tor
     return y
 
 
-def gemm_stream_gated(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+def gemm_stream_gated(x: torch.Tensor, w_gate_up: torch.Tensor, activation: int = 0) -> torch.Tensor:
     m, k = x.shape
     inter = w_gate_up.shape[0] // 2
     act = torch.empty((m, inter), dtype=torch.bfloat16, device=x.device)
     check(lib().psb_gemm_stream_gated(x.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(), m, inter, k, _sms(x.device),
-                                      stream_handle()), "gemm_stream_gated")
+                                      activation, stream_handle()), "gemm_stream_gated")
     return act
 
 
@@ -112,8 +112,8 @@ def norm_qkv_rope_bf16(x, w_qkv, positions, token_item, cos, sin, table, kv, hq,
     return q
 
 
-def norm_gated_linear_bf16(x, w_gate_up: torch.Tensor) -> torch.Tensor | None:
-    """silu(x Wg^T) * (x Wu^T) with x = rmsnorm(h + pending), all in the streaming kernel; None when it does not fit."""
+def norm_gated_linear_bf16(x, w_gate_up: torch.Tensor, activation: int = 0) -> torch.Tensor | None:
+    """act(x Wg^T) * (x Wu^T) with x = rmsnorm(h + pending), all in the streaming kernel; None when it does not fit."""
     if w_gate_up.shape[0] % 2 or x.rows is not None or not _norm_fusable(x, w_gate_up):
         return None
     m, k = x.shape
@@ -122,7 +122,7 @@ def norm_gated_linear_bf16(x, w_gate_up: torch.Tensor) -> torch.Tensor | None:
     new_h = torch.empty_like(x.h) if x.pending is not None else None
     check(lib().psb_gemm_stream_norm_gated(x.h.data_ptr(), None if x.pending is None else x.pending.data_ptr(), x.gain.data_ptr(),
                                            None if new_h is None else new_h.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(),
-                                           m, inter, k, x.eps, _sms(w_gate_up.device),
+                                           m, inter, k, x.eps, _sms(w_gate_up.device), activation,
                                            stream_handle()), "gemm_stream_norm_gated")
     x.fused(new_h)
     return act
@@ -148,13 +148,13 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return y
 
 
-def gemm_tcgen05_gated(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
-    """silu(x Wg^T) * (x Wu^T) -> bfloat16 [M, I], the activation applied in the product's epilogue."""
+def gemm_tcgen05_gated(x: torch.Tensor, w_gate_up: torch.Tensor, activation: int = 0) -> torch.Tensor:
+    """act(x Wg^T) * (x Wu^T) -> bfloat16 [M, I], the activation applied in the product's epilogue."""
     m, k = x.shape
     inter = w_gate_up.shape[0] // 2
     act = torch.empty((m, inter), dtype=torch.bfloat16, device=x.device)
     check(lib().psb_gemm_tcgen05_gated(x.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(), m, inter, k, _sms(x.device),
-                                       stream_handle()), "gemm_tcgen05_gated")
+                                       activation, stream_handle()), "gemm_tcgen05_gated")
     return act
 
 
@@ -195,20 +195,20 @@ def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> tor
     return y if out_dtype == y.dtype else y.to(out_dtype)
 
 
-def gated_linear_bf16(x: torch.Tensor, w_gate_up: torch.Tensor, limit: int | None = None) -> torch.Tensor | None:
-    """silu(x Wg^T) * (x Wu^T) in one kernel for few rows; None when the fused kernel does not take the shape."""
+def gated_linear_bf16(x: torch.Tensor, w_gate_up: torch.Tensor, limit: int | None = None, activation: int = 0) -> torch.Tensor | None:
+    """act(x Wg^T) * (x Wu^T) in one kernel for few rows; None when the fused kernel does not take the shape."""
     m, k = x.shape
     if (limit is None and small_m_ok(m, k, min(STREAM_M, 16)) and w_gate_up.shape[0] % 2 == 0 and x.is_contiguous()
             and w_gate_up.is_contiguous()):
-        return gemm_stream_gated(x, w_gate_up)
+        return gemm_stream_gated(x, w_gate_up, activation)
     if limit is None and m > max(STREAM_M, SMALL_M_GATED) and w_gate_up.shape[0] % 2 == 0 and _tcgen05_ok(x, w_gate_up, 128):
-        return gemm_tcgen05_gated(x, w_gate_up)
+        return gemm_tcgen05_gated(x, w_gate_up, activation)
     if not (small_m_ok(m, k, SMALL_M_GATED if limit is None else limit) and w_gate_up.shape[0] % 2 == 0 and x.is_contiguous() and w_gate_up.is_contiguous()):
         return None
     inter = w_gate_up.shape[0] // 2
     act = torch.empty((m, inter), dtype=torch.bfloat16, device=x.device)
     wide = 1 if (inter + 15) // 16 < WIDE_BELOW_TILES and k // 32 >= 32 else 0
-    check(lib().psb_gemm_small_m_gated(x.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(), m, inter, k, wide,
+    check(lib().psb_gemm_small_m_gated(x.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(), m, inter, k, wide, activation,
                                        stream_handle()), "gemm_small_m_gated")
     return act
 

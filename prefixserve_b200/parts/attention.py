@@ -36,6 +36,13 @@ class Attention(Mixer):
         if self.hq % self.hkv:
             raise ValueError(f"{self.hq} query heads cannot share {self.hkv} key/value heads")
         self.position = make("position", params["position"])
+        # what the position part says about its rotation (a part that does not rotate says nothing)
+        self.rotary_dim = int(getattr(self.position, "rotary_dim", None) or self.d)
+        self.interleaved = getattr(self.position, "layout", "half") == "interleaved"
+        # With head sizes that are multiples of 16, and a rotation (if any) of the split-half kind over the whole head,
+        # queries and keys are kept in the pair-interleaved element order (see load()); any other rotation keeps the
+        # natural order and goes through the general rotary kernel.
+        self.paired = self.d % 16 == 0 and self.rotary_dim == self.d and not self.interleaved
         self.w_qkv: torch.Tensor | None = None
         self.w_o: torch.Tensor | None = None
 
@@ -49,7 +56,7 @@ class Attention(Mixer):
         return specs
 
     def cache_need(self):
-        return CacheNeed(paged=PagedKV(self.hkv, self.d, self.window))
+        return CacheNeed(paged=PagedKV(self.hkv, self.d, self.window, "paired" if self.paired else "natural"))
 
     def load(self, tensors, *, compute_dtype, device):
         pieces = [tensors["q_proj"]]
@@ -62,8 +69,8 @@ class Attention(Mixer):
         # of 16 holds 8 elements of the head's first half and the 8 they are rotated with: the decode kernel that
         # computes a 16-row tile of this product can then rotate and store it itself.  Queries and keys keep that
         # element order all the way (scores do not depend on it); every attention part does this, rotating or not, so
-        # that a layer which reads another layer's keys meets the order it uses itself.
-        self.paired = self.d % 16 == 0
+        # that a layer which reads another layer's keys meets the order it uses itself (the order is part of the cache
+        # need, so a reader that would disagree is refused when the model is put together).
         if self.paired:
             order = torch.tensor(ops.pair_interleaved_order(self.d), device=pieces[0].device)
             for at in range(2 if self.own_kv else 1):
@@ -88,7 +95,8 @@ class Attention(Mixer):
             qkv = ops.linear(x, self.w_qkv)
             q = ops.rope_append(qkv, ctx.positions, ctx.token_item, self.position.cos, self.position.sin, table, cache.kv,
                                 num_heads=self.hq, num_kv_heads=self.hkv, head_dim=self.d, page_size=cache.page_size,
-                                write_kv=self.own_kv, paired=self.paired)
+                                write_kv=self.own_kv, paired=self.paired, rotary_dim=self.rotary_dim,
+                                interleaved=self.interleaved)
         o = ops.attention(q, cache.kv, table, ctx.positions, ctx.token_item, window=self.window, scale=self.scale, ctx=ctx)
         return ops.linear(o, self.w_o)
 

@@ -35,6 +35,7 @@ class PagedKV:
     num_kv_heads: int
     head_dim: int
     window: int | None = None
+    key_order: str = "natural"  # how a key head's elements are ordered in the pages; writer and readers must agree
 
 
 @dataclass(frozen=True)

@@ -18,9 +18,9 @@ class GatedMLP(FeedForward):
         super().__init__(params)
         self.hidden = int(params["hidden_size"])
         self.inter = int(params["intermediate_size"])
-        act = params.get("activation", "silu")
-        if act != "silu":
-            raise ValueError(f"activation {act!r} is not built (only silu)")
+        self.activation = str(params.get("activation", "silu"))
+        if self.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"activation {self.activation!r} is not built (one of {sorted(ops.ACTIVATIONS)})")
         self.w_gate_up: torch.Tensor | None = None
         self.w_down: torch.Tensor | None = None
 
@@ -38,7 +38,7 @@ class GatedMLP(FeedForward):
         self.w_down = tensors["down_proj"].contiguous()
 
     def forward(self, x, ctx: StepContext):
-        return ops.linear(ops.gated_linear(x, self.w_gate_up), self.w_down)
+        return ops.linear(ops.gated_linear(x, self.w_gate_up, self.activation), self.w_down)
 
 
 register_ffn("gated_mlp", GatedMLP, replace=True)

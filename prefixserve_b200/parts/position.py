@@ -7,6 +7,13 @@ original/low_freq_factor are divided by ``factor``, those shorter than
 original/high_freq_factor are kept, and the band between is blended.  The
 tables hold D/2 columns (the reference's table repeats them to D).
 ``none``: no rotation; queries and keys go through unchanged.
+
+What a rotating part tells its mixer: ``cos``/``sin`` float32 [positions,
+rotary_dim/2], ``rotary_dim`` (how many leading elements of a head turn;
+default all) and ``layout`` ("half": element j turns with j + rotary_dim/2;
+"interleaved": 2j with 2j+1).  The attention part hands that description to
+its kernels; those that bake in the split-half rotation of a whole head are
+only used when the description says exactly that.
 """
 
 from __future__ import annotations
@@ -50,20 +57,21 @@ class RotaryEncoding(PositionEncoding):
         self.head_dim = int(params["head_dim"])
         self.theta = float(params["theta"])
         self.scaling = params.get("scaling")
-        layout = params.get("layout", "half")
-        if layout != "half":
-            raise ValueError(f"rotary layout {layout!r} is not built (only the split-half layout)")
-        if self.head_dim % 2:
-            raise ValueError("rotary encoding needs an even head size")
+        self.layout = str(params.get("layout", "half"))
+        if self.layout not in ("half", "interleaved"):
+            raise ValueError(f"rotary layout {self.layout!r} is not built (half or interleaved)")
+        self.rotary_dim = int(params.get("rotary_dim") or self.head_dim)
+        if self.rotary_dim % 2 or not 2 <= self.rotary_dim <= self.head_dim:
+            raise ValueError(f"rotary_dim {self.rotary_dim} must be even and within the head size {self.head_dim}")
         self.cos: torch.Tensor | None = None
         self.sin: torch.Tensor | None = None
 
     def prepare(self, *, max_positions, compute_dtype, device):
         # layers with the same constants share one pair of tables
-        key = (self.head_dim, self.theta, repr(sorted(self.scaling.items())) if self.scaling else None, str(device))
+        key = (self.rotary_dim, self.theta, repr(sorted(self.scaling.items())) if self.scaling else None, str(device))
         held = _TABLES.get(key)
         if held is None or held[0].shape[0] < max_positions:
-            inv = rope_inverse_frequencies(self.head_dim, self.theta, self.scaling)
+            inv = rope_inverse_frequencies(self.rotary_dim, self.theta, self.scaling)
             angles = torch.outer(torch.arange(max_positions, dtype=torch.int64).float(), inv)  # float32, on the host
             held = (angles.cos().to(device).contiguous(), angles.sin().to(device).contiguous())
             _TABLES[key] = held
@@ -74,6 +82,8 @@ class NoPositions(PositionEncoding):
     rotates = False
     cos = None
     sin = None
+    rotary_dim = None
+    layout = "half"
 
 
 register_position("rope", RotaryEncoding, replace=True)

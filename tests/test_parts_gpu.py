@@ -61,8 +61,11 @@ def test_position_part_matches_plain_tables():
     assert pos.cos.dtype == torch.float32
     none = make("position", part("none"))
     assert none.cos is None and not none.rotates
+    assert make("position", part("rope", head_dim=32, theta=1.0, layout="interleaved", rotary_dim=16)).rotary_dim == 16
     with pytest.raises(ValueError):
-        make("position", part("rope", head_dim=32, theta=1.0, layout="interleaved"))
+        make("position", part("rope", head_dim=32, theta=1.0, layout="spiral"))
+    with pytest.raises(ValueError):
+        make("position", part("rope", head_dim=32, theta=1.0, rotary_dim=34))
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -94,18 +97,20 @@ def test_ffn_embedding_and_head_parts(dtype):
 
 # ---- whole models from parts -------------------------------------------------------------------------
 
-def build(spec, dtype, seed=0, pages=64, std=0.15):
+def build(spec, dtype, seed=0, pages=64, std=0.15, stored=torch.float32):
+    """``stored``: the type the "checkpoint" holds; matrices stored in float32 stay float32 in a bfloat16 run (and take
+    the float32 product), stored in bfloat16 they run on the bfloat16 kernels.  ``raw`` comes back in float32."""
     from prefixserve_b200.cache import CacheManager
     from prefixserve_b200.engine import ModelRunner
     from prefixserve_b200.parts import build_model
     from prefixserve_b200.weights import convert_tensors, random_tensors
     model = build_model(spec)
     table = model.param_table()
-    raw = random_tensors(table, seed, std=std, gain_noise=0.1, dtype=torch.float32)
+    raw = random_tensors(table, seed, std=std, gain_noise=0.1, dtype=stored)
     model.load(convert_tensors(raw, table, compute_dtype=dtype, device=DEV), compute_dtype=dtype, device=DEV, max_positions=512)
     cache = CacheManager(model.cache_needs(), num_pages=pages, num_slots=4, max_seq_len=512, dtype=dtype, device=DEV,
                          enable_prefix_cache=False)
-    return model, raw, cache, ModelRunner(model, cache, device=DEV)
+    return model, {k: v.float() for k, v in raw.items()}, cache, ModelRunner(model, cache, device=DEV)
 
 
 def run_cut(runner, cache, tokens, cuts):
@@ -233,17 +238,16 @@ def test_windowed_heads_of_64_decoded_through_captured_steps(window):
     from prefixserve_b200.ops import library
     h, hq, hkv, d = 128, 4, 2, 64
     spec = toy_model_spec([layer_of(attn_spec(h, hq, hkv, d, window=window), h=h, inter=96)], [LayerCall(0, 0)], h=h)
-    model, raw, cache, runner = build(spec, torch.bfloat16, std=0.3)
+    model, raw, cache, runner = build(spec, torch.bfloat16, std=0.3, stored=torch.bfloat16)
     mixers = {0: lambda x, w, p, kv: plain_attention_layer(x, w, p, hq, hkv, d, window)}
     tokens = helpers.random_tokens(97, window + 70, seed=8)
-    w16 = {k: v.to(torch.bfloat16).float() for k, v in raw.items()}   # the values the engine holds
-    want = plain_forward(spec, w16, tokens, mixers)
+    want = plain_forward(spec, raw, tokens, mixers)
     before = library.launch_counts["attention_decode"]
     got = run_cut(runner, cache, tokens, [1] * len(tokens))
     assert runner.graph_replays >= len(tokens) - 2 and library.launch_counts["attention_decode"] - before >= len(tokens) - 1
     assert helpers.rel_err(got, want) < 0.05
     # the same token by token without captured steps (launch shapes from each step's own lengths): the same to rounding
-    model2, _, cache2, runner2 = build(spec, torch.bfloat16, std=0.3)
+    model2, _, cache2, runner2 = build(spec, torch.bfloat16, std=0.3, stored=torch.bfloat16)
     runner2.use_graphs = False
     eager = run_cut(runner2, cache2, tokens, [1] * len(tokens))
     assert runner2.graph_replays == 0
@@ -445,3 +449,169 @@ def test_toy_routed_feed_forward_and_toy_positions(dtype):
             close(got, want, dtype)   # every token takes the same expert however the prompt is cut
         else:
             assert helpers.rel_err(got, want) < 0.08   # a near-tie at the router may pick another expert in bfloat16
+
+
+# ---- other rotations, another activation, other block arrangements --------------------------------------
+
+def register_partial_rotation():
+    """A position part, defined here, that turns only the first ``rotary_dim`` elements of a head, in either pairing.
+    It only describes its rotation (tables, rotary_dim, layout); the attention part and its kernels do the rest."""
+    from prefixserve_b200.parts import PositionEncoding, register_position
+
+    class PartialRotation(PositionEncoding):
+        rotates = True
+
+        def __init__(self, params):
+            super().__init__(params)
+            self.rotary_dim, self.layout, self.step = int(params["rotary_dim"]), params["layout"], float(params["step"])
+            self.cos = self.sin = None
+
+        def prepare(self, *, max_positions, compute_dtype, device):
+            angles = torch.outer(torch.arange(max_positions).float(), toy_frequencies(self.rotary_dim, self.step))
+            self.cos, self.sin = angles.cos().to(device).contiguous(), angles.sin().to(device).contiguous()
+
+    register_position("partial_rotation", PartialRotation, replace=True)
+
+
+def plain_partial_rotation(x, rotary_dim, layout, step):
+    """x [T, heads, D] -> the first rotary_dim elements of every head turned by position, the rest untouched."""
+    t = x.shape[0]
+    angles = torch.outer(torch.arange(t).float(), toy_frequencies(rotary_dim, step))   # [T, rot/2]
+    cos, sin = angles.cos()[:, None, :], angles.sin()[:, None, :]
+    rot, rest = x[..., :rotary_dim], x[..., rotary_dim:]
+    if layout == "half":
+        x1, x2 = rot[..., : rotary_dim // 2], rot[..., rotary_dim // 2:]
+        turned = torch.cat((x1 * cos - x2 * sin, x2 * cos + x1 * sin), dim=-1)
+    else:
+        x1, x2 = rot[..., 0::2], rot[..., 1::2]
+        turned = torch.stack((x1 * cos - x2 * sin, x2 * cos + x1 * sin), dim=-1).flatten(-2)
+    return torch.cat((turned, rest), dim=-1)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("d,rotary_dim,layout", [(64, 32, "half"), (64, 64, "interleaved"), (48, 20, "interleaved"), (128, 64, "half")])
+def test_partial_and_interleaved_rotations_from_a_toy_part(dtype, d, rotary_dim, layout):
+    """Head sizes at which the fused projections exist: a rotation they do not bake in must go round them (separate
+    product, general rotary kernel, natural element order in the cache) and still agree with plain under every cutting."""
+    from prefixserve_b200.config import LayerCall, part
+    from prefixserve_b200.ops import library
+    register_partial_rotation()
+    h, hq, hkv = 96, 4, 2
+    position = part("partial_rotation", rotary_dim=rotary_dim, layout=layout, step=0.03)
+    mixer = part("attention", hidden_size=h, num_heads=hq, num_kv_heads=hkv, head_dim=d, window=None, own_kv=True, position=position)
+    spec = toy_model_spec([layer_of(mixer, h=h, inter=64)], [LayerCall(0, 0)], h=h)
+    model, raw, cache, runner = build(spec, dtype, seed=4, std=0.2, stored=dtype)
+    assert model.blocks[0].mixer.paired is False and cache.needs[0].paged.key_order == "natural"
+
+    def attention(x, w, p, kv):
+        t = x.shape[0]
+        q = plain_partial_rotation((x @ w[p + "q_proj"].t()).view(t, hq, d), rotary_dim, layout, 0.03)
+        k = plain_partial_rotation((x @ w[p + "k_proj"].t()).view(t, hkv, d), rotary_dim, layout, 0.03)
+        v = (x @ w[p + "v_proj"].t()).view(t, hkv, d)
+        return plain_model.causal_attention(q, k, v).reshape(t, hq * d) @ w[p + "o_proj"].t(), (k, v)
+
+    tokens = helpers.random_tokens(97, 150, seed=12)
+    want = plain_forward(spec, raw, tokens, {0: attention})
+    before = library.launch_counts.copy()
+    for cuts in ([150], [110] + [1] * 40, [7, 2, 16, 3, 2, 5, 17, 2, 31, 4, 61]):
+        got = run_cut(runner, cache, tokens, cuts)
+        if dtype == torch.float32:
+            close(got, want, dtype)
+        else:
+            assert helpers.rel_err(got, want) < 0.05
+    taken = library.launch_counts - before
+    assert taken["rope_append"] > 0 and taken["gemm_stream_norm_rope"] == 0 and taken["gemm_tcgen05_rope"] == 0, dict(taken)
+
+
+def test_a_reader_with_another_element_order_is_refused():
+    """A layer that reads another layer's keys must keep a head's elements in the order the writer used."""
+    from prefixserve_b200.config import LayerCall, part
+    from prefixserve_b200.parts import build_model
+    register_partial_rotation()
+    h, hq, hkv, d = 96, 4, 2, 64
+    partial = part("attention", hidden_size=h, num_heads=hq, num_kv_heads=hkv, head_dim=d, window=None, own_kv=True,
+                   position=part("partial_rotation", rotary_dim=32, layout="half", step=0.03))
+    reader = attn_spec(h, hq, hkv, d, own_kv=False)   # whole-head rotation: pair-interleaved order
+    spec = toy_model_spec([layer_of(partial, h=h), layer_of(reader, h=h)], [LayerCall(0, 0), LayerCall(1, 0, writes_cache=False)], h=h)
+    with pytest.raises(ValueError, match="reads cache entry"):
+        build_model(spec).cache_needs()
+
+
+def gelu_mlp(x, gate_w, up_w, down_w):
+    gate = x @ gate_w.t()
+    return (torch.nn.functional.gelu(gate, approximate="tanh") * (x @ up_w.t())) @ down_w.t()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("arrangement", ["pre_norm", "parallel"])
+def test_another_activation_and_the_parallel_arrangement(dtype, arrangement):
+    """gated_mlp with the tanh form of GELU (in every kernel that applies the activation: cuts of 1, of a few and of
+    hundreds of tokens), a block whose sublayers both read the entering stream, and a layer that only mixes."""
+    from prefixserve_b200.config import LayerCall, LayerSpec, part
+    from prefixserve_b200.ops import library, tensorcore
+    h, hq, hkv, d, inter = 128, 2, 1, 64, 256
+    norm = part("rms", size=h, eps=1e-5)
+    gelu = LayerSpec(mixer=attn_spec(h, hq, hkv, d), ffn=part("gated_mlp", hidden_size=h, intermediate_size=inter, activation="gelu_tanh"),
+                     mixer_norm=norm, ffn_norm=norm, arrangement=arrangement)
+    only_mixer = LayerSpec(mixer=attn_spec(h, hq, hkv, d), ffn=None, mixer_norm=norm, ffn_norm=None, arrangement=arrangement)
+    spec = toy_model_spec([gelu, only_mixer, gelu], [LayerCall(0, 0), LayerCall(1, 1), LayerCall(2, 2)], h=h)
+    model, raw, cache, runner = build(spec, dtype, seed=6, std=0.1, stored=dtype)
+    assert "layers.1.ffn.gate_proj" not in model.param_table() and "layers.2.ffn.gate_proj" in model.param_table()
+
+    def forward(tokens):
+        w = raw
+        hh = w["embedding.weight"][torch.tensor(tokens)]
+        for i in range(3):
+            p = f"layers.{i}."
+            x = plain_model.rms_norm(hh, w[p + "mixer_norm.weight"], 1e-5)
+            mixed, _ = plain_attention_layer(x, w, p + "mixer.", hq, hkv, d, None)
+            if i == 1:
+                hh = hh + mixed
+                continue
+            if arrangement == "pre_norm":
+                hh = hh + mixed
+                x2 = plain_model.rms_norm(hh, w[p + "ffn_norm.weight"], 1e-5)
+                hh = hh + gelu_mlp(x2, w[p + "ffn.gate_proj"], w[p + "ffn.up_proj"], w[p + "ffn.down_proj"])
+            else:
+                x2 = plain_model.rms_norm(hh, w[p + "ffn_norm.weight"], 1e-5)
+                hh = hh + mixed + gelu_mlp(x2, w[p + "ffn.gate_proj"], w[p + "ffn.up_proj"], w[p + "ffn.down_proj"])
+        return plain_model.rms_norm(hh, w["final_norm.weight"], 1e-5) @ w["head.weight"].t()
+
+    tokens = helpers.random_tokens(97, 400, seed=3)
+    want = forward(tokens)
+    tiles = tensorcore.TCGEN05_MIN_TILES
+    tensorcore.TCGEN05_MIN_TILES = 1     # let the 300-token portion take the tcgen05 product with the fused activation
+    before = library.launch_counts.copy()
+    try:
+        for cuts in ([400], [300, 40] + [1] * 60, [7, 2, 16, 3, 2, 5, 17, 2, 31, 4] * 5):
+            got = run_cut(runner, cache, tokens, cuts)
+            if dtype == torch.float32:
+                close(got, want, dtype)
+            else:
+                assert helpers.rel_err(got, want) < 0.05
+    finally:
+        tensorcore.TCGEN05_MIN_TILES = tiles
+    taken = library.launch_counts - before
+    if dtype == torch.bfloat16:
+        fused = "gemm_stream_norm_gated" if arrangement == "pre_norm" else "gemm_stream_gated"
+        assert taken["gemm_tcgen05_gated"] > 0 and taken[fused] > 0, dict(taken)
+    if arrangement == "parallel":
+        assert taken["residual_add"] > 0
+
+
+def test_unknown_activation_and_arrangement_are_refused_before_anything_runs():
+    from prefixserve_b200 import ops
+    from prefixserve_b200.config import LayerSpec, part
+    from prefixserve_b200.parts import Block
+    with pytest.raises(ValueError, match="activation"):
+        layer_of(attn_spec(48, 3, 1, 16)).ffn.with_params(activation="relu6") and Block(
+            LayerSpec(mixer=attn_spec(48, 3, 1, 16), ffn=part("gated_mlp", hidden_size=48, intermediate_size=64, activation="relu6"),
+                      mixer_norm=part("rms", size=48, eps=1e-5), ffn_norm=part("rms", size=48, eps=1e-5)))
+    with pytest.raises(ValueError, match="arrangement"):
+        Block(LayerSpec(mixer=attn_spec(48, 3, 1, 16), ffn=None, mixer_norm=part("rms", size=48, eps=1e-5), ffn_norm=None,
+                        arrangement="sandwich"))
+    x = torch.zeros(2, 64, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(ops.KernelError, match="activation"):
+        ops.gated_linear(x, torch.zeros(32, 64, dtype=torch.bfloat16, device=DEV), "relu6")
+    from prefixserve_b200.ops.library import lib
+    assert lib().psb_gemm_stream_gated(x.data_ptr(), x.data_ptr(), x.data_ptr(), 2, 16, 64, 148, 7, None) != 0   # the C entry refuses too
