@@ -99,6 +99,9 @@ class CacheManager:
             self.groups[g].entries.append(i)
             self.entry_group.append(g)
 
+        # Test hook: fill every page with NaN the moment nobody holds it any more, so that a step which still reads a
+        # page it has given back (or reads a reused page beyond what its new owner wrote) cannot go unnoticed.
+        self.poison_freed = False
         self.slots = SlotPool(num_slots)
         self.records = SlotRecords(num_slots)          # host mirror of the per-slot records, owned by the C++ side
         self._position = self.records.view()[:, 0]     # tokens computed, per slot (a view of the mirror)
@@ -185,8 +188,19 @@ class CacheManager:
                 g.pool.decref_many(ids)
             except CoreError as e:  # a page freed twice: never continue silently
                 raise CacheError(f"slot {slot}: {e}") from e
+            self._poison(g, ids)
         self._position[slot] = 0
         self.slots.give_back(slot)
+
+    def _poison(self, g: _Group, ids: Sequence[int]) -> None:
+        if not self.poison_freed or not ids:
+            return
+        free = [p for p in ids if g.pool.ref_count(p) == 0]
+        if free:
+            index = torch.tensor(free, device=self.device)
+            for entry in g.entries:
+                if self.kv[entry] is not None:
+                    self.kv[entry][index] = float("nan")
 
     def position(self, slot: int) -> int:
         return int(self._position[slot])
@@ -271,6 +285,7 @@ class CacheManager:
             ids = g.tables.release_front(slot, self._first_needed_page(g, computed))
             if ids:
                 g.pool.decref_many(ids)
+                self._poison(g, ids)
 
     def page_ids(self, slot: int, group: int = 0) -> list[int]:
         return self.groups[group].tables.row(slot)

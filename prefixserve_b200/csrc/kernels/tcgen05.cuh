@@ -56,18 +56,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded: false when the barrier did not complete within SPIN_LIMIT polls or another warp has raised the abort flag.
 // The abort flag (shared memory) and the device's status word are looked at every 64th poll only: a load per poll from
 // every waiting warp crowds the path that barrier arrivals and the tensor-core instructions also take.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort, int who) {
-  for (uint32_t spin = 0; spin < SPIN_LIMIT; ++spin) {
+// ``limit`` polls at most; ``status`` is the word that records who gave up first.
+__device__ __forceinline__ bool mbar_wait_limited(uint64_t* bar, uint32_t parity, volatile uint32_t* abort, int who,
+                                                  uint32_t limit, int* status) {
+  for (uint32_t spin = 0; spin < limit; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((spin & 63u) == 63u) {
       if (*abort) return false;
       // once any CTA on the device has given up, the others do not sit out their own limits
-      if (*reinterpret_cast<volatile int*>(&g_status) != 0) { *abort = 1; return false; }
+      if (*reinterpret_cast<volatile int*>(status) != 0) { *abort = 1; return false; }
     }
   }
   *abort = 1;
-  atomicCAS(&g_status, 0, who);
+  atomicCAS(status, 0, who);
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort, int who) {
+  return mbar_wait_limited(bar, parity, abort, who, SPIN_LIMIT, &g_status);
 }
 
 // A converged warp that waits together calls mbar_wait in all its lanes: measured on B200, that costs about 120

@@ -94,6 +94,8 @@ _SIGNATURES: dict[str, list] = {
     "psb_scatter_words": [P, P, I, I, P],
     # (records, record_words, kv_len, slots, rows, row_width, out, width, num_items, num_slots, stream)
     "psb_step_prepare": [P, I, P, P, P, I, P, I, I, I, P],
+    # (limit, who, out int32[3], stream)
+    "psb_selftest_bounded_wait": [I, I, P, P],
     # (S, V) -> bytes of scratch psb_sample wants
     "psb_sample_scratch_bytes": [I, I],
 }

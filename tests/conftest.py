@@ -1,5 +1,9 @@
+import os
 import sys
 from pathlib import Path
+
+# the step function's debug check (no write into a page the prefix cache owns) is on for the whole suite
+os.environ.setdefault("PSB200_DEBUG_CHECKS", "1")
 
 import pytest
 

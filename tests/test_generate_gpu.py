@@ -182,6 +182,12 @@ def test_captured_steps_keep_their_split_scratch_when_later_captures_need_more(t
         assert len(next(iter(tensorcore._scratch.values()))) > max(generations, 1)   # the scratch did grow in between
         assert many.generate([prompt], params) == want
         many.engine.check_device_status()
+        # and against the plain implementation, not only the engine against itself: the float32 logits along the
+        # engine's own tokens must have those tokens at or next to the top
+        plain_cfg, plain_tensors = plain_model.read_folder(folder)
+        logits = plain_model.forward(plain_cfg, plain_tensors, prompt + want[0])[len(prompt) - 1: -1]
+        for step, tok in enumerate(want[0]):
+            assert float(logits[step, tok]) >= float(logits[step].max()) - 0.05 * float(logits[step].abs().max()), step
     finally:
         for key, held in earlier.items():
             tensorcore._scratch[key] = held + tensorcore._scratch.get(key, [])
@@ -254,3 +260,33 @@ def test_engine_refuses_what_it_cannot_run(sharp):
     assert runner.step([StepItem(slot, 0, toks, (0, 4))]).shape == (2, helpers.TINY_B["cfg"].vocab_size)
     with pytest.raises(ValueError, match="max_seq_len"):
         Engine(EngineConfig(model_path=folder, dtype=torch.float32, max_seq_len=100000, num_blocks=8))
+
+
+def test_the_step_function_refuses_to_write_into_a_cached_page(sharp):
+    """The debug check that is on for this whole suite (PSB200_DEBUG_CHECKS): a step may never write a position
+    whose page the prefix tree owns, because another request may be reading it (the reference's harness asserts the
+    same from outside, tests/test_llama_exact.py:146-151 of PrefixServe).  A slot that adopts a cached page but
+    claims fewer tokens than the page holds would write into it: refused before anything is launched."""
+    from prefixserve_b200.engine import Engine, EngineConfig, EngineError, StepItem
+    folder, _ = sharp
+    engine = Engine(EngineConfig(model_path=folder, dtype=torch.float32, max_num_seqs=2, max_prefill_tokens=32,
+                                 max_seq_len=64, num_blocks=8))
+    cache, runner = engine.cache, engine.runner
+    assert runner.check_writes
+    toks = np.arange(20, dtype=np.int32)
+    first = cache.open()
+    cache.reserve(first, 20)
+    runner.step([StepItem(first, 0, toks, ())])
+    cache.advance(first, 20)
+    assert cache.publish(first, toks) == 1                      # the full page is the prefix tree's now
+    matched, pages = cache.match_prefix(toks[:-1])
+    assert matched == 16
+    second = cache.open()
+    cache.adopt(second, pages, 8)                               # wrong on purpose: the page holds 16 tokens, not 8
+    cache.reserve(second, 20)
+    with pytest.raises(EngineError, match="belongs to the prefix cache"):
+        runner.step([StepItem(second, 8, toks[8:], ())])
+    runner.check_writes = False                                 # without the check the step would have run
+    cache.close(second)
+    cache.close(first)
+    cache.check()

@@ -827,3 +827,18 @@ def test_gemm_tcgen05_gated(m, inter, k):
     want = torch.nn.functional.silu(y[:, :inter]) * y[:, inter:]
     assert got.shape == (m, inter)
     assert torch.allclose(got.double(), want, rtol=3e-2, atol=3e-2), float((got.double() - want).abs().max())
+
+
+def test_a_bounded_wait_that_runs_out_gives_up_and_says_so():
+    """The tensor-core kernels wait on mbarriers through one bounded primitive.  Its give-up path runs here on a
+    barrier that nobody arrives at, with a limit of a few hundred polls, in a kernel of one warp that has nothing in
+    flight: the wait returns false, raises the abort flag and leaves its caller's code in the status word, which the
+    host reads and finds cleared afterwards.  The product kernels' own status words stay untouched."""
+    from prefixserve_b200.ops import library
+    assert library.tcgen05_status() == 0
+    out = torch.full((3,), -1, dtype=torch.int32, device=DEV)
+    for limit, who in ((256, 7), (1000, 42)):
+        library.check(library.lib().psb_selftest_bounded_wait(limit, who, out.data_ptr(), library.stream_handle()), "selftest")
+        assert out.tolist() == [0, 1, who]
+    assert library.tcgen05_status() == 0                       # not the product kernels' word
+    assert library.lib().psb_selftest_bounded_wait(1 << 20, 1, out.data_ptr(), None) != 0   # long waits are refused

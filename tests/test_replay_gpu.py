@@ -45,9 +45,13 @@ def truth(folders):
     return out
 
 
-def replay(folder, dtype, steps, max_tokens=None):
+def replay(folder, dtype, steps, max_tokens=None, poison=False):
     from prefixserve_b200.engine.replay import Replayer
     rp = Replayer(folder, dtype, max_tokens or helpers.peak_tokens(steps))
+    rp.cache.poison_freed = poison
+    if poison:
+        for kv in rp.cache.kv:
+            kv.fill_(float("nan"))   # pages nobody has written yet are as void as pages given back
     outputs = {}
     for st in steps:
         out = rp.run_step(st)
@@ -155,11 +159,37 @@ def test_cuttings_agree_in_float32(folders):
             assert float((row - other[key]).abs().max()) <= 2e-5 * float(row.abs().max()), (kind, key)
 
 
-def test_pages_are_reused_in_mixed_trace(folders):
-    seqs = sequences("B")
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", ["B", "D"])
+def test_pages_are_reused_in_mixed_trace(folders, truth, which, dtype):
+    """A pool smaller than all requests together: pages of finished requests come back to later ones.  Every page is
+    filled with NaN the moment it is given back (and before its first use), so a request that reads anything but what
+    it wrote itself shows at once; the logits must be those of the plain implementation."""
+    seqs = sequences(which)
     steps = helpers.trace_mixed(seqs, max_live=2, seed=3)
     total = sum(-(-len(t) // 64) * 64 for t in seqs.values())
     assert helpers.peak_tokens(steps) < total  # the pool is smaller than all requests together
+    from prefixserve_b200.engine.replay import Replayer
+    pages_used: dict[int, set] = {}
+    rp_probe = Replayer(folders[which], dtype, helpers.peak_tokens(steps))
+    for st in steps:   # the same trace, watched: some page serves two requests in turn
+        rp_probe.run_step(st)
+        for rid, slot in rp_probe.slot_of.items():
+            for pg in rp_probe.cache.page_ids(slot):
+                pages_used.setdefault(pg, set()).add(rid)
+    assert any(len(owners) > 1 for owners in pages_used.values()), "no page was used again"
+    rows = replay(folders[which], dtype, steps, poison=True)
+    cfg, tensors = plain_model.read_folder(folders[which])
+    for rid, toks in seqs.items():
+        got = torch.stack([rows[(rid, p)] for p in range(len(toks))])
+        want = truth[which][rid]
+        assert torch.isfinite(got).all(), f"{rid}: read a page it does not own"
+        if dtype == "float32":
+            assert float((got - want).abs().max()) <= 1e-4 * float(want.abs().max()), rid
+        else:
+            plain_bf16 = plain_model.forward(cfg, tensors, toks, dtype=torch.bfloat16)
+            ours, theirs = helpers.rel_err(got, want), helpers.rel_err(plain_bf16, want)
+            assert ours < 0.15 and ours <= 1.5 * theirs + 1e-3, (rid, ours, theirs)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

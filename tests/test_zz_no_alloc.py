@@ -4,8 +4,9 @@ Some embedders cannot call cudaMalloc around a decode step: a host process with 
 running inside another component's stream capture, C callers without a caching allocator.  For them the library keeps
 the split-KV scratch in a fixed 4 MiB array of its own.  This test drives that entry point with ctypes exactly as a C
 caller would, twice in a row on different inputs (the array keeps the previous call's contents), and compares with the
-entry point that takes a caller-provided scratch buffer.  It also checks that a request beyond the fixed size is
-refused without launching.
+entry point that takes a caller-provided scratch buffer and with a float32 attention written in plain torch over the
+pages gathered by the table (the two entry points share their kernels, so agreement between them alone would let a
+fault of both pass).  It also checks that a request beyond the fixed size is refused without launching.
 
 The file name makes pytest collect it last, so a failure here cannot hide the result of any other test.
 """
@@ -67,6 +68,21 @@ def _run(lib, pr, chunk, static):
     return out
 
 
+def _plain_attention(pr):
+    """softmax(q k^T / sqrt(D)) v per request in float32, keys and values gathered page by page through the table."""
+    b, hq, hkv, d, page = pr["b"], pr["hq"], pr["hkv"], pr["d"], pr["page"]
+    kv, table, q = pr["kv"].float().cpu(), pr["table"].cpu(), pr["q"].float().cpu()
+    out = torch.empty(b, hq * d)
+    for i, n in enumerate(pr["kv_len"].tolist()):
+        pages = kv[table[i].long()]                                            # [pages, 2, hkv, page, D]
+        keys = pages[:, 0].permute(0, 2, 1, 3).reshape(-1, hkv, d)[:n]           # [n, hkv, D] in position order
+        vals = pages[:, 1].permute(0, 2, 1, 3).reshape(-1, hkv, d)[:n]
+        keys, vals = keys.repeat_interleave(hq // hkv, dim=1), vals.repeat_interleave(hq // hkv, dim=1)
+        probs = torch.softmax(torch.einsum("hd,nhd->hn", q[i], keys) / d ** 0.5, dim=-1)
+        out[i] = torch.einsum("hn,nhd->hd", probs, vals).reshape(hq * d)
+    return out
+
+
 def test_static_scratch_entry_point_matches_the_allocating_one_twice_in_a_row():
     lib = _library()
     # two different problems back to back: the second call finds the first call's partial results in the array
@@ -76,6 +92,9 @@ def test_static_scratch_entry_point_matches_the_allocating_one_twice_in_a_row():
         got = _run(lib, pr, chunk, static=True)
         assert torch.isfinite(got.float()).all()
         assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+        plain = _plain_attention(pr)
+        assert torch.allclose(got.float().cpu(), plain, atol=2e-2, rtol=2e-2), float((got.float().cpu() - plain).abs().max())
+        assert torch.allclose(want.float().cpu(), plain, atol=2e-2, rtol=2e-2)
 
 
 def test_static_scratch_entry_point_refuses_what_does_not_fit():
