@@ -159,6 +159,20 @@ def host_only_cache(num_blocks: int, *, page_size: int = 16, num_slots: int = 25
                         enable_prefix_cache=enable_prefix_cache)
 
 
+class _StepPlan:
+    """What schedule_step is putting together: the work so far, who was preempted for it, the prompt tokens left."""
+
+    def __init__(self, budget: int) -> None:
+        self.work: list[WorkItem] = []
+        self.preempted: list[str] = []
+        self.budget = budget
+
+    def take(self, item: WorkItem, is_prompt: bool) -> None:
+        if is_prompt:  # single decoded tokens are free; portions of prompts (and recomputation) pay
+            self.budget -= item.end - item.start
+        self.work.append(item)
+
+
 class Scheduler:
     def __init__(
         self,
@@ -191,16 +205,16 @@ class Scheduler:
     # ------------------------------------------------------------ interface
     def add_request(self, req_id: str, prompt, max_tokens: int, *, ignore_eos: bool = False,
                     sampling: SamplingParams | None = None) -> AddResult:
-        checked = self._vet(req_id, prompt, max_tokens)
-        if isinstance(checked, AddResult):
+        verdict, tokens = self._vet(req_id, prompt, max_tokens)
+        if verdict is not AddResult.ACCEPTED:
             self._n_rejected += 1
-            return checked
-        req = Request(req_id, checked, max_tokens, self._arrivals, ignore_eos, sampling or SamplingParams())
+            return verdict
+        req = Request(req_id, tokens, max_tokens, self._arrivals, ignore_eos, sampling or SamplingParams())
         self._arrivals += 1
         self._by_id[req_id] = req
         self._waiting.append(req)
-        self._n_prompt += len(checked)
-        return AddResult.ACCEPTED
+        self._n_prompt += len(tokens)
+        return verdict
 
     def schedule_step(self, max_prefill_tokens: int, max_decode_seqs: int) -> Batch:
         if self._inflight is not None:
@@ -208,39 +222,11 @@ class Scheduler:
         if max_prefill_tokens < 1 or max_decode_seqs < 1:
             raise ValueError("max_prefill_tokens and max_decode_seqs must be >= 1")  # 0 would stall prompts forever
         t0 = time.perf_counter()
-        work: list[WorkItem] = []
-        preempted: list[str] = []
-        budget = max_prefill_tokens
-
-        # Running requests, oldest first.  Victims of preemption are always
-        # newer than the asker, so they are never in `work` yet.
-        at = 0
-        while at < len(self._running):
-            req = self._running[at]
-            n = self._portion(req.seq_len - req.num_computed, budget)
-            if n == 0:
-                at += 1
-                continue
-            if not self._secure(req, req.num_computed + n, preempted):
-                continue  # req itself was preempted and left the list; `at` now names the next one
-            if req.seq_len - req.num_computed > 1:
-                budget -= n
-            work.append(WorkItem(req, req.num_computed, req.num_computed + n))
-            at += 1
-
-        # Newcomers, in order of arrival.
-        while self._waiting and len(self._running) < max_decode_seqs:
-            item = self._start(self._waiting[0], budget)
-            if item is None:
-                break
-            self._waiting.popleft()
-            if item.end - item.start > 1:
-                budget -= item.end - item.start
-            work.append(item)
-
-        batch = Batch(work, preempted)
-        self._inflight = batch
-        self._ahead = None
+        plan = _StepPlan(max_prefill_tokens)
+        self._plan_running(plan)
+        self._plan_admissions(plan, max_decode_seqs)
+        batch = Batch(plan.work, plan.preempted)
+        self._inflight, self._ahead = batch, None
         took = time.perf_counter() - t0
         if took > SLOW_STEP_SECONDS:
             log.debug("schedule_step took %.2f ms", took * 1e3)
@@ -287,30 +273,21 @@ class Scheduler:
                 continue  # it ended with the step before (a stop token): what this step computed for it is dropped
             if req.num_computed != w.start:
                 raise SchedulerError(f"{req.req_id}: the batch is stale")
-            samples = w.samples
+            sampling = w.samples  # asked before the count moves: it compares the item's end with the sequence length
             req.num_computed = w.end
             self.cache.advance(req.slot, w.end)
-            if not samples:
+            if not sampling:
                 continue
-            if req.req_id not in sampled:
-                raise SchedulerError(f"no token was returned for {req.req_id}")
-            token = int(sampled[req.req_id])
-            if not req.prompt_cached:  # prompt complete for the first time: others may share it from now on
-                self._publish(req)
-                req.prompt_cached = True
-            req.output.append(token)
+            try:
+                token = int(sampled[req.req_id])
+            except KeyError:
+                raise SchedulerError(f"no token was returned for {req.req_id}") from None
             new_tokens[req.req_id] = token
-            if req.abort_pending:
-                continue
-            if (token in self._stop or token in req.sampling.stop_token_ids) and not req.ignore_eos:
-                reason = FinishReason.STOP
-            elif len(req.output) >= req.max_tokens:
-                reason = FinishReason.LENGTH
-            else:
-                continue
-            self._retire(req)
-            finished[req.req_id] = reason
-        for req in self._abort_at_commit:
+            reason = self._take_token(req, token)
+            if reason is not None:
+                self._retire(req)
+                finished[req.req_id] = reason
+        for req in self._abort_at_commit:  # aborts that had to wait because the batch could still write their pages
             if req.state is ReqState.RUNNING:
                 self._retire(req)
                 finished[req.req_id] = FinishReason.ABORT
@@ -331,17 +308,15 @@ class Scheduler:
         req = self._by_id.get(req_id)
         if req is None or req.abort_pending:
             return False
-        if req.state is ReqState.WAITING:
+        if req.state is ReqState.RUNNING and self._inflight is not None:
+            req.abort_pending = True  # the batch in flight may still write into its pages: ended at the commit
+            self._abort_at_commit.append(req)
+        elif req.state is ReqState.RUNNING:
+            self._retire(req)
+        else:  # waiting: it holds nothing
             self._waiting.remove(req)
             req.state = ReqState.FINISHED
             del self._by_id[req_id]
-            return True
-        if self._inflight is not None:
-            # the batch in flight may still write into its pages
-            req.abort_pending = True
-            self._abort_at_commit.append(req)
-            return True
-        self._retire(req)
         return True
 
     def get_request(self, req_id: str) -> Request | None:
@@ -365,36 +340,79 @@ class Scheduler:
             rejected=self._n_rejected,
         )
 
-    # ------------------------------------------------------------ decisions
+    # ------------------------------------------------------------ one step
     def _portion(self, remaining: int, budget: int) -> int:
+        """How many of a request's uncomputed tokens run now: its one decoded token whatever the budget says,
+        otherwise as much of the tail as the portion limit and the step's budget allow (0: it waits a step)."""
         return 1 if remaining == 1 else min(self._chunk, remaining, budget)
 
-    def _vet(self, req_id, prompt, max_tokens):
-        if not req_id or not isinstance(max_tokens, int) or isinstance(max_tokens, bool) or max_tokens < 1:
-            return AddResult.INVALID
-        try:
-            arr = np.asarray(prompt)
-        except (TypeError, ValueError, OverflowError):
-            return AddResult.INVALID
-        if arr.ndim != 1 or arr.size == 0 or arr.dtype.kind not in "iu":
-            return AddResult.INVALID
-        if int(arr.min()) < 0 or int(arr.max()) > np.iinfo(np.int32).max:
-            return AddResult.INVALID
-        if req_id in self._by_id:
-            return AddResult.DUPLICATE_ID
+    def _plan_running(self, plan: _StepPlan) -> None:
+        """The requests that already run, oldest first.  One that needs pages takes them from the newest running
+        request; a victim is always newer than the asker, so it has no work in the plan yet."""
+        for req in list(self._running):
+            if req.state is not ReqState.RUNNING:
+                continue  # preempted a moment ago for an older request
+            remaining = req.seq_len - req.num_computed
+            n = self._portion(remaining, plan.budget)
+            if n and self._secure(req, req.num_computed + n, plan.preempted):
+                plan.take(WorkItem(req, req.num_computed, req.num_computed + n), is_prompt=remaining > 1)
+
+    def _plan_admissions(self, plan: _StepPlan, max_running: int) -> None:
+        """Newcomers in order of arrival, while there is room to run them; the first that cannot start holds up the rest."""
+        while self._waiting and len(self._running) < max_running:
+            item = self._start(self._waiting[0], plan.budget)
+            if item is None:
+                return
+            self._waiting.popleft()
+            plan.take(item, is_prompt=item.end - item.start > 1)
+
+    def _take_token(self, req: Request, token: int) -> FinishReason | None:
+        """Appends a sampled token; says why the request ends with it, if it does."""
+        if not req.prompt_cached:  # prompt complete for the first time: others may share it from now on
+            self._publish(req)
+            req.prompt_cached = True
+        req.output.append(token)
+        if req.abort_pending:
+            return None  # ended below, with the other deferred aborts
+        stops = not req.ignore_eos and (token in self._stop or token in req.sampling.stop_token_ids)
+        if stops:
+            return FinishReason.STOP  # the stop token itself is kept
+        return FinishReason.LENGTH if len(req.output) >= req.max_tokens else None
+
+    # ------------------------------------------------------------ admission control
+    def _vet(self, req_id, prompt, max_tokens) -> tuple[AddResult, np.ndarray | None]:
+        """(verdict, the prompt as an int32 array of our own).  A request is refused if it is malformed, if its id is
+        in use, if it could not fit even alone (too many positions, or more pages than a group has: every page in a
+        group that keeps all keys; the window, a portion and a page of slack in one that keeps a window), or if the
+        queue is full.  The checks run in that order and the first that fails names the verdict."""
+        arr = None
+        if isinstance(req_id, str) and req_id and type(max_tokens) is int and max_tokens >= 1:
+            try:
+                arr = np.asarray(prompt)
+            except (TypeError, ValueError, OverflowError):
+                arr = None
+        well_formed = (arr is not None and arr.ndim == 1 and arr.size > 0 and arr.dtype.kind in "iu"
+                       and int(arr.min()) >= 0 and int(arr.max()) <= np.iinfo(np.int32).max)
+        if not well_formed:
+            return AddResult.INVALID, None
         total = int(arr.size) + max_tokens
         page = self.cache.page_size
-        # what the request holds at its largest: every page in a group of full attention; in a group with a window
-        # the window, the portion being computed and the page the window's start lies in
-        too_many_pages = any(
-            (pages_for(total, page) if g.window is None else min(pages_for(total, page), pages_for(g.window + self._chunk, page) + 1))
-            > g.pool.num_blocks for g in self.cache.groups)
-        if too_many_pages or total > self.cache.max_seq_len:
-            return AddResult.TOO_LONG
-        if len(self._waiting) >= self._max_waiting:
-            return AddResult.QUEUE_FULL
-        return arr.astype(np.int32)  # a copy: later changes by the caller do not reach us
 
+        def most_pages(g) -> int:
+            whole = pages_for(total, page)
+            return whole if g.window is None else min(whole, pages_for(g.window + self._chunk, page) + 1)
+
+        checks = (
+            (req_id in self._by_id, AddResult.DUPLICATE_ID),
+            (total > self.cache.max_seq_len or any(most_pages(g) > g.pool.num_blocks for g in self.cache.groups), AddResult.TOO_LONG),
+            (len(self._waiting) >= self._max_waiting, AddResult.QUEUE_FULL),
+        )
+        for failed, verdict in checks:
+            if failed:
+                return verdict, None
+        return AddResult.ACCEPTED, arr.astype(np.int32)  # a copy: later changes by the caller do not reach us
+
+    # ------------------------------------------------------------ pages
     def _take_pages(self, req: Request, upto: int) -> bool:
         """reserve, evicting unused cached pages if that is what it takes."""
         if self.cache.reserve(req.slot, upto):
@@ -406,6 +424,8 @@ class Scheduler:
         return self.cache.reserve(req.slot, upto)
 
     def _secure(self, req: Request, upto: int, preempted: list[str]) -> bool:
+        """Pages for a running request, taken from the newest running one for as long as that is what it takes.
+        False: the request ended up preempting itself."""
         while not self._take_pages(req, upto):
             victim = self._running[-1]
             self._preempt(victim)
@@ -415,8 +435,9 @@ class Scheduler:
         return True
 
     def _start(self, req: Request, budget: int) -> WorkItem | None:
+        """Admits the head of the queue with its first portion, or leaves everything as it was."""
         seq = req.seq()
-        # keep at least the last token to compute: its logits are what we are after
+        # all but the last token may come from the prefix cache: the last one's logits are what the request is after
         matched, pages = self.cache.match_prefix(seq[:-1]) if self._share_prefixes else (0, [])
         n = self._portion(len(seq) - matched, budget)
         slot = self.cache.open() if n > 0 else None
@@ -443,22 +464,24 @@ class Scheduler:
         if self._share_prefixes and req.num_computed >= self.cache.page_size:
             self.cache.publish(req.slot, req.seq()[: req.num_computed])
 
-    def _preempt(self, req: Request) -> None:
-        # recompute, not swap; what it computed stays findable in the prefix cache
+    def _leave_running(self, req: Request) -> None:
+        """What ending and preempting share: full pages to the prefix tree, slot and pages back."""
         self._publish(req)
         self.cache.close(req.slot)
         req.slot = None
+        self._running.remove(req)
+
+    def _preempt(self, req: Request) -> None:
+        """Recomputation, not swapping: the request starts over at the front of the queue; what it had computed
+        stays findable in the prefix cache."""
+        self._leave_running(req)
         req.num_computed = 0
         req.num_preemptions += 1
         req.state = ReqState.WAITING
-        self._running.remove(req)
         self._waiting.appendleft(req)
         self._n_preempt += 1
 
     def _retire(self, req: Request) -> None:
-        self._publish(req)
-        self.cache.close(req.slot)
-        req.slot = None
+        self._leave_running(req)
         req.state = ReqState.FINISHED
-        self._running.remove(req)
         del self._by_id[req.req_id]

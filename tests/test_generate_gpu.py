@@ -290,3 +290,40 @@ def test_the_step_function_refuses_to_write_into_a_cached_page(sharp):
     cache.close(second)
     cache.close(first)
     cache.check()
+
+
+def test_the_first_command_of_the_readme_runs_as_written():
+    """README.md's first line: a random-weights preset, default flags (the sequence limit then follows the model's
+    own 256 positions, not the 8192 the reference defaults to)."""
+    readme = (ROOT / "README.md").read_text()
+    line = next(ln for ln in readme.splitlines() if ln.startswith("python -m prefixserve_b200 --random-config"))
+    cmd = line.split("#")[0].split()
+    assert cmd[:3] == ["python", "-m", "prefixserve_b200"]
+    proc = subprocess.run([sys.executable] + cmd[1:], capture_output=True, text=True, cwd=ROOT, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = [json.loads(ln) for ln in proc.stdout.splitlines() if ln.startswith("{")]
+    assert lines[0]["prompt_ids"] == [5, 17, 3] and len(lines[0]["output_ids"]) >= 1
+    assert lines[1]["stats"]["num_running"] == 0
+
+
+def test_replay_sub_command_and_per_request_stop_ids(sharp, tmp_path):
+    """``python -m prefixserve_b200 replay`` is the trace program; ``--stop-token-ids`` ends a request on an id of its own."""
+    folder, (cfg, tensors) = sharp
+    prompt = [3, 1, 4, 1, 5, 9, 2, 6]
+    want = plain_model.greedy(cfg, tensors, prompt, 6)
+    stop = want[3]
+    cmd = [sys.executable, "-m", "prefixserve_b200", "--model", str(folder), "--dtype", "float32", "--num-blocks", "16",
+           "--max-running-requests", "2", "--chunked-prefill-size", "16", "--max-tokens", "6", "--stop-token-ids", str(stop),
+           "--prompt-ids", ",".join(map(str, prompt))]
+    proc = subprocess.run(cmd, capture_output=True, text=True, cwd=ROOT, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    got = json.loads(next(ln for ln in proc.stdout.splitlines() if ln.startswith("{")))["output_ids"]
+    assert got == want[: want.index(stop) + 1]
+    trace = json.dumps({"step": 0, "entries": [{"id": "a", "tokens": prompt, "want": [7]}], "end": ["a"]}) + "\n"
+    out = tmp_path / "out"
+    cmd = [sys.executable, "-m", "prefixserve_b200", "replay", "--model", str(folder), "--dtype", "float32", "--out", str(out),
+           "--max-tokens", "64"]
+    proc = subprocess.run(cmd, input=trace, capture_output=True, text=True, cwd=ROOT, timeout=900)
+    assert proc.returncode == 0 and "done 0" in proc.stdout, proc.stderr[-2000:]
+    row = torch.from_numpy(np.fromfile(out / "0.f32", dtype="<f4").copy())
+    assert int(row.argmax()) == want[0]
