@@ -63,60 +63,79 @@ def peaks() -> dict:
 
 
 # ------------------------------------------------------------------ model folder
-def write_model_folder(folder: Path, layers: int, seed: int = 0, model: dict | None = None) -> None:
-    """config.json + model.safetensors with N(0, 0.02) bfloat16 weights, written with torch and safetensors only
-    (both arms read this folder through their own loaders).  ``model``: config.json contents (default: the 1B sizes)."""
+def write_own_folder(folder: Path, layers: int, seed: int = 0, model: dict | None = None) -> None:
+    """The engine's random-weights mode: config.json + model.safetensors, N(0, 0.02) bfloat16, drawn on the GPU."""
+    import torch
+
+    from prefixserve_b200.config import LlamaConfig
+    from prefixserve_b200.weights import write_random_model
+    cfg = LlamaConfig.from_dicts(dict(model or MODEL, num_hidden_layers=layers))
+    write_random_model(folder, cfg, seed, std=0.02, dtype=torch.bfloat16, device="cuda")
+
+
+def write_reference_folder(folder: Path, layers: int, seed: int = 0) -> None:
+    """The same kind of folder for the reference arm, written with torch and safetensors alone: no code of this
+    repository's package runs on that arm, not even to make its weights."""
     import torch
     from safetensors.torch import save_file
 
-    cfg = dict(model or MODEL, num_hidden_layers=layers)
+    cfg = dict(MODEL, num_hidden_layers=layers)
     h, i, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
-    q = cfg["num_attention_heads"] * cfg["head_dim"]
-    kv = cfg["num_key_value_heads"] * cfg["head_dim"]
+    q, kv = cfg["num_attention_heads"] * cfg["head_dim"], cfg["num_key_value_heads"] * cfg["head_dim"]
     gen = torch.Generator(device="cuda")
     gen.manual_seed(seed)
 
     def mat(*shape):
         return (torch.randn(shape, device="cuda", generator=gen, dtype=torch.float32) * 0.02).to(torch.bfloat16).cpu()
 
-    tensors = {"model.embed_tokens.weight": mat(v, h), "model.norm.weight": torch.ones(h, dtype=torch.bfloat16)}
+    ones = torch.ones(h, dtype=torch.bfloat16)
+    tensors = {"model.embed_tokens.weight": mat(v, h), "model.norm.weight": ones.clone()}
     for n in range(layers):
-        p = f"model.layers.{n}."
-        tensors[p + "input_layernorm.weight"] = torch.ones(h, dtype=torch.bfloat16)
-        tensors[p + "post_attention_layernorm.weight"] = torch.ones(h, dtype=torch.bfloat16)
-        tensors[p + "self_attn.q_proj.weight"] = mat(q, h)
-        tensors[p + "self_attn.k_proj.weight"] = mat(kv, h)
-        tensors[p + "self_attn.v_proj.weight"] = mat(kv, h)
-        tensors[p + "self_attn.o_proj.weight"] = mat(h, q)
-        tensors[p + "mlp.gate_proj.weight"] = mat(i, h)
-        tensors[p + "mlp.up_proj.weight"] = mat(i, h)
-        tensors[p + "mlp.down_proj.weight"] = mat(h, i)
-    if not cfg.get("tie_word_embeddings", False):
-        tensors["lm_head.weight"] = mat(v, h)
+        pre = f"model.layers.{n}."
+        tensors[pre + "input_layernorm.weight"] = ones.clone()
+        tensors[pre + "post_attention_layernorm.weight"] = ones.clone()
+        for name, shape in (("self_attn.q_proj", (q, h)), ("self_attn.k_proj", (kv, h)), ("self_attn.v_proj", (kv, h)),
+                            ("self_attn.o_proj", (h, q)), ("mlp.gate_proj", (i, h)), ("mlp.up_proj", (i, h)),
+                            ("mlp.down_proj", (h, i))):
+            tensors[pre + name + ".weight"] = mat(*shape)
     folder.mkdir(parents=True, exist_ok=True)
     save_file(tensors, str(folder / "model.safetensors"), metadata={"format": "pt"})
     (folder / "config.json").write_text(json.dumps(cfg))
-
-
-def weight_bytes(layers: int) -> int:
-    h, i, v = MODEL["hidden_size"], MODEL["intermediate_size"], MODEL["vocab_size"]
-    q = MODEL["num_attention_heads"] * MODEL["head_dim"]
-    kv = MODEL["num_key_value_heads"] * MODEL["head_dim"]
-    per_layer = (q + 2 * kv) * h + h * q + 3 * h * i + 2 * h
-    return 2 * (v * h + layers * per_layer + h)  # the tied table is read once (as the LM head)
 
 
 def kv_bytes_per_token(layers: int) -> int:
     return layers * 2 * MODEL["num_key_value_heads"] * MODEL["head_dim"] * 2
 
 
-def prefill_flops(t: int, layers: int) -> float:
+def prefill_flops(t: int, layers: int, prefix: int = 0) -> float:
+    """Flops of a step that computes t tokens of one request over ``prefix`` cached ones and the last row's logits."""
     h, i, v = MODEL["hidden_size"], MODEL["intermediate_size"], MODEL["vocab_size"]
     q = MODEL["num_attention_heads"] * MODEL["head_dim"]
     kv = MODEL["num_key_value_heads"] * MODEL["head_dim"]
-    gemm = 2.0 * t * layers * (h * (q + 2 * kv) + q * h + 3 * h * i) + 2.0 * h * v  # logits for the last row only
-    attn = layers * 2.0 * t * (t + 1) * MODEL["head_dim"] * MODEL["num_attention_heads"]  # QK^T and PV, causal
+    gemm = 2.0 * t * layers * (h * (q + 2 * kv) + q * h + 3 * h * i) + 2.0 * h * v
+    attn = layers * 4.0 * t * (prefix + (t + 1) / 2) * q   # QK^T and PV, causal
     return gemm + attn
+
+
+def config_block(layers: int, batch: int, **more) -> dict:
+    """The ``config`` of the JSON line: the same keys on both arms (flat, every size named)."""
+    out = {
+        "model": "Llama-3.2-1B sizes", "layers": layers, "layers_full": FULL_LAYERS, "hidden": MODEL["hidden_size"],
+        "heads": MODEL["num_attention_heads"], "kv_heads": MODEL["num_key_value_heads"], "head_dim": MODEL["head_dim"],
+        "intermediate": MODEL["intermediate_size"], "vocab": MODEL["vocab_size"], "tied": True,
+        "global_batch": batch, "seq_len": CONTEXT, "page_size": PAGE, "prefill_tokens": PREFILL_TOKENS,
+        "parallelism": "single-gpu", "l2": "inputs larger than L2 (every step reads 2.47 GB of weights)",
+    }
+    out.update(more)
+    return out
+
+
+def e2e_request_shape(batch: int, steps: int, warmup: int) -> tuple[int, int]:
+    """(prompt tokens, tokens to generate) of the end-to-end workload.  Prompts are admitted two steps apart (the
+    budget is one 2,048-token portion a step), so the first request has decoded about 2 * batch tokens when the last
+    one starts; every request must still be alive at the last timed step and end at the benchmark's context."""
+    generate = warmup + steps + 2 * batch + 4
+    return CONTEXT - generate, generate
 
 
 # ------------------------------------------------------------------------ clocks
@@ -164,31 +183,84 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------- own arm
+def drive_e2e(engine, sched, batch: int, steps: int, warmup: int, rng, vocab: int, tag: str) -> dict:
+    """``batch`` requests through scheduler -> engine.launch/finish -> commit, as the entry point's loop does (while a
+    step runs, the one after it is scheduled and launched if that can be done without its tokens; every step's
+    tokens are read back before its commit).  Timed by the host's clock over exactly ``steps`` full decode steps
+    after ``warmup`` of them; every timed step copies its inputs from pinned host memory and reads its tokens back."""
+    import numpy as np
+    import torch
+    runner = engine.runner
+    prompt_len, generate = e2e_request_shape(batch, steps, warmup)
+    for r in range(batch):
+        sched.add_request(f"{tag}-{r}", rng.randint(0, vocab, size=prompt_len), generate, ignore_eos=True)
+    decoding = produced = timed = 0
+    t_start = None
+    h2d, marks = [], []
+    pending = None
+    first_h2d = 0
+    while (pending is not None or sched.has_work()) and timed < steps:
+        if pending is None:
+            pending = engine.launch(sched.schedule_step(PREFILL_TOKENS, batch))
+            first_h2d = runner.last_h2d_bytes
+        ahead = sched.schedule_ahead(batch)
+        following = engine.launch(ahead, feed=pending) if ahead is not None else None
+        work = pending.batch.work
+        if all(w.end - w.start == 1 for w in work) and len(work) == batch:
+            decoding += 1
+            if decoding == warmup + 1:
+                torch.cuda.synchronize()
+                t_start = time.perf_counter()
+        out = engine.finish(pending)
+        if t_start is not None:
+            produced += len(out)
+            timed += 1
+            h2d.append(runner.last_h2d_bytes if following is not None else first_h2d)
+        sched.commit(pending.batch, out)
+        if t_start is not None:
+            marks.append(time.perf_counter())
+        pending = following
+        first_h2d = runner.last_h2d_bytes
+    if pending is not None:
+        sched.commit(pending.batch, engine.finish(pending))
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t_start
+    for r in range(batch):
+        sched.free_request(f"{tag}-{r}")
+    if produced != batch * steps:
+        raise RuntimeError(f"end-to-end region produced {produced} tokens in {timed} steps, not {batch} x {steps}")
+    return {"value": round(produced / wall, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(sum(h2d) / max(len(h2d), 1)),
+            "d2h_bytes_per_step": 4 * batch, "steps": timed, "tokens": produced, "ms_per_step": round(1e3 * wall / timed, 4),
+            "ms_per_step_p50": round(1e3 * float(np.median(np.diff(marks))), 4) if len(marks) > 2 else None}
+
+
 def run_own(args) -> dict:
     import numpy as np
     import torch
 
     from prefixserve_b200.engine import Engine, EngineConfig, Scheduler, StepItem
     from prefixserve_b200.ops import library
-    from prefixserve_b200.sampling import SamplingParams
     from prefixserve_b200.sampling.sampler import choose_tokens
 
     pk = peaks()
     layers = args.layers
     work = Path(tempfile.mkdtemp(prefix="psb200-bench-"))
     try:
-        write_model_folder(work, layers)
+        write_own_folder(work, layers)
         rng = np.random.RandomState(0)
         vocab = MODEL["vocab_size"]
-        max_b = max(args.batch, 64 if not args.skip_points else args.batch)
-        pool = max_b * (CONTEXT // PAGE) + 64
         if args.only != "all":
             args.skip_points = True
+        max_b = max(args.batch, 64 if not args.skip_points else args.batch)
+        pool = max_b * (CONTEXT // PAGE) + 64
         engine = Engine(EngineConfig(model_path=work, dtype=torch.bfloat16, max_num_seqs=max_b, max_prefill_tokens=PREFILL_TOKENS,
                                      max_seq_len=CONTEXT, num_blocks=pool, page_size=PAGE, enable_prefix_cache=False,
                                      use_cuda_graphs=not args.no_graphs))
         runner, cache = engine.runner, engine.cache
-        greedy = SamplingParams()
+        weights = engine.weight_bytes()  # what a decode step reads of them: every tensor once, the tied table once
+
+        def sample(logits) -> None:
+            choose_tokens(logits, cache.records_dev, runner.last_row_slots)
 
         def fill(batch: int, upto: int) -> list[int]:
             """Opens ``batch`` requests and prefills each to ``upto`` tokens through the step function."""
@@ -212,8 +284,7 @@ def run_own(args) -> dict:
                     p = cache.position(s)
                     cache.reserve(s, p + 1)
                     items.append(StepItem(s, p, rng.randint(0, vocab, size=1).astype(np.int32), (0,)))
-                logits = runner.step(items)
-                choose_tokens(logits, cache.records_dev, runner.last_row_slots)
+                sample(runner.step(items))
                 for it in items:
                     cache.advance(it.slot, it.start + 1)
 
@@ -241,7 +312,7 @@ def run_own(args) -> dict:
             for _ in range(max(args.steps, 1)):
                 runner.step([StepItem(slot, 0, rng.randint(0, vocab, size=PREFILL_TOKENS).astype(np.int32), (PREFILL_TOKENS - 1,))])
             torch.cuda.synchronize()
-            return {"only": "prefill", "steps": args.steps, "layers": layers}
+            return {"only": "prefill", "steps": args.steps, "layers": layers, "batch": 1, "weight_bytes": weights}
 
         # ---- headline: decode at the default batch, device-timed, clocks sampled meanwhile
         with ClockSampler() as clocks:
@@ -249,105 +320,73 @@ def run_own(args) -> dict:
             ms_step, launches, mean_ctx = time_decode(args.batch, args.steps, args.warmup)
             time.sleep(0.3)
         value = args.batch / (ms_step * 1e-3)
-        step_bytes = weight_bytes(layers) + args.batch * mean_ctx * kv_bytes_per_token(layers)
+        step_bytes = weights + args.batch * mean_ctx * kv_bytes_per_token(layers)
         achieved = step_bytes / (ms_step * 1e-3) / 1e9
         if args.only == "decode":
             return {"only": "decode", "value": round(value, 1), "ms_per_step": round(ms_step, 4), "layers": layers,
-                    "batch": args.batch, "gpu_launches": launches}
+                    "batch": args.batch, "gpu_launches": launches, "weight_bytes": weights, "mean_context": mean_ctx}
 
-        # ---- end to end through the scheduler and engine.step (host tokens in and out)
-        engine.capture_decode_graphs(range(1, args.batch + 1))  # as the entry point does at start-up
+        # ---- end to end through the scheduler and engine.launch/finish (host tokens in and out)
+        engine.capture_decode_graphs(range(1, max_b + 1))  # as the entry point does at start-up
         sched = Scheduler(cache, chunk_size=PREFILL_TOKENS, stop_token_ids=())
-        total = args.steps + args.warmup
-        for r in range(args.batch):
-            # prompts end so that the timed steps finish at CONTEXT; the staggered prefill costs a few decode steps
-            sched.add_request(f"e2e-{r}", rng.randint(0, vocab, size=CONTEXT - total - args.batch - 2),
-                              total + args.batch + 2, ignore_eos=True)
-        decoding = produced = e2e_steps = 0
-        t_start = None
-        h2d = []
-        marks = []
-        # the loop of the entry point (LLM.generate): while a step runs, the one after it is scheduled and launched
-        # if that can be done without its tokens; every step's tokens are read back before its commit
-        pending = None
-        while (pending is not None or sched.has_work()) and e2e_steps < args.steps:
-            if pending is None:
-                pending = engine.launch(sched.schedule_step(PREFILL_TOKENS, args.batch))
-                first_h2d = runner.last_h2d_bytes
-            ahead = sched.schedule_ahead(args.batch)
-            following = engine.launch(ahead, feed=pending) if ahead is not None else None
-            batch = pending.batch
-            is_decode = all(w.end - w.start == 1 for w in batch.work) and len(batch.work) == args.batch
-            if is_decode:
-                decoding += 1
-                if decoding == args.warmup + 1:
-                    torch.cuda.synchronize()
-                    t_start = time.perf_counter()
-            out = engine.finish(pending)
-            if t_start is not None:
-                produced += len(out)
-                e2e_steps += 1
-                h2d.append(runner.last_h2d_bytes if following is not None else first_h2d)
-            sched.commit(batch, out)
-            if t_start is not None:
-                marks.append(time.perf_counter())
-            pending = following
-        if pending is not None:
-            sched.commit(pending.batch, engine.finish(pending))
-        torch.cuda.synchronize()
-        e2e_s = time.perf_counter() - t_start
-        for r in range(args.batch):
-            sched.free_request(f"e2e-{r}")
-        e2e = {"value": round(produced / e2e_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(sum(h2d) / max(len(h2d), 1)),
-               "d2h_bytes_per_step": 4 * args.batch, "steps": e2e_steps, "ms_per_step": round(1e3 * e2e_s / max(e2e_steps, 1), 4),
-               "ms_per_step_p50": round(1e3 * float(np.median(np.diff(marks))), 4) if len(marks) > 2 else None}
+        e2e = drive_e2e(engine, sched, args.batch, args.steps, args.warmup, rng, vocab, "e2e")
 
-        # ---- prefill: one 2,048-token prompt in one step
-        def one_prefill() -> float:
+        # ---- prefill: one 2,048-token prompt in one step, and the same prompt in four portions of 512
+        def one_prefill(portion: int) -> float:
             slot = cache.open()
             cache.reserve(slot, PREFILL_TOKENS)
             toks = rng.randint(0, vocab, size=PREFILL_TOKENS).astype(np.int32)
             t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
             t0.record()
-            logits = runner.step([StepItem(slot, 0, toks, (PREFILL_TOKENS - 1,))])
-            choose_tokens(logits, cache.records_dev, runner.last_row_slots)
+            for at in range(0, PREFILL_TOKENS, portion):
+                last = at + portion == PREFILL_TOKENS
+                logits = runner.step([StepItem(slot, at, toks[at: at + portion], (portion - 1,) if last else ())])
+                cache.advance(slot, at + portion)
+            sample(logits)
             t1.record()
             torch.cuda.synchronize()
             cache.close(slot)
             return t0.elapsed_time(t1)
 
-        for _ in range(3):
-            one_prefill()
-        pf = sorted(one_prefill() for _ in range(10))
-        pf_ms = pf[len(pf) // 2]
+        def median_prefill(portion: int) -> float:
+            for _ in range(3):
+                one_prefill(portion)
+            runs = sorted(one_prefill(portion) for _ in range(10))
+            return runs[len(runs) // 2]
+
+        pf_ms = median_prefill(PREFILL_TOKENS)
         flops = prefill_flops(PREFILL_TOKENS, layers)
         prefill = {"value": round(PREFILL_TOKENS / (pf_ms * 1e-3), 1), "tokens": PREFILL_TOKENS, "ms": round(pf_ms, 4),
                    "frac": round(flops / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4), "peak": f"{pk['bf16_tflops']} TFLOP/s of {pk['source']}"}
+        pc_ms = median_prefill(512)
+        chunk_flops = sum(prefill_flops(512, layers, prefix=at) for at in range(0, PREFILL_TOKENS, 512))
+        prefill["chunked_4x512"] = {"value": round(PREFILL_TOKENS / (pc_ms * 1e-3), 1), "ms": round(pc_ms, 4),
+                                    "frac": round(chunk_flops / (pc_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
 
-        # ---- further points
+        # ---- further points: decode at batch 1 and 64, device-timed and end to end
         points = {}
         if not args.skip_points:
             for b in (1, 64):
-                ms_b, _, _ = time_decode(b, min(args.steps, 64), 3)
+                k = min(args.steps, 64)
+                ms_b, _, ctx_b = time_decode(b, k, 3)
                 points[f"decode_b{b}"] = round(b / (ms_b * 1e-3), 1)
+                points[f"decode_b{b}_hbm_frac"] = round((weights + b * ctx_b * kv_bytes_per_token(layers)) / (ms_b * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+                e = drive_e2e(engine, sched, b, k, 3, rng, vocab, f"e2e-b{b}")
+                points[f"e2e_decode_b{b}"] = e["value"]
+                points[f"e2e_h2d_bytes_b{b}"] = e["h2d_bytes_per_step"]
 
         return {
             "metric": "decode tokens/s at batch 8, context 4096 (Llama-3.2-1B sizes, random weights)",
             "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic: seeded uniform-random token ids, N(0,0.02) random weights",
-            "config": {
-                "model": "Llama-3.2-1B sizes", "layers": layers, "layers_full": FULL_LAYERS, "hidden": MODEL["hidden_size"],
-                "heads": MODEL["num_attention_heads"], "kv_heads": MODEL["num_key_value_heads"], "head_dim": MODEL["head_dim"],
-                "intermediate": MODEL["intermediate_size"], "vocab": MODEL["vocab_size"], "tied": True,
-                "global_batch": args.batch, "seq_len": CONTEXT, "page_size": PAGE, "prefill_tokens": PREFILL_TOKENS,
-                "parallelism": "single-gpu", "l2": "inputs larger than L2 (every step reads 2.47 GB of weights)",
-            },
+            "config": config_block(layers, args.batch),
             "e2e": e2e,
             "prefill": prefill,
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                         "frac": round(achieved / pk["hbm_gbs"], 4), "of": pk["source"], "bytes_per_step": int(step_bytes)},
+                         "frac": round(achieved / pk["hbm_gbs"], 4), "of": pk["source"], "bytes_per_step": int(step_bytes),
+                         "weight_bytes": int(weights)},
             "points": points,
             "clocks": clocks.summary(),
             "gpu_launches": launches,
@@ -384,7 +423,7 @@ def run_shared_prefix(args) -> dict:
     prompts = [prefixes[r % tenants] + rng.randint(0, vocab, size=int(rng.randint(64, 513))).tolist() for r in range(requests)]
     work = Path(tempfile.mkdtemp(prefix="psb200-bench-"))
     try:
-        write_model_folder(work, layers, model=cfg)
+        write_own_folder(work, layers, model=cfg)
         pages = requests * (-(-(prefix_len + 512 + decode_tokens) // PAGE)) + 256
         runs = {}
         for name, enabled in (("prefix_cache", True), ("no_prefix_cache", False)):
@@ -440,7 +479,7 @@ def run_mixed(args) -> dict:
     vocab = cfg["vocab_size"]
     work = Path(tempfile.mkdtemp(prefix="psb200-bench-"))
     try:
-        write_model_folder(work, layers, model=cfg)
+        write_own_folder(work, layers, model=cfg)
         steps, warmup = min(args.steps, 16), 3
         pages = (decodes + 1) * (context // PAGE) + 64
         engine = Engine(EngineConfig(model_path=work, dtype=torch.bfloat16, max_num_seqs=decodes + 1, max_prefill_tokens=2048,
@@ -528,7 +567,7 @@ def run_reference(args) -> dict:
 
     work = Path(tempfile.mkdtemp(prefix="psb200-bench-ref-"))
     try:
-        write_model_folder(work, FULL_LAYERS)
+        write_reference_folder(work, FULL_LAYERS)
         rng = np.random.RandomState(0)
         vocab = MODEL["vocab_size"]
         pool = args.batch * (CONTEXT // PAGE) + 64
@@ -550,13 +589,13 @@ def run_reference(args) -> dict:
         if engine is None:
             return {"impl": "reference", "unavailable": "; ".join(why)[:400]}
 
-        total = args.steps + args.warmup
+        prompt_len, generate = e2e_request_shape(args.batch, args.steps, args.warmup)
         sched = Scheduler(engine.num_blocks, chunk_size=PREFILL_TOKENS, enable_prefix_cache=False)
         for r in range(args.batch):
-            sched.add_request(f"r{r}", rng.randint(0, vocab, size=CONTEXT - total - args.batch - 2),
-                              total + args.batch + 2, ignore_eos=True)
+            sched.add_request(f"r{r}", rng.randint(0, vocab, size=prompt_len), generate, ignore_eos=True)
         decoding = produced = steps = 0
         t_start = None
+        h2d = []
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with ClockSampler() as clocks:
             while sched.has_work() and steps < args.steps:
@@ -572,20 +611,27 @@ def run_reference(args) -> dict:
                 if t_start is not None:
                     produced += len(out)
                     steps += 1
+                    # the int32 words its engine lays out in its one pinned buffer and copies (llama_engine.py:152-227
+                    # of PrefixServe): ids and positions per token, two offset arrays, last-page lengths, the rows to
+                    # sample, and every request's whole page list
+                    t, b = sum(w.end - w.start for w in batch.work), len(batch.work)
+                    h2d.append(4 * (2 * t + 2 * (b + 1) + b + len(out) + sum(-(-w.end // PAGE) for w in batch.work)))
                 sched.commit(batch, out)
             e1.record()
             torch.cuda.synchronize()
             wall = time.perf_counter() - t_start
+        if produced != args.batch * args.steps:
+            raise RuntimeError(f"end-to-end region produced {produced} tokens in {steps} steps, not {args.batch} x {args.steps}")
         dev_ms = e0.elapsed_time(e1)
         return {
             "impl": "reference", "metric": "decode tokens/s at batch 8, context 4096 (Llama-3.2-1B sizes, random weights)",
             "value": round(produced / (dev_ms * 1e-3), 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": args.warmup,
             "ms_per_step": round(dev_ms / max(steps, 1), 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic: seeded uniform-random token ids, N(0,0.02) random weights",
-            "config": {"model": "Llama-3.2-1B sizes", "layers": FULL_LAYERS, "global_batch": args.batch, "seq_len": CONTEXT,
-                       "attention_backend": attention, "parallelism": "single-gpu"},
-            "e2e": {"value": round(produced / wall, 1), "unit": "tokens/s", "h2d_bytes_per_step": None, "d2h_bytes_per_step": 8 * args.batch},
-            "clocks": clocks.summary(), "notes": "; ".join(why),
+            "config": config_block(FULL_LAYERS, args.batch),
+            "e2e": {"value": round(produced / wall, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(sum(h2d) / max(len(h2d), 1)),
+                    "d2h_bytes_per_step": 8 * args.batch, "steps": steps, "tokens": produced},
+            "clocks": clocks.summary(), "attention_backend": attention, "notes": "; ".join(why),
         }
     finally:
         shutil.rmtree(work, ignore_errors=True)
@@ -630,9 +676,47 @@ def run_timeline(args) -> dict:
         row[0] += 1
         row[1] += max(end - prev_end, 0.0)
         prev_end = max(prev_end, end)
-    table = [{"kernel": k, "launches": n, "serial_us_each": round(t / n, 2), "serial_us_total": round(t, 1)}
-             for k, (n, t) in sorted(rows.items(), key=lambda kv: -kv[1][1])]
+    costs = kernel_costs(base) if args.profile else []
+    pk = peaks()
+    table = []
+    for k, (n, t) in sorted(rows.items(), key=lambda kv: -kv[1][1]):
+        row = {"kernel": k, "launches": n, "serial_us_each": round(t / n, 2), "serial_us_total": round(t, 1)}
+        for pattern, nbytes, flops in costs:
+            if re.search(pattern, k):
+                bound_us = max(nbytes / (pk["hbm_gbs"] * 1e9), flops / (pk["bf16_tflops"] * 1e12)) * 1e6
+                row.update({"bytes": int(nbytes), "flops": int(flops), "bound": "hbm" if nbytes / (pk["hbm_gbs"] * 1e9) >= flops / (pk["bf16_tflops"] * 1e12) else "tensor",
+                            "bound_us": round(bound_us, 1), "frac_of_" + pk["source"] + "_peak": round(bound_us / t, 3) if t else None})
+                break
+        table.append(row)
     return {**base, "step_span_us": round(prev_end - t0, 1), "kernels_in_step": len(step), "timeline": table}
+
+
+def kernel_costs(base: dict) -> list[tuple[str, float, float]]:
+    """(pattern of a kernel's name, bytes it has to move, flops it has to do) for all launches of that kernel in one
+    step of the profiled workload, from the model's sizes: weights once per use, the cache of the live requests,
+    activations where they are the bulk.  A name that serves several products carries their sum."""
+    h, i, v = MODEL["hidden_size"], MODEL["intermediate_size"], MODEL["vocab_size"]
+    d, hq = MODEL["head_dim"], MODEL["num_attention_heads"]
+    q, kv = hq * d, MODEL["num_key_value_heads"] * d
+    layers = base["layers"]
+    if base.get("only") == "decode":
+        b, ctx = base["batch"], base["mean_context"]
+        return [
+            (r"gemm_stream_norm_kernel<.*true>", layers * 2.0 * (q + 2 * kv) * h, layers * 2.0 * b * (q + 2 * kv) * h),
+            (r"gemm_stream_norm_kernel<\d+, 2,", layers * 2.0 * 2 * i * h, layers * 2.0 * b * 2 * i * h),
+            (r"gemm_stream_norm_kernel<.*float", 2.0 * v * h + 4.0 * b * v, 2.0 * b * v * h),
+            (r"gemm_stream_kernel", layers * 2.0 * (h * q + h * i), layers * 2.0 * b * (h * q + h * i)),
+            (r"attention_decode_kernel", layers * b * ctx * 2.0 * kv * 2, layers * 4.0 * b * ctx * q),
+            (r"sample_kernel", 4.0 * b * v, 0.0),
+        ]
+    t = PREFILL_TOKENS
+    return [
+        (r"gemm_tcgen05_kernel", layers * 2.0 * (h * (q + 2 * kv) + q * h + 3 * h * i), 2.0 * t * layers * (h * (q + 2 * kv) + q * h + 3 * h * i)),
+        (r"attention_prefill_tcgen05_kernel", layers * 2.0 * t * (2 * q + 2 * kv), layers * 4.0 * t * (t + 1) / 2 * q),
+        (r"add_rmsnorm_kernel", (2 * layers) * 12.0 * t * h, 0.0),
+        (r"gemm_stream_norm_kernel<.*float", 2.0 * v * h, 2.0 * v * h),
+        (r"embedding_kernel", 6.0 * t * h, 0.0),
+    ]
 
 
 def main() -> int:
@@ -650,6 +734,9 @@ def main() -> int:
     p.add_argument("--timeline", action="store_true",
                    help="with --only decode|prefill: start and end of every kernel of the last step, from the torch profiler "
                         "(numbers of a profiled run are not bench values)")
+    p.add_argument("--profile", action="store_true",
+                   help="--timeline plus, per kernel, the bytes and flops it has to do in the step and the fraction of the "
+                        "measured peak that its time inside the step amounts to")
     p.add_argument("--workload", choices=["decode", "shared-prefix", "mixed"], default="decode",
                    help="decode: the headline line.  shared-prefix: 64 requests over 4 system prefixes through the entry "
                         "point, prefix cache on and off.  mixed: steps of one 512-token prompt portion beside 64 decoded tokens")
@@ -670,8 +757,9 @@ def main() -> int:
         args.layers = None if args.layers == FULL_LAYERS and "--layers" not in sys.argv else args.layers
         result = run_shared_prefix(args) if args.workload == "shared-prefix" else run_mixed(args)
     else:
+        args.timeline = args.timeline or args.profile
         if args.timeline and (args.impl != "own" or args.only == "all"):
-            print(json.dumps({"unsupported": "--timeline needs --only decode or --only prefill of this engine"}))
+            print(json.dumps({"unsupported": "--timeline/--profile need --only decode or --only prefill of this engine"}))
             return 2
         result = run_reference(args) if args.impl == "reference" else (run_timeline(args) if args.timeline else run_own(args))
     print(json.dumps(result))

@@ -23,33 +23,35 @@ from ..parts.model import build_model
 
 
 def random_tensors(table: Mapping[str, ParamSpec], seed: int, *, std: float = 0.02, gain_noise: float = 0.0,
-                   dtype: torch.dtype = torch.bfloat16) -> dict[str, torch.Tensor]:
-    """part path -> tensor, drawn in table order from one generator."""
-    gen = torch.Generator(device="cpu")
+                   dtype: torch.dtype = torch.bfloat16, device: str = "cpu") -> dict[str, torch.Tensor]:
+    """part path -> tensor (on the host), drawn in table order from one generator.  ``device``: where the numbers
+    are drawn; the host's generator and a GPU's give different (each reproducible) values, so tests that compare
+    with stored outputs draw on the host, and benchmarks of billions of weights may draw on the GPU."""
+    gen = torch.Generator(device=device)
     gen.manual_seed(int(seed))
     out: dict[str, torch.Tensor] = {}
     for path, spec in table.items():
         if spec.role == "table_int":
             out[path] = torch.zeros(spec.shape, dtype=torch.int32)
         elif spec.init == "ones":
-            t = torch.ones(spec.shape, dtype=torch.float32)
+            t = torch.ones(spec.shape, dtype=torch.float32, device=device)
             if gain_noise:
-                t += gain_noise * torch.randn(spec.shape, generator=gen, dtype=torch.float32)
-            out[path] = t.to(dtype)
+                t += gain_noise * torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device)
+            out[path] = t.to(dtype).cpu()
         else:
-            out[path] = (std * torch.randn(spec.shape, generator=gen, dtype=torch.float32)).to(dtype)
+            out[path] = (std * torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device)).to(dtype).cpu()
     return out
 
 
 def write_random_model(folder: str | Path, config: Any, seed: int, *, std: float = 0.02, gain_noise: float = 0.0,
-                       dtype: torch.dtype = torch.bfloat16, architecture: str | None = None) -> Path:
+                       dtype: torch.dtype = torch.bfloat16, architecture: str | None = None, device: str = "cpu") -> Path:
     """Writes config.json and model.safetensors for ``config`` (a typed configuration with ``to_config_json``)."""
     folder = Path(folder)
     folder.mkdir(parents=True, exist_ok=True)
     arch = get_architecture(architecture or config.architecture)
     model = build_model(arch.to_spec(config))
     table = model.param_table()
-    by_path = random_tensors(table, seed, std=std, gain_noise=gain_noise, dtype=dtype)
+    by_path = random_tensors(table, seed, std=std, gain_noise=gain_noise, dtype=dtype, device=device)
     by_name = {arch.tensor_name(path): t.contiguous() for path, t in by_path.items()}
     save_file(by_name, str(folder / "model.safetensors"), metadata={"format": "pt"})
     (folder / "config.json").write_text(json.dumps(config.to_config_json(), indent=2) + "\n")
