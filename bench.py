@@ -307,12 +307,17 @@ def run_own(args) -> dict:
 
         if args.only == "prefill":
             torch.cuda.synchronize()
-            slot = cache.open()
-            cache.reserve(slot, PREFILL_TOKENS)
+            portion = args.portion
             for _ in range(max(args.steps, 1)):
-                runner.step([StepItem(slot, 0, rng.randint(0, vocab, size=PREFILL_TOKENS).astype(np.int32), (PREFILL_TOKENS - 1,))])
+                slot = cache.open()
+                cache.reserve(slot, PREFILL_TOKENS)
+                for at in range(0, PREFILL_TOKENS, portion):  # the last step of the last prompt is the one profiled
+                    runner.step([StepItem(slot, at, rng.randint(0, vocab, size=portion).astype(np.int32), (portion - 1,))])
+                    cache.advance(slot, at + portion)
+                cache.close(slot)
             torch.cuda.synchronize()
-            return {"only": "prefill", "steps": args.steps, "layers": layers, "batch": 1, "weight_bytes": weights}
+            return {"only": "prefill", "steps": args.steps, "layers": layers, "batch": 1, "weight_bytes": weights,
+                    "portion": portion, "prefix": PREFILL_TOKENS - portion}
 
         # ---- headline: decode at the default batch, device-timed, clocks sampled meanwhile
         with ClockSampler() as clocks:
@@ -709,10 +714,12 @@ def kernel_costs(base: dict) -> list[tuple[str, float, float]]:
             (r"attention_decode_kernel", layers * b * ctx * 2.0 * kv * 2, layers * 4.0 * b * ctx * q),
             (r"sample_kernel", 4.0 * b * v, 0.0),
         ]
-    t = PREFILL_TOKENS
+    t, prefix = base.get("portion", PREFILL_TOKENS), base.get("prefix", 0)
     return [
-        (r"gemm_tcgen05_kernel", layers * 2.0 * (h * (q + 2 * kv) + q * h + 3 * h * i), 2.0 * t * layers * (h * (q + 2 * kv) + q * h + 3 * h * i)),
-        (r"attention_prefill_tcgen05_kernel", layers * 2.0 * t * (2 * q + 2 * kv), layers * 4.0 * t * (t + 1) / 2 * q),
+        # the projection that rotates in its epilogue has a non-zero second template argument; the other three share a name
+        (r"gemm_tcgen05_kernel<\d+, [1-9]", layers * 2.0 * h * (q + 2 * kv), 2.0 * t * layers * h * (q + 2 * kv)),
+        (r"gemm_tcgen05_kernel", layers * 2.0 * (q * h + 3 * h * i), 2.0 * t * layers * (q * h + 3 * h * i)),
+        (r"attention_prefill_tcgen05_kernel", layers * 2.0 * (t * 2 * q + (prefix + t) * 2 * kv), layers * 4.0 * t * (prefix + (t + 1) / 2) * q),
         (r"add_rmsnorm_kernel", (2 * layers) * 12.0 * t * h, 0.0),
         (r"gemm_stream_norm_kernel<.*float", 2.0 * v * h, 2.0 * v * h),
         (r"embedding_kernel", 6.0 * t * h, 0.0),
@@ -730,6 +737,8 @@ def main() -> int:
     p.add_argument("--skip-points", action="store_true", help="leave out the batch-1 and batch-64 points")
     p.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
                    help="decode: only the device-timed decode steps; prefill: only the 2,048-token prefill (for profilers)")
+    p.add_argument("--portion", type=int, default=PREFILL_TOKENS, choices=[256, 512, 1024, 2048],
+                   help="with --only prefill: the 2,048-token prompt arrives in portions of this size")
     p.add_argument("--no-graphs", action="store_true", help="run decode steps without CUDA graphs (kernel launch lists)")
     p.add_argument("--timeline", action="store_true",
                    help="with --only decode|prefill: start and end of every kernel of the last step, from the torch profiler "

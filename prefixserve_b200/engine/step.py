@@ -50,7 +50,8 @@ class StepItem:
 
 @dataclass
 class _DecodeGraph:
-    """A captured pure-decode step for one batch size: fixed input buffer, fixed output, the graph."""
+    """A captured step for one shape (a batch size of single tokens, or a tuple of item lengths): fixed input buffer,
+    fixed output, the graph."""
 
     inputs: torch.Tensor
     logits: torch.Tensor
@@ -60,6 +61,7 @@ class _DecodeGraph:
     pairs_room: int  # how many pairs fit
     kernels: int = 0  # launches of this library's kernels recorded in the graph
     by_name: dict | None = None  # the same by entry point
+    layout: "_Layout | None" = None
 
 
 @dataclass
@@ -90,6 +92,15 @@ class ModelRunner:
     batch size as a CUDA graph over a fixed input buffer and replayed.  The
     logits of such a step live in the graph's own memory and are valid until
     the next step of the same batch size.
+
+    Steps with prompt portions of up to a thousand tokens are bound by the
+    host too (a step's launches take the host about two milliseconds, the
+    device less).  Their shape is the tuple of the items' lengths with, per
+    item, whether the last position's logits are wanted; a shape that comes a
+    second time is captured and replayed from then on (a long prompt cut into
+    equal portions, a portion beside the same decoding requests step after
+    step).  Everything that varies inside a shape (tokens, positions, lengths
+    of the cached prefixes, slots) is device data.
     """
 
     def __init__(self, model: DecoderModel, cache: CacheManager, *, device: torch.device | str,
@@ -113,6 +124,11 @@ class ModelRunner:
         self._graphs: dict[int, _DecodeGraph] = {}
         self._graph_pool = None  # one memory pool for all captured steps: only one of them runs at a time
         self.graph_replays = 0
+        self._shape_graphs: dict[tuple, _DecodeGraph] = {}  # steps with portions, by shape; oldest out first
+        self._shapes_seen: dict[tuple, int] = {}
+        self.max_shape_graphs = 48
+        self.capture_shapes_from = 2      # a shape is captured when it comes for this many-th time
+        self.longest_captured_portion = 1024  # longer portions keep the device busy longer than the host needs
         # Test-only, after the reference's EngineConfig.inject_bug (prefixserve/llama_engine.py:62-63, :192, :202-203):
         # "rope_relative" numbers every portion's positions from 0; "kv_len_short" reports one key too few.
         # The test suite proves with these that it notices such faults.
@@ -240,9 +256,15 @@ class ModelRunner:
                     or not device_ids.is_cuda or in_flight is None or len(in_flight) != len(items):
                 raise EngineError("token ids from the device: one int32 per item, every item a single token")
             ahead = np.asarray(in_flight, dtype=np.int64)
-        held = self._graphs.get(len(items)) if self.use_graphs else None
-        if held is not None and all(len(it.tokens) == 1 and tuple(it.want) == (0,) for it in items):
+        all_single = all(len(it.tokens) == 1 and tuple(it.want) == (0,) for it in items)
+        held = self._graphs.get(len(items)) if self.use_graphs and all_single else None
+        if held is not None:
             return self._replay(items, held, device_ids, ahead)
+        shape = None
+        if self.use_graphs and not all_single and device_ids is None:
+            shape = self._shape_of(items)
+            if shape is not None and shape in self._shape_graphs:
+                return self._replay_shape(items, self._shape_graphs[shape])
         self._check(items, ahead)
         lens = [len(it.tokens) for it in items]
         b, t = len(items), sum(lens)
@@ -252,15 +274,22 @@ class ModelRunner:
         starts_np = np.fromiter((it.start for it in items), dtype=np.int64, count=b)
         ends_np = starts_np + np.asarray(lens, dtype=np.int64)
         self._check_pages(slots_np, starts_np, ends_np)
-        static = self.use_graphs and t == b and all(tuple(it.want) == (0,) for it in items)
+        capture_shape = False
+        if shape is not None:
+            self._shapes_seen[shape] = seen = self._shapes_seen.get(shape, 0) + 1
+            if len(self._shapes_seen) > 4096:
+                self._shapes_seen.clear()
+            capture_shape = seen >= self.capture_shapes_from
+        static = self.use_graphs and (all_single or capture_shape)
         if static:  # the shapes of a captured step may not depend on the step: full-width page tables
             widths = {gi: self.cache.max_pages_per_seq for gi in range(len(self.cache.groups))}
         else:
             widths = {gi: pages_for(int(ends_np.max()), page) for gi in range(len(self.cache.groups))}
 
-        lay = _Layout(t, b, s, rows_are_items=static)
+        lay = _Layout(t, b, s, rows_are_items=static and all_single)
         n_pairs = self.cache.pending_deltas()
-        room = max(n_pairs, 4 * b + 64) if static else n_pairs  # a captured step keeps room for later steps' pairs
+        # a captured step keeps room for later steps' pairs: a page per request and what its portions fill
+        room = max(n_pairs, 4 * b + 64 + 2 * (t // page)) if static else n_pairs
         total = lay.pairs + 2 * n_pairs
         host = self._staging(total)
         buf = host.numpy()
@@ -311,11 +340,81 @@ class ModelRunner:
                 with library.pinned_stream():  # the capture's own stream
                     static_logits = self._device_step(lay, dev, widths, views, lens, static, rows)
             recorded = library.launch_counts - named
-            self._graphs[b] = _DecodeGraph(inputs=dev, logits=static_logits, graph=graph, var_at=lay.var, pairs_at=lay.pairs,
-                                           pairs_room=room, kernels=library.launches - before, by_name=dict(recorded))
+            made = _DecodeGraph(inputs=dev, logits=static_logits, graph=graph, var_at=lay.var, pairs_at=lay.pairs,
+                                pairs_room=room, kernels=library.launches - before, by_name=dict(recorded), layout=lay)
+            if all_single:
+                self._graphs[b] = made
+            else:
+                if len(self._shape_graphs) >= self.max_shape_graphs:
+                    self._shape_graphs.pop(next(iter(self._shape_graphs)))
+                self._shape_graphs[shape] = made
             library.launches = before  # recorded, not run
             library.launch_counts.subtract(recorded)
         return logits
+
+    def _shape_of(self, items: Sequence[StepItem]) -> tuple | None:
+        """What a captured step with prompt portions is keyed by: every item's length and whether it wants the logits
+        of its last position (the two forms the scheduler asks for).  None: not a step worth capturing."""
+        shape = []
+        longest = 0
+        for it in items:
+            n = len(it.tokens)
+            want = tuple(it.want)
+            if want == (n - 1,):
+                shape.append(n)
+            elif want == ():
+                shape.append(-n)
+            else:
+                return None
+            longest = max(longest, n)
+        if longest > self.longest_captured_portion:
+            return None
+        return tuple(shape)
+
+    def _replay_shape(self, items: Sequence[StepItem], held: _DecodeGraph) -> torch.Tensor:
+        """A step whose shape has been captured: the same checks as the general path, the words that change laid out
+        as the capture had them, one copy, one replay."""
+        self._check(items)
+        cache, lay = self.cache, held.layout
+        b = len(items)
+        lens = [len(it.tokens) for it in items]
+        slots_np = np.fromiter((it.slot for it in items), dtype=np.int32, count=b)
+        starts_np = np.fromiter((it.start for it in items), dtype=np.int64, count=b)
+        self._check_pages(slots_np, starts_np, starts_np + np.asarray(lens, dtype=np.int64))
+        if cache.pending_deltas() > held.pairs_room:
+            self._send_deltas_alone()
+        n_pairs = cache.pending_deltas()
+        words = lay.pairs - lay.var
+        total = words + 2 * n_pairs
+        host = self._staging(total)
+        buf = host.numpy()
+        off = -lay.var  # the host buffer starts where the changing words start
+        tok = ri = 0
+        for i, (it, n) in enumerate(zip(items, lens)):
+            buf[off + lay.ids + tok: off + lay.ids + tok + n] = it.tokens
+            first = 0 if self.inject_bug == "rope_relative" else it.start
+            buf[off + lay.pos + tok: off + lay.pos + tok + n] = np.arange(first, first + n, dtype=np.int32)
+            buf[off + lay.kvlen + i] = it.start + n - (1 if self.inject_bug == "kv_len_short" and it.start + n > n else 0)
+            buf[off + lay.slot + i] = it.slot
+            for _ in it.want:
+                buf[off + lay.rowslot + ri] = it.slot
+                ri += 1
+            tok += n
+        n_pairs = cache.drain_deltas(buf, words)
+        self.last_h2d_bytes = 4 * total
+        held.inputs[lay.var: lay.var + total].copy_(host[:total], non_blocking=True)
+        self._copied.record()
+        self._copy_pending = True
+        self.last_row_slots = held.inputs[lay.rowslot: lay.rowslot + lay.s]
+        if n_pairs:
+            with library.pinned_stream():
+                ops.scatter_words(cache.resident, held.inputs[held.pairs_at:], n_pairs)
+        held.graph.replay()
+        library.launches += held.kernels
+        library.launch_counts.update(held.by_name)
+        self.steps_run += 1
+        self.graph_replays += 1
+        return held.logits
 
     def _replay(self, items: Sequence[StepItem], held: _DecodeGraph, device_ids: torch.Tensor | None = None,
                 ahead: np.ndarray | None = None) -> torch.Tensor:

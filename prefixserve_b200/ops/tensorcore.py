@@ -244,8 +244,8 @@ def _attention_plan(new_tokens: Sequence[int], kv_lens: Sequence[int], window: i
     the same head counts and window, so a step works it out once."""
     b = len(new_tokens)
     singles = [kvl for n, kvl in zip(new_tokens, kv_lens) if n == 1]
-    if static_kv_len is not None:
-        singles = [static_kv_len] * b
+    if static_kv_len is not None:  # a captured step: its single tokens may later sit at any length up to this one
+        singles = [static_kv_len] * len(singles)
     plan = {"b": b, "use_decode": bool(singles) and group <= 16}
     if plan["use_decode"]:
         if window and static_kv_len is not None:
