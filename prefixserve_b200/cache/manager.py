@@ -123,6 +123,7 @@ class CacheManager:
         # device tensors
         self.kv: list[torch.Tensor | None] = [None] * len(self.needs)
         self.state: list[torch.Tensor | None] = [None] * len(self.needs)
+        self._pools: list = []  # the kernel library's allocations behind ``kv``
         self.resident: torch.Tensor | None = None
         self.records_dev: torch.Tensor | None = None
         self.tables_dev: list[torch.Tensor] = []
@@ -136,9 +137,30 @@ class CacheManager:
                 if need.paged is not None:
                     g = self.groups[self.entry_group[i]]
                     shape = (g.pool.num_blocks, 2, need.paged.num_kv_heads, page_size, need.paged.head_dim)
-                    self.kv[i] = torch.zeros(shape, dtype=dtype, device=self.device)
+                    self.kv[i] = self._pages(shape, dtype)
                 if need.state is not None:
                     self.state[i] = torch.zeros((num_slots, *need.state.shape), dtype=need.state.dtype, device=self.device)
+
+    def _pages(self, shape: tuple, dtype: torch.dtype) -> torch.Tensor:
+        """The pages of one cache entry, zeroed.  On a CUDA device the memory belongs to the kernel library's pool
+        (allocated once, at a fixed address, freed with this manager); elsewhere (bookkeeping tests on the host) it is
+        an ordinary tensor."""
+        if self.device.type != "cuda":
+            return torch.zeros(shape, dtype=dtype, device=self.device)
+        from ..ops.library import DevicePool
+        count = 1
+        for n in shape:
+            count *= int(n)
+        pool = DevicePool(count * torch.empty((), dtype=dtype).element_size(), self.device)
+        self._pools.append(pool)
+        return pool.tensor(shape, dtype)
+
+    def release_device_memory(self) -> None:
+        """Gives the pages' device memory back now (waits for the device).  The manager is of no use afterwards."""
+        self.kv = [None] * len(self.needs)
+        for pool in self._pools:
+            pool.free()
+        self._pools.clear()
 
     # ------------------------------------------------------------------ sizes
     @staticmethod

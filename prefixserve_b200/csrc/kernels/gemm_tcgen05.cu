@@ -1,6 +1,7 @@
 // C[M,N] = A[M,K] * W[N,K]^T in bfloat16 on the 5th-generation tensor cores, for many rows (prefill).
 //
-// Persistent, warp-specialised CTAs (one per SM), 192 threads, output tiles of 128 rows by BN columns (256 or 192):
+// Persistent, warp-specialised CTAs (one per SM), 192 threads, output tiles of 128 rows by BN columns (256, 192 or
+// 128: the widest that still gives every SM a tile; a few hundred rows against a narrow matrix take the narrow ones):
 //   warp 0      producer: one lane issues TMA loads (cp.async.bulk.tensor.2d) of a 128x64 tile of A and two
 //               (BN/2)x64 tiles of W per stage into 128-byte-swizzled shared memory; completion by mbarrier
 //               transaction bytes;
@@ -32,17 +33,17 @@ constexpr int A_BYTES = BM * BK * 2;        // 16 KB
 constexpr int THREADS = 192;
 constexpr int TMEM_COLS = 512;              // two accumulator buffers, 256 float32 columns apart
 constexpr int ACC_STRIDE = 256;
-constexpr int MAX_STAGES = 5;
+constexpr int MAX_STAGES = 6;
 
 // The output tile is 128 rows by BN columns: 256 where that fills the SMs evenly, 192 where it does not (a product of
 // 192 tiles of 256 columns takes 148 CTAs two rounds, as 256 tiles of 192 columns two rounds of three quarters the size).
 template <int BN>
 struct Tile {
-  static_assert(BN == 256 || BN == 192, "tile widths built");
+  static_assert(BN == 256 || BN == 192 || BN == 128, "tile widths built");
   static constexpr int HALF = BN / 2;                  // rows of W per TMA load
   static constexpr int B_BYTES = BN * BK * 2;          // 32 or 24 KB
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = BN == 256 ? 4 : 5;
+  static constexpr int STAGES = BN == 256 ? 4 : (BN == 192 ? 5 : 6);
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
   static_assert(STAGES <= MAX_STAGES && SMEM_BYTES <= 227 * 1024, "beyond a CTA's shared memory");
 };
@@ -356,20 +357,36 @@ int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) 
   return 0;
 }
 
-int g_forced_width = 0;  // 0: the launcher chooses the tile width; 192 or 256: tests compare the two
+int g_forced_width = 0;  // 0: the launcher chooses the tile width; 128, 192 or 256: tests compare them
+
+// The tile width for a product: the one that gets it done in the fewest, shortest rounds over the SMs.  A round of
+// tiles costs its width in tensor-core time plus a fixed share (first loads, the epilogue of the last tile).  The gated
+// form needs an even split into gate and up columns and heads of 128 held in registers need whole heads: no 192.
+int choose_width(int M, int N_out, bool gated, bool rope, int D, int sms) {
+  const int m_blocks = (M + BM - 1) / BM;
+  int best = 256;
+  long best_cost = -1;
+  for (int bn : {256, 192, 128}) {
+    if (bn == 192 && (gated || (rope && D == 128))) continue;
+    if (g_forced_width && bn != g_forced_width) continue;
+    const int span = gated ? bn / 2 : bn;
+    const long tiles = (long)m_blocks * ((N_out + span - 1) / span);
+    const long cost = ((tiles + sms - 1) / sms) * (bn + 24);
+    if (best_cost < 0 || cost * 10 <= best_cost * 9) {  // from the widest down: a narrower tile has to pay for itself
+      best = bn;
+      best_cost = cost;
+    }
+  }
+  return best;
+}
 
 int launch(const void* a, const void* w, void* c, int M, int w_rows, int N_out, int K, int up_offset, int mode, int sms,
            cudaStream_t stream, const RopeArgs& rope = RopeArgs{}) {
   const bool gated = mode == MODE_GATED || mode == MODE_GATED_GELU;
   if (M < 1 || N_out < 1 || K < 8 || K % 8) PSB_REFUSE("gemm_tcgen05: needs K a multiple of 8 (M=%d N=%d K=%d)", M, N_out, K);
   if (((uintptr_t)a | (uintptr_t)w | (uintptr_t)c) & 15) PSB_REFUSE("gemm_tcgen05: operands must be 16-byte aligned");
-  // Tile width: 256 columns unless 192 get the product done in fewer or shorter rounds over the SMs (the gated form
-  // and 128-wide heads held in registers need 256).
   const int m_blocks = (M + BM - 1) / BM;
-  auto rounds_cost = [&](int bn) { return ((m_blocks * ((N_out + bn - 1) / bn) + sms - 1) / sms) * bn; };
-  const bool may_narrow = !gated && !(mode == MODE_ROPE && rope.D == 128);
-  const bool narrow = may_narrow && (g_forced_width ? g_forced_width == 192 : rounds_cost(192) * 10 <= rounds_cost(256) * 9);
-  const int bn = narrow ? 192 : 256;
+  const int bn = choose_width(M, N_out, gated, mode == MODE_ROPE, rope.D, sms);
   CUtensorMap map_a, map_w;
   if (int rc = make_map(&map_a, a, M, K, BM)) return rc;
   if (int rc = make_map(&map_w, w, w_rows, K, bn / 2)) return rc;
@@ -389,10 +406,10 @@ int launch(const void* a, const void* w, void* c, int M, int w_rows, int N_out, 
                map_w, (__nv_bfloat16*)c, M, N_out, K, N_out, up_offset, mode, rope);                                 \
   } while (0)
   // the usual head sizes keep a row's angles in registers; every other multiple of 16 fetches them block by block
-  if (mode == MODE_ROPE && rope.D == 128) PSB_TCGEN05(256, 8);
-  else if (mode == MODE_ROPE && rope.D == 64 && narrow) PSB_TCGEN05(192, 4);
-  else if (mode == MODE_ROPE && rope.D == 64) PSB_TCGEN05(256, 4);
-  else if (narrow) PSB_TCGEN05(192, 0);
+  if (mode == MODE_ROPE && rope.D == 128) { if (bn == 128) PSB_TCGEN05(128, 8); else PSB_TCGEN05(256, 8); }
+  else if (mode == MODE_ROPE && rope.D == 64) { if (bn == 128) PSB_TCGEN05(128, 4); else if (bn == 192) PSB_TCGEN05(192, 4); else PSB_TCGEN05(256, 4); }
+  else if (bn == 128) PSB_TCGEN05(128, 0);
+  else if (bn == 192) PSB_TCGEN05(192, 0);
   else PSB_TCGEN05(256, 0);
 #undef PSB_TCGEN05
   PSB_LAUNCH_CHECK("gemm_tcgen05");
@@ -435,11 +452,21 @@ PSB_API int psb_gemm_tcgen05_rope(const void* a, const void* w, int M, int K, in
   return launch(a, w, q_out, M, N, N, K, 0, MODE_ROPE, sms, stream, rope);
 }
 
-// For tests: 192 or 256 makes every later product use that tile width where the shape allows it, 0 gives the choice back.
+// For tests: 128, 192 or 256 makes every later product use that tile width where the shape allows it, 0 gives the
+// choice back.
 PSB_API int psb_gemm_tcgen05_tile_width(int width) {
-  if (width != 0 && width != 192 && width != 256) PSB_REFUSE("gemm_tcgen05: tile widths are 192 and 256, not %d", width);
+  if (width != 0 && width != 128 && width != 192 && width != 256) PSB_REFUSE("gemm_tcgen05: tile widths are 128, 192 and 256, not %d", width);
   g_forced_width = width;
   return 0;
+}
+
+// How many output tiles the kernel would cut a product into (kind: 0 plain [M, N], 1 gated [M, N] from 2N rows, 2 the
+// projection that rotates, with heads of D).  The host sends products with too few tiles for the SMs elsewhere.
+PSB_API int psb_gemm_tcgen05_tiles(int M, int N_out, int kind, int D, int sms) {
+  if (M < 1 || N_out < 1 || sms < 1) return 0;
+  const int bn = choose_width(M, N_out, kind == 1, kind == 2, D, sms);
+  const int span = kind == 1 ? bn / 2 : bn;
+  return ((M + BM - 1) / BM) * ((N_out + span - 1) / span);
 }
 
 // 0 while no bounded wait has ever run out on the current device; reading it synchronises with the device.

@@ -229,6 +229,7 @@ class Engine:
         runner.step(items)
         torch.cuda.synchronize()
         activations = torch.cuda.max_memory_allocated() - before - held
+        cache.release_device_memory()  # the trial pages go back before the real pool is measured for
         del cache, runner
         gc.collect()
         torch.cuda.empty_cache()

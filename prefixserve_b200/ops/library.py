@@ -83,6 +83,8 @@ _SIGNATURES: dict[str, list] = {
     # (a, w, act, M, I, K, sms, activation, stream)
     "psb_gemm_tcgen05_gated": [P, P, P, I, I, I, I, I, P],
     "psb_gemm_tcgen05_tile_width": [I],
+    # (M, N_out, kind, D, sms) -> output tiles at the width the kernel would choose
+    "psb_gemm_tcgen05_tiles": [I, I, I, I, I],
     "psb_gemm_tcgen05_rope": [P, P, I, I, I, P, P, P, I, P, P, P, P, I, I, I, I, I, I, P],
     # () -> 0 while no bounded wait of the tcgen05 kernel has ever run out
     "psb_tcgen05_status": [],
@@ -96,6 +98,9 @@ _SIGNATURES: dict[str, list] = {
     "psb_step_prepare": [P, I, P, P, P, I, P, I, I, I, P],
     # (limit, who, out int32[3], stream)
     "psb_selftest_bounded_wait": [I, I, P, P],
+    # (bytes, void** out) / (pointer)
+    "psb_pool_alloc": [L, ctypes.POINTER(c_void_p)],
+    "psb_pool_free": [P],
     # (S, V) -> bytes of scratch psb_sample wants
     "psb_sample_scratch_bytes": [I, I],
 }
@@ -186,3 +191,67 @@ def check(status: int, what: str) -> None:
     if status != 0:
         detail = lib().psb_last_error().decode(errors="replace")
         raise KernelError(f"{what}: {detail} (status {status})")
+
+
+_parked: list[tuple[int, torch.device]] = []  # pool memory waiting to be freed (see DevicePool.free)
+
+
+def _free_parked() -> None:
+    if _lib is None or not _parked:
+        return
+    try:
+        if torch.cuda.is_current_stream_capturing():
+            return
+    except Exception:  # noqa: BLE001  (interpreter shutdown)
+        return
+    while _parked:
+        ptr, device = _parked.pop()
+        with torch.cuda.device(device):
+            _lib.psb_pool_free(c_void_p(ptr))
+
+
+class DevicePool:
+    """Device memory for cache pages, allocated and freed by the kernel library itself (not by torch's caching
+    allocator): the address never moves and the bytes are given back the moment the owner goes.  ``tensor`` views
+    the memory without copying; the views must not outlive the pool."""
+
+    def __init__(self, nbytes: int, device: torch.device) -> None:
+        self.nbytes, self.device = int(nbytes), torch.device(device)
+        self.ptr = 0
+        _free_parked()
+        with torch.cuda.device(self.device):
+            out = c_void_p()
+            status = lib().psb_pool_alloc(self.nbytes, ctypes.byref(out))
+            if status != 0:
+                raise KernelError("pool: " + lib().psb_last_error().decode(errors="replace"))
+            self.ptr = int(out.value)
+
+    def tensor(self, shape: tuple, dtype: torch.dtype) -> torch.Tensor:
+        typestr = {torch.bfloat16: "<u2", torch.float32: "<f4", torch.float16: "<f2"}[dtype]
+        count = 1
+        for n in shape:
+            count *= int(n)
+        if count * torch.empty((), dtype=dtype).element_size() > self.nbytes:
+            raise KernelError(f"pool of {self.nbytes} bytes cannot hold a {dtype} tensor of shape {tuple(shape)}")
+
+        class _Span:  # what torch needs to wrap foreign device memory; it keeps the pool alive while a view of it lives
+            owner = self
+            __cuda_array_interface__ = {"shape": tuple(int(n) for n in shape), "typestr": typestr, "data": (self.ptr, False),
+                                        "version": 2, "strides": None}
+        raw = torch.as_tensor(_Span(), device=self.device)
+        return raw.view(dtype) if raw.dtype != dtype else raw
+
+    def free(self) -> None:
+        """Gives the memory back.  Freeing device memory waits for the device, which a stream capture in progress does
+        not survive; a pool that dies during one (the collector may run its finaliser at any moment) is parked and
+        freed by the next pool that is made or freed outside a capture."""
+        if self.ptr:
+            _parked.append((self.ptr, self.device))
+            self.ptr = 0
+        _free_parked()
+
+    def __del__(self) -> None:
+        try:
+            self.free()
+        except Exception:  # noqa: BLE001  (interpreter shutdown)
+            pass

@@ -17,9 +17,9 @@ STREAM_MIN_TILES = 0     # ... for matrices with at least this many 16-row tiles
 SMALL_M = 8         # rows up to which the one-tile-per-CTA kernel is used when the streaming kernel is not
 SMALL_M_GATED = 8   # same for the gate/up product with the fused activation
 USE_TCGEN05 = True  # products with more rows than STREAM_M: this library's tcgen05/TMEM/TMA kernel (else cuBLAS)
-TCGEN05_MIN_TILES = 120  # ... when the product has at least this many 128x256 output tiles (the kernel itself may then
-                         # cut it into 128x192 ones); smaller ones (a few dozen rows against a narrow matrix) leave
-                         # most SMs idle without split-K and go to cuBLAS
+TCGEN05_MIN_TILES = 120  # ... when the kernel would cut the product into at least this many output tiles (128 rows by
+                         # 256, 192 or 128 columns, whichever gets it done in the fewest, shortest rounds); smaller ones
+                         # (a few dozen rows against a narrow matrix) leave most SMs idle without split-K and go to cuBLAS
 WIDE_BELOW_TILES = 600   # matrices with fewer 16-row tiles than this get 16 warps per CTA instead of 8
 TCGEN05_PREFILL_MIN_TOKENS = 64   # steps whose longest prompt portion has at least this many tokens run prefill attention
                                   # on the tcgen05 kernel (tiles of 128 rows); shorter portions fill too little of a tile
@@ -128,13 +128,13 @@ def norm_gated_linear_bf16(x, w_gate_up: torch.Tensor, activation: int = 0) -> t
     return act
 
 
-def _tcgen05_ok(x: torch.Tensor, w: torch.Tensor, n_span: int = 256, narrow_ok: bool = False) -> bool:
-    n_out = w.shape[0] if n_span == 256 else w.shape[0] // 2
-    if n_span == 256 and narrow_ok:
-        n_span = 192  # the projection with rotation in its epilogue: counted in the 128x192 tiles the kernel may cut it
-                      # into (it replaces two kernels; the plain products of this size are the library's: measured)
-    tiles = -(-x.shape[0] // 128) * -(-n_out // n_span)
-    return (USE_TCGEN05 and tiles >= TCGEN05_MIN_TILES and x.shape[1] % 8 == 0 and x.shape[1] >= 8 and x.is_contiguous() and w.is_contiguous()
+def _tcgen05_ok(x: torch.Tensor, w: torch.Tensor, kind: int = 0, head_dim: int = 0) -> bool:
+    """kind: 0 plain, 1 gated (w holds gate and up rows), 2 the projection that rotates (heads of ``head_dim``)."""
+    if not USE_TCGEN05:
+        return False
+    n_out = w.shape[0] // 2 if kind == 1 else w.shape[0]
+    tiles = lib().psb_gemm_tcgen05_tiles(x.shape[0], n_out, kind, head_dim, _sms(x.device))
+    return (tiles >= TCGEN05_MIN_TILES and x.shape[1] % 8 == 0 and x.shape[1] >= 8 and x.is_contiguous() and w.is_contiguous()
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
@@ -161,7 +161,7 @@ def gemm_tcgen05_gated(x: torch.Tensor, w_gate_up: torch.Tensor, activation: int
 def tcgen05_qkv_rope_bf16(x: torch.Tensor, w_qkv, positions, token_item, cos, sin, table, kv, hq, hkv, d, page_size) -> torch.Tensor | None:
     """The projection of an attention layer for many tokens on the tcgen05 kernel, rotation and append to the pages in
     its epilogue; None when that kernel does not take the shape."""
-    if not (_tcgen05_ok(x, w_qkv, narrow_ok=d != 128) and kv.is_contiguous() and (cos is None or (cos.is_contiguous() and sin.is_contiguous()))):
+    if not (_tcgen05_ok(x, w_qkv, 2, d) and kv.is_contiguous() and (cos is None or (cos.is_contiguous() and sin.is_contiguous()))):
         return None
     m, k = x.shape
     q = torch.empty((m, hq, d), dtype=torch.bfloat16, device=x.device)
@@ -201,7 +201,7 @@ def gated_linear_bf16(x: torch.Tensor, w_gate_up: torch.Tensor, limit: int | Non
     if (limit is None and small_m_ok(m, k, min(STREAM_M, 16)) and w_gate_up.shape[0] % 2 == 0 and x.is_contiguous()
             and w_gate_up.is_contiguous()):
         return gemm_stream_gated(x, w_gate_up, activation)
-    if limit is None and m > max(STREAM_M, SMALL_M_GATED) and w_gate_up.shape[0] % 2 == 0 and _tcgen05_ok(x, w_gate_up, 128):
+    if limit is None and m > max(STREAM_M, SMALL_M_GATED) and w_gate_up.shape[0] % 2 == 0 and _tcgen05_ok(x, w_gate_up, 1):
         return gemm_tcgen05_gated(x, w_gate_up, activation)
     if not (small_m_ok(m, k, SMALL_M_GATED if limit is None else limit) and w_gate_up.shape[0] % 2 == 0 and x.is_contiguous() and w_gate_up.is_contiguous()):
         return None

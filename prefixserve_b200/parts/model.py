@@ -3,6 +3,7 @@ of the run list, final norm on the wanted rows, LM head."""
 
 from __future__ import annotations
 
+import os
 from typing import Callable, Mapping
 
 import torch
@@ -11,6 +12,9 @@ from ..config.spec import ModelSpec
 from .base import CacheNeed, CacheView, ParamSpec, StepContext
 from .block import Block
 from .registry import make
+
+
+_NVTX = os.environ.get("PSB200_NVTX", "0") == "1"
 
 
 class DecoderModel:
@@ -82,8 +86,12 @@ class DecoderModel:
         """Runs the step's tokens; returns float32 logits [len(rows), vocab] for the wanted flat rows."""
         h = self.embedding.forward(ctx.token_ids)
         pending = None
-        for call in self.spec.schedule:
+        for at, call in enumerate(self.spec.schedule):
+            if _NVTX:  # PSB200_NVTX=1: a named range per run-list entry for timeline tools
+                torch.cuda.nvtx.range_push(f"call {at}: layer {call.layer}")
             h, pending = self.blocks[call.layer].forward(h, pending, ctx, cache_view(call.cache, call.writes_cache))
+            if _NVTX:
+                torch.cuda.nvtx.range_pop()
         if rows.numel() == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=h.device)
         if self.head.takes_deferred_input:

@@ -672,7 +672,8 @@ def test_norm_fused_linear_on_chosen_rows_and_gated():
 @pytest.mark.parametrize("lens_new,lens_old", [([130], [0]), ([64, 1, 70, 3], [5, 40, 0, 17]), ([300, 45], [16, 31])])
 @pytest.mark.parametrize("hq,hkv,d,page,k", [(8, 2, 64, 16, 512), (3, 1, 48, 8, 96), (4, 4, 128, 32, 2048), (6, 2, 128, 16, 520)])
 @pytest.mark.parametrize("rotate", [True, False])
-def test_projection_of_many_tokens_rotates_and_appends_in_its_epilogue(monkeypatch, lens_new, lens_old, hq, hkv, d, page, k, rotate):
+@pytest.mark.parametrize("width", [0, 128, 256])
+def test_projection_of_many_tokens_rotates_and_appends_in_its_epilogue(monkeypatch, lens_new, lens_old, hq, hkv, d, page, k, rotate, width):
     """The tcgen05 product with the rotary kernel's job in its epilogue: bit for bit what the same product followed by
     the rotary kernel (paired order) leaves in the queries and in the pages, and nothing anywhere else in the pages."""
     from prefixserve_b200 import ops
@@ -697,7 +698,11 @@ def test_projection_of_many_tokens_rotates_and_appends_in_its_epilogue(monkeypat
                             paired=True, **args)
     y = ops.NormedRows(h.clone(), pending, gain, 1e-5, torch.bfloat16)
     kv_one = torch.full_like(kv_two, 7.0)
-    q_one = ops.qkv_rope_append(y, w, positions, token_item, cos, sin, tab, kv_one, **args)
+    try:
+        library.check(library.lib().psb_gemm_tcgen05_tile_width(width), "tile width")
+        q_one = ops.qkv_rope_append(y, w, positions, token_item, cos, sin, tab, kv_one, **args)
+    finally:
+        library.check(library.lib().psb_gemm_tcgen05_tile_width(0), "tile width")
     assert q_one is not None and q_one.shape == (t, hq, d)
     assert torch.equal(q_one, q_two) and torch.equal(kv_one, kv_two)
     assert torch.equal(y.residual(), x.residual())
@@ -797,31 +802,36 @@ def test_gemm_tcgen05(m, n, k):
 
 @pytest.mark.parametrize("m,n,k", [(128, 192, 64), (130, 333, 264), (2048, 3072, 2048), (700, 2000, 1000), (129, 8016, 96)])
 def test_gemm_tcgen05_tile_widths_agree(m, n, k):
-    """The launcher picks 128x256 or 128x192 output tiles by how they fill the SMs; a sum does not depend on it."""
+    """The launcher picks output tiles of 256, 192 or 128 columns by how they fill the SMs; a sum does not depend on it."""
     from prefixserve_b200.ops import library
     from prefixserve_b200.ops.tensorcore import gemm_tcgen05
     x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
     w = torch.randn(n, k, device=DEV).to(torch.bfloat16)
     got = {}
     try:
-        for width in (192, 256):
+        for width in (128, 192, 256):
             library.check(library.lib().psb_gemm_tcgen05_tile_width(width), "tile width")
             got[width] = gemm_tcgen05(x, w)
     finally:
         library.check(library.lib().psb_gemm_tcgen05_tile_width(0), "tile width")
     assert library.tcgen05_status() == 0
-    assert torch.equal(got[192], got[256])
+    assert torch.equal(got[192], got[256]) and torch.equal(got[128], got[256])
     want = x.double() @ w.double().t()
     assert torch.allclose(got[192].double(), want, rtol=1e-2, atol=1e-2 * math.sqrt(k))
 
 
-@pytest.mark.parametrize("m,inter,k", [(128, 128, 64), (50, 40, 24), (257, 333, 264), (2048, 8192, 2048)])
-def test_gemm_tcgen05_gated(m, inter, k):
+@pytest.mark.parametrize("width", [0, 128, 256])
+@pytest.mark.parametrize("m,inter,k", [(128, 128, 64), (50, 40, 24), (257, 333, 264), (2048, 8192, 2048), (512, 1000, 2048)])
+def test_gemm_tcgen05_gated(m, inter, k, width):
     from prefixserve_b200.ops import library
     from prefixserve_b200.ops.tensorcore import gemm_tcgen05_gated
     x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
     w = (torch.randn(2 * inter, k, device=DEV) / math.sqrt(k)).to(torch.bfloat16)
-    got = gemm_tcgen05_gated(x, w)
+    try:
+        library.check(library.lib().psb_gemm_tcgen05_tile_width(width), "tile width")
+        got = gemm_tcgen05_gated(x, w)
+    finally:
+        library.check(library.lib().psb_gemm_tcgen05_tile_width(0), "tile width")
     assert library.tcgen05_status() == 0
     y = (x.double() @ w.double().t()).to(torch.bfloat16).double()  # the reference rounds the projections first
     want = torch.nn.functional.silu(y[:, :inter]) * y[:, inter:]
