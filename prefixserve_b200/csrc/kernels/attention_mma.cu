@@ -826,6 +826,25 @@ PSB_API int psb_attention_decode_bf16(const void* q, const void* kv, const void*
   return 0;
 }
 
+// The merge alone, for a decode kernel that lives in another file (attention_decode_tma.cu) and leaves its partial
+// results in the same layout.
+PSB_API int psb_attention_decode_merge_bf16(const void* part_o, const void* part_ml, const void* item_start, const void* kv_len,
+                                            void* out, int num_items, int hq, int D, int window, int chunk, int max_splits,
+                                            int all_single, cudaStream_t stream) {
+  if (D != 64 && D != 128) PSB_REFUSE("attention_merge: head size %d is not built", D);
+  if (max_splits < 2 || max_splits > 1024 || !part_o || !part_ml) PSB_REFUSE("attention_merge: %d key ranges, or their scratch is missing", max_splits);
+  if (num_items <= 0) return 0;
+  if (num_items > 65535) PSB_REFUSE("attention_merge: batch too large");
+  if (D == 64)
+    psb_launch(attention_merge_kernel<64>, dim3(hq, num_items), dim3(32), 0, stream, (const float*)part_o, (const float*)part_ml,
+               (const int32_t*)item_start, (const int32_t*)kv_len, (__nv_bfloat16*)out, hq, window, chunk, max_splits, all_single);
+  else
+    psb_launch(attention_merge_kernel<128>, dim3(hq, num_items), dim3(32), 0, stream, (const float*)part_o, (const float*)part_ml,
+               (const int32_t*)item_start, (const int32_t*)kv_len, (__nv_bfloat16*)out, hq, window, chunk, max_splits, all_single);
+  PSB_LAUNCH_CHECK("attention_merge");
+  return 0;
+}
+
 // ---- the same, with the scratch inside the library (see no_alloc.h: for callers that cannot allocate) -----------
 #include "no_alloc.h"
 

@@ -62,6 +62,14 @@ _SIGNATURES: dict[str, list] = {
     # (q, kv, table, table_width, item_start, kv_len, out, part_o, part_ml, num_items, hq, hkv, D, page_size, window,
     #  scale, chunk, max_splits, all_single, stream)
     "psb_attention_decode_bf16": [P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P],
+    # (hq, hkv, D, page_size) -> 1 if the TMA-fed decode attention takes the shape
+    "psb_attention_decode_tma_supported": [I, I, I, I],
+    # (q, kv, table, table_width, item_start, kv_len, out, part_o, part_ml, num_items, hq, hkv, D, page_size, num_pages,
+    #  window, scale, chunk, max_splits, all_single, stream)
+    "psb_attention_decode_tma_bf16": [P, P, P, I, P, P, P, P, P, I, I, I, I, I, L, I, F, I, I, I, P],
+    "psb_attention_decode_tma_status": [],
+    # (part_o, part_ml, item_start, kv_len, out, num_items, hq, D, window, chunk, max_splits, all_single, stream)
+    "psb_attention_decode_merge_bf16": [P, P, P, P, P, I, I, I, I, I, I, I, P],
     # (x, W, y, out_dtype, M, N, K, wide, stream)
     "psb_gemm_small_m": [P, P, P, I, I, I, I, I, P],
     # (x, W, act, M, I, K, wide, activation, stream)
@@ -167,8 +175,9 @@ class pinned_stream:
 def tcgen05_status() -> int:
     """0 unless a bounded wait inside a tcgen05 kernel ever gave up (then its results are void). Synchronises.
 
-    The product's code sits in the low byte, prefill attention's in the next."""
-    return int(lib().psb_tcgen05_status()) | (int(lib().psb_attention_tcgen05_status()) << 8)
+    The product's code sits in the low byte, prefill attention's in the next, the TMA-fed decode attention's in the third."""
+    return (int(lib().psb_tcgen05_status()) | (int(lib().psb_attention_tcgen05_status()) << 8)
+            | (int(lib().psb_attention_decode_tma_status()) << 16))
 
 
 def declare(name: str, argtypes: list) -> None:

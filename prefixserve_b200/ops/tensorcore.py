@@ -6,7 +6,7 @@ from typing import Sequence
 
 import torch
 
-from .library import check, lib, stream_handle
+from .library import check, launch_counts, lib, stream_handle
 
 
 # Tuning, set from measurements on B200 at Llama-1B sizes:
@@ -23,6 +23,13 @@ TCGEN05_MIN_TILES = 120  # ... when the kernel would cut the product into at lea
 WIDE_BELOW_TILES = 600   # matrices with fewer 16-row tiles than this get 16 warps per CTA instead of 8
 TCGEN05_PREFILL_MIN_TOKENS = 64   # steps whose longest prompt portion has at least this many tokens run prefill attention
                                   # on the tcgen05 kernel (tiles of 128 rows); shorter portions fill too little of a tile
+USE_TMA_DECODE = True     # decode attention: the kernel whose keys and values the TMA unit brings in (pages of 16 tokens
+                          # or more), for key ranges of at least TMA_DECODE_MIN_RANGE keys; otherwise the one in which
+                          # every lane copies its own pieces.  Measured at Llama-1B sizes, context 4,096: with 64 requests
+                          # (one range of 4,096 keys per CTA) the step takes 2.45 ms with the first and 2.67 with the second;
+                          # with 8 requests (ranges of 512 keys, 32 tiles a CTA) 0.90 against 0.855: a CTA that short pays
+                          # more for filling its ring through one issuing lane than the ring then saves
+TMA_DECODE_MIN_RANGE = 1024
 MIN_KEY_RANGE = 128       # split-KV: no key range shorter than this
 DECODE_CTAS_PER_SM = 4   # split-KV: key ranges are sized so that about this many CTAs per SM exist
 _OUT_CODE = {torch.float32: 0, torch.bfloat16: 1}
@@ -306,11 +313,23 @@ def attention_bf16(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, item_
         if max_splits > 1:
             part_o = _scratch_buffer(q.device, "attn_o", b * hq * max_splits * d)
             part_ml = _scratch_buffer(q.device, "attn_ml", b * hq * max_splits * 2)
-        check(lib().psb_attention_decode_bf16(
-            q.data_ptr(), kv.data_ptr(), table.data_ptr(), table.shape[1], item_start.data_ptr(), kv_len.data_ptr(),
-            out.data_ptr(), part_o.data_ptr() if part_o is not None else None,
-            part_ml.data_ptr() if part_ml is not None else None, b, hq, hkv, d, page, w, float(scale), chunk, max_splits,
-            plan["all_single"], stream), "attention_decode")
+        po = part_o.data_ptr() if part_o is not None else None
+        pm = part_ml.data_ptr() if part_ml is not None else None
+        if (USE_TMA_DECODE and chunk >= TMA_DECODE_MIN_RANGE and kv.is_contiguous()
+                and lib().psb_attention_decode_tma_supported(hq, hkv, d, page)):
+            check(lib().psb_attention_decode_tma_bf16(
+                q.data_ptr(), kv.data_ptr(), table.data_ptr(), table.shape[1], item_start.data_ptr(), kv_len.data_ptr(),
+                out.data_ptr(), po, pm, b, hq, hkv, d, page, kv.shape[0], w, float(scale), chunk, max_splits,
+                plan["all_single"], stream), "attention_decode")
+            launch_counts["attention_decode_tma"] += 1  # the same step of the model, by which kernel
+            if max_splits > 1:
+                check(lib().psb_attention_decode_merge_bf16(po, pm, item_start.data_ptr(), kv_len.data_ptr(), out.data_ptr(), b, hq, d,
+                                                            w, chunk, max_splits, plan["all_single"], stream), "attention_merge")
+        else:
+            check(lib().psb_attention_decode_bf16(
+                q.data_ptr(), kv.data_ptr(), table.data_ptr(), table.shape[1], item_start.data_ptr(), kv_len.data_ptr(),
+                out.data_ptr(), po, pm, b, hq, hkv, d, page, w, float(scale), chunk, max_splits,
+                plan["all_single"], stream), "attention_decode")
     if plan["tcgen05"] and q.is_contiguous() and kv.is_contiguous():
         check(lib().psb_attention_prefill_tcgen05(
             q.data_ptr(), kv.data_ptr(), table.data_ptr(), table.shape[1], item_start.data_ptr(), kv_len.data_ptr(),

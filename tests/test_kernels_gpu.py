@@ -306,6 +306,16 @@ def test_kernels_refuse_what_they_cannot_run():
 
 # ---- the bfloat16 tensor-core attention kernels (prefill portions, split-KV decode) -----------------------
 
+
+@pytest.fixture(params=["lanes", "tma"])
+def decode_kernel(request, monkeypatch):
+    """Both decode attention kernels: the one in which every lane copies its pieces, and the TMA-fed one (which the
+    engine takes for long key ranges; here for every range)."""
+    from prefixserve_b200.ops import tensorcore
+    monkeypatch.setattr(tensorcore, "TMA_DECODE_MIN_RANGE", 16 if request.param == "tma" else 1 << 30)
+    return request.param
+
+
 class _Batch:
     """What ops.attention reads of a step: device offsets/lengths and the host copy of the items."""
 
@@ -334,7 +344,7 @@ def _fill_pages(seqs, table, lens, hkv, d, page, num_pages):
 @pytest.mark.parametrize("hq,hkv,d,page", [(8, 2, 64, 16), (4, 4, 64, 32), (16, 2, 128, 16), (6, 2, 64, 16), (32, 1, 64, 16)])
 @pytest.mark.parametrize("window", [None, 100])
 @pytest.mark.parametrize("mix", ["decode", "prefill", "mixed"])
-def test_attention_tensor_cores(hq, hkv, d, page, window, mix):
+def test_attention_tensor_cores(hq, hkv, d, page, window, mix, decode_kernel):
     from prefixserve_b200 import ops
     lens_old, lens_new = {
         "decode": ([31, 32, 15, 700, 0, 2999], [1, 1, 1, 1, 1, 1]),           # page edges, first token, long context (split)
@@ -362,7 +372,7 @@ def test_attention_tensor_cores(hq, hkv, d, page, window, mix):
         at += n
 
 
-def test_attention_tensor_cores_find_one_far_key():
+def test_attention_tensor_cores_find_one_far_key(decode_kernel):
     """Decode over 3,000 keys split into ranges: one early key dominates; and a prompt portion whose rows each have
     their own dominant key."""
     from prefixserve_b200 import ops
@@ -391,7 +401,7 @@ def test_attention_tensor_cores_find_one_far_key():
 
 
 @pytest.mark.parametrize("static_len,window", [(256, 50), (1024, 114), (512, 16), (4096, 300), (300, 290)])
-def test_windowed_decode_with_the_launch_shapes_of_a_captured_step(static_len, window):
+def test_windowed_decode_with_the_launch_shapes_of_a_captured_step(static_len, window, decode_kernel):
     """A captured decode step is launched with key ranges sized from the engine's longest sequence, not from the
     step's own lengths.  With a window, the keys an item reads start at the 16-aligned beginning of the window, so
     their number depends on (length - window) mod 16 and reaches window + 15: the ranges must cover that for every
@@ -482,7 +492,7 @@ def test_attention_prefill_tcgen05_every_row_finds_its_own_key():
 
 
 @pytest.mark.parametrize("seed", range(12))
-def test_attention_tensor_cores_random_steps_agree_with_the_generic_kernel(seed, monkeypatch):
+def test_attention_tensor_cores_random_steps_agree_with_the_generic_kernel(seed, monkeypatch, decode_kernel):
     """Random steps (head counts, page sizes, windows, cached lengths, portion lengths from 1 to 700 tokens) through
     the tensor-core kernels and through the generic one-warp-per-row kernel on the same pages."""
     from prefixserve_b200 import ops

@@ -135,13 +135,16 @@ def many(vocab: int, live: int, seed: int, prompt: int = 100):
     return {f"q{i}": helpers.random_tokens(vocab, prompt + (i * 7) % 23 + live + 4, seed=seed + i) for i in range(live)}
 
 
+@pytest.mark.parametrize("decode_kernel", ["lanes", "tma"])
 @pytest.mark.parametrize("live", [20, 64])
 @pytest.mark.parametrize("which", ["D", "E"])
-def test_steps_with_dozens_of_requests_match_plain(tmp_path, which, live):
+def test_steps_with_dozens_of_requests_match_plain(tmp_path, which, live, decode_kernel, monkeypatch):
     """20 and 64 requests live at once, bfloat16 weights: decode steps of 17 to 64 rows (mid-size products, the
     separate norm, rotary and activation kernels, decode attention at many requests) beside one 100-token portion."""
     from prefixserve_b200.engine.replay import Replayer
-    from prefixserve_b200.ops import library
+    from prefixserve_b200.ops import library, tensorcore
+    # both decode attention kernels: the TMA-fed one is the engine's choice for long key ranges only
+    monkeypatch.setattr(tensorcore, "TMA_DECODE_MIN_RANGE", 16 if decode_kernel == "tma" else 1 << 30)
     folder = helpers.make_folder(tmp_path / f"tiny{which}16", which, dtype=torch.bfloat16)
     cfg, tensors = plain_model.read_folder(folder)
     seqs = many(helpers.TINY[which]["cfg"].vocab_size, live, seed=500)
@@ -152,6 +155,7 @@ def test_steps_with_dozens_of_requests_match_plain(tmp_path, which, live):
     rows = run(rp, steps)
     taken = library.launch_counts - before
     assert taken["attention_decode"] > 0 and taken["silu_mul"] > 0 and taken["rope_append"] > 0, dict(taken)
+    assert (taken["attention_decode_tma"] > 0) == (decode_kernel == "tma") and library.tcgen05_status() == 0
     for rid, toks in seqs.items():
         at = sorted(p for (r, p) in rows if r == rid)
         assert at[-live:] == list(range(len(toks) - live, len(toks)))
