@@ -1,6 +1,7 @@
 // Causal grouped-query attention of prompt portions over the paged cache on the 5th-generation tensor cores.
 //
-// One CTA owns up to 256 consecutive new tokens of one request for one query head, as two tiles of 128 rows, and walks
+// One CTA owns up to 256 consecutive new tokens of one request for one query head, as two tiles of 128 rows (or, when the
+// step has too few such groups to give every SM one, up to 128 tokens as a single tile), and walks
 // the keys they may see in blocks of KB keys (128 for a head size of 64, 64 for 128).  320 threads:
 //   warp 0      producer: TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle) of the two Q tiles once, and per block of
 //               the pages that hold its keys and values, one box per page, into a ring of four stages;
@@ -102,7 +103,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                                  const int32_t* __restrict__ table, int table_width, const int32_t* __restrict__ item_start,
                                  const int32_t* __restrict__ kv_len, __nv_bfloat16* __restrict__ out, int num_items, int hq,
-                                 int hkv, int page_shift, int window, float scale, int skip_single) {
+                                 int hkv, int page_shift, int window, float scale, int skip_single, int rows_per_cta) {
   using Sh = Shape<D>;
   constexpr int KB = Sh::KB;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -120,7 +121,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     for (int i = num_items - 1; i >= 0; --i) {
       const int ni = item_start[i + 1] - item_start[i];
       if (skip_single && ni == 1) continue;
-      const int pairs = (ni + ROWS_PER_CTA - 1) / ROWS_PER_CTA;
+      const int pairs = (ni + rows_per_cta - 1) / rows_per_cta;
       if (left < pairs) { item = i; pair = pairs - 1 - left; n = ni; break; }
       left -= pairs;
     }
@@ -151,8 +152,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const int t0 = item_start[item];
   const int kvl = kv_len[item];
   const int first_pos = kvl - n;                      // position of the request's first new token
-  const int row0 = pair * ROWS_PER_CTA;               // first of this CTA's rows among the new tokens
-  const int rows_here = min(ROWS_PER_CTA, n - row0);
+  const int row0 = pair * rows_per_cta;               // first of this CTA's rows among the new tokens
+  const int rows_here = min(rows_per_cta, n - row0);
   const int ntiles = rows_here > TILE_M ? 2 : 1;
   int p_first[TILES], p_last[TILES], bend[TILES];
 #pragma unroll
@@ -494,7 +495,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 template <int D>
 int launch(const CUtensorMap& map_q, const CUtensorMap& map_kv, const void* table, int table_width, const void* item_start,
            const void* kv_len, void* out, int num_items, int num_pairs, int hq, int hkv, int page_shift, int window,
-           float scale, int skip_single, cudaStream_t stream) {
+           float scale, int skip_single, int rows_per_cta, cudaStream_t stream) {
   static PsbPerDevice configured; 
   if (!configured.get()) {
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<D>());
@@ -503,7 +504,7 @@ int launch(const CUtensorMap& map_q, const CUtensorMap& map_kv, const void* tabl
   }
   psb_launch(attention_prefill_tcgen05_kernel<D>, dim3(hq, num_pairs), dim3(THREADS), (size_t)smem_bytes<D>(), stream, map_q, map_kv,
              (const int32_t*)table, table_width, (const int32_t*)item_start, (const int32_t*)kv_len, (__nv_bfloat16*)out,
-             num_items, hq, hkv, page_shift, window, scale, skip_single);
+             num_items, hq, hkv, page_shift, window, scale, skip_single, rows_per_cta);
   return 0;
 }
 
@@ -516,16 +517,18 @@ PSB_API int psb_attention_prefill_tcgen05_supported(int D, int page_size) {
   return page_size >= 8 && page_size <= kb && (page_size & (page_size - 1)) == 0 ? 1 : 0;
 }
 
-// rows (new tokens of one request, for one head) one CTA owns
+// rows (new tokens of one request, for one head) one CTA owns at most; a launch may ask for half of that
 PSB_API int psb_attention_prefill_tcgen05_rows_per_cta() { return ROWS_PER_CTA; }
 
 // q [T, hq*D] and out [T, hq*D] bfloat16; kv [num_pages, 2, hkv, page_size, D] bfloat16; table [num_items, table_width]
-// int32; item_start [num_items+1], kv_len [num_items] int32 on the device.  num_pairs: the sum over the requests this
-// kernel owns (all, or those with more than one new token when skip_single) of ceil(new tokens / 256).
+// int32; item_start [num_items+1], kv_len [num_items] int32 on the device.  rows_per_cta: 256 or 128.  num_pairs: the sum
+// over the requests this kernel owns (all, or those with more than one new token when skip_single) of
+// ceil(new tokens / rows_per_cta).
 PSB_API int psb_attention_prefill_tcgen05(const void* q, const void* kv, const void* table, int table_width, const void* item_start,
                                           const void* kv_len, void* out, int num_items, int num_pairs, int T, int hq, int hkv,
                                           int D, int page_size, long long num_pages, int window, float scale, int skip_single,
-                                          cudaStream_t stream) {
+                                          int rows_per_cta, cudaStream_t stream) {
+  if (rows_per_cta != ROWS_PER_CTA && rows_per_cta != TILE_M) PSB_REFUSE("attention_prefill_tcgen05: a CTA owns %d or %d rows, not %d", ROWS_PER_CTA, TILE_M, rows_per_cta);
   if (!psb_attention_prefill_tcgen05_supported(D, page_size))
     PSB_REFUSE("attention_prefill_tcgen05: head size %d with pages of %d is not built (64 or 128; pages a power of two, 8..keys per block)", D, page_size);
   if (hq < 1 || hkv < 1 || hq % hkv) PSB_REFUSE("attention_prefill_tcgen05: %d query heads over %d key heads", hq, hkv);
@@ -543,8 +546,8 @@ PSB_API int psb_attention_prefill_tcgen05(const void* q, const void* kv, const v
   if (r == -1) PSB_REFUSE("attention_prefill_tcgen05: the driver does not export cuTensorMapEncodeTiled");
   if (r != 0) PSB_REFUSE("attention_prefill_tcgen05: cuTensorMapEncodeTiled failed with code %d", r);
   int rc;
-  if (D == 64) rc = launch<64>(map_q, map_kv, table, table_width, item_start, kv_len, out, num_items, num_pairs, hq, hkv, page_shift, window, scale, skip_single, stream);
-  else rc = launch<128>(map_q, map_kv, table, table_width, item_start, kv_len, out, num_items, num_pairs, hq, hkv, page_shift, window, scale, skip_single, stream);
+  if (D == 64) rc = launch<64>(map_q, map_kv, table, table_width, item_start, kv_len, out, num_items, num_pairs, hq, hkv, page_shift, window, scale, skip_single, rows_per_cta, stream);
+  else rc = launch<128>(map_q, map_kv, table, table_width, item_start, kv_len, out, num_items, num_pairs, hq, hkv, page_shift, window, scale, skip_single, rows_per_cta, stream);
   if (rc) return rc;
   PSB_LAUNCH_CHECK("attention_prefill_tcgen05");
   return 0;

@@ -247,6 +247,7 @@ def attention_bf16_supported(head_dim: int, page_size: int) -> bool:
 
 def _attention_plan(new_tokens: Sequence[int], kv_lens: Sequence[int], window: int, group: int, hkv: int, d: int, page: int,
                     sms: int, static_kv_len: int | None) -> dict:
+    hq_total = group * hkv
     """Launch shapes of a step's attention, from the host copies of the items' lengths.  The same for every layer with
     the same head counts and window, so a step works it out once."""
     b = len(new_tokens)
@@ -272,7 +273,13 @@ def _attention_plan(new_tokens: Sequence[int], kv_lens: Sequence[int], window: i
     plan["tcgen05"] = bool(USE_TCGEN05 and portions and max(portions) >= TCGEN05_PREFILL_MIN_TOKENS
                            and lib().psb_attention_prefill_tcgen05_supported(d, page))
     if plan["tcgen05"]:
+        # a CTA takes 256 rows of one head as two tiles that fill each other's waits; when that leaves more than half
+        # of the SMs without a CTA (a few hundred new tokens), one tile each and twice the CTAs (measured at 32 heads:
+        # 512-token portions 7.29 -> 7.04 ms per 2,048 tokens, 1,024-token portions would lose)
         per_cta = lib().psb_attention_prefill_tcgen05_rows_per_cta()
+        if hq_total * sum(-(-n // per_cta) for n in portions) <= sms // 2:
+            per_cta //= 2
+        plan["rows_per_cta"] = per_cta
         plan["pairs"] = sum(-(-n // per_cta) for n in portions)
     else:
         rows = lib().psb_attention_prefill_rows_per_cta(d)
@@ -334,7 +341,7 @@ def attention_bf16(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, item_
         check(lib().psb_attention_prefill_tcgen05(
             q.data_ptr(), kv.data_ptr(), table.data_ptr(), table.shape[1], item_start.data_ptr(), kv_len.data_ptr(),
             out.data_ptr(), b, plan["pairs"], t, hq, hkv, d, page, kv.shape[0], w, float(scale),
-            1 if plan["use_decode"] else 0, stream), "attention_prefill_tcgen05")
+            1 if plan["use_decode"] else 0, plan["rows_per_cta"], stream), "attention_prefill_tcgen05")
         return out
     tiles = plan.get("tiles")
     if tiles is None:  # planned for the tcgen05 kernel, which these tensors' layout rules out
