@@ -711,7 +711,7 @@ def kernel_costs(base: dict) -> list[tuple[str, float, float]]:
             (r"gemm_stream_norm_kernel<\d+, 2,", layers * 2.0 * 2 * i * h, layers * 2.0 * b * 2 * i * h),
             (r"gemm_stream_norm_kernel<.*float", 2.0 * v * h + 4.0 * b * v, 2.0 * b * v * h),
             (r"gemm_stream_kernel", layers * 2.0 * (h * q + h * i), layers * 2.0 * b * (h * q + h * i)),
-            (r"attention_decode_kernel", layers * b * ctx * 2.0 * kv * 2, layers * 4.0 * b * ctx * q),
+            (r"attention_decode(_tma)?_kernel", layers * b * ctx * 2.0 * kv * 2, layers * 4.0 * b * ctx * q),
             (r"sample_kernel", 4.0 * b * v, 0.0),
         ]
     t, prefix = base.get("portion", PREFILL_TOKENS), base.get("prefix", 0)

@@ -20,6 +20,8 @@ USE_TCGEN05 = True  # products with more rows than STREAM_M: this library's tcge
 TCGEN05_MIN_TILES = 120  # ... when the kernel would cut the product into at least this many output tiles (128 rows by
                          # 256, 192 or 128 columns, whichever gets it done in the fewest, shortest rounds); smaller ones
                          # (a few dozen rows against a narrow matrix) leave most SMs idle without split-K and go to cuBLAS
+TCGEN05_MIN_ROWS = 128   # ... and it has at least one full tile of rows: with 64 rows half of every instruction is padding
+                         # (gate/up of 64 decoded tokens: 18 us against the library's 12.7 plus 2.4 for the activation)
 WIDE_BELOW_TILES = 600   # matrices with fewer 16-row tiles than this get 16 warps per CTA instead of 8
 TCGEN05_PREFILL_MIN_TOKENS = 64   # steps whose longest prompt portion has at least this many tokens run prefill attention
                                   # on the tcgen05 kernel (tiles of 128 rows); shorter portions fill too little of a tile
@@ -140,6 +142,8 @@ def _tcgen05_ok(x: torch.Tensor, w: torch.Tensor, kind: int = 0, head_dim: int =
     if not USE_TCGEN05:
         return False
     n_out = w.shape[0] // 2 if kind == 1 else w.shape[0]
+    if x.shape[0] < TCGEN05_MIN_ROWS:
+        return False
     tiles = lib().psb_gemm_tcgen05_tiles(x.shape[0], n_out, kind, head_dim, _sms(x.device))
     return (tiles >= TCGEN05_MIN_TILES and x.shape[1] % 8 == 0 and x.shape[1] >= 8 and x.is_contiguous() and w.is_contiguous()
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)

@@ -689,6 +689,7 @@ def test_projection_of_many_tokens_rotates_and_appends_in_its_epilogue(monkeypat
     from prefixserve_b200 import ops
     from prefixserve_b200.ops import library, tensorcore
     monkeypatch.setattr(tensorcore, "TCGEN05_MIN_TILES", 1)
+    monkeypatch.setattr(tensorcore, "TCGEN05_MIN_ROWS", 1)
     g = torch.Generator().manual_seed(sum(lens_new) + d)
     table, _, num_pages = _paged_setup(torch.bfloat16, lens_new, lens_old, hq, hkv, d, page, seed=5)
     positions = torch.cat([torch.arange(o, o + n) for o, n in zip(lens_old, lens_new)]).to(torch.int32).to(DEV)

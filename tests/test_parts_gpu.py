@@ -579,8 +579,8 @@ def test_another_activation_and_the_parallel_arrangement(dtype, arrangement):
 
     tokens = helpers.random_tokens(97, 400, seed=3)
     want = forward(tokens)
-    tiles = tensorcore.TCGEN05_MIN_TILES
-    tensorcore.TCGEN05_MIN_TILES = 1     # let the 300-token portion take the tcgen05 product with the fused activation
+    tiles, rows = tensorcore.TCGEN05_MIN_TILES, tensorcore.TCGEN05_MIN_ROWS
+    tensorcore.TCGEN05_MIN_TILES = tensorcore.TCGEN05_MIN_ROWS = 1     # let the portions take the tcgen05 product with the fused activation
     before = library.launch_counts.copy()
     try:
         for cuts in ([400], [300, 40] + [1] * 60, [7, 2, 16, 3, 2, 5, 17, 2, 31, 4] * 5):
@@ -590,7 +590,7 @@ def test_another_activation_and_the_parallel_arrangement(dtype, arrangement):
             else:
                 assert helpers.rel_err(got, want) < 0.05
     finally:
-        tensorcore.TCGEN05_MIN_TILES = tiles
+        tensorcore.TCGEN05_MIN_TILES, tensorcore.TCGEN05_MIN_ROWS = tiles, rows
     taken = library.launch_counts - before
     if dtype == torch.bfloat16:
         fused = "gemm_stream_norm_gated" if arrangement == "pre_norm" else "gemm_stream_gated"

@@ -120,6 +120,7 @@ def test_bfloat16_with_the_prefill_kernels_on_small_shapes(tmp_path, kind, monke
     folder = helpers.make_folder(tmp_path / "tinyD16", "D", dtype=torch.bfloat16)
     cfg, tensors = plain_model.read_folder(folder)
     monkeypatch.setattr(tensorcore, "TCGEN05_MIN_TILES", 1)
+    monkeypatch.setattr(tensorcore, "TCGEN05_MIN_ROWS", 1)
     monkeypatch.setattr(tensorcore, "TCGEN05_PREFILL_MIN_TOKENS", 2)
     taken = {"projection": 0, "gated": 0}
     projection, gated = tensorcore.tcgen05_qkv_rope_bf16, tensorcore.gemm_tcgen05_gated

@@ -84,7 +84,8 @@ def models(tmp_path_factory):
 def test_prefix_hits_steps_ahead_and_captured_steps_match_plain(models, which, dtype, monkeypatch):
     from prefixserve_b200.ops import library, tensorcore
     folder, cfg, tensors = models[which]
-    monkeypatch.setattr(tensorcore, "TCGEN05_MIN_TILES", 1)  # tiny matrices: let the tcgen05 product take the portions
+    monkeypatch.setattr(tensorcore, "TCGEN05_MIN_TILES", 1)
+    monkeypatch.setattr(tensorcore, "TCGEN05_MIN_ROWS", 1)  # tiny matrices: let the tcgen05 product take the portions
     requests, arrivals = workload(which)
     before = library.launch_counts.copy()
     rows, counters, rp = drive(folder, dtype, requests, arrivals, pool_tokens=2048)
