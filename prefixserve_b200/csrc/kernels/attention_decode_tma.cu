@@ -38,7 +38,11 @@ struct Shape {
   static constexpr int BOX_BYTES = KEYS * 128;           // [16 keys x 64 dims] bfloat16
   static constexpr int K_BYTES = DS * BOX_BYTES;
   static constexpr int STAGE_BYTES = 2 * K_BYTES;        // keys, then values
-  static constexpr int STAGES = D == 64 ? 12 : 6;
+  // A stage must always come back to the warp that used it last (stage j % STAGES, warp j % CONSUMERS): a parity wait
+  // only tells the phase in progress from the one before it, so a warp that could reach a stage a whole round ahead of
+  // another warp's turn at it would take that warp's unfinished phase for its own finished one.
+  static constexpr int STAGES = D == 64 ? 12 : 8;
+  static_assert(STAGES % CONSUMERS == 0, "every stage belongs to one consumer warp");
   static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
   static constexpr int MERGE_BYTES = CONSUMERS * 16 * (D + 4 + 2) * 4;
   static constexpr int BAR_OFF = RING_BYTES > MERGE_BYTES ? RING_BYTES : MERGE_BYTES;

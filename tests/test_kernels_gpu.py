@@ -400,6 +400,38 @@ def test_attention_tensor_cores_find_one_far_key(decode_kernel):
         assert torch.allclose(out.float().cpu(), want[old:], atol=3e-2, rtol=3e-2), (old, new)
 
 
+@pytest.mark.parametrize("hq,hkv,d", [(24, 8, 128), (32, 8, 64)])
+def test_decode_attention_with_every_sm_busy(hq, hkv, d, decode_kernel):
+    """Dozens of requests with thousands of keys each, one key range per request: every SM holds several CTAs whose
+    copies finish in any order.  (With heads of 128 the TMA-fed kernel once had six stages for four consumer warps, so a
+    stage passed from warp to warp and a warp could take another's unfinished phase for its own: only a loaded device
+    showed it.)  Compared with the generic kernel on the same pages."""
+    from prefixserve_b200 import ops
+    from prefixserve_b200.ops import library
+    page, items = 16, 40
+    g = torch.Generator().manual_seed(11)
+    lens = [int(x) for x in torch.randint(1500, 4000, (items,), generator=g)]
+    pages_per = [-(-n // page) for n in lens]
+    num_pages = sum(pages_per) + 9
+    perm = torch.randperm(num_pages, generator=g)
+    table = torch.zeros(items, max(pages_per), dtype=torch.int32)
+    at = 0
+    for i, n in enumerate(pages_per):
+        table[i, :n] = perm[at: at + n].to(torch.int32)
+        at += n
+    kv = (torch.randn(num_pages, 2, hkv, page, d, generator=g) * 0.5).to(torch.bfloat16).to(DEV)
+    q = torch.randn(items, hq, d, generator=g).to(torch.bfloat16).to(DEV)
+    batch = _Batch([n - 1 for n in lens], [1] * items)
+    positions = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
+    token_item = torch.arange(items, dtype=torch.int32, device=DEV)
+    for _ in range(3):   # several launches back to back: the second starts while the first drains
+        fast = ops.attention(q, kv, table.to(DEV), positions, token_item, ctx=batch)
+    slow = ops.attention(q, kv, table.to(DEV), positions, token_item)
+    assert library.tcgen05_status() == 0
+    assert torch.isfinite(fast.float()).all()
+    assert torch.allclose(fast.float(), slow.float(), atol=2e-2, rtol=2e-2), float((fast.float() - slow.float()).abs().max())
+
+
 @pytest.mark.parametrize("static_len,window", [(256, 50), (1024, 114), (512, 16), (4096, 300), (300, 290)])
 def test_windowed_decode_with_the_launch_shapes_of_a_captured_step(static_len, window, decode_kernel):
     """A captured decode step is launched with key ranges sized from the engine's longest sequence, not from the
