@@ -8,14 +8,15 @@
 // 8 values serve as the (2t, 2t+1, 2t+8, 2t+9) slots of two consecutive k16 steps.  Every
 // W row is therefore read in whole 64-byte runs, and nothing is staged in shared memory.
 //
-// A CTA owns one 16-row tile of W (two tiles in the gated variant: the gate rows and the
-// matching up rows); its warps split K among themselves, keep several 32-wide k chunks in
-// flight each, and add their partial tiles through shared memory in a fixed order, so the
-// result does not depend on timing.
+// A CTA works on one 16-row tile of W at a time (two tiles in the gated variant: the gate rows
+// and the matching up rows); its warps split K among themselves and add their partial tiles
+// through shared memory in a fixed order, so the result does not depend on timing.
 //
-// Variants: plain store (bfloat16 or float32 output), and gate/up with SiLU(gate)*up in
+// Variants: plain store (bfloat16 or float32 output), and gate/up with act(gate)*up in
 // the epilogue, which writes [M, I] directly (prefixserve/model/llama.py:120-121 of
-// PrefixServe; F.linear at :113, :117, :126).
+// PrefixServe; F.linear at :113, :117, :126).  (A variant with one CTA per tile, for up to 64
+// rows, was measured against the library product at 17 to 64 rows, lost at every shape, and
+// is gone.)
 #include "common.cuh"
 
 namespace {
@@ -37,163 +38,7 @@ __device__ __forceinline__ uint4 ld_stream(const void* p) {
 }
 __device__ __forceinline__ uint4 ld_cached(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
 
-// MT: 8-row tiles of x (M <= 8*MT).  U: k chunks in flight per warp.  TILES: 1 plain, 2 gate+up.  GW: warps per CTA.
-template <int MT, int U, int TILES, int GW, typename TOut>
-__global__ void __launch_bounds__(GW * 32)
-gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ W, TOut* __restrict__ y, int M, int N,
-                    int K, int ldy, int up_offset, int act) {
-  __shared__ float part[GW][TILES][16][8 * MT + 1];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int row0 = blockIdx.x * 16;
-  // rows of W this lane reads (clamped: rows past N are computed but never stored)
-  const __nv_bfloat16* wrow[TILES][2];
-#pragma unroll
-  for (int tl = 0; tl < TILES; ++tl)
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      int row = row0 + g + 8 * r;
-      row = row < N ? row : N - 1;
-      wrow[tl][r] = W + (size_t)(row + tl * up_offset) * K + t * 8;
-    }
-  const __nv_bfloat16* xrow[MT];
-  bool xlive[MT];
-#pragma unroll
-  for (int j = 0; j < MT; ++j) {
-    const int m = 8 * j + g;
-    xlive[j] = m < M;
-    xrow[j] = x + (size_t)(xlive[j] ? m : 0) * K + t * 8;
-  }
-  float acc[TILES][MT][4];
-#pragma unroll
-  for (int tl = 0; tl < TILES; ++tl)
-#pragma unroll
-    for (int j = 0; j < MT; ++j) acc[tl][j][0] = acc[tl][j][1] = acc[tl][j][2] = acc[tl][j][3] = 0.f;
-  pdl_trigger();
-  pdl_wait();
-
-  // this warp's share of the K/32 chunks
-  const int chunks = K / 32;
-  const int per = chunks / GW, extra = chunks % GW;
-  const int c_begin = warp * per + min(warp, extra);
-  const int c_end = c_begin + per + (warp < extra ? 1 : 0);
-
-  for (int c = c_begin; c < c_end; c += U) {
-    uint4 wv[U][TILES][2];
-    uint4 xv[U][MT];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const bool on = c + u < c_end;
-      const int k = (on ? c + u : c) * 32;
-#pragma unroll
-      for (int tl = 0; tl < TILES; ++tl) {
-        wv[u][tl][0] = ld_stream(wrow[tl][0] + k);
-        wv[u][tl][1] = ld_stream(wrow[tl][1] + k);
-      }
-#pragma unroll
-      for (int j = 0; j < MT; ++j) xv[u][j] = (on && xlive[j]) ? ld_cached(xrow[j] + k) : make_uint4(0u, 0u, 0u, 0u);
-    }
-#pragma unroll
-    for (int u = 0; u < U; ++u)
-#pragma unroll
-      for (int tl = 0; tl < TILES; ++tl)
-#pragma unroll
-        for (int j = 0; j < MT; ++j) {
-          mma_bf16(acc[tl][j], wv[u][tl][0].x, wv[u][tl][1].x, wv[u][tl][0].y, wv[u][tl][1].y, xv[u][j].x, xv[u][j].y);
-          mma_bf16(acc[tl][j], wv[u][tl][0].z, wv[u][tl][1].z, wv[u][tl][0].w, wv[u][tl][1].w, xv[u][j].z, xv[u][j].w);
-        }
-  }
-  // acc[tl][j]: {y^T[row g][m = 8j+2t], [row g][8j+2t+1], [row g+8][8j+2t], [row g+8][8j+2t+1]}
-#pragma unroll
-  for (int tl = 0; tl < TILES; ++tl)
-#pragma unroll
-    for (int j = 0; j < MT; ++j) {
-      part[warp][tl][g][8 * j + 2 * t] = acc[tl][j][0];
-      part[warp][tl][g][8 * j + 2 * t + 1] = acc[tl][j][1];
-      part[warp][tl][g + 8][8 * j + 2 * t] = acc[tl][j][2];
-      part[warp][tl][g + 8][8 * j + 2 * t + 1] = acc[tl][j][3];
-    }
-  __syncthreads();
-  // one thread per (m, row): rows vary fastest so that stores of one m are contiguous
-  for (int idx = threadIdx.x; idx < 16 * 8 * MT; idx += GW * 32) {
-    const int r = idx & 15, m = idx >> 4;
-    const int row = row0 + r;
-    if (m >= M || row >= N) continue;
-    float v[TILES];
-#pragma unroll
-    for (int tl = 0; tl < TILES; ++tl) {
-      float sum = 0.f;
-#pragma unroll
-      for (int w = 0; w < GW; ++w) sum += part[w][tl][r][m];
-      v[tl] = sum;
-    }
-    float out;
-    if (TILES == 2) {
-      // the reference rounds the projection to bfloat16 before the activation
-      const float gate = __bfloat162float(__float2bfloat16_rn(v[0]));
-      const float up = __bfloat162float(__float2bfloat16_rn(v[TILES - 1]));
-      out = gate_act(gate, act) * up;
-    } else {
-      out = v[0];
-    }
-    y[(size_t)m * ldy + row] = from_float<TOut>(out);
-  }
-}
-
-template <int MT, int U, int TILES, int GW, typename TOut>
-void launch(const void* x, const void* W, void* y, int M, int N, int K, int ldy, int up_offset, int act, cudaStream_t stream) {
-  const int tiles = (N + 15) / 16;
-  psb_launch(gemm_small_m_kernel<MT, U, TILES, GW, TOut>, dim3(tiles), dim3(GW * 32), 0, stream, (const __nv_bfloat16*)x, (const __nv_bfloat16*)W,
-                                                                             (TOut*)y, M, N, K, ldy, up_offset, act);
-}
-
-// wide: 16 warps per CTA split K (few row tiles: more of the matrix in flight at once), else 8.
-template <int TILES, typename TOut>
-int dispatch_m(const void* x, const void* W, void* y, int M, int N, int K, int ldy, int up_offset, int act, int wide,
-               cudaStream_t stream) {
-  if (M <= 8) {
-    if (wide) launch<1, 4, TILES, 16, TOut>(x, W, y, M, N, K, ldy, up_offset, act, stream);
-    else launch<1, 4, TILES, 8, TOut>(x, W, y, M, N, K, ldy, up_offset, act, stream);
-  } else if (M <= 16) {
-    if (wide) launch<2, 4, TILES, 16, TOut>(x, W, y, M, N, K, ldy, up_offset, act, stream);
-    else launch<2, 4, TILES, 8, TOut>(x, W, y, M, N, K, ldy, up_offset, act, stream);
-  } else if (M <= 32) launch<4, 2, TILES, 8, TOut>(x, W, y, M, N, K, ldy, up_offset, act, stream);
-  else if (M <= 64) {
-    // the gated variant's two partial tiles per warp would not fit in shared memory at this width
-    if (TILES == 2) PSB_REFUSE("gemm_small_m_gated: M=%d is beyond this kernel (at most 32 rows)", M);
-    launch<8, 2, 1, 8, TOut>(x, W, y, M, N, K, ldy, up_offset, act, stream);
-  } else PSB_REFUSE("gemm_small_m: M=%d is beyond this kernel (at most 64 rows)", M);
-  return 0;
-}
-
 }  // namespace
-
-// y[M,N] = x[M,K] W[N,K]^T.  out_dtype: PSB_BF16 or PSB_F32.
-PSB_API int psb_gemm_small_m(const void* x, const void* W, void* y, int out_dtype, int M, int N, int K, int wide,
-                             cudaStream_t stream) {
-  if (M < 0 || N < 1 || K < 32 || K % 32) PSB_REFUSE("gemm_small_m: needs K a positive multiple of 32 (M=%d N=%d K=%d)", M, N, K);
-  if (M == 0) return 0;
-  int rc;
-  if (out_dtype == PSB_F32) rc = dispatch_m<1, float>(x, W, y, M, N, K, N, 0, 0, wide, stream);
-  else if (out_dtype == PSB_BF16) rc = dispatch_m<1, __nv_bfloat16>(x, W, y, M, N, K, N, 0, 0, wide, stream);
-  else PSB_REFUSE("gemm_small_m: unknown output dtype %d", out_dtype);
-  if (rc) return rc;
-  PSB_LAUNCH_CHECK("gemm_small_m");
-  return 0;
-}
-
-// act[M,I] = f(x W[0:I]^T) * (x W[I:2I]^T), f the activation named by its code (PsbAct),, W = [2I, K] (gate rows, then up rows), bfloat16 output.
-PSB_API int psb_gemm_small_m_gated(const void* x, const void* W, void* act, int M, int I, int K, int wide, int activation,
-                                   cudaStream_t stream) {
-  if (!psb_activation_known(activation)) PSB_REFUSE("gemm_small_m_gated: activation code %d is not built", activation);
-  if (M < 0 || I < 1 || K < 32 || K % 32) PSB_REFUSE("gemm_small_m_gated: needs K a positive multiple of 32 (M=%d I=%d K=%d)", M, I, K);
-  if (M == 0) return 0;
-  if (int rc = dispatch_m<2, __nv_bfloat16>(x, W, act, M, I, K, I, I, activation, wide, stream)) return rc;
-  PSB_LAUNCH_CHECK("gemm_small_m_gated");
-  return 0;
-}
-
-// most rows of x the plain (gated = 0) or the gated (gated = 1) variant takes
-PSB_API int psb_gemm_small_m_max_rows(int gated) { return gated ? 32 : 64; }
 
 // ------------------------------------------------------------------------------------------------------------------
 // Streaming variant for at most 16 rows of x: persistent CTAs (one per SM) of 16 warps that split K; every lane feeds

@@ -70,12 +70,6 @@ _SIGNATURES: dict[str, list] = {
     "psb_attention_decode_tma_status": [],
     # (part_o, part_ml, item_start, kv_len, out, num_items, hq, D, window, chunk, max_splits, all_single, stream)
     "psb_attention_decode_merge_bf16": [P, P, P, P, P, I, I, I, I, I, I, I, P],
-    # (x, W, y, out_dtype, M, N, K, wide, stream)
-    "psb_gemm_small_m": [P, P, P, I, I, I, I, I, P],
-    # (x, W, act, M, I, K, wide, activation, stream)
-    "psb_gemm_small_m_gated": [P, P, P, I, I, I, I, I, P],
-    # (gated) -> most rows of x
-    "psb_gemm_small_m_max_rows": [I],
     # (x, W, y, out_dtype, M, N, K, sms, stream)
     "psb_gemm_stream": [P, P, P, I, I, I, I, I, P],
     # (x, W, act, M, I, K, sms, activation, stream)

@@ -11,11 +11,6 @@ from .library import check, launch_counts, lib, stream_handle
 
 # Tuning, set from measurements on B200 at Llama-1B sizes:
 STREAM_M = 16       # rows up to which the persistent streaming kernel is used (its limit is 16)
-STREAM_MIN_TILES = 0     # ... for matrices with at least this many 16-row tiles.  0: always.  The streaming kernel holds
-                         # one CTA per SM by its shared memory, so kernels that start early (programmatic dependent
-                         # launch) cannot pile up on the SMs that free up first, which the one-tile-per-CTA kernel does.
-SMALL_M = 8         # rows up to which the one-tile-per-CTA kernel is used when the streaming kernel is not
-SMALL_M_GATED = 8   # same for the gate/up product with the fused activation
 USE_TCGEN05 = True  # products with more rows than STREAM_M: this library's tcgen05/TMEM/TMA kernel (else cuBLAS)
 TCGEN05_MIN_TILES = 120  # ... when the kernel would cut the product into at least this many output tiles (128 rows by
                          # 256, 192 or 128 columns, whichever gets it done in the fewest, shortest rounds); smaller ones
@@ -39,18 +34,6 @@ _OUT_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
 def small_m_ok(m: int, k: int, limit: int) -> bool:
     return 0 < m <= limit and k >= 32 and k % 32 == 0
-
-
-def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, wide: bool | None = None) -> torch.Tensor:
-    """The weight-streaming kernel itself (at most 64 rows, K a multiple of 32)."""
-    m, k = x.shape
-    n = w.shape[0]
-    if wide is None:
-        wide = (n + 15) // 16 < WIDE_BELOW_TILES and k // 32 >= 32
-    y = torch.empty((m, n), dtype=out_dtype, device=x.device)
-    check(lib().psb_gemm_small_m(x.data_ptr(), w.data_ptr(), y.data_ptr(), _OUT_CODE[out_dtype], m, n, k, 1 if wide else 0,
-                                 stream_handle()), "gemm_small_m")
-    return y
 
 
 def gemm_stream(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
@@ -194,10 +177,8 @@ def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> tor
     """
     m, k = x.shape
     if out_dtype in _OUT_CODE and x.is_contiguous() and w.is_contiguous():
-        if small_m_ok(m, k, min(STREAM_M, 16)) and ((w.shape[0] + 15) // 16 >= STREAM_MIN_TILES or m > SMALL_M):
+        if small_m_ok(m, k, min(STREAM_M, 16)):
             return gemm_stream(x, w, out_dtype)
-        if small_m_ok(m, k, SMALL_M):
-            return gemm_small_m(x, w, out_dtype)
         if out_dtype == torch.bfloat16 and m > 0 and _tcgen05_ok(x, w):
             return gemm_tcgen05(x, w)
     if out_dtype == torch.float32:  # logits of many rows: the sums leave the library in float32, never rounded to bfloat16
@@ -206,22 +187,17 @@ def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> tor
     return y if out_dtype == y.dtype else y.to(out_dtype)
 
 
-def gated_linear_bf16(x: torch.Tensor, w_gate_up: torch.Tensor, limit: int | None = None, activation: int = 0) -> torch.Tensor | None:
-    """act(x Wg^T) * (x Wu^T) in one kernel for few rows; None when the fused kernel does not take the shape."""
+def gated_linear_bf16(x: torch.Tensor, w_gate_up: torch.Tensor, activation: int = 0) -> torch.Tensor | None:
+    """act(x Wg^T) * (x Wu^T) in one kernel (few rows: the streaming product; many: the tcgen05 product); None when
+    neither takes the shape."""
     m, k = x.shape
-    if (limit is None and small_m_ok(m, k, min(STREAM_M, 16)) and w_gate_up.shape[0] % 2 == 0 and x.is_contiguous()
-            and w_gate_up.is_contiguous()):
-        return gemm_stream_gated(x, w_gate_up, activation)
-    if limit is None and m > max(STREAM_M, SMALL_M_GATED) and w_gate_up.shape[0] % 2 == 0 and _tcgen05_ok(x, w_gate_up, 1):
-        return gemm_tcgen05_gated(x, w_gate_up, activation)
-    if not (small_m_ok(m, k, SMALL_M_GATED if limit is None else limit) and w_gate_up.shape[0] % 2 == 0 and x.is_contiguous() and w_gate_up.is_contiguous()):
+    if w_gate_up.shape[0] % 2 or not (x.is_contiguous() and w_gate_up.is_contiguous()):
         return None
-    inter = w_gate_up.shape[0] // 2
-    act = torch.empty((m, inter), dtype=torch.bfloat16, device=x.device)
-    wide = 1 if (inter + 15) // 16 < WIDE_BELOW_TILES and k // 32 >= 32 else 0
-    check(lib().psb_gemm_small_m_gated(x.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(), m, inter, k, wide, activation,
-                                       stream_handle()), "gemm_small_m_gated")
-    return act
+    if small_m_ok(m, k, min(STREAM_M, 16)):
+        return gemm_stream_gated(x, w_gate_up, activation)
+    if m > STREAM_M and _tcgen05_ok(x, w_gate_up, 1):
+        return gemm_tcgen05_gated(x, w_gate_up, activation)
+    return None
 
 
 _sm_count: dict[int, int] = {}

@@ -562,42 +562,21 @@ def test_attention_shapes_outside_the_tensor_core_kernels_fall_back():
 
 # ---- the weight-streaming product for few rows ---------------------------------------------------------------
 
-@pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 31, 32, 33, 64])
-@pytest.mark.parametrize("n,k", [(48, 64), (333, 96), (1000, 2048), (16, 8192)])
-@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("wide", [False, True])
-def test_gemm_small_m(m, n, k, out_dtype, wide):
-    from prefixserve_b200.ops.tensorcore import gemm_small_m
-    linear_bf16 = lambda a, b, c: gemm_small_m(a, b, c, wide=wide)  # noqa: E731
-    x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
-    w = torch.randn(n, k, device=DEV).to(torch.bfloat16)
-    got = linear_bf16(x, w, out_dtype)
-    want = x.double() @ w.double().t()
-    assert got.dtype == out_dtype and got.shape == (m, n)
-    if out_dtype == torch.float32:
-        assert torch.allclose(got.double(), want, rtol=1e-4, atol=1e-3 * math.sqrt(k))
-    else:
-        assert torch.allclose(got.double(), want, rtol=1e-2, atol=1e-2 * math.sqrt(k))
-    # a row alone gives bit-identical results: its sum order does not depend on the batch
-    # (the 16-warp split exists for up to 16 rows; beyond that both settings use 8 warps)
-    alone = linear_bf16(x[m - 1:].contiguous(), w, out_dtype)
-    if m <= 16 or not wide:
-        assert torch.equal(alone[0], got[m - 1])
-
-
 @pytest.mark.parametrize("m", [1, 8, 13, 32, 40])
 @pytest.mark.parametrize("inter,k", [(40, 64), (112, 96), (1000, 2048)])
 def test_gated_linear(m, inter, k):
+    """Whatever route the row count takes (streaming product, library product plus the activation kernel)."""
     from prefixserve_b200 import ops
-    from prefixserve_b200.ops.tensorcore import gated_linear_bf16
     x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
     w = (torch.randn(2 * inter, k, device=DEV) / math.sqrt(k)).to(torch.bfloat16)
-    got = gated_linear_bf16(x, w, limit=32) if m <= 32 else ops.gated_linear(x, w)
-    assert torch.allclose(got.float(), ops.gated_linear(x, w).float(), rtol=3e-2, atol=3e-2)
+    got = ops.gated_linear(x, w)
     y = x.double() @ w.double().t()
     want = torch.nn.functional.silu(y[:, :inter]) * y[:, inter:]
     assert got.shape == (m, inter)
     assert torch.allclose(got.double(), want, rtol=3e-2, atol=3e-2)
+    gelu = ops.gated_linear(x, w, "gelu_tanh")
+    want = torch.nn.functional.gelu(y[:, :inter], approximate="tanh") * y[:, inter:]
+    assert torch.allclose(gelu.double(), want, rtol=3e-2, atol=3e-2)
 
 
 @pytest.mark.parametrize("m", [1, 5, 8, 9, 16])
