@@ -15,6 +15,9 @@
 //               when that has grown by more than 2^8, and only then is the row of O rescaled (tcgen05.ld, multiply,
 //               tcgen05.st), which is rare.
 // The two tiles alternate on the tensor cores: while one tile's rows are in the softmax, the other's products run.
+// A step with few such CTAs and long cached prefixes (a prompt portion of a few hundred tokens) may also cut the keys
+// into ranges: CTA (head, rows, range) then walks its share of the blocks and leaves an unnormalised partial result
+// (float32 output, reference exponent, sum) per row, which attention_prefill_merge_kernel combines.
 // Rows are [token, head*D] of the rotated queries (prefixserve/model/llama.py:113-116 of PrefixServe computes the same
 // attention with a library kernel, prefixserve/model/attention.py:58-104); keys and values come from the pages named
 // by the request's block table; query at position p sees keys max(0, p-window+1) .. p.
@@ -103,7 +106,8 @@ __global__ void __launch_bounds__(THREADS, 1)
 attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                                  const int32_t* __restrict__ table, int table_width, const int32_t* __restrict__ item_start,
                                  const int32_t* __restrict__ kv_len, __nv_bfloat16* __restrict__ out, int num_items, int hq,
-                                 int hkv, int page_shift, int window, float scale, int skip_single, int rows_per_cta) {
+                                 int hkv, int page_shift, int window, float scale, int skip_single, int rows_per_cta,
+                                 int kv_splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
   using Sh = Shape<D>;
   constexpr int KB = Sh::KB;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -163,13 +167,18 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     bend[t] = p_last[t] / KB;
   }
   const int lo_key = (window > 0 && p_first[0] - window + 1 > 0) ? p_first[0] - window + 1 : 0;
-  const int b0 = lo_key / KB;
-  const int nblk = bend[ntiles - 1] - b0 + 1;
+  // the blocks this CTA's rows may see, and the share of them that is this CTA's key range (all of them without ranges)
+  const int b_lo = lo_key / KB;
+  const int per_range = (bend[ntiles - 1] - b_lo + kv_splits) / kv_splits;
+  const int b0 = b_lo + (int)blockIdx.z * per_range;
+#pragma unroll
+  for (int t = 0; t < TILES; ++t) bend[t] = min(bend[t], b0 + per_range - 1);
+  const int nblk = max(0, bend[ntiles - 1] - b0 + 1);
   const int kvh = head / (hq / hkv);
   // The tiles' blocks in the order their S is computed: (0,0) (1,0) (0,1) (1,1) ... while tile 0 still has blocks (n0 of
   // them), then tile 1's remaining ones.  The e-th of them uses S buffer e % 3, so S of a block is computed while the
   // softmax of the two blocks before it is still running.
-  const int n0 = bend[0] - b0 + 1;
+  const int n0 = max(0, bend[0] - b0 + 1);   // a range may hold nothing that tile 0's (earlier) rows can see
   const int total = ntiles == 2 ? n0 + nblk : n0;
   auto seq_of = [&](int t, int i) { return ntiles == 1 ? i : (i < n0 ? 2 * i + t : n0 + i); };
 
@@ -338,7 +347,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       // products use the same reference, and the quotient at the end does not depend on it.
       float m_run = -INFINITY, l_run = 0.f;
       bool ok = true;
-      const int my_blocks = bend[t] - b0 + 1;
+      const int my_blocks = max(0, bend[t] - b0 + 1);
       // The row's scores of a block, 32 keys a chunk, stay in registers from the maximum to the exponentials.  They are
       // asked for as early as they can be: a block's scores are computed up to three blocks ahead, so the loads of
       // block i+1 go out as soon as the exponentials of block i have let go of the registers, and arrive while this
@@ -356,7 +365,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         for (int cc = 0; cc < NCH; ++cc) tmem_ld32(s_addr + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[cc][0]));
         return true;
       };
-      ok = request_scores(0);
+      if (my_blocks > 0) ok = request_scores(0);
       for (int i = 0; ok && i < my_blocks; ++i) {
         const int key0 = (b0 + i) * KB;
         const int e = seq_of(t, i);
@@ -452,11 +461,35 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         if (lane == 0) mbar_arrive(&bars->p_ready[t]);
       }
       // the quotient
-      if (ok) {
+      if (ok && my_blocks > 0) {
         ok = mbar_wait(&bars->o_full[t], (my_blocks - 1) & 1, abort, 3);
         ok = __all_sync(0xffffffffu, ok);
       }
-      if (ok) {
+      if (ok && kv_splits > 1) {
+        // one key range of several: the row's unnormalised output with the exponent it refers to and its sum
+        fence_after();
+        const size_t slot = ((size_t)(t0 + row) * hq + head) * kv_splits + blockIdx.z;
+        if (valid) {
+          part_ml[slot * 2] = (my_blocks > 0 && m_run != -INFINITY) ? m_run * c : -INFINITY;
+          part_ml[slot * 2 + 1] = my_blocks > 0 ? l_run : 0.f;
+        }
+        if (my_blocks > 0) {
+          float* dst = part_o + slot * D;
+#pragma unroll 1
+          for (int cc = 0; cc < D / 32; ++cc) {
+            uint32_t v[32];
+            tmem_ld32(o_addr + cc * 32, v);
+            tmem_ld_wait();
+            if (valid) {
+#pragma unroll
+              for (int k = 0; k < 32; k += 4)
+                *reinterpret_cast<float4*>(dst + cc * 32 + k) = make_float4(__uint_as_float(v[k]), __uint_as_float(v[k + 1]),
+                                                                            __uint_as_float(v[k + 2]), __uint_as_float(v[k + 3]));
+            }
+          }
+        }
+        fence_before();
+      } else if (ok) {
         fence_after();
         const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
         __nv_bfloat16* dst = out + ((size_t)(t0 + row) * hq + head) * D;
@@ -492,19 +525,63 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   }
 }
 
+// One warp per (token, head): combines the key ranges' partial results.  out = sum_s w_s O_s / sum_s w_s l_s with
+// w_s = 2^(e_s - max e); a range that saw nothing (sum 0) has weight 0 and its output is not read.
+template <int D>
+__global__ void attention_prefill_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                               const int32_t* __restrict__ token_item, const int32_t* __restrict__ item_start,
+                                               __nv_bfloat16* __restrict__ out, int T, int hq, int kv_splits, int skip_single) {
+  pdl_trigger();
+  const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  const int row = unit / hq, head = unit - row * hq;
+  int n = 0;
+  if (row < T) {
+    const int item = token_item[row];
+    n = item_start[item + 1] - item_start[item];
+  }
+  pdl_wait();
+  if (row >= T || (skip_single && n == 1)) return;  // a single token's row belongs to the decode kernel
+  const size_t base = ((size_t)row * hq + head) * kv_splits;
+  const float e = lane < kv_splits ? part_ml[(base + lane) * 2] : -INFINITY;
+  const float l = lane < kv_splits ? part_ml[(base + lane) * 2 + 1] : 0.f;
+  const float top = warp_max(e);
+  float w = (l > 0.f && e != -INFINITY) ? ex2(e - top) : 0.f;
+  const float total = warp_sum(w * l);
+  const float inv = total > 0.f ? 1.f / total : 0.f;
+  float acc[D / 32];
+#pragma unroll
+  for (int i = 0; i < D / 32; ++i) acc[i] = 0.f;
+  for (int s = 0; s < kv_splits; ++s) {
+    const float ws = __shfl_sync(0xffffffffu, w, s);
+    if (ws == 0.f) continue;
+#pragma unroll
+    for (int i = 0; i < D / 32; ++i) acc[i] = fmaf(ws, part_o[(base + s) * D + lane + 32 * i], acc[i]);
+  }
+  __nv_bfloat16* dst = out + ((size_t)row * hq + head) * D;
+#pragma unroll
+  for (int i = 0; i < D / 32; ++i) dst[lane + 32 * i] = __float2bfloat16_rn(acc[i] * inv);
+}
+
 template <int D>
 int launch(const CUtensorMap& map_q, const CUtensorMap& map_kv, const void* table, int table_width, const void* item_start,
            const void* kv_len, void* out, int num_items, int num_pairs, int hq, int hkv, int page_shift, int window,
-           float scale, int skip_single, int rows_per_cta, cudaStream_t stream) {
+           float scale, int skip_single, int rows_per_cta, int kv_splits, void* part_o, void* part_ml, const void* token_item,
+           int T, cudaStream_t stream) {
   static PsbPerDevice configured; 
   if (!configured.get()) {
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<D>());
     if (e != cudaSuccess) PSB_REFUSE("attention_prefill_tcgen05: cannot reserve %d bytes of shared memory: %s", smem_bytes<D>(), cudaGetErrorString(e));
     configured.set(); 
   }
-  psb_launch(attention_prefill_tcgen05_kernel<D>, dim3(hq, num_pairs), dim3(THREADS), (size_t)smem_bytes<D>(), stream, map_q, map_kv,
+  psb_launch(attention_prefill_tcgen05_kernel<D>, dim3(hq, num_pairs, kv_splits), dim3(THREADS), (size_t)smem_bytes<D>(), stream, map_q, map_kv,
              (const int32_t*)table, table_width, (const int32_t*)item_start, (const int32_t*)kv_len, (__nv_bfloat16*)out,
-             num_items, hq, hkv, page_shift, window, scale, skip_single, rows_per_cta);
+             num_items, hq, hkv, page_shift, window, scale, skip_single, rows_per_cta, kv_splits, (float*)part_o, (float*)part_ml);
+  if (kv_splits > 1) {
+    const long long units = (long long)T * hq;
+    psb_launch(attention_prefill_merge_kernel<D>, dim3((unsigned)((units + 3) / 4)), dim3(128), 0, stream, (const float*)part_o,
+               (const float*)part_ml, (const int32_t*)token_item, (const int32_t*)item_start, (__nv_bfloat16*)out, T, hq, kv_splits,
+               skip_single);
+  }
   return 0;
 }
 
@@ -523,11 +600,16 @@ PSB_API int psb_attention_prefill_tcgen05_rows_per_cta() { return ROWS_PER_CTA; 
 // q [T, hq*D] and out [T, hq*D] bfloat16; kv [num_pages, 2, hkv, page_size, D] bfloat16; table [num_items, table_width]
 // int32; item_start [num_items+1], kv_len [num_items] int32 on the device.  rows_per_cta: 256 or 128.  num_pairs: the sum
 // over the requests this kernel owns (all, or those with more than one new token when skip_single) of
-// ceil(new tokens / rows_per_cta).
+// ceil(new tokens / rows_per_cta).  kv_splits > 1: the keys are cut into that many ranges; part_o (float32
+// [T, hq, kv_splits, D]) and part_ml ([T, hq, kv_splits, 2]) take the ranges' partial results, token_item ([T] int32)
+// tells the merge which request a row belongs to.
 PSB_API int psb_attention_prefill_tcgen05(const void* q, const void* kv, const void* table, int table_width, const void* item_start,
                                           const void* kv_len, void* out, int num_items, int num_pairs, int T, int hq, int hkv,
                                           int D, int page_size, long long num_pages, int window, float scale, int skip_single,
-                                          int rows_per_cta, cudaStream_t stream) {
+                                          int rows_per_cta, int kv_splits, void* part_o, void* part_ml, const void* token_item,
+                                          cudaStream_t stream) {
+  if (kv_splits < 1 || kv_splits > 32 || (kv_splits > 1 && (!part_o || !part_ml || !token_item)))
+    PSB_REFUSE("attention_prefill_tcgen05: %d key ranges (1 to 32), or their scratch is missing", kv_splits);
   if (rows_per_cta != ROWS_PER_CTA && rows_per_cta != TILE_M) PSB_REFUSE("attention_prefill_tcgen05: a CTA owns %d or %d rows, not %d", ROWS_PER_CTA, TILE_M, rows_per_cta);
   if (!psb_attention_prefill_tcgen05_supported(D, page_size))
     PSB_REFUSE("attention_prefill_tcgen05: head size %d with pages of %d is not built (64 or 128; pages a power of two, 8..keys per block)", D, page_size);
@@ -546,8 +628,8 @@ PSB_API int psb_attention_prefill_tcgen05(const void* q, const void* kv, const v
   if (r == -1) PSB_REFUSE("attention_prefill_tcgen05: the driver does not export cuTensorMapEncodeTiled");
   if (r != 0) PSB_REFUSE("attention_prefill_tcgen05: cuTensorMapEncodeTiled failed with code %d", r);
   int rc;
-  if (D == 64) rc = launch<64>(map_q, map_kv, table, table_width, item_start, kv_len, out, num_items, num_pairs, hq, hkv, page_shift, window, scale, skip_single, rows_per_cta, stream);
-  else rc = launch<128>(map_q, map_kv, table, table_width, item_start, kv_len, out, num_items, num_pairs, hq, hkv, page_shift, window, scale, skip_single, rows_per_cta, stream);
+  if (D == 64) rc = launch<64>(map_q, map_kv, table, table_width, item_start, kv_len, out, num_items, num_pairs, hq, hkv, page_shift, window, scale, skip_single, rows_per_cta, kv_splits, part_o, part_ml, token_item, T, stream);
+  else rc = launch<128>(map_q, map_kv, table, table_width, item_start, kv_len, out, num_items, num_pairs, hq, hkv, page_shift, window, scale, skip_single, rows_per_cta, kv_splits, part_o, part_ml, token_item, T, stream);
   if (rc) return rc;
   PSB_LAUNCH_CHECK("attention_prefill_tcgen05");
   return 0;

@@ -270,7 +270,7 @@ def attention(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, positions:
         extras = getattr(ctx, "extras", None)
         fast = attention_bf16(q, kv, table, ctx.item_start, ctx.kv_len, None, None, window=window, scale=scale,
                               static_kv_len=extras.get("static_kv_len") if extras is not None else None,
-                              plans=extras, items=ctx.items)
+                              plans=extras, items=ctx.items, token_item=_i32(token_item, "token-to-item map"))
         if fast is not None:
             return fast
     return attention_generic(q, kv, table, positions, token_item, window=window, scale=scale)

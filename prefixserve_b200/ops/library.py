@@ -55,8 +55,8 @@ _SIGNATURES: dict[str, list] = {
     # () -> rows per CTA
     "psb_attention_prefill_tcgen05_rows_per_cta": [],
     # (q, kv, table, table_width, item_start, kv_len, out, num_items, num_pairs, T, hq, hkv, D, page_size, num_pages,
-    #  window, scale, skip_single, rows_per_cta, stream)
-    "psb_attention_prefill_tcgen05": [P, P, P, I, P, P, P, I, I, I, I, I, I, I, L, I, F, I, I, P],
+    #  window, scale, skip_single, rows_per_cta, kv_splits, part_o, part_ml, token_item, stream)
+    "psb_attention_prefill_tcgen05": [P, P, P, I, P, P, P, I, I, I, I, I, I, I, L, I, F, I, I, I, P, P, P, P],
     # () -> 0 while no bounded wait of the tcgen05 attention kernel has ever run out
     "psb_attention_tcgen05_status": [],
     # (q, kv, table, table_width, item_start, kv_len, out, part_o, part_ml, num_items, hq, hkv, D, page_size, window,

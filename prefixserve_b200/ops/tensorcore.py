@@ -27,6 +27,8 @@ USE_TMA_DECODE = True     # decode attention: the kernel whose keys and values t
                           # with 8 requests (ranges of 512 keys, 32 tiles a CTA) 0.90 against 0.855: a CTA that short pays
                           # more for filling its ring through one issuing lane than the ring then saves
 TMA_DECODE_MIN_RANGE = 1024
+PREFILL_MAX_KEY_RANGES = 8        # prefill attention with few CTAs: at most this many key ranges ...
+PREFILL_MIN_BLOCKS_PER_RANGE = 4  # ... of at least this many key blocks each (a range pays for a partial result per row)
 MIN_KEY_RANGE = 128       # split-KV: no key range shorter than this
 DECODE_CTAS_PER_SM = 4   # split-KV: key ranges are sized so that about this many CTAs per SM exist
 _OUT_CODE = {torch.float32: 0, torch.bfloat16: 1}
@@ -227,9 +229,9 @@ def attention_bf16_supported(head_dim: int, page_size: int) -> bool:
 
 def _attention_plan(new_tokens: Sequence[int], kv_lens: Sequence[int], window: int, group: int, hkv: int, d: int, page: int,
                     sms: int, static_kv_len: int | None) -> dict:
-    hq_total = group * hkv
     """Launch shapes of a step's attention, from the host copies of the items' lengths.  The same for every layer with
     the same head counts and window, so a step works it out once."""
+    hq_total = group * hkv
     b = len(new_tokens)
     singles = [kvl for n, kvl in zip(new_tokens, kv_lens) if n == 1]
     if static_kv_len is not None:  # a captured step: its single tokens may later sit at any length up to this one
@@ -257,8 +259,18 @@ def _attention_plan(new_tokens: Sequence[int], kv_lens: Sequence[int], window: i
         # of the SMs without a CTA (a few hundred new tokens), one tile each and twice the CTAs (measured at 32 heads:
         # 512-token portions 7.29 -> 7.04 ms per 2,048 tokens, 1,024-token portions would lose)
         per_cta = lib().psb_attention_prefill_tcgen05_rows_per_cta()
-        if hq_total * sum(-(-n // per_cta) for n in portions) <= sms // 2:
-            per_cta //= 2
+        ctas = hq_total * sum(-(-n // per_cta) for n in portions)
+        plan["kv_splits"] = 1
+        if ctas <= sms // 2:
+            # few CTAs: cut the keys into ranges if the portions' contexts are long enough (at least
+            # PREFILL_MIN_BLOCKS_PER_RANGE blocks a range), else give every CTA one tile instead of two
+            longest = static_kv_len if static_kv_len is not None else max(kvl for n, kvl in zip(new_tokens, kv_lens) if not (plan["use_decode"] and n == 1))
+            blocks = -(-longest // (128 if d == 64 else 64))
+            splits = min(PREFILL_MAX_KEY_RANGES, sms // ctas, blocks // PREFILL_MIN_BLOCKS_PER_RANGE)
+            if splits >= 2:
+                plan["kv_splits"] = splits
+            else:
+                per_cta //= 2
         plan["rows_per_cta"] = per_cta
         plan["pairs"] = sum(-(-n // per_cta) for n in portions)
     else:
@@ -269,7 +281,8 @@ def _attention_plan(new_tokens: Sequence[int], kv_lens: Sequence[int], window: i
 
 def attention_bf16(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, item_start: torch.Tensor, kv_len: torch.Tensor,
                    new_tokens: Sequence[int] | None, kv_lens: Sequence[int] | None, *, window: int | None, scale: float,
-                   static_kv_len: int | None = None, plans: dict | None = None, items=None) -> torch.Tensor | None:
+                   static_kv_len: int | None = None, plans: dict | None = None, items=None,
+                   token_item: torch.Tensor | None = None) -> torch.Tensor | None:
     """Tensor-core attention for a step.  ``new_tokens``/``kv_lens`` are the host copies of what ``item_start`` and
     ``kv_len`` hold on the device (or ``items`` with ``.start``/``.end``, read only when no plan is cached yet).
     Returns None when no kernel here takes the shape (the caller falls back).  ``plans``: a dict that lives as long as
@@ -318,10 +331,16 @@ def attention_bf16(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, item_
                 out.data_ptr(), po, pm, b, hq, hkv, d, page, w, float(scale), chunk, max_splits,
                 plan["all_single"], stream), "attention_decode")
     if plan["tcgen05"] and q.is_contiguous() and kv.is_contiguous():
+        splits = plan["kv_splits"] if token_item is not None else 1
+        po = pm = None
+        if splits > 1:
+            po = _scratch_buffer(q.device, "prefill_o", t * hq * splits * d).data_ptr()
+            pm = _scratch_buffer(q.device, "prefill_ml", t * hq * splits * 2).data_ptr()
         check(lib().psb_attention_prefill_tcgen05(
             q.data_ptr(), kv.data_ptr(), table.data_ptr(), table.shape[1], item_start.data_ptr(), kv_len.data_ptr(),
             out.data_ptr(), b, plan["pairs"], t, hq, hkv, d, page, kv.shape[0], w, float(scale),
-            1 if plan["use_decode"] else 0, plan["rows_per_cta"], stream), "attention_prefill_tcgen05")
+            1 if plan["use_decode"] else 0, plan["rows_per_cta"], splits, po, pm,
+            token_item.data_ptr() if token_item is not None else None, stream), "attention_prefill_tcgen05")
         return out
     tiles = plan.get("tiles")
     if tiles is None:  # planned for the tcgen05 kernel, which these tensors' layout rules out

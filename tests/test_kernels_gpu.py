@@ -523,6 +523,50 @@ def test_attention_prefill_tcgen05_every_row_finds_its_own_key():
     assert torch.allclose(out.float().cpu(), want[old:], atol=3e-2, rtol=3e-2)
 
 
+@pytest.mark.parametrize("d,page", [(64, 16), (128, 32)])
+@pytest.mark.parametrize("ranges,min_blocks", [(2, 1), (3, 1), (5, 2), (8, 1)])
+@pytest.mark.parametrize("window", [None, 260])
+def test_attention_prefill_over_several_key_ranges(d, page, ranges, min_blocks, window, monkeypatch):
+    """A short portion over a long cached prefix: the keys are cut into ranges, each CTA keeps a partial result and a
+    second kernel merges them.  Range counts that do not divide the number of key blocks, ranges that come out empty
+    (a launch sized for a longer sequence than the step has; a window that leaves the first ranges nothing; a
+    neighbouring item without a prefix), and one key per row, anywhere before it, that must win."""
+    from prefixserve_b200 import ops
+    from prefixserve_b200.ops import library, tensorcore
+    monkeypatch.setattr(tensorcore, "TCGEN05_PREFILL_MIN_TOKENS", 2)
+    monkeypatch.setattr(tensorcore, "PREFILL_MAX_KEY_RANGES", ranges)
+    monkeypatch.setattr(tensorcore, "PREFILL_MIN_BLOCKS_PER_RANGE", min_blocks)
+    hq, hkv = 4, 2
+    lens_old, lens_new = [1390, 0, 700], [170, 40, 130]
+    table, seqs, num_pages = _paged_setup(torch.bfloat16, lens_new, lens_old, hq, hkv, d, page, seed=21)
+    for s, o, n in zip(seqs, lens_old, lens_new):
+        for row in range(o, o + n):
+            lo = max(0, row - window + 1) if window else 0
+            key = lo + (row * 7919) % (row + 1 - lo)
+            s["q"][row, :, row % d] = 30.0
+            s["k"][key, :, row % d] += 30.0
+    totals = [o + n for o, n in zip(lens_old, lens_new)]
+    kv = _fill_pages(seqs, table, totals, hkv, d, page, num_pages)
+    q = torch.cat([s["q"][o:] for s, o in zip(seqs, lens_old)]).to(torch.bfloat16).to(DEV)
+    positions = torch.cat([torch.arange(o, o + n) for o, n in zip(lens_old, lens_new)]).to(torch.int32).to(DEV)
+    token_item = torch.cat([torch.full((n,), i) for i, n in enumerate(lens_new)]).to(torch.int32).to(DEV)
+    batch = _Batch(lens_old, lens_new)
+    bf = lambda x: x.to(torch.bfloat16).float()  # noqa: E731
+    for static_len in (None, 4096):
+        plan = tensorcore._attention_plan(lens_new, totals, int(window or 0), hq // hkv, hkv, d, page, 148, static_len)
+        assert plan["tcgen05"] and plan["kv_splits"] > 1, plan
+        out = tensorcore.attention_bf16(q, kv, table.to(DEV), batch.item_start, batch.kv_len, lens_new, totals, window=window,
+                                        scale=1.0 / math.sqrt(d), static_kv_len=static_len, token_item=token_item)
+        assert library.tcgen05_status() == 0
+        at = 0
+        for i, (s, o, n) in enumerate(zip(seqs, lens_old, lens_new)):
+            want = plain_model.causal_attention(bf(s["q"]), bf(s["k"]), bf(s["v"]), window=window)[o:].reshape(n, hq * d)
+            got = out[at:at + n].float().cpu()
+            assert torch.isfinite(got).all(), (i, static_len)
+            assert torch.allclose(got, want, atol=3e-2, rtol=3e-2), (i, static_len, float((got - want).abs().max()))
+            at += n
+
+
 @pytest.mark.parametrize("seed", range(12))
 def test_attention_tensor_cores_random_steps_agree_with_the_generic_kernel(seed, monkeypatch, decode_kernel):
     """Random steps (head counts, page sizes, windows, cached lengths, portion lengths from 1 to 700 tokens) through
