@@ -183,28 +183,40 @@ class Engine:
             raise EngineError(f"a tcgen05 kernel gave up waiting on a barrier (status {status:#x}); results are void")
 
     def capture_decode_graphs(self, batch_sizes) -> int:
-        """Captures the pure-decode step for the given batch sizes now, so that no request pays for a capture
-        (a few milliseconds each) in the middle of serving.  Needs the cache to have that many free slots and pages.
-        Returns how many graphs were captured."""
+        """Captures the pure-decode step for the given batch sizes and every class of sequence lengths now, so that no
+        request pays for a capture (a few milliseconds each) in the middle of serving.  Needs the cache to have that
+        many free slots and pages.  Returns how many graphs were captured."""
         if not self.runner.use_graphs:
             return 0
         done = 0
         for b in sorted(set(int(x) for x in batch_sizes)):
-            if b < 1 or b > self.cfg.max_num_seqs or b in self.runner._graphs:
+            if b < 1 or b > self.cfg.max_num_seqs:
                 continue
             if self.cache.slots.num_free < b or self.cache.free_pages(0) < b:
                 break
+            wanted = [k for k in self.runner.length_classes if not self.runner.has_decode_graph(b, k)]
+            if not wanted:
+                continue
             slots = []
             for _ in range(b):
                 slot = self.cache.open()
                 self.cache.reserve(slot, 1)
                 slots.append(slot)
-            self.runner.step([StepItem(s, 0, np.zeros(1, dtype=np.int32), (0,)) for s in slots])  # runs, then captures
+            for klass in wanted:  # each call runs the step, then captures it
+                self.runner.step([StepItem(s, 0, np.zeros(1, dtype=np.int32), (0,)) for s in slots], length_class=klass)
+                done += 1
             for s in slots:
                 self.cache.close(s)
-            done += 1
         torch.cuda.synchronize()
         return done
+
+    def graph_bytes_estimate(self) -> int:
+        """What the captured decode steps of every batch size and length class keep for themselves: their logits."""
+        if not self.cfg.use_cuda_graphs:
+            return 0
+        n = self.cfg.max_num_seqs
+        classes = len(ModelRunner._length_classes(self.cfg.max_seq_len))
+        return classes * (n * (n + 1) // 2) * self.model.spec.vocab_size * 4
 
     # ---- pool sizing ----------------------------------------------------------
     def _size_pool(self) -> int:
@@ -234,7 +246,7 @@ class Engine:
         gc.collect()
         torch.cuda.empty_cache()
         free, _ = torch.cuda.mem_get_info()
-        usable = free - activations - cfg.reserve_bytes
+        usable = free - activations - cfg.reserve_bytes - self.graph_bytes_estimate()
         # Groups with a window are given what every running request can hold at once (the window, a portion and a
         # page of slack); what is left goes to the groups that keep all keys, which share it page for page.
         by_group = CacheManager.group_page_bytes(self.needs, cfg.page_size, self.dtype)

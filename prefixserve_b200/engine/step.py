@@ -121,7 +121,12 @@ class ModelRunner:
         self.last_row_slots: torch.Tensor | None = None  # int32 [wanted rows]: the request slot of each row of the last logits
         # graphs need every part to do the same device work for the same shapes, whatever the host-side item list says
         self.use_graphs = use_graphs and all(getattr(p, "graph_safe", False) for _, p in model.named_parts())
-        self._graphs: dict[int, _DecodeGraph] = {}
+        self._graphs: dict[tuple[int, int], _DecodeGraph] = {}  # pure-decode steps, by (batch size, length class)
+        # A captured step's launch shapes (key ranges of attention, width of the page tables) cannot follow the
+        # step's lengths, so they are sized for a class of lengths: the step's longest sequence rounded up to a power
+        # of two (from 1,024), at most the longest the cache allows.  A batch of short sequences thus does not run
+        # with the few, long key ranges that the longest possible sequence would need.
+        self.length_classes = self._length_classes(cache.max_seq_len)
         self._graph_pool = None  # one memory pool for all captured steps: only one of them runs at a time
         self.graph_replays = 0
         self._shape_graphs: dict[tuple, _DecodeGraph] = {}  # steps with portions, by shape; oldest out first
@@ -136,6 +141,26 @@ class ModelRunner:
         # Debug check, after the reference's test harness (tests/test_llama_exact.py:146-151 of PrefixServe): a step
         # must never write a position whose page the prefix tree owns (another request may be reading it).
         self.check_writes = os.environ.get("PSB200_DEBUG_CHECKS", "0") == "1"
+
+    @staticmethod
+    def _length_classes(max_seq_len: int, smallest: int = 1024) -> tuple[int, ...]:
+        out = []
+        n = smallest
+        while n < max_seq_len:
+            out.append(n)
+            n *= 2
+        out.append(max_seq_len)
+        return tuple(out)
+
+    def length_class(self, longest: int) -> int:
+        """The smallest length class that holds a sequence of ``longest`` tokens."""
+        for n in self.length_classes:
+            if longest <= n:
+                return n
+        raise EngineError(f"a position exceeds max_seq_len {self.cache.max_seq_len}")
+
+    def has_decode_graph(self, batch_size: int, longest: int = 1) -> bool:
+        return (batch_size, self.length_class(longest)) in self._graphs
 
     # ------------------------------------------------------------------ checks
     def _check(self, items: Sequence[StepItem], ahead: np.ndarray | None = None) -> None:
@@ -200,9 +225,10 @@ class ModelRunner:
         self._copy_pending = True
         ops.scatter_words(self.cache.resident, dev, n)
 
-    def _device_step(self, lay: _Layout, dev: torch.Tensor, widths: dict[int, int], views, lens, static: bool, rows: torch.Tensor):
+    def _device_step(self, lay: _Layout, dev: torch.Tensor, widths: dict[int, int], views, lens, static: int | None, rows: torch.Tensor):
         """The device work of a step whose inputs lie in ``dev``: the step's page tables from the resident rows, the
-        slots' positions, then the model.  The same launches whether run at once or captured."""
+        slots' positions, then the model.  The same launches whether run at once or captured.  ``static``: the length
+        class the launch shapes are sized for (a step that is captured), or None (shapes from the step's own lengths)."""
         cache = self.cache
         t, b = lay.t, lay.b
         kv_len = dev[lay.kvlen: lay.kvlen + b]
@@ -232,16 +258,20 @@ class ModelRunner:
             max_kv_len=max(v.end for v in views),
             all_decode=all(n == 1 for n in lens),
         )
-        if static:
-            ctx.extras["static_kv_len"] = cache.max_seq_len
+        if static is not None:
+            ctx.extras["static_kv_len"] = static
         return self.model.forward(ctx, cache.view, rows)
 
     # ------------------------------------------------------------------- step
     @torch.inference_mode()
     def step(self, items: Sequence[StepItem], device_ids: torch.Tensor | None = None,
-             in_flight: Sequence[int] | None = None) -> torch.Tensor:
+             in_flight: Sequence[int] | None = None, length_class: int | None = None) -> torch.Tensor:
         """Runs the batch. Returns float32 logits [number of wanted positions, vocab] on the device,
         in the order of the items and of each item's ``want``; ``last_row_slots`` then names the slot of each row.
+        The logits of a replayed step live in the capture's own buffer: they hold until the next step.
+
+        ``length_class``: size a captured step for this class of sequence lengths instead of the smallest that holds
+        the step (to capture a class before any sequence has grown into it).
 
         ``device_ids`` (int32 [len(items)] on the device): the items are single tokens that follow a step which has been
         launched but whose result the host has not seen; their token ids are taken from this tensor on the device (the
@@ -257,14 +287,22 @@ class ModelRunner:
                 raise EngineError("token ids from the device: one int32 per item, every item a single token")
             ahead = np.asarray(in_flight, dtype=np.int64)
         all_single = all(len(it.tokens) == 1 and tuple(it.want) == (0,) for it in items)
-        held = self._graphs.get(len(items)) if self.use_graphs and all_single else None
+        # (a step that reaches beyond max_seq_len is refused by the checks below, whichever path it takes)
+        klass = self.length_class(min(self.cache.max_seq_len, max(it.start + len(it.tokens) for it in items)))
+        if length_class is not None:
+            if length_class not in self.length_classes or length_class < klass:
+                raise EngineError(f"length class {length_class} is none of {self.length_classes} or too short for the step")
+            klass = length_class
+        held = self._graphs.get((len(items), klass)) if self.use_graphs and all_single else None
         if held is not None:
             return self._replay(items, held, device_ids, ahead)
         shape = None
         if self.use_graphs and not all_single and device_ids is None:
             shape = self._shape_of(items)
-            if shape is not None and shape in self._shape_graphs:
-                return self._replay_shape(items, self._shape_graphs[shape])
+            if shape is not None:
+                shape = (klass,) + shape
+                if shape in self._shape_graphs:
+                    return self._replay_shape(items, self._shape_graphs[shape])
         self._check(items, ahead)
         lens = [len(it.tokens) for it in items]
         b, t = len(items), sum(lens)
@@ -280,16 +318,16 @@ class ModelRunner:
             if len(self._shapes_seen) > 4096:
                 self._shapes_seen.clear()
             capture_shape = seen >= self.capture_shapes_from
-        static = self.use_graphs and (all_single or capture_shape)
-        if static:  # the shapes of a captured step may not depend on the step: full-width page tables
-            widths = {gi: self.cache.max_pages_per_seq for gi in range(len(self.cache.groups))}
+        static = klass if self.use_graphs and (all_single or capture_shape) else None
+        if static is not None:  # the shapes of a captured step may not depend on the step: page tables as wide as the class
+            widths = {gi: pages_for(klass, page) for gi in range(len(self.cache.groups))}
         else:
             widths = {gi: pages_for(int(ends_np.max()), page) for gi in range(len(self.cache.groups))}
 
-        lay = _Layout(t, b, s, rows_are_items=static and all_single)
+        lay = _Layout(t, b, s, rows_are_items=static is not None and all_single)
         n_pairs = self.cache.pending_deltas()
         # a captured step keeps room for later steps' pairs: a page per request and what its portions fill
-        room = max(n_pairs, 4 * b + 64 + 2 * (t // page)) if static else n_pairs
+        room = max(n_pairs, 4 * b + 64 + 2 * (t // page)) if static is not None else n_pairs
         total = lay.pairs + 2 * n_pairs
         host = self._staging(total)
         buf = host.numpy()
@@ -313,7 +351,7 @@ class ModelRunner:
         n_pairs = self.cache.drain_deltas(buf, lay.pairs)
 
         self.last_h2d_bytes = 4 * total
-        if static:
+        if static is not None:
             dev = torch.empty(lay.pairs + 2 * room, dtype=torch.int32, device=self.device)
             dev[:total].copy_(host[:total], non_blocking=True)
         else:
@@ -329,8 +367,8 @@ class ModelRunner:
                 ops.scatter_words(self.cache.resident, dev[lay.pairs:], n_pairs)
             logits = self._device_step(lay, dev, widths, views, lens, static, rows)  # this step's result, computed eagerly
         self.steps_run += 1
-        if static:
-            # Capture the same launches for later steps of this batch size.  Nothing runs during capture; the eager
+        if static is not None:
+            # Capture the same launches for later steps of this batch size and length class.  Nothing runs during capture; the eager
             # run above has already sized every scratch buffer the kernels use.
             graph = torch.cuda.CUDAGraph()
             if self._graph_pool is None:
@@ -343,7 +381,7 @@ class ModelRunner:
             made = _DecodeGraph(inputs=dev, logits=static_logits, graph=graph, var_at=lay.var, pairs_at=lay.pairs,
                                 pairs_room=room, kernels=library.launches - before, by_name=dict(recorded), layout=lay)
             if all_single:
-                self._graphs[b] = made
+                self._graphs[(b, klass)] = made
             else:
                 if len(self._shape_graphs) >= self.max_shape_graphs:
                     self._shape_graphs.pop(next(iter(self._shape_graphs)))

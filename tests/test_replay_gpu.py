@@ -45,9 +45,11 @@ def truth(folders):
     return out
 
 
-def replay(folder, dtype, steps, max_tokens=None, poison=False):
+def replay(folder, dtype, steps, max_tokens=None, poison=False, smallest_class=None, seen=None):
     from prefixserve_b200.engine.replay import Replayer
     rp = Replayer(folder, dtype, max_tokens or helpers.peak_tokens(steps))
+    if smallest_class:
+        rp.runner.length_classes = rp.runner._length_classes(rp.cache.max_seq_len, smallest_class)
     rp.cache.poison_freed = poison
     if poison:
         for kv in rp.cache.kv:
@@ -59,6 +61,9 @@ def replay(folder, dtype, steps, max_tokens=None, poison=False):
             outputs[st["step"]] = torch.from_numpy(out.copy())
     rp.cache.check()
     assert rp.cache.free_pages(0) == rp.cache.num_pages(0), "pages were not all given back"
+    if seen is not None:
+        seen["decode"] = sorted(rp.runner._graphs)
+        seen["shapes"] = sorted(rp.runner._shape_graphs)
     return helpers.collect(steps, outputs)
 
 
@@ -191,6 +196,58 @@ def test_pages_are_reused_in_mixed_trace(folders, truth, which, dtype):
             plain_bf16 = plain_model.forward(cfg, tensors, toks, dtype=torch.bfloat16)
             ours, theirs = helpers.rel_err(got, want), helpers.rel_err(plain_bf16, want)
             assert ours < 0.15 and ours <= 1.5 * theirs + 1e-3, (rid, ours, theirs)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("kind", ["tail_decode", "mixed"])
+def test_captured_steps_of_every_length_class(tmp_path, kind, dtype):
+    """A captured step is sized for a class of sequence lengths (powers of two).  With classes from 32 tokens up, the
+    requests here grow through three or four of them while they decode: every class gets a capture of its own, a
+    step is replayed from the capture of its own class, and the logits stay those of the plain model."""
+    folder = helpers.make_folder(tmp_path / "tinyE16", "E", dtype=torch.bfloat16 if dtype == "bfloat16" else torch.float32)
+    cfg, tensors = plain_model.read_folder(folder)
+    seqs = sequences("E")
+    seen = {}
+    rows = replay(folder, dtype, TRACES[kind](seqs), smallest_class=32, seen=seen)
+    assert len({klass for _, klass in seen["decode"]}) >= (3 if kind == "tail_decode" else 1), seen
+    for rid, toks in seqs.items():
+        want = plain_model.forward(cfg, tensors, toks)
+        got = torch.stack([rows[(rid, p)] for p in range(len(toks))])
+        if dtype == "float32":
+            assert float((got - want).abs().max()) <= 1e-4 * float(want.abs().max()), rid
+        else:
+            plain_bf16 = plain_model.forward(cfg, tensors, toks, dtype=torch.bfloat16)
+            ours, theirs = helpers.rel_err(got, want), helpers.rel_err(plain_bf16, want)
+            assert ours < 0.15 and ours <= 1.5 * theirs + 1e-3, f"{kind}/{rid}: engine {ours:.4f}, plain bf16 {theirs:.4f}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_captured_steps_with_portions_of_every_length_class(tmp_path, dtype):
+    """The same for captured steps that hold a prompt portion: one request is fed eight tokens a step and asks for
+    the last of them while another decodes, so the same shape comes back step after step while both sequences grow
+    through the length classes."""
+    folder = helpers.make_folder(tmp_path / "tinyE16", "E", dtype=torch.bfloat16 if dtype == "bfloat16" else torch.float32)
+    cfg, tensors = plain_model.read_folder(folder)
+    vocab = helpers.TINY["E"]["cfg"].vocab_size
+    seqs = {"fed": helpers.random_tokens(vocab, 248, seed=7), "decoding": helpers.random_tokens(vocab, 70, seed=8)}
+    steps = [{"step": 0, "entries": [{"id": "decoding", "tokens": seqs["decoding"][:39], "want": [38]}], "end": []}]
+    for k in range(31):
+        steps.append({"step": k + 1, "entries": [
+            {"id": "fed", "tokens": seqs["fed"][8 * k: 8 * k + 8], "want": [7]},
+            {"id": "decoding", "tokens": seqs["decoding"][39 + k: 40 + k], "want": [0]}], "end": ["fed", "decoding"] if k == 30 else []})
+    seen = {}
+    rows = replay(folder, dtype, steps, smallest_class=32, seen=seen)
+    assert len({shape[0] for shape in seen["shapes"]}) >= 3, seen
+    for rid, toks in seqs.items():
+        places = sorted(p for r, p in rows if r == rid)
+        got = torch.stack([rows[(rid, p)] for p in places])
+        want = plain_model.forward(cfg, tensors, toks)[places]
+        if dtype == "float32":
+            assert float((got - want).abs().max()) <= 1e-4 * float(want.abs().max()), rid
+        else:
+            plain_bf16 = plain_model.forward(cfg, tensors, toks, dtype=torch.bfloat16)[places]
+            ours, theirs = helpers.rel_err(got, want), helpers.rel_err(plain_bf16, want)
+            assert ours < 0.15 and ours <= 1.5 * theirs + 1e-3, f"{rid}: engine {ours:.4f}, plain bf16 {theirs:.4f}"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
