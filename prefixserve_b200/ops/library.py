@@ -90,6 +90,14 @@ _SIGNATURES: dict[str, list] = {
     "psb_gemm_tcgen05_rope": [P, P, I, I, I, P, P, P, I, P, P, P, P, I, I, I, I, I, I, P],
     # () -> 0 while no bounded wait of the tcgen05 kernel has ever run out
     "psb_tcgen05_status": [],
+    # the product for 17..64 rows: (a, w, c, M, N, K, stream)
+    "psb_gemm_fewrows": [P, P, P, I, I, I, P],
+    # (a, w, act, M, I, K, activation, stream)
+    "psb_gemm_fewrows_gated": [P, P, P, I, I, I, I, P],
+    # (a, w, M, K, positions, token_item, table, table_width, cos, sin, kv, q_out, hq, hkv, D, page_size, num_pages, max_positions, stream)
+    "psb_gemm_fewrows_rope": [P, P, I, I, P, P, P, I, P, P, P, P, I, I, I, I, I, I, P],
+    "psb_gemm_fewrows_splits": [I],
+    "psb_gemm_fewrows_status": [],
     # (logits, temperature, seed, position, out, scratch, S, V, stream)
     "psb_sample": [P, P, P, P, P, P, I, I, P],
     # (logits, records, row_slot, record_words, out, scratch, S, V, stream)
@@ -169,9 +177,10 @@ class pinned_stream:
 def tcgen05_status() -> int:
     """0 unless a bounded wait inside a tcgen05 kernel ever gave up (then its results are void). Synchronises.
 
-    The product's code sits in the low byte, prefill attention's in the next, the TMA-fed decode attention's in the third."""
+    The product's code sits in the low byte, prefill attention's in the next, the TMA-fed decode attention's in the
+    third, the few-row product's in the fourth."""
     return (int(lib().psb_tcgen05_status()) | (int(lib().psb_attention_tcgen05_status()) << 8)
-            | (int(lib().psb_attention_decode_tma_status()) << 16))
+            | (int(lib().psb_attention_decode_tma_status()) << 16) | (int(lib().psb_gemm_fewrows_status()) << 24))
 
 
 def declare(name: str, argtypes: list) -> None:

@@ -17,6 +17,15 @@ TCGEN05_MIN_TILES = 120  # ... when the kernel would cut the product into at lea
                          # (a few dozen rows against a narrow matrix) leave most SMs idle without split-K and go to cuBLAS
 TCGEN05_MIN_ROWS = 128   # ... and it has at least one full tile of rows: with 64 rows half of every instruction is padding
                          # (gate/up of 64 decoded tokens: 18 us against the library's 12.7 plus 2.4 for the activation)
+USE_FEWROWS = True   # products with more rows than STREAM_M and at most FEWROWS_MAX[kind]: the kernel that puts the rows in
+                     # the instruction's N dimension and shares the contraction out over a cluster (else cuBLAS).  Decode
+                     # steps at Llama-1B sizes, context 4,096, ms a step without / with the kernel for all three kinds:
+                     # 20 requests 1.420 / 1.350, 32: 1.681 / 1.610, 48: 2.372 / 2.361 (plain alone 2.349), 64: 2.395 /
+                     # 2.420.  Alone, the kernel matches cuBLAS on the narrow matrices (O 5.9 us both at 64 rows, down
+                     # 11.8 against 13.4) and loses on gate/up from 33 rows on (17.5 against 12.6 + 2.4 for the
+                     # activation kernel: 128 one-tile CTAs that fill, stream and drain in step leave the memory idle
+                     # at both ends)
+FEWROWS_MAX = {"plain": 48, "gated": 32, "rope": 32}
 WIDE_BELOW_TILES = 600   # matrices with fewer 16-row tiles than this get 16 warps per CTA instead of 8
 TCGEN05_PREFILL_MIN_TOKENS = 64   # steps whose longest prompt portion has at least this many tokens run prefill attention
                                   # on the tcgen05 kernel (tiles of 128 rows); shorter portions fill too little of a tile
@@ -122,6 +131,30 @@ def norm_gated_linear_bf16(x, w_gate_up: torch.Tensor, activation: int = 0) -> t
     return act
 
 
+def _fewrows_ok(x: torch.Tensor, w: torch.Tensor, kind: str = "plain") -> bool:
+    m, k = x.shape
+    return (USE_FEWROWS and STREAM_M < m <= FEWROWS_MAX[kind] and k >= 64 and k % 8 == 0 and x.is_contiguous() and w.is_contiguous()
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_fewrows(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """x[M,K] @ w[N,K]^T -> bfloat16 for 17..64 rows: W as the tensor-core instruction's M operand, the contraction
+    shared out over a thread-block cluster that adds its partial sums up through distributed shared memory."""
+    m, k = x.shape
+    y = torch.empty((m, w.shape[0]), dtype=torch.bfloat16, device=x.device)
+    check(lib().psb_gemm_fewrows(x.data_ptr(), w.data_ptr(), y.data_ptr(), m, w.shape[0], k, stream_handle()), "gemm_fewrows")
+    return y
+
+
+def gemm_fewrows_gated(x: torch.Tensor, w_gate_up: torch.Tensor, activation: int = 0) -> torch.Tensor:
+    m, k = x.shape
+    inter = w_gate_up.shape[0] // 2
+    act = torch.empty((m, inter), dtype=torch.bfloat16, device=x.device)
+    check(lib().psb_gemm_fewrows_gated(x.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(), m, inter, k, activation,
+                                       stream_handle()), "gemm_fewrows_gated")
+    return act
+
+
 def _tcgen05_ok(x: torch.Tensor, w: torch.Tensor, kind: int = 0, head_dim: int = 0) -> bool:
     """kind: 0 plain, 1 gated (w holds gate and up rows), 2 the projection that rotates (heads of ``head_dim``)."""
     if not USE_TCGEN05:
@@ -156,10 +189,19 @@ def gemm_tcgen05_gated(x: torch.Tensor, w_gate_up: torch.Tensor, activation: int
 
 def tcgen05_qkv_rope_bf16(x: torch.Tensor, w_qkv, positions, token_item, cos, sin, table, kv, hq, hkv, d, page_size) -> torch.Tensor | None:
     """The projection of an attention layer for many tokens on the tcgen05 kernel, rotation and append to the pages in
-    its epilogue; None when that kernel does not take the shape."""
-    if not (_tcgen05_ok(x, w_qkv, 2, d) and kv.is_contiguous() and (cos is None or (cos.is_contiguous() and sin.is_contiguous()))):
+    its epilogue (for 17..64 tokens: on the few-row kernel, which does the same); None when neither takes the shape."""
+    if not (kv.is_contiguous() and (cos is None or (cos.is_contiguous() and sin.is_contiguous()))):
         return None
     m, k = x.shape
+    if _fewrows_ok(x, w_qkv, "rope"):
+        q = torch.empty((m, hq, d), dtype=torch.bfloat16, device=x.device)
+        check(lib().psb_gemm_fewrows_rope(
+            x.data_ptr(), w_qkv.data_ptr(), m, k, positions.data_ptr(), token_item.data_ptr(), table.data_ptr(), table.shape[1],
+            None if cos is None else cos.data_ptr(), None if sin is None else sin.data_ptr(), kv.data_ptr(), q.data_ptr(),
+            hq, hkv, d, page_size, kv.shape[0], 0 if cos is None else cos.shape[0], stream_handle()), "gemm_fewrows_rope")
+        return q
+    if not _tcgen05_ok(x, w_qkv, 2, d):
+        return None
     q = torch.empty((m, hq, d), dtype=torch.bfloat16, device=x.device)
     check(lib().psb_gemm_tcgen05_rope(
         x.data_ptr(), w_qkv.data_ptr(), m, k, _sms(x.device), positions.data_ptr(), token_item.data_ptr(), table.data_ptr(),
@@ -172,8 +214,9 @@ def tcgen05_qkv_rope_bf16(x: torch.Tensor, w_qkv, positions, token_item, cos, si
 def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     """x[M,K] @ w[N,K]^T for bfloat16 operands, float32 accumulation.
 
-    Up to 16 rows (decode): the weight-streaming kernel of this library.  Prefill-sized products with bfloat16
-    output: its tcgen05 kernel.  What lies between (and outputs in float32 with many rows) goes to the library
+    Up to 16 rows (decode): the weight-streaming kernel of this library.  A few dozen rows: its few-row tcgen05
+    kernel.  Prefill-sized products with bfloat16 output: its tcgen05 kernel.  What lies between (and outputs in
+    float32 with many rows) goes to the library
     product (cuBLAS through torch), which is where the reference calls F.linear for everything
     (prefixserve/model/llama.py:113-126).
     """
@@ -181,6 +224,8 @@ def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> tor
     if out_dtype in _OUT_CODE and x.is_contiguous() and w.is_contiguous():
         if small_m_ok(m, k, min(STREAM_M, 16)):
             return gemm_stream(x, w, out_dtype)
+        if out_dtype == torch.bfloat16 and _fewrows_ok(x, w):
+            return gemm_fewrows(x, w)
         if out_dtype == torch.bfloat16 and m > 0 and _tcgen05_ok(x, w):
             return gemm_tcgen05(x, w)
     if out_dtype == torch.float32:  # logits of many rows: the sums leave the library in float32, never rounded to bfloat16
@@ -197,6 +242,8 @@ def gated_linear_bf16(x: torch.Tensor, w_gate_up: torch.Tensor, activation: int 
         return None
     if small_m_ok(m, k, min(STREAM_M, 16)):
         return gemm_stream_gated(x, w_gate_up, activation)
+    if _fewrows_ok(x, w_gate_up, "gated"):
+        return gemm_fewrows_gated(x, w_gate_up, activation)
     if m > STREAM_M and _tcgen05_ok(x, w_gate_up, 1):
         return gemm_tcgen05_gated(x, w_gate_up, activation)
     return None

@@ -905,6 +905,102 @@ def test_gemm_tcgen05_gated(m, inter, k, width):
     assert torch.allclose(got.double(), want, rtol=3e-2, atol=3e-2), float((got.double() - want).abs().max())
 
 
+# ---- the product for a few dozen rows: rows in the instruction's N dimension, the contraction shared out over a cluster --
+
+@pytest.fixture
+def fewrows_splits():
+    from prefixserve_b200.ops import library
+    def force(n):
+        library.check(library.lib().psb_gemm_fewrows_splits(n), "splits")
+    yield force
+    force(0)
+
+
+@pytest.mark.parametrize("splits", [0, 1, 4, 8])
+@pytest.mark.parametrize("m,n,k", [(17, 256, 512), (64, 2048, 2048), (33, 333, 264), (40, 3072, 2048), (64, 2048, 8192),
+                                   (50, 1000, 1000), (20, 128, 64), (31, 8016, 96)])
+def test_gemm_fewrows(m, n, k, splits, fewrows_splits):
+    from prefixserve_b200.ops import library
+    from prefixserve_b200.ops.tensorcore import gemm_fewrows
+    x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = torch.randn(n, k, device=DEV).to(torch.bfloat16)
+    fewrows_splits(splits)
+    got = gemm_fewrows(x, w)
+    assert library.tcgen05_status() == 0, "a bounded wait in the kernel gave up"
+    want = x.double() @ w.double().t()
+    assert got.shape == (m, n) and got.dtype == torch.bfloat16
+    assert torch.allclose(got.double(), want, rtol=1e-2, atol=1e-2 * math.sqrt(k)), float((got.double() - want).abs().max())
+    # the same rows inside another batch give the same bits (a token's sums do not depend on its neighbours)
+    part = gemm_fewrows(x[:17].contiguous(), w)
+    assert torch.equal(part, got[:17])
+    assert torch.equal(gemm_fewrows(x, w), got)
+
+
+@pytest.mark.parametrize("splits", [0, 2, 8])
+@pytest.mark.parametrize("m,inter,k", [(64, 8192, 2048), (50, 40, 128), (17, 333, 264), (33, 1000, 2048)])
+def test_gemm_fewrows_gated(m, inter, k, splits, fewrows_splits):
+    from prefixserve_b200.ops import library
+    from prefixserve_b200.ops.tensorcore import gemm_fewrows_gated
+    x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(2 * inter, k, device=DEV) / math.sqrt(k)).to(torch.bfloat16)
+    fewrows_splits(splits)
+    y = (x.double() @ w.double().t()).to(torch.bfloat16).double()  # the reference rounds the projections first
+    for name, code, f in (("silu", 0, torch.nn.functional.silu),
+                          ("gelu_tanh", 1, lambda v: torch.nn.functional.gelu(v, approximate="tanh"))):
+        got = gemm_fewrows_gated(x, w, code)
+        assert library.tcgen05_status() == 0
+        want = f(y[:, :inter]) * y[:, inter:]
+        assert got.shape == (m, inter)
+        assert torch.allclose(got.double(), want, rtol=3e-2, atol=3e-2), (name, float((got.double() - want).abs().max()))
+
+
+@pytest.mark.parametrize("m", [17, 33, 64])
+@pytest.mark.parametrize("hq,hkv,d,page,k", [(8, 2, 64, 16, 512), (3, 1, 48, 8, 96), (4, 4, 128, 32, 2048), (32, 8, 64, 16, 2048),
+                                              (6, 2, 128, 16, 3072)])
+@pytest.mark.parametrize("rotate", [True, False])
+def test_fewrows_projection_rotation_and_append_in_one_kernel(m, hq, hkv, d, page, k, rotate, monkeypatch):
+    """Bit for bit what the same product followed by the rotary kernel (paired order) produces, for single tokens of
+    many requests and for one portion."""
+    from prefixserve_b200 import ops
+    from prefixserve_b200.ops import library, tensorcore
+    monkeypatch.setattr(tensorcore, "FEWROWS_MAX", {"plain": 64, "gated": 64, "rope": 64})
+    g = torch.Generator().manual_seed(m + d)
+    for portion in (False, True):
+        if portion:
+            lens_old, lens_new = [23], [m]
+        else:
+            lens_old, lens_new = [int(x) for x in torch.randint(0, 60, (m,), generator=g)], [1] * m
+        table, _, num_pages = _paged_setup(torch.bfloat16, lens_new, lens_old, hq, hkv, d, page, seed=11)
+        positions = torch.cat([torch.arange(o, o + n) for o, n in zip(lens_old, lens_new)]).to(torch.int32).to(DEV)
+        token_item = torch.cat([torch.full((n,), i) for i, n in enumerate(lens_new)]).to(torch.int32).to(DEV)
+        h = torch.randn(m, k, generator=g).to(DEV) * 2
+        pending = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+        gain = (1.0 + 0.2 * torch.randn(k, generator=g)).to(DEV)
+        w = (torch.randn((hq + 2 * hkv) * d, k, generator=g) / math.sqrt(k)).to(torch.bfloat16).to(DEV)
+        angles = torch.outer(torch.arange(120).float(), 1.0 / (10000.0 ** (torch.arange(0, d, 2).float() / d)))
+        cos, sin = (angles.cos().to(DEV).contiguous(), angles.sin().to(DEV).contiguous()) if rotate else (None, None)
+        args = dict(num_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page)
+        x = ops.NormedRows(h.clone(), pending, gain, 1e-5, torch.bfloat16)
+        kv_two = torch.zeros(num_pages, 2, hkv, page, d, dtype=torch.bfloat16, device=DEV)
+        q_two = ops.rope_append(ops.linear(x, w), positions, token_item, cos, sin, table.to(DEV), kv_two, write_kv=True, paired=True, **args)
+        y = ops.NormedRows(h.clone(), pending, gain, 1e-5, torch.bfloat16)
+        kv_one = torch.zeros_like(kv_two)
+        before = library.launch_counts["gemm_fewrows_rope"]
+        q_one = ops.qkv_rope_append(y, w, positions, token_item, cos, sin, table.to(DEV), kv_one, **args)
+        assert q_one is not None and library.launch_counts["gemm_fewrows_rope"] == before + 1
+        assert library.tcgen05_status() == 0
+        assert torch.equal(q_one, q_two) and torch.equal(kv_one, kv_two)
+        assert float(kv_one.float().abs().sum()) > 0
+        # and against plain arithmetic on the normalised rows
+        xn = x.tensor().double()
+        want_v = (xn @ w.double().t())[:, (hq + hkv) * d:].to(torch.bfloat16)
+        for tok in (0, m - 1):
+            pos = int(positions[tok])
+            pg = int(table[int(token_item[tok]), pos // page])
+            got_v = kv_one[pg, 1, :, pos % page].reshape(-1)
+            assert torch.allclose(got_v.double(), want_v[tok].double(), rtol=2e-2, atol=2e-2)
+
+
 def test_a_bounded_wait_that_runs_out_gives_up_and_says_so():
     """The tensor-core kernels wait on mbarriers through one bounded primitive.  Its give-up path runs here on a
     barrier that nobody arrives at, with a limit of a few hundred polls, in a kernel of one warp that has nothing in

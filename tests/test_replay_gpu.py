@@ -127,6 +127,7 @@ def test_bfloat16_with_the_prefill_kernels_on_small_shapes(tmp_path, kind, monke
     monkeypatch.setattr(tensorcore, "TCGEN05_MIN_TILES", 1)
     monkeypatch.setattr(tensorcore, "TCGEN05_MIN_ROWS", 1)
     monkeypatch.setattr(tensorcore, "TCGEN05_PREFILL_MIN_TOKENS", 2)
+    monkeypatch.setattr(tensorcore, "USE_FEWROWS", False)  # the kernel for a few dozen rows has the test below
     taken = {"projection": 0, "gated": 0}
     projection, gated = tensorcore.tcgen05_qkv_rope_bf16, tensorcore.gemm_tcgen05_gated
 
@@ -153,6 +154,29 @@ def test_bfloat16_with_the_prefill_kernels_on_small_shapes(tmp_path, kind, monke
         plain_bf16 = plain_model.forward(cfg, tensors, toks, dtype=torch.bfloat16)
         ours, theirs = helpers.rel_err(got, want), helpers.rel_err(plain_bf16, want)
         assert ours < 0.15 and ours <= 1.5 * theirs + 1e-3, f"D/{kind}/{rid}: engine {ours:.4f}, plain bf16 {theirs:.4f}"
+
+
+@pytest.mark.parametrize("kind", ["portions", "mixed"])
+def test_bfloat16_with_the_few_row_products(tmp_path, kind, monkeypatch):
+    """Portions of 17 to 64 tokens take the few-row tcgen05 product (plain, gated, and the projection that rotates
+    and appends) inside the whole engine: portions cut anywhere, other requests in the batch, pages used again."""
+    from prefixserve_b200.ops import library, tensorcore
+    folder = helpers.make_folder(tmp_path / "tinyD16", "D", dtype=torch.bfloat16)
+    cfg, tensors = plain_model.read_folder(folder)
+    monkeypatch.setattr(tensorcore, "FEWROWS_MAX", {"plain": 64, "gated": 64, "rope": 64})
+    seqs = sequences("D")
+    steps = helpers.trace_portions(seqs, sizes=(17, 40, 64, 33, 20)) if kind == "portions" else TRACES[kind](seqs)
+    before = library.launch_counts.copy()
+    rows = replay(folder, "bfloat16", steps)
+    ran = library.launch_counts - before
+    assert library.tcgen05_status() == 0
+    assert ran["gemm_fewrows"] > 0 and ran["gemm_fewrows_gated"] > 0 and ran["gemm_fewrows_rope"] > 0, ran
+    for rid, toks in seqs.items():
+        want = plain_model.forward(cfg, tensors, toks)
+        got = torch.stack([rows[(rid, p)] for p in range(len(toks))])
+        plain_bf16 = plain_model.forward(cfg, tensors, toks, dtype=torch.bfloat16)
+        ours, theirs = helpers.rel_err(got, want), helpers.rel_err(plain_bf16, want)
+        assert ours < 0.15 and ours <= 1.5 * theirs + 1e-3, f"{kind}/{rid}: engine {ours:.4f}, plain bf16 {theirs:.4f}"
 
 
 def test_cuttings_agree_in_float32(folders):
