@@ -793,7 +793,8 @@ PSB_API int psb_attention_decode_bf16(const void* q, const void* kv, const void*
                                       int max_splits, int all_single, cudaStream_t stream) {
   if (int rc = check_common("attention_decode", hq, hkv, D, page_size, table_width, window)) return rc;
   if (hq / hkv > 16) PSB_REFUSE("attention_decode: groups of more than 16 query heads are not built");
-  if (chunk < WARPS * 16 || chunk % (WARPS * 16)) PSB_REFUSE("attention_decode: key range %d is not a multiple of %d", chunk, WARPS * 16);
+  // a range is walked in tiles of 16 keys that its warps take in turn: it may end after any whole tile
+  if (chunk < WARPS * 16 || chunk % 16) PSB_REFUSE("attention_decode: key range %d is shorter than %d or no multiple of 16", chunk, WARPS * 16);
   if (max_splits < 1 || max_splits > 1024 || (max_splits > 1 && (!part_o || !part_ml)))
     PSB_REFUSE("attention_decode: %d key ranges (at most 1024), or their scratch is missing", max_splits);
   if (page_size & (page_size - 1)) PSB_REFUSE("attention_decode: page size %d is not a power of two", page_size);

@@ -39,6 +39,9 @@ TMA_DECODE_MIN_RANGE = 1024
 PREFILL_MAX_KEY_RANGES = 8        # prefill attention with few CTAs: at most this many key ranges ...
 PREFILL_MIN_BLOCKS_PER_RANGE = 4  # ... of at least this many key blocks each (a range pays for a partial result per row)
 MIN_KEY_RANGE = 128       # split-KV: no key range shorter than this
+DECODE_RANGE_OVERHEAD = 100  # split-KV: what a key range costs beside its keys, in keys
+DECODE_LANES_FACTOR = 1.2    # split-KV: the kernel for short ranges against the TMA-fed one, per key of a long range
+DECODE_FORCE_CHUNK = 0   # tests and sweeps: the key range of split-KV decode attention, whatever the plan would choose
 DECODE_CTAS_PER_SM = 4   # split-KV: key ranges are sized so that about this many CTAs per SM exist
 _OUT_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -274,6 +277,28 @@ def attention_bf16_supported(head_dim: int, page_size: int) -> bool:
     return head_dim in (64, 128) and page_size >= 16 and page_size & (page_size - 1) == 0
 
 
+def _decode_key_range(pairs: int, longest: int, sms: int, tma_kernel: bool) -> int:
+    """The key range of split-KV decode attention for ``pairs`` (request, key/value head) pairs of up to ``longest``
+    keys.  An SM runs DECODE_CTAS_PER_SM CTAs at a time, each at its own pace (a CTA alone on an SM is no faster), so a
+    launch takes as many rounds as its CTAs fill those slots, each as long as a range plus a fixed share: one round of
+    the shortest ranges that fit into it, unless that leaves many slots empty and several rounds of shorter ranges
+    come out ahead (48 requests with 8 heads at 4,096 keys: one round of 384 whole sequences against two rounds of
+    1,152 thirds, measured 2.34 against 2.00 ms a step).  Ranges below TMA_DECODE_MIN_RANGE go to the kernel whose
+    lanes copy for themselves, which is slower on long ranges (111 against 93 us at 64 requests)."""
+    slots = DECODE_CTAS_PER_SM * sms
+    pairs = max(1, pairs)
+    most = max(1, min(-(-longest // MIN_KEY_RANGE), 4 * (slots // pairs + 1)))  # shorter ranges cost more to merge than they save
+    best_cost, best, best_rounds = None, 64, 0
+    for splits in range(1, most + 1):
+        chunk = -(-(-(-longest // splits)) // 64) * 64
+        rounds = -(-(pairs * -(-longest // chunk)) // slots)
+        cost = rounds * (chunk + DECODE_RANGE_OVERHEAD) * (1.0 if tma_kernel and chunk >= TMA_DECODE_MIN_RANGE else DECODE_LANES_FACTOR)
+        # more rounds only for a clear gain: the estimate is rough
+        if best_cost is None or cost < (best_cost if rounds <= best_rounds else 0.92 * best_cost):
+            best_cost, best, best_rounds = cost, chunk, rounds
+    return best
+
+
 def _attention_plan(new_tokens: Sequence[int], kv_lens: Sequence[int], window: int, group: int, hkv: int, d: int, page: int,
                     sms: int, static_kv_len: int | None) -> dict:
     """Launch shapes of a step's attention, from the host copies of the items' lengths.  The same for every layer with
@@ -293,9 +318,8 @@ def _attention_plan(new_tokens: Sequence[int], kv_lens: Sequence[int], window: i
             longest = max(kvl - (max(0, kvl - window) // 16) * 16 for kvl in singles)
         else:
             longest = max(singles)
-        want = max(1, (DECODE_CTAS_PER_SM * sms) // max(1, b * hkv))
-        splits = max(1, min(want, -(-longest // MIN_KEY_RANGE)))  # shorter ranges cost more to merge than they save
-        plan["chunk"] = -(-(-(-longest // splits)) // 64) * 64
+        plan["chunk"] = DECODE_FORCE_CHUNK or _decode_key_range(b * hkv, longest, sms, bool(
+            USE_TMA_DECODE and lib().psb_attention_decode_tma_supported(hq_total, hkv, d, page)))
         plan["max_splits"] = -(-longest // plan["chunk"])
         plan["all_single"] = 1 if len(singles) == b else 0
     portions = [n for n in new_tokens if not (plan["use_decode"] and n == 1)]

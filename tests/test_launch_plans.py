@@ -1,0 +1,36 @@
+"""Host-side launch planning of split-KV decode attention (no GPU needed: pure arithmetic)."""
+
+import random
+
+from prefixserve_b200.ops import tensorcore
+
+
+def test_key_ranges_cover_the_longest_sequence_in_multiples_of_64():
+    rnd = random.Random(0)
+    for _ in range(2000):
+        pairs = rnd.randint(1, 2048)
+        longest = rnd.randint(1, 20000)
+        sms = rnd.choice([1, 16, 132, 148])
+        chunk = tensorcore._decode_key_range(pairs, longest, sms, rnd.random() < 0.5)
+        assert chunk >= 64 and chunk % 64 == 0
+        assert -(-longest // chunk) * chunk >= longest
+        assert chunk >= min(tensorcore.MIN_KEY_RANGE, -(-longest // 64) * 64) or chunk >= longest
+
+
+def test_one_round_of_the_shortest_ranges_that_fit():
+    slots = tensorcore.DECODE_CTAS_PER_SM * 148
+    for pairs, longest in ((8, 4096), (64, 4096), (128, 4096), (256, 4096), (64, 8192)):
+        chunk = tensorcore._decode_key_range(pairs, longest, 148, False)  # (one kernel for every range: no step at 1,024)
+        ranges = -(-longest // chunk)
+        assert pairs * ranges <= slots                      # one round
+        if chunk > tensorcore.MIN_KEY_RANGE:                # and no shorter range would still make one round
+            shorter = -(-(-(-longest // (ranges + 1))) // 64) * 64
+            assert shorter == chunk or pairs * -(-longest // shorter) > slots
+
+
+def test_several_rounds_where_one_would_leave_many_slots_empty():
+    # 48 requests, 8 key/value heads, 4,096 keys: 384 whole sequences fill two thirds of the 592 slots; thirds of them
+    # make two rounds of a third the length each (measured: 2.00 against 2.34 ms a decode step)
+    assert tensorcore._decode_key_range(48 * 8, 4096, 148, True) == 1408
+    # 64 requests fill 512 of 592 slots: nothing shorter pays
+    assert tensorcore._decode_key_range(64 * 8, 4096, 148, True) == 4096
