@@ -36,10 +36,14 @@ USE_TMA_DECODE = True     # decode attention: the kernel whose keys and values t
                           # with 8 requests (ranges of 512 keys, 32 tiles a CTA) 0.90 against 0.855: a CTA that short pays
                           # more for filling its ring through one issuing lane than the ring then saves
 TMA_DECODE_MIN_RANGE = 1024
+PREFILL_MIN_KEY_RANGES = 3        # ... at least this many: two ranges lose to one tile a CTA (512-token portions, 32 heads
+                                  # of 64: 7.24 against 7.04 ms per 2,048 tokens)
 PREFILL_MAX_KEY_RANGES = 8        # prefill attention with few CTAs: at most this many key ranges ...
 PREFILL_MIN_BLOCKS_PER_RANGE = 4  # ... of at least this many key blocks each (a range pays for a partial result per row)
 MIN_KEY_RANGE = 128       # split-KV: no key range shorter than this
 DECODE_RANGE_OVERHEAD = 100  # split-KV: what a key range costs beside its keys, in keys
+DECODE_MERGE_COST = 16       # split-KV: what one more range costs the merge, in keys (one request at 4,096 keys: ranges of
+                             # 128 keys 674 us a step, of 256 keys 655, of 512 keys 670)
 DECODE_LANES_FACTOR = 1.2    # split-KV: the kernel for short ranges against the TMA-fed one, per key of a long range
 DECODE_FORCE_CHUNK = 0   # tests and sweeps: the key range of split-KV decode attention, whatever the plan would choose
 DECODE_CTAS_PER_SM = 4   # split-KV: key ranges are sized so that about this many CTAs per SM exist
@@ -293,6 +297,7 @@ def _decode_key_range(pairs: int, longest: int, sms: int, tma_kernel: bool) -> i
         chunk = -(-(-(-longest // splits)) // 64) * 64
         rounds = -(-(pairs * -(-longest // chunk)) // slots)
         cost = rounds * (chunk + DECODE_RANGE_OVERHEAD) * (1.0 if tma_kernel and chunk >= TMA_DECODE_MIN_RANGE else DECODE_LANES_FACTOR)
+        cost += DECODE_MERGE_COST * -(-longest // chunk)  # the kernel that joins the ranges reads one partial result a range
         # more rounds only for a clear gain: the estimate is rough
         if best_cost is None or cost < (best_cost if rounds <= best_rounds else 0.92 * best_cost):
             best_cost, best, best_rounds = cost, chunk, rounds
@@ -338,7 +343,7 @@ def _attention_plan(new_tokens: Sequence[int], kv_lens: Sequence[int], window: i
             longest = static_kv_len if static_kv_len is not None else max(kvl for n, kvl in zip(new_tokens, kv_lens) if not (plan["use_decode"] and n == 1))
             blocks = -(-longest // (128 if d == 64 else 64))
             splits = min(PREFILL_MAX_KEY_RANGES, sms // ctas, blocks // PREFILL_MIN_BLOCKS_PER_RANGE)
-            if splits >= 2:
+            if splits >= PREFILL_MIN_KEY_RANGES:
                 plan["kv_splits"] = splits
             else:
                 per_cta //= 2

@@ -535,6 +535,7 @@ def test_attention_prefill_over_several_key_ranges(d, page, ranges, min_blocks, 
     from prefixserve_b200.ops import library, tensorcore
     monkeypatch.setattr(tensorcore, "TCGEN05_PREFILL_MIN_TOKENS", 2)
     monkeypatch.setattr(tensorcore, "PREFILL_MAX_KEY_RANGES", ranges)
+    monkeypatch.setattr(tensorcore, "PREFILL_MIN_KEY_RANGES", 2)
     monkeypatch.setattr(tensorcore, "PREFILL_MIN_BLOCKS_PER_RANGE", min_blocks)
     hq, hkv = 4, 2
     lens_old, lens_new = [1390, 0, 700], [170, 40, 130]
