@@ -36,14 +36,17 @@ constexpr int ACC_STRIDE = 256;
 constexpr int MAX_STAGES = 6;
 
 // The output tile is 128 rows by BN columns: 256 where that fills the SMs evenly, 192 where it does not (a product of
-// 192 tiles of 256 columns takes 148 CTAs two rounds, as 256 tiles of 192 columns two rounds of three quarters the size).
+// 192 tiles of 256 columns takes 148 CTAs two rounds, as 256 tiles of 192 columns two rounds of three quarters the size),
+// 240 for plain products that 256 would cut into a few tiles less than there are SMs (2,048 rows by 2,048 columns:
+// 128 tiles of 256 leave 20 SMs idle, 144 tiles of 240 do the same work in one round of 15/16 the length).
 template <int BN>
 struct Tile {
-  static_assert(BN == 256 || BN == 192 || BN == 128, "tile widths built");
+  static_assert(BN == 256 || BN == 240 || BN == 192 || BN == 128, "tile widths built");
   static constexpr int HALF = BN / 2;                  // rows of W per TMA load
-  static constexpr int B_BYTES = BN * BK * 2;          // 32 or 24 KB
+  static constexpr int B_BYTES = BN * BK * 2;          // 32 to 16 KB, a multiple of 1,024 (the swizzle's period)
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = BN == 256 ? 4 : (BN == 192 ? 5 : 6);
+  static constexpr int STAGES = BN >= 240 ? 4 : (BN == 192 ? 5 : 6);
+  static_assert(B_BYTES % 1024 == 0 && (HALF * BK * 2) % 1024 == 0, "operand tiles start on the swizzle's period");
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
   static_assert(STAGES <= MAX_STAGES && SMEM_BYTES <= 227 * 1024, "beyond a CTA's shared memory");
 };
@@ -310,11 +313,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll 1
         for (int c = 0; c < BN; c += 32) {
           uint32_t v[32];
-          tmem_ld32(taddr + c, v);
+          tmem_ld32(taddr + c, v);  // (a tile of 240 columns: the last load reads 16 columns beyond it, which nobody stores)
           tmem_ld_wait();
           if (row < M) {
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
+              if (BN % 32 != 0 && c + j >= BN) break;
               const int col = n0 + c + j;
               uint32_t packed[4];
 #pragma unroll
@@ -366,13 +370,15 @@ int choose_width(int M, int N_out, bool gated, bool rope, int D, int sms) {
   const int m_blocks = (M + BM - 1) / BM;
   int best = 256;
   long best_cost = -1;
-  for (int bn : {256, 192, 128}) {
+  for (int bn : {256, 240, 192, 128}) {
     if (bn == 192 && (gated || (rope && D == 128))) continue;
+    if (bn == 240 && (gated || rope)) continue;  // whole heads and even halves want a power of two or 192
     if (g_forced_width && bn != g_forced_width) continue;
     const int span = gated ? bn / 2 : bn;
     const long tiles = (long)m_blocks * ((N_out + span - 1) / span);
     const long cost = ((tiles + sms - 1) / sms) * (bn + 24);
-    if (best_cost < 0 || cost * 10 <= best_cost * 9) {  // from the widest down: a narrower tile has to pay for itself
+    // from the widest down: a narrower tile has to pay for itself (240 against 256 is the same kernel but for the width)
+    if (best_cost < 0 || (bn == 240 ? cost < best_cost : cost * 10 <= best_cost * 9)) {
       best = bn;
       best_cost = cost;
     }
@@ -410,6 +416,7 @@ int launch(const void* a, const void* w, void* c, int M, int w_rows, int N_out, 
   else if (mode == MODE_ROPE && rope.D == 64) { if (bn == 128) PSB_TCGEN05(128, 4); else if (bn == 192) PSB_TCGEN05(192, 4); else PSB_TCGEN05(256, 4); }
   else if (bn == 128) PSB_TCGEN05(128, 0);
   else if (bn == 192) PSB_TCGEN05(192, 0);
+  else if (bn == 240) PSB_TCGEN05(240, 0);
   else PSB_TCGEN05(256, 0);
 #undef PSB_TCGEN05
   PSB_LAUNCH_CHECK("gemm_tcgen05");
@@ -452,10 +459,10 @@ PSB_API int psb_gemm_tcgen05_rope(const void* a, const void* w, int M, int K, in
   return launch(a, w, q_out, M, N, N, K, 0, MODE_ROPE, sms, stream, rope);
 }
 
-// For tests: 128, 192 or 256 makes every later product use that tile width where the shape allows it, 0 gives the
+// For tests: 128, 192, 240 or 256 makes every later product use that tile width where the shape allows it, 0 gives the
 // choice back.
 PSB_API int psb_gemm_tcgen05_tile_width(int width) {
-  if (width != 0 && width != 128 && width != 192 && width != 256) PSB_REFUSE("gemm_tcgen05: tile widths are 128, 192 and 256, not %d", width);
+  if (width != 0 && width != 128 && width != 192 && width != 240 && width != 256) PSB_REFUSE("gemm_tcgen05: tile widths are 128, 192, 240 and 256, not %d", width);
   g_forced_width = width;
   return 0;
 }

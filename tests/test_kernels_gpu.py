@@ -869,20 +869,20 @@ def test_gemm_tcgen05(m, n, k):
 
 @pytest.mark.parametrize("m,n,k", [(128, 192, 64), (130, 333, 264), (2048, 3072, 2048), (700, 2000, 1000), (129, 8016, 96)])
 def test_gemm_tcgen05_tile_widths_agree(m, n, k):
-    """The launcher picks output tiles of 256, 192 or 128 columns by how they fill the SMs; a sum does not depend on it."""
+    """The launcher picks output tiles of 256, 240, 192 or 128 columns by how they fill the SMs; a sum does not depend on it."""
     from prefixserve_b200.ops import library
     from prefixserve_b200.ops.tensorcore import gemm_tcgen05
     x = torch.randn(m, k, device=DEV).to(torch.bfloat16)
     w = torch.randn(n, k, device=DEV).to(torch.bfloat16)
     got = {}
     try:
-        for width in (128, 192, 256):
+        for width in (128, 192, 240, 256):
             library.check(library.lib().psb_gemm_tcgen05_tile_width(width), "tile width")
             got[width] = gemm_tcgen05(x, w)
     finally:
         library.check(library.lib().psb_gemm_tcgen05_tile_width(0), "tile width")
     assert library.tcgen05_status() == 0
-    assert torch.equal(got[192], got[256]) and torch.equal(got[128], got[256])
+    assert torch.equal(got[192], got[256]) and torch.equal(got[128], got[256]) and torch.equal(got[240], got[256])
     want = x.double() @ w.double().t()
     assert torch.allclose(got[192].double(), want, rtol=1e-2, atol=1e-2 * math.sqrt(k))
 
