@@ -246,7 +246,7 @@ def run_own(args) -> dict:
     layers = args.layers
     work = Path(tempfile.mkdtemp(prefix="psb200-bench-"))
     try:
-        write_own_folder(work, layers)
+        write_own_folder(work, layers, model=MODEL)
         rng = np.random.RandomState(0)
         vocab = MODEL["vocab_size"]
         if args.only != "all":
@@ -329,7 +329,10 @@ def run_own(args) -> dict:
         achieved = step_bytes / (ms_step * 1e-3) / 1e9
         if args.only == "decode":
             return {"only": "decode", "value": round(value, 1), "ms_per_step": round(ms_step, 4), "layers": layers,
-                    "batch": args.batch, "gpu_launches": launches, "weight_bytes": weights, "mean_context": mean_ctx}
+                    "batch": args.batch, "gpu_launches": launches, "weight_bytes": weights, "mean_context": mean_ctx,
+                    "hbm_gbs": round(achieved, 1), "hbm_frac": round(achieved / pk["hbm_gbs"], 4),
+                    "sizes": f"hidden {MODEL['hidden_size']}, heads {MODEL['num_attention_heads']}/{MODEL['num_key_value_heads']} of "
+                             f"{MODEL['head_dim']}, vocabulary {MODEL['vocab_size']}", "clocks": clocks.summary()}
 
         # ---- end to end through the scheduler and engine.launch/finish (host tokens in and out)
         engine.capture_decode_graphs(range(1, max_b + 1))  # as the entry point does at start-up
@@ -727,6 +730,7 @@ def kernel_costs(base: dict) -> list[tuple[str, float, float]]:
 
 
 def main() -> int:
+    global MODEL, FULL_LAYERS, CONTEXT  # --only decode may be asked for other sizes and contexts
     p = argparse.ArgumentParser()
     p.add_argument("--gpus", type=int, default=1)
     p.add_argument("--steps", type=int, default=128)
@@ -749,11 +753,24 @@ def main() -> int:
     p.add_argument("--workload", choices=["decode", "shared-prefix", "mixed"], default="decode",
                    help="decode: the headline line.  shared-prefix: 64 requests over 4 system prefixes through the entry "
                         "point, prefix cache on and off.  mixed: steps of one 512-token prompt portion beside 64 decoded tokens")
-    p.add_argument("--model", choices=sorted(SIZES), default=None, help="layer sizes for --workload shared-prefix (8b) / mixed (3b)")
+    p.add_argument("--model", choices=sorted(SIZES), default=None,
+                   help="layer sizes for --workload shared-prefix (8b) / mixed (3b), and for --only decode (the headline stays 1b)")
     p.add_argument("--requests", type=int, default=64, help="requests of --workload shared-prefix")
-    p.add_argument("--context", type=int, default=8192, help="context of --workload mixed")
+    p.add_argument("--context", type=int, default=None,
+                   help="context of --workload mixed (8192 unless given) and of --only decode (the headline stays 4096)")
     args = p.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.workload == "decode" and args.only == "decode" and args.impl == "own" and (args.model or args.context):
+        # further sizes and context lengths for the device-timed decode steps; the headline line is not touched
+        if args.model:
+            MODEL, full = _model_config(args.model)
+            args.layers = full if args.layers == FULL_LAYERS and "--layers" not in sys.argv else args.layers
+            FULL_LAYERS = full
+        CONTEXT = args.context or CONTEXT
+    elif args.workload == "decode" and (args.model or args.context):
+        print(json.dumps({"unsupported": "--model and --context go with --only decode, --workload shared-prefix or --workload mixed"}))
+        return 2
+    args.context = args.context or 8192
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
         if int(os.environ.get("RANK", "0")) == 0:
             print(json.dumps({"unsupported": f"this engine runs on one GPU; --gpus {args.gpus} is not built", "n_gpus": args.gpus}))

@@ -680,16 +680,20 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   }
 }
 
-// grid (hq, items), one warp: combines the key ranges of one (item, head).  Lanes first share out the ranges
-// (maximum and weights), then the head dims.
-template <int D>
-__global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                       const int32_t* __restrict__ item_start, const int32_t* __restrict__ kv_len,
-                                       __nv_bfloat16* __restrict__ out, int hq, int window, int chunk, int max_splits,
-                                       int all_single) {
-  __shared__ float weight[1024];
+// grid (hq, items), MW warps: combines the key ranges of one (item, head).  Every warp finds the maximum over all
+// ranges for itself (a few 8-byte loads a lane); the ranges are then shared out in contiguous runs, a warp adds up its
+// run's weighted partial outputs (lanes over the head dims, eight ranges' loads in flight at a time), and the warps'
+// sums are joined in warp order through shared memory.  One warp (MW = 1) is right for a handful of ranges; dozens of
+// them (one request with tens of thousands of keys) are nothing but load latency in a single warp.
+template <int D, int MW>
+__global__ void __launch_bounds__(32 * MW)
+attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                       const int32_t* __restrict__ item_start, const int32_t* __restrict__ kv_len,
+                       __nv_bfloat16* __restrict__ out, int hq, int window, int chunk, int max_splits, int all_single) {
+  __shared__ float sum_o[MW][D];
+  __shared__ float sum_l[MW];
   pdl_trigger();
-  const int item = blockIdx.y, head = blockIdx.x, lane = threadIdx.x;
+  const int item = blockIdx.y, head = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   int t0 = item;
   bool mine = true;
   if (!all_single) {
@@ -704,42 +708,88 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
   // never more ranges than the launch provided scratch for (the host sizes them from the longest span it expects)
   const int splits = min((kvl - (lo_key & ~15) + chunk - 1) / chunk, max_splits);
   const size_t base = ((size_t)item * hq + head) * max_splits;
-  // The first eight ranges' partial outputs are asked for together with the maxima: where they lie does not depend on
-  // the weights, and this kernel is nothing but the latency of its loads.
+  const int per = (splits + MW - 1) / MW;
+  const int s_lo = min(warp * per, splits), s_hi = min(s_lo + per, splits);
+  // This warp's first eight partial outputs are asked for together with the maxima: where they lie does not depend
+  // on the weights, and this kernel is nothing but the latency of its loads.
   float first[D / 32][8];
 #pragma unroll
   for (int i = 0; i < D / 32; ++i)
 #pragma unroll
-    for (int j = 0; j < 8; ++j) first[i][j] = j < splits ? part_o[(base + j) * D + lane + 32 * i] : 0.f;
+    for (int j = 0; j < 8; ++j) first[i][j] = s_lo + j < s_hi ? part_o[(base + s_lo + j) * D + lane + 32 * i] : 0.f;
   float m = -INFINITY;
   for (int s = lane; s < splits; s += 32) m = fmaxf(m, part_ml[(base + s) * 2]);
   m = warp_max(m);
   const float m_safe = m == -INFINITY ? 0.f : m;
+  // The run in blocks of 32 ranges: a lane works out one range's weight, then the partial outputs are added up eight
+  // ranges at a time, the next eight's loads on their way while these are used.
+  float o[D / 32];
+#pragma unroll
+  for (int i = 0; i < D / 32; ++i) o[i] = 0.f;
   float l = 0.f;
-  for (int s = lane; s < max_splits; s += 32) {
-    const float a = s < splits ? fast_exp2(part_ml[(base + s) * 2] - m_safe) : 0.f;
-    weight[s] = a;
-    if (s < splits) l += a * part_ml[(base + s) * 2 + 1];
+  for (int blk = s_lo; blk < s_hi; blk += 32) {
+    float a = 0.f;
+    if (blk + lane < s_hi) {
+      a = fast_exp2(part_ml[(base + blk + lane) * 2] - m_safe);
+      l += a * part_ml[(base + blk + lane) * 2 + 1];
+    }
+    const int blk_hi = min(blk + 32, s_hi);
+    for (int s0 = blk; s0 < blk_hi; s0 += 8) {
+      float next[D / 32][8];
+      const int n0 = s0 + 8;
+      if (n0 < s_hi) {
+#pragma unroll
+        for (int i = 0; i < D / 32; ++i)
+#pragma unroll
+          for (int j = 0; j < 8; ++j) next[i][j] = n0 + j < s_hi ? part_o[(base + n0 + j) * D + lane + 32 * i] : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float w = __shfl_sync(0xffffffffu, a, (s0 - blk + j) & 31);
+#pragma unroll
+        for (int i = 0; i < D / 32; ++i) o[i] = fmaf(s0 + j < blk_hi ? w : 0.f, first[i][j], o[i]);
+      }
+      if (n0 < s_hi) {
+#pragma unroll
+        for (int i = 0; i < D / 32; ++i)
+#pragma unroll
+          for (int j = 0; j < 8; ++j) first[i][j] = next[i][j];
+      }
+    }
   }
   l = warp_sum(l);
-  __syncwarp();
+  if (MW > 1) {
+#pragma unroll
+    for (int i = 0; i < D / 32; ++i) sum_o[warp][lane + 32 * i] = o[i];
+    if (lane == 0) sum_l[warp] = l;
+    __syncthreads();
+    if (warp != 0) return;
+    l = 0.f;
+#pragma unroll
+    for (int i = 0; i < D / 32; ++i) o[i] = 0.f;
+#pragma unroll
+    for (int w = 0; w < MW; ++w) {
+      l += sum_l[w];
+#pragma unroll
+      for (int i = 0; i < D / 32; ++i) o[i] += sum_o[w][lane + 32 * i];
+    }
+  }
   const float inv = 1.f / l;
 #pragma unroll
-  for (int i = 0; i < D / 32; ++i) {
-    const int d = lane + 32 * i;
-    float o = 0.f;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) o = fmaf(j < splits ? weight[j] : 0.f, first[i][j], o);
-    // eight ranges per round, all loads issued before any is used; ranges past the item's own are skipped by weight
-    for (int s0 = 8; s0 < splits; s0 += 8) {
-      float v[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = s0 + j < splits ? part_o[(base + s0 + j) * D + d] : 0.f;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) o = fmaf(s0 + j < splits ? weight[s0 + j] : 0.f, v[j], o);
-    }
-    out[((size_t)t0 * hq + head) * D + d] = __float2bfloat16_rn(o * inv);
-  }
+  for (int i = 0; i < D / 32; ++i)
+    out[((size_t)t0 * hq + head) * D + lane + 32 * i] = __float2bfloat16_rn(o[i] * inv);
+}
+
+// The merge with one warp up to eight ranges (one round of loads), four warps beyond.
+template <int D>
+void launch_merge(const float* part_o, const float* part_ml, const int32_t* item_start, const int32_t* kv_len, __nv_bfloat16* out,
+                  int num_items, int hq, int window, int chunk, int max_splits, int all_single, cudaStream_t stream) {
+  if (max_splits <= 8)
+    psb_launch(attention_merge_kernel<D, 1>, dim3(hq, num_items), dim3(32), 0, stream, part_o, part_ml, item_start, kv_len, out, hq,
+               window, chunk, max_splits, all_single);
+  else
+    psb_launch(attention_merge_kernel<D, 4>, dim3(hq, num_items), dim3(128), 0, stream, part_o, part_ml, item_start, kv_len, out, hq,
+               window, chunk, max_splits, all_single);
 }
 
 int check_common(const char* who, int hq, int hkv, int D, int page_size, int table_width, int window) {
@@ -817,9 +867,8 @@ PSB_API int psb_attention_decode_bf16(const void* q, const void* kv, const void*
         (const int32_t*)kv_len, (__nv_bfloat16*)out, (float*)part_o, (float*)part_ml, hq, hkv, page_shift, window, scale, \
         chunk, max_splits, all_single);                                                                              \
     if (max_splits > 1)                                                                                              \
-      psb_launch(attention_merge_kernel<DD>, dim3(hq, num_items), dim3(32), 0, stream, \
-          (const float*)part_o, (const float*)part_ml, (const int32_t*)item_start, (const int32_t*)kv_len,           \
-          (__nv_bfloat16*)out, hq, window, chunk, max_splits, all_single);                                           \
+      launch_merge<DD>((const float*)part_o, (const float*)part_ml, (const int32_t*)item_start, (const int32_t*)kv_len, \
+                       (__nv_bfloat16*)out, num_items, hq, window, chunk, max_splits, all_single, stream);             \
   } while (0)
   if (D == 64) PSB_DECODE(64); else PSB_DECODE(128);
 #undef PSB_DECODE
@@ -837,11 +886,11 @@ PSB_API int psb_attention_decode_merge_bf16(const void* part_o, const void* part
   if (num_items <= 0) return 0;
   if (num_items > 65535) PSB_REFUSE("attention_merge: batch too large");
   if (D == 64)
-    psb_launch(attention_merge_kernel<64>, dim3(hq, num_items), dim3(32), 0, stream, (const float*)part_o, (const float*)part_ml,
-               (const int32_t*)item_start, (const int32_t*)kv_len, (__nv_bfloat16*)out, hq, window, chunk, max_splits, all_single);
+    launch_merge<64>((const float*)part_o, (const float*)part_ml, (const int32_t*)item_start, (const int32_t*)kv_len,
+                     (__nv_bfloat16*)out, num_items, hq, window, chunk, max_splits, all_single, stream);
   else
-    psb_launch(attention_merge_kernel<128>, dim3(hq, num_items), dim3(32), 0, stream, (const float*)part_o, (const float*)part_ml,
-               (const int32_t*)item_start, (const int32_t*)kv_len, (__nv_bfloat16*)out, hq, window, chunk, max_splits, all_single);
+    launch_merge<128>((const float*)part_o, (const float*)part_ml, (const int32_t*)item_start, (const int32_t*)kv_len,
+                      (__nv_bfloat16*)out, num_items, hq, window, chunk, max_splits, all_single, stream);
   PSB_LAUNCH_CHECK("attention_merge");
   return 0;
 }

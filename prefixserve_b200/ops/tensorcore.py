@@ -42,8 +42,9 @@ PREFILL_MAX_KEY_RANGES = 8        # prefill attention with few CTAs: at most thi
 PREFILL_MIN_BLOCKS_PER_RANGE = 4  # ... of at least this many key blocks each (a range pays for a partial result per row)
 MIN_KEY_RANGE = 128       # split-KV: no key range shorter than this
 DECODE_RANGE_OVERHEAD = 100  # split-KV: what a key range costs beside its keys, in keys
-DECODE_MERGE_COST = 16       # split-KV: what one more range costs the merge, in keys (one request at 4,096 keys: ranges of
-                             # 128 keys 674 us a step, of 256 keys 655, of 512 keys 670)
+DECODE_MERGE_COST = 8        # split-KV: what one more range costs the merge, in keys (one request, us a step by range:
+                             # 4,096 keys 643 at 128, 645 at 256, 669 at 512; 16,384 keys 767 at 128, 733 at 256, 780
+                             # at 512, 949 at 1,024; 32,768 keys 950 at 128, 866 at 256, 833 at 512, 956 at 1,024)
 DECODE_LANES_FACTOR = 1.2    # split-KV: the kernel for short ranges against the TMA-fed one, per key of a long range
 DECODE_FORCE_CHUNK = 0   # tests and sweeps: the key range of split-KV decode attention, whatever the plan would choose
 DECODE_CTAS_PER_SM = 4   # split-KV: key ranges are sized so that about this many CTAs per SM exist
@@ -299,7 +300,7 @@ def _decode_key_range(pairs: int, longest: int, sms: int, tma_kernel: bool) -> i
         cost = rounds * (chunk + DECODE_RANGE_OVERHEAD) * (1.0 if tma_kernel and chunk >= TMA_DECODE_MIN_RANGE else DECODE_LANES_FACTOR)
         cost += DECODE_MERGE_COST * -(-longest // chunk)  # the kernel that joins the ranges reads one partial result a range
         # more rounds only for a clear gain: the estimate is rough
-        if best_cost is None or cost < (best_cost if rounds <= best_rounds else 0.92 * best_cost):
+        if best_cost is None or cost < (best_cost if rounds <= best_rounds else 0.85 * best_cost):
             best_cost, best, best_rounds = cost, chunk, rounds
     return best
 
