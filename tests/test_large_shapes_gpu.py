@@ -186,3 +186,43 @@ def test_sixty_four_requests_at_benchmark_layer_sizes(big):
         assert ours < 0.15 and ours <= 1.5 * theirs + 1e-3, f"{rid}: engine {ours:.4f}, plain bf16 {theirs:.4f}"
         worst = max(worst, (ours, theirs))
     assert worst[0] > 0
+
+
+# ---- the widths of the larger presets: heads of 128, hidden 4,096, feed-forward 14,336, untied head -------------------
+
+def config_8b_widths(layers: int = 2):
+    from prefixserve_b200.config import Llama3RopeScaling, LlamaConfig
+    return LlamaConfig(vocab_size=32064, hidden_size=4096, intermediate_size=14336, num_layers=layers, num_heads=32,
+                       num_kv_heads=8, head_dim=128, rms_norm_eps=1e-5, rope_theta=500000.0,
+                       rope_scaling=Llama3RopeScaling(8.0, 1.0, 4.0, 8192), max_position_embeddings=131072,
+                       tie_word_embeddings=False)
+
+
+@pytest.mark.parametrize("kind", ["portions", "mixed", "tail_decode"])
+def test_layer_widths_of_the_8b_preset_in_bfloat16(tmp_path_factory, kind):
+    """Two layers with the widths of Llama-3.1-8B (a smaller vocabulary keeps the plain model quick): heads of 128 on
+    every attention kernel, products with K of 4,096 and 14,336, the few-row product on portions of 17 to 33 tokens."""
+    from prefixserve_b200.engine.replay import Replayer
+    from prefixserve_b200.ops import library
+    from prefixserve_b200.weights import write_random_model
+    torch.backends.cuda.matmul.allow_tf32 = False
+    folder = write_random_model(tmp_path_factory.mktemp("llama8b2"), config_8b_widths(), seed=11, std=0.02, gain_noise=0.05,
+                                dtype=torch.bfloat16)
+    cfg, tensors = plain_model.read_folder(folder)
+    on_gpu = {k: v.cuda() for k, v in tensors.items()}
+    seqs = {f"r{i}": helpers.random_tokens(32064, n, seed=500 + i) for i, n in enumerate([5, 90, 170, 260])}
+    keep = lambda rid, p: p % 5 == 0 or p >= len(seqs[rid]) - 34   # noqa: E731
+    steps = thin(TRACES[kind](seqs), keep)
+    before = library.launch_counts.copy()
+    rows = run(Replayer(folder, "bfloat16", 1536, max_live=8), steps)
+    ran = library.launch_counts - before
+    assert library.tcgen05_status() == 0
+    if kind != "tail_decode":
+        assert ran["gemm_fewrows"] > 0 and ran["gemm_fewrows_rope"] > 0, ran
+    for rid, toks in seqs.items():
+        at = [p for p in range(len(toks)) if keep(rid, p)]
+        got = torch.stack([rows[(rid, p)] for p in at])
+        want = plain_model.forward(cfg, on_gpu, toks, device="cuda").cpu()[at]
+        plain_bf16 = plain_model.forward(cfg, on_gpu, toks, dtype=torch.bfloat16, device="cuda").cpu()[at]
+        ours, theirs = helpers.rel_err(got, want), helpers.rel_err(plain_bf16, want)
+        assert ours < 0.15 and ours <= 1.5 * theirs + 1e-3, f"{kind}/{rid}: engine {ours:.4f}, plain bf16 {theirs:.4f}"
