@@ -260,7 +260,8 @@ def run_own(args) -> dict:
         weights = engine.weight_bytes()  # what a decode step reads of them: every tensor once, the tied table once
 
         def sample(logits) -> None:
-            choose_tokens(logits, cache.records_dev, runner.last_row_slots)
+            if not runner.sample_in_step:  # the engine's runner chooses the tokens inside the step
+                choose_tokens(logits, cache.records_dev, runner.last_row_slots)
 
         def fill(batch: int, upto: int) -> list[int]:
             """Opens ``batch`` requests and prefills each to ``upto`` tokens through the step function."""
@@ -520,7 +521,8 @@ def run_mixed(args) -> dict:
                 cache.reserve(s, p + 1)
                 items.append(StepItem(s, p, rng.randint(0, vocab, size=1).astype(np.int32), (0,)))
             logits = runner.step(items)
-            choose_tokens(logits, cache.records_dev, runner.last_row_slots)
+            if not runner.sample_in_step:  # the engine's runner chooses the tokens inside the step
+                choose_tokens(logits, cache.records_dev, runner.last_row_slots)
             for it in items:
                 cache.advance(it.slot, it.start + len(it.tokens))
 

@@ -20,7 +20,6 @@ import numpy as np
 import torch
 
 from ..cache.manager import CacheManager, pages_for
-from ..sampling.sampler import choose_tokens
 from ..config.registry import read_model_folder
 from .loading import load_model, parse_dtype
 from .scheduler import Batch
@@ -78,7 +77,7 @@ class Engine:
         self.bytes_per_block = CacheManager.bytes_per_page(self.needs, cfg.page_size, dtype)
         num_blocks = cfg.num_blocks if cfg.num_blocks is not None else self._size_pool()
         self.cache = self._make_cache(num_blocks)
-        self.runner = ModelRunner(self.model, self.cache, device=self.device, use_graphs=cfg.use_cuda_graphs)
+        self.runner = ModelRunner(self.model, self.cache, device=self.device, use_graphs=cfg.use_cuda_graphs, sample=True)
         self.capture_logits = False
         self.last_logits: dict[str, torch.Tensor] = {}
         # sampled tokens come back through pinned host memory; two buffers, because a step may be launched while the
@@ -147,7 +146,7 @@ class Engine:
         sampling = [w for w in work if w.samples]
         if not sampling:
             return PendingStep(batch, [], None, None, None)  # nothing to read back: the host runs ahead
-        tokens = choose_tokens(logits, self.cache.records_dev, self.runner.last_row_slots)
+        tokens = self.runner.last_tokens  # chosen inside the step (and inside its capture, where it has one)
         if override is not None:
             given = [override.get(w.req.req_id) for w in sampling]
             if all(g is not None for g in given):

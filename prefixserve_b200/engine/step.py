@@ -62,6 +62,7 @@ class _DecodeGraph:
     kernels: int = 0  # launches of this library's kernels recorded in the graph
     by_name: dict | None = None  # the same by entry point
     layout: "_Layout | None" = None
+    tokens: torch.Tensor | None = None  # with sampling inside the step: int32 [wanted rows], the chosen tokens
 
 
 @dataclass
@@ -104,7 +105,7 @@ class ModelRunner:
     """
 
     def __init__(self, model: DecoderModel, cache: CacheManager, *, device: torch.device | str,
-                 use_graphs: bool = True) -> None:
+                 use_graphs: bool = True, sample: bool = False) -> None:
         if model.compute_dtype is None:
             raise EngineError("the model has no weights yet")
         self.model = model
@@ -119,6 +120,11 @@ class ModelRunner:
         self.steps_run = 0
         self.last_h2d_bytes = 0  # size of the last step's single host-to-device copy
         self.last_row_slots: torch.Tensor | None = None  # int32 [wanted rows]: the request slot of each row of the last logits
+        # With ``sample`` every step also chooses a token for each wanted row (sampling/sampler.py: the temperature,
+        # seed and position of the row's slot record), as part of the captured launches where the step is captured:
+        # launched after a replay instead, the sampling kernels start only when the whole graph has drained.
+        self.sample_in_step = sample
+        self.last_tokens: torch.Tensor | None = None  # int32 [wanted rows] on the device (with ``sample``)
         # graphs need every part to do the same device work for the same shapes, whatever the host-side item list says
         self.use_graphs = use_graphs and all(getattr(p, "graph_safe", False) for _, p in model.named_parts())
         self._graphs: dict[tuple[int, int], _DecodeGraph] = {}  # pure-decode steps, by (batch size, length class)
@@ -366,6 +372,7 @@ class ModelRunner:
             if n_pairs:
                 ops.scatter_words(self.cache.resident, dev[lay.pairs:], n_pairs)
             logits = self._device_step(lay, dev, widths, views, lens, static, rows)  # this step's result, computed eagerly
+            self.last_tokens = self._choose(logits, self.last_row_slots) if s else None
         self.steps_run += 1
         if static is not None:
             # Capture the same launches for later steps of this batch size and length class.  Nothing runs during capture; the eager
@@ -377,9 +384,11 @@ class ModelRunner:
             with torch.cuda.graph(graph, pool=self._graph_pool):
                 with library.pinned_stream():  # the capture's own stream
                     static_logits = self._device_step(lay, dev, widths, views, lens, static, rows)
+                    static_tokens = self._choose(static_logits, self.last_row_slots) if s else None
             recorded = library.launch_counts - named
             made = _DecodeGraph(inputs=dev, logits=static_logits, graph=graph, var_at=lay.var, pairs_at=lay.pairs,
-                                pairs_room=room, kernels=library.launches - before, by_name=dict(recorded), layout=lay)
+                                pairs_room=room, kernels=library.launches - before, by_name=dict(recorded), layout=lay,
+                                tokens=static_tokens)
             if all_single:
                 self._graphs[(b, klass)] = made
             else:
@@ -389,6 +398,12 @@ class ModelRunner:
             library.launches = before  # recorded, not run
             library.launch_counts.subtract(recorded)
         return logits
+
+    def _choose(self, logits: torch.Tensor, row_slots: torch.Tensor) -> torch.Tensor | None:
+        if not self.sample_in_step:
+            return None
+        from ..sampling.sampler import choose_tokens
+        return choose_tokens(logits, self.cache.records_dev, row_slots)
 
     def _shape_of(self, items: Sequence[StepItem]) -> tuple | None:
         """What a captured step with prompt portions is keyed by: every item's length and whether it wants the logits
@@ -452,6 +467,7 @@ class ModelRunner:
         library.launch_counts.update(held.by_name)
         self.steps_run += 1
         self.graph_replays += 1
+        self.last_tokens = held.tokens
         return held.logits
 
     def _replay(self, items: Sequence[StepItem], held: _DecodeGraph, device_ids: torch.Tensor | None = None,
@@ -502,6 +518,7 @@ class ModelRunner:
         library.launch_counts.update(held.by_name)
         self.steps_run += 1
         self.graph_replays += 1
+        self.last_tokens = held.tokens
         return held.logits
 
     def _staging(self, words: int) -> torch.Tensor:
