@@ -34,3 +34,12 @@ def test_several_rounds_where_one_would_leave_many_slots_empty():
     assert tensorcore._decode_key_range(48 * 8, 4096, 148, True) == 1408
     # 64 requests fill 512 of 592 slots: nothing shorter pays
     assert tensorcore._decode_key_range(64 * 8, 4096, 148, True) == 4096
+
+
+def test_length_classes_of_captured_steps():
+    from prefixserve_b200.engine.step import ModelRunner
+    assert ModelRunner._length_classes(8192) == (1024, 2048, 4096, 8192)
+    assert ModelRunner._length_classes(256) == (256,)            # shorter than the smallest class: one class
+    assert ModelRunner._length_classes(1024) == (1024,)
+    assert ModelRunner._length_classes(5000) == (1024, 2048, 4096, 5000)
+    assert ModelRunner._length_classes(300, 64) == (64, 128, 256, 300)
