@@ -1,4 +1,4 @@
-// C[M,N] = A[M,K] * W[N,K]^T in bfloat16 for a few dozen rows (17..64: decoding with that many requests, short
+// C[M,N] = A[M,K] * W[N,K]^T in bfloat16 for a few dozen rows (up to 64: decoding with that many requests, short
 // prompt portions).  Such a product is bound by reading W once, and a kernel that tiles the output 128 rows at a time
 // would fill a quarter of every instruction and of few SMs.  Here the roles are swapped and the contraction is shared:
 //   * W is the instruction's M operand: an output tile is 128 rows of W by all MT (32 or 64) rows of A, which sit in
@@ -26,7 +26,7 @@ constexpr int W_BYTES = FEATURES * BK * 2;  // 16 KB a stage
 
 template <int MT>
 struct Shape {
-  static_assert(MT == 32 || MT == 64, "row tiles built");
+  static_assert(MT == 32 || MT == 64, "row tiles built");  // (a tile of 16 rows was no faster for 9 to 16 of them)
   static constexpr int X_BYTES = MT * BK * 2;
   static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
   static constexpr int PART_BYTES = MT * FEATURES * 4;  // [token][feature] float32

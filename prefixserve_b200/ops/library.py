@@ -90,7 +90,7 @@ _SIGNATURES: dict[str, list] = {
     "psb_gemm_tcgen05_rope": [P, P, I, I, I, P, P, P, I, P, P, P, P, I, I, I, I, I, I, P],
     # () -> 0 while no bounded wait of the tcgen05 kernel has ever run out
     "psb_tcgen05_status": [],
-    # the product for 17..64 rows: (a, w, c, M, N, K, stream)
+    # the product for a few dozen rows (up to 64): (a, w, c, M, N, K, stream)
     "psb_gemm_fewrows": [P, P, P, I, I, I, P],
     # (a, w, act, M, I, K, activation, stream)
     "psb_gemm_fewrows_gated": [P, P, P, I, I, I, I, P],

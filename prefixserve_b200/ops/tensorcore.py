@@ -10,7 +10,12 @@ from .library import check, launch_counts, lib, stream_handle
 
 
 # Tuning, set from measurements on B200 at Llama-1B sizes:
-STREAM_M = 16       # rows up to which the persistent streaming kernel is used (its limit is 16)
+STREAM_M = 8        # rows up to which a layer's products run on the persistent streaming kernels (their limit is 16, but
+                    # from 9 rows on they stream a second tile of rows beside every weight tile and the few-row tcgen05
+                    # product, with the norm as a kernel of its own, is ahead: decode steps at Llama-1B sizes, context
+                    # 4,096, ms a step with the streaming kernels / the few-row product: 8 requests 0.908 / 1.011,
+                    # 9: 1.079 / 1.058, 10: 1.130 / 1.089, 12: 1.230 / 1.136, 14: 1.242 / 1.182, 16: 1.267 / 1.187)
+STREAM_M_HEAD = 16  # ... and products with float32 output (the LM head, which the few-row product does not do)
 USE_TCGEN05 = True  # products with more rows than STREAM_M: this library's tcgen05/TMEM/TMA kernel (else cuBLAS)
 TCGEN05_MIN_TILES = 120  # ... when the kernel would cut the product into at least this many output tiles (128 rows by
                          # 256, 192 or 128 columns, whichever gets it done in the fewest, shortest rounds); smaller ones
@@ -77,8 +82,10 @@ def gemm_stream_gated(x: torch.Tensor, w_gate_up: torch.Tensor, activation: int 
 FUSE_NORM = True    # few rows: fold the residual sum and the RMSNorm in front of a product into the streaming kernel
 
 
-def _norm_fusable(x, w: torch.Tensor) -> bool:
+def _norm_fusable(x, w: torch.Tensor, limit: int | None = None) -> bool:
     m, k = x.shape
+    if m > min(16, STREAM_M if limit is None else limit):
+        return False
     pending = x.pending
     return (FUSE_NORM and w.is_contiguous() and w.shape[1] == k and x.h.is_contiguous() and x.h.dtype == torch.float32
             and (pending is None or (pending.dtype == torch.bfloat16 and pending.is_contiguous() and pending.shape == x.h.shape))
@@ -91,7 +98,7 @@ def norm_linear_bf16(x, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor
     ``x`` is an ``ops.NormedRows`` that nobody has turned into a tensor yet.  The float32 stream after the sum goes to
     a new tensor (other CTAs still read the old one while the first CTA writes), which ``x`` is told of.
     """
-    if out_dtype not in _OUT_CODE or not _norm_fusable(x, w):
+    if out_dtype not in _OUT_CODE or not _norm_fusable(x, w, STREAM_M_HEAD if out_dtype == torch.float32 else STREAM_M):
         return None
     m, k = x.shape
     n = w.shape[0]
@@ -146,7 +153,7 @@ def _fewrows_ok(x: torch.Tensor, w: torch.Tensor, kind: str = "plain") -> bool:
 
 
 def gemm_fewrows(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-    """x[M,K] @ w[N,K]^T -> bfloat16 for 17..64 rows: W as the tensor-core instruction's M operand, the contraction
+    """x[M,K] @ w[N,K]^T -> bfloat16 for up to 64 rows: W as the tensor-core instruction's M operand, the contraction
     shared out over a thread-block cluster that adds its partial sums up through distributed shared memory."""
     m, k = x.shape
     y = torch.empty((m, w.shape[0]), dtype=torch.bfloat16, device=x.device)
@@ -197,7 +204,7 @@ def gemm_tcgen05_gated(x: torch.Tensor, w_gate_up: torch.Tensor, activation: int
 
 def tcgen05_qkv_rope_bf16(x: torch.Tensor, w_qkv, positions, token_item, cos, sin, table, kv, hq, hkv, d, page_size) -> torch.Tensor | None:
     """The projection of an attention layer for many tokens on the tcgen05 kernel, rotation and append to the pages in
-    its epilogue (for 17..64 tokens: on the few-row kernel, which does the same); None when neither takes the shape."""
+    its epilogue (for a few dozen tokens: on the few-row kernel, which does the same); None when neither takes the shape."""
     if not (kv.is_contiguous() and (cos is None or (cos.is_contiguous() and sin.is_contiguous()))):
         return None
     m, k = x.shape
@@ -222,7 +229,7 @@ def tcgen05_qkv_rope_bf16(x: torch.Tensor, w_qkv, positions, token_item, cos, si
 def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     """x[M,K] @ w[N,K]^T for bfloat16 operands, float32 accumulation.
 
-    Up to 16 rows (decode): the weight-streaming kernel of this library.  A few dozen rows: its few-row tcgen05
+    Up to STREAM_M rows (decode): the weight-streaming kernel of this library.  A few dozen rows: its few-row tcgen05
     kernel.  Prefill-sized products with bfloat16 output: its tcgen05 kernel.  What lies between (and outputs in
     float32 with many rows) goes to the library
     product (cuBLAS through torch), which is where the reference calls F.linear for everything
@@ -230,7 +237,7 @@ def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> tor
     """
     m, k = x.shape
     if out_dtype in _OUT_CODE and x.is_contiguous() and w.is_contiguous():
-        if small_m_ok(m, k, min(STREAM_M, 16)):
+        if small_m_ok(m, k, min(STREAM_M_HEAD if out_dtype == torch.float32 else STREAM_M, 16)):
             return gemm_stream(x, w, out_dtype)
         if out_dtype == torch.bfloat16 and _fewrows_ok(x, w):
             return gemm_fewrows(x, w)
