@@ -36,11 +36,13 @@ TCGEN05_PREFILL_MIN_TOKENS = 64   # steps whose longest prompt portion has at le
                                   # on the tcgen05 kernel (tiles of 128 rows); shorter portions fill too little of a tile
 USE_TMA_DECODE = True     # decode attention: the kernel whose keys and values the TMA unit brings in (pages of 16 tokens
                           # or more), for key ranges of at least TMA_DECODE_MIN_RANGE keys; otherwise the one in which
-                          # every lane copies its own pieces.  Measured at Llama-1B sizes, context 4,096: with 64 requests
-                          # (one range of 4,096 keys per CTA) the step takes 2.45 ms with the first and 2.67 with the second;
-                          # with 8 requests (ranges of 512 keys, 32 tiles a CTA) 0.90 against 0.855: a CTA that short pays
-                          # more for filling its ring through one issuing lane than the ring then saves
-TMA_DECODE_MIN_RANGE = 1024
+                          # every lane copies its own pieces.  Measured at Llama-1B sizes, context 4,096, ms a decode step
+                          # with the limit at 1,024 / 512 keys: 8 requests (ranges of 512 keys) 0.874 / 0.857 (means of
+                          # three interleaved runs each, single runs from 0.833 to 0.878), 9 requests 1.086 / 1.049,
+                          # 12: 1.168 / 1.103, 14: 1.220 / 1.149, 16 (ranges of 1,024 either way) 1.209 / 1.193; with 64
+                          # requests (one range of 4,096 keys) 2.45 with this kernel and 2.67 with the other.  Below 512
+                          # keys it loses: one request (ranges of 256 keys) 0.654 with the limit at 512, 0.676 at 256
+TMA_DECODE_MIN_RANGE = 512
 PREFILL_MIN_KEY_RANGES = 3        # ... at least this many: two ranges lose to one tile a CTA (512-token portions, 32 heads
                                   # of 64: 7.24 against 7.04 ms per 2,048 tokens)
 PREFILL_MAX_KEY_RANGES = 8        # prefill attention with few CTAs: at most this many key ranges ...
