@@ -54,7 +54,9 @@ DECODE_MERGE_COST = 8        # split-KV: what one more range costs the merge, in
                              # at 512, 949 at 1,024; 32,768 keys 950 at 128, 866 at 256, 833 at 512, 956 at 1,024)
 DECODE_LANES_FACTOR = 1.2    # split-KV: the kernel for short ranges against the TMA-fed one, per key of a long range
 DECODE_FORCE_CHUNK = 0   # tests and sweeps: the key range of split-KV decode attention, whatever the plan would choose
-DECODE_CTAS_PER_SM = 4   # split-KV: key ranges are sized so that about this many CTAs per SM exist
+DECODE_CTAS_PER_SM = 4   # split-KV: CTAs of the decode kernels an SM holds at a time, heads of 64 (93 to 118 registers, 48 KB)
+DECODE_CTAS_PER_SM_128 = 2  # ... and heads of 128 (168 registers, 64 to 96 KB).  Llama-3B sizes, 8 requests at 4,096 keys: ranges
+                            # of 512 keys (two rounds) 2.349 ms a step, of 1,024 (one round) 2.311; 8B sizes 3.913 / 3.883
 _OUT_CODE = {torch.float32: 0, torch.bfloat16: 1}
 
 
@@ -291,27 +293,33 @@ def attention_bf16_supported(head_dim: int, page_size: int) -> bool:
     return head_dim in (64, 128) and page_size >= 16 and page_size & (page_size - 1) == 0
 
 
-def _decode_key_range(pairs: int, longest: int, sms: int, tma_kernel: bool) -> int:
+def _decode_key_range(pairs: int, longest: int, sms: int, tma_kernel: bool, ctas_per_sm: int | None = None) -> int:
     """The key range of split-KV decode attention for ``pairs`` (request, key/value head) pairs of up to ``longest``
-    keys.  An SM runs DECODE_CTAS_PER_SM CTAs at a time, each at its own pace (a CTA alone on an SM is no faster), so a
+    keys.  An SM runs ``ctas_per_sm`` CTAs at a time (DECODE_CTAS_PER_SM for heads of 64), each at its own pace (a CTA alone on an SM is no faster), so a
     launch takes as many rounds as its CTAs fill those slots, each as long as a range plus a fixed share: one round of
     the shortest ranges that fit into it, unless that leaves many slots empty and several rounds of shorter ranges
     come out ahead (48 requests with 8 heads at 4,096 keys: one round of 384 whole sequences against two rounds of
     1,152 thirds, measured 2.34 against 2.00 ms a step).  Ranges below TMA_DECODE_MIN_RANGE go to the kernel whose
     lanes copy for themselves, which is slower on long ranges (111 against 93 us at 64 requests)."""
-    slots = DECODE_CTAS_PER_SM * sms
+    slots = (ctas_per_sm or DECODE_CTAS_PER_SM) * sms
     pairs = max(1, pairs)
     most = max(1, min(-(-longest // MIN_KEY_RANGE), 4 * (slots // pairs + 1)))  # shorter ranges cost more to merge than they save
-    best_cost, best, best_rounds = None, 64, 0
+    fewest = None   # (rounds, cost, range) of the best plan among those with the fewest rounds
+    best = None     # ... and of the best plan of all
     for splits in range(1, most + 1):
         chunk = -(-(-(-longest // splits)) // 64) * 64
         rounds = -(-(pairs * -(-longest // chunk)) // slots)
         cost = rounds * (chunk + DECODE_RANGE_OVERHEAD) * (1.0 if tma_kernel and chunk >= TMA_DECODE_MIN_RANGE else DECODE_LANES_FACTOR)
         cost += DECODE_MERGE_COST * -(-longest // chunk)  # the kernel that joins the ranges reads one partial result a range
-        # more rounds only for a clear gain: the estimate is rough
-        if best_cost is None or cost < (best_cost if rounds <= best_rounds else 0.85 * best_cost):
-            best_cost, best, best_rounds = cost, chunk, rounds
-    return best
+        plan = (rounds, cost, chunk)
+        if fewest is None or rounds < fewest[0] or (rounds == fewest[0] and cost < fewest[1]):
+            fewest = plan
+        if best is None or cost < best[1]:
+            best = plan
+    # more rounds only for a clear gain: the estimate is rough
+    if best[0] > fewest[0] and best[1] > 0.85 * fewest[1]:
+        best = fewest
+    return best[2]
 
 
 def _attention_plan(new_tokens: Sequence[int], kv_lens: Sequence[int], window: int, group: int, hkv: int, d: int, page: int,
@@ -334,7 +342,8 @@ def _attention_plan(new_tokens: Sequence[int], kv_lens: Sequence[int], window: i
         else:
             longest = max(singles)
         plan["chunk"] = DECODE_FORCE_CHUNK or _decode_key_range(b * hkv, longest, sms, bool(
-            USE_TMA_DECODE and lib().psb_attention_decode_tma_supported(hq_total, hkv, d, page)))
+            USE_TMA_DECODE and lib().psb_attention_decode_tma_supported(hq_total, hkv, d, page)),
+            DECODE_CTAS_PER_SM if d <= 64 else DECODE_CTAS_PER_SM_128)
         plan["max_splits"] = -(-longest // plan["chunk"])
         plan["all_single"] = 1 if len(singles) == b else 0
     portions = [n for n in new_tokens if not (plan["use_decode"] and n == 1)]

@@ -34,6 +34,9 @@ def test_several_rounds_where_one_would_leave_many_slots_empty():
     assert tensorcore._decode_key_range(48 * 8, 4096, 148, True) == 1408
     # 64 requests fill 512 of 592 slots: nothing shorter pays
     assert tensorcore._decode_key_range(64 * 8, 4096, 148, True) == 4096
+    # heads of 128: an SM holds two CTAs, so eight requests take four ranges of 1,024 keys, not eight of 512
+    assert tensorcore._decode_key_range(8 * 8, 4096, 148, True, 2) == 1024
+    assert tensorcore._decode_key_range(8 * 8, 4096, 148, True, 4) == 512
 
 
 def test_length_classes_of_captured_steps():
