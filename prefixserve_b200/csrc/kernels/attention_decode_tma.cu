@@ -241,9 +241,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const __
             if (key > p || key < lo_key) s[half][i] = -INFINITY;
           }
       }
-      float pr[2][4];
+      float pr[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
+        if (r == 1 && G <= 8) continue;  // rows 8..15 of the tile are padding when a group has at most 8 query heads
         float mx = fmaxf(fmaxf(s[0][2 * r], s[0][2 * r + 1]), fmaxf(s[1][2 * r], s[1][2 * r + 1]));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));

@@ -126,11 +126,13 @@ __device__ __forceinline__ void scores(float (&s)[2][4], const uint32_t (&qa)[D 
 }
 
 // Folds one tile's (already masked: -inf where hidden) scores into the running state and accumulates P.V.
+// upper: rows 8..15 of the tile exist (false for the single token of a group of at most 8 query heads: they are padding).
 template <int D>
-__device__ __forceinline__ void fold(RowState<D>& st, float (&s)[2][4], const KVTile<D>& tile, float sl2) {
-  float p[2][4];
+__device__ __forceinline__ void fold(RowState<D>& st, float (&s)[2][4], const KVTile<D>& tile, float sl2, bool upper = true) {
+  float p[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
+    if (r == 1 && !upper) continue;
     float mx = fmaxf(fmaxf(s[0][2 * r], s[0][2 * r + 1]), fmaxf(s[1][2 * r], s[1][2 * r + 1]));
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
@@ -632,7 +634,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     float s[2][4];
     scores<D>(s, qa, cur);
     if (key0 + 15 > p || key0 < lo_key) mask_tile(s, key0, t, pos, lo);
-    fold<D>(st, s, cur, sl2);
+    fold<D>(st, s, cur, sl2, G > 8);
   }
   cp_async_wait<0>();
   __syncthreads();  // every warp is done with its ring: the same memory now carries the merge
