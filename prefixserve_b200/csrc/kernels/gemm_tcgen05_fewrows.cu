@@ -12,6 +12,11 @@
 //     activation (W = [gate; up], a tile = 64 gate rows and the 64 up rows that go with them), or the rotation and the
 //     append to the cache pages (RopeArgs in common.cuh; the tile's features are then in the pair-interleaved order,
 //     so the partners of a thread's four elements sit two lanes away).
+// The RMSNorm between two such products needs no kernel of its own (prefixserve/model/llama.py:63-69, :117-121 of
+// PrefixServe).  The product in front of it (O or down) adds its sums, rounded to bfloat16 as a stored product would
+// be, to the float32 stream, writes the stream back, writes v * gain in bfloat16 for the product behind the norm, and
+// leaves its tile's share of every row's sum(v^2); the product behind it (QKV, gate/up) adds those shares up in tile
+// order and scales its own sums by rsqrt(mean + eps): the same order of roundings as the streaming kernels' norm.
 // 192 threads: warp 0 producer (W before the dependency wait, since weights do not depend on the preceding kernel;
 // A after it), warp 1 issues tcgen05.mma (M=128, N=MT, K=16), warps 2..5 read the accumulator and do the reduction.
 // Every mbarrier wait is bounded (tcgen05.cuh); the cluster barriers are reached by every thread whatever happened.
@@ -46,6 +51,22 @@ struct Barriers {
 static_assert(sizeof(Barriers) <= 256, "room kept for the barriers");
 
 enum : int { MODE_PLAIN = 0, MODE_GATED = 1, MODE_ROPE = 2 };
+
+constexpr int SSQ_PITCH = 64;  // floats per tile in the array of partial sums of squares: one per row of A
+
+// The norm around a product (all null: none).  Behind a norm: ssq_in [ssq_parts][SSQ_PITCH] float32, the tiles' shares of
+// every row's sum of squares; the row's sums are scaled by rsqrt(sum / width + eps).  In front of a norm (plain products
+// only): stream [M, N] float32 is read, added to and written; gained [M, N] bfloat16 takes v * gain; ssq_out
+// [tiles][SSQ_PITCH] this product's shares.
+struct NormArgs {
+  const float* ssq_in;
+  int ssq_parts;
+  float eps, inv_width;
+  float* stream;
+  const float* gain;
+  __nv_bfloat16* gained;
+  float* ssq_out;
+};
 
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
@@ -94,7 +115,7 @@ template <int MT>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_fewrows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     __nv_bfloat16* __restrict__ C, int M, int N_out, int K, int ldc, int up_offset, int mode, int activation,
-                    const RopeArgs rope) {
+                    const RopeArgs rope, const NormArgs norm) {
   using S = Shape<MT>;
   constexpr uint32_t INSTR_DESC = instr_desc(FEATURES, MT, false);
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -112,6 +133,12 @@ gemm_fewrows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   const int k_blocks = (K + BK - 1) / BK;
   const int kb0 = (int)(((long)rank * k_blocks) / ks), kb1 = (int)(((long)(rank + 1) * k_blocks) / ks);
   const int nkb = kb1 - kb0;
+
+  __shared__ float row_factor[SSQ_PITCH];  // behind a norm: rsqrt(mean(v^2) + eps) of every row
+  constexpr int EARLY = 4;                 // in front of a norm: rows whose piece of the stream a thread fetches ahead
+  float4 early_h[EARLY], early_gain = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int it = 0; it < EARLY; ++it) early_h[it] = make_float4(0.f, 0.f, 0.f, 0.f);
 
   pdl_trigger();
   if (threadIdx.x == 0) {
@@ -181,6 +208,28 @@ gemm_fewrows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     pdl_wait();
     const int quarter = warp & 3;  // a warp may only read tensor-memory lanes [32*(warp%4), +32)
     const int feature = quarter * 32 + lane;
+    // What the reduction below needs of the norm around this product does not depend on the product: it is fetched
+    // now, while the instructions run.  Behind a norm: every row's factor, into shared memory (the cluster barrier
+    // below publishes it).  In front of one: this thread's pieces of the stream and of the gain, into registers.
+    {
+      const int e = threadIdx.x - 64;
+      if (norm.ssq_in && e < M && e < SSQ_PITCH) {
+        float total = 0.f;
+#pragma unroll 8
+        for (int p = 0; p < norm.ssq_parts; ++p) total += __ldg(norm.ssq_in + p * SSQ_PITCH + e);
+        row_factor[e] = rsqrtf(total * norm.inv_width + norm.eps);
+      }
+      if (norm.stream) {
+        const int col = n0 + (e & 31) * 4;
+        const bool whole = col + 4 <= N_out && (ldc & 3) == 0;
+        early_gain = whole ? __ldg(reinterpret_cast<const float4*>(norm.gain + col)) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int it = 0; it < EARLY; ++it) {
+          const int t = (int)rank + (int)ks * ((e >> 5) + 4 * it);
+          early_h[it] = (whole && t < M) ? *reinterpret_cast<const float4*>(norm.stream + (size_t)t * ldc + col) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+    }
     if (mbar_wait(&bars->acc_full, 0, abort, 3)) {
       fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
@@ -203,6 +252,8 @@ gemm_fewrows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const int e = threadIdx.x - 64;  // 0..127
     const uint32_t part_addr = smem_u32(part);
     const bool aligned = (ldc & 3) == 0;
+    // behind a norm: the factor of row t
+    auto row_scale = [&](int t) { return norm.ssq_in ? row_factor[t] : 1.f; };
     if (gated) {
       // 64 output columns a tile: features 4g..4g+3 of the gate half go with 64+4g.. of the up half; sixteen threads
       // a token, eight tokens at a time
@@ -212,10 +263,11 @@ gemm_fewrows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         const float4 g4 = cluster_sum4(part_addr + (uint32_t)(t * FEATURES + f) * 4u, ks);
         const float4 u4 = cluster_sum4(part_addr + (uint32_t)(t * FEATURES + 64 + f) * 4u, ks);
         const float g[4] = {g4.x, g4.y, g4.z, g4.w}, u[4] = {u4.x, u4.y, u4.z, u4.w};
+        const float inv = row_scale(t);
         float o[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i)  // the reference rounds both projections to bfloat16 before the activation
-          o[i] = gate_act(round_bf16(g[i]), activation) * round_bf16(u[i]);
+          o[i] = gate_act(round_bf16(g[i] * inv), activation) * round_bf16(u[i] * inv);
         store4(C + (size_t)t * ldc, col, N_out, aligned, o);
       }
     } else {
@@ -224,9 +276,40 @@ gemm_fewrows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 #pragma unroll 2
       for (int t = (int)rank + (int)ks * (e >> 5); t < M; t += 4 * (int)ks) {
         const float4 v4 = cluster_sum4(part_addr + (uint32_t)(t * FEATURES + f) * 4u, ks);
-        float o[4] = {v4.x, v4.y, v4.z, v4.w};
+        const float inv = row_scale(t);
+        float o[4] = {v4.x * inv, v4.y * inv, v4.z * inv, v4.w * inv};
         if (mode == MODE_PLAIN) {
-          store4(C + (size_t)t * ldc, col, N_out, aligned, o);
+          if (norm.stream) {
+            // in front of a norm: the residual sum, the gained rows and this tile's share of the row's sum of squares
+            float ss = 0.f;
+            float gained[4] = {0.f, 0.f, 0.f, 0.f};
+            float* hrow = norm.stream + (size_t)t * ldc;
+            const int it = (t - (int)rank) / (int)ks / 4;  // which of this thread's rows
+            if (col + 4 <= N_out && aligned && it < EARLY) {
+              float4 hv = early_h[0];
+#pragma unroll
+              for (int k = 1; k < EARLY; ++k)
+                if (it == k) hv = early_h[k];
+              const float v[4] = {hv.x + round_bf16(o[0]), hv.y + round_bf16(o[1]), hv.z + round_bf16(o[2]), hv.w + round_bf16(o[3])};
+              *reinterpret_cast<float4*>(hrow + col) = make_float4(v[0], v[1], v[2], v[3]);
+              gained[0] = v[0] * early_gain.x; gained[1] = v[1] * early_gain.y; gained[2] = v[2] * early_gain.z; gained[3] = v[3] * early_gain.w;
+              ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+            } else {
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                if (col + i < N_out) {
+                  const float v = hrow[col + i] + round_bf16(o[i]);
+                  hrow[col + i] = v;
+                  gained[i] = v * __ldg(norm.gain + col + i);
+                  ss += v * v;
+                }
+            }
+            store4(norm.gained + (size_t)t * ldc, col, N_out, aligned, gained);
+            ss = warp_sum(ss);  // a warp a token
+            if ((e & 31) == 0) norm.ssq_out[tile * SSQ_PITCH + t] = ss;
+          } else {
+            store4(C + (size_t)t * ldc, col, N_out, aligned, o);
+          }
           continue;
         }
         // the projection of an attention layer: what rope_store_row of the many-row kernel does.  A block of 16
@@ -297,7 +380,8 @@ int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) 
 
 template <int MT>
 cudaError_t launch_kernel(dim3 grid, cudaStream_t stream, const CUtensorMap& map_w, const CUtensorMap& map_x, __nv_bfloat16* c,
-                          int M, int N_out, int K, int ldc, int up_offset, int mode, int activation, const RopeArgs& rope) {
+                          int M, int N_out, int K, int ldc, int up_offset, int mode, int activation, const RopeArgs& rope,
+                          const NormArgs& norm) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(THREADS);
@@ -315,7 +399,7 @@ cudaError_t launch_kernel(dim3 grid, cudaStream_t stream, const CUtensorMap& map
     cfg.numAttrs = 2;
   }
   cfg.attrs = attr;
-  return cudaLaunchKernelEx(&cfg, gemm_fewrows_kernel<MT>, map_w, map_x, c, M, N_out, K, ldc, up_offset, mode, activation, rope);
+  return cudaLaunchKernelEx(&cfg, gemm_fewrows_kernel<MT>, map_w, map_x, c, M, N_out, K, ldc, up_offset, mode, activation, rope, norm);
 }
 
 // How many clusters of `ks` CTAs the device holds at once (one CTA an SM, a cluster inside one GPC); asked once per
@@ -370,7 +454,7 @@ int choose_splits(int tiles, int k_blocks) {
 
 template <int MT>
 int launch_shape(const void* a, const void* w, void* c, int M, int w_rows, int N_out, int K, int up_offset, int mode, int activation,
-                 cudaStream_t stream, const RopeArgs& rope) {
+                 cudaStream_t stream, const RopeArgs& rope, const NormArgs& norm) {
   static PsbPerDevice configured;  // more than 48 KB of dynamic shared memory has to be asked for once
   if (!configured.get()) {
     cudaError_t e = cudaFuncSetAttribute(gemm_fewrows_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape<MT>::SMEM_BYTES);
@@ -385,7 +469,7 @@ int launch_shape(const void* a, const void* w, void* c, int M, int w_rows, int N
   const int k_blocks = (K + BK - 1) / BK;
   const int ks = choose_splits<MT>(tiles, k_blocks);
   cudaError_t e = launch_kernel<MT>(dim3(ks, tiles), stream, map_w, map_x, (__nv_bfloat16*)c, M, N_out, K, N_out, up_offset, mode,
-                                    activation, rope);
+                                    activation, rope, norm);
   if (e != cudaSuccess) {
     cudaGetLastError();
     PSB_REFUSE("gemm_fewrows: launch failed: %s (M=%d N=%d K=%d ranges=%d)", cudaGetErrorString(e), M, N_out, K, ks);
@@ -394,11 +478,14 @@ int launch_shape(const void* a, const void* w, void* c, int M, int w_rows, int N
 }
 
 int launch(const void* a, const void* w, void* c, int M, int w_rows, int N_out, int K, int up_offset, int mode, int activation,
-           cudaStream_t stream, const RopeArgs& rope = RopeArgs{}) {
+           cudaStream_t stream, const RopeArgs& rope = RopeArgs{}, const NormArgs& norm = NormArgs{}) {
+  if (norm.ssq_in && (norm.ssq_parts < 1 || !(norm.eps > 0.f))) PSB_REFUSE("gemm_fewrows: the norm in front needs its parts and a positive eps");
+  if (norm.stream && (mode != MODE_PLAIN || !norm.gain || !norm.gained || !norm.ssq_out || (((uintptr_t)norm.stream | (uintptr_t)norm.gained) & 15)))
+    PSB_REFUSE("gemm_fewrows: a product in front of a norm is a plain one with stream, gain, gained rows and shares given (16-byte aligned)");
   if (M < 1 || M > 64 || N_out < 1 || K < 8 || K % 8) PSB_REFUSE("gemm_fewrows: needs 1..64 rows and K a multiple of 8 (M=%d N=%d K=%d)", M, N_out, K);
   if (((uintptr_t)a | (uintptr_t)w | (uintptr_t)c) & 15) PSB_REFUSE("gemm_fewrows: operands must be 16-byte aligned");
-  if (M <= 32) return launch_shape<32>(a, w, c, M, w_rows, N_out, K, up_offset, mode, activation, stream, rope);
-  return launch_shape<64>(a, w, c, M, w_rows, N_out, K, up_offset, mode, activation, stream, rope);
+  if (M <= 32) return launch_shape<32>(a, w, c, M, w_rows, N_out, K, up_offset, mode, activation, stream, rope, norm);
+  return launch_shape<64>(a, w, c, M, w_rows, N_out, K, up_offset, mode, activation, stream, rope, norm);
 }
 
 }  // namespace
@@ -432,6 +519,54 @@ PSB_API int psb_gemm_fewrows_rope(const void* a, const void* w, int M, int K, co
   while ((1 << rope.page_shift) < page_size) ++rope.page_shift;
   const int N = (hq + 2 * hkv) * D;
   return launch(a, w, q_out, M, N, N, K, 0, MODE_ROPE, 0, stream, rope);
+}
+
+namespace {
+NormArgs behind_norm(const void* ssq_in, int ssq_parts, float eps, int width) {
+  NormArgs n{};
+  n.ssq_in = (const float*)ssq_in; n.ssq_parts = ssq_parts; n.eps = eps; n.inv_width = 1.f / (float)width;
+  return n;
+}
+}  // namespace
+
+// The same three products behind a norm whose rows arrive as v * gain (bfloat16) with the shares of their sums of squares
+// (ssq_in [ssq_parts][64] float32, from psb_gemm_fewrows_add_norm): every sum is scaled by rsqrt(sum(v^2) / K + eps).
+PSB_API int psb_gemm_fewrows_scaled(const void* a, const void* w, void* c, int M, int N, int K, const void* ssq_in, int ssq_parts,
+                                    float eps, cudaStream_t stream) {
+  return launch(a, w, c, M, N, N, K, 0, MODE_PLAIN, 0, stream, RopeArgs{}, behind_norm(ssq_in, ssq_parts, eps, K));
+}
+PSB_API int psb_gemm_fewrows_gated_scaled(const void* a, const void* w, void* act, int M, int I, int K, int activation,
+                                          const void* ssq_in, int ssq_parts, float eps, cudaStream_t stream) {
+  if (!psb_activation_known(activation)) PSB_REFUSE("gemm_fewrows_gated: activation code %d is not built", activation);
+  return launch(a, w, act, M, 2 * I, I, K, I, MODE_GATED, activation, stream, RopeArgs{}, behind_norm(ssq_in, ssq_parts, eps, K));
+}
+PSB_API int psb_gemm_fewrows_rope_scaled(const void* a, const void* w, int M, int K, const void* positions, const void* token_item,
+                                         const void* table, int table_width, const void* cos_t, const void* sin_t, void* kv,
+                                         void* q_out, int hq, int hkv, int D, int page_size, int num_pages, int max_positions,
+                                         const void* ssq_in, int ssq_parts, float eps, cudaStream_t stream) {
+  if (hq < 1 || hkv < 1 || D < 16 || D % 16) PSB_REFUSE("gemm_fewrows_rope: needs a head size that is a multiple of 16 (hq=%d hkv=%d D=%d)", hq, hkv, D);
+  if (page_size < 1 || (page_size & (page_size - 1)) || num_pages < 1 || table_width < 1) PSB_REFUSE("gemm_fewrows_rope: page size %d must be a power of two (pages=%d, width=%d)", page_size, num_pages, table_width);
+  if (!positions || !token_item || !table || !kv || !q_out) PSB_REFUSE("gemm_fewrows_rope: cache arguments missing");
+  if ((cos_t == nullptr) != (sin_t == nullptr) || (cos_t && max_positions < 1)) PSB_REFUSE("gemm_fewrows_rope: angle tables incomplete");
+  if (((uintptr_t)kv | (uintptr_t)q_out | (uintptr_t)cos_t | (uintptr_t)sin_t) & 15) PSB_REFUSE("gemm_fewrows_rope: cache, queries and angle tables must be 16-byte aligned");
+  RopeArgs rope;
+  rope.positions = (const int32_t*)positions; rope.token_item = (const int32_t*)token_item; rope.table = (const int32_t*)table;
+  rope.cos_t = (const float*)cos_t; rope.sin_t = (const float*)sin_t; rope.kv = (__nv_bfloat16*)kv; rope.q_out = (__nv_bfloat16*)q_out;
+  rope.table_width = table_width; rope.hq = hq; rope.hkv = hkv; rope.D = D; rope.num_pages = num_pages; rope.max_positions = max_positions;
+  rope.page_shift = 0;
+  while ((1 << rope.page_shift) < page_size) ++rope.page_shift;
+  const int N = (hq + 2 * hkv) * D;
+  return launch(a, w, q_out, M, N, N, K, 0, MODE_ROPE, 0, stream, rope, behind_norm(ssq_in, ssq_parts, eps, K));
+}
+
+// A product in front of a norm: stream[M,N] += bfloat16(A W^T) (float32, in place); gained[M,N] = bfloat16(stream * gain);
+// ssq_out [ceil(N/128)][64] float32 takes each tile's share of every row's sum of stream^2.  Returns the number of tiles
+// through *tiles_out.
+PSB_API int psb_gemm_fewrows_add_norm(const void* a, const void* w, void* stream_io, const void* gain, void* gained, void* ssq_out,
+                                      int M, int N, int K, cudaStream_t stream) {
+  NormArgs n{};
+  n.stream = (float*)stream_io; n.gain = (const float*)gain; n.gained = (__nv_bfloat16*)gained; n.ssq_out = (float*)ssq_out;
+  return launch(a, w, gained, M, N, N, K, 0, MODE_PLAIN, 0, stream, RopeArgs{}, n);
 }
 
 // For tests: 1, 2, 4 or 8 makes every later product cut the contraction into that many ranges (where it has that many

@@ -2,7 +2,7 @@
 the host and raises ``KernelError`` instead of launching on arguments a kernel
 was not written for."""
 
-from .deferred import NormedRows  # noqa: F401
+from .deferred import NormedRows, PendingProduct  # noqa: F401
 from .kernels import (  # noqa: F401
     ACTIVATIONS,
     KernelError,
@@ -11,6 +11,7 @@ from .kernels import (  # noqa: F401
     attention,
     embedding,
     gated_linear,
+    last_product,
     linear,
     pair_interleaved_order,
     qkv_rope_append,

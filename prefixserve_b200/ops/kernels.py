@@ -10,7 +10,7 @@ import math
 
 import torch
 
-from .deferred import NormedRows
+from .deferred import NormedRows, PendingProduct
 from .library import KernelError, check, lib, stream_handle
 
 F32, BF16 = 0, 1
@@ -61,6 +61,8 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None =
 def add_rmsnorm(h: torch.Tensor, delta: torch.Tensor | None, gain: torch.Tensor, eps: float,
                 out_dtype: torch.dtype, rows: torch.Tensor | None = None) -> torch.Tensor:
     """h += delta (float32, in place, unless ``rows``); returns gain * rmsnorm(h) for all or the chosen rows."""
+    if isinstance(delta, PendingProduct):
+        delta = delta.tensor()
     _dev(h, "residual stream")
     if h.dtype != torch.float32 or h.dim() != 2:
         raise KernelError(f"residual stream must be float32 [T, H], is {h.dtype} {tuple(h.shape)}")
@@ -115,12 +117,30 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
             y = norm_linear_bf16(x, w, out_dtype or x.dtype)
             if y is not None:
                 return y
+        if (out_dtype or x.dtype) == torch.bfloat16 and w.dtype == torch.bfloat16:
+            from .tensorcore import fewrows_behind_norm
+            y = fewrows_behind_norm(x, w, "plain")
+            if y is not None:
+                return y
         x = x.tensor()
     out_dtype = out_dtype or x.dtype
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
         from .tensorcore import linear_bf16
         return linear_bf16(x, w, out_dtype)
     return gemm_nt_simt(x, w, out_dtype)
+
+
+def last_product(x: torch.Tensor, w: torch.Tensor, ctx=None):
+    """A sublayer's last product, x @ w^T, whose only reader is the residual sum in front of the next norm.  Where the
+    step says that every norm downstream takes one (``ctx.extras["lazy_products"]``) and the rows are few enough for
+    the kernel that can carry that sum and the norm's share in its epilogue, the product is handed on unrun
+    (``PendingProduct``); otherwise it runs now."""
+    extras = getattr(ctx, "extras", None)
+    if extras is not None and extras.get("lazy_products") and x.dim() == 2 and x.is_cuda:
+        from .tensorcore import fewrows_lazy_ok
+        if fewrows_lazy_ok(x, w):
+            return PendingProduct(x, w)
+    return linear(x, w)
 
 
 ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}  # the codes the kernels know (PsbAct in common.cuh)
@@ -140,6 +160,11 @@ def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, activation: str = "si
         if x.fusable and x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16:
             from .tensorcore import norm_gated_linear_bf16
             act = norm_gated_linear_bf16(x, w_gate_up, code)
+            if act is not None:
+                return act
+        if w_gate_up.dtype == torch.bfloat16:
+            from .tensorcore import fewrows_behind_norm
+            act = fewrows_behind_norm(x, w_gate_up, "gated", activation=code)
             if act is not None:
                 return act
         x = x.tensor()
@@ -236,6 +261,10 @@ def qkv_rope_append(x: NormedRows, w_qkv: torch.Tensor, positions: torch.Tensor,
         q = norm_qkv_rope_bf16(x, w_qkv, positions, token_item, cos, sin, table, kv, num_heads, num_kv_heads, head_dim, page_size)
         if q is not None:
             return q
+    from .tensorcore import fewrows_behind_norm
+    q = fewrows_behind_norm(x, w_qkv, "rope", rope=(positions, token_item, cos, sin, table, kv, num_heads, num_kv_heads, head_dim, page_size))
+    if q is not None:
+        return q
     return tcgen05_qkv_rope_bf16(x.tensor(), w_qkv, positions, token_item, cos, sin, table, kv, num_heads, num_kv_heads,
                                  head_dim, page_size)
 
@@ -295,6 +324,8 @@ def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
 
 def residual_add(h: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
     """h += delta in place (h float32, delta float32 or bfloat16 of the same shape); returns h."""
+    if isinstance(delta, PendingProduct):
+        delta = delta.tensor()
     _dev(h, "residual stream"), _dev(delta, "sublayer output")
     if h.dtype != torch.float32 or delta.shape != h.shape:
         raise KernelError(f"residual stream must be float32 and the output must match it: {h.dtype} {tuple(h.shape)} vs {tuple(delta.shape)}")

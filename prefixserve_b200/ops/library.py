@@ -96,6 +96,12 @@ _SIGNATURES: dict[str, list] = {
     "psb_gemm_fewrows_gated": [P, P, P, I, I, I, I, P],
     # (a, w, M, K, positions, token_item, table, table_width, cos, sin, kv, q_out, hq, hkv, D, page_size, num_pages, max_positions, stream)
     "psb_gemm_fewrows_rope": [P, P, I, I, P, P, P, I, P, P, P, P, I, I, I, I, I, I, P],
+    # behind a norm: (..., ssq_in, ssq_parts, eps, stream)
+    "psb_gemm_fewrows_scaled": [P, P, P, I, I, I, P, I, F, P],
+    "psb_gemm_fewrows_gated_scaled": [P, P, P, I, I, I, I, P, I, F, P],
+    "psb_gemm_fewrows_rope_scaled": [P, P, I, I, P, P, P, I, P, P, P, P, I, I, I, I, I, I, P, I, F, P],
+    # in front of a norm: (a, w, stream float32 in/out, gain, gained bf16 out, ssq_out, M, N, K, stream)
+    "psb_gemm_fewrows_add_norm": [P, P, P, P, P, P, I, I, I, P],
     "psb_gemm_fewrows_splits": [I],
     "psb_gemm_fewrows_status": [],
     # (logits, temperature, seed, position, out, scratch, S, V, stream)

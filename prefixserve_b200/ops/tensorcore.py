@@ -24,13 +24,15 @@ TCGEN05_MIN_ROWS = 128   # ... and it has at least one full tile of rows: with 6
                          # (gate/up of 64 decoded tokens: 18 us against the library's 12.7 plus 2.4 for the activation)
 USE_FEWROWS = True   # products with more rows than STREAM_M and at most FEWROWS_MAX[kind]: the kernel that puts the rows in
                      # the instruction's N dimension and shares the contraction out over a cluster (else cuBLAS).  Decode
-                     # steps at Llama-1B sizes, context 4,096, ms a step without / with the kernel for all three kinds:
-                     # 20 requests 1.420 / 1.350, 32: 1.681 / 1.610, 48: 2.372 / 2.361 (plain alone 2.349), 64: 2.395 /
-                     # 2.420.  Alone, the kernel matches cuBLAS on the narrow matrices (O 5.9 us both at 64 rows, down
-                     # 11.8 against 13.4) and loses on gate/up from 33 rows on (17.5 against 12.6 + 2.4 for the
-                     # activation kernel: 128 one-tile CTAs that fill, stream and drain in step leave the memory idle
-                     # at both ends)
-FEWROWS_MAX = {"plain": 48, "gated": 32, "rope": 32}
+                     # steps at Llama-1B sizes, context 4,096, ms a step, the library products with their norm, rotary
+                     # and activation kernels / this kernel with a norm kernel between the products / this kernel with
+                     # the norm carried by the products around it (FEWROWS_FUSE_NORM): 32 requests 1.681 / 1.610 / 1.533,
+                     # 48: 2.372 / 2.361 / 1.922 (the last two after the key ranges of attention changed as well),
+                     # 64: 2.335 / 2.420 / 2.342.  Alone, the kernel matches cuBLAS on the narrow matrices (O 5.9 us
+                     # both at 64 rows, down 11.8 against 13.4) and loses on gate/up from 33 rows on (17.5 against
+                     # 12.6 + 2.4 for the activation kernel: 128 one-tile CTAs that fill, stream and drain in step
+                     # leave the memory idle at both ends); what it saves is the kernels between the products
+FEWROWS_MAX = {"plain": 64, "gated": 64, "rope": 64}
 WIDE_BELOW_TILES = 600   # matrices with fewer 16-row tiles than this get 16 warps per CTA instead of 8
 TCGEN05_PREFILL_MIN_TOKENS = 64   # steps whose longest prompt portion has at least this many tokens run prefill attention
                                   # on the tcgen05 kernel (tiles of 128 rows); shorter portions fill too little of a tile
@@ -91,6 +93,8 @@ def _norm_fusable(x, w: torch.Tensor, limit: int | None = None) -> bool:
     if m > min(16, STREAM_M if limit is None else limit):
         return False
     pending = x.pending
+    if pending is not None and not isinstance(pending, torch.Tensor):
+        return False  # a product that has not run yet: the few-row kernels take it
     return (FUSE_NORM and w.is_contiguous() and w.shape[1] == k and x.h.is_contiguous() and x.h.dtype == torch.float32
             and (pending is None or (pending.dtype == torch.bfloat16 and pending.is_contiguous() and pending.shape == x.h.shape))
             and k % 32 == 0 and 0 < m <= 16 and bool(lib().psb_gemm_stream_norm_supported(m, k)))
@@ -172,6 +176,73 @@ def gemm_fewrows_gated(x: torch.Tensor, w_gate_up: torch.Tensor, activation: int
     check(lib().psb_gemm_fewrows_gated(x.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(), m, inter, k, activation,
                                        stream_handle()), "gemm_fewrows_gated")
     return act
+
+
+FEWROWS_FUSE_NORM = True  # few-row products around a norm: the one in front carries the residual sum, the gain and its share of
+                          # the sums of squares in its epilogue, the one behind scales its sums (no norm kernel between them)
+SSQ_PITCH = 64            # floats a tile in the array of shares (as in gemm_tcgen05_fewrows.cu)
+
+
+def fewrows_lazy_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether a sublayer's last product may be handed on unrun: bfloat16, and so few rows that both the few-row
+    products in front of and behind the next norm take them."""
+    m = x.shape[0]
+    return (FEWROWS_FUSE_NORM and USE_FEWROWS and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and STREAM_M < m <= min(FEWROWS_MAX.values()) and _fewrows_ok(x, w, "plain"))
+
+
+def fewrows_add_norm(x: torch.Tensor, w: torch.Tensor, h: torch.Tensor, gain: torch.Tensor):
+    """h += bfloat16(x @ w^T) in place (float32); returns (bfloat16(h * gain) [M, N], the tiles' shares of every row's
+    sum(h^2) as float32 [tiles, 64]), or None when the few-row kernel does not take the shapes."""
+    m, k = x.shape
+    n = w.shape[0]
+    if not (_fewrows_ok(x, w, "plain") and h.dtype == torch.float32 and h.is_contiguous() and h.shape == (m, n)
+            and gain.dtype == torch.float32 and gain.numel() == n and h.data_ptr() % 16 == 0):
+        return None
+    gained = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+    shares = torch.empty((-(-n // 128), SSQ_PITCH), dtype=torch.float32, device=x.device)
+    check(lib().psb_gemm_fewrows_add_norm(x.data_ptr(), w.data_ptr(), h.data_ptr(), gain.data_ptr(), gained.data_ptr(),
+                                          shares.data_ptr(), m, n, k, stream_handle()), "gemm_fewrows_add_norm")
+    return gained, shares
+
+
+def fewrows_behind_norm(x, w: torch.Tensor, kind: str, activation: int = 0, rope=None) -> torch.Tensor | None:
+    """The product behind a norm whose input is still ``x`` (a NormedRows with a product pending in front of it), on the
+    few-row kernel with the norm's factor applied to its sums; None when that does not apply (the caller goes on as usual).
+    kind: "plain", "gated" or "rope" (then ``rope`` = positions, token_item, cos, sin, table, kv, hq, hkv, d, page_size)."""
+    from .deferred import PendingProduct
+    if not (FEWROWS_FUSE_NORM and isinstance(x.pending, PendingProduct) and x.rows is None and x.dtype == torch.bfloat16):
+        return None
+    m, k = x.shape
+    if not (USE_FEWROWS and STREAM_M < m <= FEWROWS_MAX[kind] and k >= 64 and k % 8 == 0 and w.is_contiguous() and w.data_ptr() % 16 == 0):
+        return None
+    if kind == "rope":
+        positions, token_item, cos, sin, table, kv, hq, hkv, d, page_size = rope
+        if not (kv.is_contiguous() and (cos is None or (cos.is_contiguous() and sin.is_contiguous()))):
+            return None
+    raw = x.raw()
+    if raw is None:
+        return None
+    gained, shares = raw
+    parts = shares.shape[0]
+    if kind == "plain":
+        y = torch.empty((m, w.shape[0]), dtype=torch.bfloat16, device=w.device)
+        check(lib().psb_gemm_fewrows_scaled(gained.data_ptr(), w.data_ptr(), y.data_ptr(), m, w.shape[0], k, shares.data_ptr(), parts,
+                                            x.eps, stream_handle()), "gemm_fewrows")
+        return y
+    if kind == "gated":
+        inter = w.shape[0] // 2
+        act = torch.empty((m, inter), dtype=torch.bfloat16, device=w.device)
+        check(lib().psb_gemm_fewrows_gated_scaled(gained.data_ptr(), w.data_ptr(), act.data_ptr(), m, inter, k, activation,
+                                                  shares.data_ptr(), parts, x.eps, stream_handle()), "gemm_fewrows_gated")
+        return act
+    q = torch.empty((m, hq, d), dtype=torch.bfloat16, device=w.device)
+    check(lib().psb_gemm_fewrows_rope_scaled(
+        gained.data_ptr(), w.data_ptr(), m, k, positions.data_ptr(), token_item.data_ptr(), table.data_ptr(), table.shape[1],
+        None if cos is None else cos.data_ptr(), None if sin is None else sin.data_ptr(), kv.data_ptr(), q.data_ptr(),
+        hq, hkv, d, page_size, kv.shape[0], 0 if cos is None else cos.shape[0], shares.data_ptr(), parts, x.eps,
+        stream_handle()), "gemm_fewrows_rope")
+    return q
 
 
 def _tcgen05_ok(x: torch.Tensor, w: torch.Tensor, kind: int = 0, head_dim: int = 0) -> bool:

@@ -98,7 +98,7 @@ class Attention(Mixer):
                                 write_kv=self.own_kv, paired=self.paired, rotary_dim=self.rotary_dim,
                                 interleaved=self.interleaved)
         o = ops.attention(q, cache.kv, table, ctx.positions, ctx.token_item, window=self.window, scale=self.scale, ctx=ctx)
-        return ops.linear(o, self.w_o)
+        return ops.last_product(o, self.w_o, ctx)  # may be handed on unrun: the next norm's kernels take it from there
 
 
 register_mixer("attention", Attention, replace=True)

@@ -38,7 +38,7 @@ class GatedMLP(FeedForward):
         self.w_down = tensors["down_proj"].contiguous()
 
     def forward(self, x, ctx: StepContext):
-        return ops.linear(ops.gated_linear(x, self.w_gate_up, self.activation), self.w_down)
+        return ops.last_product(ops.gated_linear(x, self.w_gate_up, self.activation), self.w_down, ctx)
 
 
 register_ffn("gated_mlp", GatedMLP, replace=True)

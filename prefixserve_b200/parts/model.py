@@ -25,6 +25,7 @@ class DecoderModel:
         self.final_norm = make("norm", spec.final_norm)
         self.head = make("head", spec.head)
         self.compute_dtype: torch.dtype | None = None
+        self._lazy_products: bool | None = None  # worked out at the first step (see forward)
 
     # ---- tensors ---------------------------------------------------------
     def named_parts(self):
@@ -84,6 +85,15 @@ class DecoderModel:
     # ---- one step ----------------------------------------------------------
     def forward(self, ctx: StepContext, cache_view: Callable[[int, bool], CacheView], rows: torch.Tensor) -> torch.Tensor:
         """Runs the step's tokens; returns float32 logits [len(rows), vocab] for the wanted flat rows."""
+        if self._lazy_products is None:
+            # A sublayer may hand its last product on unrun only if whatever meets it next knows what that is: every
+            # block arranged the built-in pre-norm way and every norm saying that it takes one.
+            from .block import pre_norm
+            norms = [self.final_norm] + [n for b in self.blocks for n in (b.mixer_norm, b.ffn_norm) if n is not None]
+            self._lazy_products = (all(b.run is pre_norm for b in self.blocks)
+                                   and all(getattr(n, "takes_pending_products", False) for n in norms))
+        if self._lazy_products:
+            ctx.extras["lazy_products"] = True
         h = self.embedding.forward(ctx.token_ids)
         pending = None
         for at, call in enumerate(self.spec.schedule):

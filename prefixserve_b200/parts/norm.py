@@ -17,6 +17,7 @@ from .registry import register_norm
 
 class RMSNorm(Norm):
     graph_safe = True  # device work depends only on tensor shapes and device-side inputs
+    takes_pending_products = True  # ``delta`` may be an ops.PendingProduct (a product that has not run yet)
 
     def __init__(self, params):
         super().__init__(params)

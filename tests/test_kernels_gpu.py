@@ -1004,6 +1004,52 @@ def test_fewrows_projection_rotation_and_append_in_one_kernel(m, hq, hkv, d, pag
             assert torch.allclose(got_v.double(), want_v[tok].double(), rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("splits", [0, 1, 4])
+@pytest.mark.parametrize("m,hidden,inter", [(17, 256, 384), (32, 2048, 8192), (24, 200, 328), (9, 2048, 1000)])
+def test_fewrows_products_around_a_norm(m, hidden, inter, splits, fewrows_splits, monkeypatch):
+    """The product in front of a norm adds itself to the stream and leaves the gained rows and the shares of the sums
+    of squares; the products behind it (plain, gated) scale their sums.  Against float64, and against the same chain
+    through the norm's own kernel."""
+    from prefixserve_b200 import ops
+    from prefixserve_b200.ops import library, tensorcore
+    monkeypatch.setattr(tensorcore, "FEWROWS_MAX", {"plain": 64, "gated": 64, "rope": 64})
+    fewrows_splits(splits)
+    eps = 1e-5
+    g = torch.Generator().manual_seed(m + hidden)
+    a = torch.randn(m, inter, generator=g).to(torch.bfloat16).to(DEV)
+    w_front = (torch.randn(hidden, inter, generator=g) / math.sqrt(inter)).to(torch.bfloat16).to(DEV)
+    h = (torch.randn(m, hidden, generator=g) * 2).to(DEV)
+    gain = (1.0 + 0.2 * torch.randn(hidden, generator=g)).to(DEV)
+    w_plain = (torch.randn(333, hidden, generator=g) / math.sqrt(hidden)).to(torch.bfloat16).to(DEV)
+    w_gated = (torch.randn(2 * 200, hidden, generator=g) / math.sqrt(hidden)).to(torch.bfloat16).to(DEV)
+    # float64: the product rounded to bfloat16, the residual sum, the norm, the products behind it
+    delta = (a.double() @ w_front.double().t()).to(torch.bfloat16).double()
+    v = h.double() + delta
+    normed = v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps) * gain.double()
+    want_plain = normed @ w_plain.double().t()
+    y = (normed @ w_gated.double().t()).to(torch.bfloat16).double()
+    want_gated = torch.nn.functional.silu(y[:, :200]) * y[:, 200:]
+    for kind, w_behind, want in (("plain", w_plain, want_plain), ("gated", w_gated, want_gated)):
+        stream = h.clone()
+        x = ops.NormedRows(stream, ops.PendingProduct(a, w_front), gain, eps, torch.bfloat16)
+        before = library.launch_counts.copy()
+        got = ops.linear(x, w_behind) if kind == "plain" else ops.gated_linear(x, w_behind)
+        ran = library.launch_counts - before
+        assert ran["gemm_fewrows_add_norm"] == 1 and ran["add_rmsnorm"] == 0, ran
+        assert library.tcgen05_status() == 0
+        # the stream after the sum (the product is rounded to bfloat16 on its way in: a unit in its last place may differ from float64's)
+        assert torch.allclose(x.residual().double(), v, rtol=0, atol=2.0 ** -8 * float(delta.abs().max())), kind
+        tol = 3e-2 * float(want.abs().max())
+        assert float((got.double() - want).abs().max()) <= tol, (kind, float((got.double() - want).abs().max()), tol)
+        # the same through the norm's own kernel: no further from float64 than a factor
+        stream2 = h.clone()
+        y2 = ops.NormedRows(stream2, ops.linear(a, w_front), gain, eps, torch.bfloat16)
+        unfused = ops.linear(y2.tensor(), w_behind) if kind == "plain" else ops.gated_linear(y2.tensor(), w_behind)
+        err, err2 = float((got.double() - want).abs().max()), float((unfused.double() - want).abs().max())
+        assert err <= 2.0 * err2 + 1e-3 * float(want.abs().max()), (kind, err, err2)
+        assert torch.equal(stream, stream2)   # the same float32 stream bit for bit
+
+
 def test_a_bounded_wait_that_runs_out_gives_up_and_says_so():
     """The tensor-core kernels wait on mbarriers through one bounded primitive.  Its give-up path runs here on a
     barrier that nobody arrives at, with a limit of a few hundred polls, in a kernel of one warp that has nothing in
