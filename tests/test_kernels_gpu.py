@@ -400,6 +400,81 @@ def test_attention_tensor_cores_find_one_far_key(decode_kernel):
         assert torch.allclose(out.float().cpu(), want[old:], atol=3e-2, rtol=3e-2), (old, new)
 
 
+def _rows_of_causal_attention(q_rows, first, k, v):
+    """Plain float32 attention of the rows first.. of one sequence: q_rows [n, hq, D], k/v [T, hkv, D] -> [n, hq * D]."""
+    n, hq, d = q_rows.shape
+    group = hq // k.shape[1]
+    keys, vals = k.repeat_interleave(group, dim=1), v.repeat_interleave(group, dim=1)
+    scores = torch.einsum("nhd,thd->hnt", q_rows, keys) / math.sqrt(d)
+    hidden = torch.arange(k.shape[0])[None, :] > (first + torch.arange(n))[:, None]
+    probs = torch.softmax(scores.masked_fill(hidden[None], float("-inf")), dim=-1)
+    return torch.einsum("hnt,thd->nhd", probs, vals).reshape(n, hq * d)
+
+
+@pytest.mark.parametrize("hq,hkv,d", [(16, 8, 128), (32, 8, 64)])
+def test_pages_beyond_four_gigabytes_of_the_pool(hq, hkv, d, decode_kernel):
+    """A pool of one layer with more than 2^31 elements (what 64 requests of 16,384 tokens take at Llama-8B sizes):
+    the requests' pages lie at its far end, beyond what a 32-bit element or byte offset reaches.  A decoding request
+    over 9,000 keys, a prompt portion over a prefix, and a short request on the first pages; the new tokens' keys and
+    values go in through the append kernel, and one early key of the long request is made to dominate its query."""
+    from prefixserve_b200 import ops
+    page = 16
+    per_page = 2 * hkv * page * d
+    num_pages = (1 << 31) // per_page + 3000
+    assert num_pages * per_page > (1 << 31)
+    g = torch.Generator().manual_seed(5)
+    lens_old, lens_new = [8999, 700, 40], [1, 200, 1]
+    totals = [o + n for o, n in zip(lens_old, lens_new)]
+    pages_per = [-(-t // page) for t in totals]
+    far = num_pages - 1 - torch.randperm(2900, generator=g)        # the last pages of the pool, in random order
+    table = torch.full((3, max(pages_per)), -1, dtype=torch.int32)
+    table[0, :pages_per[0]] = far[:pages_per[0]].to(torch.int32)
+    table[1, :pages_per[1]] = far[pages_per[0]: pages_per[0] + pages_per[1]].to(torch.int32)
+    table[2, :pages_per[2]] = torch.tensor([2, 0, 1], dtype=torch.int32)[:pages_per[2]]
+    kv = torch.empty(num_pages, 2, hkv, page, d, dtype=torch.bfloat16, device=DEV)
+    kv[:64].fill_(float("nan"))
+    kv[-3000:].fill_(float("nan"))
+    seqs = []
+    for i, (o, t) in enumerate(zip(lens_old, totals)):
+        q = torch.randn(t, hq, d, generator=g) * 0.3
+        k = torch.randn(t, hkv, d, generator=g) * 0.3
+        v = torch.randn(t, hkv, d, generator=g)
+        if i == 0:
+            q[t - 1, :, 7] = 30.0
+            k[1234, :, 7] += 30.0
+        seqs.append(dict(q=q.to(torch.bfloat16), k=k.to(torch.bfloat16), v=v.to(torch.bfloat16)))
+        pos = torch.arange(o)
+        pg = table[i, pos // page].long().to(DEV)
+        kv[pg, 0, :, (pos % page).to(DEV)] = seqs[i]["k"][:o].to(DEV)
+        kv[pg, 1, :, (pos % page).to(DEV)] = seqs[i]["v"][:o].to(DEV)
+    # the new tokens arrive through the append kernel (angles of zero: the keys are stored as they are)
+    cos = torch.ones(max(totals), d // 2, device=DEV)
+    sin = torch.zeros(max(totals), d // 2, device=DEV)
+    qkv = torch.cat([torch.cat([s[n][o:].reshape(t - o, -1) for n in ("q", "k", "v")], dim=1)
+                     for s, o, t in zip(seqs, lens_old, totals)]).to(DEV)
+    positions = torch.cat([torch.arange(o, t) for o, t in zip(lens_old, totals)]).to(torch.int32).to(DEV)
+    token_item = torch.cat([torch.full((n,), i) for i, n in enumerate(lens_new)]).to(torch.int32).to(DEV)
+    table_dev = table.to(DEV)
+    q_rot = ops.rope_append(qkv, positions, token_item, cos, sin, table_dev, kv, num_heads=hq, num_kv_heads=hkv,
+                            head_dim=d, page_size=page, write_kv=True)
+    last = int(table[0, (totals[0] - 1) // page])
+    assert last * per_page > (1 << 31) - 3000 * per_page
+    assert torch.equal(kv[last, 1, :, (totals[0] - 1) % page].cpu(), seqs[0]["v"][-1]), "the append kernel missed its page"
+    out = ops.attention(q_rot, kv, table_dev, positions, token_item, ctx=_Batch(lens_old, lens_new))
+    torch.cuda.synchronize()
+    at = 0
+    for i, (s, o, t) in enumerate(zip(seqs, lens_old, totals)):
+        want = _rows_of_causal_attention(s["q"][o:].float(), o, s["k"].float(), s["v"].float())
+        got = out[at: at + t - o].float().cpu()
+        assert torch.isfinite(got).all(), f"item {i} read a page that is not its own"
+        assert torch.allclose(got, want, atol=3e-2, rtol=3e-2), (i, float((got - want).abs().max()))
+        at += t - o
+    needle = seqs[0]["v"][1234].float().repeat_interleave(hq // hkv, dim=0).reshape(-1)
+    assert torch.allclose(out[0].float().cpu(), needle, atol=3e-2, rtol=3e-2), "the dominant key of the long request was missed"
+    del kv
+    torch.cuda.empty_cache()
+
+
 @pytest.mark.parametrize("hq,hkv,d", [(24, 8, 128), (32, 8, 64)])
 def test_decode_attention_with_every_sm_busy(hq, hkv, d, decode_kernel):
     """Dozens of requests with thousands of keys each, one key range per request: every SM holds several CTAs whose
