@@ -306,6 +306,37 @@ def run_own(args) -> dict:
                 cache.close(s)
             return t0.elapsed_time(t1) / steps, launched, ctx_sum / (batch * steps)
 
+        if args.only == "prefill" and args.prompt:
+            # one prompt of --prompt tokens in portions of --portion, as the scheduler cuts it: device-timed, median of five
+            total, portion = args.prompt, args.portion
+            toks = rng.randint(0, vocab, size=total).astype(np.int32)
+
+            def whole_prompt() -> float:
+                slot = cache.open()
+                cache.reserve(slot, total)
+                t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                t0.record()
+                for at in range(0, total, portion):
+                    n = min(portion, total - at)
+                    logits = runner.step([StepItem(slot, at, toks[at: at + n], (n - 1,) if at + n == total else ())])
+                    cache.advance(slot, at + n)
+                sample(logits)
+                t1.record()
+                torch.cuda.synchronize()
+                cache.close(slot)
+                return t0.elapsed_time(t1)
+
+            with ClockSampler() as clocks:
+                for _ in range(2):
+                    whole_prompt()
+                runs = sorted(whole_prompt() for _ in range(5))
+            ms = runs[len(runs) // 2]
+            flops = sum(prefill_flops(min(portion, total - at), layers, prefix=at) for at in range(0, total, portion))
+            return {"only": "prefill", "prompt": total, "portion": portion, "layers": layers, "ms": round(ms, 3),
+                    "value": round(total / (ms * 1e-3), 1), "tflops": round(flops / (ms * 1e-3) / 1e12, 1),
+                    "frac": round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4), "clocks": clocks.summary()}
+
         if args.only == "prefill":
             torch.cuda.synchronize()
             portion = args.portion
@@ -758,19 +789,26 @@ def main() -> int:
     p.add_argument("--model", choices=sorted(SIZES), default=None,
                    help="layer sizes for --workload shared-prefix (8b) / mixed (3b), and for --only decode (the headline stays 1b)")
     p.add_argument("--requests", type=int, default=64, help="requests of --workload shared-prefix")
+    p.add_argument("--prompt", type=int, default=None,
+                   help="with --only prefill: time one prompt of this many tokens, cut into portions of --portion "
+                        "(--context must be at least as long)")
     p.add_argument("--context", type=int, default=None,
                    help="context of --workload mixed (8192 unless given) and of --only decode (the headline stays 4096)")
     args = p.parse_args()
     args.warmup = max(args.warmup, 3)
-    if args.workload == "decode" and args.only == "decode" and args.impl == "own" and (args.model or args.context):
-        # further sizes and context lengths for the device-timed decode steps; the headline line is not touched
+    if args.prompt and (args.only != "prefill" or args.impl != "own" or (args.context or CONTEXT) < args.prompt):
+        print(json.dumps({"unsupported": "--prompt goes with --only prefill of this engine and a --context at least as long"}))
+        return 2
+    if args.workload == "decode" and args.impl == "own" and (args.model or args.context) and \
+            (args.only == "decode" or (args.only == "prefill" and args.prompt)):
+        # further sizes and context lengths for the device-timed decode steps and prompts; the headline line is not touched
         if args.model:
             MODEL, full = _model_config(args.model)
             args.layers = full if args.layers == FULL_LAYERS and "--layers" not in sys.argv else args.layers
             FULL_LAYERS = full
         CONTEXT = args.context or CONTEXT
     elif args.workload == "decode" and (args.model or args.context):
-        print(json.dumps({"unsupported": "--model and --context go with --only decode, --workload shared-prefix or --workload mixed"}))
+        print(json.dumps({"unsupported": "--model and --context go with --only decode, --only prefill --prompt N, --workload shared-prefix or --workload mixed"}))
         return 2
     args.context = args.context or 8192
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
