@@ -34,13 +34,18 @@ constexpr int TILES = 2;
 constexpr int ROWS_PER_CTA = TILE_M * TILES;
 constexpr int SOFTMAX_WARPS = 4;                     // per tile: one thread per row, a warp per quarter of tensor-memory lanes
 constexpr int THREADS = 32 * (2 + SOFTMAX_WARPS * TILES);  // producer, MMA, softmax
-constexpr int STAGES = 4;  // blocks of keys and values in shared memory at a time: S runs up to three blocks ahead of P V
+constexpr int MAX_STAGES = 5, MAX_S_BUFS = 4;
 constexpr int TMEM_COLS = 512;
 constexpr float LOG2E_F = 1.4426950408889634f;
 
 template <int D>
 struct Shape {
   static constexpr int KB = D == 64 ? 128 : 64;           // keys per block
+  // S buffers, used in turn by the tiles' blocks: as many as tensor memory has room for beside the two output tiles.
+  // With four, each of two tiles has two of its own and its next scores never wait for the other tile's softmax.
+  static constexpr int S_BUFS = (TMEM_COLS - TILES * D) / KB >= 4 ? 4 : 3;
+  // blocks of keys and values in shared memory at a time: S of one tile alone runs S_BUFS blocks ahead of its P V
+  static constexpr int STAGES = S_BUFS + 1;
   static constexpr int DS = D / 64;                       // 64-element sub-tiles along the head dim
   static constexpr int Q_TILE_BYTES = TILE_M * D * 2;
   static constexpr int Q_SUB_BYTES = TILE_M * 128;        // one [128 x 64] sub-tile
@@ -50,17 +55,16 @@ struct Shape {
   static constexpr int K_OFF = Q_OFF + TILES * Q_TILE_BYTES;
   static constexpr int V_OFF = K_OFF + STAGES * KV_STAGE_BYTES;
   static constexpr int BAR_OFF = V_OFF + STAGES * KV_STAGE_BYTES;
-  static constexpr int S_BUFS = 3;                        // S buffers, used in turn by the tiles' blocks
   static constexpr int S_COL = 0;                         // S buffer j: columns [j*KB, +KB)
   static constexpr int O_COL = S_BUFS * KB;               // O of tile t: columns [O_COL + t*D, +D)
-  static_assert(O_COL + TILES * D <= TMEM_COLS, "tensor memory");
+  static_assert(O_COL + TILES * D <= TMEM_COLS && S_BUFS <= MAX_S_BUFS && STAGES <= MAX_STAGES, "tensor memory");
   static_assert(Q_TILE_BYTES % 1024 == 0 && KV_STAGE_BYTES % 1024 == 0, "swizzle atoms");
 };
 
 struct Barriers {
   uint64_t q_full;
-  uint64_t k_full[STAGES], v_full[STAGES], kv_empty[STAGES];
-  uint64_t s_full[3], p_ready[TILES], o_full[TILES];
+  uint64_t kv_full[MAX_STAGES], kv_empty[MAX_STAGES];  // a block's keys and values arrive on one barrier
+  uint64_t s_full[MAX_S_BUFS], p_ready[TILES], o_full[TILES];
   uint32_t tmem_base;
   uint32_t abort;
 };
@@ -109,7 +113,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                                  int hkv, int page_shift, int window, float scale, int skip_single, int rows_per_cta,
                                  int kv_splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
   using Sh = Shape<D>;
-  constexpr int KB = Sh::KB;
+  constexpr int KB = Sh::KB, NB = Sh::S_BUFS, STAGES = Sh::STAGES;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   Barriers* bars = reinterpret_cast<Barriers*>(smem + Sh::BAR_OFF);
@@ -135,11 +139,10 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, 1);
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&bars->k_full[s], 1);
-      mbar_init(&bars->v_full[s], 1);
+      mbar_init(&bars->kv_full[s], 1);
       mbar_init(&bars->kv_empty[s], 1);
     }
-    for (int j = 0; j < 3; ++j) mbar_init(&bars->s_full[j], 1);
+    for (int j = 0; j < NB; ++j) mbar_init(&bars->s_full[j], 1);
     for (int t = 0; t < TILES; ++t) {
       mbar_init(&bars->p_ready[t], SOFTMAX_WARPS);  // one arrival per softmax warp of the tile (arrivals on one barrier serialise)
       mbar_init(&bars->o_full[t], 1);
@@ -176,7 +179,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const int nblk = max(0, bend[ntiles - 1] - b0 + 1);
   const int kvh = head / (hq / hkv);
   // The tiles' blocks in the order their S is computed: (0,0) (1,0) (0,1) (1,1) ... while tile 0 still has blocks (n0 of
-  // them), then tile 1's remaining ones.  The e-th of them uses S buffer e % 3, so S of a block is computed while the
+  // them), then tile 1's remaining ones.  The e-th of them uses S buffer e % NB, so S of a block is computed while the
   // softmax of the two blocks before it is still running.
   const int n0 = max(0, bend[0] - b0 + 1);   // a range may hold nothing that tile 0's (earlier) rows can see
   const int total = ntiles == 2 ? n0 + nblk : n0;
@@ -214,8 +217,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       if (lane == 0) {
-        mbar_expect_tx(&bars->k_full[stage], (uint32_t)Sh::KV_STAGE_BYTES);
-        mbar_expect_tx(&bars->v_full[stage], (uint32_t)Sh::KV_STAGE_BYTES);
+        mbar_expect_tx(&bars->kv_full[stage], 2u * (uint32_t)Sh::KV_STAGE_BYTES);
       }
       __syncwarp();
       if (lane < pages_per_block) {
@@ -224,7 +226,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
           unsigned char* dst = smem + (which ? Sh::V_OFF : Sh::K_OFF) + stage * Sh::KV_STAGE_BYTES + lane * page * 128;
 #pragma unroll
           for (int j = 0; j < Sh::DS; ++j)
-            tma_load_2d(dst + j * Sh::KV_SUB_BYTES, &map_kv, 64 * j, which ? row_v : row_k, which ? &bars->v_full[stage] : &bars->k_full[stage]);
+            tma_load_2d(dst + j * Sh::KV_SUB_BYTES, &map_kv, 64 * j, which ? row_v : row_k, &bars->kv_full[stage]);
         }
       }
       if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -264,31 +266,32 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     };
     bool ok = mbar_wait(&bars->q_full, 0, abort, 2);
     ok = __all_sync(0xffffffffu, ok);
-    int k_seen = 0, v_seen = 0;  // blocks (from b0) whose keys / values have been waited for
+    // blocks (from b0) that have been waited for (keys and values arrive together, and S of a block needs its keys
+    // before P V needs its values: by then nothing is left to wait for), and blocks whose values have been looked at
+    int k_seen = 0, v_seen = 0;
     auto tile_of = [&](int e) { return ntiles == 1 ? 0 : (e < 2 * n0 ? (e & 1) : 1); };
     auto block_of = [&](int e) { return ntiles == 1 ? e : (e < 2 * n0 ? (e >> 1) : e - n0); };
     auto keys_ready = [&](int i) {  // waits (once) for the keys of every block up to i
       while (k_seen <= i) {
-        bool got = mbar_wait(&bars->k_full[k_seen % STAGES], (k_seen / STAGES) & 1, abort, 2);
+        bool got = mbar_wait(&bars->kv_full[k_seen % STAGES], (k_seen / STAGES) & 1, abort, 2);
         got = __all_sync(0xffffffffu, got);
         if (!got) return false;
         ++k_seen;
       }
       return true;
     };
-    for (int e = 0; ok && e < 3 && e < total; ++e) {
+    for (int e = 0; ok && e < NB && e < total; ++e) {
       ok = keys_ready(block_of(e));
       if (ok && elect_one()) {
-        issue_s(tile_of(e), block_of(e) % STAGES, e % 3);
-        mma_commit(&bars->s_full[e % 3]);
+        issue_s(tile_of(e), block_of(e) % STAGES, e % NB);
+        mma_commit(&bars->s_full[e % NB]);
       }
       __syncwarp();
     }
     for (int e = 0; ok && e < total; ++e) {
       const int t = tile_of(e), i = block_of(e);
       while (ok && v_seen <= i) {
-        ok = mbar_wait(&bars->v_full[v_seen % STAGES], (v_seen / STAGES) & 1, abort, 2);
-        ok = __all_sync(0xffffffffu, ok);
+        ok = keys_ready(v_seen);  // no wait: S of this block has been issued
         if (!ok) break;
         const int written = kvl - (b0 + v_seen) * KB;  // rows of this block that hold the request's values
         if (written < KB) {
@@ -303,20 +306,20 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         }
         ++v_seen;
       }
-      const bool ahead = e + 3 < total;  // S of the block three steps on goes out together with this P V
-      if (ok && ahead) ok = keys_ready(block_of(e + 3));
+      const bool ahead = e + NB < total;  // S of the block NB steps on (it takes this block's buffer) goes out together with this P V
+      if (ok && ahead) ok = keys_ready(block_of(e + NB));
       if (!ok) break;
       ok = mbar_wait(&bars->p_ready[t], i & 1, abort, 2);  // P of this block is written (over its S)
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       fence_after();
       if (elect_one()) {
-        issue_pv(t, i % STAGES, e % 3, i);
+        issue_pv(t, i % STAGES, e % NB, i);
         mma_commit(&bars->o_full[t]);
         if (t == ntiles - 1) mma_commit(&bars->kv_empty[i % STAGES]);  // the last tile to use this block
         if (ahead) {
-          issue_s(tile_of(e + 3), block_of(e + 3) % STAGES, (e + 3) % 3);
-          mma_commit(&bars->s_full[(e + 3) % 3]);
+          issue_s(tile_of(e + NB), block_of(e + NB) % STAGES, e % NB);
+          mma_commit(&bars->s_full[e % NB]);
         }
       }
       __syncwarp();
@@ -354,22 +357,31 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       // thread waits for its stores and hands block i over.
       constexpr int NCH = KB / 32;
       float sv[NCH][32];
-      auto request_scores = [&](int i) {  // false: a wait gave up
-        const int e = seq_of(t, i);
-        bool got = mbar_wait(&bars->s_full[e % 3], (e / 3) & 1, abort, 3);
-        got = __all_sync(0xffffffffu, got);
-        if (!got) return false;
+      auto load_scores = [&](int e) {
         fence_after();
-        const uint32_t s_addr = lane_addr + Sh::S_COL + (e % 3) * KB;
+        const uint32_t s_addr = lane_addr + Sh::S_COL + (e % NB) * KB;
 #pragma unroll
         for (int cc = 0; cc < NCH; ++cc) tmem_ld32(s_addr + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[cc][0]));
+      };
+      auto request_scores = [&](int i) {  // false: a wait gave up
+        const int e = seq_of(t, i);
+        bool got = mbar_wait(&bars->s_full[e % NB], (e / NB) & 1, abort, 3);
+        got = __all_sync(0xffffffffu, got);
+        if (!got) return false;
+        load_scores(e);
+        return true;
+      };
+      auto request_scores_if_there = [&](int i) {  // asks for them only if they are computed already (the whole warp agrees)
+        const int e = seq_of(t, i);
+        if (!__all_sync(0xffffffffu, mbar_test_wait(&bars->s_full[e % NB], (e / NB) & 1))) return false;
+        load_scores(e);
         return true;
       };
       if (my_blocks > 0) ok = request_scores(0);
       for (int i = 0; ok && i < my_blocks; ++i) {
         const int key0 = (b0 + i) * KB;
         const int e = seq_of(t, i);
-        const uint32_t s_addr = lane_addr + Sh::S_COL + (e % 3) * KB;
+        const uint32_t s_addr = lane_addr + Sh::S_COL + (e % NB) * KB;
         const bool need_mask = partial || key0 + KB - 1 > p_first[t] || (window > 0 && key0 < p_last[t] - window + 1);
         float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
         tmem_ld_wait();
@@ -392,18 +404,24 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         const float m_new = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
         const bool grow = (m_new - m_run) * c > 8.f;  // false while the row has seen nothing (-inf - -inf)
         // Each phase of o_full (P V of this tile's block i-1 has finished) is waited for exactly once, during block i:
-        // a parity wait can only tell the phase in progress from the one before it.  Early if O has to be rescaled,
-        // otherwise at the end of the block, when it has long completed.
+        // a parity wait can only tell the phase in progress from the one before it.  If O has to be rescaled, before
+        // that.  Otherwise, with 128 keys a block, ahead of the exponentials too: P V of the block before has completed
+        // by then as a rule, and nothing stands between this block's last store and its hand-over (8,192 tokens: 440 ->
+        // 432 us); with 64 keys a block it often has not, and the wait comes at the end of the block (727 against 734).
+        constexpr bool WAIT_EARLY = KB == 128;
         bool waited = i == 0;
-        if (__any_sync(0xffffffffu, grow)) {
+        const bool any_grow = __any_sync(0xffffffffu, grow);
+        if (i > 0 && (WAIT_EARLY || any_grow)) {
+          ok = mbar_wait(&bars->o_full[t], (i - 1) & 1, abort, 3);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          waited = true;
+        }
+        if (any_grow) {
           // tensor-memory loads and stores are warp-wide: every lane takes part, with a factor of 1 where nothing grew
           const float alpha = grow ? ex2((m_run - m_new) * c) : 1.f;  // 0 from -inf
           if (grow) { m_run = m_new; l_run *= alpha; }
           if (i > 0) {
-            ok = mbar_wait(&bars->o_full[t], (i - 1) & 1, abort, 3);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            waited = true;
             fence_after();
 #pragma unroll 1
             for (int cc = 0; cc < D / 32; ++cc) {
@@ -444,10 +462,10 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         };
 #pragma unroll
         for (int cc = 0; cc < NCH; ++cc) emit(cc, sv[cc]);
-        if (i + 1 < my_blocks) {  // the registers are free again: the next block's scores may start on their way
-          ok = request_scores(i + 1);
-          if (!ok) break;
-        }
+        // The registers are free again: the next block's scores may start on their way, if they exist.  If they do
+        // not, this block is handed over first: the other tile's next scores, and through them this tile's, are
+        // computed behind this block's P V, and a warp that waited here would hold all of that up.
+        const bool asked = i + 1 < my_blocks && request_scores_if_there(i + 1);
         tmem_st_wait();
         if constexpr (PAIRS) halves_of(sum_pair, sum0, sum1);
         l_run += sum0 + sum1;
@@ -459,6 +477,10 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         fence_before();       // P written, O rescaled
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->p_ready[t]);
+        if (i + 1 < my_blocks && !asked) {
+          ok = request_scores(i + 1);
+          if (!ok) break;
+        }
       }
       // the quotient
       if (ok && my_blocks > 0) {

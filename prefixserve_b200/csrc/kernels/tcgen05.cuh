@@ -53,6 +53,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return done != 0;
 }
+// try_wait may suspend the thread for a while (a limit of the hardware's choosing) before it answers no; test_wait
+// answers at once.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
 // Bounded: false when the barrier did not complete within SPIN_LIMIT polls or another warp has raised the abort flag.
 // The abort flag (shared memory) and the device's status word are looked at every 64th poll only: a load per poll from
 // every waiting warp crowds the path that barrier arrivals and the tensor-core instructions also take.
