@@ -4,10 +4,14 @@
 // step has too few such groups to give every SM one, up to 128 tokens as a single tile), and walks
 // the keys they may see in blocks of KB keys (128 for a head size of 64, 64 for 128).  320 threads:
 //   warp 0      producer: TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle) of the two Q tiles once, and per block of
-//               the pages that hold its keys and values, one box per page, into a ring of four stages;
+//               the pages that hold its keys and values, one box per page, into a ring of four or five stages (one
+//               mbarrier per stage takes both, so the MMA warp waits once per block);
 //   warp 1      MMA: one lane issues tcgen05.mma (cta_group::1, kind::f16, M=128):  S = Q K^T  (A and B K-major, N=KB)
 //               into tensor memory, and  O += P V  (A = P from tensor memory, B = V MN-major exactly as the
-//               cache stores it: keys x head dim, N = head dim);
+//               cache stores it: keys x head dim, N = head dim).  S goes into three (128 keys a block) or four (64)
+//               buffers in turn, so it is computed while the softmax of the blocks before it still runs.  This warp
+//               sets the kernel's pace: what it waits on and issues per block and tile takes about as long as a
+//               softmax warp's work on the block;
 //   warps 2..5  softmax of tile 0, warps 6..9 of tile 1: one thread per row.  tcgen05.ld of the row of S, masks,
 //               maximum and sum in float32 (three-input maxima and arithmetic on register pairs: the loop is bound by
 //               the instructions it issues), P as bfloat16 into tensor memory over the scores it came from.  O
@@ -352,7 +356,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       bool ok = true;
       const int my_blocks = max(0, bend[t] - b0 + 1);
       // The row's scores of a block, 32 keys a chunk, stay in registers from the maximum to the exponentials.  They are
-      // asked for as early as they can be: a block's scores are computed up to three blocks ahead, so the loads of
+      // asked for as early as they can be: a block's scores are computed blocks ahead, so as a rule the loads of
       // block i+1 go out as soon as the exponentials of block i have let go of the registers, and arrive while this
       // thread waits for its stores and hands block i over.
       constexpr int NCH = KB / 32;
