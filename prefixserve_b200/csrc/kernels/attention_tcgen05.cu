@@ -2,11 +2,11 @@
 //
 // One CTA owns up to 256 consecutive new tokens of one request for one query head, as two tiles of 128 rows (or, when the
 // step has too few such groups to give every SM one, up to 128 tokens as a single tile), and walks
-// the keys they may see in blocks of KB keys (128 for a head size of 64, 64 for 128).  320 threads:
+// the keys they may see in blocks of KB keys (128 for a head size of 64, 64 for 128).  352 threads:
 //   warp 0      producer: TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle) of the two Q tiles once, and per block of
 //               the pages that hold its keys and values, one box per page, into a ring of four or five stages (one
 //               mbarrier per stage takes both, so the MMA warp waits once per block);
-//   warp 1      MMA: one lane issues tcgen05.mma (cta_group::1, kind::f16, M=128):  S = Q K^T  (A and B K-major, N=KB)
+//   warp 1      (and, with 64 keys a block, warp 10 for S) MMA: one lane issues tcgen05.mma (cta_group::1, kind::f16, M=128):  S = Q K^T  (A and B K-major, N=KB)
 //               into tensor memory, and  O += P V  (A = P from tensor memory, B = V MN-major exactly as the
 //               cache stores it: keys x head dim, N = head dim).  S goes into three (128 keys a block) or four (64)
 //               buffers in turn, so it is computed while the softmax of the blocks before it still runs.  This warp
@@ -37,7 +37,8 @@ constexpr int TILE_M = 128;
 constexpr int TILES = 2;
 constexpr int ROWS_PER_CTA = TILE_M * TILES;
 constexpr int SOFTMAX_WARPS = 4;                     // per tile: one thread per row, a warp per quarter of tensor-memory lanes
-constexpr int THREADS = 32 * (2 + SOFTMAX_WARPS * TILES);  // producer, MMA, softmax
+constexpr int S_WARP = 2 + SOFTMAX_WARPS * TILES;         // the warp that issues S = Q K^T (warp 1 issues O += P V)
+constexpr int THREADS = 32 * (3 + SOFTMAX_WARPS * TILES);  // producer, two MMA warps, softmax
 constexpr int MAX_STAGES = 5, MAX_S_BUFS = 4;
 constexpr int TMEM_COLS = 512;
 constexpr float LOG2E_F = 1.4426950408889634f;
@@ -50,6 +51,7 @@ struct Shape {
   static constexpr int S_BUFS = (TMEM_COLS - TILES * D) / KB >= 4 ? 4 : 3;
   // blocks of keys and values in shared memory at a time: S of one tile alone runs S_BUFS blocks ahead of its P V
   static constexpr int STAGES = S_BUFS + 1;
+  static constexpr bool TWO_ISSUERS = KB == 64;           // S and P V issued by two warps (see the MMA warps)
   static constexpr int DS = D / 64;                       // 64-element sub-tiles along the head dim
   static constexpr int Q_TILE_BYTES = TILE_M * D * 2;
   static constexpr int Q_SUB_BYTES = TILE_M * 128;        // one [128 x 64] sub-tile
@@ -68,7 +70,7 @@ struct Shape {
 struct Barriers {
   uint64_t q_full;
   uint64_t kv_full[MAX_STAGES], kv_empty[MAX_STAGES];  // a block's keys and values arrive on one barrier
-  uint64_t s_full[MAX_S_BUFS], p_ready[TILES], o_full[TILES];
+  uint64_t s_full[MAX_S_BUFS], p_used[MAX_S_BUFS], p_ready[TILES], o_full[TILES];
   uint32_t tmem_base;
   uint32_t abort;
 };
@@ -146,7 +148,10 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       mbar_init(&bars->kv_full[s], 1);
       mbar_init(&bars->kv_empty[s], 1);
     }
-    for (int j = 0; j < NB; ++j) mbar_init(&bars->s_full[j], 1);
+    for (int j = 0; j < NB; ++j) {
+      mbar_init(&bars->s_full[j], 1);
+      mbar_init(&bars->p_used[j], 1);
+    }
     for (int t = 0; t < TILES; ++t) {
       mbar_init(&bars->p_ready[t], SOFTMAX_WARPS);  // one arrival per softmax warp of the tile (arrivals on one barrier serialise)
       mbar_init(&bars->o_full[t], 1);
@@ -235,12 +240,19 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       }
       if (++stage == STAGES) { stage = 0; phase ^= 1; }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp == S_WARP) {
     // --------------------------------------------------------------------------------------------------- MMA
-    // All lanes follow the barriers; an elected lane issues each instruction (tcgen05.cuh says why).  All of them work on
-    // the block that holds the request's last
-    // key: value rows behind it were never written by this request, and 0 x (whatever an earlier owner of the page
-    // left there) must be 0, so those rows are cleared in shared memory before P V runs.
+    // With 64 keys a block (heads of 128) two warps issue the tensor-core instructions, S = Q K^T from one and
+    // O += P V from the other: what one warp waits on and issues for both, per block and tile, took longer than a
+    // softmax warp's work on the block and set the kernel's pace (8,192 tokens: 724 -> 568 us).  With 128 keys a block
+    // the softmax takes twice as long per block and one warp keeps up; two were 5 % slower there (431 -> 452 us).
+    // S of event e + NB takes the buffer that holds P of event e: one warp issues it behind that P V; with two, the S
+    // warp waits until the P V has completed (p_used).  A block's keys are no longer needed once P V of its last tile
+    // has been issued, because that follows the block's S of every tile through s_full, the softmax and p_ready.
+    // All lanes follow the barriers; an elected lane issues each instruction (tcgen05.cuh says why).  All of them work
+    // on the block that holds the request's last key: value rows behind it were never written by this request, and
+    // 0 x (whatever an earlier owner of the page left there) must be 0, so those rows are cleared in shared memory
+    // before P V runs.
     constexpr uint32_t IDESC_S = instr_desc(TILE_M, KB, false);
     constexpr uint32_t IDESC_O = instr_desc(TILE_M, D, true);
     // descriptors: low words (address field in 16-byte units, leading byte offset) of the operands' first tiles; the high
@@ -268,35 +280,23 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       for (int kk = 0; kk < KB / 16; ++kk)
         mma_f16_tmem_a(dst, src + (kk >> 1) * 32 + (kk & 1) * 8, bv + ((kk * 2048) >> 4), hi, IDESC_O, (accumulate | kk) != 0);
     };
-    bool ok = mbar_wait(&bars->q_full, 0, abort, 2);
-    ok = __all_sync(0xffffffffu, ok);
-    // blocks (from b0) that have been waited for (keys and values arrive together, and S of a block needs its keys
-    // before P V needs its values: by then nothing is left to wait for), and blocks whose values have been looked at
-    int k_seen = 0, v_seen = 0;
+    // blocks (from b0) whose keys and values this warp has waited for (they arrive together), and blocks whose values
+    // it has looked at
+    int kv_seen = 0, v_seen = 0;
     auto tile_of = [&](int e) { return ntiles == 1 ? 0 : (e < 2 * n0 ? (e & 1) : 1); };
     auto block_of = [&](int e) { return ntiles == 1 ? e : (e < 2 * n0 ? (e >> 1) : e - n0); };
-    auto keys_ready = [&](int i) {  // waits (once) for the keys of every block up to i
-      while (k_seen <= i) {
-        bool got = mbar_wait(&bars->kv_full[k_seen % STAGES], (k_seen / STAGES) & 1, abort, 2);
+    auto block_ready = [&](int i) {  // waits (once) for every block up to i
+      while (kv_seen <= i) {
+        bool got = mbar_wait(&bars->kv_full[kv_seen % STAGES], (kv_seen / STAGES) & 1, abort, 2);
         got = __all_sync(0xffffffffu, got);
         if (!got) return false;
-        ++k_seen;
+        ++kv_seen;
       }
       return true;
     };
-    for (int e = 0; ok && e < NB && e < total; ++e) {
-      ok = keys_ready(block_of(e));
-      if (ok && elect_one()) {
-        issue_s(tile_of(e), block_of(e) % STAGES, e % NB);
-        mma_commit(&bars->s_full[e % NB]);
-      }
-      __syncwarp();
-    }
-    for (int e = 0; ok && e < total; ++e) {
-      const int t = tile_of(e), i = block_of(e);
-      while (ok && v_seen <= i) {
-        ok = keys_ready(v_seen);  // no wait: S of this block has been issued
-        if (!ok) break;
+    auto values_ready = [&](int i) {  // every block up to i: arrived, and the rows behind the request's last key cleared
+      while (v_seen <= i) {
+        if (!block_ready(v_seen)) return false;  // as a rule no wait: S of this block has been issued long ago
         const int written = kvl - (b0 + v_seen) * KB;  // rows of this block that hold the request's values
         if (written < KB) {
           unsigned char* stage = smem + Sh::V_OFF + (v_seen % STAGES) * Sh::KV_STAGE_BYTES;
@@ -310,23 +310,78 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         }
         ++v_seen;
       }
-      const bool ahead = e + NB < total;  // S of the block NB steps on (it takes this block's buffer) goes out together with this P V
-      if (ok && ahead) ok = keys_ready(block_of(e + NB));
-      if (!ok) break;
-      ok = mbar_wait(&bars->p_ready[t], i & 1, abort, 2);  // P of this block is written (over its S)
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      fence_after();
-      if (elect_one()) {
-        issue_pv(t, i % STAGES, e % NB, i);
-        mma_commit(&bars->o_full[t]);
-        if (t == ntiles - 1) mma_commit(&bars->kv_empty[i % STAGES]);  // the last tile to use this block
-        if (ahead) {
-          issue_s(tile_of(e + NB), block_of(e + NB) % STAGES, e % NB);
-          mma_commit(&bars->s_full[e % NB]);
+      return true;
+    };
+    if constexpr (!Sh::TWO_ISSUERS) {
+      if (warp == 1) {  // one warp issues both products, S of event e + NB behind P V of event e
+        bool ok = mbar_wait(&bars->q_full, 0, abort, 2);
+        ok = __all_sync(0xffffffffu, ok);
+        for (int e = 0; ok && e < NB && e < total; ++e) {
+          ok = block_ready(block_of(e));
+          if (ok && elect_one()) {
+            issue_s(tile_of(e), block_of(e) % STAGES, e % NB);
+            mma_commit(&bars->s_full[e % NB]);
+          }
+          __syncwarp();
+        }
+        for (int e = 0; ok && e < total; ++e) {
+          const int t = tile_of(e), i = block_of(e);
+          ok = values_ready(i);
+          const bool ahead = e + NB < total;  // S of the block NB steps on (it takes this block's buffer) goes out together with this P V
+          if (ok && ahead) ok = block_ready(block_of(e + NB));
+          if (!ok) break;
+          ok = mbar_wait(&bars->p_ready[t], i & 1, abort, 2);  // P of this block is written (over its S)
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          fence_after();
+          if (elect_one()) {
+            issue_pv(t, i % STAGES, e % NB, i);
+            mma_commit(&bars->o_full[t]);
+            if (t == ntiles - 1) mma_commit(&bars->kv_empty[i % STAGES]);  // the last tile to use this block
+            if (ahead) {
+              issue_s(tile_of(e + NB), block_of(e + NB) % STAGES, e % NB);
+              mma_commit(&bars->s_full[e % NB]);
+            }
+          }
+          __syncwarp();
         }
       }
-      __syncwarp();
+    } else if (warp == S_WARP) {
+      bool ok = mbar_wait(&bars->q_full, 0, abort, 2);
+      ok = __all_sync(0xffffffffu, ok);
+      for (int e = 0; ok && e < total; ++e) {
+        if (e >= NB) {  // P V of the event that had this buffer has read its P
+          ok = mbar_wait(&bars->p_used[e % NB], ((e / NB) - 1) & 1, abort, 2);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          fence_after();
+        }
+        ok = block_ready(block_of(e));
+        if (!ok) break;
+        if (elect_one()) {
+          issue_s(tile_of(e), block_of(e) % STAGES, e % NB);
+          mma_commit(&bars->s_full[e % NB]);
+        }
+        __syncwarp();
+      }
+    } else {
+      bool ok = true;
+      for (int e = 0; ok && e < total; ++e) {
+        const int t = tile_of(e), i = block_of(e);
+        ok = values_ready(i);
+        if (!ok) break;
+        ok = mbar_wait(&bars->p_ready[t], i & 1, abort, 2);  // P of this block is written (over its S)
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        fence_after();
+        if (elect_one()) {
+          issue_pv(t, i % STAGES, e % NB, i);
+          mma_commit(&bars->o_full[t]);
+          mma_commit(&bars->p_used[e % NB]);
+          if (t == ntiles - 1) mma_commit(&bars->kv_empty[i % STAGES]);  // the last tile to use this block
+        }
+        __syncwarp();
+      }
     }
   } else {
     // ----------------------------------------------------------------------------------------------- softmax
@@ -336,7 +391,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     // (three warps on a scheduler), and arithmetic on register pairs, which wants them aligned, costs more in spills
     // than it saves in instructions; with 64 keys a block there is room and it pays.
     constexpr bool PAIRS = D == 128;
-    const int sw = warp - 2;
+    const int sw = warp - 2;  // 0 .. SOFTMAX_WARPS * TILES - 1
     const int t = sw / SOFTMAX_WARPS;
     const int quarter = warp & 3;  // a warp may only touch tensor-memory lanes [32*(warp%4), +32)
     const int r = quarter * 32 + lane;
