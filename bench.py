@@ -762,6 +762,18 @@ def kernel_costs(base: dict) -> list[tuple[str, float, float]]:
     ]
 
 
+def _no_device(args) -> bool:
+    """Neither arm has a CPU path: without a CUDA device, one line says so instead of a stack of CUDA errors."""
+    import torch
+    if torch.cuda.is_available():
+        return False
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": "no CUDA device on this machine"}))
+    else:
+        print(json.dumps({"error": "no CUDA device on this machine; the engine has no CPU path"}))
+    return True
+
+
 def main() -> int:
     global MODEL, FULL_LAYERS, CONTEXT  # --only decode may be asked for other sizes and contexts
     p = argparse.ArgumentParser()
@@ -819,6 +831,8 @@ def main() -> int:
         if args.impl == "reference":
             print(json.dumps({"impl": "reference", "unavailable": "the reference arm runs the headline workload only"}))
             return 0
+        if _no_device(args):
+            return 1
         args.model = args.model or ("8b" if args.workload == "shared-prefix" else "3b")
         args.layers = None if args.layers == FULL_LAYERS and "--layers" not in sys.argv else args.layers
         result = run_shared_prefix(args) if args.workload == "shared-prefix" else run_mixed(args)
@@ -827,6 +841,8 @@ def main() -> int:
         if args.timeline and (args.impl != "own" or args.only == "all"):
             print(json.dumps({"unsupported": "--timeline/--profile need --only decode or --only prefill of this engine"}))
             return 2
+        if _no_device(args):
+            return 0 if args.impl == "reference" else 1
         result = run_reference(args) if args.impl == "reference" else (run_timeline(args) if args.timeline else run_own(args))
     print(json.dumps(result))
     return 0
