@@ -13,8 +13,11 @@ designed, not its compilation), runs the agents in random interleavings for ever
 """
 
 import random
+from pathlib import Path
 
 import pytest
+
+KERNEL = Path(__file__).resolve().parents[1] / "prefixserve_b200" / "csrc" / "kernels" / "attention_tcgen05.cu"
 
 
 class Barrier:
@@ -251,3 +254,18 @@ def test_the_model_notices_a_protocol_that_is_wrong():
                     next(a)
                 except StopIteration:
                     agents.remove(a)
+
+
+def test_the_model_has_the_kernels_constants():
+    """The shapes modelled above are the ones the kernel is compiled with: buffers by tensor-memory room, one stage more
+    than buffers, two issuing warps and the late wait with 64 keys a block, one warp and the early wait with 128."""
+    text = KERNEL.read_text()
+    for line in ("static constexpr int S_BUFS = (TMEM_COLS - TILES * D) / KB >= 4 ? 4 : 3;",
+                 "static constexpr int STAGES = S_BUFS + 1;",
+                 "static constexpr bool TWO_ISSUERS = KB == 64;",
+                 "constexpr bool WAIT_EARLY = KB == 128;",
+                 "mbar_init(&bars->p_ready[t], SOFTMAX_WARPS);",
+                 "constexpr int SOFTMAX_WARPS = 4;"):
+        assert line in text, f"the kernel no longer says: {line}"
+    tmem, tiles = 512, 2
+    assert [(tmem - tiles * d) // kb >= 4 for d, kb in ((64, 128), (128, 64))] == [False, True]
