@@ -46,3 +46,30 @@ def test_length_classes_of_captured_steps():
     assert ModelRunner._length_classes(1024) == (1024,)
     assert ModelRunner._length_classes(5000) == (1024, 2048, 4096, 5000)
     assert ModelRunner._length_classes(300, 64) == (64, 128, 256, 300)
+
+
+def test_the_few_row_kernels_reduction_covers_every_row_once():
+    """csrc/kernels/gemm_tcgen05_fewrows.cu: after the cluster barrier, CTA `rank` of `ks` adds up the partial sums of rows
+    rank, rank + ks, ... : thread e (0..127) takes row rank + ks * (e >> 5) and every 4 * ks-th after it, four features
+    wide (plain products; a warp a row), or rank + ks * (e >> 4) and every 8 * ks-th with sixteen threads a row (gated).
+    In front of a norm a thread fetches the stream's pieces of its first EARLY rows before the accumulator is complete
+    and picks them by it = (row - rank) / ks / 4.  Restated here: every (row, feature) is taken exactly once, and the
+    early pieces are the ones used."""
+    early = 4
+    for ks in (1, 2, 4, 8):
+        for m in range(1, 65):
+            plain, gated = {}, {}
+            for rank in range(ks):
+                for e in range(128):
+                    rows = list(range(rank + ks * (e >> 5), m, 4 * ks))
+                    for it, t in enumerate(rows):
+                        for f in range((e & 31) * 4, (e & 31) * 4 + 4):
+                            plain[(t, f)] = plain.get((t, f), 0) + 1
+                        assert (t - rank) // ks // 4 == it
+                        if it < early:  # fetched ahead as row rank + ks * ((e >> 5) + 4 * it)
+                            assert rank + ks * ((e >> 5) + 4 * it) == t
+                    for t in range(rank + ks * (e >> 4), m, 8 * ks):
+                        for f in range((e & 15) * 4, (e & 15) * 4 + 4):   # gate features f.., up features 64 + f..
+                            gated[(t, f)] = gated.get((t, f), 0) + 1
+            assert plain == {(t, f): 1 for t in range(m) for f in range(128)}, (ks, m)
+            assert gated == {(t, f): 1 for t in range(m) for f in range(64)}, (ks, m)
